@@ -1,0 +1,141 @@
+/* C ABI of the sm_100a routed-MoE layer (libnetra_sm100.so).
+ *
+ * Two groups of entry points:
+ *
+ * 1. Per-kernel bridges with the names, argument order and return convention of the
+ *    reference's bridges (0 = ok, -1 = see last_error, otherwise a raw runtime error code;
+ *    thread-local last_error string; load() idempotent; launch() does not allocate,
+ *    synchronise or touch module state and is stream-capture safe):
+ *      runtime/gfx950/routing/verify/qwen36_router_bf16_bridge.h:10-21
+ *      runtime/gfx950/routing/decode/qwen36_shared_gate_append_bridge.h:10-23
+ *      runtime/gfx950/fp8/moe/qwen36_moe_silu_mul_quant_bridge.h:14-64
+ *    Differences: hipStream_t -> cudaStream_t; the kernels are linked into the library, so
+ *    load(path) ignores its argument (NULL is accepted) and only performs one-time set-up;
+ *    `rows` may be any positive count (the reference kernels take 1..16).
+ *
+ * 2. The fused layer: router logits -> softmax/top-8/renormalise (+ shared slot) -> stable
+ *    expert sort -> per-token FP8 quantisation -> grouped gate_up with SiLU*up requantising
+ *    epilogue -> grouped down -> slot-ordered weighted combine.  The reference has no single
+ *    entry point for this sequence: it spans the engine launch of
+ *    runtime/gfx950/engine/netra_engine.h:84-86 plus third-party top-k / sort / quantisation
+ *    (SGLang fused_topk, AITER moe_sorting, per_token_group_quant_fp8).  All buffers are
+ *    caller-owned device memory; the library allocates no device memory.
+ */
+#pragma once
+
+#include <cuda_runtime_api.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ reference bridges */
+int netra_qwen36_router_bf16_load(const char* unused_path);
+int netra_qwen36_router_bf16_launch(void* output_logits_bf16, const void* hidden_bf16,
+                                    const void* router_weight_bf16, uint32_t rows, cudaStream_t stream);
+int netra_qwen36_router_bf16_unload(void);
+const char* netra_qwen36_router_bf16_last_error(void);
+
+int netra_qwen36_shared_gate_append_load(const char* unused_path);
+int netra_qwen36_shared_gate_append_launch(void* output_ids_i32, void* output_weights_f32,
+                                           const void* hidden_bf16, const void* shared_gate_weight_bf16,
+                                           const void* routed_ids_i32, const void* routed_weights_f32,
+                                           uint32_t rows, cudaStream_t stream);
+int netra_qwen36_shared_gate_append_unload(void);
+const char* netra_qwen36_shared_gate_append_last_error(void);
+
+int netra_qwen36_moe_gate_up_load(const char* unused_path);
+int netra_qwen36_moe_gate_up_launch(const void* hidden_fp8, const float* hidden_scale_f32,
+                                    const void* w13_fp8, const float* w13_scale_f32,
+                                    const int32_t* topk_ids_i32, float* output_f32, int rows,
+                                    cudaStream_t stream);
+int netra_qwen36_moe_gate_up_unload(void);
+const char* netra_qwen36_moe_gate_up_last_error(void);
+
+int netra_qwen36_moe_silu_mul_quant_load(const char* unused_path);
+int netra_qwen36_moe_silu_mul_quant_launch(const float* input_f32, void* output_fp8,
+                                           float* output_scale_f32, int rows, cudaStream_t stream);
+int netra_qwen36_moe_silu_mul_quant_unload(void);
+const char* netra_qwen36_moe_silu_mul_quant_last_error(void);
+
+int netra_qwen36_moe_down_reduce_load(const char* unused_path);
+int netra_qwen36_moe_down_reduce_launch(const void* activation_fp8, const float* activation_scale_f32,
+                                        const void* w2_fp8, const float* w2_scale_f32,
+                                        const float* topk_weights_f32, const int32_t* topk_ids_i32,
+                                        void* output_bf16, int rows, cudaStream_t stream);
+int netra_qwen36_moe_down_reduce_unload(void);
+const char* netra_qwen36_moe_down_reduce_last_error(void);
+
+/* ------------------------------------------------------------------ fused layer */
+typedef struct netra_moe_layer netra_moe_layer_t;
+
+/* Byte offsets of every intermediate inside the caller-owned workspace for a capacity of
+ * `tokens` rows (P = tokens * 8 routed pairs).  Row spaces: rows [0, P) of a_fp8 / a_scale /
+ * h_fp8 / h_scale / down_f32 are in expert-sorted order, rows [P, P + tokens) are in token
+ * order and belong to the shared expert. */
+typedef struct netra_moe_workspace_layout {
+  uint32_t struct_size;
+  uint32_t tokens;
+  uint64_t total_bytes;
+  uint64_t logits_bf16;   /* [tokens, 256] bf16 */
+  uint64_t topk_ids;      /* [tokens, 9] i32, slot 8 = 256 (shared) */
+  uint64_t topk_weights;  /* [tokens, 9] f32 */
+  uint64_t perm;          /* [P] i32: sorted position -> pair index t*8+slot */
+  uint64_t inv_perm;      /* [P] i32: pair index -> sorted position */
+  uint64_t counts;        /* [256] i32 */
+  uint64_t offsets;       /* [258] i32: exclusive prefix; [256] = P, [257] = P + tokens */
+  uint64_t seg_hist;      /* sort scratch */
+  uint64_t a_fp8;         /* [P + tokens, 2048] e4m3 */
+  uint64_t a_scale;       /* [P + tokens, 16] f32 */
+  uint64_t h_fp8;         /* [P + tokens, 512] e4m3 */
+  uint64_t h_scale;       /* [P + tokens, 4] f32 */
+  uint64_t down_f32;      /* [P + tokens, 2048] f32 */
+  uint64_t status;        /* [4] u32 device status words (0 = ok) */
+} netra_moe_workspace_layout_t;
+
+int netra_moe_workspace_layout_query(uint32_t tokens, netra_moe_workspace_layout_t* output);
+
+typedef struct netra_moe_layer_desc {
+  uint32_t struct_size;
+  uint32_t max_tokens;                /* capacity the workspace was sized for */
+  const void* router_weight_bf16;     /* [256, 2048] */
+  const float* router_bias_f32;       /* [256] or NULL */
+  const void* w13_fp8;                /* [257, 1024, 2048], slab 256 = shared expert */
+  const float* w13_scale_f32;         /* [257, 8, 16] */
+  const void* w2_fp8;                 /* [257, 2048, 512] */
+  const float* w2_scale_f32;          /* [257, 16, 4] */
+  void* workspace;                    /* device, 1024-byte aligned */
+  uint64_t workspace_bytes;
+} netra_moe_layer_desc_t;
+
+/* Control plane (serialised by the caller): encodes the tensor maps of the persistent buffers
+ * and clears the status words.  No device memory is allocated. */
+int netra_moe_layer_create(const netra_moe_layer_desc_t* desc, netra_moe_layer_t** output);
+
+/* Enqueues one layer call on the caller's stream: no allocation, no synchronisation, no host
+ * read-back, so the call may be captured into a CUDA graph.  shared_weight_f32 may be NULL
+ * (the shared expert is then always on with weight 1). */
+int netra_moe_layer_launch(netra_moe_layer_t* layer, const void* hidden_bf16,
+                           const float* shared_weight_f32, void* output_bf16, uint32_t tokens,
+                           cudaStream_t stream);
+
+/* Launches ONE stage of the same sequence (0 router logits, 1 top-k + input quantisation,
+ * 2-4 sort, 5 row gather, 6 grouped gate_up, 7 grouped down, 8 combine), for callers that
+ * migrate one boundary at a time and for per-kernel timing; same rules as the call above.
+ * Counterpart: netra_engine_launch_operation, runtime/gfx950/engine/netra_engine.h:90-92. */
+int netra_moe_layer_launch_stage(netra_moe_layer_t* layer, uint32_t stage, const void* hidden_bf16,
+                                 const float* shared_weight_f32, void* output_bf16, uint32_t tokens,
+                                 cudaStream_t stream);
+
+/* Copies the four device status words to the host (synchronises the device). */
+int netra_moe_layer_status(netra_moe_layer_t* layer, uint32_t status_out[4]);
+/* Kernels launched by one netra_moe_layer_launch call. */
+uint32_t netra_moe_layer_launch_count(const netra_moe_layer_t* layer);
+int netra_moe_layer_destroy(netra_moe_layer_t* layer);
+const char* netra_moe_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif

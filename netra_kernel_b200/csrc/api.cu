@@ -1,0 +1,304 @@
+// Host side of the C ABI declared in include/netra_moe.h: argument checks, tensor-map encoding
+// and kernel launches.  Launch functions do not allocate, synchronise or read back.
+#include <cuda.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <new>
+
+#include "../../include/netra_moe.h"
+#include "common.cuh"
+
+// Single translation unit: the kernels are included so that no relocatable device code is needed.
+#include "bridge_kernels.cu"
+#include "route_kernels.cu"
+#include "umma_kernels.cu"
+
+using namespace netra;
+
+namespace {
+
+thread_local char g_error[512] = "";
+
+int fail(const char* message) {
+  snprintf(g_error, sizeof g_error, "%s", message);
+  return -1;
+}
+int fail_cuda(const char* what, cudaError_t e) {
+  snprintf(g_error, sizeof g_error, "%s: %s", what, cudaGetErrorString(e));
+  return (int)e;
+}
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : fail_cuda(what, e);
+}
+
+uint64_t align_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// 2-D byte tensor [rows, row_bytes], box = 128 bytes x box_rows, 128-byte swizzle.
+int encode_u8_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return fail("cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {row_bytes, rows};
+  cuuint64_t strides[1] = {row_bytes};
+  cuuint32_t box[2] = {128, box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_error, sizeof g_error, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return -1;
+  }
+  return 0;
+}
+
+bool g_umma_ready = false;
+
+int umma_setup() {
+  if (g_umma_ready) return 0;
+  cudaError_t e = cudaFuncSetAttribute(netra_moe_gate_up_umma_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       gate_up_smem_bytes());
+  if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(gate_up)", e);
+  e = cudaFuncSetAttribute(netra_moe_down_umma_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, down_smem_bytes());
+  if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(down)", e);
+  g_umma_ready = true;
+  return 0;
+}
+
+}  // namespace
+
+struct netra_moe_layer {
+  netra_moe_layer_desc_t desc;
+  netra_moe_workspace_layout_t lay;
+  CUtensorMap tm_w13, tm_w2, tm_a32, tm_a64, tm_h32, tm_h64;
+  int sm_count;
+  uint32_t launches;
+};
+
+extern "C" {
+
+// ------------------------------------------------------------------ bridges
+#define NETRA_BRIDGE_COMMON(name)                                       \
+  int name##_load(const char*) { return 0; }                            \
+  int name##_unload(void) { return 0; }                                 \
+  const char* name##_last_error(void) { return g_error; }
+
+NETRA_BRIDGE_COMMON(netra_qwen36_router_bf16)
+NETRA_BRIDGE_COMMON(netra_qwen36_shared_gate_append)
+NETRA_BRIDGE_COMMON(netra_qwen36_moe_gate_up)
+NETRA_BRIDGE_COMMON(netra_qwen36_moe_silu_mul_quant)
+NETRA_BRIDGE_COMMON(netra_qwen36_moe_down_reduce)
+
+int netra_qwen36_router_bf16_launch(void* out, const void* hidden, const void* weight, uint32_t rows, cudaStream_t stream) {
+  if (!out || !hidden || !weight || rows == 0) return fail("router_bf16: null pointer or zero rows");
+  dim3 grid((rows + 3) / 4, 4);
+  netra_router_logits_bf16_sm100<<<grid, 256, 0, stream>>>((uint16_t*)out, (const uint16_t*)hidden, (const uint16_t*)weight, rows);
+  return check_launch("router_bf16 launch");
+}
+
+int netra_qwen36_shared_gate_append_launch(void* out_ids, void* out_w, const void* hidden, const void* gate_w,
+                                           const void* ids, const void* w, uint32_t rows, cudaStream_t stream) {
+  if (!out_ids || !out_w || !hidden || !gate_w || !ids || !w || rows == 0) return fail("shared_gate_append: null pointer or zero rows");
+  netra_qwen36_shared_gate_append_sm100<<<rows, 32, 0, stream>>>((int32_t*)out_ids, (float*)out_w, (const uint16_t*)hidden,
+                                                                 (const uint16_t*)gate_w, (const int32_t*)ids, (const float*)w, rows);
+  return check_launch("shared_gate_append launch");
+}
+
+int netra_qwen36_moe_gate_up_launch(const void* hidden_fp8, const float* hidden_scale, const void* w13, const float* w13_scale,
+                                    const int32_t* topk_ids, float* out, int rows, cudaStream_t stream) {
+  if (!hidden_fp8 || !hidden_scale || !w13 || !w13_scale || !topk_ids || !out || rows <= 0) return fail("gate_up: null pointer or bad rows");
+  dim3 grid(2 * kInter / 64, rows * kSlots);
+  netra_qwen36_moe_gate_up_fp8_sm100<<<grid, 256, 0, stream>>>((const uint8_t*)hidden_fp8, hidden_scale, (const uint8_t*)w13,
+                                                               w13_scale, topk_ids, out, (uint32_t)rows);
+  return check_launch("gate_up launch");
+}
+
+int netra_qwen36_moe_silu_mul_quant_launch(const float* in, void* out_fp8, float* out_scale, int rows, cudaStream_t stream) {
+  if (!in || !out_fp8 || !out_scale || rows <= 0) return fail("silu_mul_quant: null pointer or bad rows");
+  netra_qwen36_moe_silu_mul_quant_fp8_sm100<<<rows, 64, 0, stream>>>(in, (uint8_t*)out_fp8, out_scale, (uint32_t)rows);
+  return check_launch("silu_mul_quant launch");
+}
+
+int netra_qwen36_moe_down_reduce_launch(const void* act_fp8, const float* act_scale, const void* w2, const float* w2_scale,
+                                        const float* topk_w, const int32_t* topk_ids, void* out, int rows, cudaStream_t stream) {
+  if (!act_fp8 || !act_scale || !w2 || !w2_scale || !topk_w || !topk_ids || !out || rows <= 0) return fail("down_reduce: null pointer or bad rows");
+  dim3 grid(kHidden / 64, rows);
+  netra_qwen36_moe_down_reduce_fp8_sm100<<<grid, 256, 0, stream>>>((const uint8_t*)act_fp8, act_scale, (const uint8_t*)w2, w2_scale,
+                                                                   topk_w, topk_ids, (uint16_t*)out, (uint32_t)rows);
+  return check_launch("down_reduce launch");
+}
+
+// ------------------------------------------------------------------ fused layer
+const char* netra_moe_last_error(void) { return g_error; }
+
+int netra_moe_workspace_layout_query(uint32_t tokens, netra_moe_workspace_layout_t* out) {
+  if (out == nullptr || out->struct_size != sizeof(netra_moe_workspace_layout_t)) return fail("workspace_layout: bad struct_size");
+  if (tokens == 0 || tokens > (1u << 20)) return fail("workspace_layout: tokens out of range");
+  const uint64_t t = tokens, p = t * kTopK, rows = p + t;
+  const uint64_t nseg = (p + kSortSegment - 1) / kSortSegment;
+  uint64_t o = 0;
+  auto take = [&](uint64_t bytes) { uint64_t at = o; o = align_up(o + bytes, 1024); return at; };
+  out->tokens = tokens;
+  out->logits_bf16 = take(t * kRouted * 2);
+  out->topk_ids = take(t * kSlots * 4);
+  out->topk_weights = take(t * kSlots * 4);
+  out->perm = take(p * 4);
+  out->inv_perm = take(p * 4);
+  out->counts = take(kRouted * 4);
+  out->offsets = take((kRouted + 2) * 4);
+  out->seg_hist = take(nseg * kRouted * 4);
+  out->a_fp8 = take(rows * kHidden);
+  out->a_scale = take(rows * kHiddenBlocks * 4);
+  out->h_fp8 = take(rows * kInter);
+  out->h_scale = take(rows * kInterBlocks * 4);
+  out->down_f32 = take(rows * kHidden * 4);
+  out->status = take(16);
+  out->total_bytes = o;
+  return 0;
+}
+
+int netra_moe_layer_create(const netra_moe_layer_desc_t* desc, netra_moe_layer_t** output) {
+  if (desc == nullptr || output == nullptr || desc->struct_size != sizeof(netra_moe_layer_desc_t)) return fail("layer_create: bad struct_size");
+  if (!desc->router_weight_bf16 || !desc->w13_fp8 || !desc->w13_scale_f32 || !desc->w2_fp8 || !desc->w2_scale_f32 || !desc->workspace)
+    return fail("layer_create: null pointer");
+  if (((uintptr_t)desc->workspace & 1023) != 0) return fail("layer_create: workspace must be 1024-byte aligned");
+  netra_moe_workspace_layout_t lay;
+  lay.struct_size = sizeof lay;
+  if (int rc = netra_moe_workspace_layout_query(desc->max_tokens, &lay)) return rc;
+  if (desc->workspace_bytes < lay.total_bytes) return fail("layer_create: workspace too small");
+  int device = 0, major = 0, sms = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return fail_cuda("cudaGetDevice", e);
+  cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  if (major != 10) return fail("layer_create: this library targets sm_100a (compute capability 10.x)");
+  if (int rc = umma_setup()) return rc;
+  netra_moe_layer* layer = new (std::nothrow) netra_moe_layer;
+  if (layer == nullptr) return fail("layer_create: out of host memory");
+  layer->desc = *desc;
+  layer->lay = lay;
+  layer->sm_count = sms;
+  layer->launches = 9;  // stages of launch_stage()
+  uint8_t* ws = (uint8_t*)desc->workspace;
+  const uint64_t rows = (uint64_t)desc->max_tokens * (kTopK + 1);
+  int rc = 0;
+  rc = rc ? rc : encode_u8_2d(&layer->tm_w13, desc->w13_fp8, (uint64_t)(kRouted + 1) * 2 * kInter, kHidden, 128);
+  rc = rc ? rc : encode_u8_2d(&layer->tm_w2, desc->w2_fp8, (uint64_t)(kRouted + 1) * kHidden, kInter, 128);
+  rc = rc ? rc : encode_u8_2d(&layer->tm_a32, ws + lay.a_fp8, rows, kHidden, 32);
+  rc = rc ? rc : encode_u8_2d(&layer->tm_a64, ws + lay.a_fp8, rows, kHidden, 64);
+  rc = rc ? rc : encode_u8_2d(&layer->tm_h32, ws + lay.h_fp8, rows, kInter, 32);
+  rc = rc ? rc : encode_u8_2d(&layer->tm_h64, ws + lay.h_fp8, rows, kInter, 64);
+  if (rc == 0) {
+    e = cudaMemset(ws + lay.status, 0, 16);
+    if (e != cudaSuccess) rc = fail_cuda("cudaMemset(status)", e);
+  }
+  if (rc != 0) { delete layer; return rc; }
+  *output = layer;
+  return 0;
+}
+
+uint32_t netra_moe_layer_launch_count(const netra_moe_layer_t* layer) { return layer ? layer->launches : 0; }
+
+}  // extern "C" (reopened below)
+
+namespace {
+constexpr uint32_t kStageCount = 9;
+
+// One launch of the layer's fixed sequence (same idea as the reference's per-operation launch,
+// runtime/gfx950/engine/netra_engine.h:90-92).
+void launch_stage(netra_moe_layer* layer, uint32_t stage, const void* hidden, const float* shared_w, void* out,
+                  uint32_t tokens, cudaStream_t stream) {
+  const netra_moe_workspace_layout_t& L = layer->lay;
+  uint8_t* ws = (uint8_t*)layer->desc.workspace;
+  uint16_t* logits = (uint16_t*)(ws + L.logits_bf16);
+  int32_t* ids9 = (int32_t*)(ws + L.topk_ids);
+  float* w9 = (float*)(ws + L.topk_weights);
+  int32_t* perm = (int32_t*)(ws + L.perm);
+  int32_t* inv_perm = (int32_t*)(ws + L.inv_perm);
+  int32_t* counts = (int32_t*)(ws + L.counts);
+  int32_t* offsets = (int32_t*)(ws + L.offsets);
+  int32_t* seg_hist = (int32_t*)(ws + L.seg_hist);
+  uint8_t* a_fp8 = ws + L.a_fp8;
+  float* a_scale = (float*)(ws + L.a_scale);
+  uint8_t* h_fp8 = ws + L.h_fp8;
+  float* h_scale = (float*)(ws + L.h_scale);
+  float* down = (float*)(ws + L.down_f32);
+  uint32_t* status = (uint32_t*)(ws + L.status);
+  const uint32_t pairs = tokens * kTopK;
+  const uint32_t nseg = (pairs + kSortSegment - 1) / kSortSegment;
+  switch (stage) {
+    case 0:
+      netra_router_logits_bf16_sm100<<<dim3((tokens + 3) / 4, 4), 256, 0, stream>>>(
+          logits, (const uint16_t*)hidden, (const uint16_t*)layer->desc.router_weight_bf16, tokens);
+      break;
+    case 1:
+      netra_moe_topk_quant_sm100<<<(tokens + 3) / 4, 128, 0, stream>>>(
+          ids9, w9, a_fp8, a_scale, logits, layer->desc.router_bias_f32, shared_w, (const uint16_t*)hidden, tokens, pairs);
+      break;
+    case 2: netra_moe_sort_hist_sm100<<<nseg, 256, 0, stream>>>(seg_hist, ids9, tokens); break;
+    case 3: netra_moe_sort_scan_sm100<<<1, 256, 0, stream>>>(seg_hist, counts, offsets, tokens, nseg); break;
+    case 4: netra_moe_sort_scatter_sm100<<<nseg, 256, 0, stream>>>(perm, inv_perm, seg_hist, ids9, tokens); break;
+    case 5: netra_moe_gather_rows_sm100<<<(pairs + 7) / 8, 256, 0, stream>>>(a_fp8, a_scale, perm, tokens); break;
+    case 6:
+      netra_moe_gate_up_umma_sm100<<<layer->sm_count, 192, gate_up_smem_bytes(), stream>>>(
+          layer->tm_w13, layer->tm_a32, layer->tm_a64, a_scale, layer->desc.w13_scale_f32, offsets, h_fp8, h_scale,
+          kRouted + 1, status);
+      break;
+    case 7:
+      netra_moe_down_umma_sm100<<<layer->sm_count, 192, down_smem_bytes(), stream>>>(
+          layer->tm_w2, layer->tm_h32, layer->tm_h64, h_scale, layer->desc.w2_scale_f32, offsets, down, kRouted + 1,
+          status + 1);
+      break;
+    default: netra_moe_combine_sm100<<<tokens, 256, 0, stream>>>((uint16_t*)out, down, w9, inv_perm, tokens); break;
+  }
+}
+}  // namespace
+
+extern "C" {
+
+int netra_moe_layer_launch(netra_moe_layer_t* layer, const void* hidden, const float* shared_w, void* out, uint32_t tokens,
+                           cudaStream_t stream) {
+  if (layer == nullptr || hidden == nullptr || out == nullptr) return fail("layer_launch: null pointer");
+  if (tokens == 0 || tokens > layer->desc.max_tokens) return fail("layer_launch: tokens exceed the bound capacity");
+  for (uint32_t stage = 0; stage < kStageCount; ++stage) launch_stage(layer, stage, hidden, shared_w, out, tokens, stream);
+  return check_launch("layer launch");
+}
+
+int netra_moe_layer_launch_stage(netra_moe_layer_t* layer, uint32_t stage, const void* hidden, const float* shared_w, void* out,
+                                 uint32_t tokens, cudaStream_t stream) {
+  if (layer == nullptr || hidden == nullptr || out == nullptr) return fail("layer_launch_stage: null pointer");
+  if (tokens == 0 || tokens > layer->desc.max_tokens) return fail("layer_launch_stage: tokens exceed the bound capacity");
+  if (stage >= kStageCount) return fail("layer_launch_stage: stage out of range");
+  launch_stage(layer, stage, hidden, shared_w, out, tokens, stream);
+  return check_launch("layer stage launch");
+}
+
+int netra_moe_layer_status(netra_moe_layer_t* layer, uint32_t status_out[4]) {
+  if (layer == nullptr || status_out == nullptr) return fail("layer_status: null pointer");
+  cudaError_t e = cudaMemcpy(status_out, (uint8_t*)layer->desc.workspace + layer->lay.status, 16, cudaMemcpyDeviceToHost);
+  return e == cudaSuccess ? 0 : fail_cuda("cudaMemcpy(status)", e);
+}
+
+int netra_moe_layer_destroy(netra_moe_layer_t* layer) {
+  delete layer;
+  return 0;
+}
+
+}  // extern "C"

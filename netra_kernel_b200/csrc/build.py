@@ -1,0 +1,45 @@
+"""Builds libnetra_sm100.so (kernels + C ABI) for sm_100a with nvcc, in-tree.
+
+Usage: python -m netra_kernel_b200.csrc.build [--verbose]
+"""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+LIB = HERE / "libnetra_sm100.so"
+SOURCES = ["api.cu"]
+DEPENDS = ["api.cu", "common.cuh", "route_kernels.cu", "bridge_kernels.cu", "umma_kernels.cu",
+           "../../include/netra_moe.h"]
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "--shared", "-Xcompiler", "-fPIC", "-Xptxas", "-v", "-ccbin", "g++"]
+
+
+def stale() -> bool:
+    if not LIB.exists():
+        return True
+    built = LIB.stat().st_mtime
+    return any((HERE / d).stat().st_mtime > built for d in DEPENDS)
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    if not force and not stale():
+        return LIB
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    cmd = [nvcc, *NVCC_FLAGS, "-o", str(LIB), *[str(HERE / s) for s in SOURCES], "-lcudart"]
+    proc = subprocess.run(cmd, capture_output=True, text=True, cwd=HERE)
+    log = proc.stdout + proc.stderr
+    (HERE / "build.log").write_text(log)
+    if verbose or proc.returncode != 0:
+        print(log)
+    if proc.returncode != 0:
+        raise RuntimeError("nvcc failed building libnetra_sm100.so (see csrc/build.log)")
+    return LIB
+
+
+if __name__ == "__main__":
+    build(force=True, verbose="--verbose" in sys.argv)
+    print(LIB)

@@ -1,0 +1,200 @@
+"""Host-side mirror of the routed-MoE boundary: torch tensors for device memory and streams,
+every computation through the C ABI (``abi.py``).
+
+``RoutedMoELayer.__call__(hidden)`` plays the role of the reference's serving adapter call
+``apply(layer, hidden, topk_w, topk_ids)`` (``scripts/rocm/integrations/sglang/netra_gfx1151_sglang.py:1297-1311``)
+with routing included; the ``bridge_*`` functions mirror the reference's per-kernel bridges
+(``runtime/gfx950/fp8/moe/qwen36_moe_silu_mul_quant_bridge.h:14-64``).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import abi
+from .synth import HIDDEN, INTER, N_ROUTED, SLOTS, TOPK
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and (not t.is_cuda or not t.is_contiguous()):
+            raise ValueError("operands must be contiguous CUDA tensors")
+
+
+def workspace_layout(tokens: int) -> abi.WorkspaceLayout:
+    lay = abi.WorkspaceLayout()
+    lay.struct_size = ctypes.sizeof(lay)
+    abi.check(abi.load().netra_moe_workspace_layout_query(tokens, ctypes.byref(lay)), "workspace_layout_query")
+    return lay
+
+
+class RoutedMoELayer:
+    """One routed-MoE layer bound to persistent device weights and a private workspace."""
+
+    def __init__(self, router_w: torch.Tensor, w13: torch.Tensor, w13_scale: torch.Tensor,
+                 w2: torch.Tensor, w2_scale: torch.Tensor, max_tokens: int,
+                 router_bias: Optional[torch.Tensor] = None):
+        _require_cuda(router_w, w13, w13_scale, w2, w2_scale, router_bias)
+        if tuple(router_w.shape) != (N_ROUTED, HIDDEN) or router_w.dtype != torch.bfloat16:
+            raise ValueError("router weight must be bf16 [256, 2048]")
+        if tuple(w13.shape) != (N_ROUTED + 1, 2 * INTER, HIDDEN) or tuple(w2.shape) != (N_ROUTED + 1, HIDDEN, INTER):
+            raise ValueError("expert slabs must be [257, 1024, 2048] and [257, 2048, 512] (slab 256 = shared expert)")
+        if tuple(w13_scale.shape) != (N_ROUTED + 1, 8, 16) or tuple(w2_scale.shape) != (N_ROUTED + 1, 16, 4):
+            raise ValueError("block scales must be f32 [257, 8, 16] and [257, 16, 4]")
+        self.lib = abi.load()
+        self.max_tokens = int(max_tokens)
+        self.layout = workspace_layout(self.max_tokens)
+        self._keep = (router_w, w13, w13_scale, w2, w2_scale, router_bias)
+        raw = torch.zeros(self.layout.total_bytes + 1024, dtype=torch.uint8, device=router_w.device)
+        shift = (-raw.data_ptr()) % 1024
+        self.workspace = raw[shift:shift + self.layout.total_bytes]
+        self._raw = raw
+        desc = abi.LayerDesc()
+        desc.struct_size = ctypes.sizeof(desc)
+        desc.max_tokens = self.max_tokens
+        desc.router_weight_bf16 = router_w.data_ptr()
+        desc.router_bias_f32 = _ptr(router_bias)
+        desc.w13_fp8, desc.w13_scale_f32 = w13.data_ptr(), w13_scale.data_ptr()
+        desc.w2_fp8, desc.w2_scale_f32 = w2.data_ptr(), w2_scale.data_ptr()
+        desc.workspace, desc.workspace_bytes = self.workspace.data_ptr(), self.layout.total_bytes
+        handle = ctypes.c_void_p()
+        abi.check(self.lib.netra_moe_layer_create(ctypes.byref(desc), ctypes.byref(handle)), "layer_create")
+        self.handle = handle
+        self.device = router_w.device
+
+    @classmethod
+    def from_operands(cls, ops, max_tokens: Optional[int] = None, device="cuda"):
+        dev = torch.device(device)
+        bias = None if ops.router_bias is None else ops.router_bias.to(dev)
+        return cls(ops.router_w.to(dev), ops.w13.to(dev), ops.w13_scale.to(dev), ops.w2.to(dev),
+                   ops.w2_scale.to(dev), max_tokens or ops.tokens, bias)
+
+    @property
+    def launches_per_call(self) -> int:
+        return int(self.lib.netra_moe_layer_launch_count(self.handle))
+
+    def __call__(self, hidden: torch.Tensor, shared_weight: Optional[torch.Tensor] = None,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        _require_cuda(hidden, shared_weight, out)
+        if hidden.dtype != torch.bfloat16 or hidden.dim() != 2 or hidden.shape[1] != HIDDEN:
+            raise ValueError("hidden must be bf16 [tokens, 2048]")
+        tokens = hidden.shape[0]
+        if out is None:
+            out = torch.empty_like(hidden)
+        abi.check(self.lib.netra_moe_layer_launch(self.handle, hidden.data_ptr(), _ptr(shared_weight),
+                                                  out.data_ptr(), tokens, _stream()), "layer_launch")
+        return out
+
+    STAGES = ("router_logits", "topk_quant", "sort_hist", "sort_scan", "sort_scatter", "gather_rows",
+              "gate_up", "down", "combine")
+
+    def launch_stage(self, stage: int, hidden: torch.Tensor, out: torch.Tensor,
+                     shared_weight: Optional[torch.Tensor] = None) -> None:
+        """Launch one stage of the layer sequence on the current stream."""
+        abi.check(self.lib.netra_moe_layer_launch_stage(self.handle, stage, hidden.data_ptr(), _ptr(shared_weight),
+                                                        out.data_ptr(), hidden.shape[0], _stream()), "layer_launch_stage")
+
+    def status(self):
+        words = (ctypes.c_uint32 * 4)()
+        abi.check(self.lib.netra_moe_layer_status(self.handle, ctypes.byref(words)), "layer_status")
+        return list(words)
+
+    def check_status(self) -> None:
+        words = self.status()
+        if any(words):
+            raise abi.NetraError(f"device status words {words}: a bounded wait expired inside a grouped GEMM")
+
+    def intermediates(self, tokens: int) -> dict:
+        """Views of the workspace tensors written by the last call with ``tokens`` rows."""
+        lay, ws = self.layout, self.workspace
+        pairs, rows = tokens * TOPK, tokens * SLOTS
+
+        def view(offset, count, dtype):
+            nbytes = count * torch.empty((), dtype=dtype).element_size()
+            return ws[offset:offset + nbytes].view(dtype)
+
+        return {
+            "logits": view(lay.logits_bf16, tokens * N_ROUTED, torch.bfloat16).view(tokens, N_ROUTED),
+            "topk_ids": view(lay.topk_ids, tokens * SLOTS, torch.int32).view(tokens, SLOTS),
+            "topk_w": view(lay.topk_weights, tokens * SLOTS, torch.float32).view(tokens, SLOTS),
+            "perm": view(lay.perm, pairs, torch.int32),
+            "inv_perm": view(lay.inv_perm, pairs, torch.int32),
+            "counts": view(lay.counts, N_ROUTED, torch.int32),
+            "offsets": view(lay.offsets, N_ROUTED + 2, torch.int32),
+            "a_fp8": view(lay.a_fp8, rows * HIDDEN, torch.uint8).view(rows, HIDDEN),
+            "a_scale": view(lay.a_scale, rows * 16, torch.float32).view(rows, 16),
+            "h_fp8": view(lay.h_fp8, rows * INTER, torch.uint8).view(rows, INTER),
+            "h_scale": view(lay.h_scale, rows * 4, torch.float32).view(rows, 4),
+            "down": view(lay.down_f32, rows * HIDDEN, torch.float32).view(rows, HIDDEN),
+        }
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            self.lib.netra_moe_layer_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+# ----------------------------------------------------------------------------- per-kernel bridges
+def bridge_router_bf16(hidden: torch.Tensor, router_w: torch.Tensor) -> torch.Tensor:
+    _require_cuda(hidden, router_w)
+    out = torch.empty(hidden.shape[0], N_ROUTED, dtype=torch.bfloat16, device=hidden.device)
+    abi.check(abi.load().netra_qwen36_router_bf16_launch(out.data_ptr(), hidden.data_ptr(), router_w.data_ptr(),
+                                                         hidden.shape[0], _stream()), "router_bf16_launch")
+    return out
+
+
+def bridge_shared_gate_append(hidden, gate_w, ids8, w8):
+    _require_cuda(hidden, gate_w, ids8, w8)
+    rows = hidden.shape[0]
+    ids9 = torch.empty(rows, SLOTS, dtype=torch.int32, device=hidden.device)
+    w9 = torch.empty(rows, SLOTS, dtype=torch.float32, device=hidden.device)
+    abi.check(abi.load().netra_qwen36_shared_gate_append_launch(
+        ids9.data_ptr(), w9.data_ptr(), hidden.data_ptr(), gate_w.data_ptr(), ids8.data_ptr(), w8.data_ptr(),
+        rows, _stream()), "shared_gate_append_launch")
+    return ids9, w9
+
+
+def bridge_gate_up(hidden_fp8, hidden_scale, w13, w13_scale, topk_ids9) -> torch.Tensor:
+    _require_cuda(hidden_fp8, hidden_scale, w13, w13_scale, topk_ids9)
+    rows = hidden_fp8.shape[0]
+    out = torch.empty(rows * SLOTS, 2 * INTER, dtype=torch.float32, device=hidden_fp8.device)
+    abi.check(abi.load().netra_qwen36_moe_gate_up_launch(
+        hidden_fp8.data_ptr(), hidden_scale.data_ptr(), w13.data_ptr(), w13_scale.data_ptr(),
+        topk_ids9.data_ptr(), out.data_ptr(), rows, _stream()), "gate_up_launch")
+    return out
+
+
+def bridge_silu_mul_quant(gate_up_f32: torch.Tensor):
+    _require_cuda(gate_up_f32)
+    rows = gate_up_f32.shape[0]
+    q = torch.empty(rows, INTER, dtype=torch.uint8, device=gate_up_f32.device)
+    s = torch.empty(rows, INTER // 128, dtype=torch.float32, device=gate_up_f32.device)
+    abi.check(abi.load().netra_qwen36_moe_silu_mul_quant_launch(
+        gate_up_f32.data_ptr(), q.data_ptr(), s.data_ptr(), rows, _stream()), "silu_mul_quant_launch")
+    return q, s
+
+
+def bridge_down_reduce(act_fp8, act_scale, w2, w2_scale, topk_w9, topk_ids9) -> torch.Tensor:
+    _require_cuda(act_fp8, act_scale, w2, w2_scale, topk_w9, topk_ids9)
+    rows = topk_ids9.shape[0]
+    out = torch.empty(rows, HIDDEN, dtype=torch.bfloat16, device=act_fp8.device)
+    abi.check(abi.load().netra_qwen36_moe_down_reduce_launch(
+        act_fp8.data_ptr(), act_scale.data_ptr(), w2.data_ptr(), w2_scale.data_ptr(), topk_w9.data_ptr(),
+        topk_ids9.data_ptr(), out.data_ptr(), rows, _stream()), "down_reduce_launch")
+    return out

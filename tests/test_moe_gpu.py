@@ -1,0 +1,235 @@
+"""GPU parity tests: the sm_100a path through the C ABI against the CPU checker on identical
+seeded operands.  Integer results (logits bits, ids, permutation, counts, offsets, input FP8
+codes) must be bit-exact; the BF16 output must be within max-abs 2e-2 and relative-L2 5e-3."""
+import numpy as np
+import pytest
+import torch
+
+from netra_kernel_b200 import synth
+from oracle import moe_ref as R
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def gpu_weights(expert_weights):
+    return tuple(t.cuda() for t in expert_weights)
+
+
+def make_layer(gpu_weights, router_w, max_tokens, bias=None):
+    from netra_kernel_b200.moe import RoutedMoELayer
+    w13, w13_s, w2, w2_s = gpu_weights
+    return RoutedMoELayer(router_w.cuda(), w13, w13_s, w2, w2_s, max_tokens,
+                          None if bias is None else bias.cuda())
+
+
+def run_layer(layer, hidden, shared_w=None):
+    sw = None if shared_w is None else torch.from_numpy(shared_w).cuda()
+    out = layer(hidden.cuda(), sw)
+    torch.cuda.synchronize()
+    layer.check_status()
+    inter = {k: v.cpu() for k, v in layer.intermediates(hidden.shape[0]).items()}
+    return out.cpu(), inter
+
+
+def check_against(ref, out, inter, tokens, *, subset=None):
+    pairs = tokens * 8
+    assert np.array_equal(helpers.bits(inter["logits"]), ref["logits"]), "router logits must be bit-exact"
+    assert np.array_equal(inter["topk_ids"].numpy(), ref["topk_ids"]), "top-k ids must be bit-exact"
+    assert np.array_equal(inter["perm"].numpy(), ref["perm"]), "permutation must be bit-exact"
+    assert np.array_equal(inter["counts"].numpy(), ref["counts"])
+    assert np.array_equal(inter["offsets"].numpy()[:257], ref["offsets"][:257])
+    assert inter["offsets"][257].item() == pairs + tokens
+    inv = inter["inv_perm"].numpy()
+    assert np.array_equal(inv[ref["perm"]], np.arange(pairs))
+    np.testing.assert_allclose(inter["topk_w"].numpy(), ref["topk_w"], rtol=2e-6, atol=1e-7)
+    # input quantisation: rows [pairs, pairs+tokens) are token order, rows [0, pairs) the gather
+    a = inter["a_fp8"].numpy()
+    assert np.array_equal(a[pairs:], ref["a_fp8"]), "input FP8 codes must be bit-exact"
+    assert np.array_equal(inter["a_scale"].numpy()[pairs:], ref["a_scale"])
+    assert np.array_equal(a[:pairs], ref["a_fp8"][ref["perm"] // 8])
+    toks = np.arange(tokens) if subset is None else np.asarray(subset)
+    # intermediate FP8 codes: slot order in the checker, sorted rows on the GPU
+    h = inter["h_fp8"].numpy()
+    pos = np.concatenate([inv.reshape(tokens, 8), (pairs + np.arange(tokens))[:, None]], axis=1)[toks]
+    got_h = h[pos]
+    mism = (got_h != ref["h_fp8"]).mean()
+    assert mism < 2e-3, f"intermediate FP8 code mismatch fraction {mism}"
+    m = R.parity_metrics(helpers.bits(out)[toks], ref["out"])
+    assert m["max_abs"] <= helpers.MAX_ABS and m["rel_l2"] <= helpers.REL_L2, m
+    return m
+
+
+def test_layer_t16_matches_golden_fixture(gpu_weights):
+    data = dict(np.load(helpers.GOLDEN / "moe_layer_t16.npz"))
+    hidden, router_w, _ = synth.make_activations(16)
+    layer = make_layer(gpu_weights, router_w, 16)
+    assert layer.launches_per_call == 9
+    out, inter = run_layer(layer, hidden)
+    m = check_against(data, out, inter, 16)
+    assert m["rel_l2"] < 1e-3
+
+
+def test_layer_t256_decode_matches_c_checker(gpu_weights, expert_weights, c_oracle):
+    hidden, router_w, _ = synth.make_activations(256)
+    ref = helpers.c_layer(c_oracle, helpers.bits(hidden), helpers.bits(router_w), *helpers.np_weights(expert_weights))
+    layer = make_layer(gpu_weights, router_w, 256)
+    out, inter = run_layer(layer, hidden)
+    check_against(ref, out, inter, 256)
+    assert int((ref["counts"] > 0).sum()) == 256      # every expert is hit at T=256
+
+
+@pytest.mark.parametrize("tokens", [1, 7, 129])
+def test_ragged_token_counts(gpu_weights, expert_weights, c_oracle, tokens):
+    hidden, router_w, _ = synth.make_activations(tokens, seed=20 + tokens)
+    shared_w = np.linspace(0.25, 1.0, tokens).astype(np.float32)
+    ref = helpers.c_layer(c_oracle, helpers.bits(hidden), helpers.bits(router_w), *helpers.np_weights(expert_weights),
+                          shared_w=shared_w)
+    layer = make_layer(gpu_weights, router_w, 256)        # capacity above the call size
+    out, inter = run_layer(layer, hidden, shared_w)
+    check_against(ref, out, inter, tokens)
+
+
+def test_skewed_routing_with_empty_and_overfull_experts(gpu_weights, expert_weights):
+    """Strong Zipf bias: most experts empty, the hottest far above 64 rows (several work items)."""
+    tokens = 1024
+    hidden, router_w, _ = synth.make_activations(tokens, seed=5)
+    bias = synth.zipf_bias(3.0)
+    subset = np.arange(0, tokens, 37)
+    ref = R.moe_layer(helpers.bits(hidden), helpers.bits(router_w), *helpers.np_weights(expert_weights),
+                      bias=bias.numpy(), token_subset=subset)
+    assert (ref["counts"] == 0).sum() > 50 and ref["counts"].max() > 512
+    layer = make_layer(gpu_weights, router_w, tokens, bias)
+    out, inter = run_layer(layer, hidden)
+    check_against(ref, out, inter, tokens, subset=subset)
+
+
+def test_prefill_t8192_zipf_sampled_tokens(gpu_weights, expert_weights):
+    tokens = 8192
+    hidden, router_w, bias = synth.make_activations(tokens, synth.ZIPF_ALPHA_T8192)
+    subset = np.arange(5, tokens, 257)
+    ref = R.moe_layer(helpers.bits(hidden), helpers.bits(router_w), *helpers.np_weights(expert_weights),
+                      bias=bias.numpy(), token_subset=subset)
+    layer = make_layer(gpu_weights, router_w, tokens, bias)
+    out, inter = run_layer(layer, hidden)
+    check_against(ref, out, inter, tokens, subset=subset)
+    # size-independent properties at full size: permutation is a bijection, expert-major, stable
+    perm = inter["perm"].numpy()
+    flat = inter["topk_ids"].numpy()[:, :8].reshape(-1)
+    assert np.array_equal(np.sort(perm), np.arange(tokens * 8))
+    keys = flat[perm].astype(np.int64) * (tokens * 8) + perm
+    assert np.all(np.diff(keys) > 0)
+    assert np.array_equal(np.bincount(flat, minlength=256), inter["counts"].numpy())
+
+
+def test_bridge_kernels_against_checker(gpu_weights, expert_weights):
+    """The three-launch slot-order boundary of the reference's decode bridges."""
+    from netra_kernel_b200 import moe
+    tokens = 16
+    data = dict(np.load(helpers.GOLDEN / "moe_layer_t16.npz"))
+    hidden, router_w, _ = synth.make_activations(tokens)
+    w13, w13_s, w2, w2_s = gpu_weights
+    logits = moe.bridge_router_bf16(hidden.cuda(), router_w.cuda())
+    assert np.array_equal(helpers.bits(logits), data["logits"])
+    a_fp8 = torch.from_numpy(data["a_fp8"]).cuda()
+    a_scale = torch.from_numpy(data["a_scale"]).cuda()
+    ids9 = torch.from_numpy(data["topk_ids"]).cuda()
+    w9 = torch.from_numpy(data["topk_w"]).cuda()
+    gu = moe.bridge_gate_up(a_fp8, a_scale, w13, w13_s, ids9)
+    cw13, cw13_s, cw2, cw2_s = helpers.np_weights(expert_weights)
+    want = np.stack([R.blockscale_matmul(data["a_fp8"][t:t + 1], data["a_scale"][t:t + 1], cw13[e], cw13_s[e])[0]
+                     for t in range(tokens) for e in data["topk_ids"][t]])
+    np.testing.assert_allclose(gu.cpu().numpy(), want, rtol=1e-4, atol=2e-5)
+    # SiLU*up + requant on the SAME FP32 input: codes and scales as the checker computes them
+    q, s = moe.bridge_silu_mul_quant(gu)
+    want_q, want_s, _ = R.silu_mul_quant(gu.cpu().numpy())
+    assert (q.cpu().numpy() != want_q).mean() < 5e-4
+    np.testing.assert_allclose(s.cpu().numpy(), want_s, rtol=1e-6)
+    out = moe.bridge_down_reduce(q, s, w2, w2_s, w9, ids9)
+    torch.cuda.synchronize()
+    m = R.parity_metrics(helpers.bits(out), data["out"])
+    assert m["max_abs"] <= helpers.MAX_ABS and m["rel_l2"] <= helpers.REL_L2, m
+
+
+def test_shared_gate_append_bridge():
+    from netra_kernel_b200 import moe
+    g = torch.Generator().manual_seed(9)
+    hidden = torch.randn(5, 2048, generator=g).to(torch.bfloat16)
+    gate_w = (0.02 * torch.randn(2048, generator=g)).to(torch.bfloat16)
+    ids8 = torch.randint(0, 256, (5, 8), generator=g, dtype=torch.int32)
+    w8 = torch.rand(5, 8, generator=g)
+    ids9, w9 = moe.bridge_shared_gate_append(hidden.cuda(), gate_w.cuda(), ids8.cuda(), w8.cuda())
+    assert torch.equal(ids9[:, :8].cpu(), ids8) and torch.equal(w9[:, :8].cpu(), w8)
+    assert ids9[:, 8].cpu().tolist() == [256] * 5
+    logit = (hidden.double() @ gate_w.double()).float().to(torch.bfloat16).float()
+    want = torch.sigmoid(logit).to(torch.bfloat16).float()
+    assert torch.allclose(w9[:, 8].cpu(), want, atol=8e-3)
+
+
+def test_grouped_tensor_core_path_agrees_with_bridge_path(gpu_weights):
+    """Independent GPU cross-check at a size the CPU checker does not cover in full."""
+    from netra_kernel_b200 import moe
+    tokens = 512
+    hidden, router_w, bias = synth.make_activations(tokens, 1.0, seed=3)
+    layer = make_layer(gpu_weights, router_w, tokens, bias)
+    out, inter = run_layer(layer, hidden)
+    w13, w13_s, w2, w2_s = gpu_weights
+    pairs = tokens * 8
+    a_fp8 = inter["a_fp8"][pairs:].cuda()
+    a_scale = inter["a_scale"][pairs:].cuda()
+    ids9, w9 = inter["topk_ids"].cuda(), inter["topk_w"].cuda()
+    q, s = moe.bridge_silu_mul_quant(moe.bridge_gate_up(a_fp8, a_scale, w13, w13_s, ids9))
+    ref = moe.bridge_down_reduce(q, s, w2, w2_s, w9, ids9)
+    torch.cuda.synchronize()
+    m = R.parity_metrics(helpers.bits(out), helpers.bits(ref))
+    assert m["max_abs"] <= helpers.MAX_ABS and m["rel_l2"] <= 1e-3, m
+
+
+def test_repeat_launch_and_graph_replay_are_bitwise_identical(gpu_weights):
+    tokens = 256
+    hidden, router_w, _ = synth.make_activations(tokens)
+    layer = make_layer(gpu_weights, router_w, tokens)
+    h = hidden.cuda()
+    first = layer(h).clone()
+    for _ in range(5):
+        assert torch.equal(layer(h), first)
+    stream = torch.cuda.Stream()
+    static_out = torch.empty_like(h)
+    with torch.cuda.stream(stream):
+        layer(h, out=static_out)
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            layer(h, out=static_out)
+    for _ in range(20):
+        static_out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(static_out, first)
+    layer.check_status()
+
+
+def test_outputs_stay_inside_their_buffers(gpu_weights):
+    """Guard words around the output catch out-of-bounds stores (no sanitizer on this pool)."""
+    tokens = 33
+    hidden, router_w, _ = synth.make_activations(tokens, seed=8)
+    layer = make_layer(gpu_weights, router_w, 64)
+    guard = 4096
+    buf = torch.full((guard + tokens * 2048 + guard,), -7.0, dtype=torch.bfloat16, device="cuda")
+    out = buf[guard:guard + tokens * 2048].view(tokens, 2048)
+    layer(hidden.cuda(), out=out)
+    torch.cuda.synchronize()
+    layer.check_status()
+    assert torch.all(buf[:guard] == -7.0) and torch.all(buf[-guard:] == -7.0)
+    assert torch.isfinite(out.float()).all()
+
+
+def test_argument_errors_are_reported(gpu_weights):
+    from netra_kernel_b200 import abi
+    hidden, router_w, _ = synth.make_activations(8)
+    layer = make_layer(gpu_weights, router_w, 8)
+    with pytest.raises(abi.NetraError, match="capacity"):
+        layer(torch.zeros(9, 2048, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(ValueError):
+        layer(torch.zeros(8, 1024, dtype=torch.bfloat16, device="cuda"))
