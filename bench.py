@@ -213,6 +213,16 @@ def run_ours(args) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    if args.profile_only:
+        # plain launches only, for a profiler: no graph, no soak loop, no CPU baseline
+        with torch.cuda.stream(stream):
+            for _ in range(args.profile_only):
+                layer(hidden, out=out)
+            stream.synchronize()
+        layer.check_status()
+        print(json.dumps({"profile_only": args.profile_only, "tokens": tokens, "launches": args.profile_only * layer.launches_per_call}))
+        return
+
     uuid = str(torch.cuda.get_device_properties(dev).uuid)
     uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
     with torch.cuda.stream(stream), ClockSampler(uuid) as clocks:
@@ -334,6 +344,8 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=256)
     ap.add_argument("--zipf-alpha", type=float, default=0.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-only", type=int, default=0, metavar="CALLS",
+                    help="run CALLS plain layer calls and exit (the command captured under ncu)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
