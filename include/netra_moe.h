@@ -136,6 +136,19 @@ uint32_t netra_moe_layer_launch_count(const netra_moe_layer_t* layer);
 int netra_moe_layer_destroy(netra_moe_layer_t* layer);
 const char* netra_moe_last_error(void);
 
+/* No counterpart in the reference.  Stable expert-major sort of the rows*8 routed pairs for
+ * callers that cannot allocate device memory (a process whose memory belongs to one framework
+ * allocator, a plugin barred from driver allocations after start-up, a step inside stream
+ * capture): the scratch table lives in a fixed 128 KiB device array inside the library, so only
+ * inputs and outputs are passed.  topk_ids_i32 is [rows, 9] (slot 8 ignored); outputs are
+ * perm [rows*8], inv_perm [rows*8], counts [256], offsets [258], identical to the fused layer's.
+ * rows must be 1..16384 (larger is refused).  The first call on a device resolves the array's
+ * address and should be made outside stream capture.  All calls on a device share the array:
+ * calls that overlap on the GPU race and must be serialised by the caller. */
+int netra_moe_sort_static_scratch_launch(const int32_t* topk_ids_i32, int32_t* perm_i32,
+                                         int32_t* inv_perm_i32, int32_t* counts_i32,
+                                         int32_t* offsets_i32, uint32_t rows, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -46,6 +46,7 @@ SIGNATURES = {
     "netra_moe_layer_launch_count": (c_u32, [c_void_p]),
     "netra_moe_layer_destroy": (c_int, [c_void_p]),
     "netra_moe_last_error": (ctypes.c_char_p, []),
+    "netra_moe_sort_static_scratch_launch": (c_int, [c_void_p] * 5 + [c_u32, c_void_p]),
 }
 for _b in BRIDGES:
     SIGNATURES[_b + "_load"] = (c_int, [ctypes.c_char_p])

@@ -302,3 +302,6 @@ int netra_moe_layer_destroy(netra_moe_layer_t* layer) {
 }
 
 }  // extern "C"
+
+// Entry point with library-owned scratch (needs fail(), fail_cuda(), check_launch() from above).
+#include "static_scratch_sort.cu"

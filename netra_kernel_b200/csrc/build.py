@@ -12,7 +12,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 LIB = HERE / "libnetra_sm100.so"
 SOURCES = ["api.cu"]
-DEPENDS = ["api.cu", "common.cuh", "route_kernels.cu", "bridge_kernels.cu", "umma_kernels.cu",
+DEPENDS = ["api.cu", "common.cuh", "route_kernels.cu", "bridge_kernels.cu", "umma_kernels.cu", "static_scratch_sort.cu",
            "../../include/netra_moe.h"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--shared", "-Xcompiler", "-fPIC", "-Xptxas", "-v", "-ccbin", "g++"]

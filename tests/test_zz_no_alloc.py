@@ -1,0 +1,77 @@
+"""GPU test of the entry point that owns its scratch memory (collected last on purpose).
+
+`netra_moe_sort_static_scratch_launch` exists for callers that must not allocate device memory
+(their memory belongs to a framework allocator, or allocation is barred after start-up or
+during stream capture): its histogram table is a fixed array inside the library.  The test
+drives it through the C ABI on two calls in a row - the second larger and differently routed,
+so anything left in the shared table by the first call would show - and requires results
+identical to the regular sort stages of the fused layer, which use caller-provided scratch."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from netra_kernel_b200 import abi, synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _regular_sort(layer, hidden):
+    out = torch.empty_like(hidden)
+    for stage in range(5):                      # router logits, top-k, sort_hist, sort_scan, sort_scatter
+        layer.launch_stage(stage, hidden, out)
+    torch.cuda.synchronize()
+    inter = layer.intermediates(hidden.shape[0])
+    return {k: inter[k].clone() for k in ("topk_ids", "perm", "inv_perm", "counts", "offsets")}
+
+
+def _static_sort(ids9: torch.Tensor):
+    rows = ids9.shape[0]
+    dev = ids9.device
+    perm = torch.full((rows * 8,), -1, dtype=torch.int32, device=dev)
+    inv_perm = torch.full((rows * 8,), -1, dtype=torch.int32, device=dev)
+    counts = torch.full((256,), -1, dtype=torch.int32, device=dev)
+    offsets = torch.full((258,), -1, dtype=torch.int32, device=dev)
+    rc = abi.load().netra_moe_sort_static_scratch_launch(
+        ids9.data_ptr(), perm.data_ptr(), inv_perm.data_ptr(), counts.data_ptr(), offsets.data_ptr(),
+        rows, torch.cuda.current_stream().cuda_stream)
+    abi.check(rc, "sort_static_scratch_launch")
+    torch.cuda.synchronize()
+    return {"perm": perm, "inv_perm": inv_perm, "counts": counts, "offsets": offsets}
+
+
+def test_static_scratch_sort_matches_regular_sort_on_consecutive_calls():
+    from netra_kernel_b200.moe import RoutedMoELayer
+    dev = torch.device("cuda", 0)
+    # the sort stages never read expert weights: zero slabs of the right shape are enough
+    w13 = torch.zeros(257, 1024, 2048, dtype=torch.uint8, device=dev)
+    w2 = torch.zeros(257, 2048, 512, dtype=torch.uint8, device=dev)
+    w13_s = torch.ones(257, 8, 16, device=dev)
+    w2_s = torch.ones(257, 16, 4, device=dev)
+    cases = [(256, None, 0), (1000, 1.2, 3)]    # (tokens, Zipf bias strength, hidden seed)
+    for tokens, alpha, seed in cases:
+        hidden, router_w, bias = synth.make_activations(tokens, alpha, seed=seed)
+        layer = RoutedMoELayer(router_w.to(dev), w13, w13_s, w2, w2_s, tokens,
+                               None if bias is None else bias.to(dev))
+        want = _regular_sort(layer, hidden.to(dev))
+        got = _static_sort(want["topk_ids"])
+        for key in ("perm", "inv_perm", "counts", "offsets"):
+            assert torch.equal(got[key], want[key]), (tokens, key)
+        # and the result is a stable expert-major order in its own right
+        flat = want["topk_ids"][:, :8].reshape(-1).cpu().numpy().astype(np.int64)
+        perm = got["perm"].cpu().numpy()
+        assert np.all(np.diff(flat[perm] * (tokens * 8) + perm) > 0)
+        layer.close()
+
+
+def test_static_scratch_sort_refuses_sizes_beyond_its_table():
+    lib = abi.load()
+    ids = torch.zeros(8, 9, dtype=torch.int32, device="cuda")
+    buf = torch.zeros(300, dtype=torch.int32, device="cuda")
+    rc = lib.netra_moe_sort_static_scratch_launch(ids.data_ptr(), buf.data_ptr(), buf.data_ptr(), buf.data_ptr(),
+                                                  buf.data_ptr(), 16385, None)
+    assert rc == -1 and b"16384" in lib.netra_moe_last_error()
+    rc = lib.netra_moe_sort_static_scratch_launch(None, buf.data_ptr(), buf.data_ptr(), buf.data_ptr(),
+                                                  buf.data_ptr(), 8, None)
+    assert rc == -1
