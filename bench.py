@@ -196,7 +196,9 @@ def run_ours(args) -> None:
     weights = synth.make_expert_weights(0)
     hidden_cpu, router_w, bias = synth.make_activations(tokens, args.zipf_alpha or None, seed=rank)
     w13, w13_s, w2, w2_s = (t.to(dev) for t in weights)
-    layer = RoutedMoELayer(router_w.to(dev), w13, w13_s, w2, w2_s, tokens, None if bias is None else bias.to(dev))
+    layer = RoutedMoELayer(router_w.to(dev), w13, w13_s, w2, w2_s, tokens, None if bias is None else bias.to(dev),
+                           tiled=not args.row_major_weights)
+    del w13, w2
     hidden = hidden_cpu.to(dev)
     out = torch.empty_like(hidden)
     stream = torch.cuda.Stream(device=dev)
@@ -220,7 +222,7 @@ def run_ours(args) -> None:
                 layer(hidden, out=out)
             stream.synchronize()
         layer.check_status()
-        print(json.dumps({"profile_only": args.profile_only, "tokens": tokens, "launches": args.profile_only * layer.launches_per_call}))
+        print(json.dumps({"profile_only": args.profile_only, "tokens": tokens, "launches": args.profile_only * layer.launches_per_call(tokens)}))
         return
 
     uuid = str(torch.cuda.get_device_properties(dev).uuid)
@@ -311,8 +313,9 @@ def run_ours(args) -> None:
                    "parallelism": "single GPU" if world == 1 else f"{world} independent replicas (no collective)",
                    "zipf_alpha": args.zipf_alpha or 0.0,
                    "l2": "inputs larger than L2: every step streams %.1f MB of expert weights (L2 is 126 MB)" % (layer_bytes / 1e6),
-                   "launch": "CUDA graph replay of the layer's 9 kernels"},
-        "gpu_launches": steps * layer.launches_per_call,
+                   "weights": "row-major slabs" if args.row_major_weights else "tile order (repacked once at load)",
+                   "launch": "CUDA graph replay of the layer's %d kernels" % layer.launches_per_call(tokens)},
+        "gpu_launches": steps * layer.launches_per_call(tokens),
         "e2e": {"value": world * tokens / (e2e_ms / 1e3), "unit": UNIT, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": tokens * 2048 * 2, "d2h_bytes_per_step": tokens * 2048 * 2},
         "roofline": {"bound": "hbm", "kernel": "netra_moe_gate_up_umma_sm100", "achieved": achieved, "peak": peak,
@@ -344,6 +347,8 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=256)
     ap.add_argument("--zipf-alpha", type=float, default=0.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--row-major-weights", action="store_true",
+                    help="stream the checkpoint's row-major slabs instead of the repacked tile order")
     ap.add_argument("--profile-only", type=int, default=0, metavar="CALLS",
                     help="run CALLS plain layer calls and exit (the command captured under ncu)")
     args = ap.parse_args()

@@ -108,7 +108,19 @@ typedef struct netra_moe_layer_desc {
   const float* w2_scale_f32;          /* [257, 16, 4] */
   void* workspace;                    /* device, 1024-byte aligned */
   uint64_t workspace_bytes;
+  uint32_t weights_tiled;             /* 0: w13/w2 are the row-major slabs above; 1: they were rewritten by
+                                         netra_moe_repack_tiles_launch (same bytes, tile order) */
+  uint32_t reserved;                  /* must be 0 */
 } netra_moe_layer_desc_t;
+
+/* Load-time weight layout step (the role of the reference's repack plan,
+ * compiler/netra_compiler/layouts.py:109-164): rewrites row-major byte rows [total_rows, k_bytes]
+ * into consecutive tiles of 128 rows x 128 bytes ordered (row tile, K-block), so that every TMA
+ * box of the grouped GEMMs is one contiguous 16 KiB read.  dst and src must not alias; total_rows
+ * and k_bytes are multiples of 128.  Call once per weight tensor: (257*1024, 2048) for W13 and
+ * (257*2048, 512) for W2.  Scales are not touched. */
+int netra_moe_repack_tiles_launch(void* dst, const void* src, uint64_t total_rows, uint32_t k_bytes,
+                                  cudaStream_t stream);
 
 /* Control plane (serialised by the caller): encodes the tensor maps of the persistent buffers
  * and clears the status words.  No device memory is allocated. */
@@ -122,7 +134,7 @@ int netra_moe_layer_launch(netra_moe_layer_t* layer, const void* hidden_bf16,
                            cudaStream_t stream);
 
 /* Launches ONE stage of the same sequence (0 router logits, 1 top-k + input quantisation,
- * 2-4 sort, 5 row gather, 6 grouped gate_up, 7 grouped down, 8 combine), for callers that
+ * 2-4 sort (stage 2 alone sorts up to 1024 rows; 3 and 4 then launch nothing), 5 row gather, 6 grouped gate_up, 7 grouped down, 8 combine), for callers that
  * migrate one boundary at a time and for per-kernel timing; same rules as the call above.
  * Counterpart: netra_engine_launch_operation, runtime/gfx950/engine/netra_engine.h:90-92. */
 int netra_moe_layer_launch_stage(netra_moe_layer_t* layer, uint32_t stage, const void* hidden_bf16,
@@ -131,8 +143,9 @@ int netra_moe_layer_launch_stage(netra_moe_layer_t* layer, uint32_t stage, const
 
 /* Copies the four device status words to the host (synchronises the device). */
 int netra_moe_layer_status(netra_moe_layer_t* layer, uint32_t status_out[4]);
-/* Kernels launched by one netra_moe_layer_launch call. */
-uint32_t netra_moe_layer_launch_count(const netra_moe_layer_t* layer);
+/* Kernels launched by one netra_moe_layer_launch call with `tokens` rows (the sort is one launch
+ * up to 1024 rows and three above). */
+uint32_t netra_moe_layer_launch_count(const netra_moe_layer_t* layer, uint32_t tokens);
 int netra_moe_layer_destroy(netra_moe_layer_t* layer);
 const char* netra_moe_last_error(void);
 

@@ -25,7 +25,8 @@ class LayerDesc(ctypes.Structure):
                 ("router_weight_bf16", c_void_p), ("router_bias_f32", c_void_p),
                 ("w13_fp8", c_void_p), ("w13_scale_f32", c_void_p),
                 ("w2_fp8", c_void_p), ("w2_scale_f32", c_void_p),
-                ("workspace", c_void_p), ("workspace_bytes", c_u64)]
+                ("workspace", c_void_p), ("workspace_bytes", c_u64),
+                ("weights_tiled", c_u32), ("reserved", c_u32)]
 
 
 BRIDGES = ("netra_qwen36_router_bf16", "netra_qwen36_shared_gate_append", "netra_qwen36_moe_gate_up",
@@ -42,8 +43,9 @@ SIGNATURES = {
     "netra_moe_layer_create": (c_int, [ctypes.POINTER(LayerDesc), ctypes.POINTER(c_void_p)]),
     "netra_moe_layer_launch": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_u32, c_void_p]),
     "netra_moe_layer_launch_stage": (c_int, [c_void_p, c_u32, c_void_p, c_void_p, c_void_p, c_u32, c_void_p]),
+    "netra_moe_repack_tiles_launch": (c_int, [c_void_p, c_void_p, c_u64, c_u32, c_void_p]),
     "netra_moe_layer_status": (c_int, [c_void_p, ctypes.POINTER(c_u32 * 4)]),
-    "netra_moe_layer_launch_count": (c_u32, [c_void_p]),
+    "netra_moe_layer_launch_count": (c_u32, [c_void_p, c_u32]),
     "netra_moe_layer_destroy": (c_int, [c_void_p]),
     "netra_moe_last_error": (ctypes.c_char_p, []),
     "netra_moe_sort_static_scratch_launch": (c_int, [c_void_p] * 5 + [c_u32, c_void_p]),

@@ -87,7 +87,7 @@ int umma_setup() {
 struct netra_moe_layer {
   netra_moe_layer_desc_t desc;
   netra_moe_workspace_layout_t lay;
-  CUtensorMap tm_w13, tm_w2, tm_a32, tm_a64, tm_h32, tm_h64;
+  CUtensorMap tm_w13, tm_w2, tm_a32, tm_a64, tm_a128, tm_h32, tm_h64, tm_h128;
   int sm_count;
   uint32_t launches;
 };
@@ -108,7 +108,7 @@ NETRA_BRIDGE_COMMON(netra_qwen36_moe_down_reduce)
 
 int netra_qwen36_router_bf16_launch(void* out, const void* hidden, const void* weight, uint32_t rows, cudaStream_t stream) {
   if (!out || !hidden || !weight || rows == 0) return fail("router_bf16: null pointer or zero rows");
-  dim3 grid((rows + 3) / 4, 4);
+  dim3 grid((rows + 15) / 16, 8);
   netra_router_logits_bf16_sm100<<<grid, 256, 0, stream>>>((uint16_t*)out, (const uint16_t*)hidden, (const uint16_t*)weight, rows);
   return check_launch("router_bf16 launch");
 }
@@ -165,9 +165,9 @@ int netra_moe_workspace_layout_query(uint32_t tokens, netra_moe_workspace_layout
   out->offsets = take((kRouted + 2) * 4);
   out->seg_hist = take(nseg * kRouted * 4);
   out->a_fp8 = take(rows * kHidden);
-  out->a_scale = take(rows * kHiddenBlocks * 4);
+  out->a_scale = take((rows + 128) * kHiddenBlocks * 4);   // +128 rows: scale tiles are copied 128 rows at a time
   out->h_fp8 = take(rows * kInter);
-  out->h_scale = take(rows * kInterBlocks * 4);
+  out->h_scale = take((rows + 128) * kInterBlocks * 4);
   out->down_f32 = take(rows * kHidden * 4);
   out->status = take(16);
   out->total_bytes = o;
@@ -199,12 +199,19 @@ int netra_moe_layer_create(const netra_moe_layer_desc_t* desc, netra_moe_layer_t
   uint8_t* ws = (uint8_t*)desc->workspace;
   const uint64_t rows = (uint64_t)desc->max_tokens * (kTopK + 1);
   int rc = 0;
-  rc = rc ? rc : encode_u8_2d(&layer->tm_w13, desc->w13_fp8, (uint64_t)(kRouted + 1) * 2 * kInter, kHidden, 128);
-  rc = rc ? rc : encode_u8_2d(&layer->tm_w2, desc->w2_fp8, (uint64_t)(kRouted + 1) * kHidden, kInter, 128);
+  if (desc->weights_tiled) {   // tiles of 128 rows x 128 bytes, one after another
+    rc = rc ? rc : encode_u8_2d(&layer->tm_w13, desc->w13_fp8, (uint64_t)(kRouted + 1) * 2 * kInter * kHiddenBlocks, kBlock, 128);
+    rc = rc ? rc : encode_u8_2d(&layer->tm_w2, desc->w2_fp8, (uint64_t)(kRouted + 1) * kHidden * kInterBlocks, kBlock, 128);
+  } else {
+    rc = rc ? rc : encode_u8_2d(&layer->tm_w13, desc->w13_fp8, (uint64_t)(kRouted + 1) * 2 * kInter, kHidden, 128);
+    rc = rc ? rc : encode_u8_2d(&layer->tm_w2, desc->w2_fp8, (uint64_t)(kRouted + 1) * kHidden, kInter, 128);
+  }
   rc = rc ? rc : encode_u8_2d(&layer->tm_a32, ws + lay.a_fp8, rows, kHidden, 32);
   rc = rc ? rc : encode_u8_2d(&layer->tm_a64, ws + lay.a_fp8, rows, kHidden, 64);
+  rc = rc ? rc : encode_u8_2d(&layer->tm_a128, ws + lay.a_fp8, rows, kHidden, 128);
   rc = rc ? rc : encode_u8_2d(&layer->tm_h32, ws + lay.h_fp8, rows, kInter, 32);
   rc = rc ? rc : encode_u8_2d(&layer->tm_h64, ws + lay.h_fp8, rows, kInter, 64);
+  rc = rc ? rc : encode_u8_2d(&layer->tm_h128, ws + lay.h_fp8, rows, kInter, 128);
   if (rc == 0) {
     e = cudaMemset(ws + lay.status, 0, 16);
     if (e != cudaSuccess) rc = fail_cuda("cudaMemset(status)", e);
@@ -214,7 +221,10 @@ int netra_moe_layer_create(const netra_moe_layer_desc_t* desc, netra_moe_layer_t
   return 0;
 }
 
-uint32_t netra_moe_layer_launch_count(const netra_moe_layer_t* layer) { return layer ? layer->launches : 0; }
+uint32_t netra_moe_layer_launch_count(const netra_moe_layer_t* layer, uint32_t tokens) {
+  if (layer == nullptr) return 0;
+  return tokens <= (uint32_t)kSortSmallMaxRows ? layer->launches - 2 : layer->launches;
+}
 
 }  // extern "C" (reopened below)
 
@@ -245,26 +255,35 @@ void launch_stage(netra_moe_layer* layer, uint32_t stage, const void* hidden, co
   const uint32_t nseg = (pairs + kSortSegment - 1) / kSortSegment;
   switch (stage) {
     case 0:
-      netra_router_logits_bf16_sm100<<<dim3((tokens + 3) / 4, 4), 256, 0, stream>>>(
+      netra_router_logits_bf16_sm100<<<dim3((tokens + 15) / 16, 8), 256, 0, stream>>>(
           logits, (const uint16_t*)hidden, (const uint16_t*)layer->desc.router_weight_bf16, tokens);
       break;
     case 1:
       netra_moe_topk_quant_sm100<<<(tokens + 3) / 4, 128, 0, stream>>>(
           ids9, w9, a_fp8, a_scale, logits, layer->desc.router_bias_f32, shared_w, (const uint16_t*)hidden, tokens, pairs);
       break;
-    case 2: netra_moe_sort_hist_sm100<<<nseg, 256, 0, stream>>>(seg_hist, ids9, tokens); break;
-    case 3: netra_moe_sort_scan_sm100<<<1, 256, 0, stream>>>(seg_hist, counts, offsets, tokens, nseg); break;
-    case 4: netra_moe_sort_scatter_sm100<<<nseg, 256, 0, stream>>>(perm, inv_perm, seg_hist, ids9, tokens); break;
+    case 2:
+      if (tokens <= (uint32_t)kSortSmallMaxRows)   // one block does the whole sort; stages 3 and 4 launch nothing
+        netra_moe_sort_small_sm100<<<1, 1024, 0, stream>>>(perm, inv_perm, counts, offsets, ids9, tokens);
+      else
+        netra_moe_sort_hist_sm100<<<nseg, 256, 0, stream>>>(seg_hist, ids9, tokens);
+      break;
+    case 3:
+      if (tokens > (uint32_t)kSortSmallMaxRows) netra_moe_sort_scan_sm100<<<1, 256, 0, stream>>>(seg_hist, counts, offsets, tokens, nseg);
+      break;
+    case 4:
+      if (tokens > (uint32_t)kSortSmallMaxRows) netra_moe_sort_scatter_sm100<<<nseg, 256, 0, stream>>>(perm, inv_perm, seg_hist, ids9, tokens);
+      break;
     case 5: netra_moe_gather_rows_sm100<<<(pairs + 7) / 8, 256, 0, stream>>>(a_fp8, a_scale, perm, tokens); break;
     case 6:
-      netra_moe_gate_up_umma_sm100<<<layer->sm_count, 192, gate_up_smem_bytes(), stream>>>(
-          layer->tm_w13, layer->tm_a32, layer->tm_a64, a_scale, layer->desc.w13_scale_f32, offsets, h_fp8, h_scale,
-          kRouted + 1, status);
+      netra_moe_gate_up_umma_sm100<<<layer->sm_count, kGemmThreads, gate_up_smem_bytes(), stream>>>(
+          layer->tm_w13, layer->tm_a32, layer->tm_a64, layer->tm_a128, a_scale, layer->desc.w13_scale_f32, offsets, h_fp8,
+          h_scale, kRouted + 1, layer->desc.weights_tiled, status);
       break;
     case 7:
-      netra_moe_down_umma_sm100<<<layer->sm_count, 192, down_smem_bytes(), stream>>>(
-          layer->tm_w2, layer->tm_h32, layer->tm_h64, h_scale, layer->desc.w2_scale_f32, offsets, down, kRouted + 1,
-          status + 1);
+      netra_moe_down_umma_sm100<<<layer->sm_count, kGemmThreads, down_smem_bytes(), stream>>>(
+          layer->tm_w2, layer->tm_h32, layer->tm_h64, layer->tm_h128, h_scale, layer->desc.w2_scale_f32, offsets, down,
+          kRouted + 1, layer->desc.weights_tiled, status + 1);
       break;
     default: netra_moe_combine_sm100<<<tokens, 256, 0, stream>>>((uint16_t*)out, down, w9, inv_perm, tokens); break;
   }
@@ -290,6 +309,16 @@ int netra_moe_layer_launch_stage(netra_moe_layer_t* layer, uint32_t stage, const
   return check_launch("layer stage launch");
 }
 
+int netra_moe_repack_tiles_launch(void* dst, const void* src, uint64_t total_rows, uint32_t k_bytes, cudaStream_t stream) {
+  if (!dst || !src || dst == src) return fail("repack_tiles: null or aliased pointers");
+  if (total_rows == 0 || total_rows % 128 != 0 || k_bytes == 0 || k_bytes % 128 != 0 || total_rows > (1ull << 31))
+    return fail("repack_tiles: rows and row bytes must be positive multiples of 128");
+  const uint64_t chunks = total_rows * k_bytes / 16;
+  netra_moe_repack_tiles_sm100<<<(unsigned)((chunks + 255) / 256), 256, 0, stream>>>((uint4*)dst, (const uint4*)src,
+                                                                                     (uint32_t)total_rows, k_bytes);
+  return check_launch("repack_tiles launch");
+}
+
 int netra_moe_layer_status(netra_moe_layer_t* layer, uint32_t status_out[4]) {
   if (layer == nullptr || status_out == nullptr) return fail("layer_status: null pointer");
   cudaError_t e = cudaMemcpy(status_out, (uint8_t*)layer->desc.workspace + layer->lay.status, 16, cudaMemcpyDeviceToHost);
@@ -305,3 +334,9 @@ int netra_moe_layer_destroy(netra_moe_layer_t* layer) {
 
 // Entry point with library-owned scratch (needs fail(), fail_cuda(), check_launch() from above).
 #include "static_scratch_sort.cu"
+
+#ifdef NETRA_TRACE
+extern "C" int netra_debug_read_trace(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, netra::g_trace, sizeof(long long) * 8 * 256);
+}
+#endif

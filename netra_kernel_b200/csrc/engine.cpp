@@ -1,0 +1,747 @@
+// Netra engine runtime for sm_100a: loads an engine directory written by the compiler, binds
+// caller-owned pointers, optionally captures a CUDA graph, and launches on the caller's stream.
+//
+// Behavioural contract followed: runtime/gfx950/engine/netra_engine.hip:249-566 (create / query /
+// bind / finalize / prepare / launch / launch_operation / launch_operation_bound / destroy) with
+// its status codes, ordering rules and hot-path rules (no allocation, synchronisation, file, env
+// or string work in the launch functions).  Kernels come from cubins through the CUDA driver API,
+// reached through cudaGetDriverEntryPoint so that the library has no link-time libcuda dependency.
+#include <cuda.h>
+#include <cuda_runtime_api.h>
+
+#include <array>
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <fstream>
+#include <limits>
+#include <map>
+#include <memory>
+#include <new>
+#include <sstream>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../../include/netra_engine.h"
+
+namespace {
+
+// ----------------------------------------------------------------------------- JSON
+struct Json {
+  enum Kind { Null, Bool, Number, String, Array, Object } kind = Null;
+  bool boolean = false;
+  uint64_t number = 0;      // manifests only carry non-negative integers
+  bool integral = true;
+  std::string string;
+  std::vector<Json> array;
+  std::vector<std::pair<std::string, Json>> object;
+
+  const Json* find(const char* key) const {
+    if (kind != Object) return nullptr;
+    for (const auto& kv : object)
+      if (kv.first == key) return &kv.second;
+    return nullptr;
+  }
+  const Json& at(const char* key) const {
+    const Json* v = find(key);
+    if (!v) throw std::runtime_error(std::string("missing manifest field: ") + key);
+    return *v;
+  }
+};
+
+class JsonReader {
+ public:
+  explicit JsonReader(const std::string& text) : t_(text) {}
+  Json parse() {
+    Json v = value(0);
+    space();
+    if (p_ != t_.size()) fail("trailing characters after JSON value");
+    return v;
+  }
+
+ private:
+  const std::string& t_;
+  size_t p_ = 0;
+  [[noreturn]] void fail(const char* what) const {
+    throw std::runtime_error(std::string("engine.json: ") + what + " at byte " + std::to_string(p_));
+  }
+  void space() { while (p_ < t_.size() && (t_[p_] == ' ' || t_[p_] == '\n' || t_[p_] == '\t' || t_[p_] == '\r')) ++p_; }
+  bool take(char c) { space(); if (p_ < t_.size() && t_[p_] == c) { ++p_; return true; } return false; }
+  void expect(char c) { if (!take(c)) fail("unexpected character"); }
+  Json value(int depth) {
+    if (depth > 64) fail("nesting too deep");
+    space();
+    if (p_ >= t_.size()) fail("unexpected end");
+    const char c = t_[p_];
+    Json v;
+    if (c == '{') {
+      ++p_; v.kind = Json::Object;
+      if (take('}')) return v;
+      do {
+        space();
+        Json key = string_value();
+        expect(':');
+        v.object.emplace_back(key.string, value(depth + 1));
+      } while (take(','));
+      expect('}');
+    } else if (c == '[') {
+      ++p_; v.kind = Json::Array;
+      if (take(']')) return v;
+      do { v.array.push_back(value(depth + 1)); } while (take(','));
+      expect(']');
+    } else if (c == '"') {
+      v = string_value();
+    } else if (c == 't' && t_.compare(p_, 4, "true") == 0) {
+      p_ += 4; v.kind = Json::Bool; v.boolean = true;
+    } else if (c == 'f' && t_.compare(p_, 5, "false") == 0) {
+      p_ += 5; v.kind = Json::Bool;
+    } else if (c == 'n' && t_.compare(p_, 4, "null") == 0) {
+      p_ += 4;
+    } else {
+      v.kind = Json::Number;
+      const size_t begin = p_;
+      if (t_[p_] == '-') { v.integral = false; ++p_; }
+      uint64_t n = 0; bool any = false;
+      while (p_ < t_.size() && t_[p_] >= '0' && t_[p_] <= '9') {
+        const uint64_t d = (uint64_t)(t_[p_] - '0');
+        if (n > (std::numeric_limits<uint64_t>::max() - d) / 10) fail("integer overflows uint64");
+        n = n * 10 + d; any = true; ++p_;
+      }
+      if (!any) fail("invalid value");
+      if (p_ < t_.size() && (t_[p_] == '.' || t_[p_] == 'e' || t_[p_] == 'E')) {
+        v.integral = false;
+        while (p_ < t_.size() && (std::strchr("+-.eE", t_[p_]) || (t_[p_] >= '0' && t_[p_] <= '9'))) ++p_;
+      }
+      v.number = n;
+      (void)begin;
+    }
+    return v;
+  }
+  Json string_value() {
+    if (p_ >= t_.size() || t_[p_] != '"') fail("expected string");
+    ++p_;
+    Json v; v.kind = Json::String;
+    while (p_ < t_.size() && t_[p_] != '"') {
+      char c = t_[p_++];
+      if (c == '\\') {
+        if (p_ >= t_.size()) fail("bad escape");
+        const char e = t_[p_++];
+        switch (e) {
+          case 'n': c = '\n'; break; case 't': c = '\t'; break; case 'r': c = '\r'; break;
+          case 'b': c = '\b'; break; case 'f': c = '\f'; break;
+          case '"': case '\\': case '/': c = e; break;
+          case 'u': {
+            if (p_ + 4 > t_.size()) fail("bad unicode escape");
+            unsigned code = 0;
+            for (int i = 0; i < 4; ++i) {
+              const char h = t_[p_++];
+              code = code * 16 + (unsigned)(h >= '0' && h <= '9' ? h - '0' : (h | 32) >= 'a' && (h | 32) <= 'f' ? (h | 32) - 'a' + 10 : 99);
+            }
+            if (code > 0x7f) fail("non-ASCII escape is not supported in engine manifests");
+            c = (char)code; break;
+          }
+          default: fail("bad escape");
+        }
+      }
+      v.string.push_back(c);
+    }
+    if (p_ >= t_.size()) fail("unterminated string");
+    ++p_;
+    return v;
+  }
+};
+
+uint32_t as_u32(const Json& v, const char* name) {
+  if (v.kind != Json::Number || !v.integral || v.number > UINT32_MAX) throw std::runtime_error(std::string(name) + " must be uint32");
+  return (uint32_t)v.number;
+}
+uint64_t as_u64(const Json& v, const char* name) {
+  if (v.kind != Json::Number || !v.integral) throw std::runtime_error(std::string(name) + " must be uint64");
+  return v.number;
+}
+const std::string& as_text(const Json& v, const char* name) {
+  if (v.kind != Json::String) throw std::runtime_error(std::string(name) + " must be a string");
+  return v.string;
+}
+
+std::string read_file(const std::string& path) {
+  std::ifstream in(path, std::ios::binary);
+  if (!in) throw std::runtime_error("cannot open " + path);
+  std::ostringstream ss; ss << in.rdbuf();
+  return ss.str();
+}
+
+// "cubin/<name>" only: no absolute paths, backslashes, empty or dot components.
+std::string checked_cubin_path(const std::string& rel) {
+  if (rel.rfind("cubin/", 0) != 0 || rel.size() <= 6 || rel.find('\\') != std::string::npos || rel.find("//") != std::string::npos)
+    throw std::runtime_error("cubin must be a normalized engine-relative path");
+  size_t begin = 0;
+  while (begin <= rel.size()) {
+    const size_t end = rel.find('/', begin);
+    const std::string part = rel.substr(begin, end == std::string::npos ? std::string::npos : end - begin);
+    if (part.empty() || part == "." || part == "..") throw std::runtime_error("cubin path traversal is forbidden");
+    if (end == std::string::npos) break;
+    begin = end + 1;
+  }
+  return rel;
+}
+
+std::pair<uint32_t, uint32_t> major_minor(const std::string& text) {
+  const size_t dot = text.find('.');
+  if (dot == std::string::npos || dot == 0 || dot + 1 == text.size() || text.find('.', dot + 1) != std::string::npos)
+    throw std::runtime_error("required_cuda.minimum must be MAJOR.MINOR");
+  for (char c : text)
+    if (c != '.' && (c < '0' || c > '9')) throw std::runtime_error("required_cuda.minimum must be MAJOR.MINOR");
+  const unsigned long a = std::stoul(text.substr(0, dot)), b = std::stoul(text.substr(dot + 1));
+  if (a > 1000 || b > 1000) throw std::runtime_error("required_cuda.minimum is out of range");
+  return {(uint32_t)a, (uint32_t)b};
+}
+
+// ----------------------------------------------------------------------------- manifest model
+constexpr uint32_t kMaxArguments = 32;
+
+struct TensorMapSpec {
+  uint64_t rows = 0, row_bytes = 0;
+  uint32_t box_rows = 0, box_bytes = 0;
+};
+
+struct ArgSpec {
+  enum Kind { Pointer, U32, TensorMap } kind = Pointer;
+  bool bindable = false;          // source == binding
+  uint64_t workspace_offset = 0;  // source == workspace
+  uint32_t value = 0;             // u32_constant
+  TensorMapSpec map;
+};
+
+struct OpSpec {
+  bool fallback = true;
+  uint32_t grid[3] = {1, 1, 1}, block[3] = {1, 1, 1}, lds_bytes = 0, dynamic_lds_bytes = 0;
+  std::string cubin, symbol;
+  std::vector<ArgSpec> args;
+};
+
+struct ProfileSpec {
+  netra_profile_info_t info{};
+};
+
+struct Manifest {
+  uint64_t workspace_bytes = 0;
+  std::pair<uint32_t, uint32_t> required_cuda{0, 0};
+  std::vector<ProfileSpec> profiles;
+  std::vector<OpSpec> operations;
+};
+
+Manifest parse_manifest(const std::string& directory) {
+  const Json root = JsonReader(read_file(directory + "/engine.json")).parse();
+  if (as_text(root.at("format_version"), "format_version") != "netra-engine-1" ||
+      as_text(root.at("target"), "target") != "sm_100a" || as_u32(root.at("wave_size"), "wave_size") != 32)
+    throw std::runtime_error("engine target/format/wave contract mismatch");
+  Manifest m;
+  m.required_cuda = major_minor(as_text(root.at("required_cuda").at("minimum"), "required_cuda.minimum"));
+  m.workspace_bytes = as_u64(root.at("workspace_bytes"), "workspace_bytes");
+  const Json& profiles = root.at("profiles");
+  const Json& operations = root.at("operations");
+  if (profiles.kind != Json::Array || operations.kind != Json::Array) throw std::runtime_error("profiles and operations must be arrays");
+  if (profiles.array.empty()) throw std::runtime_error("engine has no profile");
+  for (const Json& op : operations.array) {
+    OpSpec spec;
+    spec.fallback = as_text(op.at("execution"), "execution") != "kernel";
+    const Json* launch = op.find("launch");
+    if (launch && launch->kind == Json::Object) {
+      const Json& grid = launch->at("grid");
+      const Json& block = launch->at("block");
+      if (grid.kind != Json::Array || block.kind != Json::Array || grid.array.size() != 3 || block.array.size() != 3)
+        throw std::runtime_error("launch grid and block must have three dimensions");
+      for (int i = 0; i < 3; ++i) {
+        spec.grid[i] = as_u32(grid.array[i], "grid");
+        spec.block[i] = as_u32(block.array[i], "block");
+        if (!spec.grid[i] || !spec.block[i]) throw std::runtime_error("launch dimensions must be nonzero");
+      }
+      spec.lds_bytes = as_u32(launch->at("lds_bytes"), "lds_bytes");
+      const Json* dyn = launch->find("dynamic_lds_bytes");
+      spec.dynamic_lds_bytes = dyn ? as_u32(*dyn, "dynamic_lds_bytes") : 0;
+    } else if (!spec.fallback) {
+      throw std::runtime_error("selected kernel requires a launch record");
+    }
+    if (!spec.fallback) {
+      spec.cubin = checked_cubin_path(as_text(op.at("cubin"), "cubin"));
+      spec.symbol = as_text(op.at("kernel_symbol"), "kernel_symbol");
+      const Json& args = op.at("arguments");
+      if (args.kind != Json::Array || args.array.empty()) throw std::runtime_error("selected kernel requires typed arguments");
+      if (args.array.size() > kMaxArguments) throw std::runtime_error("more than 32 kernel arguments");
+      for (const Json& a : args.array) {
+        ArgSpec arg;
+        const std::string& kind = as_text(a.at("kind"), "argument.kind");
+        if (kind == "pointer" || kind == "tensor_map") {
+          arg.kind = kind == "pointer" ? ArgSpec::Pointer : ArgSpec::TensorMap;
+          const Json* source = a.find("source");
+          const std::string src = source ? as_text(*source, "argument.source") : "binding";
+          if (src == "binding") {
+            arg.bindable = true;
+          } else if (src == "workspace") {
+            arg.workspace_offset = as_u64(a.at("workspace_offset"), "workspace_offset");
+            if (arg.workspace_offset >= m.workspace_bytes) throw std::runtime_error("kernel workspace argument is out of range");
+          } else {
+            throw std::runtime_error("unsupported pointer argument source: " + src);
+          }
+          if (arg.kind == ArgSpec::TensorMap) {
+            const Json& t = a.at("tensor_map");
+            arg.map.rows = as_u64(t.at("rows"), "tensor_map.rows");
+            arg.map.row_bytes = as_u64(t.at("row_bytes"), "tensor_map.row_bytes");
+            arg.map.box_rows = as_u32(t.at("box_rows"), "tensor_map.box_rows");
+            arg.map.box_bytes = as_u32(t.at("box_bytes"), "tensor_map.box_bytes");
+            if (as_text(t.at("swizzle"), "tensor_map.swizzle") != "128B" || arg.map.box_bytes != 128 || !arg.map.rows ||
+                !arg.map.row_bytes || arg.map.row_bytes % 16 || !arg.map.box_rows || arg.map.box_rows > 256)
+              throw std::runtime_error("unsupported tensor_map description");
+            if (!arg.bindable && arg.workspace_offset % 16) throw std::runtime_error("tensor_map workspace offset must be 16-byte aligned");
+          }
+        } else if (kind == "u32_constant") {
+          arg.kind = ArgSpec::U32;
+          arg.value = as_u32(a.at("value"), "argument.value");
+        } else {
+          throw std::runtime_error("unsupported kernel argument kind: " + kind);
+        }
+        spec.args.push_back(arg);
+      }
+    }
+    m.operations.push_back(std::move(spec));
+  }
+  uint32_t id = 0;
+  for (const Json& p : profiles.array) {
+    ProfileSpec spec;
+    const Json& guards = p.at("guards");
+    spec.info.struct_size = sizeof(spec.info);
+    spec.info.profile_id = id++;
+    spec.info.min_m = as_u32(guards.at("m").at("min"), "m.min");
+    spec.info.max_m = as_u32(guards.at("m").at("max"), "m.max");
+    spec.info.min_batch = as_u32(guards.at("batch").at("min"), "batch.min");
+    spec.info.max_batch = as_u32(guards.at("batch").at("max"), "batch.max");
+    spec.info.min_sequence = as_u64(guards.at("sequence").at("min"), "sequence.min");
+    spec.info.max_sequence = as_u64(guards.at("sequence").at("max"), "sequence.max");
+    spec.info.tensor_parallel = as_u32(p.at("tensor_parallel"), "tensor_parallel");
+    spec.info.workspace_bytes = m.workspace_bytes;
+    for (const OpSpec& op : m.operations)
+      if (op.fallback) spec.info.requires_fallback = 1;
+    m.profiles.push_back(spec);
+  }
+  return m;
+}
+
+// ----------------------------------------------------------------------------- driver entry points
+struct Driver {
+  CUresult (*ModuleLoadData)(CUmodule*, const void*) = nullptr;
+  CUresult (*ModuleUnload)(CUmodule) = nullptr;
+  CUresult (*ModuleGetFunction)(CUfunction*, CUmodule, const char*) = nullptr;
+  CUresult (*FuncSetAttribute)(CUfunction, CUfunction_attribute, int) = nullptr;
+  CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
+                           void**, void**) = nullptr;
+  CUresult (*TensorMapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill) = nullptr;
+  bool ok = false;
+};
+
+const Driver& driver() {
+  static Driver d = [] {
+    Driver r;
+    auto get = [](const char* name, void** out) {
+      cudaDriverEntryPointQueryResult q;
+      return cudaGetDriverEntryPoint(name, out, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess && *out;
+    };
+    r.ok = get("cuModuleLoadData", (void**)&r.ModuleLoadData) && get("cuModuleUnload", (void**)&r.ModuleUnload) &&
+           get("cuModuleGetFunction", (void**)&r.ModuleGetFunction) && get("cuFuncSetAttribute", (void**)&r.FuncSetAttribute) &&
+           get("cuLaunchKernel", (void**)&r.LaunchKernel) && get("cuTensorMapEncodeTiled", (void**)&r.TensorMapEncodeTiled);
+    return r;
+  }();
+  return d;
+}
+
+bool encode_map(CUtensorMap* map, void* base, const TensorMapSpec& s) {
+  cuuint64_t dims[2] = {s.row_bytes, s.rows};
+  cuuint64_t strides[1] = {s.row_bytes};
+  cuuint32_t box[2] = {s.box_bytes, s.box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  return driver().TensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, elem,
+                                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// ----------------------------------------------------------------------------- engine records
+struct ArgSlot {
+  ArgSpec spec;
+  void* pointer = nullptr;            // bound or workspace-resolved pointer
+  uint32_t scalar = 0;
+  alignas(64) CUtensorMap map;
+  bool map_ready = false;
+};
+
+struct OpRecord {
+  OpSpec spec;
+  CUfunction function = nullptr;
+  uint32_t argc = 0;
+  std::unique_ptr<ArgSlot[]> slots;   // allocated at create; never resized afterwards
+  void* addresses[kMaxArguments] = {};
+};
+
+struct ProfileRecord {
+  netra_profile_info_t info{};
+  std::vector<OpRecord> operations;
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t graph_exec = nullptr;
+  bool graph_prepared = false;
+};
+
+}  // namespace
+
+struct netra_engine {
+  std::string directory;
+  int device_id = 0;
+  bool graph_enabled = false;
+  void* workspace = nullptr;
+  uint64_t workspace_bytes = 0;
+  std::vector<ProfileRecord> profiles;
+  std::map<std::string, CUmodule> modules;
+  std::atomic<bool> bindings_finalized{false};
+  std::atomic<uint32_t> in_flight{0};
+  std::array<char, 512> last_error{};
+};
+
+namespace {
+
+netra_status_t fail(netra_engine* e, netra_status_t status, const char* message) {
+  if (e) std::snprintf(e->last_error.data(), e->last_error.size(), "%s", message);
+  return status;
+}
+netra_status_t cuda_fail(netra_engine* e, const char* what, cudaError_t err) {
+  if (e) std::snprintf(e->last_error.data(), e->last_error.size(), "%s: %s", what, cudaGetErrorString(err));
+  return NETRA_STATUS_CUDA;
+}
+netra_status_t driver_fail(netra_engine* e, const char* what, CUresult err) {
+  if (e) std::snprintf(e->last_error.data(), e->last_error.size(), "%s: CUresult %d", what, (int)err);
+  return NETRA_STATUS_CUDA;
+}
+
+bool guard_matches(const netra_profile_info_t& info, const netra_launch_shape_t& shape) {
+  return shape.m >= info.min_m && shape.m <= info.max_m && shape.batch >= info.min_batch && shape.batch <= info.max_batch &&
+         shape.sequence >= info.min_sequence && shape.sequence <= info.max_sequence &&
+         shape.tensor_parallel == info.tensor_parallel;
+}
+
+netra_status_t launch_record(netra_engine* e, OpRecord& op, void** addresses, cudaStream_t stream) {
+  const CUresult r = driver().LaunchKernel(op.function, op.spec.grid[0], op.spec.grid[1], op.spec.grid[2], op.spec.block[0],
+                                           op.spec.block[1], op.spec.block[2], op.spec.dynamic_lds_bytes, (CUstream)stream,
+                                           addresses, nullptr);
+  return r == CUDA_SUCCESS ? NETRA_STATUS_OK : driver_fail(e, "cuLaunchKernel", r);
+}
+
+netra_status_t launch_one(netra_engine* e, OpRecord& op, cudaStream_t stream) {
+  if (op.spec.fallback) return fail(e, NETRA_STATUS_FALLBACK_REQUIRED, "operation requires framework fallback");
+  for (uint32_t i = 0; i < op.argc; ++i)
+    if (op.slots[i].spec.bindable && !op.slots[i].pointer) return fail(e, NETRA_STATUS_BINDING, "kernel pointer argument is unbound");
+  return launch_record(e, op, op.addresses, stream);
+}
+
+netra_status_t direct_launch(netra_engine* e, ProfileRecord& profile, cudaStream_t stream) {
+  for (auto& op : profile.operations) {
+    const netra_status_t s = launch_one(e, op, stream);
+    if (s != NETRA_STATUS_OK) return s;
+  }
+  return NETRA_STATUS_OK;
+}
+
+void release(netra_engine* e) {
+  for (auto& p : e->profiles) {
+    if (p.graph_exec) (void)cudaGraphExecDestroy(p.graph_exec);
+    if (p.graph) (void)cudaGraphDestroy(p.graph);
+  }
+  if (driver().ok)
+    for (auto& kv : e->modules)
+      if (kv.second) (void)driver().ModuleUnload(kv.second);
+  if (e->workspace) (void)cudaFree(e->workspace);
+}
+
+}  // namespace
+
+extern "C" netra_status_t netra_engine_check_manifest(const char* directory, char* error, size_t error_bytes) {
+  if (!directory || !*directory) return NETRA_STATUS_INVALID_ARGUMENT;
+  try {
+    (void)parse_manifest(directory);
+    if (error && error_bytes) error[0] = '\0';
+    return NETRA_STATUS_OK;
+  } catch (const std::exception& ex) {
+    if (error && error_bytes) std::snprintf(error, error_bytes, "%s", ex.what());
+    return NETRA_STATUS_MANIFEST;
+  }
+}
+
+extern "C" netra_status_t netra_engine_create(const char* directory, const netra_engine_options_t* options,
+                                              netra_engine_t** output) {
+  if (!directory || !*directory || !options || !output || options->struct_size != sizeof(netra_engine_options_t))
+    return NETRA_STATUS_INVALID_ARGUMENT;
+  *output = nullptr;
+  netra_engine* e = new (std::nothrow) netra_engine;
+  if (!e) return NETRA_STATUS_IO;
+  int previous = -1;
+  try {
+    e->directory = directory;
+    e->device_id = options->device_id;
+    e->graph_enabled = options->enable_graph_capture != 0;
+    cudaError_t err = cudaGetDevice(&previous);
+    if (err != cudaSuccess) { delete e; return NETRA_STATUS_CUDA; }
+    err = cudaSetDevice(e->device_id);
+    if (err != cudaSuccess) { delete e; return NETRA_STATUS_CUDA; }
+    int major = 0, warp = 0;
+    (void)cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, e->device_id);
+    (void)cudaDeviceGetAttribute(&warp, cudaDevAttrWarpSize, e->device_id);
+    if (major != 10 || warp != 32) { (void)cudaSetDevice(previous); delete e; return NETRA_STATUS_UNSUPPORTED_TARGET; }
+    (void)cudaFree(nullptr);   // make the primary context current for the driver entry points
+    if (!driver().ok) throw std::runtime_error("CUDA driver entry points are unavailable");
+    const Manifest manifest = parse_manifest(e->directory);
+    int driver_version = 0;
+    err = cudaDriverGetVersion(&driver_version);
+    if (err != cudaSuccess) throw std::runtime_error(std::string("cudaDriverGetVersion: ") + cudaGetErrorString(err));
+    const std::pair<uint32_t, uint32_t> actual{(uint32_t)(driver_version / 1000), (uint32_t)((driver_version % 1000) / 10)};
+    if (actual < manifest.required_cuda) throw std::runtime_error("CUDA driver is older than required_cuda.minimum");
+    e->workspace_bytes = manifest.workspace_bytes;
+    if (e->workspace_bytes) {
+      err = cudaMalloc(&e->workspace, (size_t)e->workspace_bytes);
+      if (err != cudaSuccess) { const auto s = cuda_fail(e, "cudaMalloc(workspace)", err); (void)cudaSetDevice(previous); delete e; return s; }
+      (void)cudaMemset(e->workspace, 0, (size_t)e->workspace_bytes);
+    }
+    for (const ProfileSpec& pspec : manifest.profiles) {
+      e->profiles.emplace_back();
+      ProfileRecord& profile = e->profiles.back();
+      profile.info = pspec.info;
+      profile.operations.reserve(manifest.operations.size());
+      for (const OpSpec& ospec : manifest.operations) {
+        profile.operations.emplace_back();
+        OpRecord& op = profile.operations.back();
+        op.spec = ospec;
+        if (ospec.fallback) continue;
+        CUmodule& module = e->modules[ospec.cubin];
+        if (!module) {
+          const std::string image = read_file(e->directory + "/" + ospec.cubin);
+          const CUresult r = driver().ModuleLoadData(&module, image.data());
+          if (r != CUDA_SUCCESS) throw std::runtime_error("cuModuleLoadData(" + ospec.cubin + "): CUresult " + std::to_string((int)r));
+        }
+        CUresult r = driver().ModuleGetFunction(&op.function, module, ospec.symbol.c_str());
+        if (r != CUDA_SUCCESS) throw std::runtime_error("cuModuleGetFunction(" + ospec.symbol + "): CUresult " + std::to_string((int)r));
+        if (ospec.dynamic_lds_bytes > 48 * 1024) {
+          r = driver().FuncSetAttribute(op.function, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)ospec.dynamic_lds_bytes);
+          if (r != CUDA_SUCCESS) throw std::runtime_error("cuFuncSetAttribute(max dynamic shared memory): CUresult " + std::to_string((int)r));
+        }
+        op.argc = (uint32_t)ospec.args.size();
+        op.slots.reset(new ArgSlot[op.argc]);
+        for (uint32_t i = 0; i < op.argc; ++i) {
+          ArgSlot& slot = op.slots[i];
+          slot.spec = ospec.args[i];
+          if (slot.spec.kind == ArgSpec::U32) {
+            slot.scalar = slot.spec.value;
+            op.addresses[i] = &slot.scalar;
+          } else {
+            if (!slot.spec.bindable) slot.pointer = static_cast<unsigned char*>(e->workspace) + slot.spec.workspace_offset;
+            if (slot.spec.kind == ArgSpec::TensorMap) {
+              if (!slot.spec.bindable) {
+                if (!encode_map(&slot.map, slot.pointer, slot.spec.map)) throw std::runtime_error("cuTensorMapEncodeTiled failed for a workspace tensor map");
+                slot.map_ready = true;
+              }
+              op.addresses[i] = &slot.map;
+            } else {
+              op.addresses[i] = &slot.pointer;
+            }
+          }
+        }
+      }
+    }
+    (void)cudaSetDevice(previous);
+    e->last_error[0] = '\0';
+    *output = e;
+    return NETRA_STATUS_OK;
+  } catch (const std::exception& ex) {
+    // the message is lost with the engine; callers that need it use netra_engine_check_manifest
+    (void)ex;
+    release(e);
+    if (previous >= 0) (void)cudaSetDevice(previous);
+    delete e;
+    return NETRA_STATUS_MANIFEST;
+  }
+}
+
+extern "C" size_t netra_engine_profile_count(const netra_engine_t* e) { return e ? e->profiles.size() : 0; }
+
+extern "C" netra_status_t netra_engine_query_profile(const netra_engine_t* e, uint32_t profile_id, netra_profile_info_t* output) {
+  if (!e || !output || output->struct_size != sizeof(netra_profile_info_t)) return NETRA_STATUS_INVALID_ARGUMENT;
+  if (profile_id >= e->profiles.size()) return NETRA_STATUS_UNSUPPORTED_PROFILE;
+  *output = e->profiles[profile_id].info;
+  return NETRA_STATUS_OK;
+}
+
+extern "C" netra_status_t netra_engine_bind(netra_engine_t* e, uint32_t profile_id, uint32_t operation_index,
+                                            uint32_t argument_index, void* pointer) {
+  if (!e || !pointer) return NETRA_STATUS_INVALID_ARGUMENT;
+  if (e->bindings_finalized.load(std::memory_order_acquire)) return fail(e, NETRA_STATUS_BUSY, "bindings are finalized and immutable");
+  if (e->in_flight.load(std::memory_order_acquire)) return fail(e, NETRA_STATUS_BUSY, "cannot bind during launch");
+  if (profile_id >= e->profiles.size() || operation_index >= e->profiles[profile_id].operations.size())
+    return fail(e, NETRA_STATUS_BINDING, "binding index out of range");
+  ProfileRecord& profile = e->profiles[profile_id];
+  if (profile.graph_prepared) return fail(e, NETRA_STATUS_BUSY, "bindings are immutable after graph preparation");
+  OpRecord& op = profile.operations[operation_index];
+  if (argument_index >= op.argc) return fail(e, NETRA_STATUS_BINDING, "argument index out of range");
+  ArgSlot& slot = op.slots[argument_index];
+  if (!slot.spec.bindable) return fail(e, NETRA_STATUS_BINDING, "constant kernel arguments cannot be rebound");
+  if (slot.spec.kind == ArgSpec::TensorMap) {
+    if (((uintptr_t)pointer & 15) != 0) return fail(e, NETRA_STATUS_BINDING, "tensor-map pointers must be 16-byte aligned");
+    if (!encode_map(&slot.map, pointer, slot.spec.map)) return fail(e, NETRA_STATUS_BINDING, "cuTensorMapEncodeTiled rejected the bound pointer");
+    slot.map_ready = true;
+  }
+  slot.pointer = pointer;
+  e->last_error[0] = '\0';
+  return NETRA_STATUS_OK;
+}
+
+extern "C" netra_status_t netra_engine_finalize_bindings(netra_engine_t* e) {
+  if (!e) return NETRA_STATUS_INVALID_ARGUMENT;
+  if (e->in_flight.load(std::memory_order_acquire)) return fail(e, NETRA_STATUS_BUSY, "cannot finalize bindings during launch");
+  for (const auto& profile : e->profiles)
+    for (const auto& op : profile.operations)
+      for (uint32_t i = 0; i < op.argc; ++i)
+        if (op.slots[i].spec.bindable && !op.slots[i].pointer)
+          return fail(e, NETRA_STATUS_BINDING, "all direct-launch pointers must be bound before finalization");
+  e->bindings_finalized.store(true, std::memory_order_release);
+  e->last_error[0] = '\0';
+  return NETRA_STATUS_OK;
+}
+
+extern "C" netra_status_t netra_engine_prepare_profile(netra_engine_t* e, uint32_t profile_id, cudaStream_t stream) {
+  if (!e || profile_id >= e->profiles.size()) return NETRA_STATUS_INVALID_ARGUMENT;
+  ProfileRecord& profile = e->profiles[profile_id];
+  if (!e->graph_enabled) return NETRA_STATUS_OK;
+  if (profile.graph_prepared) return NETRA_STATUS_OK;
+  if (profile.info.requires_fallback) return fail(e, NETRA_STATUS_FALLBACK_REQUIRED, "fallback profile cannot be captured by Netra runtime");
+  const netra_status_t finalized = netra_engine_finalize_bindings(e);
+  if (finalized != NETRA_STATUS_OK) return finalized;
+  cudaError_t err = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal);
+  if (err != cudaSuccess) return cuda_fail(e, "cudaStreamBeginCapture", err);
+  const netra_status_t status = direct_launch(e, profile, stream);
+  if (status != NETRA_STATUS_OK) {
+    (void)cudaStreamEndCapture(stream, &profile.graph);
+    if (profile.graph) (void)cudaGraphDestroy(profile.graph);
+    profile.graph = nullptr;
+    return status;
+  }
+  err = cudaStreamEndCapture(stream, &profile.graph);
+  if (err != cudaSuccess) return cuda_fail(e, "cudaStreamEndCapture", err);
+  err = cudaGraphInstantiate(&profile.graph_exec, profile.graph, 0);
+  if (err != cudaSuccess) return cuda_fail(e, "cudaGraphInstantiate", err);
+  profile.graph_prepared = true;
+  return NETRA_STATUS_OK;
+}
+
+extern "C" netra_status_t netra_engine_launch(netra_engine_t* e, uint32_t profile_id, const netra_launch_shape_t* shape,
+                                              cudaStream_t stream) {
+  if (!e || !shape || profile_id >= e->profiles.size()) return NETRA_STATUS_INVALID_ARGUMENT;
+  int device = -1;
+  const cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return cuda_fail(e, "cudaGetDevice", err);
+  if (device != e->device_id) return fail(e, NETRA_STATUS_UNSUPPORTED_TARGET, "caller stream/device does not belong to engine device");
+  ProfileRecord& profile = e->profiles[profile_id];
+  if (!guard_matches(profile.info, *shape))
+    return fail(e, NETRA_STATUS_UNSUPPORTED_PROFILE, "exact/bounded profile guard failed; framework fallback required");
+  if (profile.info.requires_fallback) return fail(e, NETRA_STATUS_FALLBACK_REQUIRED, "profile contains a framework fallback operation");
+  if (!profile.graph_prepared && !e->bindings_finalized.load(std::memory_order_acquire))
+    return fail(e, NETRA_STATUS_BINDING, "direct-launch bindings were not finalized");
+  e->in_flight.fetch_add(1, std::memory_order_acq_rel);
+  netra_status_t status;
+  if (profile.graph_prepared) {
+    const cudaError_t launch = cudaGraphLaunch(profile.graph_exec, stream);
+    status = launch == cudaSuccess ? NETRA_STATUS_OK : cuda_fail(e, "cudaGraphLaunch", launch);
+  } else {
+    status = direct_launch(e, profile, stream);
+  }
+  e->in_flight.fetch_sub(1, std::memory_order_acq_rel);
+  return status;
+}
+
+extern "C" netra_status_t netra_engine_launch_operation(netra_engine_t* e, uint32_t profile_id, uint32_t operation_index,
+                                                        const netra_launch_shape_t* shape, cudaStream_t stream) {
+  if (!e || !shape || profile_id >= e->profiles.size() || operation_index >= e->profiles[profile_id].operations.size())
+    return NETRA_STATUS_INVALID_ARGUMENT;
+  int device = -1;
+  const cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return cuda_fail(e, "cudaGetDevice", err);
+  if (device != e->device_id) return fail(e, NETRA_STATUS_UNSUPPORTED_TARGET, "caller stream/device does not belong to engine device");
+  ProfileRecord& profile = e->profiles[profile_id];
+  if (!guard_matches(profile.info, *shape))
+    return fail(e, NETRA_STATUS_UNSUPPORTED_PROFILE, "exact/bounded profile guard failed; framework fallback required");
+  if (profile.graph_prepared) return fail(e, NETRA_STATUS_BUSY, "individual operations cannot launch after graph preparation");
+  if (profile.operations[operation_index].spec.fallback) return fail(e, NETRA_STATUS_FALLBACK_REQUIRED, "operation requires framework fallback");
+  if (!e->bindings_finalized.load(std::memory_order_acquire)) return fail(e, NETRA_STATUS_BINDING, "direct-launch bindings were not finalized");
+  e->in_flight.fetch_add(1, std::memory_order_acq_rel);
+  const netra_status_t status = launch_one(e, profile.operations[operation_index], stream);
+  e->in_flight.fetch_sub(1, std::memory_order_acq_rel);
+  return status;
+}
+
+extern "C" netra_status_t netra_engine_launch_operation_bound(netra_engine_t* e, uint32_t profile_id, uint32_t operation_index,
+                                                              const netra_launch_shape_t* shape,
+                                                              const netra_pointer_binding_t* bindings, uint32_t binding_count,
+                                                              cudaStream_t stream) {
+  if (!e || !shape || profile_id >= e->profiles.size() || operation_index >= e->profiles[profile_id].operations.size() ||
+      (binding_count && !bindings) || binding_count > 16)
+    return NETRA_STATUS_INVALID_ARGUMENT;
+  int device = -1;
+  const cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return cuda_fail(e, "cudaGetDevice", err);
+  if (device != e->device_id) return fail(e, NETRA_STATUS_UNSUPPORTED_TARGET, "caller stream/device does not belong to engine device");
+  ProfileRecord& profile = e->profiles[profile_id];
+  if (!guard_matches(profile.info, *shape))
+    return fail(e, NETRA_STATUS_UNSUPPORTED_PROFILE, "exact/bounded profile guard failed; framework fallback required");
+  if (profile.graph_prepared) return fail(e, NETRA_STATUS_BUSY, "operation bindings are immutable after graph preparation");
+  OpRecord& op = profile.operations[operation_index];
+  if (op.spec.fallback) return fail(e, NETRA_STATUS_FALLBACK_REQUIRED, "operation requires framework fallback");
+  uint32_t expected = 0;
+  for (uint32_t i = 0; i < op.argc; ++i)
+    if (op.slots[i].spec.bindable) ++expected;
+  if (binding_count != expected) return fail(e, NETRA_STATUS_BINDING, "bound operation must provide every declared pointer slot");
+  for (uint32_t i = 0; i < binding_count; ++i) {
+    const uint32_t arg = bindings[i].argument_index;
+    if (bindings[i].reserved || !bindings[i].pointer || arg >= op.argc || !op.slots[arg].spec.bindable)
+      return fail(e, NETRA_STATUS_BINDING, "bound operation contains an invalid pointer slot");
+    for (uint32_t prev = 0; prev < i; ++prev)
+      if (bindings[prev].argument_index == arg) return fail(e, NETRA_STATUS_BINDING, "bound operation contains a duplicate pointer slot");
+  }
+  // caller-local launch storage: concurrent calls cannot mix pointer sets
+  void* values[kMaxArguments];
+  void* addresses[kMaxArguments];
+  alignas(64) CUtensorMap local_maps[16];
+  uint32_t maps_used = 0;
+  for (uint32_t i = 0; i < op.argc; ++i) addresses[i] = op.addresses[i];
+  for (uint32_t i = 0; i < binding_count; ++i) {
+    const uint32_t arg = bindings[i].argument_index;
+    if (op.slots[arg].spec.kind == ArgSpec::TensorMap) {
+      if (((uintptr_t)bindings[i].pointer & 15) != 0 || !encode_map(&local_maps[maps_used], bindings[i].pointer, op.slots[arg].spec.map))
+        return fail(e, NETRA_STATUS_BINDING, "cuTensorMapEncodeTiled rejected a bound pointer");
+      addresses[arg] = &local_maps[maps_used++];
+    } else {
+      values[arg] = bindings[i].pointer;
+      addresses[arg] = &values[arg];
+    }
+  }
+  e->in_flight.fetch_add(1, std::memory_order_acq_rel);
+  const netra_status_t status = launch_record(e, op, addresses, stream);
+  e->in_flight.fetch_sub(1, std::memory_order_acq_rel);
+  return status;
+}
+
+extern "C" const char* netra_engine_last_error(const netra_engine_t* e) { return e ? e->last_error.data() : "netra_engine is null"; }
+
+extern "C" void* netra_engine_workspace(const netra_engine_t* e) { return e ? e->workspace : nullptr; }
+
+extern "C" netra_status_t netra_engine_destroy(netra_engine_t* e) {
+  if (!e) return NETRA_STATUS_OK;
+  if (e->in_flight.load(std::memory_order_acquire)) return fail(e, NETRA_STATUS_BUSY, "launches remain in flight");
+  release(e);
+  delete e;
+  return NETRA_STATUS_OK;
+}

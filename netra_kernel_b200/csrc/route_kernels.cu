@@ -14,15 +14,14 @@
 namespace netra {
 
 // ------------------------------------------------------------------------------------------
-// Router logits.  logits[t,e] = RNE_bf16(exact dot(hidden[t,:], w[e,:])): BF16 products are
-// exact in FP64 and a 2048-term FP64 sum is far below half a BF16 ulp from the exact value, so
-// the single FP64->BF16 rounding is order independent in practice and bit-reproducible here
-// (fixed lane-strided order + xor tree).
-// grid (ceil(rows/4), 4), block 256: a warp owns 4 tokens x 8 experts.
+// Router logits.  logits[t,e] = RNE_bf16(exact dot(hidden[t,:], w[e,:])).  BF16 values convert to
+// FP64 exactly, their products are exact in FP64, and a 2048-term FP64 sum lies within 2^-42 of
+// the exact value relative to the sum of magnitudes - far below half a BF16 ulp - so the single
+// FP64->BF16 rounding gives the correctly rounded dot product whatever the summation order.
+// The sums run on the FP64 tensor cores (mma.sync m8n8k4): a warp owns 16 tokens x 16 experts
+// over one quarter of K; the four K-quarters are added in fixed order through shared memory.
+// grid (ceil(rows/16), 8), block 256 = 2 expert halves x 4 K-quarters.
 // ------------------------------------------------------------------------------------------
-constexpr int kRtTok = 4;
-constexpr int kRtExp = 8;
-
 __device__ __forceinline__ uint16_t f64_to_bf16_bits(double d) {
   long long bits = __double_as_longlong(d);
   uint16_t sign = (uint16_t)(((unsigned long long)bits >> 63) << 15);
@@ -33,57 +32,82 @@ __device__ __forceinline__ uint16_t f64_to_bf16_bits(double d) {
   return (uint16_t)(sign | (uint16_t)r);
 }
 
+// exact BF16 -> FP64 with integer ops (the FP64 pipe is kept for the MMAs)
+__device__ __forceinline__ double bf16_bits_to_f64(uint32_t b) {
+  const uint32_t e = b & 0x7f80u;
+  if (e != 0u && e != 0x7f80u)
+    return __hiloint2double((int)(((b & 0x8000u) << 16) | (((b & 0x7fffu) << 13) + 0x38000000u)), 0);
+  return (double)bf16_bits_to_f32(b);   // zero, subnormal, inf, nan
+}
+
+__device__ __forceinline__ void dmma_m8n8k4(double& c0, double& c1, double a, double b) {
+  asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0, %1}, {%2}, {%3}, {%0, %1};"
+               : "+d"(c0), "+d"(c1) : "d"(a), "d"(b));
+}
+
 extern "C" __global__ void __launch_bounds__(256)
 netra_router_logits_bf16_sm100(uint16_t* __restrict__ logits, const uint16_t* __restrict__ hidden,
                                const uint16_t* __restrict__ weight, uint32_t rows) {
-  __shared__ uint4 sh[kRtTok][kHidden / 8];
-  const int tok0 = blockIdx.x * kRtTok;
+  __shared__ double part[4][2][16][16];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int i = threadIdx.x; i < kRtTok * (kHidden / 8); i += blockDim.x) {
-    int t = i / (kHidden / 8), c = i % (kHidden / 8);
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (tok0 + t < (int)rows) v = reinterpret_cast<const uint4*>(hidden + (size_t)(tok0 + t) * kHidden)[c];
-    sh[t][c] = v;
-  }
-  __syncthreads();
-  const int e0 = blockIdx.y * 64 + warp * kRtExp;
-  double acc[kRtTok][kRtExp];
+  const int kq = warp & 3, eh = warp >> 2;           // K-quarter, expert half
+  const int tok0 = blockIdx.x * 16;
+  const int exp0 = blockIdx.y * 32 + eh * 16;
+  const int frow = lane >> 2, fk = lane & 3;         // fragment row (token or expert), K position
+  double acc[2][2][2];                               // [token tile][expert tile][2 columns]
 #pragma unroll
-  for (int t = 0; t < kRtTok; ++t)
+  for (int i = 0; i < 8; ++i) (&acc[0][0][0])[i] = 0.0;
+  // Any permutation of K is valid as long as both operands use it: in MMA step j of a 32-wide
+  // chunk, fragment position fk holds element k = chunk + 8*fk + j, so a lane needs 8 consecutive
+  // BF16 (one 16-byte load) per row and chunk.
+  const int kbase = kq * (kHidden / 4);
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+#pragma unroll 2
+  for (int kc = 0; kc < kHidden / 4; kc += 32) {
+    const int k = kbase + kc + 8 * fk;
+    uint4 hv[2], wv[2];
 #pragma unroll
-    for (int e = 0; e < kRtExp; ++e) acc[t][e] = 0.0;
-  for (int i = 0; i < kHidden / 256; ++i) {
-    const int c = i * 32 + lane;  // 16-byte chunk (8 values) index along K
-    uint4 hv[kRtTok];
+    for (int m = 0; m < 2; ++m) {
+      const int t = tok0 + m * 8 + frow;
+      hv[m] = t < (int)rows ? __ldg(reinterpret_cast<const uint4*>(hidden + (size_t)t * kHidden + k)) : zero;
+      wv[m] = __ldg(reinterpret_cast<const uint4*>(weight + (size_t)(exp0 + m * 8 + frow) * kHidden + k));
+    }
 #pragma unroll
-    for (int t = 0; t < kRtTok; ++t) hv[t] = sh[t][c];
+    for (int j = 0; j < 8; ++j) {
+      double a[2], b[2];
 #pragma unroll
-    for (int e = 0; e < kRtExp; ++e) {
-      uint4 wv = __ldg(reinterpret_cast<const uint4*>(weight + (size_t)(e0 + e) * kHidden) + c);
-      const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        double w_lo = (double)bf16_bits_to_f32(ww[q] & 0xffffu);
-        double w_hi = (double)bf16_bits_to_f32(ww[q] >> 16);
-#pragma unroll
-        for (int t = 0; t < kRtTok; ++t) {
-          const uint32_t hh = (&hv[t].x)[q];
-          acc[t][e] = fma((double)bf16_bits_to_f32(hh & 0xffffu), w_lo, acc[t][e]);
-          acc[t][e] = fma((double)bf16_bits_to_f32(hh >> 16), w_hi, acc[t][e]);
-        }
+      for (int m = 0; m < 2; ++m) {
+        const uint32_t hw = (&hv[m].x)[j >> 1], ww = (&wv[m].x)[j >> 1];
+        a[m] = bf16_bits_to_f64((j & 1) ? (hw >> 16) : (hw & 0xffffu));
+        b[m] = bf16_bits_to_f64((j & 1) ? (ww >> 16) : (ww & 0xffffu));
       }
+#pragma unroll
+      for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int n = 0; n < 2; ++n) dmma_m8n8k4(acc[m][n][0], acc[m][n][1], a[m], b[n]);
     }
   }
 #pragma unroll
-  for (int t = 0; t < kRtTok; ++t)
+  for (int m = 0; m < 2; ++m)
 #pragma unroll
-    for (int e = 0; e < kRtExp; ++e) {
-      double v = acc[t][e];
-#pragma unroll
-      for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
-      if (lane == 0 && tok0 + t < (int)rows)
-        logits[(size_t)(tok0 + t) * kRouted + e0 + e] = f64_to_bf16_bits(v);
+    for (int n = 0; n < 2; ++n) {
+      part[kq][eh][m * 8 + frow][n * 8 + fk * 2] = acc[m][n][0];
+      part[kq][eh][m * 8 + frow][n * 8 + fk * 2 + 1] = acc[m][n][1];
     }
+  __syncthreads();
+  // 16 tokens x 32 experts: a thread finishes two adjacent experts of one token
+  const int t = threadIdx.x >> 4, e2 = (threadIdx.x & 15) * 2;
+  if (tok0 + t < (int)rows) {
+    uint32_t packed = 0;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int e = e2 + i;
+      const double v = ((part[0][e >> 4][t][e & 15] + part[1][e >> 4][t][e & 15]) + part[2][e >> 4][t][e & 15]) +
+                       part[3][e >> 4][t][e & 15];
+      packed |= (uint32_t)f64_to_bf16_bits(v) << (16 * i);
+    }
+    *reinterpret_cast<uint32_t*>(logits + (size_t)(tok0 + t) * kRouted + blockIdx.y * 32 + e2) = packed;
+  }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -278,6 +302,72 @@ netra_moe_sort_scatter_sm100(int32_t* __restrict__ perm, int32_t* __restrict__ i
   __syncthreads();
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
+    const int pair = wstart + c * 32 + lane;
+    const int e = my_e[c];
+    const unsigned active = __ballot_sync(0xffffffffu, e >= 0);
+    if (e >= 0) {
+      const unsigned same = __match_any_sync(active, e);
+      const int rank = __popc(same & ((1u << lane) - 1u));
+      const int pos = wbase[warp][e] + rank;
+      perm[pos] = pair;
+      inv_perm[pair] = pos;
+      __syncwarp(active);
+      if (rank == 0) wbase[warp][e] += __popc(same);
+    }
+    __syncwarp();
+  }
+}
+
+// Whole sort in one block for up to 8192 pairs (rows <= 1024): 32 warps x 256 consecutive pairs.
+// Same result as the three-launch path; no global scratch.  grid 1, block 1024.
+constexpr int kSortSmallMaxRows = 1024;
+
+extern "C" __global__ void __launch_bounds__(1024)
+netra_moe_sort_small_sm100(int32_t* __restrict__ perm, int32_t* __restrict__ inv_perm, int32_t* __restrict__ counts,
+                           int32_t* __restrict__ offsets, const int32_t* __restrict__ ids9, uint32_t rows) {
+  __shared__ int wbase[32][kRouted];
+  __shared__ int warp_tot[8];
+  const int pairs = (int)rows * kTopK;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < 32 * kRouted; i += 1024) (&wbase[0][0])[i] = 0;
+  __syncthreads();
+  const int wstart = warp * 256;
+  int my_e[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const int pair = wstart + c * 32 + lane;
+    my_e[c] = pair < pairs ? pair_expert(ids9, pair) : -1;
+    if (my_e[c] >= 0) atomicAdd(&wbase[warp][my_e[c]], 1);   // counts only: order independent
+  }
+  __syncthreads();
+  if (threadIdx.x < kRouted) {
+    const int e = threadIdx.x;
+    int total = 0;
+#pragma unroll 8
+    for (int w = 0; w < 32; ++w) total += wbase[w][e];
+    counts[e] = total;
+    int incl = total;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      int o = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += o;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    int before = 0;
+    for (int w = 0; w < warp; ++w) before += warp_tot[w];
+    int running = before + incl - total;
+    offsets[e] = running;
+    if (e == kRouted - 1) {
+      offsets[kRouted] = running + total;
+      offsets[kRouted + 1] = running + total + (int)rows;
+    }
+#pragma unroll 8
+    for (int w = 0; w < 32; ++w) { int c = wbase[w][e]; wbase[w][e] = running; running += c; }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
     const int pair = wstart + c * 32 + lane;
     const int e = my_e[c];
     const unsigned active = __ballot_sync(0xffffffffu, e >= 0);

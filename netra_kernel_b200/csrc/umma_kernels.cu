@@ -1,23 +1,26 @@
 // Block-scaled FP8 grouped GEMMs on the sm_100a tensor cores (tcgen05 + TMEM), fed by TMA.
 //
 // Both expert projections run "swap-AB": the 128 weight rows of a tile are the MMA M dimension
-// and the (few) token rows of an expert are the MMA N dimension, so a decode-sized expert
+// and the token rows of an expert are the MMA N dimension (16..64), so a decode-sized expert
 // (about 8 rows) streams its weights exactly once with no padded M work.
 //
 //   gate_up (replaces kernels/gfx950/templates/moe/decode/gate_up_mfma.inc:13-95 and
 //            kernels/gfx950/templates/moe/decode/silu_quant.inc:54-169):
 //     tile = expert x 128 intermediate channels: W13 gate rows [c*128, +128) and up rows
 //     [512 + c*128, +128) against the expert's token rows; per K-block (128) the raw FP8 partial
-//     sums leave TMEM and are promoted in FP32 as acc += (part * a_scale[row,kb]) * w_scale[kb]
-//     (gfx950 order, kernels/gfx950/templates/common/mfma.inc:20-24); the epilogue forms
+//     sums leave TMEM and are promoted in FP32 as acc = fma(part, a_scale[row,kb] * w_scale[kb], acc)
+//     (the order of kernels/gfx950/templates/moe/prefill/fused_splitk2/gate_up.inc:275-300); the epilogue forms
 //     bf16(silu(gate) * up), takes the per-128 amax (the tile is exactly one quantisation
 //     group per row), and stores FP8 codes + FP32 scale.
 //   down (replaces kernels/gfx950/templates/moe/decode/down_reduce_mfma_2wave.inc:73-217,
 //         the GEMM part): tile = expert x 128 output columns, K = 512, FP32 rows written in
 //     expert-sorted order for the slot-ordered combine kernel.
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer (owns TMEM),
-// warps 2..5 = promotion/epilogue (TMEM lane quadrant = warp id % 4).
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer (owns TMEM),
+// warps 2..9 = promotion/epilogue (TMEM lane quadrant = warp id % 4; warps 2..5 own token
+// first half of an item's token columns, warps 6..9 the second half).
+// Weight tiles come either from the checkpoint's row-major layout or from the tiled layout
+// written by netra_moe_repack_tiles_sm100 (one contiguous 16 KiB block per tile and K-block).
 // Every mbarrier wait is bounded; on expiry the CTA records a code in status[] and drains.
 #include <cuda.h>
 
@@ -27,12 +30,21 @@ namespace netra {
 
 constexpr int kTileRows = 128;          // weight rows per MMA (UMMA M)
 constexpr int kTokMax = 64;             // token rows per work item (UMMA N <= 64)
+constexpr int kColsPerGroup = 32;       // token columns owned by one epilogue warp group
 constexpr int kWTileBytes = kTileRows * kBlock;   // 16 KiB: 128 rows x 128 K bytes
 constexpr int kTokTileBytes = kTokMax * kBlock;   // 8 KiB
-constexpr int kMaxGroups = 257;
+constexpr int kGemmThreads = 320;
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 enum : uint32_t { kStatusOk = 0, kStatusProducerTimeout = 1, kStatusMmaTimeout = 2, kStatusEpilogueTimeout = 3 };
+
+#ifdef NETRA_TRACE
+// Debug builds only: per-K-block SM-clock timestamps of CTA 0 (never compiled into the product library).
+__device__ long long g_trace[8][256];
+#define NETRA_TRACE_MARK(role, idx) do { if (blockIdx.x == 0 && (idx) < 256) g_trace[role][idx] = clock64(); } while (0)
+#else
+#define NETRA_TRACE_MARK(role, idx) do { } while (0)
+#endif
 
 // ---------------------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -63,10 +75,26 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
   return false;
 }
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+__device__ __forceinline__ uint64_t policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, uint64_t policy) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y) : "memory");
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y), "l"(policy) : "memory");
+}
+// contiguous global -> shared copy; both addresses 16-byte aligned, size a multiple of 16
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"((uint64_t)src), "r"(bytes), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
@@ -87,18 +115,32 @@ __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float v[16]) {
-  uint32_t r[16];
+// 32 lanes x 16 consecutive 32-bit columns; the caller issues tmem_ld_wait() before reading r[]
+__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t r[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr) : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
-__device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld8_nowait(uint32_t taddr, uint32_t r[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// 1/x for a normal positive x: hardware approximation plus one Newton step (the reference's quantiser does
+// the same, kernels/gfx950/templates/moe/decode/silu_quant.inc:140-150)
+__device__ __forceinline__ float rcp_newton(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return fmaf(r, fmaf(-x, r, 1.0f), r);
+}
+// barrier among the 128 threads of one epilogue warp group (ids 1 and 2)
+__device__ __forceinline__ void group_barrier(int group) {
+  if (group == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+  else asm volatile("bar.sync 2, 128;" ::: "memory");
+}
 
 // K-major, 128-byte-swizzled operand tile: rows of 128 bytes, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr) {
@@ -113,12 +155,12 @@ __device__ __forceinline__ uint32_t make_idesc(uint32_t n) {
 // ---------------------------------------------------------------------------- work items
 struct Item {
   int group;    // expert slab index
-  int ntile;    // 128-row weight tile inside the slab
+  int ntile;    // first 128-row weight tile of the item inside the slab
   int row0;     // first token row (expert-sorted row space)
   int m_valid;  // token rows in this item (1..64)
 };
 
-template <int kNTiles>
+template <int kNTiles, int kSubTiles>
 __device__ __forceinline__ Item decode_item(int item, const int* item_pre, const int* offs, int num_groups) {
   int lo = 0, hi = num_groups;            // largest idx with item_pre[idx] <= item
   while (hi - lo > 1) {
@@ -128,7 +170,7 @@ __device__ __forceinline__ Item decode_item(int item, const int* item_pre, const
   const int local = item - item_pre[lo];
   Item it;
   it.group = lo == 0 ? num_groups - 1 : lo - 1;   // the last group (shared expert) is scheduled first
-  it.ntile = local % kNTiles;
+  it.ntile = (local % kNTiles) * kSubTiles;
   it.row0 = offs[it.group] + (local / kNTiles) * kTokMax;
   it.m_valid = min(kTokMax, offs[it.group + 1] - it.row0);
   return it;
@@ -139,37 +181,48 @@ template <bool kGateUp>
 struct Cfg {
   static constexpr int kATiles = kGateUp ? 2 : 1;
   static constexpr int kKBlocks = kGateUp ? kHiddenBlocks : kInterBlocks;
-  static constexpr int kNTiles = kGateUp ? kInter / kTileRows : kHidden / kTileRows;   // 4 | 16
+  static constexpr int kSubTiles = kGateUp ? 1 : 4;       // consecutive weight tiles per work item (same token rows)
+  static constexpr int kNTiles = (kGateUp ? kInter / kTileRows : kHidden / kTileRows) / kSubTiles;   // items per slab and chunk: 4 | 4
   static constexpr int kSlabRows = kGateUp ? 2 * kInter : kHidden;                     // 1024 | 2048
-  static constexpr int kStages = kGateUp ? 4 : 6;
+  static constexpr int kSlabTiles = kSlabRows / kTileRows;                             // 8 | 16
+  static constexpr int kKbPerStep = kGateUp ? 1 : 4;      // K-blocks the MMA warp issues per accumulator hand-off
+  static constexpr int kAccCols = kKbPerStep * kATiles * kTokMax;                      // TMEM columns per hand-off: 128 | 256
+  static constexpr int kAccStages = 512 / kAccCols;                                    // 4 | 2
+  static constexpr int kStages = kGateUp ? 5 : 8;
   static constexpr int kStageBytes = kATiles * kWTileBytes + kTokTileBytes;            // 40 KiB | 24 KiB
-  static constexpr int kTmemCols = 2 * kATiles * kTokMax;                              // 256 | 128
-  static constexpr int kEpiBytes = kGateUp ? kTokMax * 272 : kTokMax * 132 * 4;        // staging tile
-  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kEpiBytes + kTokMax * kKBlocks * 4 +
-                                    kATiles * kKBlocks * 4 + 2 * 264 * 4 + 256;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kXsBytes = kTokMax * kKBlocks * 4;                              // 4 KiB | 1 KiB
+  static constexpr int kWsBytes = kKBlocks * 4;                                        // 64 B | 16 B per tile
+  static constexpr int kItemList = 256;                                                // work items of this CTA decoded once
+  static constexpr int kScaleSlotBytes = kXsBytes + 128;                               // xs, then ws tiles
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + 2 * kScaleSlotBytes + 2 * 4 * kColsPerGroup * 4 +
+                                    2 * 264 * 4 + kItemList * 16 + 256;
 };
 
 template <bool kGateUp>
 __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const CUtensorMap* tm_x32,
-                                                  const CUtensorMap* tm_x64, const float* __restrict__ x_scale,
-                                                  const float* __restrict__ w_scale, const int32_t* __restrict__ offsets,
-                                                  uint8_t* __restrict__ h_fp8, float* __restrict__ h_scale,
-                                                  float* __restrict__ down, uint32_t num_groups, uint32_t* status) {
+                                                  const CUtensorMap* tm_x64, const CUtensorMap* tm_x128,
+                                                  const float* __restrict__ x_scale, const float* __restrict__ w_scale,
+                                                  const int32_t* __restrict__ offsets, uint8_t* __restrict__ h_fp8,
+                                                  float* __restrict__ h_scale, float* __restrict__ down,
+                                                  uint32_t num_groups, uint32_t w_tiled, uint32_t* status) {
   using C = Cfg<kGateUp>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* stage_base = smem;
-  uint8_t* epi_tile = stage_base + C::kStages * C::kStageBytes;
-  float* xs_tile = reinterpret_cast<float*>(epi_tile + C::kEpiBytes);            // [64][kKBlocks]
-  float* ws_tile = xs_tile + kTokMax * C::kKBlocks;                              // [kATiles][kKBlocks]
-  int* offs = reinterpret_cast<int*>(ws_tile + C::kATiles * C::kKBlocks);        // [264]
+  uint8_t* scale_base = stage_base + C::kStages * C::kStageBytes;                // 2 slots
+  uint32_t* red = reinterpret_cast<uint32_t*>(scale_base + 2 * C::kScaleSlotBytes);   // [2 groups][4 warps][64]
+  int* offs = reinterpret_cast<int*>(red + 2 * 4 * kColsPerGroup);               // [264]
   int* item_pre = offs + 264;                                                    // [264]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(item_pre + 264);
+  int4* item_list = reinterpret_cast<int4*>(item_pre + 264);                     // [kItemList]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(item_list + C::kItemList);
   uint64_t* full_bar = bars;                       // [kStages]
   uint64_t* empty_bar = bars + C::kStages;         // [kStages]
-  uint64_t* tfull_bar = bars + 2 * C::kStages;     // [2]
-  uint64_t* tempty_bar = tfull_bar + 2;            // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  uint64_t* tfull_bar = bars + 2 * C::kStages;     // [C::kAccStages]
+  uint64_t* tempty_bar = tfull_bar + C::kAccStages;   // [C::kAccStages]
+  uint64_t* sfull_bar = tempty_bar + C::kAccStages;   // [2]
+  uint64_t* sempty_bar = sfull_bar + 2;            // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sempty_bar + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -179,7 +232,8 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
   for (int i = threadIdx.x; i <= groups; i += blockDim.x) offs[i] = offsets[i];
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&tfull_bar[a]), 1); mbar_init(smem_u32(&tempty_bar[a]), 4); }
+    for (int a = 0; a < C::kAccStages; ++a) { mbar_init(smem_u32(&tfull_bar[a]), 1); mbar_init(smem_u32(&tempty_bar[a]), 8); }
+    for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&sfull_bar[a]), 1); mbar_init(smem_u32(&sempty_bar[a]), 8); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -216,180 +270,252 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const int total_items = item_pre[groups];
+  // this CTA's first kItemList work items, decoded once for all roles
+  for (int n = threadIdx.x; n < C::kItemList; n += blockDim.x) {
+    const int item = blockIdx.x + n * gridDim.x;
+    if (item < total_items) {
+      const Item w = decode_item<C::kNTiles, C::kSubTiles>(item, item_pre, offs, groups);
+      item_list[n] = make_int4(w.group, w.ntile, w.row0, w.m_valid);
+    }
+  }
+  __syncthreads();
+  auto get_item = [&](int n, int item) -> Item {
+    if (n < C::kItemList) { const int4 v = item_list[n]; Item w; w.group = v.x; w.ntile = v.y; w.row0 = v.z; w.m_valid = v.w; return w; }
+    return decode_item<C::kNTiles, C::kSubTiles>(item, item_pre, offs, groups);
+  };
 
   if (warp == 0) {
     // =========================== TMA producer ===========================
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)tm_w) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)tm_x32) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)tm_x64) : "memory");
-      uint32_t it = 0;
+      const uint64_t pol_w = policy_evict_first();     // weights are read once per launch
+      const uint64_t pol_x = policy_evict_last();      // token rows are re-read by every tile of the expert
+      uint32_t it = 0, n_item = 0;
       bool ok = true;
-      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
-        const Item w = decode_item<C::kNTiles>(item, item_pre, offs, groups);
-        const bool small = w.m_valid <= 32;
-        const uint32_t bytes = C::kATiles * kWTileBytes + (small ? 32 : 64) * kBlock;
-        const int wrow = w.group * C::kSlabRows + w.ntile * kTileRows;
+      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x, ++n_item) {
+        const Item w = get_item((int)n_item, item);
+        const int box = w.m_valid <= 32 ? 32 : 64;
+        const CUtensorMap* tm_x = box == 32 ? tm_x32 : tm_x64;
+        const uint32_t bytes = C::kATiles * kWTileBytes + box * kBlock;
+        // scales of this item: token-row scales [128][KB] and the tile's weight scales
+        {
+          const int slot = n_item & 1;
+          if (!mbar_wait(smem_u32(&sempty_bar[slot]), ((n_item >> 1) & 1) ^ 1, abort_flag)) {
+            status[0] = kStatusProducerTimeout; *abort_flag = 1; ok = false; break;
+          }
+          const uint32_t sbar = smem_u32(&sfull_bar[slot]);
+          const uint32_t sdst = smem_u32(scale_base + slot * C::kScaleSlotBytes);
+          mbar_expect_tx(sbar, C::kXsBytes + C::kATiles * C::kSubTiles * C::kWsBytes);
+          bulk_load(sdst, x_scale + (size_t)w.row0 * C::kKBlocks, C::kXsBytes, sbar);
+          const float* wsrc = w_scale + ((size_t)w.group * C::kSlabTiles + w.ntile) * C::kKBlocks;
+          bulk_load(sdst + C::kXsBytes, wsrc, C::kSubTiles * C::kWsBytes, sbar);   // the item's tiles are consecutive
+          if (kGateUp) bulk_load(sdst + C::kXsBytes + C::kWsBytes, wsrc + (kInter / kBlock) * C::kKBlocks, C::kWsBytes, sbar);
+        }
+        for (int sub = 0; ok && sub < C::kSubTiles; ++sub)
         for (int kb = 0; kb < C::kKBlocks; ++kb, ++it) {
           const int s = it % C::kStages;
           if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / C::kStages) & 1) ^ 1, abort_flag)) {
             status[0] = kStatusProducerTimeout; *abort_flag = 1; ok = false; break;
           }
+          NETRA_TRACE_MARK(0, it);
           const uint32_t bar = smem_u32(&full_bar[s]);
           const uint32_t dst = smem_u32(stage_base + s * C::kStageBytes);
           mbar_expect_tx(bar, bytes);
-          tma_load_2d(dst, tm_w, bar, kb * kBlock, wrow);
-          if (kGateUp) tma_load_2d(dst + kWTileBytes, tm_w, bar, kb * kBlock, wrow + kInter);
-          tma_load_2d(dst + C::kATiles * kWTileBytes, small ? tm_x32 : tm_x64, bar, kb * kBlock, w.row0);
+          int wx, wy0, wy1;
+          if (w_tiled) {   // one contiguous 16 KiB block per (slab tile, K-block)
+            wx = 0;
+            wy0 = ((w.group * C::kSlabTiles + w.ntile + sub) * C::kKBlocks + kb) * kTileRows;
+            wy1 = wy0 + (kInter / kTileRows) * C::kKBlocks * kTileRows;
+          } else {
+            wx = kb * kBlock;
+            wy0 = w.group * C::kSlabRows + (w.ntile + sub) * kTileRows;
+            wy1 = wy0 + kInter;
+          }
+          tma_load_2d(dst, tm_w, bar, wx, wy0, pol_w);
+          if (kGateUp) tma_load_2d(dst + kWTileBytes, tm_w, bar, wx, wy1, pol_w);
+          tma_load_2d(dst + C::kATiles * kWTileBytes, tm_x, bar, kb * kBlock, w.row0, pol_x);
         }
       }
     }
   } else if (warp == 1) {
     // =========================== MMA issuer ===========================
     if (lane == 0) {
-      uint32_t it = 0, jt = 0;
+      uint32_t it = 0, jt = 0, n_item = 0;
       bool ok = true;
-      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
-        const Item w = decode_item<C::kNTiles>(item, item_pre, offs, groups);
+      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x, ++n_item) {
+        const Item w = get_item((int)n_item, item);
         const uint32_t n_mma = (uint32_t)((w.m_valid + 15) & ~15);
         const uint32_t idesc = make_idesc(n_mma);
-        for (int kb = 0; kb < C::kKBlocks; ++kb, ++it, ++jt) {
-          const int s = it % C::kStages, a = jt & 1;
-          if (!mbar_wait(smem_u32(&tempty_bar[a]), ((jt >> 1) & 1) ^ 1, abort_flag) ||
-              !mbar_wait(smem_u32(&full_bar[s]), (it / C::kStages) & 1, abort_flag)) {
+        for (int step = 0; ok && step < C::kSubTiles * C::kKBlocks / C::kKbPerStep; ++step, ++jt) {
+          const int a = jt % C::kAccStages;
+          NETRA_TRACE_MARK(1, it);
+          if (!mbar_wait(smem_u32(&tempty_bar[a]), ((jt / C::kAccStages) & 1) ^ 1, abort_flag)) {
             status[0] = kStatusMmaTimeout; *abort_flag = 1; ok = false; break;
           }
-          tc_fence_after();
-          const uint32_t sa = smem_u32(stage_base + s * C::kStageBytes);
-          const uint64_t bdesc = make_smem_desc(sa + C::kATiles * kWTileBytes);
+          NETRA_TRACE_MARK(2, it);
+#pragma unroll 1
+          for (int q = 0; q < C::kKbPerStep; ++q, ++it) {
+            const int s = it % C::kStages;
+            if (!mbar_wait(smem_u32(&full_bar[s]), (it / C::kStages) & 1, abort_flag)) {
+              status[0] = kStatusMmaTimeout; *abort_flag = 1; ok = false; break;
+            }
+            NETRA_TRACE_MARK(3, it);
+            tc_fence_after();
+            const uint32_t sa = smem_u32(stage_base + s * C::kStageBytes);
+            const uint64_t bdesc = make_smem_desc(sa + C::kATiles * kWTileBytes);
+            const uint32_t d0 = tmem_base + (uint32_t)(a * C::kAccCols + q * C::kATiles * kTokMax);
+            // the two tiles accumulate into different TMEM columns: alternate them so that consecutive
+            // MMAs never depend on each other
 #pragma unroll
-          for (int tile = 0; tile < C::kATiles; ++tile) {
-            const uint64_t adesc = make_smem_desc(sa + tile * kWTileBytes);
-            const uint32_t d = tmem_base + (uint32_t)(a * C::kATiles * kTokMax + tile * kTokMax);
+            for (int k = 0; k < kBlock / 32; ++k) {
 #pragma unroll
-            for (int k = 0; k < kBlock / 32; ++k) umma_f8(d, adesc + 2 * k, bdesc + 2 * k, idesc, k > 0);
+              for (int tile = 0; tile < C::kATiles; ++tile)
+                umma_f8(d0 + (uint32_t)(tile * kTokMax), make_smem_desc(sa + tile * kWTileBytes) + 2 * k, bdesc + 2 * k, idesc, k > 0);
+            }
+            umma_commit(smem_u32(&empty_bar[s]));
+            NETRA_TRACE_MARK(4, it);
           }
-          umma_commit(smem_u32(&empty_bar[s]));
-          umma_commit(smem_u32(&tfull_bar[a]));
+          if (ok) umma_commit(smem_u32(&tfull_bar[a]));
         }
       }
     }
   } else {
-    // =========================== promotion + epilogue (128 threads) ===========================
-    const int et = threadIdx.x - 64;         // 0..127
+    // =========================== promotion + epilogue (2 groups x 128 threads) ===========================
+    const int grp = (warp - 2) >> 2;         // the two groups split an item's token columns in halves
+    const int gw = (warp - 2) & 3;           // warp inside the group
     const int quad = warp & 3;               // TMEM lane quadrant this warp may read
     const int r = quad * 32 + lane;          // weight row inside the tile == TMEM lane
-    uint32_t jt = 0;
+    uint32_t jt = 0, n_item = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
-      const Item w = decode_item<C::kNTiles>(item, item_pre, offs, groups);
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++n_item) {
+      const Item w = get_item((int)n_item, item);
       const int n_mma = (w.m_valid + 15) & ~15;
-      // scales of this item -> smem
-      for (int i = et; i < kTokMax * C::kKBlocks; i += 128) {
-        const int c = i / C::kKBlocks;
-        xs_tile[i] = c < w.m_valid ? x_scale[(size_t)(w.row0 + c) * C::kKBlocks + (i % C::kKBlocks)] : 0.0f;
+      const int col_base = grp * (n_mma >> 1);   // this group's first column; it owns n_mma/2 columns
+      const int nsl = n_mma >> 4;                // ... in 8-column slices: 1..4
+      const int slot = n_item & 1;
+      const float* xs_tile = reinterpret_cast<const float*>(scale_base + slot * C::kScaleSlotBytes);
+      const float* ws_tile = xs_tile + kTokMax * C::kKBlocks;
+      if (warp == 2 && lane == 0) NETRA_TRACE_MARK(7, n_item * 8 + 5);
+      if (ok && !mbar_wait(smem_u32(&sfull_bar[slot]), (n_item >> 1) & 1, abort_flag)) {
+        status[0] = kStatusEpilogueTimeout; *abort_flag = 1; ok = false;
       }
-      if (et < C::kATiles * C::kKBlocks) {
-        const int tile = et / C::kKBlocks, kb = et % C::kKBlocks;
-        const int nb = kGateUp ? tile * (kInter / kBlock) + w.ntile : w.ntile;
-        ws_tile[et] = w_scale[((size_t)w.group * (C::kSlabRows / kBlock) + nb) * C::kKBlocks + kb];
-      }
-      epi_barrier();
-      float acc[C::kATiles][kTokMax];
+      if (warp == 2 && lane == 0) NETRA_TRACE_MARK(7, n_item * 8 + 6);
+      const int my_cols = min(n_mma >> 1, w.m_valid - col_base);         // columns holding real rows; may be <= 0
+#pragma unroll 1
+      for (int sub = 0; sub < C::kSubTiles; ++sub) {
+      const int ntile = w.ntile + sub;
+      float acc[C::kATiles][kColsPerGroup];
 #pragma unroll
       for (int tile = 0; tile < C::kATiles; ++tile)
 #pragma unroll
-        for (int c = 0; c < kTokMax; ++c) acc[tile][c] = 0.0f;
-      for (int kb = 0; kb < C::kKBlocks; ++kb, ++jt) {
-        const int a = jt & 1;
-        if (ok && !mbar_wait(smem_u32(&tfull_bar[a]), (jt >> 1) & 1, abort_flag)) {
+        for (int c = 0; c < kColsPerGroup; ++c) acc[tile][c] = 0.0f;
+      for (int step = 0; step < C::kKBlocks / C::kKbPerStep; ++step, ++jt) {
+        const int a = jt % C::kAccStages;
+        if (ok && !mbar_wait(smem_u32(&tfull_bar[a]), (jt / C::kAccStages) & 1, abort_flag)) {
           status[0] = kStatusEpilogueTimeout; *abort_flag = 1; ok = false;
         }
         if (!ok) continue;
+        if (warp == 2 && lane == 0) NETRA_TRACE_MARK(5, jt);
         tc_fence_after();
-        const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * C::kATiles * kTokMax);
 #pragma unroll
-        for (int tile = 0; tile < C::kATiles; ++tile) {
-          const float ws = ws_tile[tile * C::kKBlocks + kb];
+        for (int q = 0; q < C::kKbPerStep; ++q) {
+        const int kb = step * C::kKbPerStep + q;
+        const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) +
+                               (uint32_t)(a * C::kAccCols + q * C::kATiles * kTokMax + col_base);
+        // all TMEM loads of this K-block are issued before the single wait
+        uint32_t v[C::kATiles][4][8];
 #pragma unroll
-          for (int sl = 0; sl < kTokMax / 16; ++sl) {
-            if (sl * 16 < n_mma) {
-              float v[16];
-              tmem_ld16(tbase + (uint32_t)(tile * kTokMax + sl * 16), v);
+        for (int sl = 0; sl < 4; ++sl)
+          if (sl < nsl) {
 #pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                const float xs = xs_tile[(sl * 16 + i) * C::kKBlocks + kb];
-                acc[tile][sl * 16 + i] = __fadd_rn(acc[tile][sl * 16 + i], __fmul_rn(__fmul_rn(v[i], xs), ws));
+            for (int tile = 0; tile < C::kATiles; ++tile) tmem_ld8_nowait(tbase + (uint32_t)(tile * kTokMax + sl * 8), v[tile][sl]);
+          }
+        tmem_ld_wait();
+        if (q == C::kKbPerStep - 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[a]));   // the partials now live in registers
+        }
+        float ws[C::kATiles];
+#pragma unroll
+        for (int tile = 0; tile < C::kATiles; ++tile) ws[tile] = ws_tile[(sub + tile) * C::kKBlocks + kb];
+#pragma unroll
+        for (int sl = 0; sl < 4; ++sl)
+          if (sl < nsl) {
+            const float* xs = xs_tile + (col_base + sl * 8) * C::kKBlocks + kb;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float x = xs[i * C::kKBlocks];
+#pragma unroll
+              for (int tile = 0; tile < C::kATiles; ++tile)
+                acc[tile][sl * 8 + i] = fmaf(__uint_as_float(v[tile][sl][i]), __fmul_rn(x, ws[tile]), acc[tile][sl * 8 + i]);
+            }
+          }
+        }   // K-block of the step
+        if (warp == 2 && lane == 0) NETRA_TRACE_MARK(6, jt);
+      }
+      if (sub == C::kSubTiles - 1) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sempty_bar[slot]));   // the scale tiles were last read above
+      }
+      // ---- tile epilogue (columns of this group that hold real rows), eight columns at a time
+      if (warp == 2 && lane == 0) NETRA_TRACE_MARK(7, n_item * 8 + 0);
+      if constexpr (kGateUp) {
+        uint32_t* my_red = red + (grp * 4 + gw) * kColsPerGroup;
+#pragma unroll
+        for (int c0 = 0; c0 < kColsPerGroup; c0 += 8) {
+          if (c0 < my_cols) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {     // independent chains first ...
+              const float g = acc[0][c0 + j];
+              const float silu = __fdividef(g, 1.0f + __expf(-g));
+              acc[0][c0 + j] = bf16_round(__fmul_rn(silu, acc[C::kATiles - 1][c0 + j]));
+            }
+            uint32_t mine = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {     // ... then the warp reductions back to back
+              const uint32_t m = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(acc[0][c0 + j])));
+              if (lane == j) mine = m;
+            }
+            if (lane < 8) my_red[c0 + lane] = mine;
+          }
+        }
+        if (warp == 2 && lane == 0) NETRA_TRACE_MARK(7, n_item * 8 + 1);
+        group_barrier(grp);
+        if (warp == 2 && lane == 0) NETRA_TRACE_MARK(7, n_item * 8 + 2);
+        const uint32_t* g_red = red + grp * 4 * kColsPerGroup;
+#pragma unroll
+        for (int c0 = 0; c0 < kColsPerGroup; c0 += 8) {
+          if (c0 < my_cols) {
+            uint8_t q[8];
+            float scale[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int c = c0 + j;
+              const uint32_t m = max(max(g_red[c], g_red[kColsPerGroup + c]), max(g_red[2 * kColsPerGroup + c], g_red[3 * kColsPerGroup + c]));
+              scale[j] = fmaxf(__uint_as_float(m), amax_floor()) * inv448();
+              q[j] = f32_to_e4m3(acc[0][c] * rcp_newton(scale[j]));
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (c0 + j < my_cols) {
+                const size_t row = (size_t)(w.row0 + col_base + c0 + j);
+                h_fp8[row * kInter + ntile * kTileRows + r] = q[j];
+                if (r == 0) h_scale[row * kInterBlocks + ntile] = scale[j];
               }
             }
           }
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[a]));
-      }
-      // ---- item epilogue
-      if constexpr (kGateUp) {
-        __nv_bfloat16* hs = reinterpret_cast<__nv_bfloat16*>(epi_tile);   // [64][136]
-#pragma unroll
-        for (int c = 0; c < kTokMax; ++c) {
-          if (c < n_mma) {
-            const float g = acc[0][c];
-            const float sig = 1.0f / (1.0f + expf(-g));
-            hs[c * 136 + r] = __float2bfloat16_rn(__fmul_rn(__fmul_rn(g, sig), acc[C::kATiles - 1][c]));
-          }
-        }
-        epi_barrier();
-        const int c = et >> 1, half = et & 1;   // 2 threads per token row, 64 channels each
-        const bool valid = c < w.m_valid;
-        float x[64];
-        float amax = amax_floor();
-        const uint4* src = reinterpret_cast<const uint4*>(hs + c * 136 + half * 64);
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          uint4 v = src[q];
-          const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            x[q * 8 + 2 * j] = bf16_bits_to_f32(u[j] & 0xffffu);
-            x[q * 8 + 2 * j + 1] = bf16_bits_to_f32(u[j] >> 16);
-          }
-        }
-#pragma unroll
-        for (int i = 0; i < 64; ++i) amax = fmaxf(amax, fabsf(x[i]));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-        if (valid) {
-          const float scale = amax * inv448();
-          const float inv = 1.0f / scale;
-          const size_t row = (size_t)(w.row0 + c);
-          if (half == 0) h_scale[row * kInterBlocks + w.ntile] = scale;
-          uint4* dst = reinterpret_cast<uint4*>(h_fp8 + row * kInter + w.ntile * kTileRows + half * 64);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint32_t pk[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uint32_t b = 0;
-#pragma unroll
-              for (int i = 0; i < 4; ++i) b |= (uint32_t)f32_to_e4m3(x[q * 16 + j * 4 + i] * inv) << (8 * i);
-              pk[j] = b;
-            }
-            dst[q] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-          }
-        }
+        if (warp == 2 && lane == 0) NETRA_TRACE_MARK(7, n_item * 8 + 3);
+        group_barrier(grp);   // red[] is free for the next item
+        if (warp == 2 && lane == 0) NETRA_TRACE_MARK(7, n_item * 8 + 4);
       } else {
-        float* ds = reinterpret_cast<float*>(epi_tile);   // [64][132]
 #pragma unroll
-        for (int c = 0; c < kTokMax; ++c)
-          if (c < n_mma) ds[c * 132 + r] = acc[0][c];
-        epi_barrier();
-        const int ew = et >> 5;
-        for (int c = ew; c < w.m_valid; c += 4) {
-          float4 v = *reinterpret_cast<const float4*>(ds + c * 132 + lane * 4);
-          *reinterpret_cast<float4*>(down + (size_t)(w.row0 + c) * kHidden + w.ntile * kTileRows + lane * 4) = v;
-        }
+        for (int c = 0; c < kColsPerGroup; ++c)
+          if (c < my_cols) down[(size_t)(w.row0 + col_base + c) * kHidden + ntile * kTileRows + r] = acc[0][c];
       }
-      epi_barrier();   // staging tile and scale tiles are free for the next item
+      }   // sub tile
     }
   }
 
@@ -404,19 +530,41 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
   }
 }
 
-extern "C" __global__ void __launch_bounds__(192, 1)
+extern "C" __global__ void __launch_bounds__(kGemmThreads, 1)
 netra_moe_gate_up_umma_sm100(const __grid_constant__ CUtensorMap tm_w13, const __grid_constant__ CUtensorMap tm_a32,
-                             const __grid_constant__ CUtensorMap tm_a64, const float* a_scale, const float* w13_scale,
-                             const int32_t* offsets, uint8_t* h_fp8, float* h_scale, uint32_t num_groups,
-                             uint32_t* status) {
-  grouped_gemm_body<true>(&tm_w13, &tm_a32, &tm_a64, a_scale, w13_scale, offsets, h_fp8, h_scale, nullptr, num_groups, status);
+                             const __grid_constant__ CUtensorMap tm_a64, const __grid_constant__ CUtensorMap tm_a128,
+                             const float* a_scale, const float* w13_scale, const int32_t* offsets, uint8_t* h_fp8,
+                             float* h_scale, uint32_t num_groups, uint32_t w_tiled, uint32_t* status) {
+  grouped_gemm_body<true>(&tm_w13, &tm_a32, &tm_a64, &tm_a128, a_scale, w13_scale, offsets, h_fp8, h_scale, nullptr,
+                          num_groups, w_tiled, status);
 }
 
-extern "C" __global__ void __launch_bounds__(192, 1)
+extern "C" __global__ void __launch_bounds__(kGemmThreads, 1)
 netra_moe_down_umma_sm100(const __grid_constant__ CUtensorMap tm_w2, const __grid_constant__ CUtensorMap tm_h32,
-                          const __grid_constant__ CUtensorMap tm_h64, const float* h_scale, const float* w2_scale,
-                          const int32_t* offsets, float* down, uint32_t num_groups, uint32_t* status) {
-  grouped_gemm_body<false>(&tm_w2, &tm_h32, &tm_h64, h_scale, w2_scale, offsets, nullptr, nullptr, down, num_groups, status);
+                          const __grid_constant__ CUtensorMap tm_h64, const __grid_constant__ CUtensorMap tm_h128,
+                          const float* h_scale, const float* w2_scale, const int32_t* offsets, float* down,
+                          uint32_t num_groups, uint32_t w_tiled, uint32_t* status) {
+  grouped_gemm_body<false>(&tm_w2, &tm_h32, &tm_h64, &tm_h128, h_scale, w2_scale, offsets, nullptr, nullptr, down,
+                           num_groups, w_tiled, status);
+}
+
+// Repack row-major slabs [groups * slab_rows, k_bytes] into tiles: destination row
+// ((slab_tile * kblocks + kb) * 128 + r) holds bytes [kb*128, +128) of source row slab_tile*128 + r.
+// One thread moves 16 bytes.  grid = total_bytes / 16 / 256.
+extern "C" __global__ void __launch_bounds__(256)
+netra_moe_repack_tiles_sm100(uint4* __restrict__ dst, const uint4* __restrict__ src, uint32_t total_rows, uint32_t k_bytes) {
+  const uint32_t kblocks = k_bytes / kBlock;
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;      // 16-byte chunk of the destination
+  const size_t total = (size_t)total_rows * k_bytes / 16;
+  if (idx >= total) return;
+  const uint32_t chunk = idx & 7;                 // 16-byte chunk inside the 128-byte row
+  const size_t drow = idx >> 3;
+  const uint32_t r = drow % kTileRows;
+  const size_t t = drow / kTileRows;              // slab_tile * kblocks + kb
+  const uint32_t kb = t % kblocks;
+  const size_t slab_tile = t / kblocks;
+  const size_t srow = slab_tile * kTileRows + r;
+  dst[idx] = src[(srow * k_bytes + (size_t)kb * kBlock) / 16 + chunk];
 }
 
 int gate_up_smem_bytes() { return Cfg<true>::kSmemBytes; }

@@ -43,7 +43,10 @@ class RoutedMoELayer:
 
     def __init__(self, router_w: torch.Tensor, w13: torch.Tensor, w13_scale: torch.Tensor,
                  w2: torch.Tensor, w2_scale: torch.Tensor, max_tokens: int,
-                 router_bias: Optional[torch.Tensor] = None):
+                 router_bias: Optional[torch.Tensor] = None, tiled: bool = True):
+        """``w13`` / ``w2`` are the checkpoint's row-major slabs.  With ``tiled`` (default) they are
+        rewritten once into the tile order the grouped GEMMs stream best and only that copy is kept
+        by the layer; the caller may drop the row-major tensors."""
         _require_cuda(router_w, w13, w13_scale, w2, w2_scale, router_bias)
         if tuple(router_w.shape) != (N_ROUTED, HIDDEN) or router_w.dtype != torch.bfloat16:
             raise ValueError("router weight must be bf16 [256, 2048]")
@@ -52,6 +55,9 @@ class RoutedMoELayer:
         if tuple(w13_scale.shape) != (N_ROUTED + 1, 8, 16) or tuple(w2_scale.shape) != (N_ROUTED + 1, 16, 4):
             raise ValueError("block scales must be f32 [257, 8, 16] and [257, 16, 4]")
         self.lib = abi.load()
+        self.tiled = bool(tiled)
+        if self.tiled:
+            w13, w2 = self._repack(w13), self._repack(w2)
         self.max_tokens = int(max_tokens)
         self.layout = workspace_layout(self.max_tokens)
         self._keep = (router_w, w13, w13_scale, w2, w2_scale, router_bias)
@@ -67,10 +73,17 @@ class RoutedMoELayer:
         desc.w13_fp8, desc.w13_scale_f32 = w13.data_ptr(), w13_scale.data_ptr()
         desc.w2_fp8, desc.w2_scale_f32 = w2.data_ptr(), w2_scale.data_ptr()
         desc.workspace, desc.workspace_bytes = self.workspace.data_ptr(), self.layout.total_bytes
+        desc.weights_tiled, desc.reserved = int(self.tiled), 0
         handle = ctypes.c_void_p()
         abi.check(self.lib.netra_moe_layer_create(ctypes.byref(desc), ctypes.byref(handle)), "layer_create")
         self.handle = handle
         self.device = router_w.device
+
+    def _repack(self, w: torch.Tensor) -> torch.Tensor:
+        out = torch.empty_like(w)
+        abi.check(self.lib.netra_moe_repack_tiles_launch(out.data_ptr(), w.data_ptr(), w.shape[0] * w.shape[1],
+                                                         w.shape[2] * w.element_size(), _stream()), "repack_tiles_launch")
+        return out
 
     @classmethod
     def from_operands(cls, ops, max_tokens: Optional[int] = None, device="cuda"):
@@ -79,9 +92,8 @@ class RoutedMoELayer:
         return cls(ops.router_w.to(dev), ops.w13.to(dev), ops.w13_scale.to(dev), ops.w2.to(dev),
                    ops.w2_scale.to(dev), max_tokens or ops.tokens, bias)
 
-    @property
-    def launches_per_call(self) -> int:
-        return int(self.lib.netra_moe_layer_launch_count(self.handle))
+    def launches_per_call(self, tokens: int) -> int:
+        return int(self.lib.netra_moe_layer_launch_count(self.handle, tokens))
 
     def __call__(self, hidden: torch.Tensor, shared_weight: Optional[torch.Tensor] = None,
                  out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -53,7 +53,7 @@ def test_static_scratch_sort_matches_regular_sort_on_consecutive_calls():
     for tokens, alpha, seed in cases:
         hidden, router_w, bias = synth.make_activations(tokens, alpha, seed=seed)
         layer = RoutedMoELayer(router_w.to(dev), w13, w13_s, w2, w2_s, tokens,
-                               None if bias is None else bias.to(dev))
+                               None if bias is None else bias.to(dev), tiled=False)
         want = _regular_sort(layer, hidden.to(dev))
         got = _static_sort(want["topk_ids"])
         for key in ("perm", "inv_perm", "counts", "offsets"):
