@@ -141,6 +141,10 @@ int netra_moe_layer_launch_stage(netra_moe_layer_t* layer, uint32_t stage, const
                                  const float* shared_weight_f32, void* output_bf16, uint32_t tokens,
                                  cudaStream_t stream);
 
+/* Block size and dynamic shared memory of the grouped GEMM kernels (which: 0 gate_up, 1 down), so
+ * that an engine manifest written ahead of time can be checked against the built library. */
+int netra_moe_kernel_launch_info(uint32_t which, uint32_t* block_threads, uint32_t* dynamic_smem_bytes);
+
 /* Copies the four device status words to the host (synchronises the device). */
 int netra_moe_layer_status(netra_moe_layer_t* layer, uint32_t status_out[4]);
 /* Kernels launched by one netra_moe_layer_launch call with `tokens` rows (the sort is one launch

@@ -1,0 +1,159 @@
+"""Model manifest -> graph.  One family is built: ``routed_moe_layer`` (router logits, top-8 with
+the shared slot and input quantisation, token sort, row gather, grouped gate_up, grouped down,
+combine).  Role of the reference's ``compiler/netra_compiler/frontends/model_json.py:22-47`` and
+``frontends/qwen.py``; the operation list is fixed by the family, its shapes by the profile."""
+from __future__ import annotations
+
+import json
+from pathlib import Path
+from typing import Any
+
+from .contracts import KernelSemantics
+from .ir import Graph, Operation, Tensor
+from .profiles import ShapeProfile
+from .types import TARGET, ValidationError
+
+MODEL_FORMAT = "netra-model-1"
+REQUIRED_CONSTANTS = ("hidden", "intermediate", "routed_experts", "top_k", "shared_experts", "scale_block", "sm_count")
+SORT_SINGLE_BLOCK_MAX_ROWS = 1024
+SORT_SEGMENT_PAIRS = 1024
+
+
+def load_model(path: Path) -> dict[str, Any]:
+    try:
+        doc = json.loads(Path(path).read_text(encoding="utf-8"))
+    except (OSError, json.JSONDecodeError) as exc:
+        raise ValidationError(f"cannot read model manifest {path}: {exc}") from exc
+    if doc.get("format") != MODEL_FORMAT:
+        raise ValidationError(f"{path}: not a {MODEL_FORMAT} manifest")
+    if doc.get("target") != TARGET:
+        raise ValidationError(f"{path}: target must be {TARGET}")
+    if doc.get("family") != "routed_moe_layer":
+        raise ValidationError(f"{path}: unsupported model family {doc.get('family')!r}")
+    constants = doc.get("constants", {})
+    for key in REQUIRED_CONSTANTS:
+        if not isinstance(constants.get(key), int) or isinstance(constants.get(key), bool) or constants[key] <= 0:
+            raise ValidationError(f"{path}: constant {key} must be a positive integer")
+    if constants["shared_experts"] != 1:
+        raise ValidationError(f"{path}: exactly one shared expert is supported")
+    deployment = doc.setdefault("deployment", {})
+    deployment.setdefault("tensor_parallel", 1)
+    deployment.setdefault("data_parallel_workers", 1)
+    options = doc.setdefault("options", {})
+    options.setdefault("router_bias", False)
+    options.setdefault("shared_weight", False)
+    options.setdefault("weight_layout", "tiles128")
+    if options["weight_layout"] not in ("tiles128", "row_major"):
+        raise ValidationError(f"{path}: weight_layout must be tiles128 or row_major")
+    return doc
+
+
+def semantics(abi: str, dtypes: str, quantization: str, layouts: str, numerical: str) -> dict[str, str]:
+    return KernelSemantics(abi, dtypes, quantization, layouts, numerical).to_dict()
+
+
+def dimensions_for(model: dict[str, Any], profile: ShapeProfile) -> dict[str, int]:
+    m = profile.exact_value("m")
+    c = model["constants"]
+    pairs = m * c["top_k"]
+    return {"m": m, "pairs": pairs, "rows": pairs + m, "nseg": -(-pairs // SORT_SEGMENT_PAIRS)}
+
+
+def options_for(model: dict[str, Any]) -> dict[str, int]:
+    c = model["constants"]
+    return {"groups": c["routed_experts"] + c["shared_experts"], "sm_count": c["sm_count"],
+            "w_tiled": 1 if model["options"]["weight_layout"] == "tiles128" else 0}
+
+
+def routed_moe_layer_graph(model: dict[str, Any], profile: ShapeProfile) -> Graph:
+    c = model["constants"]
+    opt = model["options"]
+    d = dimensions_for(model, profile)
+    m, pairs, rows, nseg = d["m"], d["pairs"], d["rows"], d["nseg"]
+    hidden, inter, experts, slots = c["hidden"], c["intermediate"], c["routed_experts"], c["top_k"] + 1
+    groups = experts + 1
+    kb_h, kb_i = hidden // c["scale_block"], inter // c["scale_block"]
+    segmented = m > SORT_SINGLE_BLOCK_MAX_ROWS
+
+    tensors = [
+        Tensor("hidden", "bf16", (m, hidden), "input", m * hidden * 2),
+        Tensor("output", "bf16", (m, hidden), "output", m * hidden * 2),
+        Tensor("router_weight", "bf16", (experts, hidden), "weight", experts * hidden * 2),
+        Tensor("w13", "fp8_e4m3", (groups, 2 * inter, hidden), "weight", groups * 2 * inter * hidden),
+        Tensor("w13_scale", "fp32", (groups, 2 * inter // c["scale_block"], kb_h), "weight", groups * (2 * inter // c["scale_block"]) * kb_h * 4),
+        Tensor("w2", "fp8_e4m3", (groups, hidden, inter), "weight", groups * hidden * inter),
+        Tensor("w2_scale", "fp32", (groups, kb_h, kb_i), "weight", groups * kb_h * kb_i * 4),
+        Tensor("logits", "bf16", (m, experts), "workspace", m * experts * 2),
+        Tensor("topk_ids", "int32", (m, slots), "workspace", m * slots * 4),
+        Tensor("topk_weights", "fp32", (m, slots), "workspace", m * slots * 4),
+        Tensor("perm", "int32", (pairs,), "workspace", pairs * 4),
+        Tensor("inv_perm", "int32", (pairs,), "workspace", pairs * 4),
+        Tensor("counts", "int32", (experts,), "workspace", experts * 4),
+        Tensor("offsets", "int32", (experts + 2,), "workspace", (experts + 2) * 4),
+        Tensor("a_fp8", "fp8_e4m3", (rows, hidden), "workspace", rows * hidden),
+        # scale tiles are copied 64 rows at a time: 128 spare rows keep the last copy inside the buffer
+        Tensor("a_scale", "fp32", (rows + 128, kb_h), "workspace", (rows + 128) * kb_h * 4),
+        Tensor("h_fp8", "fp8_e4m3", (rows, inter), "workspace", rows * inter),
+        Tensor("h_scale", "fp32", (rows + 128, kb_i), "workspace", (rows + 128) * kb_i * 4),
+        Tensor("down_f32", "fp32", (rows, hidden), "workspace", rows * hidden * 4),
+        Tensor("status", "uint32", (4,), "workspace", 16),
+    ]
+    if opt["router_bias"]:
+        tensors.append(Tensor("router_bias", "fp32", (experts,), "weight", experts * 4))
+    if opt["shared_weight"]:
+        tensors.append(Tensor("shared_weight", "fp32", (m,), "input", m * 4))
+    if segmented:
+        tensors.append(Tensor("seg_hist", "int32", (nseg, experts), "workspace", nseg * experts * 4))
+
+    routing_constants = {"hidden": hidden, "routed_experts": experts}
+    gemm_constants = {"hidden": hidden, "intermediate": inter, "scale_block": c["scale_block"], "tile_rows": 128}
+
+    def op(name, family, operation, inputs, outputs, constants, sem):
+        return Operation(name, "fixed_kernel", family, operation, tuple(inputs), tuple(outputs),
+                         {"constants": constants, "semantics": sem, "fallback": f"framework.{operation}"})
+
+    optional_inputs = [t for t, on in (("router_bias", opt["router_bias"]), ("shared_weight", opt["shared_weight"])) if on]
+    ops = [
+        op("router_logits", "moe_routing", "router_logits", ["hidden", "router_weight"], ["logits"], routing_constants,
+           semantics("router_logits.ptr3_u32.v1", "bf16_bf16_to_bf16", "none", "row_major", "exact_dot_rne_bf16.v1")),
+        op("topk_quant", "moe_routing", "softmax_top8_shared_slot_fp8_quant",
+           ["logits", "hidden", *optional_inputs], ["topk_ids", "topk_weights", "a_fp8", "a_scale"],
+           {**routing_constants, "top_k": c["top_k"], "scale_block": c["scale_block"]},
+           semantics("topk_quant.ptr8_u32x2.v1", "bf16_to_i32_f32_fp8e4m3_f32", "fp8_e4m3_per_token_block128_amax448",
+                     "slot9_shared_last.token_rows_after_pairs", "logit_desc_id_asc.fp32_softmax_renorm.v1")),
+    ]
+    if segmented:
+        ops += [
+            op("sort_hist", "moe_sort", "sort_histogram", ["topk_ids"], ["seg_hist"], {"routed_experts": experts, "top_k": c["top_k"]},
+               semantics("sort_hist.ptr2_u32.v1", "i32", "none", "segments_of_1024_pairs", "counting.v1")),
+            op("sort_scan", "moe_sort", "sort_scan", ["seg_hist"], ["seg_hist", "counts", "offsets"], {"routed_experts": experts, "top_k": c["top_k"]},
+               semantics("sort_scan.ptr3_u32x2.v1", "i32", "none", "offsets258_shared_group_last", "exclusive_prefix.v1")),
+            op("sort_scatter", "moe_sort", "sort_scatter", ["seg_hist", "topk_ids"], ["perm", "inv_perm"], {"routed_experts": experts, "top_k": c["top_k"]},
+               semantics("sort_scatter.ptr4_u32.v1", "i32", "none", "pair_index_t8_plus_slot", "stable_expert_major.v1")),
+        ]
+    else:
+        ops.append(op("token_sort", "moe_sort", "token_sort", ["topk_ids"], ["perm", "inv_perm", "counts", "offsets"],
+                      {"routed_experts": experts, "top_k": c["top_k"]},
+                      semantics("token_sort.ptr5_u32.v1", "i32", "none", "pair_index_t8_plus_slot.offsets258_shared_group_last",
+                                "stable_expert_major.v1")))
+    ops += [
+        op("gather_rows", "moe_sort", "gather_quantized_rows", ["perm", "a_fp8", "a_scale"], ["a_fp8", "a_scale"],
+           {"hidden": hidden, "top_k": c["top_k"], "scale_block": c["scale_block"]},
+           semantics("gather_rows.ptr3_u32.v1", "fp8e4m3_f32", "fp8_e4m3_per_token_block128_amax448",
+                     "sorted_rows_first.token_rows_after_pairs", "copy.v1")),
+        op("gate_up", "moe_fp8_grouped_gemm", "gate_up_silu_requant", ["a_fp8", "a_scale", "w13", "w13_scale", "offsets"],
+           ["h_fp8", "h_scale", "status"], gemm_constants,
+           semantics("gate_up_grouped.tmap4_ptr5_u32x2_ptr.v1", "fp8e4m3_fp8e4m3_to_fp8e4m3_f32", "fp8_e4m3_w128x128_a1x128_amax448",
+                     "swap_ab.sorted_rows." + ("tiles128" if opt["weight_layout"] == "tiles128" else "row_major"),
+                     "kblock_fma_ascending.silu_fp32.bf16_round_then_amax.v1")),
+        op("down", "moe_fp8_grouped_gemm", "down_projection", ["h_fp8", "h_scale", "w2", "w2_scale", "offsets"],
+           ["down_f32", "status"], gemm_constants,
+           semantics("down_grouped.tmap4_ptr4_u32x2_ptr.v1", "fp8e4m3_fp8e4m3_to_f32", "fp8_e4m3_w128x128_a1x128_amax448",
+                     "swap_ab.sorted_rows." + ("tiles128" if opt["weight_layout"] == "tiles128" else "row_major"),
+                     "kblock_fma_ascending.v1")),
+        op("combine", "moe_combine", "weighted_slot_combine", ["down_f32", "topk_weights", "inv_perm"], ["output"],
+           {"hidden": hidden, "top_k": c["top_k"]},
+           semantics("combine.ptr4_u32.v1", "f32_f32_to_bf16", "none", "sorted_rows_first.token_rows_after_pairs",
+                     "slot_ascending_mul_add_fp32_rne_bf16.v1")),
+    ]
+    return Graph(f"{model['name']}@{profile.name}", tuple(tensors), tuple(ops))

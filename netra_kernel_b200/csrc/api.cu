@@ -319,6 +319,13 @@ int netra_moe_repack_tiles_launch(void* dst, const void* src, uint64_t total_row
   return check_launch("repack_tiles launch");
 }
 
+int netra_moe_kernel_launch_info(uint32_t which, uint32_t* block_threads, uint32_t* dynamic_smem_bytes) {
+  if (!block_threads || !dynamic_smem_bytes || which > 1) return fail("kernel_launch_info: bad argument");
+  *block_threads = kGemmThreads;
+  *dynamic_smem_bytes = (uint32_t)(which == 0 ? gate_up_smem_bytes() : down_smem_bytes());
+  return 0;
+}
+
 int netra_moe_layer_status(netra_moe_layer_t* layer, uint32_t status_out[4]) {
   if (layer == nullptr || status_out == nullptr) return fail("layer_status: null pointer");
   cudaError_t e = cudaMemcpy(status_out, (uint8_t*)layer->desc.workspace + layer->lay.status, 16, cudaMemcpyDeviceToHost);

@@ -11,17 +11,18 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 LIB = HERE / "libnetra_sm100.so"
-SOURCES = ["api.cu"]
-DEPENDS = ["api.cu", "common.cuh", "route_kernels.cu", "bridge_kernels.cu", "umma_kernels.cu", "static_scratch_sort.cu",
-           "../../include/netra_moe.h"]
-NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "--shared", "-Xcompiler", "-fPIC", "-Xptxas", "-v", "-ccbin", "g++"]
+CUBIN = HERE / "netra_moe_sm100a.cubin"
+SOURCES = ["api.cu", "engine.cpp"]
+DEPENDS = ["api.cu", "engine.cpp", "kernels_cubin.cu", "common.cuh", "route_kernels.cu", "bridge_kernels.cu",
+           "umma_kernels.cu", "static_scratch_sort.cu", "../../include/netra_moe.h", "../../include/netra_engine.h"]
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-ccbin", "g++"]
+NVCC_FLAGS = [*ARCH_FLAGS, "--shared", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 
 
 def stale() -> bool:
-    if not LIB.exists():
+    if not LIB.exists() or not CUBIN.exists():
         return True
-    built = LIB.stat().st_mtime
+    built = min(LIB.stat().st_mtime, CUBIN.stat().st_mtime)
     return any((HERE / d).stat().st_mtime > built for d in DEPENDS)
 
 
@@ -37,6 +38,14 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         print(log)
     if proc.returncode != 0:
         raise RuntimeError("nvcc failed building libnetra_sm100.so (see csrc/build.log)")
+    # the same kernels as a stand-alone code object for the engine runtime (cuModuleLoadData)
+    cmd = [nvcc, *ARCH_FLAGS, "-cubin", "-o", str(CUBIN), str(HERE / "kernels_cubin.cu")]
+    proc = subprocess.run(cmd, capture_output=True, text=True, cwd=HERE)
+    (HERE / "build_cubin.log").write_text(proc.stdout + proc.stderr)
+    if proc.returncode != 0:
+        if verbose:
+            print(proc.stdout + proc.stderr)
+        raise RuntimeError("nvcc failed building netra_moe_sm100a.cubin (see csrc/build_cubin.log)")
     return LIB
 
 

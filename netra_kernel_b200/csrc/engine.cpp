@@ -209,6 +209,7 @@ struct TensorMapSpec {
 struct ArgSpec {
   enum Kind { Pointer, U32, TensorMap } kind = Pointer;
   bool bindable = false;          // source == binding
+  bool null_pointer = false;      // source == null: an optional operand the model does not have
   uint64_t workspace_offset = 0;  // source == workspace
   uint32_t value = 0;             // u32_constant
   TensorMapSpec map;
@@ -282,6 +283,8 @@ Manifest parse_manifest(const std::string& directory) {
           } else if (src == "workspace") {
             arg.workspace_offset = as_u64(a.at("workspace_offset"), "workspace_offset");
             if (arg.workspace_offset >= m.workspace_bytes) throw std::runtime_error("kernel workspace argument is out of range");
+          } else if (src == "null" && arg.kind == ArgSpec::Pointer) {
+            arg.null_pointer = true;
           } else {
             throw std::runtime_error("unsupported pointer argument source: " + src);
           }
@@ -540,7 +543,8 @@ extern "C" netra_status_t netra_engine_create(const char* directory, const netra
             slot.scalar = slot.spec.value;
             op.addresses[i] = &slot.scalar;
           } else {
-            if (!slot.spec.bindable) slot.pointer = static_cast<unsigned char*>(e->workspace) + slot.spec.workspace_offset;
+            if (!slot.spec.bindable && !slot.spec.null_pointer)
+              slot.pointer = static_cast<unsigned char*>(e->workspace) + slot.spec.workspace_offset;
             if (slot.spec.kind == ArgSpec::TensorMap) {
               if (!slot.spec.bindable) {
                 if (!encode_map(&slot.map, slot.pointer, slot.spec.map)) throw std::runtime_error("cuTensorMapEncodeTiled failed for a workspace tensor map");
