@@ -1,0 +1,205 @@
+"""GPU tests of the compiler -> engine directory -> runtime ABI path: the layer launched through
+netra_engine_launch must match the CPU checker, replay identically from a captured CUDA graph,
+and answer the reference's status codes for guard misses and call-order errors."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from netra_kernel_b200 import engine_runtime as er
+from netra_kernel_b200 import synth
+from netra_kernel_b200.compiler import compile_engine
+from netra_kernel_b200.compiler.library import KernelLibrary
+from oracle import moe_ref as R
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+
+MANIFESTS = KernelLibrary.discover().root / "manifests" / "sm_100a" / "models"
+MODEL = MANIFESTS / "routed-moe-layer-fp8.json"
+MODEL_ZIPF = MANIFESTS / "routed-moe-layer-fp8-zipf.json"
+
+
+@pytest.fixture(autouse=True)
+def side_stream():
+    """Stream capture is not allowed on the legacy default stream: every test runs on its own stream."""
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        yield stream
+    torch.cuda.synchronize()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _session(tmp_path, model, profile, tensors, graph=True):
+    compile_engine(model, profile, tmp_path / profile)
+    session = er.EngineSession(tmp_path / profile, device_id=0, enable_graph_capture=graph)
+    bound = session.prepare_weights(tensors)
+    torch.cuda.synchronize()
+    session.bind(bound)
+    session.finalize()
+    return session
+
+
+def _tensors(expert_weights, tokens, zipf_alpha=None, shared=False, seed=0):
+    hidden, router_w, bias = synth.make_activations(tokens, zipf_alpha, seed=seed)
+    w13, w13_s, w2, w2_s = (t.cuda() for t in expert_weights)
+    t = {"hidden": hidden.cuda(), "output": torch.zeros(tokens, 2048, dtype=torch.bfloat16, device="cuda"),
+         "router_weight": router_w.cuda(), "w13": w13, "w13_scale": w13_s, "w2": w2, "w2_scale": w2_s}
+    if bias is not None:
+        t["router_bias"] = bias.cuda()
+    if shared:
+        t["shared_weight"] = torch.linspace(0.5, 1.0, tokens).cuda()
+    return t, hidden, router_w, bias
+
+
+def _status_words(session):
+    words = session.workspace_view("status", torch.int32, "cuda").cpu()
+    return words.tolist()
+
+
+def test_engine_t16_matches_golden_fixture_direct_and_graph(tmp_path, expert_weights):
+    data = dict(np.load(helpers.GOLDEN / "moe_layer_t16.npz"))
+    tensors, *_ = _tensors(expert_weights, 16)
+    session = _session(tmp_path, MODEL, "cpu_t16", tensors)
+    info = session.profile()
+    assert (info.min_m, info.max_m, info.requires_fallback, info.tensor_parallel) == (16, 16, 0, 1)
+    assert info.workspace_bytes == session.manifest["workspace_bytes"] and er.load().netra_engine_profile_count(session.handle) == 1
+    session.launch(_stream())                       # direct launches
+    torch.cuda.synchronize()
+    assert _status_words(session) == [0, 0, 0, 0]
+    direct = tensors["output"].clone()
+    assert np.array_equal(session.workspace_view("topk_ids", torch.int32, "cuda").cpu().numpy().reshape(16, 9), data["topk_ids"])
+    assert np.array_equal(session.workspace_view("perm", torch.int32, "cuda").cpu().numpy(), data["perm"])
+    assert np.array_equal(session.workspace_view("counts", torch.int32, "cuda").cpu().numpy(), data["counts"])
+    m = R.parity_metrics(helpers.bits(direct), data["out"])
+    assert m["max_abs"] <= helpers.MAX_ABS and m["rel_l2"] <= helpers.REL_L2, m
+    session.prepare(_stream())                      # capture, then replay 20 times
+    for _ in range(20):
+        tensors["output"].zero_()
+        session.launch(_stream())
+        torch.cuda.synchronize()
+        assert torch.equal(tensors["output"], direct)
+    assert session.close() == 0
+
+
+def test_engine_t256_matches_c_checker(tmp_path, expert_weights, c_oracle):
+    tensors, hidden, router_w, _ = _tensors(expert_weights, 256)
+    ref = helpers.c_layer(c_oracle, helpers.bits(hidden), helpers.bits(router_w), *helpers.np_weights(expert_weights))
+    session = _session(tmp_path, MODEL, "decode_t256", tensors)
+    session.prepare(_stream())
+    session.launch(_stream())
+    torch.cuda.synchronize()
+    assert _status_words(session) == [0, 0, 0, 0]
+    assert np.array_equal(session.workspace_view("topk_ids", torch.int32, "cuda").cpu().numpy().reshape(256, 9), ref["topk_ids"])
+    assert np.array_equal(session.workspace_view("perm", torch.int32, "cuda").cpu().numpy(), ref["perm"])
+    assert np.array_equal(session.workspace_view("offsets", torch.int32, "cuda").cpu().numpy()[:257], ref["offsets"])
+    m = R.parity_metrics(helpers.bits(tensors["output"]), ref["out"])
+    assert m["max_abs"] <= helpers.MAX_ABS and m["rel_l2"] <= helpers.REL_L2, m
+
+
+def test_engine_with_bias_shared_weight_row_major_and_segmented_sort(tmp_path, expert_weights):
+    """Second model manifest: router bias + shared-weight column bound, row-major weights, 2048
+    tokens (above the single-block sort limit)."""
+    tokens = 2048
+    tensors, hidden, router_w, bias = _tensors(expert_weights, tokens, zipf_alpha=0.8, shared=True, seed=4)
+    subset = np.arange(3, tokens, 131)
+    ref = R.moe_layer(helpers.bits(hidden), helpers.bits(router_w), *helpers.np_weights(expert_weights), bias=bias.numpy(),
+                      shared_w=tensors["shared_weight"].cpu().numpy(), token_subset=subset)
+    session = _session(tmp_path, MODEL_ZIPF, "ep8_local_t2048", tensors)
+    assert [o["name"] for o in session.manifest["operations"]][2:5] == ["sort_hist", "sort_scan", "sort_scatter"]
+    session.launch(_stream())
+    torch.cuda.synchronize()
+    assert _status_words(session) == [0, 0, 0, 0]
+    assert np.array_equal(session.workspace_view("perm", torch.int32, "cuda").cpu().numpy(), ref["perm"])
+    m = R.parity_metrics(helpers.bits(tensors["output"])[subset], ref["out"])
+    assert m["max_abs"] <= helpers.MAX_ABS and m["rel_l2"] <= helpers.REL_L2, m
+
+
+def test_status_codes_for_guards_and_call_order(tmp_path, expert_weights):
+    lib = er.load()
+    tensors, *_ = _tensors(expert_weights, 16)
+    compile_engine(MODEL, "cpu_t16", tmp_path / "e")
+    session = er.EngineSession(tmp_path / "e", 0, True)
+    shape = er.LaunchShape(16, 1, 0, 1)
+    stream = _stream()
+    # launch before bindings are finalised
+    assert lib.netra_engine_launch(session.handle, 0, ctypes.byref(shape), stream) == 6          # BINDING
+    assert lib.netra_engine_finalize_bindings(session.handle) == 6                                # unbound pointers
+    assert b"must be bound" in lib.netra_engine_last_error(session.handle)
+    slot = session.recipe["binding_slots"]["hidden"][0]
+    assert lib.netra_engine_bind(session.handle, 0, slot["operation"], 31, tensors["hidden"].data_ptr()) == 6
+    assert lib.netra_engine_bind(session.handle, 0, 99, 0, tensors["hidden"].data_ptr()) == 6
+    assert lib.netra_engine_bind(session.handle, 0, 0, 3, tensors["hidden"].data_ptr()) == 6     # a u32 constant slot
+    assert lib.netra_engine_bind(session.handle, 0, 0, 0, tensors["hidden"].data_ptr()) == 6     # a workspace slot
+    assert lib.netra_engine_bind(session.handle, 0, slot["operation"], slot["argument"], None) == 1
+    bound = session.prepare_weights(tensors)
+    session.bind(bound)
+    session.finalize()
+    assert lib.netra_engine_bind(session.handle, 0, slot["operation"], slot["argument"], tensors["hidden"].data_ptr()) == 8  # BUSY
+    for bad in (er.LaunchShape(17, 1, 0, 1), er.LaunchShape(16, 0, 0, 1), er.LaunchShape(16, 1, 0, 2), er.LaunchShape(16, 1, 1 << 30, 1)):
+        assert lib.netra_engine_launch(session.handle, 0, ctypes.byref(bad), stream) == 5       # UNSUPPORTED_PROFILE
+    assert lib.netra_engine_launch(session.handle, 7, ctypes.byref(shape), stream) == 1
+    assert lib.netra_engine_launch(session.handle, 0, None, stream) == 1
+    info = er.ProfileInfo()
+    info.struct_size = 8
+    assert lib.netra_engine_query_profile(session.handle, 0, ctypes.byref(info)) == 1
+    info.struct_size = ctypes.sizeof(info)
+    assert lib.netra_engine_query_profile(session.handle, 3, ctypes.byref(info)) == 5
+    # one operation at a time, then with caller-local pointers
+    for index in range(len(session.manifest["operations"])):
+        session.launch_operation(index, stream)
+    torch.cuda.synchronize()
+    first = tensors["output"].clone()
+    other = torch.zeros_like(first)
+    last = len(session.manifest["operations"]) - 1
+    binding = (er.PointerBinding * 1)(er.PointerBinding(0, 0, other.data_ptr()))
+    assert lib.netra_engine_launch_operation_bound(session.handle, 0, last, ctypes.byref(shape), binding, 1, stream) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(other, first) and first.float().abs().sum() > 0
+    assert lib.netra_engine_launch_operation_bound(session.handle, 0, last, ctypes.byref(shape), binding, 0, stream) == 6
+    dup = (er.PointerBinding * 1)(er.PointerBinding(0, 1, other.data_ptr()))
+    assert lib.netra_engine_launch_operation_bound(session.handle, 0, last, ctypes.byref(shape), dup, 1, stream) == 6
+    assert lib.netra_engine_launch_operation_bound(session.handle, 0, last, ctypes.byref(shape), binding, 17, stream) == 1
+    session.prepare(stream)
+    assert lib.netra_engine_launch_operation(session.handle, 0, 0, ctypes.byref(shape), stream) == 8   # BUSY after capture
+    assert lib.netra_engine_launch_operation_bound(session.handle, 0, last, ctypes.byref(shape), binding, 1, stream) == 8
+    session.launch(stream)
+    torch.cuda.synchronize()
+    assert torch.equal(tensors["output"], first)
+    assert session.close() == 0
+
+
+def test_engine_with_fallback_operation_refuses_to_launch(tmp_path, expert_weights):
+    import json
+    doc = json.loads(MODEL.read_text())
+    doc["constants"]["hidden"] = 4096                      # no kernel is built for this width
+    (tmp_path / "m.json").write_text(json.dumps(doc))
+    compile_engine(tmp_path / "m.json", "cpu_t16", tmp_path / "e")
+    session = er.EngineSession(tmp_path / "e", 0, True)
+    assert session.profile().requires_fallback == 1
+    lib = er.load()
+    shape = er.LaunchShape(16, 1, 0, 1)
+    assert lib.netra_engine_finalize_bindings(session.handle) == 0      # nothing to bind
+    assert lib.netra_engine_launch(session.handle, 0, ctypes.byref(shape), _stream()) == 9        # FALLBACK_REQUIRED
+    assert lib.netra_engine_prepare_profile(session.handle, 0, _stream()) == 9
+    assert lib.netra_engine_launch_operation(session.handle, 0, 0, ctypes.byref(shape), _stream()) == 9
+
+
+def test_create_reports_a_broken_manifest_and_a_missing_cubin(tmp_path):
+    import json
+    compile_engine(MODEL, "cpu_t16", tmp_path / "e")
+    (tmp_path / "e" / "cubin" / "netra_moe_sm100a.cubin").unlink()
+    with pytest.raises(er.EngineError) as err:
+        er.EngineSession(tmp_path / "e")
+    assert err.value.status == 3
+    compile_engine(MODEL, "cpu_t16", tmp_path / "f")
+    doc = json.loads((tmp_path / "f" / "engine.json").read_text())
+    doc["required_cuda"]["minimum"] = "99.0"
+    (tmp_path / "f" / "engine.json").write_text(json.dumps(doc))
+    with pytest.raises(er.EngineError) as err:
+        er.EngineSession(tmp_path / "f")
+    assert err.value.status == 3
