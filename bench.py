@@ -31,8 +31,8 @@ METRIC = "routed_moe_layer_tokens_per_s"
 UNIT = "tokens/s"
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes (read + write) of one grouped gate_up launch from the committed ncu capture
-# (profiles/); None until a capture of this kernel at this workload exists.
-GATE_UP_DRAM_TRAFFIC_BYTES = None
+# (profiles/gate_up_umma_decode_t256.md: dram__bytes_read.sum + dram__bytes_write.sum, decode T=256).
+GATE_UP_DRAM_TRAFFIC_BYTES = 549_117_440   # profiles/gate_up_umma_decode_t256.md
 
 _REASONS = {
     0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
@@ -178,6 +178,31 @@ def run_reference(args) -> None:
 
 
 # --------------------------------------------------------------------------- GPU arm
+def make_engine_session(args, tokens, device_id, layer, hidden, out):
+    """Compiles an engine directory for this token count and binds it to the layer's own (already
+    repacked) weights; None when no engine profile covers the workload."""
+    import tempfile
+    from netra_kernel_b200 import engine_runtime
+    from netra_kernel_b200.compiler import compile_engine
+    from netra_kernel_b200.compiler.library import KernelLibrary
+    from netra_kernel_b200.compiler.profiles import load_profile_registry
+    if args.zipf_alpha or args.row_major_weights:
+        return None
+    root = KernelLibrary.discover().root
+    profile = next((p for p in load_profile_registry(root, "sm_100a", 1)
+                    if p.guard("m").is_exact and p.guard("m").minimum == tokens), None)
+    if profile is None:
+        return None
+    directory = tempfile.mkdtemp(prefix=f"netra_engine_r{device_id}_")
+    compile_engine(root / "manifests" / "sm_100a" / "models" / "routed-moe-layer-fp8.json", profile.name, directory)
+    session = engine_runtime.EngineSession(directory, device_id=device_id, enable_graph_capture=True)
+    router_w, w13, w13_s, w2, w2_s, _ = layer._keep
+    session.bind({"hidden": hidden, "output": out, "router_weight": router_w, "w13": w13, "w13_scale": w13_s,
+                  "w2": w2, "w2_scale": w2_s})
+    session.finalize()
+    return session
+
+
 def run_ours(args) -> None:
     import torch
     import torch.distributed as dist
@@ -228,14 +253,27 @@ def run_ours(args) -> None:
     uuid = str(torch.cuda.get_device_properties(dev).uuid)
     uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
     with torch.cuda.stream(stream), ClockSampler(uuid) as clocks:
-        # ---- device-resident loop (value): one CUDA graph holding the layer's launches, replayed per step
+        # ---- device-resident loop (value): the layer's launches captured once into a CUDA graph and replayed
+        # per step, through the engine runtime ABI (netra_engine_launch) when an engine profile exists for this
+        # token count, otherwise through the fused-layer entry point
         for _ in range(warmup):
             layer(hidden, out=out)
         stream.synchronize()
         layer.check_status()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            layer(hidden, out=out)
+        session = make_engine_session(args, tokens, local_rank, layer, hidden, out) if args.api == "engine" else None
+        if session is not None:
+            session.prepare(stream.cuda_stream)
+
+            class _EngineGraph:
+                def replay(self_inner):
+                    session.launch(stream.cuda_stream)
+            graph = _EngineGraph()
+            api_name = "netra_engine_launch (engine runtime ABI, captured CUDA graph)"
+        else:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                layer(hidden, out=out)
+            api_name = "netra_moe_layer_launch (fused-layer ABI, captured CUDA graph)"
         for _ in range(warmup):
             graph.replay()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -264,11 +302,9 @@ def run_ours(args) -> None:
         # ---- end to end through the public call with pinned host buffers
         host_in = hidden_cpu.pin_memory()
         host_out = torch.empty_like(hidden_cpu).pin_memory()
-        dev_in = torch.empty_like(hidden)
-
         def e2e_step():
-            dev_in.copy_(host_in, non_blocking=True)
-            layer(dev_in, out=out)
+            hidden.copy_(host_in, non_blocking=True)     # the bound input buffer
+            graph.replay()
             host_out.copy_(out, non_blocking=True)
 
         for _ in range(warmup):
@@ -314,7 +350,8 @@ def run_ours(args) -> None:
                    "zipf_alpha": args.zipf_alpha or 0.0,
                    "l2": "inputs larger than L2: every step streams %.1f MB of expert weights (L2 is 126 MB)" % (layer_bytes / 1e6),
                    "weights": "row-major slabs" if args.row_major_weights else "tile order (repacked once at load)",
-                   "launch": "CUDA graph replay of the layer's %d kernels" % layer.launches_per_call(tokens)},
+                   "launch": "CUDA graph replay of the layer's %d kernels" % layer.launches_per_call(tokens),
+                   "api": api_name},
         "gpu_launches": steps * layer.launches_per_call(tokens),
         "e2e": {"value": world * tokens / (e2e_ms / 1e3), "unit": UNIT, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": tokens * 2048 * 2, "d2h_bytes_per_step": tokens * 2048 * 2},
@@ -349,6 +386,8 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--row-major-weights", action="store_true",
                     help="stream the checkpoint's row-major slabs instead of the repacked tile order")
+    ap.add_argument("--api", default="engine", choices=["engine", "layer"],
+                    help="entry point timed for value/e2e: the engine runtime ABI (default) or the fused-layer call")
     ap.add_argument("--profile-only", type=int, default=0, metavar="CALLS",
                     help="run CALLS plain layer calls and exit (the command captured under ncu)")
     args = ap.parse_args()
