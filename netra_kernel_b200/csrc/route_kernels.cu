@@ -411,19 +411,26 @@ netra_moe_combine_sm100(uint16_t* __restrict__ out, const float* __restrict__ do
                         const float* __restrict__ w9, const int32_t* __restrict__ inv_perm, uint32_t rows) {
   const int t = blockIdx.x;
   const int pairs = (int)rows * kTopK;
+  // all nine rows are requested before the first is used; the sum itself stays slot-ascending
+  float4 a[kSlots], b[kSlots];
+  float w[kSlots];
+#pragma unroll
+  for (int s = 0; s < kSlots; ++s) {
+    const size_t pos = s < kTopK ? (size_t)inv_perm[t * kTopK + s] : (size_t)pairs + t;
+    w[s] = w9[t * kSlots + s];
+    const float4* src = reinterpret_cast<const float4*>(down + pos * kHidden) + threadIdx.x * 2;
+    a[s] = src[0];
+    b[s] = src[1];
+  }
   float acc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
-#pragma unroll 1
+#pragma unroll
   for (int s = 0; s < kSlots; ++s) {
-    const size_t pos = s < kTopK ? (size_t)inv_perm[t * kTopK + s] : (size_t)pairs + t;
-    const float w = w9[t * kSlots + s];
-    const float4* src = reinterpret_cast<const float4*>(down + pos * kHidden) + threadIdx.x * 2;
-    float4 a = src[0], b = src[1];
-    acc[0] = __fadd_rn(acc[0], __fmul_rn(a.x, w)); acc[1] = __fadd_rn(acc[1], __fmul_rn(a.y, w));
-    acc[2] = __fadd_rn(acc[2], __fmul_rn(a.z, w)); acc[3] = __fadd_rn(acc[3], __fmul_rn(a.w, w));
-    acc[4] = __fadd_rn(acc[4], __fmul_rn(b.x, w)); acc[5] = __fadd_rn(acc[5], __fmul_rn(b.y, w));
-    acc[6] = __fadd_rn(acc[6], __fmul_rn(b.z, w)); acc[7] = __fadd_rn(acc[7], __fmul_rn(b.w, w));
+    acc[0] = __fadd_rn(acc[0], __fmul_rn(a[s].x, w[s])); acc[1] = __fadd_rn(acc[1], __fmul_rn(a[s].y, w[s]));
+    acc[2] = __fadd_rn(acc[2], __fmul_rn(a[s].z, w[s])); acc[3] = __fadd_rn(acc[3], __fmul_rn(a[s].w, w[s]));
+    acc[4] = __fadd_rn(acc[4], __fmul_rn(b[s].x, w[s])); acc[5] = __fadd_rn(acc[5], __fmul_rn(b[s].y, w[s]));
+    acc[6] = __fadd_rn(acc[6], __fmul_rn(b[s].z, w[s])); acc[7] = __fadd_rn(acc[7], __fmul_rn(b[s].w, w[s]));
   }
   uint32_t pk[4];
 #pragma unroll

@@ -181,8 +181,8 @@ template <bool kGateUp>
 struct Cfg {
   static constexpr int kATiles = kGateUp ? 2 : 1;
   static constexpr int kKBlocks = kGateUp ? kHiddenBlocks : kInterBlocks;
-  static constexpr int kSubTiles = kGateUp ? 1 : 4;       // consecutive weight tiles per work item (same token rows)
-  static constexpr int kNTiles = (kGateUp ? kInter / kTileRows : kHidden / kTileRows) / kSubTiles;   // items per slab and chunk: 4 | 4
+  static constexpr int kSubTiles = 1;                     // consecutive weight tiles per work item (same token rows)
+  static constexpr int kNTiles = (kGateUp ? kInter / kTileRows : kHidden / kTileRows) / kSubTiles;   // items per slab and chunk: 4 | 16
   static constexpr int kSlabRows = kGateUp ? 2 * kInter : kHidden;                     // 1024 | 2048
   static constexpr int kSlabTiles = kSlabRows / kTileRows;                             // 8 | 16
   static constexpr int kKbPerStep = kGateUp ? 1 : 4;      // K-blocks the MMA warp issues per accumulator hand-off
@@ -270,9 +270,15 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const int total_items = item_pre[groups];
+  // Work items all cost about the same, so the launch is balanced when every participating CTA gets the
+  // same count: with R = ceil(items / grid) rounds only ceil(items / R) CTAs take part (e.g. 130 of 148 for
+  // 1040 items); the memory system, not the SM count, bounds these kernels.
+  const int rounds = (total_items + (int)gridDim.x - 1) / (int)gridDim.x;
+  const int stride = rounds > 0 ? (total_items + rounds - 1) / rounds : 1;
+  const int first_item = (int)blockIdx.x < stride ? (int)blockIdx.x : total_items;
   // this CTA's first kItemList work items, decoded once for all roles
   for (int n = threadIdx.x; n < C::kItemList; n += blockDim.x) {
-    const int item = blockIdx.x + n * gridDim.x;
+    const int item = first_item + n * stride;
     if (item < total_items) {
       const Item w = decode_item<C::kNTiles, C::kSubTiles>(item, item_pre, offs, groups);
       item_list[n] = make_int4(w.group, w.ntile, w.row0, w.m_valid);
@@ -293,7 +299,7 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
       const uint64_t pol_x = policy_evict_last();      // token rows are re-read by every tile of the expert
       uint32_t it = 0, n_item = 0;
       bool ok = true;
-      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x, ++n_item) {
+      for (int item = first_item; ok && item < total_items; item += stride, ++n_item) {
         const Item w = get_item((int)n_item, item);
         const int box = w.m_valid <= 32 ? 32 : 64;
         const CUtensorMap* tm_x = box == 32 ? tm_x32 : tm_x64;
@@ -343,7 +349,7 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
     if (lane == 0) {
       uint32_t it = 0, jt = 0, n_item = 0;
       bool ok = true;
-      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x, ++n_item) {
+      for (int item = first_item; ok && item < total_items; item += stride, ++n_item) {
         const Item w = get_item((int)n_item, item);
         const uint32_t n_mma = (uint32_t)((w.m_valid + 15) & ~15);
         const uint32_t idesc = make_idesc(n_mma);
@@ -388,7 +394,7 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
     const int r = quad * 32 + lane;          // weight row inside the tile == TMEM lane
     uint32_t jt = 0, n_item = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++n_item) {
+    for (int item = first_item; item < total_items; item += stride, ++n_item) {
       const Item w = get_item((int)n_item, item);
       const int n_mma = (w.m_valid + 15) & ~15;
       const int col_base = grp * (n_mma >> 1);   // this group's first column; it owns n_mma/2 columns
