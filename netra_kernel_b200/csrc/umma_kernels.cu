@@ -29,10 +29,7 @@
 namespace netra {
 
 constexpr int kTileRows = 128;          // weight rows per MMA (UMMA M)
-constexpr int kTokMax = 64;             // token rows per work item (UMMA N <= 64)
-constexpr int kColsPerGroup = 32;       // token columns owned by one epilogue warp group
 constexpr int kWTileBytes = kTileRows * kBlock;   // 16 KiB: 128 rows x 128 K bytes
-constexpr int kTokTileBytes = kTokMax * kBlock;   // 8 KiB
 constexpr int kGemmThreads = 320;
 constexpr uint32_t kSpinLimit = 1u << 22;
 
@@ -160,7 +157,7 @@ struct Item {
   int m_valid;  // token rows in this item (1..64)
 };
 
-template <int kNTiles, int kSubTiles>
+template <int kNTiles, int kSubTiles, int kTokMax>
 __device__ __forceinline__ Item decode_item(int item, const int* item_pre, const int* offs, int num_groups) {
   int lo = 0, hi = num_groups;            // largest idx with item_pre[idx] <= item
   while (hi - lo > 1) {
@@ -180,23 +177,28 @@ __device__ __forceinline__ Item decode_item(int item, const int* item_pre, const
 template <bool kGateUp>
 struct Cfg {
   static constexpr int kATiles = kGateUp ? 2 : 1;
+  static constexpr int kTokMax = kGateUp ? 64 : 32;       // token rows per work item (UMMA N)
+  static constexpr int kColsPerGroup = kTokMax / 2;       // token columns owned by one epilogue warp group
+  static constexpr int kSlices = kColsPerGroup / 8;       // 8-column TMEM loads per group and tile
+  static constexpr int kTokTileBytes = kTokMax * kBlock;  // 8 KiB | 4 KiB
+  static constexpr int kScaleSlots = kGateUp ? 2 : 4;
   static constexpr int kKBlocks = kGateUp ? kHiddenBlocks : kInterBlocks;
   static constexpr int kSubTiles = 1;                     // consecutive weight tiles per work item (same token rows)
   static constexpr int kNTiles = (kGateUp ? kInter / kTileRows : kHidden / kTileRows) / kSubTiles;   // items per slab and chunk: 4 | 16
   static constexpr int kSlabRows = kGateUp ? 2 * kInter : kHidden;                     // 1024 | 2048
   static constexpr int kSlabTiles = kSlabRows / kTileRows;                             // 8 | 16
   static constexpr int kKbPerStep = kGateUp ? 1 : 4;      // K-blocks the MMA warp issues per accumulator hand-off
-  static constexpr int kAccCols = kKbPerStep * kATiles * kTokMax;                      // TMEM columns per hand-off: 128 | 256
-  static constexpr int kAccStages = 512 / kAccCols;                                    // 4 | 2
-  static constexpr int kStages = kGateUp ? 5 : 8;
-  static constexpr int kStageBytes = kATiles * kWTileBytes + kTokTileBytes;            // 40 KiB | 24 KiB
+  static constexpr int kAccCols = kKbPerStep * kATiles * kTokMax;                      // TMEM columns per hand-off: 128 | 128
+  static constexpr int kAccStages = 512 / kAccCols;                                    // 4 | 4
+  static constexpr int kStages = kGateUp ? 5 : 10;
+  static constexpr int kStageBytes = kATiles * kWTileBytes + kTokTileBytes;            // 40 KiB | 20 KiB
   static constexpr int kTmemCols = 512;
   static constexpr int kXsBytes = kTokMax * kKBlocks * 4;                              // 4 KiB | 1 KiB
   static constexpr int kWsBytes = kKBlocks * 4;                                        // 64 B | 16 B per tile
   static constexpr int kItemList = 256;                                                // work items of this CTA decoded once
   static constexpr int kScaleSlotBytes = kXsBytes + 128;                               // xs, then ws tiles
-  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + 2 * kScaleSlotBytes + 2 * 4 * kColsPerGroup * 4 +
-                                    2 * 264 * 4 + kItemList * 16 + 256;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kScaleSlots * kScaleSlotBytes + 2 * 4 * kColsPerGroup * 4 +
+                                    2 * 264 * 4 + kItemList * 16 + 512;
 };
 
 template <bool kGateUp>
@@ -211,8 +213,8 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* stage_base = smem;
   uint8_t* scale_base = stage_base + C::kStages * C::kStageBytes;                // 2 slots
-  uint32_t* red = reinterpret_cast<uint32_t*>(scale_base + 2 * C::kScaleSlotBytes);   // [2 groups][4 warps][64]
-  int* offs = reinterpret_cast<int*>(red + 2 * 4 * kColsPerGroup);               // [264]
+  uint32_t* red = reinterpret_cast<uint32_t*>(scale_base + C::kScaleSlots * C::kScaleSlotBytes);   // [2 groups][4 warps][64]
+  int* offs = reinterpret_cast<int*>(red + 2 * 4 * C::kColsPerGroup);               // [264]
   int* item_pre = offs + 264;                                                    // [264]
   int4* item_list = reinterpret_cast<int4*>(item_pre + 264);                     // [kItemList]
   uint64_t* bars = reinterpret_cast<uint64_t*>(item_list + C::kItemList);
@@ -220,9 +222,9 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
   uint64_t* empty_bar = bars + C::kStages;         // [kStages]
   uint64_t* tfull_bar = bars + 2 * C::kStages;     // [C::kAccStages]
   uint64_t* tempty_bar = tfull_bar + C::kAccStages;   // [C::kAccStages]
-  uint64_t* sfull_bar = tempty_bar + C::kAccStages;   // [2]
-  uint64_t* sempty_bar = sfull_bar + 2;            // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sempty_bar + 2);
+  uint64_t* sfull_bar = tempty_bar + C::kAccStages;   // [kScaleSlots]
+  uint64_t* sempty_bar = sfull_bar + C::kScaleSlots;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sempty_bar + C::kScaleSlots);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -233,7 +235,7 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
     for (int a = 0; a < C::kAccStages; ++a) { mbar_init(smem_u32(&tfull_bar[a]), 1); mbar_init(smem_u32(&tempty_bar[a]), 8); }
-    for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&sfull_bar[a]), 1); mbar_init(smem_u32(&sempty_bar[a]), 8); }
+    for (int a = 0; a < C::kScaleSlots; ++a) { mbar_init(smem_u32(&sfull_bar[a]), 1); mbar_init(smem_u32(&sempty_bar[a]), 8); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -249,7 +251,7 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
       if (idx < groups) {
         const int g = idx == 0 ? groups - 1 : idx - 1;
         const int m = offs[g + 1] - offs[g];
-        c = ((m + kTokMax - 1) / kTokMax) * C::kNTiles;
+        c = ((m + C::kTokMax - 1) / C::kTokMax) * C::kNTiles;
       }
       cnt[j] = c; sum += c;
     }
@@ -280,14 +282,14 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
   for (int n = threadIdx.x; n < C::kItemList; n += blockDim.x) {
     const int item = first_item + n * stride;
     if (item < total_items) {
-      const Item w = decode_item<C::kNTiles, C::kSubTiles>(item, item_pre, offs, groups);
+      const Item w = decode_item<C::kNTiles, C::kSubTiles, C::kTokMax>(item, item_pre, offs, groups);
       item_list[n] = make_int4(w.group, w.ntile, w.row0, w.m_valid);
     }
   }
   __syncthreads();
   auto get_item = [&](int n, int item) -> Item {
     if (n < C::kItemList) { const int4 v = item_list[n]; Item w; w.group = v.x; w.ntile = v.y; w.row0 = v.z; w.m_valid = v.w; return w; }
-    return decode_item<C::kNTiles, C::kSubTiles>(item, item_pre, offs, groups);
+    return decode_item<C::kNTiles, C::kSubTiles, C::kTokMax>(item, item_pre, offs, groups);
   };
 
   if (warp == 0) {
@@ -301,13 +303,13 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
       bool ok = true;
       for (int item = first_item; ok && item < total_items; item += stride, ++n_item) {
         const Item w = get_item((int)n_item, item);
-        const int box = w.m_valid <= 32 ? 32 : 64;
+        const int box = (C::kTokMax == 32 || w.m_valid <= 32) ? 32 : 64;
         const CUtensorMap* tm_x = box == 32 ? tm_x32 : tm_x64;
         const uint32_t bytes = C::kATiles * kWTileBytes + box * kBlock;
         // scales of this item: token-row scales [128][KB] and the tile's weight scales
         {
-          const int slot = n_item & 1;
-          if (!mbar_wait(smem_u32(&sempty_bar[slot]), ((n_item >> 1) & 1) ^ 1, abort_flag)) {
+          const int slot = n_item % C::kScaleSlots;
+          if (!mbar_wait(smem_u32(&sempty_bar[slot]), ((n_item / C::kScaleSlots) & 1) ^ 1, abort_flag)) {
             status[0] = kStatusProducerTimeout; *abort_flag = 1; ok = false; break;
           }
           const uint32_t sbar = smem_u32(&sfull_bar[slot]);
@@ -370,14 +372,14 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
             tc_fence_after();
             const uint32_t sa = smem_u32(stage_base + s * C::kStageBytes);
             const uint64_t bdesc = make_smem_desc(sa + C::kATiles * kWTileBytes);
-            const uint32_t d0 = tmem_base + (uint32_t)(a * C::kAccCols + q * C::kATiles * kTokMax);
+            const uint32_t d0 = tmem_base + (uint32_t)(a * C::kAccCols + q * C::kATiles * C::kTokMax);
             // the two tiles accumulate into different TMEM columns: alternate them so that consecutive
             // MMAs never depend on each other
 #pragma unroll
             for (int k = 0; k < kBlock / 32; ++k) {
 #pragma unroll
               for (int tile = 0; tile < C::kATiles; ++tile)
-                umma_f8(d0 + (uint32_t)(tile * kTokMax), make_smem_desc(sa + tile * kWTileBytes) + 2 * k, bdesc + 2 * k, idesc, k > 0);
+                umma_f8(d0 + (uint32_t)(tile * C::kTokMax), make_smem_desc(sa + tile * kWTileBytes) + 2 * k, bdesc + 2 * k, idesc, k > 0);
             }
             umma_commit(smem_u32(&empty_bar[s]));
             NETRA_TRACE_MARK(4, it);
@@ -399,11 +401,11 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
       const int n_mma = (w.m_valid + 15) & ~15;
       const int col_base = grp * (n_mma >> 1);   // this group's first column; it owns n_mma/2 columns
       const int nsl = n_mma >> 4;                // ... in 8-column slices: 1..4
-      const int slot = n_item & 1;
+      const int slot = n_item % C::kScaleSlots;
       const float* xs_tile = reinterpret_cast<const float*>(scale_base + slot * C::kScaleSlotBytes);
-      const float* ws_tile = xs_tile + kTokMax * C::kKBlocks;
+      const float* ws_tile = xs_tile + C::kTokMax * C::kKBlocks;
       if (warp == 2 && lane == 0) NETRA_TRACE_MARK(7, n_item * 8 + 5);
-      if (ok && !mbar_wait(smem_u32(&sfull_bar[slot]), (n_item >> 1) & 1, abort_flag)) {
+      if (ok && !mbar_wait(smem_u32(&sfull_bar[slot]), (n_item / C::kScaleSlots) & 1, abort_flag)) {
         status[0] = kStatusEpilogueTimeout; *abort_flag = 1; ok = false;
       }
       if (warp == 2 && lane == 0) NETRA_TRACE_MARK(7, n_item * 8 + 6);
@@ -411,11 +413,11 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
 #pragma unroll 1
       for (int sub = 0; sub < C::kSubTiles; ++sub) {
       const int ntile = w.ntile + sub;
-      float acc[C::kATiles][kColsPerGroup];
+      float acc[C::kATiles][C::kColsPerGroup];
 #pragma unroll
       for (int tile = 0; tile < C::kATiles; ++tile)
 #pragma unroll
-        for (int c = 0; c < kColsPerGroup; ++c) acc[tile][c] = 0.0f;
+        for (int c = 0; c < C::kColsPerGroup; ++c) acc[tile][c] = 0.0f;
       for (int step = 0; step < C::kKBlocks / C::kKbPerStep; ++step, ++jt) {
         const int a = jt % C::kAccStages;
         if (ok && !mbar_wait(smem_u32(&tfull_bar[a]), (jt / C::kAccStages) & 1, abort_flag)) {
@@ -428,14 +430,14 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
         for (int q = 0; q < C::kKbPerStep; ++q) {
         const int kb = step * C::kKbPerStep + q;
         const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) +
-                               (uint32_t)(a * C::kAccCols + q * C::kATiles * kTokMax + col_base);
+                               (uint32_t)(a * C::kAccCols + q * C::kATiles * C::kTokMax + col_base);
         // all TMEM loads of this K-block are issued before the single wait
-        uint32_t v[C::kATiles][4][8];
+        uint32_t v[C::kATiles][C::kSlices][8];
 #pragma unroll
-        for (int sl = 0; sl < 4; ++sl)
+        for (int sl = 0; sl < C::kSlices; ++sl)
           if (sl < nsl) {
 #pragma unroll
-            for (int tile = 0; tile < C::kATiles; ++tile) tmem_ld8_nowait(tbase + (uint32_t)(tile * kTokMax + sl * 8), v[tile][sl]);
+            for (int tile = 0; tile < C::kATiles; ++tile) tmem_ld8_nowait(tbase + (uint32_t)(tile * C::kTokMax + sl * 8), v[tile][sl]);
           }
         tmem_ld_wait();
         if (q == C::kKbPerStep - 1) {
@@ -447,7 +449,7 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
 #pragma unroll
         for (int tile = 0; tile < C::kATiles; ++tile) ws[tile] = ws_tile[(sub + tile) * C::kKBlocks + kb];
 #pragma unroll
-        for (int sl = 0; sl < 4; ++sl)
+        for (int sl = 0; sl < C::kSlices; ++sl)
           if (sl < nsl) {
             const float* xs = xs_tile + (col_base + sl * 8) * C::kKBlocks + kb;
 #pragma unroll
@@ -468,9 +470,9 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
       // ---- tile epilogue (columns of this group that hold real rows), eight columns at a time
       if (warp == 2 && lane == 0) NETRA_TRACE_MARK(7, n_item * 8 + 0);
       if constexpr (kGateUp) {
-        uint32_t* my_red = red + (grp * 4 + gw) * kColsPerGroup;
+        uint32_t* my_red = red + (grp * 4 + gw) * C::kColsPerGroup;
 #pragma unroll
-        for (int c0 = 0; c0 < kColsPerGroup; c0 += 8) {
+        for (int c0 = 0; c0 < C::kColsPerGroup; c0 += 8) {
           if (c0 < my_cols) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) {     // independent chains first ...
@@ -490,16 +492,16 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
         if (warp == 2 && lane == 0) NETRA_TRACE_MARK(7, n_item * 8 + 1);
         group_barrier(grp);
         if (warp == 2 && lane == 0) NETRA_TRACE_MARK(7, n_item * 8 + 2);
-        const uint32_t* g_red = red + grp * 4 * kColsPerGroup;
+        const uint32_t* g_red = red + grp * 4 * C::kColsPerGroup;
 #pragma unroll
-        for (int c0 = 0; c0 < kColsPerGroup; c0 += 8) {
+        for (int c0 = 0; c0 < C::kColsPerGroup; c0 += 8) {
           if (c0 < my_cols) {
             uint8_t q[8];
             float scale[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               const int c = c0 + j;
-              const uint32_t m = max(max(g_red[c], g_red[kColsPerGroup + c]), max(g_red[2 * kColsPerGroup + c], g_red[3 * kColsPerGroup + c]));
+              const uint32_t m = max(max(g_red[c], g_red[C::kColsPerGroup + c]), max(g_red[2 * C::kColsPerGroup + c], g_red[3 * C::kColsPerGroup + c]));
               scale[j] = fmaxf(__uint_as_float(m), amax_floor()) * inv448();
               q[j] = f32_to_e4m3(acc[0][c] * rcp_newton(scale[j]));
             }
@@ -518,7 +520,7 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
         if (warp == 2 && lane == 0) NETRA_TRACE_MARK(7, n_item * 8 + 4);
       } else {
 #pragma unroll
-        for (int c = 0; c < kColsPerGroup; ++c)
+        for (int c = 0; c < C::kColsPerGroup; ++c)
           if (c < my_cols) down[(size_t)(w.row0 + col_base + c) * kHidden + ntile * kTileRows + r] = acc[0][c];
       }
       }   // sub tile
