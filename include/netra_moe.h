@@ -110,7 +110,8 @@ typedef struct netra_moe_layer_desc {
   uint64_t workspace_bytes;
   uint32_t weights_tiled;             /* 0: w13/w2 are the row-major slabs above; 1: they were rewritten by
                                          netra_moe_repack_tiles_launch (same bytes, tile order) */
-  uint32_t reserved;                  /* must be 0 */
+  uint32_t num_expert_slabs;          /* slabs behind w13/w2; 0 means 257.  Fewer is only meaningful for callers that
+                                         use the routing stages (0-5, 8) and run the experts elsewhere */
 } netra_moe_layer_desc_t;
 
 /* Load-time weight layout step (the role of the reference's repack plan,
@@ -140,6 +141,45 @@ int netra_moe_layer_launch(netra_moe_layer_t* layer, const void* hidden_bf16,
 int netra_moe_layer_launch_stage(netra_moe_layer_t* layer, uint32_t stage, const void* hidden_bf16,
                                  const float* shared_weight_f32, void* output_bf16, uint32_t tokens,
                                  cudaStream_t stream);
+
+/* ------------------------------------------------------------------ expert parallelism
+ * No counterpart in the reference (its multi-GPU mode is independent replicas).  An expert block
+ * runs the grouped gate_up and down kernels over `num_groups` expert slabs held by this GPU on a
+ * caller-provided row space: rows of group g are [offsets[g], offsets[g+1]); the last group is
+ * scheduled first (by convention the shared expert).  a_scale / h_scale need 64 spare rows after
+ * max_rows.  status_u32 points at two device words (0 = ok). */
+typedef struct netra_moe_expert_block netra_moe_expert_block_t;
+typedef struct netra_moe_expert_block_desc {
+  uint32_t struct_size;
+  uint32_t num_groups;
+  uint32_t max_rows;
+  uint32_t weights_tiled;
+  const void* w13_fp8;          /* [num_groups, 1024, 2048] (or its tile order) */
+  const float* w13_scale_f32;   /* [num_groups, 8, 16] */
+  const void* w2_fp8;           /* [num_groups, 2048, 512] */
+  const float* w2_scale_f32;    /* [num_groups, 16, 4] */
+  const void* a_fp8;            /* in  [max_rows, 2048] e4m3, rows grouped by slab */
+  const float* a_scale_f32;     /* in  [max_rows + 64, 16] */
+  void* h_fp8;                  /* scratch [max_rows, 512] */
+  float* h_scale_f32;           /* scratch [max_rows + 64, 4] */
+  float* down_f32;              /* out [max_rows, 2048] */
+  const int32_t* offsets_i32;   /* device, [num_groups + 1] */
+  uint32_t* status_u32;         /* device, [2] */
+} netra_moe_expert_block_desc_t;
+int netra_moe_expert_block_create(const netra_moe_expert_block_desc_t* desc, netra_moe_expert_block_t** output);
+int netra_moe_expert_block_launch(netra_moe_expert_block_t* block, cudaStream_t stream);
+int netra_moe_expert_block_destroy(netra_moe_expert_block_t* block);
+
+/* Rows received source-rank-major (source ascending, local expert ascending inside a source) ->
+ * expert-major positions.  counts is [sources, experts] on the device; writes src_base / dst_base
+ * [sources*experts], offsets [experts + 2] (prefix over local experts, total, total + extra_rows)
+ * and index[i] = expert-major row of source-major row i for i < total (max_rows bounds the grid). */
+int netra_ep_regroup_launch(int32_t* src_base, int32_t* dst_base, int32_t* offsets, int32_t* index,
+                            const int32_t* counts, uint32_t sources, uint32_t experts, uint32_t extra_rows,
+                            uint32_t max_rows, cudaStream_t stream);
+/* scatter == 0: dst[r] = src[index[r]];  scatter == 1: dst[index[r]] = src[r];  r < rows. */
+int netra_moe_move_rows_launch(void* dst, const void* src, const int32_t* index, uint32_t rows, uint32_t row_bytes,
+                               uint32_t scatter, cudaStream_t stream);
 
 /* Block size and dynamic shared memory of the grouped GEMM kernels (which: 0 gate_up, 1 down), so
  * that an engine manifest written ahead of time can be checked against the built library. */

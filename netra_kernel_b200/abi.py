@@ -26,7 +26,13 @@ class LayerDesc(ctypes.Structure):
                 ("w13_fp8", c_void_p), ("w13_scale_f32", c_void_p),
                 ("w2_fp8", c_void_p), ("w2_scale_f32", c_void_p),
                 ("workspace", c_void_p), ("workspace_bytes", c_u64),
-                ("weights_tiled", c_u32), ("reserved", c_u32)]
+                ("weights_tiled", c_u32), ("num_expert_slabs", c_u32)]
+
+
+class ExpertBlockDesc(ctypes.Structure):
+    _fields_ = [("struct_size", c_u32), ("num_groups", c_u32), ("max_rows", c_u32), ("weights_tiled", c_u32)] + [
+        (name, c_void_p) for name in ("w13_fp8", "w13_scale_f32", "w2_fp8", "w2_scale_f32", "a_fp8", "a_scale_f32",
+                                      "h_fp8", "h_scale_f32", "down_f32", "offsets_i32", "status_u32")]
 
 
 BRIDGES = ("netra_qwen36_router_bf16", "netra_qwen36_shared_gate_append", "netra_qwen36_moe_gate_up",
@@ -44,6 +50,11 @@ SIGNATURES = {
     "netra_moe_layer_launch": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_u32, c_void_p]),
     "netra_moe_layer_launch_stage": (c_int, [c_void_p, c_u32, c_void_p, c_void_p, c_void_p, c_u32, c_void_p]),
     "netra_moe_repack_tiles_launch": (c_int, [c_void_p, c_void_p, c_u64, c_u32, c_void_p]),
+    "netra_moe_expert_block_create": (c_int, [ctypes.POINTER(ExpertBlockDesc), ctypes.POINTER(c_void_p)]),
+    "netra_moe_expert_block_launch": (c_int, [c_void_p, c_void_p]),
+    "netra_moe_expert_block_destroy": (c_int, [c_void_p]),
+    "netra_ep_regroup_launch": (c_int, [c_void_p] * 5 + [c_u32] * 4 + [c_void_p]),
+    "netra_moe_move_rows_launch": (c_int, [c_void_p] * 3 + [c_u32] * 3 + [c_void_p]),
     "netra_moe_kernel_launch_info": (c_int, [c_u32, ctypes.POINTER(c_u32), ctypes.POINTER(c_u32)]),
     "netra_moe_layer_status": (c_int, [c_void_p, ctypes.POINTER(c_u32 * 4)]),
     "netra_moe_layer_launch_count": (c_u32, [c_void_p, c_u32]),

@@ -13,6 +13,7 @@
 #include "bridge_kernels.cu"
 #include "route_kernels.cu"
 #include "umma_kernels.cu"
+#include "ep_kernels.cu"
 
 using namespace netra;
 
@@ -196,15 +197,17 @@ int netra_moe_layer_create(const netra_moe_layer_desc_t* desc, netra_moe_layer_t
   layer->lay = lay;
   layer->sm_count = sms;
   layer->launches = 9;  // stages of launch_stage()
+  const uint64_t slabs = desc->num_expert_slabs ? desc->num_expert_slabs : (uint64_t)(kRouted + 1);
+  if (slabs > (uint64_t)(kRouted + 1)) { delete layer; return fail("layer_create: at most 257 expert slabs"); }
   uint8_t* ws = (uint8_t*)desc->workspace;
   const uint64_t rows = (uint64_t)desc->max_tokens * (kTopK + 1);
   int rc = 0;
   if (desc->weights_tiled) {   // tiles of 128 rows x 128 bytes, one after another
-    rc = rc ? rc : encode_u8_2d(&layer->tm_w13, desc->w13_fp8, (uint64_t)(kRouted + 1) * 2 * kInter * kHiddenBlocks, kBlock, 128);
-    rc = rc ? rc : encode_u8_2d(&layer->tm_w2, desc->w2_fp8, (uint64_t)(kRouted + 1) * kHidden * kInterBlocks, kBlock, 128);
+    rc = rc ? rc : encode_u8_2d(&layer->tm_w13, desc->w13_fp8, slabs * 2 * kInter * kHiddenBlocks, kBlock, 128);
+    rc = rc ? rc : encode_u8_2d(&layer->tm_w2, desc->w2_fp8, slabs * kHidden * kInterBlocks, kBlock, 128);
   } else {
-    rc = rc ? rc : encode_u8_2d(&layer->tm_w13, desc->w13_fp8, (uint64_t)(kRouted + 1) * 2 * kInter, kHidden, 128);
-    rc = rc ? rc : encode_u8_2d(&layer->tm_w2, desc->w2_fp8, (uint64_t)(kRouted + 1) * kHidden, kInter, 128);
+    rc = rc ? rc : encode_u8_2d(&layer->tm_w13, desc->w13_fp8, slabs * 2 * kInter, kHidden, 128);
+    rc = rc ? rc : encode_u8_2d(&layer->tm_w2, desc->w2_fp8, slabs * kHidden, kInter, 128);
   }
   rc = rc ? rc : encode_u8_2d(&layer->tm_a32, ws + lay.a_fp8, rows, kHidden, 32);
   rc = rc ? rc : encode_u8_2d(&layer->tm_a64, ws + lay.a_fp8, rows, kHidden, 64);
@@ -317,6 +320,88 @@ int netra_moe_repack_tiles_launch(void* dst, const void* src, uint64_t total_row
   netra_moe_repack_tiles_sm100<<<(unsigned)((chunks + 255) / 256), 256, 0, stream>>>((uint4*)dst, (const uint4*)src,
                                                                                      (uint32_t)total_rows, k_bytes);
   return check_launch("repack_tiles launch");
+}
+
+// ------------------------------------------------------------------ expert block (expert parallelism)
+struct netra_moe_expert_block {
+  netra_moe_expert_block_desc_t desc;
+  CUtensorMap tm_w13, tm_w2, tm_a32, tm_a64, tm_a128, tm_h32, tm_h64, tm_h128;
+  int sm_count;
+};
+
+int netra_moe_expert_block_create(const netra_moe_expert_block_desc_t* desc, netra_moe_expert_block_t** output) {
+  if (!desc || !output || desc->struct_size != sizeof(netra_moe_expert_block_desc_t)) return fail("expert_block_create: bad struct_size");
+  if (!desc->w13_fp8 || !desc->w13_scale_f32 || !desc->w2_fp8 || !desc->w2_scale_f32 || !desc->a_fp8 || !desc->a_scale_f32 ||
+      !desc->h_fp8 || !desc->h_scale_f32 || !desc->down_f32 || !desc->offsets_i32 || !desc->status_u32)
+    return fail("expert_block_create: null pointer");
+  if (desc->num_groups == 0 || desc->num_groups > kRouted + 1 || desc->max_rows == 0) return fail("expert_block_create: bad group or row count");
+  int device = 0, major = 0, sms = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return fail_cuda("cudaGetDevice", e);
+  cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  if (major != 10) return fail("expert_block_create: this library targets sm_100a (compute capability 10.x)");
+  if (int rc = umma_setup()) return rc;
+  netra_moe_expert_block* b = new (std::nothrow) netra_moe_expert_block;
+  if (!b) return fail("expert_block_create: out of host memory");
+  b->desc = *desc;
+  b->sm_count = sms;
+  const uint64_t g = desc->num_groups, rows = desc->max_rows;
+  int rc = 0;
+  if (desc->weights_tiled) {
+    rc = rc ? rc : encode_u8_2d(&b->tm_w13, desc->w13_fp8, g * 2 * kInter * kHiddenBlocks, kBlock, 128);
+    rc = rc ? rc : encode_u8_2d(&b->tm_w2, desc->w2_fp8, g * kHidden * kInterBlocks, kBlock, 128);
+  } else {
+    rc = rc ? rc : encode_u8_2d(&b->tm_w13, desc->w13_fp8, g * 2 * kInter, kHidden, 128);
+    rc = rc ? rc : encode_u8_2d(&b->tm_w2, desc->w2_fp8, g * kHidden, kInter, 128);
+  }
+  rc = rc ? rc : encode_u8_2d(&b->tm_a32, desc->a_fp8, rows, kHidden, 32);
+  rc = rc ? rc : encode_u8_2d(&b->tm_a64, desc->a_fp8, rows, kHidden, 64);
+  rc = rc ? rc : encode_u8_2d(&b->tm_a128, desc->a_fp8, rows, kHidden, 128);
+  rc = rc ? rc : encode_u8_2d(&b->tm_h32, desc->h_fp8, rows, kInter, 32);
+  rc = rc ? rc : encode_u8_2d(&b->tm_h64, desc->h_fp8, rows, kInter, 64);
+  rc = rc ? rc : encode_u8_2d(&b->tm_h128, desc->h_fp8, rows, kInter, 128);
+  if (rc) { delete b; return rc; }
+  *output = b;
+  return 0;
+}
+
+int netra_moe_expert_block_launch(netra_moe_expert_block_t* b, cudaStream_t stream) {
+  if (!b) return fail("expert_block_launch: null handle");
+  const netra_moe_expert_block_desc_t& d = b->desc;
+  netra_moe_gate_up_umma_sm100<<<b->sm_count, kGemmThreads, gate_up_smem_bytes(), stream>>>(
+      b->tm_w13, b->tm_a32, b->tm_a64, b->tm_a128, d.a_scale_f32, d.w13_scale_f32, d.offsets_i32, (uint8_t*)d.h_fp8,
+      d.h_scale_f32, d.num_groups, d.weights_tiled, d.status_u32);
+  netra_moe_down_umma_sm100<<<b->sm_count, kGemmThreads, down_smem_bytes(), stream>>>(
+      b->tm_w2, b->tm_h32, b->tm_h64, b->tm_h128, d.h_scale_f32, d.w2_scale_f32, d.offsets_i32, d.down_f32, d.num_groups,
+      d.weights_tiled, d.status_u32 + 1);
+  return check_launch("expert_block launch");
+}
+
+int netra_moe_expert_block_destroy(netra_moe_expert_block_t* b) {
+  delete b;
+  return 0;
+}
+
+int netra_ep_regroup_launch(int32_t* src_base, int32_t* dst_base, int32_t* offsets, int32_t* index, const int32_t* counts,
+                            uint32_t sources, uint32_t experts, uint32_t extra_rows, uint32_t max_rows, cudaStream_t stream) {
+  if (!src_base || !dst_base || !offsets || !index || !counts) return fail("ep_regroup: null pointer");
+  if (sources == 0 || experts == 0 || sources * experts > 1024) return fail("ep_regroup: sources * experts must be 1..1024");
+  netra_ep_regroup_bases_sm100<<<1, 1024, 0, stream>>>(src_base, dst_base, offsets, counts, sources, experts, extra_rows);
+  if (max_rows > 0)
+    netra_ep_regroup_index_sm100<<<(max_rows + 255) / 256, 256, 0, stream>>>(index, src_base, dst_base, sources * experts,
+                                                                           offsets + experts);
+  return check_launch("ep_regroup launch");
+}
+
+int netra_moe_move_rows_launch(void* dst, const void* src, const int32_t* index, uint32_t rows, uint32_t row_bytes,
+                               uint32_t scatter, cudaStream_t stream) {
+  if (!dst || !src || !index) return fail("move_rows: null pointer");
+  if (row_bytes == 0 || row_bytes % 16 != 0) return fail("move_rows: row bytes must be a positive multiple of 16");
+  if (rows == 0) return 0;
+  netra_moe_move_rows_sm100<<<(rows + 7) / 8, 256, 0, stream>>>((uint8_t*)dst, (const uint8_t*)src, index, nullptr, rows, row_bytes,
+                                                               scatter);
+  return check_launch("move_rows launch");
 }
 
 int netra_moe_kernel_launch_info(uint32_t which, uint32_t* block_threads, uint32_t* dynamic_smem_bytes) {

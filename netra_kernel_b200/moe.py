@@ -43,17 +43,21 @@ class RoutedMoELayer:
 
     def __init__(self, router_w: torch.Tensor, w13: torch.Tensor, w13_scale: torch.Tensor,
                  w2: torch.Tensor, w2_scale: torch.Tensor, max_tokens: int,
-                 router_bias: Optional[torch.Tensor] = None, tiled: bool = True):
+                 router_bias: Optional[torch.Tensor] = None, tiled: bool = True, routing_only: bool = False):
         """``w13`` / ``w2`` are the checkpoint's row-major slabs.  With ``tiled`` (default) they are
         rewritten once into the tile order the grouped GEMMs stream best and only that copy is kept
         by the layer; the caller may drop the row-major tensors."""
         _require_cuda(router_w, w13, w13_scale, w2, w2_scale, router_bias)
         if tuple(router_w.shape) != (N_ROUTED, HIDDEN) or router_w.dtype != torch.bfloat16:
             raise ValueError("router weight must be bf16 [256, 2048]")
-        if tuple(w13.shape) != (N_ROUTED + 1, 2 * INTER, HIDDEN) or tuple(w2.shape) != (N_ROUTED + 1, HIDDEN, INTER):
-            raise ValueError("expert slabs must be [257, 1024, 2048] and [257, 2048, 512] (slab 256 = shared expert)")
-        if tuple(w13_scale.shape) != (N_ROUTED + 1, 8, 16) or tuple(w2_scale.shape) != (N_ROUTED + 1, 16, 4):
-            raise ValueError("block scales must be f32 [257, 8, 16] and [257, 16, 4]")
+        slabs = w13.shape[0]
+        if not routing_only and slabs != N_ROUTED + 1:
+            raise ValueError("a full layer needs 257 expert slabs (slab 256 = shared expert)")
+        if tuple(w13.shape) != (slabs, 2 * INTER, HIDDEN) or tuple(w2.shape) != (slabs, HIDDEN, INTER):
+            raise ValueError("expert slabs must be [S, 1024, 2048] and [S, 2048, 512]")
+        if tuple(w13_scale.shape) != (slabs, 8, 16) or tuple(w2_scale.shape) != (slabs, 16, 4):
+            raise ValueError("block scales must be f32 [S, 8, 16] and [S, 16, 4]")
+        self.routing_only = routing_only
         self.lib = abi.load()
         self.tiled = bool(tiled)
         if self.tiled:
@@ -73,7 +77,7 @@ class RoutedMoELayer:
         desc.w13_fp8, desc.w13_scale_f32 = w13.data_ptr(), w13_scale.data_ptr()
         desc.w2_fp8, desc.w2_scale_f32 = w2.data_ptr(), w2_scale.data_ptr()
         desc.workspace, desc.workspace_bytes = self.workspace.data_ptr(), self.layout.total_bytes
-        desc.weights_tiled, desc.reserved = int(self.tiled), 0
+        desc.weights_tiled, desc.num_expert_slabs = int(self.tiled), int(w13.shape[0])
         handle = ctypes.c_void_p()
         abi.check(self.lib.netra_moe_layer_create(ctypes.byref(desc), ctypes.byref(handle)), "layer_create")
         self.handle = handle
@@ -100,6 +104,8 @@ class RoutedMoELayer:
         _require_cuda(hidden, shared_weight, out)
         if hidden.dtype != torch.bfloat16 or hidden.dim() != 2 or hidden.shape[1] != HIDDEN:
             raise ValueError("hidden must be bf16 [tokens, 2048]")
+        if self.routing_only:
+            raise RuntimeError("this layer object only serves the routing stages (expert-parallel use)")
         tokens = hidden.shape[0]
         if out is None:
             out = torch.empty_like(hidden)
