@@ -181,6 +181,7 @@ class ExpertParallelMoELayer:
             out = torch.empty_like(hidden)
         for stage in range(6):                                        # router .. gather, local tokens, 256 experts
             route.launch_stage(stage, hidden, out, shared_weight)
+        launches = route.launches_per_call(t_l) - 3                   # this library's kernels launched by the call
         inter = route.intermediates(t_l)
         recv_counts = plan.exchange_counts(inter["counts"])
         splits = plan.splits(inter["counts"], recv_counts)            # the one host read-back of the call
@@ -194,9 +195,11 @@ class ExpertParallelMoELayer:
         self.abi.check(self.lib.netra_ep_regroup_launch(self.src_base.data_ptr(), self.dst_base.data_ptr(), self.offsets.data_ptr(),
                                                         self.index.data_ptr(), recv_counts.data_ptr(), plan.world,
                                                         plan.experts_per_rank, t_l, r, self._stream()), "ep_regroup_launch")
+        launches += 2 if r else 1
         if r:
             self._move(self.blk_a, self.recv_a, self.index, r, HIDDEN, scatter=True)
             self._move(self.blk_as, self.recv_as, self.index, r, HIDDEN // 128 * 4, scatter=True)
+            launches += 3
         self.blk_a[r:r + t_l].copy_(inter["a_fp8"][p_l:p_l + t_l])    # the shared expert's rows: the local tokens
         self.blk_as[r:r + t_l].copy_(inter["a_scale"][p_l:p_l + t_l])
         self.abi.check(self.lib.netra_moe_expert_block_launch(self.block, self._stream()), "expert_block_launch")
@@ -206,7 +209,12 @@ class ExpertParallelMoELayer:
         plan.all_to_all_rows(self.back[:r], splits.recv, splits.send, out=inter["down"][:p_l])
         inter["down"][p_l:p_l + t_l].copy_(self.blk_down[r:r + t_l])
         route.launch_stage(8, hidden, out, shared_weight)             # slot-ordered combine, as on one GPU
+        self.launches_last_call = launches + 3                        # gate_up, down, combine
         return out
+
+    def launch_expert_block(self) -> None:
+        """The two grouped GEMMs over the rows of the last call (for isolated timing)."""
+        self.abi.check(self.lib.netra_moe_expert_block_launch(self.block, self._stream()), "expert_block_launch")
 
     def check_status(self) -> None:
         words = self.status.cpu().tolist()
