@@ -98,6 +98,17 @@ def measured_hbm_peak():
     return FALLBACK_HBM_GBS, "fallback"
 
 
+def measured_fp8_peak():
+    """Dense FP8 tensor peak is not measured on this pool; twice the measured BF16 GEMM burst rate stands in."""
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return 2.0 * float(json.loads(path.read_text())["bf16_tflops"]), "2 x measured bf16 GEMM"
+        except Exception:
+            pass
+    return 2.0 * 1590.0, "2 x fallback bf16 GEMM"
+
+
 def dist_env():
     return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
 
@@ -105,7 +116,7 @@ def dist_env():
 # --------------------------------------------------------------------------- CPU restatement arm
 def load_cpu_checker():
     lib_path = ROOT / "oracle" / "libmoe_ref.so"
-    if not lib_path.exists():
+    if not lib_path.exists() or lib_path.stat().st_mtime < (ROOT / "oracle" / "moe_ref.c").stat().st_mtime:
         subprocess.run(["make", "-C", str(ROOT / "oracle")], check=True, capture_output=True)
     return ctypes.CDLL(str(lib_path))
 
@@ -117,6 +128,7 @@ def time_cpu_layer(tokens: int, budget_s: float, weights=None, min_reps: int = 1
     import torch
     from netra_kernel_b200 import synth
     lib = load_cpu_checker()
+    lib.moe_ref_set_threads(os.cpu_count() or 1)      # all host threads, whatever OMP_NUM_THREADS the launcher exported
     threads = lib.moe_ref_threads()
     hidden, router_w, _ = synth.make_activations(tokens)
     w13, w13_s, w2, w2_s = weights if weights is not None else synth.make_expert_weights(0)
@@ -340,6 +352,10 @@ def run_ours(args) -> None:
     gu_s, dn_s = stage_ms[6] / 1e3, stage_ms[7] / 1e3
     achieved = gate_up_bytes / gu_s / 1e9
     layer_bytes = synth.workload_bytes_decode(tokens, experts_hit)
+    prefill = tokens >= 2048     # tensor-bound regime: report FP8 flops against 2x the measured BF16 GEMM rate
+    fp8_peak, fp8_kind = measured_fp8_peak()
+    gate_up_flops = tokens * 9 * 2 * 2048 * 1024
+    layer_flops = synth.workload_flops(tokens)
     line = {
         "metric": METRIC, "value": world * tokens / (ms_per_step / 1e3), "unit": UNIT, "n_gpus": world,
         "steps": steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
@@ -355,10 +371,16 @@ def run_ours(args) -> None:
         "gpu_launches": steps * layer.launches_per_call(tokens),
         "e2e": {"value": world * tokens / (e2e_ms / 1e3), "unit": UNIT, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": tokens * 2048 * 2, "d2h_bytes_per_step": tokens * 2048 * 2},
-        "roofline": {"bound": "hbm", "kernel": "netra_moe_gate_up_umma_sm100", "achieved": achieved, "peak": peak,
-                     "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
-                     "algorithmic_bytes": gate_up_bytes, "avg_launch_ms": stage_ms[6],
-                     "traffic": GATE_UP_DRAM_TRAFFIC_BYTES},
+        "roofline": ({"bound": "tensor", "kernel": "netra_moe_gate_up_umma_sm100", "achieved": gate_up_flops / gu_s / 1e12,
+                      "peak": fp8_peak, "unit": "TFLOP/s", "frac": gate_up_flops / gu_s / 1e12 / fp8_peak, "peak_source": fp8_kind,
+                      "algorithmic_flops": gate_up_flops, "avg_launch_ms": stage_ms[6], "traffic": None}
+                     if prefill else
+                     {"bound": "hbm", "kernel": "netra_moe_gate_up_umma_sm100", "achieved": achieved, "peak": peak,
+                      "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
+                      "algorithmic_bytes": gate_up_bytes, "avg_launch_ms": stage_ms[6],
+                      "traffic": GATE_UP_DRAM_TRAFFIC_BYTES if tokens == 256 else None}),
+        "layer_tensor": {"algorithmic_flops": layer_flops, "achieved": layer_flops / (ms_per_step / 1e3) / 1e12, "unit": "TFLOP/s",
+                         "frac": layer_flops / (ms_per_step / 1e3) / 1e12 / fp8_peak, "peak": fp8_peak, "peak_source": fp8_kind},
         "kernels_ms": {name: round(ms, 5) for name, ms in zip(layer.STAGES, stage_ms)},
         "down_kernel": {"achieved": down_bytes / dn_s / 1e9, "unit": "GB/s", "frac": down_bytes / dn_s / 1e9 / peak},
         "layer_hbm": {"algorithmic_bytes": layer_bytes, "achieved": layer_bytes / (ms_per_step / 1e3) / 1e9,

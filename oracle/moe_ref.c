@@ -84,6 +84,15 @@ int moe_ref_threads(void) {
 #endif
 }
 
+/* torchrun exports OMP_NUM_THREADS=1; callers that time this library set the thread count themselves */
+void moe_ref_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 uint8_t moe_ref_e4m3_encode(float x) { return e4m3_encode(x); }
 
 /* per-128 quantiser: x FP32 [rows, cols] -> codes [rows, cols], scales [rows, cols/128] */
