@@ -301,7 +301,7 @@ def run_ours(args) -> None:
         n_stage = len(layer.STAGES)
         marks = [[torch.cuda.Event(enable_timing=True) for _ in range(n_stage + 1)] for _ in range(steps)]
         for _ in range(warmup):
-            layer(hidden, out=out)
+            step()
         barrier()
         for k in range(steps):
             marks[k][0].record(stream)
@@ -415,10 +415,24 @@ def run_expert_parallel(args) -> None:
     local = tuple(t.to(dev) for t in shard_expert_weights(weights, plan))
     del weights
     hidden_cpu, router_w, _ = synth.make_activations(tokens, None, seed=rank)
-    layer = ExpertParallelMoELayer(plan, router_w.to(dev), *local, max_local_tokens=tokens)
+    router_dev = router_w.to(dev)
+    layer = ExpertParallelMoELayer(plan, router_dev, *local, max_local_tokens=tokens, exchange=args.ep_exchange)
     hidden = hidden_cpu.to(dev)
     out = torch.empty_like(hidden)
     stream = torch.cuda.Stream(device=dev)
+    if args.ep_exchange == "fixed":
+        # one untimed call sizes the slots: every rank must use the same slot, large enough for the fullest pair
+        with torch.cuda.stream(stream):
+            layer(hidden, out=out)
+        stream.synchronize()
+        need = layer.status[2:3].to(torch.int64).clone()
+        dist.all_reduce(need, op=dist.ReduceOp.MAX)
+        if int(need.item()) > 0:
+            layer.close()
+            slot = -(-int(int(need.item()) * 1.05) // 64) * 64
+            layer = ExpertParallelMoELayer(plan, router_dev, *local, max_local_tokens=tokens, exchange="fixed", slot_rows=slot)
+    def step():
+        layer(hidden, out=out)
 
     def barrier():
         dist.barrier()
@@ -434,11 +448,11 @@ def run_expert_parallel(args) -> None:
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream), ClockSampler(uuid) as clocks:
         for _ in range(warmup):
-            layer(hidden, out=out)
+            step()
         barrier()
         e0.record(stream)
         for _ in range(steps):
-            layer(hidden, out=out)
+            step()
         e1.record(stream)
         barrier()
         ms_per_step = max_over_ranks(e0.elapsed_time(e1) / steps)
@@ -449,7 +463,7 @@ def run_expert_parallel(args) -> None:
 
         def e2e_step():
             hidden.copy_(host_in, non_blocking=True)
-            layer(hidden, out=out)
+            step()
             host_out.copy_(out, non_blocking=True)
 
         for _ in range(warmup):
@@ -488,7 +502,9 @@ def run_expert_parallel(args) -> None:
                                       "NCCL all-to-all dispatch and return",
                        "l2": "each step re-reads this GPU's expert slabs (%.1f MB); below the 126 MB L2 at 8 GPUs, so the step is "
                              "bound by routing and all-to-all latency, not by HBM" % (block_bytes / 1e6),
-                       "launch": "direct launches (the split sizes are read on the host once per call)",
+                       "exchange": (f"fixed slots of {layer.slot_rows} rows per rank pair, no host read-back"
+                                    if args.ep_exchange == "fixed" else "exact split sizes, read on the host once per call"),
+                       "launch": "direct launches",
                        "api": "ExpertParallelMoELayer over netra_moe_layer_launch_stage / netra_moe_expert_block_launch"},
             "gpu_launches": steps * launches,
             "e2e": {"value": world * tokens / (e2e_ms / 1e3), "unit": UNIT, "ms_per_step": e2e_ms,
@@ -516,6 +532,8 @@ def main() -> None:
                     help="stream the checkpoint's row-major slabs instead of the repacked tile order")
     ap.add_argument("--replicas", action="store_true",
                     help="with N > 1 ranks run N independent replicas of the layer instead of expert parallelism")
+    ap.add_argument("--ep-exchange", default="fixed", choices=["fixed", "exact"],
+                    help="expert-parallel row exchange: fixed slots per rank pair (no host sync) or exact split sizes")
     ap.add_argument("--api", default="engine", choices=["engine", "layer"],
                     help="entry point timed for value/e2e: the engine runtime ABI (default) or the fused-layer call")
     ap.add_argument("--profile-only", type=int, default=0, metavar="CALLS",

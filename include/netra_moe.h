@@ -171,15 +171,30 @@ int netra_moe_expert_block_launch(netra_moe_expert_block_t* block, cudaStream_t 
 int netra_moe_expert_block_destroy(netra_moe_expert_block_t* block);
 
 /* Rows received source-rank-major (source ascending, local expert ascending inside a source) ->
- * expert-major positions.  counts is [sources, experts] on the device; writes src_base / dst_base
- * [sources*experts], offsets [experts + 2] (prefix over local experts, total, total + extra_rows)
- * and index[i] = expert-major row of source-major row i for i < total (max_rows bounds the grid). */
+ * expert-major positions.  counts is [sources, experts] on the device.  Writes src_base / dst_base
+ * [sources*experts], offsets [experts + 2] and index[i] for i < index_rows (-1 for an unused slot
+ * row).  slot_rows == 0: the rows are compact; slot_rows > 0: source s owns rows
+ * [s*slot_rows, (s+1)*slot_rows) (fixed-capacity exchange, index_rows = sources*slot_rows).
+ * shared_first == 0: offsets = prefix over local experts, then total, then total + extra_rows;
+ * shared_first == 1: group 0 is the extra (shared-expert) rows at [0, extra_rows), routed groups follow. */
 int netra_ep_regroup_launch(int32_t* src_base, int32_t* dst_base, int32_t* offsets, int32_t* index,
                             const int32_t* counts, uint32_t sources, uint32_t experts, uint32_t extra_rows,
-                            uint32_t max_rows, cudaStream_t stream);
-/* scatter == 0: dst[r] = src[index[r]];  scatter == 1: dst[index[r]] = src[r];  r < rows. */
-int netra_moe_move_rows_launch(void* dst, const void* src, const int32_t* index, uint32_t rows, uint32_t row_bytes,
+                            uint32_t index_rows, uint32_t slot_rows, uint32_t shared_first, cudaStream_t stream);
+/* scatter == 0: dst row r <- src row index[r];  scatter == 1: dst row index[r] <- src row r;  r < rows,
+ * rows with index[r] < 0 are skipped.  copy_bytes at column offsets dst_col / src_col of rows with
+ * pitches dst_pitch / src_pitch (all multiples of 16). */
+int netra_moe_move_rows_launch(void* dst, const void* src, const int32_t* index, uint32_t rows, uint32_t copy_bytes,
+                               uint32_t dst_pitch, uint32_t src_pitch, uint32_t dst_col, uint32_t src_col,
                                uint32_t scatter, cudaStream_t stream);
+/* Fixed-capacity exchange.  pack: this rank's sorted FP8 rows and scales for rank g -> slot rows
+ * [g*slot_rows, ...) of send_slots (2112 bytes per row: 2048 codes + 16 FP32 scales); a destination
+ * that needs more than slot_rows rows records its count in *overflow (device word, 0 = fits).
+ * unpack: returned FP32 rows, slot row (g, i) -> sorted row offsets[g*experts_per_rank] + i of down. */
+int netra_ep_pack_rows_launch(void* send_slots, const void* a_fp8, const float* a_scale_f32, const int32_t* offsets_i32,
+                              uint32_t ranks, uint32_t experts_per_rank, uint32_t slot_rows, uint32_t* overflow,
+                              cudaStream_t stream);
+int netra_ep_unpack_rows_launch(float* down_f32, const float* back_slots_f32, const int32_t* offsets_i32, uint32_t ranks,
+                                uint32_t experts_per_rank, uint32_t slot_rows, cudaStream_t stream);
 
 /* Block size and dynamic shared memory of the grouped GEMM kernels (which: 0 gate_up, 1 down), so
  * that an engine manifest written ahead of time can be checked against the built library. */

@@ -53,8 +53,10 @@ SIGNATURES = {
     "netra_moe_expert_block_create": (c_int, [ctypes.POINTER(ExpertBlockDesc), ctypes.POINTER(c_void_p)]),
     "netra_moe_expert_block_launch": (c_int, [c_void_p, c_void_p]),
     "netra_moe_expert_block_destroy": (c_int, [c_void_p]),
-    "netra_ep_regroup_launch": (c_int, [c_void_p] * 5 + [c_u32] * 4 + [c_void_p]),
-    "netra_moe_move_rows_launch": (c_int, [c_void_p] * 3 + [c_u32] * 3 + [c_void_p]),
+    "netra_ep_regroup_launch": (c_int, [c_void_p] * 5 + [c_u32] * 6 + [c_void_p]),
+    "netra_moe_move_rows_launch": (c_int, [c_void_p] * 3 + [c_u32] * 7 + [c_void_p]),
+    "netra_ep_pack_rows_launch": (c_int, [c_void_p] * 4 + [c_u32] * 3 + [c_void_p, c_void_p]),
+    "netra_ep_unpack_rows_launch": (c_int, [c_void_p] * 3 + [c_u32] * 3 + [c_void_p]),
     "netra_moe_kernel_launch_info": (c_int, [c_u32, ctypes.POINTER(c_u32), ctypes.POINTER(c_u32)]),
     "netra_moe_layer_status": (c_int, [c_void_p, ctypes.POINTER(c_u32 * 4)]),
     "netra_moe_layer_launch_count": (c_u32, [c_void_p, c_u32]),

@@ -384,24 +384,47 @@ int netra_moe_expert_block_destroy(netra_moe_expert_block_t* b) {
 }
 
 int netra_ep_regroup_launch(int32_t* src_base, int32_t* dst_base, int32_t* offsets, int32_t* index, const int32_t* counts,
-                            uint32_t sources, uint32_t experts, uint32_t extra_rows, uint32_t max_rows, cudaStream_t stream) {
+                            uint32_t sources, uint32_t experts, uint32_t extra_rows, uint32_t index_rows, uint32_t slot_rows,
+                            uint32_t shared_first, cudaStream_t stream) {
   if (!src_base || !dst_base || !offsets || !index || !counts) return fail("ep_regroup: null pointer");
   if (sources == 0 || experts == 0 || sources * experts > 1024) return fail("ep_regroup: sources * experts must be 1..1024");
-  netra_ep_regroup_bases_sm100<<<1, 1024, 0, stream>>>(src_base, dst_base, offsets, counts, sources, experts, extra_rows);
-  if (max_rows > 0)
-    netra_ep_regroup_index_sm100<<<(max_rows + 255) / 256, 256, 0, stream>>>(index, src_base, dst_base, sources * experts,
-                                                                           offsets + experts);
+  if (slot_rows && index_rows != sources * slot_rows) return fail("ep_regroup: with slots, index_rows must be sources * slot_rows");
+  netra_ep_regroup_bases_sm100<<<1, 1024, 0, stream>>>(src_base, dst_base, offsets, counts, sources, experts, extra_rows, slot_rows,
+                                                     shared_first);
+  if (index_rows > 0)
+    netra_ep_regroup_index_sm100<<<(index_rows + 255) / 256, 256, 0, stream>>>(index, src_base, dst_base, counts, sources * experts,
+                                                                             index_rows);
   return check_launch("ep_regroup launch");
 }
 
-int netra_moe_move_rows_launch(void* dst, const void* src, const int32_t* index, uint32_t rows, uint32_t row_bytes,
-                               uint32_t scatter, cudaStream_t stream) {
+int netra_moe_move_rows_launch(void* dst, const void* src, const int32_t* index, uint32_t rows, uint32_t copy_bytes,
+                               uint32_t dst_pitch, uint32_t src_pitch, uint32_t dst_col, uint32_t src_col, uint32_t scatter,
+                               cudaStream_t stream) {
   if (!dst || !src || !index) return fail("move_rows: null pointer");
-  if (row_bytes == 0 || row_bytes % 16 != 0) return fail("move_rows: row bytes must be a positive multiple of 16");
+  if (copy_bytes == 0 || (copy_bytes | dst_pitch | src_pitch | dst_col | src_col) % 16 != 0)
+    return fail("move_rows: sizes, pitches and column offsets must be multiples of 16");
+  if (dst_col + copy_bytes > dst_pitch || src_col + copy_bytes > src_pitch) return fail("move_rows: copy exceeds a row pitch");
   if (rows == 0) return 0;
-  netra_moe_move_rows_sm100<<<(rows + 7) / 8, 256, 0, stream>>>((uint8_t*)dst, (const uint8_t*)src, index, nullptr, rows, row_bytes,
-                                                               scatter);
+  netra_moe_move_rows_sm100<<<(rows + 7) / 8, 256, 0, stream>>>((uint8_t*)dst, (const uint8_t*)src, index, rows, copy_bytes, dst_pitch,
+                                                               src_pitch, dst_col, src_col, scatter);
   return check_launch("move_rows launch");
+}
+
+int netra_ep_pack_rows_launch(void* send_slots, const void* a_fp8, const float* a_scale, const int32_t* offsets, uint32_t ranks,
+                              uint32_t experts_per_rank, uint32_t slot_rows, uint32_t* overflow, cudaStream_t stream) {
+  if (!send_slots || !a_fp8 || !a_scale || !offsets || !overflow) return fail("ep_pack_rows: null pointer");
+  if (ranks == 0 || slot_rows == 0 || ranks * experts_per_rank != (uint32_t)kRouted) return fail("ep_pack_rows: ranks * experts_per_rank must be 256");
+  netra_ep_pack_rows_sm100<<<dim3((slot_rows + 7) / 8, ranks), 256, 0, stream>>>((uint8_t*)send_slots, (const uint8_t*)a_fp8, a_scale,
+                                                                                offsets, experts_per_rank, slot_rows, overflow);
+  return check_launch("ep_pack_rows launch");
+}
+
+int netra_ep_unpack_rows_launch(float* down, const float* back_slots, const int32_t* offsets, uint32_t ranks,
+                                uint32_t experts_per_rank, uint32_t slot_rows, cudaStream_t stream) {
+  if (!down || !back_slots || !offsets) return fail("ep_unpack_rows: null pointer");
+  if (ranks == 0 || slot_rows == 0 || ranks * experts_per_rank != (uint32_t)kRouted) return fail("ep_unpack_rows: ranks * experts_per_rank must be 256");
+  netra_ep_unpack_rows_sm100<<<dim3((slot_rows + 7) / 8, ranks), 256, 0, stream>>>(down, back_slots, offsets, experts_per_rank, slot_rows);
+  return check_launch("ep_unpack_rows launch");
 }
 
 int netra_moe_kernel_launch_info(uint32_t which, uint32_t* block_threads, uint32_t* dynamic_smem_bytes) {

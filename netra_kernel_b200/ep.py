@@ -95,35 +95,69 @@ class ExpertParallelPlan:
         return out
 
     # ------------------------------------------------------------------ index math (torch reference)
-    def regroup_reference(self, recv_counts: torch.Tensor, extra_rows: int):
-        """Same result as ``netra_ep_regroup_launch``: (index [R] source-major -> expert-major,
-        offsets [E_l + 2])."""
+    def regroup_reference(self, recv_counts: torch.Tensor, extra_rows: int, slot_rows: int = 0, shared_first: bool = False):
+        """Same result as ``netra_ep_regroup_launch``: (index source-major -> expert-major with -1 for
+        unused slot rows, offsets [E_l + 2])."""
         c = recv_counts.to(torch.int64).cpu()                       # [world, E_l]
-        flat = c.reshape(-1)
-        src_base = torch.cumsum(flat, 0) - flat
+        world, e_l = c.shape
+        if slot_rows:                                                # a sender never delivers more than one slot
+            start = torch.cumsum(c, 1) - c
+            c = torch.clamp(torch.clamp(start + c, max=slot_rows) - torch.clamp(start, max=slot_rows), min=0)
         per_expert = c.sum(0)
-        expert_base = torch.cumsum(per_expert, 0) - per_expert
-        within = torch.cumsum(c, 0) - c                              # rows of earlier sources, same expert
-        dst_base = (expert_base[None, :] + within).reshape(-1)
-        total = int(flat.sum())
-        bucket = torch.repeat_interleave(torch.arange(flat.numel()), flat)
-        index = dst_base[bucket] + (torch.arange(total) - src_base[bucket])
-        offsets = torch.cat([expert_base, torch.tensor([total, total + extra_rows])])
+        base = extra_rows if shared_first else 0
+        expert_base = torch.cumsum(per_expert, 0) - per_expert + base
+        within_expert = torch.cumsum(c, 0) - c                       # rows of earlier sources, same expert
+        dst_base = expert_base[None, :] + within_expert              # [world, E_l]
+        total = int(c.sum())
+        rows = world * slot_rows if slot_rows else total
+        index = torch.full((rows,), -1, dtype=torch.int64)
+        pos = 0
+        for s in range(world):
+            if slot_rows:
+                pos = s * slot_rows
+            for e in range(e_l):
+                n = int(c[s, e])
+                index[pos:pos + n] = dst_base[s, e] + torch.arange(n)
+                pos += n
+        if shared_first:
+            offsets = torch.cat([torch.tensor([0]), expert_base, torch.tensor([base + total])])
+        else:
+            offsets = torch.cat([expert_base, torch.tensor([total, total + extra_rows])])
         return index.to(torch.int32), offsets.to(torch.int32)
+
+    def slot_rows_for(self, local_tokens: int, headroom: float = 8.0) -> int:
+        """Fixed capacity per (source, destination) pair: the mean of near-uniform routing plus
+        ``headroom`` standard deviations, rounded up to 64 rows and never more than all pairs."""
+        pairs = local_tokens * TOPK
+        if self.world == 1:
+            return pairs
+        p = 1.0 / self.world
+        mean, sd = pairs * p, (pairs * p * (1 - p)) ** 0.5
+        return min(pairs, int(-(-(mean + headroom * sd + 32) // 64) * 64))
+
+
+EP_ROW_BYTES = HIDDEN + HIDDEN // 128 * 4      # FP8 codes followed by the 16 FP32 scales
 
 
 class ExpertParallelMoELayer:
-    """One rank of the expert-parallel layer on a B200.  ``w13`` etc. hold this rank's
-    ``E_l`` routed slabs followed by the (replicated) shared expert's slab."""
+    """One rank of the expert-parallel layer on a B200.  ``w13`` etc. hold the (replicated) shared
+    expert's slab FIRST, then this rank's ``E_l`` routed slabs (``shard_expert_weights``).
+
+    ``exchange="fixed"`` (default) moves a fixed number of slot rows per rank pair, so a call is
+    enqueued without any host read-back and can be captured into a CUDA graph; a destination that
+    would need more rows than a slot holds is reported by ``check_status``.  ``exchange="exact"``
+    reads the split sizes on the host once per call and moves exactly the routed rows."""
 
     def __init__(self, plan: ExpertParallelPlan, router_w, w13, w13_scale, w2, w2_scale, max_local_tokens: int,
-                 router_bias=None, tiled: bool = True, max_recv_rows: Optional[int] = None):
+                 router_bias=None, tiled: bool = True, exchange: str = "fixed", slot_rows: Optional[int] = None):
         from . import abi
         from .moe import RoutedMoELayer
-        self.plan, self.abi, self.lib = plan, abi, abi.load()
-        e_l = plan.experts_per_rank
+        if exchange not in ("fixed", "exact"):
+            raise ValueError("exchange must be 'fixed' or 'exact'")
+        self.plan, self.abi, self.lib, self.exchange = plan, abi, abi.load(), exchange
+        e_l, world = plan.experts_per_rank, plan.world
         if w13.shape[0] != e_l + 1:
-            raise ValueError(f"this rank holds {e_l} routed slabs + the shared slab, got {w13.shape[0]}")
+            raise ValueError(f"this rank holds the shared slab + {e_l} routed slabs, got {w13.shape[0]}")
         dev = router_w.device
         self.device, self.t_max = dev, int(max_local_tokens)
         # routing stages (0-5) and the combine (8) of the single-GPU layer, on the local tokens
@@ -131,8 +165,8 @@ class ExpertParallelMoELayer:
                                     routing_only=True)
         w13, w2 = self.route._keep[1], self.route._keep[3]           # the copies the kernels read (tile order if tiled)
         pairs = self.t_max * TOPK
-        # worst case every pair of every rank lands here; callers with tighter knowledge pass max_recv_rows
-        self.r_max = int(max_recv_rows) if max_recv_rows else pairs * plan.world
+        self.slot_rows = int(slot_rows) if slot_rows else (plan.slot_rows_for(self.t_max) if exchange == "fixed" else pairs)
+        self.r_max = self.slot_rows * world                          # rows that can arrive here
         rows = self.r_max + self.t_max
         u8, f32, i32 = torch.uint8, torch.float32, torch.int32
         self.blk_a = torch.zeros(rows, HIDDEN, dtype=u8, device=dev)
@@ -140,15 +174,17 @@ class ExpertParallelMoELayer:
         self.blk_h = torch.zeros(rows, INTER, dtype=u8, device=dev)
         self.blk_hs = torch.zeros(rows + 64, INTER // 128, dtype=f32, device=dev)
         self.blk_down = torch.zeros(rows, HIDDEN, dtype=f32, device=dev)
-        self.recv_a = torch.empty(self.r_max, HIDDEN, dtype=u8, device=dev)
-        self.recv_as = torch.empty(self.r_max, HIDDEN // 128, dtype=f32, device=dev)
-        self.back = torch.empty(self.r_max, HIDDEN, dtype=f32, device=dev)
-        n_bucket = plan.world * e_l
+        self.send = torch.zeros(self.r_max, EP_ROW_BYTES, dtype=u8, device=dev)
+        self.recv = torch.zeros(self.r_max, EP_ROW_BYTES, dtype=u8, device=dev)
+        self.back = torch.zeros(self.r_max, HIDDEN, dtype=f32, device=dev)
+        self.back_recv = torch.zeros(self.r_max, HIDDEN, dtype=f32, device=dev)
+        self.recv_counts = torch.zeros(world * e_l, dtype=i32, device=dev)
+        n_bucket = world * e_l
         self.src_base = torch.zeros(n_bucket, dtype=i32, device=dev)
         self.dst_base = torch.zeros(n_bucket, dtype=i32, device=dev)
         self.offsets = torch.zeros(e_l + 2, dtype=i32, device=dev)
-        self.index = torch.zeros(self.r_max, dtype=i32, device=dev)
-        self.status = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.index = torch.full((self.r_max,), -1, dtype=i32, device=dev)
+        self.status = torch.zeros(4, dtype=torch.int32, device=dev)   # [gate_up, down, slot overflow, unused]
         desc = abi.ExpertBlockDesc()
         desc.struct_size = ctypes.sizeof(desc)
         desc.num_groups, desc.max_rows, desc.weights_tiled = e_l + 1, rows, int(tiled)
@@ -162,17 +198,20 @@ class ExpertParallelMoELayer:
         self.block = handle
         self._keep = (w13, w13_scale, w2, w2_scale)
         self.last_splits: Optional[Splits] = None
+        self.launches_last_call = 0
 
     def _stream(self) -> int:
         return torch.cuda.current_stream().cuda_stream
 
-    def _move(self, dst, src, index, rows: int, row_bytes: int, scatter: bool) -> None:
-        self.abi.check(self.lib.netra_moe_move_rows_launch(dst.data_ptr(), src.data_ptr(), index.data_ptr(), rows, row_bytes,
-                                                           int(scatter), self._stream()), "move_rows_launch")
+    def _move(self, dst, src, rows, copy_bytes, dst_pitch, src_pitch, dst_col, src_col, scatter) -> None:
+        self.abi.check(self.lib.netra_moe_move_rows_launch(dst.data_ptr(), src.data_ptr(), self.index.data_ptr(), rows, copy_bytes,
+                                                           dst_pitch, src_pitch, dst_col, src_col, int(scatter), self._stream()),
+                       "move_rows_launch")
 
     def __call__(self, hidden: torch.Tensor, shared_weight: Optional[torch.Tensor] = None,
                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        plan, route = self.plan, self.route
+        plan, route, lib, check = self.plan, self.route, self.lib, self.abi.check
+        world, e_l = plan.world, plan.experts_per_rank
         t_l = hidden.shape[0]
         p_l = t_l * TOPK
         if t_l > self.t_max:
@@ -181,35 +220,49 @@ class ExpertParallelMoELayer:
             out = torch.empty_like(hidden)
         for stage in range(6):                                        # router .. gather, local tokens, 256 experts
             route.launch_stage(stage, hidden, out, shared_weight)
-        launches = route.launches_per_call(t_l) - 3                   # this library's kernels launched by the call
         inter = route.intermediates(t_l)
+        fixed = self.exchange == "fixed"
+        slot = self.slot_rows if fixed else 0
+        # ---- dispatch
         recv_counts = plan.exchange_counts(inter["counts"])
-        splits = plan.splits(inter["counts"], recv_counts)            # the one host read-back of the call
-        self.last_splits = splits
-        r = splits.total_recv
-        if r > self.r_max:
-            raise RuntimeError(f"{r} rows arrive but the receive buffers hold {self.r_max}")
-        # dispatch: the sorted rows are already grouped by owner rank
-        plan.all_to_all_rows(inter["a_fp8"][:p_l], splits.send, splits.recv, out=self.recv_a[:r])
-        plan.all_to_all_rows(inter["a_scale"][:p_l], splits.send, splits.recv, out=self.recv_as[:r])
-        self.abi.check(self.lib.netra_ep_regroup_launch(self.src_base.data_ptr(), self.dst_base.data_ptr(), self.offsets.data_ptr(),
-                                                        self.index.data_ptr(), recv_counts.data_ptr(), plan.world,
-                                                        plan.experts_per_rank, t_l, r, self._stream()), "ep_regroup_launch")
-        launches += 2 if r else 1
-        if r:
-            self._move(self.blk_a, self.recv_a, self.index, r, HIDDEN, scatter=True)
-            self._move(self.blk_as, self.recv_as, self.index, r, HIDDEN // 128 * 4, scatter=True)
-            launches += 3
-        self.blk_a[r:r + t_l].copy_(inter["a_fp8"][p_l:p_l + t_l])    # the shared expert's rows: the local tokens
-        self.blk_as[r:r + t_l].copy_(inter["a_scale"][p_l:p_l + t_l])
-        self.abi.check(self.lib.netra_moe_expert_block_launch(self.block, self._stream()), "expert_block_launch")
-        # return: back into the order the rows arrived in, which is each sender's own sorted order
-        if r:
-            self._move(self.back, self.blk_down, self.index, r, HIDDEN * 4, scatter=False)
-        plan.all_to_all_rows(self.back[:r], splits.recv, splits.send, out=inter["down"][:p_l])
-        inter["down"][p_l:p_l + t_l].copy_(self.blk_down[r:r + t_l])
+        if fixed:
+            check(lib.netra_ep_pack_rows_launch(self.send.data_ptr(), inter["a_fp8"].data_ptr(), inter["a_scale"].data_ptr(),
+                                                inter["offsets"].data_ptr(), world, e_l, slot, self.status[2:].data_ptr(),
+                                                self._stream()), "ep_pack_rows_launch")
+            equal = [slot] * world
+            plan.all_to_all_rows(self.send, equal, equal, out=self.recv)
+            arrived = self.r_max
+        else:
+            splits = plan.splits(inter["counts"], recv_counts)        # the one host read-back of the call
+            self.last_splits = splits
+            arrived = splits.total_recv
+            if arrived > self.r_max:
+                raise RuntimeError(f"{arrived} rows arrive but the receive buffers hold {self.r_max}")
+            packed = torch.cat([inter["a_fp8"][:p_l], inter["a_scale"][:p_l].view(torch.uint8).view(p_l, -1)], dim=1)
+            plan.all_to_all_rows(packed, splits.send, splits.recv, out=self.recv[:arrived])
+        # ---- regroup source-major -> expert-major; the shared expert's rows (local tokens) are group 0
+        check(lib.netra_ep_regroup_launch(self.src_base.data_ptr(), self.dst_base.data_ptr(), self.offsets.data_ptr(),
+                                          self.index.data_ptr(), recv_counts.data_ptr(), world, e_l, t_l, arrived, slot, 1,
+                                          self._stream()), "ep_regroup_launch")
+        if arrived:
+            self._move(self.blk_a, self.recv, arrived, HIDDEN, HIDDEN, EP_ROW_BYTES, 0, 0, scatter=True)
+            self._move(self.blk_as, self.recv, arrived, HIDDEN // 128 * 4, HIDDEN // 128 * 4, EP_ROW_BYTES, 0, HIDDEN, scatter=True)
+        self.blk_a[:t_l].copy_(inter["a_fp8"][p_l:p_l + t_l])
+        self.blk_as[:t_l].copy_(inter["a_scale"][p_l:p_l + t_l])
+        check(lib.netra_moe_expert_block_launch(self.block, self._stream()), "expert_block_launch")
+        # ---- return the FP32 rows in arrival order, which is each sender's own sorted order
+        if arrived:
+            self._move(self.back, self.blk_down, arrived, HIDDEN * 4, HIDDEN * 4, HIDDEN * 4, 0, 0, scatter=False)
+        if fixed:
+            equal = [slot] * world
+            plan.all_to_all_rows(self.back, equal, equal, out=self.back_recv)
+            check(lib.netra_ep_unpack_rows_launch(inter["down"].data_ptr(), self.back_recv.data_ptr(), inter["offsets"].data_ptr(),
+                                                  world, e_l, slot, self._stream()), "ep_unpack_rows_launch")
+        else:
+            plan.all_to_all_rows(self.back[:arrived], splits.recv, splits.send, out=inter["down"][:p_l])
+        inter["down"][p_l:p_l + t_l].copy_(self.blk_down[:t_l])
         route.launch_stage(8, hidden, out, shared_weight)             # slot-ordered combine, as on one GPU
-        self.launches_last_call = launches + 3                        # gate_up, down, combine
+        self.launches_last_call = route.launches_per_call(t_l) - 2 + 2 + (3 if arrived else 0) + (2 if fixed else 0) + 2
         return out
 
     def launch_expert_block(self) -> None:
@@ -218,7 +271,10 @@ class ExpertParallelMoELayer:
 
     def check_status(self) -> None:
         words = self.status.cpu().tolist()
-        if any(words):
+        if words[2]:
+            raise self.abi.NetraError(f"a destination rank needed {words[2]} rows but a slot holds {self.slot_rows}: "
+                                      "construct the layer with a larger slot_rows or exchange='exact'")
+        if any(words[:2]):
             raise self.abi.NetraError(f"device status words {words}: a bounded wait expired inside a grouped GEMM")
 
     def close(self) -> None:
@@ -229,6 +285,6 @@ class ExpertParallelMoELayer:
 
 
 def shard_expert_weights(weights, plan: ExpertParallelPlan):
-    """(w13, w13_scale, w2, w2_scale) with 257 slabs -> this rank's E_l routed slabs + the shared slab."""
+    """(w13, w13_scale, w2, w2_scale) with 257 slabs -> the shared slab followed by this rank's E_l routed slabs."""
     lo, hi = plan.local_expert_range().start, plan.local_expert_range().stop
-    return tuple(torch.cat([t[lo:hi], t[-1:]]).contiguous() for t in weights)
+    return tuple(torch.cat([t[-1:], t[lo:hi]]).contiguous() for t in weights)

@@ -157,6 +157,13 @@ def test_plan_ownership_and_regroup_index():
     index, off = small.regroup_reference(counts, extra_rows=4)
     # source-major rows: s0:[e0,e0,e2] s1:[e0,e1,e1,e1] -> expert-major: e0:[s0,s0,s1] e1:[s1,s1,s1] e2:[s0]
     assert index.tolist() == [0, 1, 6, 2, 3, 4, 5] and off.tolist() == [0, 3, 6, 7, 11]
+    # shared expert's rows first, fixed slots of 5 rows per source (unused slot rows are -1)
+    index, off = small.regroup_reference(counts, extra_rows=4, slot_rows=5, shared_first=True)
+    assert index.tolist() == [4, 5, 10, -1, -1, 6, 7, 8, 9, -1] and off.tolist() == [0, 4, 7, 10, 11]
+    # a slot of 3 rows truncates source 1 to its first three rows: nothing points past world * slot rows
+    index, off = small.regroup_reference(counts, extra_rows=4, slot_rows=3, shared_first=True)
+    assert index.tolist() == [4, 5, 9, 6, 7, 8] and off.tolist() == [0, 4, 7, 9, 10]
+    assert ExpertParallelPlan(8, 0).slot_rows_for(2048) % 64 == 0 and ExpertParallelPlan(8, 0).slot_rows_for(2048) < 2048 * 8 // 4
     world1 = ExpertParallelPlan(1, 0)
     c = torch.arange(256, dtype=torch.int32)
     assert torch.equal(world1.exchange_counts(c).view(-1), c)
