@@ -403,7 +403,7 @@ def run_expert_parallel(args) -> None:
     import torch
     import torch.distributed as dist
     from netra_kernel_b200 import synth
-    from netra_kernel_b200.ep import ExpertParallelMoELayer, ExpertParallelPlan, shard_expert_weights
+    from netra_kernel_b200.ep import ExpertParallelMoELayer, ExpertParallelPlan, PeerExpertParallelLayer, shard_expert_weights
 
     rank, local_rank, world = dist_env()
     torch.cuda.set_device(local_rank)
@@ -416,23 +416,51 @@ def run_expert_parallel(args) -> None:
     del weights
     hidden_cpu, router_w, _ = synth.make_activations(tokens, None, seed=rank)
     router_dev = router_w.to(dev)
-    layer = ExpertParallelMoELayer(plan, router_dev, *local, max_local_tokens=tokens, exchange=args.ep_exchange)
     hidden = hidden_cpu.to(dev)
     out = torch.empty_like(hidden)
     stream = torch.cuda.Stream(device=dev)
-    if args.ep_exchange == "fixed":
-        # one untimed call sizes the slots: every rank must use the same slot, large enough for the fullest pair
+    graph = None
+    if args.ep_exchange == "peer":
+        # the library's own kernels move the rows through the peers' windows; one CUDA graph replay per step
+        layer = PeerExpertParallelLayer(plan, router_dev, *local, max_local_tokens=tokens)
+        torch.cuda.synchronize(dev)
+        dist.barrier()
         with torch.cuda.stream(stream):
-            layer(hidden, out=out)
+            for _ in range(2):
+                layer(hidden, out=out)
         stream.synchronize()
-        need = layer.status[2:3].to(torch.int64).clone()
-        dist.all_reduce(need, op=dist.ReduceOp.MAX)
-        if int(need.item()) > 0:
-            layer.close()
-            slot = -(-int(int(need.item()) * 1.05) // 64) * 64
-            layer = ExpertParallelMoELayer(plan, router_dev, *local, max_local_tokens=tokens, exchange="fixed", slot_rows=slot)
+        layer.check_status()
+        dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            layer(hidden, out=out)
+        launches = layer.launches_per_call(tokens)
+    else:
+        layer = ExpertParallelMoELayer(plan, router_dev, *local, max_local_tokens=tokens, exchange=args.ep_exchange)
+        if args.ep_exchange == "fixed":
+            # one untimed call sizes the slots: every rank must use the same slot, large enough for the fullest pair
+            with torch.cuda.stream(stream):
+                layer(hidden, out=out)
+            stream.synchronize()
+            need = layer.status[2:3].to(torch.int64).clone()
+            dist.all_reduce(need, op=dist.ReduceOp.MAX)
+            if int(need.item()) > 0:
+                layer.close()
+                slot = -(-int(int(need.item()) * 1.05) // 64) * 64
+                layer = ExpertParallelMoELayer(plan, router_dev, *local, max_local_tokens=tokens, exchange="fixed", slot_rows=slot)
+
     def step():
-        layer(hidden, out=out)
+        if graph is not None:
+            graph.replay()
+        else:
+            layer(hidden, out=out)
+
+    def expert_block():
+        if args.ep_exchange == "peer":
+            layer.launch_stage(7, hidden, out)
+            layer.launch_stage(8, hidden, out)
+        else:
+            layer.launch_expert_block()
 
     def barrier():
         dist.barrier()
@@ -456,7 +484,8 @@ def run_expert_parallel(args) -> None:
         e1.record(stream)
         barrier()
         ms_per_step = max_over_ranks(e0.elapsed_time(e1) / steps)
-        launches = layer.launches_last_call
+        if args.ep_exchange != "peer":
+            launches = layer.launches_last_call
 
         host_in = hidden_cpu.pin_memory()
         host_out = torch.empty_like(hidden_cpu).pin_memory()
@@ -478,11 +507,11 @@ def run_expert_parallel(args) -> None:
 
         # the grouped GEMMs alone, over the rows of the last call
         for _ in range(warmup):
-            layer.launch_expert_block()
+            expert_block()
         barrier()
         e0.record(stream)
         for _ in range(steps):
-            layer.launch_expert_block()
+            expert_block()
         e1.record(stream)
         barrier()
         block_ms = max_over_ranks(e0.elapsed_time(e1) / steps)
@@ -499,13 +528,16 @@ def run_expert_parallel(args) -> None:
             "config": {"workload": f"decode_t{tokens} per GPU (1 layer, hidden 2048, 256 routed experts top-8 + shared, inter 512)",
                        "tokens_per_gpu": tokens, "tokens_total": world * tokens,
                        "parallelism": f"ep{world}: {plan.experts_per_rank} routed experts per GPU, shared expert and router replicated, "
-                                      "NCCL all-to-all dispatch and return",
+                                      "rows dispatched to the owners and returned",
                        "l2": "each step re-reads this GPU's expert slabs (%.1f MB); below the 126 MB L2 at 8 GPUs, so the step is "
                              "bound by routing and all-to-all latency, not by HBM" % (block_bytes / 1e6),
-                       "exchange": (f"fixed slots of {layer.slot_rows} rows per rank pair, no host read-back"
-                                    if args.ep_exchange == "fixed" else "exact split sizes, read on the host once per call"),
-                       "launch": "direct launches",
-                       "api": "ExpertParallelMoELayer over netra_moe_layer_launch_stage / netra_moe_expert_block_launch"},
+                       "exchange": {"peer": "this library's kernels store rows into the peers' windows over NVLink (CUDA IPC), "
+                                            "epoch flags with bounded waits, no NCCL on the data path",
+                                    "fixed": "NCCL all-to-all, fixed slots per rank pair, no host read-back",
+                                    "exact": "NCCL all-to-all, exact split sizes read on the host once per call"}[args.ep_exchange],
+                       "launch": "one CUDA graph replay per step" if graph is not None else "direct launches",
+                       "api": "netra_ep_layer_launch" if args.ep_exchange == "peer"
+                              else "ExpertParallelMoELayer over netra_moe_layer_launch_stage / netra_moe_expert_block_launch"},
             "gpu_launches": steps * launches,
             "e2e": {"value": world * tokens / (e2e_ms / 1e3), "unit": UNIT, "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": tokens * 2048 * 2, "d2h_bytes_per_step": tokens * 2048 * 2},
@@ -532,8 +564,9 @@ def main() -> None:
                     help="stream the checkpoint's row-major slabs instead of the repacked tile order")
     ap.add_argument("--replicas", action="store_true",
                     help="with N > 1 ranks run N independent replicas of the layer instead of expert parallelism")
-    ap.add_argument("--ep-exchange", default="fixed", choices=["fixed", "exact"],
-                    help="expert-parallel row exchange: fixed slots per rank pair (no host sync) or exact split sizes")
+    ap.add_argument("--ep-exchange", default="peer", choices=["peer", "fixed", "exact"],
+                    help="expert-parallel row exchange: own kernels over peer memory (default), or NCCL all-to-all with "
+                         "fixed slots per rank pair / exact split sizes")
     ap.add_argument("--api", default="engine", choices=["engine", "layer"],
                     help="entry point timed for value/e2e: the engine runtime ABI (default) or the fused-layer call")
     ap.add_argument("--profile-only", type=int, default=0, metavar="CALLS",

@@ -196,6 +196,66 @@ int netra_ep_pack_rows_launch(void* send_slots, const void* a_fp8, const float* 
 int netra_ep_unpack_rows_launch(float* down_f32, const float* back_slots_f32, const int32_t* offsets_i32, uint32_t ranks,
                                 uint32_t experts_per_rank, uint32_t slot_rows, cudaStream_t stream);
 
+/* ---- Expert parallelism over peer memory (no counterpart in the reference, whose 8-GPU mode is
+ * eight replicas: manifests/gfx950/models/qwen36-moe-m1-golden.json:11-12).
+ * Rank r owns routed experts [r*256/world, (r+1)*256/world) and a copy of the shared expert; its
+ * weight arrays hold the shared slab FIRST, then its routed slabs.  Every exchange (pair counts,
+ * FP8 rows to the owners' expert-major blocks, FP32 rows back to the senders' sorted order) is done
+ * by this library's kernels with stores into the peers' windows and epoch flags; every wait is
+ * bounded by wait_timeout_ns and reports through the status words instead of hanging.  One call is
+ * netra_ep_layer_stage_count() launches (two more above 1024 tokens), no host read-back, so a
+ * caller may capture it into a CUDA graph.  All ranks must make the same sequence of calls.
+ *
+ * A window is device memory that the peers can write: netra_ep_window_create allocates one
+ * (cudaMalloc, zero-filled) and exports a 64-byte CUDA IPC handle that another PROCESS on the same
+ * node opens with netra_ep_window_open; ranks inside one process pass each other's pointers
+ * directly.  All ranks must have created (zeroed) their windows before any rank's first call. */
+int netra_ep_sizes_query(uint32_t world, uint32_t max_tokens, uint32_t row_capacity, uint64_t* workspace_bytes,
+                         uint64_t* window_bytes);
+int netra_ep_window_create(uint64_t bytes, void** window, void* ipc_handle_64);
+int netra_ep_window_open(const void* ipc_handle_64, void** window);
+int netra_ep_window_close(void* window);     /* a window obtained from netra_ep_window_open */
+int netra_ep_window_destroy(void* window);   /* a window obtained from netra_ep_window_create */
+
+typedef struct netra_ep_layer netra_ep_layer_t;
+typedef struct netra_ep_layer_desc {
+  uint32_t struct_size;
+  uint32_t world;               /* ranks; divides 256, at most 16 */
+  uint32_t rank;
+  uint32_t max_tokens;          /* this rank's tokens per call, at most */
+  uint32_t row_capacity;        /* rows one rank's expert block can hold (its own tokens + routed rows from all
+                                   ranks); the same on every rank.  A call that needs more reports the needed
+                                   count in status word 2 and its result is invalid. */
+  uint32_t weights_tiled;
+  uint64_t wait_timeout_ns;     /* bound of every flag wait */
+  const void* router_weight_bf16;
+  const float* router_bias_f32; /* may be NULL */
+  const void* w13_fp8;          /* [1 + 256/world, 1024, 2048] (or its tile order), shared slab first */
+  const float* w13_scale_f32;
+  const void* w2_fp8;           /* [1 + 256/world, 2048, 512] */
+  const float* w2_scale_f32;
+  void* workspace;              /* local device scratch, 1024-byte aligned, netra_ep_sizes_query bytes */
+  uint64_t workspace_bytes;
+  void* const* windows;         /* host array of `world` device pointers; windows[rank] is this rank's own */
+  uint64_t window_bytes;
+} netra_ep_layer_desc_t;
+int netra_ep_layer_create(const netra_ep_layer_desc_t* desc, netra_ep_layer_t** output);
+/* hidden BF16 [tokens, 2048], out BF16 [tokens, 2048], shared_weight FP32 [tokens] or NULL (1.0). */
+int netra_ep_layer_launch(netra_ep_layer_t* layer, const void* hidden_bf16, const float* shared_weight_f32, void* out_bf16,
+                          uint32_t tokens, cudaStream_t stream);
+/* One stage of the call (0 router, 1 top-8 + quantise, 2 sort, 3 publish counts, 4 plan, 5 push rows,
+ * 6 wait, 7 gate_up, 8 down, 9 return rows, 10 wait, 11 combine): for per-stage timing, and for
+ * running several ranks' calls interleaved stage by stage on one stream of one GPU, where every wait
+ * finds its flags already raised. */
+int netra_ep_layer_launch_stage(netra_ep_layer_t* layer, uint32_t stage, const void* hidden_bf16, const float* shared_weight_f32,
+                                void* out_bf16, uint32_t tokens, cudaStream_t stream);
+uint32_t netra_ep_layer_stage_count(void);
+uint32_t netra_ep_layer_launch_count(const netra_ep_layer_t* layer, uint32_t tokens);
+/* Status words (synchronises): 0 gate_up wait expired, 1 down wait expired, 2 rows needed when that
+ * exceeds row_capacity, 3 bit (8*phase + min(rank,7)) set when the flag of that phase and rank timed out. */
+int netra_ep_layer_status(netra_ep_layer_t* layer, uint32_t status_out[4]);
+int netra_ep_layer_destroy(netra_ep_layer_t* layer);
+
 /* Block size and dynamic shared memory of the grouped GEMM kernels (which: 0 gate_up, 1 down), so
  * that an engine manifest written ahead of time can be checked against the built library. */
 int netra_moe_kernel_launch_info(uint32_t which, uint32_t* block_threads, uint32_t* dynamic_smem_bytes);

@@ -35,6 +35,15 @@ class ExpertBlockDesc(ctypes.Structure):
                                       "h_fp8", "h_scale_f32", "down_f32", "offsets_i32", "status_u32")]
 
 
+class EpLayerDesc(ctypes.Structure):
+    _fields_ = [("struct_size", c_u32), ("world", c_u32), ("rank", c_u32), ("max_tokens", c_u32), ("row_capacity", c_u32),
+                ("weights_tiled", c_u32), ("wait_timeout_ns", c_u64),
+                ("router_weight_bf16", c_void_p), ("router_bias_f32", c_void_p),
+                ("w13_fp8", c_void_p), ("w13_scale_f32", c_void_p), ("w2_fp8", c_void_p), ("w2_scale_f32", c_void_p),
+                ("workspace", c_void_p), ("workspace_bytes", c_u64),
+                ("windows", ctypes.POINTER(c_void_p)), ("window_bytes", c_u64)]
+
+
 BRIDGES = ("netra_qwen36_router_bf16", "netra_qwen36_shared_gate_append", "netra_qwen36_moe_gate_up",
            "netra_qwen36_moe_silu_mul_quant", "netra_qwen36_moe_down_reduce")
 
@@ -57,6 +66,18 @@ SIGNATURES = {
     "netra_moe_move_rows_launch": (c_int, [c_void_p] * 3 + [c_u32] * 7 + [c_void_p]),
     "netra_ep_pack_rows_launch": (c_int, [c_void_p] * 4 + [c_u32] * 3 + [c_void_p, c_void_p]),
     "netra_ep_unpack_rows_launch": (c_int, [c_void_p] * 3 + [c_u32] * 3 + [c_void_p]),
+    "netra_ep_sizes_query": (c_int, [c_u32, c_u32, c_u32, ctypes.POINTER(c_u64), ctypes.POINTER(c_u64)]),
+    "netra_ep_window_create": (c_int, [c_u64, ctypes.POINTER(c_void_p), c_void_p]),
+    "netra_ep_window_open": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),
+    "netra_ep_window_close": (c_int, [c_void_p]),
+    "netra_ep_window_destroy": (c_int, [c_void_p]),
+    "netra_ep_layer_create": (c_int, [ctypes.POINTER(EpLayerDesc), ctypes.POINTER(c_void_p)]),
+    "netra_ep_layer_launch": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_u32, c_void_p]),
+    "netra_ep_layer_launch_stage": (c_int, [c_void_p, c_u32, c_void_p, c_void_p, c_void_p, c_u32, c_void_p]),
+    "netra_ep_layer_stage_count": (c_u32, []),
+    "netra_ep_layer_launch_count": (c_u32, [c_void_p, c_u32]),
+    "netra_ep_layer_status": (c_int, [c_void_p, ctypes.POINTER(c_u32 * 4)]),
+    "netra_ep_layer_destroy": (c_int, [c_void_p]),
     "netra_moe_kernel_launch_info": (c_int, [c_u32, ctypes.POINTER(c_u32), ctypes.POINTER(c_u32)]),
     "netra_moe_layer_status": (c_int, [c_void_p, ctypes.POINTER(c_u32 * 4)]),
     "netra_moe_layer_launch_count": (c_u32, [c_void_p, c_u32]),

@@ -447,6 +447,9 @@ int netra_moe_layer_destroy(netra_moe_layer_t* layer) {
 
 }  // extern "C"
 
+// Expert parallelism over peer memory (kernels and host side; uses the helpers and launch_stage() above).
+#include "ep_p2p.cu"
+
 // Entry point with library-owned scratch (needs fail(), fail_cuda(), check_launch() from above).
 #include "static_scratch_sort.cu"
 

@@ -288,3 +288,163 @@ def shard_expert_weights(weights, plan: ExpertParallelPlan):
     """(w13, w13_scale, w2, w2_scale) with 257 slabs -> the shared slab followed by this rank's E_l routed slabs."""
     lo, hi = plan.local_expert_range().start, plan.local_expert_range().stop
     return tuple(torch.cat([t[-1:], t[lo:hi]]).contiguous() for t in weights)
+
+
+# ---------------------------------------------------------------------------------------------
+# Expert parallelism over peer memory: the library's own kernels move the rows (NVLink stores
+# into the peers' windows, epoch flags), no NCCL collective and no host read-back in a call.
+# ---------------------------------------------------------------------------------------------
+class PeerWindow:
+    """Device memory that peer ranks write into.  ``handle`` (64 bytes) lets another process on
+    the node open it; ranks in the same process use ``ptr`` directly."""
+
+    def __init__(self, nbytes: int):
+        from . import abi
+        self.abi, self.lib = abi, abi.load()
+        ptr, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+        abi.check(self.lib.netra_ep_window_create(nbytes, ctypes.byref(ptr), handle), "ep_window_create")
+        self.ptr, self.handle, self.nbytes = ptr.value, handle.raw, nbytes
+        self.opened: list[int] = []
+
+    def open_peer(self, handle: bytes) -> int:
+        ptr = ctypes.c_void_p()
+        self.abi.check(self.lib.netra_ep_window_open(ctypes.create_string_buffer(handle, 64), ctypes.byref(ptr)), "ep_window_open")
+        self.opened.append(ptr.value)
+        return ptr.value
+
+    def close(self) -> None:
+        for p in self.opened:
+            self.lib.netra_ep_window_close(p)
+        self.opened = []
+        if self.ptr:
+            self.lib.netra_ep_window_destroy(self.ptr)
+            self.ptr = None
+
+
+def ep_sizes(world: int, max_tokens: int, row_capacity: int) -> tuple[int, int]:
+    """(local workspace bytes, window bytes) of one rank."""
+    from . import abi
+    ws, win = ctypes.c_uint64(), ctypes.c_uint64()
+    abi.check(abi.load().netra_ep_sizes_query(world, max_tokens, row_capacity, ctypes.byref(ws), ctypes.byref(win)), "ep_sizes_query")
+    return ws.value, win.value
+
+
+def default_row_capacity(world: int, max_tokens: int, headroom: Optional[float] = None) -> int:
+    """Rows of one rank's expert block: its own tokens plus the routed rows of all ranks for its experts.
+    Without ``headroom`` this is the worst case (every pair of every rank routed here), which can never
+    overflow; with it, the mean of near-uniform routing plus ``headroom`` standard deviations."""
+    pairs = world * max_tokens * TOPK
+    if world == 1 or headroom is None:
+        return max_tokens + pairs
+    p = 1.0 / world
+    mean, sd = pairs * p, (pairs * p * (1 - p)) ** 0.5
+    return max_tokens + min(pairs, int(-(-(mean + headroom * sd + 64) // 64) * 64))
+
+
+class PeerExpertParallelLayer:
+    """One rank of the expert-parallel layer with peer-memory exchange (``netra_ep_layer_*``).
+
+    ``w13`` etc. hold the shared expert's slab first, then this rank's routed slabs
+    (``shard_expert_weights``).  ``windows`` is the list of all ranks' window pointers (this rank's
+    own at index ``plan.rank``); when it is None the layer creates its window and exchanges the
+    handles through ``torch.distributed`` (one process per GPU).  A call enqueues a fixed sequence
+    of kernels and may be captured into a CUDA graph; all ranks must make the same calls."""
+
+    def __init__(self, plan: ExpertParallelPlan, router_w, w13, w13_scale, w2, w2_scale, max_local_tokens: int,
+                 router_bias=None, tiled: bool = True, row_capacity: Optional[int] = None, wait_timeout_s: float = 2.0,
+                 windows: Optional[list[int]] = None):
+        from . import abi
+        self.plan, self.abi, self.lib = plan, abi, abi.load()
+        world, e_l = plan.world, plan.experts_per_rank
+        if w13.shape[0] != e_l + 1:
+            raise ValueError(f"this rank holds the shared slab + {e_l} routed slabs, got {w13.shape[0]}")
+        dev = router_w.device
+        self.device, self.t_max = dev, int(max_local_tokens)
+        self.row_capacity = int(row_capacity) if row_capacity else default_row_capacity(world, self.t_max)
+        ws_bytes, win_bytes = ep_sizes(world, self.t_max, self.row_capacity)
+        self.window_bytes = win_bytes
+        self.own_window: Optional[PeerWindow] = None
+        if windows is None:
+            self.own_window = PeerWindow(win_bytes)
+            if world > 1:
+                handles: list = [None] * world
+                dist.all_gather_object(handles, self.own_window.handle, group=plan.group)
+                windows = [self.own_window.ptr if g == plan.rank else self.own_window.open_peer(handles[g]) for g in range(world)]
+                dist.barrier(group=plan.group)          # every window exists and is zeroed before anyone's first call
+            else:
+                windows = [self.own_window.ptr]
+        if len(windows) != world:
+            raise ValueError("one window pointer per rank is required")
+        if tiled:
+            w13, w2 = self._repack(w13), self._repack(w2)
+        self.workspace = torch.zeros(ws_bytes + 1024, dtype=torch.uint8, device=dev)
+        base = (self.workspace.data_ptr() + 1023) // 1024 * 1024
+        desc = abi.EpLayerDesc()
+        desc.struct_size = ctypes.sizeof(desc)
+        desc.world, desc.rank, desc.max_tokens, desc.row_capacity = world, plan.rank, self.t_max, self.row_capacity
+        desc.weights_tiled, desc.wait_timeout_ns = int(tiled), int(wait_timeout_s * 1e9)
+        desc.router_weight_bf16 = router_w.data_ptr()
+        desc.router_bias_f32 = router_bias.data_ptr() if router_bias is not None else None
+        desc.w13_fp8, desc.w13_scale_f32 = w13.data_ptr(), w13_scale.data_ptr()
+        desc.w2_fp8, desc.w2_scale_f32 = w2.data_ptr(), w2_scale.data_ptr()
+        desc.workspace, desc.workspace_bytes = base, ws_bytes
+        self._windows = (ctypes.c_void_p * world)(*windows)
+        desc.windows, desc.window_bytes = self._windows, win_bytes
+        handle = ctypes.c_void_p()
+        torch.cuda.synchronize(dev)
+        abi.check(self.lib.netra_ep_layer_create(ctypes.byref(desc), ctypes.byref(handle)), "ep_layer_create")
+        self.handle = handle
+        self._keep = (router_w, w13, w13_scale, w2, w2_scale, router_bias)
+        self.stage_count = int(self.lib.netra_ep_layer_stage_count())
+
+    def _repack(self, w: torch.Tensor) -> torch.Tensor:
+        out = torch.empty_like(w)
+        self.abi.check(self.lib.netra_moe_repack_tiles_launch(out.data_ptr(), w.data_ptr(), w.shape[0] * w.shape[1],
+                                                              w.shape[2] * w.element_size(), torch.cuda.current_stream().cuda_stream),
+                       "repack_tiles_launch")
+        return out
+
+    def launches_per_call(self, tokens: int) -> int:
+        return int(self.lib.netra_ep_layer_launch_count(self.handle, tokens))
+
+    def _args(self, hidden, shared_weight, out):
+        if hidden.dtype != torch.bfloat16 or hidden.dim() != 2 or hidden.shape[1] != HIDDEN or not hidden.is_contiguous():
+            raise ValueError("hidden must be contiguous BF16 [tokens, 2048]")
+        if hidden.shape[0] > self.t_max:
+            raise ValueError("more local tokens than the layer was sized for")
+        if out is None:
+            out = torch.empty_like(hidden)
+        sw = shared_weight.data_ptr() if shared_weight is not None else None
+        return hidden.data_ptr(), sw, out, hidden.shape[0], torch.cuda.current_stream().cuda_stream
+
+    def __call__(self, hidden: torch.Tensor, shared_weight: Optional[torch.Tensor] = None,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        h, sw, out, tokens, stream = self._args(hidden, shared_weight, out)
+        self.abi.check(self.lib.netra_ep_layer_launch(self.handle, h, sw, out.data_ptr(), tokens, stream), "ep_layer_launch")
+        return out
+
+    def launch_stage(self, stage: int, hidden: torch.Tensor, out: torch.Tensor, shared_weight: Optional[torch.Tensor] = None) -> None:
+        h, sw, out, tokens, stream = self._args(hidden, shared_weight, out)
+        self.abi.check(self.lib.netra_ep_layer_launch_stage(self.handle, stage, h, sw, out.data_ptr(), tokens, stream), "ep_layer_launch_stage")
+
+    def status(self) -> list[int]:
+        words = (ctypes.c_uint32 * 4)()
+        self.abi.check(self.lib.netra_ep_layer_status(self.handle, ctypes.byref(words)), "ep_layer_status")
+        return list(words)
+
+    def check_status(self) -> None:
+        words = self.status()
+        if words[2]:
+            raise self.abi.NetraError(f"an expert block needed {words[2]} rows but row_capacity is {self.row_capacity}")
+        if words[3]:
+            raise self.abi.NetraError(f"a wait for a peer's flag timed out (mask {words[3]:#x}): a rank is missing or late")
+        if any(words[:2]):
+            raise self.abi.NetraError(f"device status words {words}: a bounded wait expired inside a grouped GEMM")
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            self.lib.netra_ep_layer_destroy(self.handle)
+            self.handle = None
+        if self.own_window is not None:
+            self.own_window.close()
+            self.own_window = None

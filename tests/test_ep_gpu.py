@@ -116,7 +116,7 @@ def _ep_rank(rank, world, port, tokens, exchange, results):
         local = tuple(t.to(dev) for t in shard_expert_weights(weights, plan))
         t_l = tokens // world
         layer = ExpertParallelMoELayer(plan, router_w.to(dev), *local, max_local_tokens=t_l, router_bias=bias.to(dev),
-                                       exchange=exchange)
+                                       exchange=exchange, slot_rows=t_l * 8)   # skewed routing: size the slots for the worst case
         mine = hidden[rank * t_l:(rank + 1) * t_l].to(dev)
         out = layer(mine)
         out2 = layer(mine)                                   # a second call reuses every buffer
