@@ -515,6 +515,23 @@ def run_expert_parallel(args) -> None:
         e1.record(stream)
         barrier()
         block_ms = max_over_ranks(e0.elapsed_time(e1) / steps)
+
+        stage_us = None
+        if args.ep_exchange == "peer":
+            # each stage between two events, direct launches (small stages read high: the gap includes launch latency)
+            names = ["router", "topk_quant", "sort", "publish_counts", "plan", "push_rows", "wait_rows", "gate_up", "down",
+                     "return_rows", "wait_return", "combine"]
+            reps = min(steps, 50)
+            evs = [[torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)] for _ in range(reps)]
+            barrier()
+            for it in range(reps):
+                for st in range(len(names)):
+                    evs[it][st].record(stream)
+                    layer.launch_stage(st, hidden, out)
+                evs[it][len(names)].record(stream)
+            barrier()
+            stage_us = {name: round(sum(evs[it][st].elapsed_time(evs[it][st + 1]) for it in range(reps)) / reps * 1e3, 1)
+                        for st, name in enumerate(names)}
     layer.check_status()
     if rank == 0:
         peak, peak_kind = measured_hbm_peak()
@@ -539,6 +556,7 @@ def run_expert_parallel(args) -> None:
                        "api": "netra_ep_layer_launch" if args.ep_exchange == "peer"
                               else "ExpertParallelMoELayer over netra_moe_layer_launch_stage / netra_moe_expert_block_launch"},
             "gpu_launches": steps * launches,
+            "stage_us_rank0": stage_us,
             "e2e": {"value": world * tokens / (e2e_ms / 1e3), "unit": UNIT, "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": tokens * 2048 * 2, "d2h_bytes_per_step": tokens * 2048 * 2},
             "roofline": {"bound": "hbm", "kernel": "netra_moe_gate_up_umma_sm100 + netra_moe_down_umma_sm100 (expert block, timed alone)",

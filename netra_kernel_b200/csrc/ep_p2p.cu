@@ -88,8 +88,7 @@ netra_ep_publish_counts_sm100(EpPeers peers, EpWindowLayout lay, EpTables* __res
     for (uint32_t g = 0; g < world; ++g)
       reinterpret_cast<int32_t*>(peers.win[g] + lay.matrix)[rank * kEpMatrixPitch + tid] = v;
   }
-  __threadfence_system();
-  __syncthreads();
+  __syncthreads();                 // the release stores below are cumulative over the block's stores
   if (tid < (int)world) st_release_sys(reinterpret_cast<uint32_t*>(peers.win[tid] + lay.flags) + 0 * kEpFlagPitch + rank, s_epoch);
 }
 
@@ -110,7 +109,9 @@ extern "C" __global__ void __launch_bounds__(1024)
 netra_ep_plan_sm100(const uint8_t* __restrict__ window, EpWindowLayout lay, EpTables* __restrict__ tab, uint32_t world,
                     uint32_t rank, uint32_t capacity, uint64_t timeout_ns) {
   __shared__ int C[kEpMaxRanks][kRouted];    // C[s][e]: pairs of rank s for global expert e
+  __shared__ int rowpre[kEpMaxRanks][kRouted];
   __shared__ int colsum[kRouted];
+  __shared__ int colpre[kRouted];
   __shared__ int exp_base[kRouted];          // first row of expert e in its owner's block
   __shared__ int tok[kEpMaxRanks];
   const int tid = threadIdx.x;
@@ -128,16 +129,49 @@ netra_ep_plan_sm100(const uint8_t* __restrict__ window, EpWindowLayout lay, EpTa
   }
   if (tid < (int)world) tok[tid] = min(max(__ldcg(matrix + tid * kEpMatrixPitch + kRouted), 0), (int)capacity);
   __syncthreads();
+  // rowpre[s][e] = pairs of source s for experts below e (its sorted row of expert e): one warp per source,
+  // eight experts per lane, shuffle scan across the lanes
+  {
+    const int w = tid >> 5, lane = tid & 31;
+    if (w < (int)world) {
+      int v[8], sum = 0;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { v[k] = C[w][lane * 8 + k]; sum += v[k]; }
+      int incl = sum;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += o;
+      }
+      int run = incl - sum;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { rowpre[w][lane * 8 + k] = run; run += v[k]; }
+    }
+  }
   if (tid < kRouted) {
     int sum = 0;
     for (int s = 0; s < (int)world; ++s) sum += C[s][tid];
     colsum[tid] = sum;
   }
   __syncthreads();
+  if (tid < 32) {                            // colpre[e] = rows of all experts below e, over all sources
+    int v[8], sum = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { v[k] = colsum[tid * 8 + k]; sum += v[k]; }
+    int incl = sum;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int o = __shfl_up_sync(0xffffffffu, incl, d);
+      if (tid >= d) incl += o;
+    }
+    int run = incl - sum;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { colpre[tid * 8 + k] = run; run += v[k]; }
+  }
+  __syncthreads();
   if (tid < kRouted) {
     const int g = tid / e_l;
-    int base = tok[g];
-    for (int e = g * e_l; e < tid; ++e) base += colsum[e];
+    const int base = tok[g] + colpre[tid] - colpre[g * e_l];
     exp_base[tid] = base;
     int mine = base;
     for (int s = 0; s < (int)rank; ++s) mine += C[s][tid];
@@ -149,10 +183,8 @@ netra_ep_plan_sm100(const uint8_t* __restrict__ window, EpWindowLayout lay, EpTa
     const int j = tid / (int)world, s = tid % (int)world, e = (int)rank * e_l + j;
     int start = exp_base[e];
     for (int ss = 0; ss < s; ++ss) start += C[ss][e];
-    int sorted_row = 0;
-    for (int ee = 0; ee < e; ++ee) sorted_row += C[s][ee];
     tab->blk_start[tid] = start;
-    tab->ret_row[tid] = sorted_row;
+    tab->ret_row[tid] = rowpre[s][e];
   }
   if (tid < e_l) tab->offsets[1 + tid] = min(exp_base[(int)rank * e_l + tid], (int)capacity);
   if (tid == 0) {
@@ -173,13 +205,22 @@ netra_ep_plan_sm100(const uint8_t* __restrict__ window, EpWindowLayout lay, EpTa
 __device__ __forceinline__ void ep_signal_when_last(const EpPeers& peers, const EpWindowLayout& lay, EpTables* tab, uint32_t* counter,
                                                     uint32_t phase, uint32_t world, uint32_t rank) {
   __shared__ uint32_t s_last;
-  __threadfence_system();
+  // Each block orders its stores before its count at GPU scope (thread 0's fence is cumulative over the
+  // block's stores after the barrier); the last block alone pays for the system-scope fence, which is
+  // cumulative over everything it has observed, before it raises the flags.  A system-scope fence per
+  // block costs several microseconds per kernel on this part.
   __syncthreads();
-  if (threadIdx.x == 0) s_last = atomicAdd(counter, 1u) == gridDim.x - 1;
+  if (threadIdx.x == 0) {
+    __threadfence();
+    s_last = atomicAdd(counter, 1u) == gridDim.x - 1;
+  }
   __syncthreads();
   if (s_last) {
-    __threadfence_system();
-    if (threadIdx.x == 0) *counter = 0;
+    if (threadIdx.x == 0) {
+      *counter = 0;
+      __threadfence_system();
+    }
+    __syncthreads();
     if (threadIdx.x < world)
       st_release_sys(reinterpret_cast<uint32_t*>(peers.win[threadIdx.x] + lay.flags) + phase * kEpFlagPitch + rank, tab->epoch);
   }
@@ -226,14 +267,16 @@ netra_ep_push_rows_sm100(EpPeers peers, EpWindowLayout lay, EpTables* __restrict
 
 // return: block row r -> the sorted-order FP32 buffer of the rank it came from (the shared group's
 // rows go to this rank's own shared rows, pairs + t).  One warp per row.
-// grid ceil(capacity / 8), block 256.
+// grid: any (rows are taken in a grid-stride loop), block 256.
 extern "C" __global__ void __launch_bounds__(256)
 netra_ep_return_rows_sm100(EpPeers peers, EpWindowLayout lay, EpTables* __restrict__ tab, const float* __restrict__ blk_down,
                            uint32_t tokens, uint32_t max_tokens, uint32_t world, uint32_t rank, uint32_t capacity) {
-  const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+  __shared__ int s_start[kRouted + 1];
+  for (int i = threadIdx.x; i <= kRouted; i += 256) s_start[i] = tab->blk_start[i];
+  __syncthreads();
   const int lane = threadIdx.x & 31;
-  const int total = min(tab->blk_start[kRouted], (int)capacity);
-  if (r < total) {
+  const int total = min(s_start[kRouted], (int)capacity);
+  for (int r = blockIdx.x * 8 + (threadIdx.x >> 5); r < total; r += gridDim.x * 8) {
     int g, dst_row;
     if (r < (int)tokens) {
       g = (int)rank;
@@ -242,10 +285,10 @@ netra_ep_return_rows_sm100(EpPeers peers, EpWindowLayout lay, EpTables* __restri
       int lo = 0, hi = kRouted;              // last bucket whose first row is <= r
       while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
-        if (tab->blk_start[mid] <= r) lo = mid; else hi = mid;
+        if (s_start[mid] <= r) lo = mid; else hi = mid;
       }
       g = lo % (int)world;
-      dst_row = tab->ret_row[lo] + (r - tab->blk_start[lo]);
+      dst_row = tab->ret_row[lo] + (r - s_start[lo]);
     }
     if (dst_row >= 0 && dst_row < (int)max_tokens * kSlots) {
       const uint4* src = reinterpret_cast<const uint4*>(blk_down + (size_t)r * kHidden);
@@ -321,6 +364,14 @@ int ep_check_shape(uint32_t world, uint32_t max_tokens, uint32_t capacity) {
   return 0;
 }
 
+// enough blocks for the expected rows (own tokens + an even share of all pairs, doubled), at most four per SM
+uint32_t ep_return_grid(const netra_ep_layer* L) {
+  const uint64_t expected = (uint64_t)L->desc.max_tokens * (1 + 2 * kTopK);
+  const uint64_t blocks = (expected < L->desc.row_capacity ? expected : L->desc.row_capacity) / 8 + 1;
+  const uint64_t most = (uint64_t)L->sm_count * 4;
+  return (uint32_t)(blocks < most ? blocks : most);
+}
+
 void ep_launch_stage(netra_ep_layer* L, uint32_t stage, const void* hidden, const float* shared_w, void* out, uint32_t tokens,
                      cudaStream_t stream) {
   const netra_ep_layer_desc_t& d = L->desc;
@@ -356,7 +407,7 @@ void ep_launch_stage(netra_ep_layer* L, uint32_t stage, const void* hidden, cons
           d.weights_tiled, L->tab->status + 1);
       break;
     case 9:
-      netra_ep_return_rows_sm100<<<(d.row_capacity + 7) / 8, 256, 0, stream>>>(L->peers, L->wl, L->tab, L->blk_down, tokens, d.max_tokens,
+      netra_ep_return_rows_sm100<<<ep_return_grid(L), 256, 0, stream>>>(L->peers, L->wl, L->tab, L->blk_down, tokens, d.max_tokens,
                                                                              d.world, d.rank, d.row_capacity);
       break;
     case 10: netra_ep_wait_sm100<<<1, 32, 0, stream>>>(L->window, L->wl, L->tab, 2, d.world, d.wait_timeout_ns); break;
