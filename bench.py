@@ -519,8 +519,8 @@ def run_expert_parallel(args) -> None:
         stage_us = None
         if args.ep_exchange == "peer":
             # each stage between two events, direct launches (small stages read high: the gap includes launch latency)
-            names = ["router", "topk_quant", "sort", "publish_counts", "plan", "push_rows", "wait_rows", "gate_up", "down",
-                     "return_rows", "wait_return", "combine"]
+            names = ["router", "topk_quant", "sort", "publish_counts", "plan", "push_rows", "wait_rows_and_table", "gate_up",
+                     "down_and_return", "wait_return", "combine"]
             reps = min(steps, 50)
             evs = [[torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)] for _ in range(reps)]
             barrier()

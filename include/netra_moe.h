@@ -244,7 +244,7 @@ int netra_ep_layer_create(const netra_ep_layer_desc_t* desc, netra_ep_layer_t** 
 int netra_ep_layer_launch(netra_ep_layer_t* layer, const void* hidden_bf16, const float* shared_weight_f32, void* out_bf16,
                           uint32_t tokens, cudaStream_t stream);
 /* One stage of the call (0 router, 1 top-8 + quantise, 2 sort, 3 publish counts, 4 plan, 5 push rows,
- * 6 wait, 7 gate_up, 8 down, 9 return rows, 10 wait, 11 combine): for per-stage timing, and for
+ * 6 wait + return table, 7 gate_up, 8 down with the return fused in, 9 wait, 10 combine): for per-stage timing, and for
  * running several ranks' calls interleaved stage by stage on one stream of one GPU, where every wait
  * finds its flags already raised. */
 int netra_ep_layer_launch_stage(netra_ep_layer_t* layer, uint32_t stage, const void* hidden_bf16, const float* shared_weight_f32,

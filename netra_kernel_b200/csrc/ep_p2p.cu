@@ -13,8 +13,10 @@
 //   push     each sorted row (2048 FP8 codes + 16 scales) is stored straight into its expert-major
 //            position in the owner's activation block; the rank's own tokens become the shared
 //            expert's rows (group 0)                                                        (flag 1)
-//   wait, grouped gate_up and down GEMMs over E_l + 1 slabs
-//   return   each FP32 down row is stored into the sending rank's sorted-order buffer        (flag 2)
+//   wait     for the pushed rows; the same launch builds the table "block row -> where its result goes"
+//   gate_up  grouped GEMM over E_l + 1 slabs
+//   down     grouped GEMM whose epilogue stores each FP32 row straight into the sending rank's
+//            sorted-order buffer (the return overlaps the remaining tiles)                   (flag 2)
 //   wait, slot-ordered combine (the same kernel as on one GPU)
 // A flag holds the epoch (call number) of its writer; a wait spins until the flag reaches the
 // current epoch or a time limit passes, in which case a status word records it and the kernel
@@ -265,18 +267,19 @@ netra_ep_push_rows_sm100(EpPeers peers, EpWindowLayout lay, EpTables* __restrict
   ep_signal_when_last(peers, lay, tab, &tab->done_push, 1, world, rank);
 }
 
-// return: block row r -> the sorted-order FP32 buffer of the rank it came from (the shared group's
-// rows go to this rank's own shared rows, pairs + t).  One warp per row.
-// grid: any (rows are taken in a grid-stride loop), block 256.
+// wait for the pushed rows (flag 1 of every rank; block 0) and build the return table: row_ptr[r] = where
+// block row r's FP32 down row goes - the sorted-order buffer of the rank it came from, or this rank's
+// own shared rows (pairs + t) for the shared group.  Rows without a valid destination point at the local
+// block buffer.  grid: any (grid-stride), block 256.
 extern "C" __global__ void __launch_bounds__(256)
-netra_ep_return_rows_sm100(EpPeers peers, EpWindowLayout lay, EpTables* __restrict__ tab, const float* __restrict__ blk_down,
-                           uint32_t tokens, uint32_t max_tokens, uint32_t world, uint32_t rank, uint32_t capacity) {
+netra_ep_wait_table_sm100(EpPeers peers, EpWindowLayout lay, EpTables* __restrict__ tab, float** __restrict__ row_ptr,
+                          float* __restrict__ blk_down, uint32_t tokens, uint32_t max_tokens, uint32_t world, uint32_t rank,
+                          uint32_t capacity, uint64_t timeout_ns) {
   __shared__ int s_start[kRouted + 1];
   for (int i = threadIdx.x; i <= kRouted; i += 256) s_start[i] = tab->blk_start[i];
   __syncthreads();
-  const int lane = threadIdx.x & 31;
   const int total = min(s_start[kRouted], (int)capacity);
-  for (int r = blockIdx.x * 8 + (threadIdx.x >> 5); r < total; r += gridDim.x * 8) {
+  for (int r = blockIdx.x * 256 + threadIdx.x; r < total; r += gridDim.x * 256) {
     int g, dst_row;
     if (r < (int)tokens) {
       g = (int)rank;
@@ -290,13 +293,27 @@ netra_ep_return_rows_sm100(EpPeers peers, EpWindowLayout lay, EpTables* __restri
       g = lo % (int)world;
       dst_row = tab->ret_row[lo] + (r - s_start[lo]);
     }
-    if (dst_row >= 0 && dst_row < (int)max_tokens * kSlots) {
-      const uint4* src = reinterpret_cast<const uint4*>(blk_down + (size_t)r * kHidden);
-      uint4* dst = reinterpret_cast<uint4*>(peers.win[g] + lay.down + (size_t)dst_row * kHidden * 4);
-#pragma unroll
-      for (int c = 0; c < 16; ++c) dst[c * 32 + lane] = src[c * 32 + lane];
-    }
+    row_ptr[r] = (dst_row >= 0 && dst_row < (int)max_tokens * kSlots)
+                     ? reinterpret_cast<float*>(peers.win[g] + lay.down) + (size_t)dst_row * kHidden
+                     : blk_down + (size_t)r * kHidden;
   }
+  if (blockIdx.x == 0 && threadIdx.x < world) {
+    const uint32_t* flag = reinterpret_cast<const uint32_t*>(peers.win[rank] + lay.flags) + 1 * kEpFlagPitch + threadIdx.x;
+    if (!ep_wait_flag(flag, tab->epoch, timeout_ns)) atomicOr(&tab->status[3], (1u << 8) << min((int)threadIdx.x, 7));
+  }
+}
+
+// The down projection with the return fused in: every FP32 output row is stored straight to row_ptr[row]
+// (a peer's sorted-order buffer over NVLink, overlapping the remaining tiles), and the last CTA to finish
+// raises flag 2 at every peer.
+extern "C" __global__ void __launch_bounds__(kGemmThreads, 1)
+netra_ep_down_return_umma_sm100(const __grid_constant__ CUtensorMap tm_w2, const __grid_constant__ CUtensorMap tm_h32,
+                                const __grid_constant__ CUtensorMap tm_h64, const __grid_constant__ CUtensorMap tm_h128,
+                                const float* h_scale, const float* w2_scale, const int32_t* offsets, float* const* row_ptr,
+                                uint32_t num_groups, uint32_t w_tiled, uint32_t* status, EpPeers peers, EpWindowLayout lay,
+                                EpTables* tab, uint32_t world, uint32_t rank) {
+  grouped_gemm_body<false>(&tm_w2, &tm_h32, &tm_h64, &tm_h128, h_scale, w2_scale, offsets, nullptr, nullptr, nullptr, row_ptr,
+                           num_groups, w_tiled, status);
   ep_signal_when_last(peers, lay, tab, &tab->done_ret, 2, world, rank);
 }
 
@@ -315,6 +332,7 @@ struct netra_ep_layer {
   uint8_t* blk_h;
   float* blk_hs;
   float* blk_down;
+  float** row_ptr;
   EpTables* tab;
   CUtensorMap tm_w13, tm_w2, tm_a32, tm_a64, tm_a128, tm_h32, tm_h64, tm_h128;
   int sm_count;
@@ -323,7 +341,7 @@ struct netra_ep_layer {
 
 namespace {
 
-constexpr uint32_t kEpStageCount = 12;
+constexpr uint32_t kEpStageCount = 11;
 
 EpWindowLayout ep_window_layout(uint32_t world, uint32_t max_tokens, uint32_t capacity) {
   EpWindowLayout l;
@@ -339,7 +357,7 @@ EpWindowLayout ep_window_layout(uint32_t world, uint32_t max_tokens, uint32_t ca
 }
 
 struct EpWorkspaceLayout {
-  uint64_t route, blk_h, blk_hs, blk_down, tables, total;
+  uint64_t route, blk_h, blk_hs, blk_down, row_ptr, tables, total;
 };
 
 int ep_workspace_layout(uint32_t max_tokens, uint32_t capacity, EpWorkspaceLayout* out) {
@@ -352,6 +370,7 @@ int ep_workspace_layout(uint32_t max_tokens, uint32_t capacity, EpWorkspaceLayou
   out->blk_h = take((uint64_t)capacity * kInter);
   out->blk_hs = take(((uint64_t)capacity + 128) * kInterBlocks * 4);
   out->blk_down = take((uint64_t)capacity * kHidden * 4);
+  out->row_ptr = take((uint64_t)capacity * 8);
   out->tables = take(sizeof(EpTables));
   out->total = o;
   return 0;
@@ -362,14 +381,6 @@ int ep_check_shape(uint32_t world, uint32_t max_tokens, uint32_t capacity) {
   if (max_tokens == 0 || max_tokens > (1u << 20)) return fail("expert parallelism: max_tokens out of range");
   if (capacity < max_tokens || capacity > (1u << 24)) return fail("expert parallelism: row_capacity must hold at least the rank's own tokens");
   return 0;
-}
-
-// enough blocks for the expected rows (own tokens + an even share of all pairs, doubled), at most four per SM
-uint32_t ep_return_grid(const netra_ep_layer* L) {
-  const uint64_t expected = (uint64_t)L->desc.max_tokens * (1 + 2 * kTopK);
-  const uint64_t blocks = (expected < L->desc.row_capacity ? expected : L->desc.row_capacity) / 8 + 1;
-  const uint64_t most = (uint64_t)L->sm_count * 4;
-  return (uint32_t)(blocks < most ? blocks : most);
 }
 
 void ep_launch_stage(netra_ep_layer* L, uint32_t stage, const void* hidden, const float* shared_w, void* out, uint32_t tokens,
@@ -395,22 +406,24 @@ void ep_launch_stage(netra_ep_layer* L, uint32_t stage, const void* hidden, cons
           L->peers, L->wl, L->tab, ws + R.a_fp8, (const float*)(ws + R.a_scale), (const int32_t*)(ws + R.perm),
           (const int32_t*)(ws + R.topk_ids), (const int32_t*)(ws + R.offsets), tokens, d.world, d.rank, d.row_capacity);
       break;
-    case 6: netra_ep_wait_sm100<<<1, 32, 0, stream>>>(L->window, L->wl, L->tab, 1, d.world, d.wait_timeout_ns); break;
+    case 6: {
+      const uint32_t expected = d.max_tokens * (1 + 2 * kTopK);          // own tokens + twice an even share of the pairs
+      const uint32_t rows = expected < d.row_capacity ? expected : d.row_capacity;
+      netra_ep_wait_table_sm100<<<(rows + 255) / 256, 256, 0, stream>>>(L->peers, L->wl, L->tab, L->row_ptr, L->blk_down, tokens,
+                                                                       d.max_tokens, d.world, d.rank, d.row_capacity, d.wait_timeout_ns);
+      break;
+    }
     case 7:
       netra_moe_gate_up_umma_sm100<<<L->sm_count, kGemmThreads, gate_up_smem_bytes(), stream>>>(
           L->tm_w13, L->tm_a32, L->tm_a64, L->tm_a128, (const float*)(L->window + L->wl.blk_as), d.w13_scale_f32, L->tab->offsets,
           L->blk_h, L->blk_hs, L->e_l + 1, d.weights_tiled, L->tab->status);
       break;
     case 8:
-      netra_moe_down_umma_sm100<<<L->sm_count, kGemmThreads, down_smem_bytes(), stream>>>(
-          L->tm_w2, L->tm_h32, L->tm_h64, L->tm_h128, L->blk_hs, d.w2_scale_f32, L->tab->offsets, L->blk_down, L->e_l + 1,
-          d.weights_tiled, L->tab->status + 1);
+      netra_ep_down_return_umma_sm100<<<L->sm_count, kGemmThreads, down_smem_bytes(), stream>>>(
+          L->tm_w2, L->tm_h32, L->tm_h64, L->tm_h128, L->blk_hs, d.w2_scale_f32, L->tab->offsets, L->row_ptr, L->e_l + 1,
+          d.weights_tiled, L->tab->status + 1, L->peers, L->wl, L->tab, d.world, d.rank);
       break;
-    case 9:
-      netra_ep_return_rows_sm100<<<ep_return_grid(L), 256, 0, stream>>>(L->peers, L->wl, L->tab, L->blk_down, tokens, d.max_tokens,
-                                                                             d.world, d.rank, d.row_capacity);
-      break;
-    case 10: netra_ep_wait_sm100<<<1, 32, 0, stream>>>(L->window, L->wl, L->tab, 2, d.world, d.wait_timeout_ns); break;
+    case 9: netra_ep_wait_sm100<<<1, 32, 0, stream>>>(L->window, L->wl, L->tab, 2, d.world, d.wait_timeout_ns); break;
     default:
       netra_moe_combine_sm100<<<tokens, 256, 0, stream>>>((uint16_t*)out, (const float*)(L->window + L->wl.down),
                                                           (const float*)(ws + R.topk_weights), (const int32_t*)(ws + R.inv_perm), tokens);
@@ -498,6 +511,7 @@ int netra_ep_layer_create(const netra_ep_layer_desc_t* desc, netra_ep_layer_t** 
   L->blk_h = ws + wsl.blk_h;
   L->blk_hs = (float*)(ws + wsl.blk_hs);
   L->blk_down = (float*)(ws + wsl.blk_down);
+  L->row_ptr = (float**)(ws + wsl.row_ptr);
   L->tab = (EpTables*)(ws + wsl.tables);
   L->route = nullptr;
   netra_moe_layer_desc_t rd;
@@ -517,6 +531,10 @@ int netra_ep_layer_create(const netra_ep_layer_desc_t* desc, netra_ep_layer_t** 
   int rc = netra_moe_layer_create(&rd, &L->route);
   if (rc) { delete L; return rc; }
   L->sm_count = L->route->sm_count;
+  {
+    cudaError_t e = cudaFuncSetAttribute(netra_ep_down_return_umma_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, down_smem_bytes());
+    if (e != cudaSuccess) { netra_moe_layer_destroy(L->route); delete L; return fail_cuda("cudaFuncSetAttribute(down_return)", e); }
+  }
   const uint64_t g = L->e_l + 1, rows = desc->row_capacity;
   if (desc->weights_tiled) {
     rc = rc ? rc : encode_u8_2d(&L->tm_w13, desc->w13_fp8, g * 2 * kInter * kHiddenBlocks, kBlock, 128);

@@ -207,7 +207,8 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
                                                   const float* __restrict__ x_scale, const float* __restrict__ w_scale,
                                                   const int32_t* __restrict__ offsets, uint8_t* __restrict__ h_fp8,
                                                   float* __restrict__ h_scale, float* __restrict__ down,
-                                                  uint32_t num_groups, uint32_t w_tiled, uint32_t* status) {
+                                                  float* const* __restrict__ row_ptr, uint32_t num_groups, uint32_t w_tiled,
+                                                  uint32_t* status) {
   using C = Cfg<kGateUp>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -519,9 +520,14 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
         group_barrier(grp);   // red[] is free for the next item
         if (warp == 2 && lane == 0) NETRA_TRACE_MARK(7, n_item * 8 + 4);
       } else {
+        // row_ptr (expert parallelism): each output row goes to its own destination, possibly a peer GPU's memory
 #pragma unroll
         for (int c = 0; c < C::kColsPerGroup; ++c)
-          if (c < my_cols) down[(size_t)(w.row0 + col_base + c) * kHidden + ntile * kTileRows + r] = acc[0][c];
+          if (c < my_cols) {
+            const int row = w.row0 + col_base + c;
+            float* dst = row_ptr != nullptr ? row_ptr[row] : down + (size_t)row * kHidden;
+            dst[ntile * kTileRows + r] = acc[0][c];
+          }
       }
       }   // sub tile
     }
@@ -543,7 +549,7 @@ netra_moe_gate_up_umma_sm100(const __grid_constant__ CUtensorMap tm_w13, const _
                              const __grid_constant__ CUtensorMap tm_a64, const __grid_constant__ CUtensorMap tm_a128,
                              const float* a_scale, const float* w13_scale, const int32_t* offsets, uint8_t* h_fp8,
                              float* h_scale, uint32_t num_groups, uint32_t w_tiled, uint32_t* status) {
-  grouped_gemm_body<true>(&tm_w13, &tm_a32, &tm_a64, &tm_a128, a_scale, w13_scale, offsets, h_fp8, h_scale, nullptr,
+  grouped_gemm_body<true>(&tm_w13, &tm_a32, &tm_a64, &tm_a128, a_scale, w13_scale, offsets, h_fp8, h_scale, nullptr, nullptr,
                           num_groups, w_tiled, status);
 }
 
@@ -552,7 +558,7 @@ netra_moe_down_umma_sm100(const __grid_constant__ CUtensorMap tm_w2, const __gri
                           const __grid_constant__ CUtensorMap tm_h64, const __grid_constant__ CUtensorMap tm_h128,
                           const float* h_scale, const float* w2_scale, const int32_t* offsets, float* down,
                           uint32_t num_groups, uint32_t w_tiled, uint32_t* status) {
-  grouped_gemm_body<false>(&tm_w2, &tm_h32, &tm_h64, &tm_h128, h_scale, w2_scale, offsets, nullptr, nullptr, down,
+  grouped_gemm_body<false>(&tm_w2, &tm_h32, &tm_h64, &tm_h128, h_scale, w2_scale, offsets, nullptr, nullptr, down, nullptr,
                            num_groups, w_tiled, status);
 }
 
