@@ -19,7 +19,8 @@
  *    entry point for this sequence: it spans the engine launch of
  *    runtime/gfx950/engine/netra_engine.h:84-86 plus third-party top-k / sort / quantisation
  *    (SGLang fused_topk, AITER moe_sorting, per_token_group_quant_fp8).  All buffers are
- *    caller-owned device memory; the library allocates no device memory.
+ *    caller-owned device memory; the library allocates no device memory (the one exception is
+ *    netra_ep_window_create in the expert-parallel group below, which says so).
  */
 #pragma once
 
