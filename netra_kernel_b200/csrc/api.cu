@@ -13,6 +13,7 @@
 #include "bridge_kernels.cu"
 #include "route_kernels.cu"
 #include "umma_kernels.cu"
+#include "umma_tokmajor.cu"
 #include "ep_kernels.cu"
 
 using namespace netra;
@@ -71,6 +72,7 @@ int encode_u8_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row
 }
 
 bool g_umma_ready = false;
+bool g_tokmajor_ok = false;   // the token-major kernels were built with the register allocation they assume
 
 int umma_setup() {
   if (g_umma_ready) return 0;
@@ -79,8 +81,27 @@ int umma_setup() {
   if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(gate_up)", e);
   e = cudaFuncSetAttribute(netra_moe_down_umma_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, down_smem_bytes());
   if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(down)", e);
+  e = cudaFuncSetAttribute(netra_moe_gate_up_tokmajor_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, gate_up_tokmajor_smem_bytes());
+  if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(gate_up_tokmajor)", e);
+  e = cudaFuncSetAttribute(netra_moe_down_tokmajor_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, down_tokmajor_smem_bytes());
+  if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(down_tokmajor)", e);
+  {
+    // the register re-balancing inside these kernels is only deadlock-free for the launch allocation it was written for
+    cudaFuncAttributes a0, a1;
+    e = cudaFuncGetAttributes(&a0, netra_moe_gate_up_tokmajor_sm100);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a1, netra_moe_down_tokmajor_sm100);
+    if (e != cudaSuccess) return fail_cuda("cudaFuncGetAttributes(tokmajor)", e);
+    g_tokmajor_ok = a0.numRegs == kTmRegsLaunch && a1.numRegs == kTmRegsLaunch;
+  }
   g_umma_ready = true;
   return 0;
+}
+
+// The token-major GEMMs pay off once an expert's rows fill a good part of a 128-row tile: from an average
+// of 48 rows per routed expert (1,536 tokens on one GPU) the layer switches to them.
+constexpr uint32_t kTokMajorMinRowsPerExpert = 48;
+bool use_tokmajor(uint64_t pairs, uint32_t routed_experts) {
+  return g_tokmajor_ok && pairs >= (uint64_t)kTokMajorMinRowsPerExpert * routed_experts;
 }
 
 }  // namespace
@@ -91,6 +112,7 @@ struct netra_moe_layer {
   CUtensorMap tm_w13, tm_w2, tm_a32, tm_a64, tm_a128, tm_h32, tm_h64, tm_h128;
   int sm_count;
   uint32_t launches;
+  uint32_t gemm_mode;   // 0: pick the GEMM form by size, 1: always the swap-AB (decode) kernels
 };
 
 extern "C" {
@@ -197,6 +219,7 @@ int netra_moe_layer_create(const netra_moe_layer_desc_t* desc, netra_moe_layer_t
   layer->lay = lay;
   layer->sm_count = sms;
   layer->launches = 9;  // stages of launch_stage()
+  layer->gemm_mode = 0;
   const uint64_t slabs = desc->num_expert_slabs ? desc->num_expert_slabs : (uint64_t)(kRouted + 1);
   if (slabs > (uint64_t)(kRouted + 1)) { delete layer; return fail("layer_create: at most 257 expert slabs"); }
   uint8_t* ws = (uint8_t*)desc->workspace;
@@ -279,14 +302,24 @@ void launch_stage(netra_moe_layer* layer, uint32_t stage, const void* hidden, co
       break;
     case 5: netra_moe_gather_rows_sm100<<<(pairs + 7) / 8, 256, 0, stream>>>(a_fp8, a_scale, perm, tokens); break;
     case 6:
-      netra_moe_gate_up_umma_sm100<<<layer->sm_count, kGemmThreads, gate_up_smem_bytes(), stream>>>(
-          layer->tm_w13, layer->tm_a32, layer->tm_a64, layer->tm_a128, a_scale, layer->desc.w13_scale_f32, offsets, h_fp8,
-          h_scale, kRouted + 1, layer->desc.weights_tiled, status);
+      if (use_tokmajor(pairs, kRouted) && layer->gemm_mode != 1)
+        netra_moe_gate_up_tokmajor_sm100<<<layer->sm_count, kTmThreads, gate_up_tokmajor_smem_bytes(), stream>>>(
+            layer->tm_w13, layer->tm_a128, a_scale, layer->desc.w13_scale_f32, offsets, h_fp8, h_scale, kRouted + 1,
+            layer->desc.weights_tiled, status);
+      else
+        netra_moe_gate_up_umma_sm100<<<layer->sm_count, kGemmThreads, gate_up_smem_bytes(), stream>>>(
+            layer->tm_w13, layer->tm_a32, layer->tm_a64, layer->tm_a128, a_scale, layer->desc.w13_scale_f32, offsets, h_fp8,
+            h_scale, kRouted + 1, layer->desc.weights_tiled, status);
       break;
     case 7:
-      netra_moe_down_umma_sm100<<<layer->sm_count, kGemmThreads, down_smem_bytes(), stream>>>(
-          layer->tm_w2, layer->tm_h32, layer->tm_h64, layer->tm_h128, h_scale, layer->desc.w2_scale_f32, offsets, down,
-          kRouted + 1, layer->desc.weights_tiled, status + 1);
+      if (use_tokmajor(pairs, kRouted) && layer->gemm_mode != 1)
+        netra_moe_down_tokmajor_sm100<<<layer->sm_count, kTmThreads, down_tokmajor_smem_bytes(), stream>>>(
+            layer->tm_w2, layer->tm_h128, h_scale, layer->desc.w2_scale_f32, offsets, down, kRouted + 1,
+            layer->desc.weights_tiled, status + 1);
+      else
+        netra_moe_down_umma_sm100<<<layer->sm_count, kGemmThreads, down_smem_bytes(), stream>>>(
+            layer->tm_w2, layer->tm_h32, layer->tm_h64, layer->tm_h128, h_scale, layer->desc.w2_scale_f32, offsets, down,
+            kRouted + 1, layer->desc.weights_tiled, status + 1);
       break;
     default: netra_moe_combine_sm100<<<tokens, 256, 0, stream>>>((uint16_t*)out, down, w9, inv_perm, tokens); break;
   }
@@ -431,6 +464,12 @@ int netra_moe_kernel_launch_info(uint32_t which, uint32_t* block_threads, uint32
   if (!block_threads || !dynamic_smem_bytes || which > 1) return fail("kernel_launch_info: bad argument");
   *block_threads = kGemmThreads;
   *dynamic_smem_bytes = (uint32_t)(which == 0 ? gate_up_smem_bytes() : down_smem_bytes());
+  return 0;
+}
+
+int netra_moe_layer_set_gemm_mode(netra_moe_layer_t* layer, uint32_t mode) {
+  if (layer == nullptr || mode > 1) return fail("layer_set_gemm_mode: null layer or unknown mode");
+  layer->gemm_mode = mode;
   return 0;
 }
 

@@ -96,6 +96,10 @@ class RoutedMoELayer:
         return cls(ops.router_w.to(dev), ops.w13.to(dev), ops.w13_scale.to(dev), ops.w2.to(dev),
                    ops.w2_scale.to(dev), max_tokens or ops.tokens, bias)
 
+    def set_gemm_mode(self, mode: int) -> None:
+        """0: the layer picks the grouped-GEMM form by token count (token-major from 1,536 tokens); 1: always swap-AB."""
+        abi.check(self.lib.netra_moe_layer_set_gemm_mode(self.handle, mode), "layer_set_gemm_mode")
+
     def launches_per_call(self, tokens: int) -> int:
         return int(self.lib.netra_moe_layer_launch_count(self.handle, tokens))
 

@@ -124,6 +124,24 @@ def test_prefill_t8192_zipf_sampled_tokens(gpu_weights, expert_weights):
     assert np.array_equal(np.bincount(flat, minlength=256), inter["counts"].numpy())
 
 
+@pytest.mark.parametrize("tokens,alpha", [(2048, 0.0), (3000, 1.2)])
+def test_token_major_and_swap_ab_gemms_agree_bitwise(gpu_weights, tokens, alpha):
+    """From 1,536 tokens the layer runs the token-major GEMMs (128 token rows x 256 weight rows per MMA); the
+    swap-AB kernels computing the same rows must give the same intermediate codes, scales, FP32 rows and output."""
+    hidden, router_w, bias = synth.make_activations(tokens, alpha or None, seed=9)
+    layer = make_layer(gpu_weights, router_w, tokens, bias)
+    out_tm, inter_tm = run_layer(layer, hidden)
+    layer.set_gemm_mode(1)
+    out_sw, inter_sw = run_layer(layer, hidden)
+    rows = tokens * 9
+    for key in ("h_fp8", "h_scale", "down"):
+        assert torch.equal(inter_tm[key][:rows], inter_sw[key][:rows]), key
+    assert torch.equal(out_tm.view(torch.int16), out_sw.view(torch.int16))
+    if alpha:
+        counts = inter_tm["counts"].numpy()
+        assert counts.max() > 256 and counts.min() < 16      # several 128-row tiles for the hottest, ragged tails elsewhere
+
+
 def test_bridge_kernels_against_checker(gpu_weights, expert_weights):
     """The three-launch slot-order boundary of the reference's decode bridges."""
     from netra_kernel_b200 import moe
