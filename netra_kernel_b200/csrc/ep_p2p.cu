@@ -317,6 +317,17 @@ netra_ep_down_return_umma_sm100(const __grid_constant__ CUtensorMap tm_w2, const
   ep_signal_when_last(peers, lay, tab, &tab->done_ret, 2, world, rank);
 }
 
+// The same for the token-major form (blocks whose experts hold many rows).
+extern "C" __global__ void __launch_bounds__(kTmThreads, 1)
+netra_ep_down_return_tokmajor_sm100(const __grid_constant__ CUtensorMap tm_w2, const __grid_constant__ CUtensorMap tm_h128,
+                                    const float* h_scale, const float* w2_scale, const int32_t* offsets, float* const* row_ptr,
+                                    uint32_t num_groups, uint32_t w_tiled, uint32_t* status, EpPeers peers, EpWindowLayout lay,
+                                    EpTables* tab, uint32_t world, uint32_t rank) {
+  tokmajor_gemm_body<false>(&tm_w2, &tm_h128, h_scale, w2_scale, offsets, nullptr, nullptr, nullptr, row_ptr, num_groups, w_tiled,
+                            status);
+  ep_signal_when_last(peers, lay, tab, &tab->done_ret, 2, world, rank);
+}
+
 }  // namespace netra
 
 // ------------------------------------------------------------------ host side (C ABI, include/netra_moe.h)
@@ -337,6 +348,7 @@ struct netra_ep_layer {
   CUtensorMap tm_w13, tm_w2, tm_a32, tm_a64, tm_a128, tm_h32, tm_h64, tm_h128;
   int sm_count;
   uint32_t e_l;
+  bool tokmajor_ok;                // the fused-return token-major kernel was built with the register allocation it assumes
 };
 
 namespace {
@@ -414,14 +426,25 @@ void ep_launch_stage(netra_ep_layer* L, uint32_t stage, const void* hidden, cons
       break;
     }
     case 7:
-      netra_moe_gate_up_umma_sm100<<<L->sm_count, kGemmThreads, gate_up_smem_bytes(), stream>>>(
-          L->tm_w13, L->tm_a32, L->tm_a64, L->tm_a128, (const float*)(L->window + L->wl.blk_as), d.w13_scale_f32, L->tab->offsets,
-          L->blk_h, L->blk_hs, L->e_l + 1, d.weights_tiled, L->tab->status);
+      // the pairs of all ranks (equal token counts assumed) spread over 256 routed experts decide the GEMM form
+      if (L->tokmajor_ok && use_tokmajor((uint64_t)d.world * pairs, kRouted))
+        netra_moe_gate_up_tokmajor_sm100<<<L->sm_count, kTmThreads, gate_up_tokmajor_smem_bytes(), stream>>>(
+            L->tm_w13, L->tm_a128, (const float*)(L->window + L->wl.blk_as), d.w13_scale_f32, L->tab->offsets, L->blk_h, L->blk_hs,
+            L->e_l + 1, d.weights_tiled, L->tab->status);
+      else
+        netra_moe_gate_up_umma_sm100<<<L->sm_count, kGemmThreads, gate_up_smem_bytes(), stream>>>(
+            L->tm_w13, L->tm_a32, L->tm_a64, L->tm_a128, (const float*)(L->window + L->wl.blk_as), d.w13_scale_f32, L->tab->offsets,
+            L->blk_h, L->blk_hs, L->e_l + 1, d.weights_tiled, L->tab->status);
       break;
     case 8:
-      netra_ep_down_return_umma_sm100<<<L->sm_count, kGemmThreads, down_smem_bytes(), stream>>>(
-          L->tm_w2, L->tm_h32, L->tm_h64, L->tm_h128, L->blk_hs, d.w2_scale_f32, L->tab->offsets, L->row_ptr, L->e_l + 1,
-          d.weights_tiled, L->tab->status + 1, L->peers, L->wl, L->tab, d.world, d.rank);
+      if (L->tokmajor_ok && use_tokmajor((uint64_t)d.world * pairs, kRouted))
+        netra_ep_down_return_tokmajor_sm100<<<L->sm_count, kTmThreads, down_tokmajor_smem_bytes(), stream>>>(
+            L->tm_w2, L->tm_h128, L->blk_hs, d.w2_scale_f32, L->tab->offsets, L->row_ptr, L->e_l + 1, d.weights_tiled,
+            L->tab->status + 1, L->peers, L->wl, L->tab, d.world, d.rank);
+      else
+        netra_ep_down_return_umma_sm100<<<L->sm_count, kGemmThreads, down_smem_bytes(), stream>>>(
+            L->tm_w2, L->tm_h32, L->tm_h64, L->tm_h128, L->blk_hs, d.w2_scale_f32, L->tab->offsets, L->row_ptr, L->e_l + 1,
+            d.weights_tiled, L->tab->status + 1, L->peers, L->wl, L->tab, d.world, d.rank);
       break;
     case 9: netra_ep_wait_sm100<<<1, 32, 0, stream>>>(L->window, L->wl, L->tab, 2, d.world, d.wait_timeout_ns); break;
     default:
@@ -533,7 +556,12 @@ int netra_ep_layer_create(const netra_ep_layer_desc_t* desc, netra_ep_layer_t** 
   L->sm_count = L->route->sm_count;
   {
     cudaError_t e = cudaFuncSetAttribute(netra_ep_down_return_umma_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, down_smem_bytes());
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(netra_ep_down_return_tokmajor_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, down_tokmajor_smem_bytes());
+    cudaFuncAttributes attr;
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&attr, netra_ep_down_return_tokmajor_sm100);
     if (e != cudaSuccess) { netra_moe_layer_destroy(L->route); delete L; return fail_cuda("cudaFuncSetAttribute(down_return)", e); }
+    L->tokmajor_ok = g_tokmajor_ok && attr.numRegs == kTmRegsLaunch;
   }
   const uint64_t g = L->e_l + 1, rows = desc->row_capacity;
   if (desc->weights_tiled) {
