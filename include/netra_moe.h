@@ -257,7 +257,8 @@ uint32_t netra_ep_layer_launch_count(const netra_ep_layer_t* layer, uint32_t tok
 int netra_ep_layer_status(netra_ep_layer_t* layer, uint32_t status_out[4]);
 int netra_ep_layer_destroy(netra_ep_layer_t* layer);
 
-/* Block size and dynamic shared memory of the grouped GEMM kernels (which: 0 gate_up, 1 down), so
+/* Block size and dynamic shared memory of the grouped GEMM kernels (which: 0 gate_up, 1 down, 2 and 3 their
+ * token-major forms), so
  * that an engine manifest written ahead of time can be checked against the built library. */
 int netra_moe_kernel_launch_info(uint32_t which, uint32_t* block_threads, uint32_t* dynamic_smem_bytes);
 

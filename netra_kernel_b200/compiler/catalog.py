@@ -96,7 +96,8 @@ class FixedCudaTactic:
         launch = Launch(tuple(evaluate(v, env) for v in self.launch["grid"]),
                         tuple(evaluate(v, env) for v in self.launch["block"]),
                         evaluate(self.launch.get("lds_bytes", 0), env),
-                        evaluate(self.launch.get("dynamic_lds_bytes", 0), env))
+                        evaluate(self.launch.get("dynamic_lds_bytes", 0), env),
+                        int(self.launch.get("registers_per_thread", 0)))
         return FixedKernelContract(
             target=TARGET, wave_size=WARP_SIZE, operation=self.operation, family=self.family,
             constants=self.constants, specialization=tuple(sorted(request["dimensions"].items())),

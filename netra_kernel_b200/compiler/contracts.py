@@ -35,6 +35,7 @@ class Launch:
     block: tuple[int, int, int]
     lds_bytes: int = 0
     dynamic_lds_bytes: int = 0
+    registers_per_thread: int = 0      # nonzero: the loaded code object must report exactly this allocation
 
     def __post_init__(self) -> None:
         object.__setattr__(self, "grid", _triple(self.grid, "grid"))
@@ -44,12 +45,17 @@ class Launch:
             raise ValidationError("threads per block exceeds 1024")
         if min(self.lds_bytes, self.dynamic_lds_bytes) < 0:
             raise ValidationError("shared-memory bytes must be nonnegative")
+        if not 0 <= self.registers_per_thread <= 255:
+            raise ValidationError("registers per thread must be 0 (unchecked) or 1..255")
         if self.lds_bytes + self.dynamic_lds_bytes > MAX_BLOCK_SMEM:
             raise ValidationError("shared memory exceeds what one B200 block can use")
 
     def to_dict(self) -> dict[str, Any]:
-        return {"grid": list(self.grid), "block": list(self.block), "lds_bytes": self.lds_bytes,
-                "dynamic_lds_bytes": self.dynamic_lds_bytes}
+        doc = {"grid": list(self.grid), "block": list(self.block), "lds_bytes": self.lds_bytes,
+               "dynamic_lds_bytes": self.dynamic_lds_bytes}
+        if self.registers_per_thread:      # kernels that re-balance registers between warpgroups (setmaxnreg)
+            doc["registers_per_thread"] = self.registers_per_thread
+        return doc
 
 
 @dataclass(frozen=True)

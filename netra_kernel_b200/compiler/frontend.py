@@ -108,6 +108,11 @@ def routed_moe_layer_graph(model: dict[str, Any], profile: ShapeProfile) -> Grap
     routing_constants = {"hidden": hidden, "routed_experts": experts}
     gemm_constants = {"hidden": hidden, "intermediate": inter, "scale_block": c["scale_block"], "tile_rows": 128}
 
+    # grouped-GEMM form: token-major (128 token rows x 256 weight rows per MMA) from an average of 48 rows per routed expert
+    token_major = m * c["top_k"] >= 48 * experts
+    form = ("token_major" if token_major else "swap_ab") + ".sorted_rows." + ("tiles128" if opt["weight_layout"] == "tiles128" else "row_major")
+    maps = "tmap2" if token_major else "tmap4"
+
     def op(name, family, operation, inputs, outputs, constants, sem):
         return Operation(name, "fixed_kernel", family, operation, tuple(inputs), tuple(outputs),
                          {"constants": constants, "semantics": sem, "fallback": f"framework.{operation}"})
@@ -143,14 +148,12 @@ def routed_moe_layer_graph(model: dict[str, Any], profile: ShapeProfile) -> Grap
                      "sorted_rows_first.token_rows_after_pairs", "copy.v1")),
         op("gate_up", "moe_fp8_grouped_gemm", "gate_up_silu_requant", ["a_fp8", "a_scale", "w13", "w13_scale", "offsets"],
            ["h_fp8", "h_scale", "status"], gemm_constants,
-           semantics("gate_up_grouped.tmap4_ptr5_u32x2_ptr.v1", "fp8e4m3_fp8e4m3_to_fp8e4m3_f32", "fp8_e4m3_w128x128_a1x128_amax448",
-                     "swap_ab.sorted_rows." + ("tiles128" if opt["weight_layout"] == "tiles128" else "row_major"),
-                     "kblock_fma_ascending.silu_fp32.bf16_round_then_amax.v1")),
+           semantics(f"gate_up_grouped.{maps}_ptr5_u32x2_ptr.v1", "fp8e4m3_fp8e4m3_to_fp8e4m3_f32", "fp8_e4m3_w128x128_a1x128_amax448",
+                     form, "kblock_fma_ascending.silu_fp32.bf16_round_then_amax.v1")),
         op("down", "moe_fp8_grouped_gemm", "down_projection", ["h_fp8", "h_scale", "w2", "w2_scale", "offsets"],
            ["down_f32", "status"], gemm_constants,
-           semantics("down_grouped.tmap4_ptr4_u32x2_ptr.v1", "fp8e4m3_fp8e4m3_to_f32", "fp8_e4m3_w128x128_a1x128_amax448",
-                     "swap_ab.sorted_rows." + ("tiles128" if opt["weight_layout"] == "tiles128" else "row_major"),
-                     "kblock_fma_ascending.v1")),
+           semantics(f"down_grouped.{maps}_ptr4_u32x2_ptr.v1", "fp8e4m3_fp8e4m3_to_f32", "fp8_e4m3_w128x128_a1x128_amax448",
+                     form, "kblock_fma_ascending.v1")),
         op("combine", "moe_combine", "weighted_slot_combine", ["down_f32", "topk_weights", "inv_perm"], ["output"],
            {"hidden": hidden, "top_k": c["top_k"]},
            semantics("combine.ptr4_u32.v1", "f32_f32_to_bf16", "none", "sorted_rows_first.token_rows_after_pairs",

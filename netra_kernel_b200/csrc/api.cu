@@ -461,9 +461,10 @@ int netra_ep_unpack_rows_launch(float* down, const float* back_slots, const int3
 }
 
 int netra_moe_kernel_launch_info(uint32_t which, uint32_t* block_threads, uint32_t* dynamic_smem_bytes) {
-  if (!block_threads || !dynamic_smem_bytes || which > 1) return fail("kernel_launch_info: bad argument");
-  *block_threads = kGemmThreads;
-  *dynamic_smem_bytes = (uint32_t)(which == 0 ? gate_up_smem_bytes() : down_smem_bytes());
+  if (!block_threads || !dynamic_smem_bytes || which > 3) return fail("kernel_launch_info: bad argument");
+  *block_threads = which < 2 ? kGemmThreads : kTmThreads;
+  const int bytes[4] = {gate_up_smem_bytes(), down_smem_bytes(), gate_up_tokmajor_smem_bytes(), down_tokmajor_smem_bytes()};
+  *dynamic_smem_bytes = (uint32_t)bytes[which];
   return 0;
 }
 

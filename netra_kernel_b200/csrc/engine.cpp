@@ -218,6 +218,7 @@ struct ArgSpec {
 struct OpSpec {
   bool fallback = true;
   uint32_t grid[3] = {1, 1, 1}, block[3] = {1, 1, 1}, lds_bytes = 0, dynamic_lds_bytes = 0;
+  uint32_t registers_per_thread = 0;   // nonzero: the code object must report exactly this allocation
   std::string cubin, symbol;
   std::vector<ArgSpec> args;
 };
@@ -262,6 +263,8 @@ Manifest parse_manifest(const std::string& directory) {
       spec.lds_bytes = as_u32(launch->at("lds_bytes"), "lds_bytes");
       const Json* dyn = launch->find("dynamic_lds_bytes");
       spec.dynamic_lds_bytes = dyn ? as_u32(*dyn, "dynamic_lds_bytes") : 0;
+      const Json* regs = launch->find("registers_per_thread");
+      spec.registers_per_thread = regs ? as_u32(*regs, "registers_per_thread") : 0;
     } else if (!spec.fallback) {
       throw std::runtime_error("selected kernel requires a launch record");
     }
@@ -337,6 +340,7 @@ struct Driver {
   CUresult (*ModuleUnload)(CUmodule) = nullptr;
   CUresult (*ModuleGetFunction)(CUfunction*, CUmodule, const char*) = nullptr;
   CUresult (*FuncSetAttribute)(CUfunction, CUfunction_attribute, int) = nullptr;
+  CUresult (*FuncGetAttribute)(int*, CUfunction_attribute, CUfunction) = nullptr;
   CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
                            void**, void**) = nullptr;
   CUresult (*TensorMapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -354,6 +358,7 @@ const Driver& driver() {
     };
     r.ok = get("cuModuleLoadData", (void**)&r.ModuleLoadData) && get("cuModuleUnload", (void**)&r.ModuleUnload) &&
            get("cuModuleGetFunction", (void**)&r.ModuleGetFunction) && get("cuFuncSetAttribute", (void**)&r.FuncSetAttribute) &&
+           get("cuFuncGetAttribute", (void**)&r.FuncGetAttribute) &&
            get("cuLaunchKernel", (void**)&r.LaunchKernel) && get("cuTensorMapEncodeTiled", (void**)&r.TensorMapEncodeTiled);
     return r;
   }();
@@ -533,6 +538,15 @@ extern "C" netra_status_t netra_engine_create(const char* directory, const netra
         if (ospec.dynamic_lds_bytes > 48 * 1024) {
           r = driver().FuncSetAttribute(op.function, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)ospec.dynamic_lds_bytes);
           if (r != CUDA_SUCCESS) throw std::runtime_error("cuFuncSetAttribute(max dynamic shared memory): CUresult " + std::to_string((int)r));
+        }
+        if (ospec.registers_per_thread) {
+          // kernels that move registers between warpgroups (setmaxnreg) only work for the allocation they were written for
+          int regs = 0;
+          r = driver().FuncGetAttribute(&regs, CU_FUNC_ATTRIBUTE_NUM_REGS, op.function);
+          if (r != CUDA_SUCCESS) throw std::runtime_error("cuFuncGetAttribute(registers): CUresult " + std::to_string((int)r));
+          if ((uint32_t)regs != ospec.registers_per_thread)
+            throw std::runtime_error(ospec.symbol + " was built with " + std::to_string(regs) + " registers per thread, the contract requires " +
+                                     std::to_string(ospec.registers_per_thread));
         }
         op.argc = (uint32_t)ospec.args.size();
         op.slots.reset(new ArgSlot[op.argc]);

@@ -3,3 +3,4 @@
 #include "bridge_kernels.cu"
 #include "route_kernels.cu"
 #include "umma_kernels.cu"
+#include "umma_tokmajor.cu"

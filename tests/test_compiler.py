@@ -127,7 +127,7 @@ def test_catalog_is_locked_to_the_kernel_sources_and_model_independent(tmp_path)
     root = tmp_path / "lib"
     shutil.copytree(LIB_ROOT / "manifests", root / "manifests")
     (root / "csrc").mkdir()
-    for rel in ("common.cuh", "route_kernels.cu", "bridge_kernels.cu", "umma_kernels.cu", "kernels_cubin.cu"):
+    for rel in ("common.cuh", "route_kernels.cu", "bridge_kernels.cu", "umma_kernels.cu", "umma_tokmajor.cu", "kernels_cubin.cu"):
         shutil.copyfile(LIB_ROOT / "csrc" / rel, root / "csrc" / rel)
     catalog.load_fixed_tactic_catalog(root, TARGET)
     with open(root / "csrc" / "umma_kernels.cu", "a") as f:
@@ -139,7 +139,8 @@ def test_catalog_is_locked_to_the_kernel_sources_and_model_independent(tmp_path)
 def test_catalog_launch_constants_match_the_built_library():
     lib = abi.load()
     tactics = {t.name: t for t in catalog.load_fixed_tactic_catalog(LIB_ROOT, TARGET)}
-    for which, name in ((0, "gate_up_silu_requant_umma_swapab_tiles128"), (1, "down_projection_umma_swapab_tiles128")):
+    for which, name in ((0, "gate_up_silu_requant_umma_swapab_tiles128"), (1, "down_projection_umma_swapab_tiles128"),
+                        (2, "gate_up_silu_requant_umma_tokmajor_tiles128"), (3, "down_projection_umma_tokmajor_row_major")):
         block, smem = ctypes.c_uint32(), ctypes.c_uint32()
         assert lib.netra_moe_kernel_launch_info(which, ctypes.byref(block), ctypes.byref(smem)) == 0
         assert tactics[name].launch["block"][0] == block.value
@@ -167,10 +168,17 @@ def test_planner_selects_by_layout_size_and_never_a_rejected_tactic():
     big = _plan(MODEL_ZIPF, "prefill_t8192")
     names = [p.operation.name for p in big.operations]
     assert names[2:5] == ["sort_hist", "sort_scan", "sort_scatter"]
-    assert {p.operation.name: p.tactic.name for p in big.operations}["down"].endswith("row_major")
+    # 8,192 tokens: the token-major GEMM form (row-major weights in this model), with its register contract
+    down = next(p for p in big.operations if p.operation.name == "down")
+    assert down.tactic.name == "down_projection_umma_tokmajor_row_major"
+    assert down.contract.launch.registers_per_thread == 168 and down.contract.launch.block == (384, 1, 1)
     gate = next(p for p in big.operations if p.operation.name == "gate_up")
+    assert gate.tactic.name == "gate_up_silu_requant_umma_tokmajor_row_major"
     other = [c for c in gate.explanation if c["tactic"] == "gate_up_silu_requant_umma_swapab_tiles128"][0]
     assert any("semantic layouts mismatch" in r for r in other["reasons"])
+    # below 1,536 tokens the token-major tactics are out of their size limits and the swap-AB form is requested
+    small_gate = next(p for p in plan.operations if p.operation.name == "gate_up")
+    assert small_gate.tactic.name == "gate_up_silu_requant_umma_swapab_tiles128" and "registers_per_thread" not in small_gate.contract.launch.to_dict()
 
 
 def test_planner_falls_back_and_refuses_ambiguity():
