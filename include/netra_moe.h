@@ -124,6 +124,17 @@ typedef struct netra_moe_layer_desc {
 int netra_moe_repack_tiles_launch(void* dst, const void* src, uint64_t total_rows, uint32_t k_bytes,
                                   cudaStream_t stream);
 
+/* MXFP4 expert weights (E2M1 codes, one E8M0 scale per 32 K-elements; encoding of the reference's
+ * tools/checkpoint/quantize_qwen36_lm_head_mxfp4.py:58-67 and tests/gfx1151/test_netra_mxfp4_sgl_decode.py:23-31):
+ * load-time expansion into the layer's operand format - E4M3 codes [total_rows, k] and one power-of-two FP32
+ * scale per 128 x 128 tile [total_rows/128, k/128] - after which the MXFP4 checkpoint runs on the FP8 tensor-core
+ * kernels with exactly the MXFP4 products.  packed is [total_rows, k/2] (low nibble = even k, K contiguous per
+ * row), scales_e8m0 is [total_rows, k/32].  The expansion is exact while the scales inside a tile span at most
+ * 15 binades; elements below that are rounded to nearest and counted in *inexact (device word, caller-zeroed).
+ * The 4-bit codes are not streamed by the GEMMs: the weight traffic is that of FP8. */
+int netra_moe_mxfp4_expand_launch(void* dst_fp8, float* dst_scale_f32, uint32_t* inexact_u32, const void* packed_e2m1,
+                                  const void* scales_e8m0, uint64_t total_rows, uint32_t k, cudaStream_t stream);
+
 /* Control plane (serialised by the caller): encodes the tensor maps of the persistent buffers
  * and clears the status words.  No device memory is allocated. */
 int netra_moe_layer_create(const netra_moe_layer_desc_t* desc, netra_moe_layer_t** output);

@@ -15,6 +15,7 @@
 #include "umma_kernels.cu"
 #include "umma_tokmajor.cu"
 #include "ep_kernels.cu"
+#include "mxfp4_kernels.cu"
 
 using namespace netra;
 
@@ -353,6 +354,17 @@ int netra_moe_repack_tiles_launch(void* dst, const void* src, uint64_t total_row
   netra_moe_repack_tiles_sm100<<<(unsigned)((chunks + 255) / 256), 256, 0, stream>>>((uint4*)dst, (const uint4*)src,
                                                                                      (uint32_t)total_rows, k_bytes);
   return check_launch("repack_tiles launch");
+}
+
+int netra_moe_mxfp4_expand_launch(void* dst_fp8, float* dst_scale, uint32_t* inexact, const void* packed, const void* scales_e8m0,
+                                  uint64_t total_rows, uint32_t k, cudaStream_t stream) {
+  if (!dst_fp8 || !dst_scale || !inexact || !packed || !scales_e8m0) return fail("mxfp4_expand: null pointer");
+  if (total_rows == 0 || total_rows % 128 != 0 || k == 0 || k % 128 != 0 || total_rows / 128 > 65535u * 128u)
+    return fail("mxfp4_expand: rows and k must be positive multiples of 128");
+  if (total_rows / 128 > 65535) return fail("mxfp4_expand: at most 65,535 row tiles per call");
+  netra_moe_mxfp4_expand_sm100<<<dim3(k / 128, (unsigned)(total_rows / 128)), 128, 0, stream>>>(
+      (uint8_t*)dst_fp8, dst_scale, inexact, (const uint8_t*)packed, (const uint8_t*)scales_e8m0, k);
+  return check_launch("mxfp4_expand launch");
 }
 
 // ------------------------------------------------------------------ expert block (expert parallelism)

@@ -172,6 +172,24 @@ class RoutedMoELayer:
             pass
 
 
+def expand_mxfp4(packed: torch.Tensor, scales: torch.Tensor):
+    """MXFP4 slabs (packed E2M1 ``[G, N, K/2]`` u8, E8M0 scales ``[G, N, K/32]`` u8, on the GPU) -> the layer's
+    FP8 operands: (E4M3 codes ``[G, N, K]`` as float8, tile scales ``[G, N/128, K/128]`` FP32, count of elements
+    that could not be held exactly).  ``netra_moe_mxfp4_expand_launch``."""
+    _require_cuda(packed, scales)
+    g, n, half_k = packed.shape
+    k = half_k * 2
+    if packed.dtype != torch.uint8 or scales.dtype != torch.uint8 or scales.shape != (g, n, k // 32):
+        raise ValueError("packed must be u8 [G, N, K/2] and scales u8 [G, N, K/32]")
+    codes = torch.empty(g, n, k, dtype=torch.uint8, device=packed.device)
+    tile_scale = torch.empty(g, n // 128, k // 128, dtype=torch.float32, device=packed.device)
+    inexact = torch.zeros(1, dtype=torch.int32, device=packed.device)
+    abi.check(abi.load().netra_moe_mxfp4_expand_launch(codes.data_ptr(), tile_scale.data_ptr(), inexact.data_ptr(),
+                                                      packed.contiguous().data_ptr(), scales.contiguous().data_ptr(), g * n, k, _stream()),
+              "mxfp4_expand_launch")
+    return codes.view(torch.float8_e4m3fn), tile_scale, int(inexact.item())
+
+
 # ----------------------------------------------------------------------------- per-kernel bridges
 def bridge_router_bf16(hidden: torch.Tensor, router_w: torch.Tensor) -> torch.Tensor:
     _require_cuda(hidden, router_w)

@@ -283,6 +283,24 @@ def mxfp4_quantize(w: np.ndarray):
     return (code[:, 0::2] | (code[:, 1::2] << 4)).astype(np.uint8), scale_byte
 
 
+def mxfp4_expand(packed: np.ndarray, scales: np.ndarray):
+    """MXFP4 rows -> the FP8 operand format of the grouped GEMMs: E4M3 codes [rows, K] and one
+    power-of-two FP32 scale per 128 x 128 tile [rows/128, K/128], plus the number of nonzero elements
+    that E4M3 cannot hold exactly (scales inside a tile more than 15 binades apart).
+    Per tile s_ref = max(scale byte) - 6, tile scale 2^(s_ref - 127), element = lut * 2^(s - s_ref)."""
+    rows, k = packed.shape[0], packed.shape[1] * 2
+    s = scales.astype(np.int32).reshape(rows // 128, 128, k // 128, 4)
+    s_ref = s.max(axis=(1, 3)) - 6                                        # [rows/128, K/128]
+    j = s - s_ref[:, None, :, None]                                       # <= 6
+    low, high = packed & 15, packed >> 4
+    code = np.stack([low, high], axis=-1).reshape(rows, k)
+    mag = E2M1_LUT[code & 7] * np.where(code & 8, -1.0, 1.0)
+    jj = np.repeat(j.reshape(rows, k // 32), 32, axis=1)
+    vals = (mag * np.exp2(np.maximum(jj, -30).astype(np.float64))).astype(np.float32)
+    inexact = int(np.count_nonzero(((code & 7) != 0) & (jj < -8)))
+    return e4m3_encode(vals), np.exp2((s_ref - 127).astype(np.float64)).astype(np.float32), inexact
+
+
 def parity_metrics(got_bits: np.ndarray, ref_bits: np.ndarray) -> dict:
     """Metric definitions of ``tests/gfx1151/test_netra_mxfp4_sgl_decode.py:137-152``."""
     g = bf16_bits_to_f32(got_bits).astype(np.float64)

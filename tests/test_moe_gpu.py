@@ -142,6 +142,42 @@ def test_token_major_and_swap_ab_gemms_agree_bitwise(gpu_weights, tokens, alpha)
         assert counts.max() > 256 and counts.min() < 16      # several 128-row tiles for the hottest, ragged tails elsewhere
 
 
+def test_mxfp4_expansion_kernel_and_layer(expert_weights):
+    """MXFP4 expert weights (the reference's quantiser) expanded on the GPU into FP8 tiles: the kernel must equal
+    the CPU restatement bit for bit, the expansion must be exact, and the layer on the expanded weights must
+    match the checker run on the same operands."""
+    from netra_kernel_b200.moe import RoutedMoELayer, expand_mxfp4
+    g = torch.Generator().manual_seed(21)
+    slabs, tokens = 257, 64
+    # a handful of distinct FP32 slabs reused cyclically keeps the host-side quantisation cheap
+    base13 = [0.02 * torch.randn(1024, 2048, generator=g) for _ in range(3)]
+    base2 = [0.02 * torch.randn(2048, 512, generator=g) for _ in range(3)]
+    q13 = [synth.quantize_mxfp4(w) for w in base13]
+    q2 = [synth.quantize_mxfp4(w) for w in base2]
+    p13 = torch.stack([q13[e % 3][0] for e in range(slabs)]).cuda()
+    s13 = torch.stack([q13[e % 3][1] for e in range(slabs)]).cuda()
+    p2 = torch.stack([q2[e % 3][0] for e in range(slabs)]).cuda()
+    s2 = torch.stack([q2[e % 3][1] for e in range(slabs)]).cuda()
+    w13, w13_s, bad13 = expand_mxfp4(p13, s13)
+    w2, w2_s, bad2 = expand_mxfp4(p2, s2)
+    torch.cuda.synchronize()
+    assert bad13 == 0 and bad2 == 0
+    for e in range(3):                                  # kernel == CPU restatement, and exact against the reference dequantiser
+        codes, tile_scale, _ = R.mxfp4_expand(q13[e][0].numpy(), q13[e][1].numpy())
+        assert np.array_equal(w13[e].view(torch.uint8).cpu().numpy(), codes)
+        assert np.array_equal(w13_s[e].cpu().numpy(), tile_scale)
+        deq = R.e4m3_decode(codes).astype(np.float64) * np.repeat(np.repeat(tile_scale.astype(np.float64), 128, 0), 128, 1)
+        assert np.array_equal(deq, R.mxfp4_dequant(q13[e][0].numpy(), q13[e][1].numpy()))
+    codes2, tile2, _ = R.mxfp4_expand(q2[1][0].numpy(), q2[1][1].numpy())
+    assert np.array_equal(w2[1].view(torch.uint8).cpu().numpy(), codes2) and np.array_equal(w2_s[1].cpu().numpy(), tile2)
+    hidden, router_w, _ = synth.make_activations(tokens, seed=6)
+    layer = RoutedMoELayer(router_w.cuda(), w13, w13_s, w2, w2_s, tokens)
+    out, inter = run_layer(layer, hidden)
+    ref = R.moe_layer(helpers.bits(hidden), helpers.bits(router_w), w13.view(torch.uint8).cpu().numpy(), w13_s.cpu().numpy(),
+                      w2.view(torch.uint8).cpu().numpy(), w2_s.cpu().numpy())
+    check_against(ref, out, inter, tokens)
+
+
 def test_bridge_kernels_against_checker(gpu_weights, expert_weights):
     """The three-launch slot-order boundary of the reference's decode bridges."""
     from netra_kernel_b200 import moe

@@ -74,6 +74,24 @@ def test_mxfp4_quantiser_round_trip_and_generator_agreement():
     assert np.array_equal(R.mxfp4_dequant(p, s), (exact * 0.25).astype(np.float64))
 
 
+def test_mxfp4_expansion_to_fp8_tiles_is_exact_within_fifteen_binades():
+    """The load-time expansion (E4M3 codes x one power-of-two scale per 128 x 128 tile) must reproduce the
+    reference dequantiser exactly, and must count what it cannot hold."""
+    g = torch.Generator().manual_seed(12)
+    w = 0.02 * torch.randn(256, 512, generator=g)
+    w[:, 130:160] *= 2.0 ** -9                       # one scale group far below its neighbours, still inside 15 binades
+    packed, scales = R.mxfp4_quantize(w.numpy())
+    codes, tile_scale, inexact = R.mxfp4_expand(packed, scales)
+    assert inexact == 0 and codes.shape == (256, 512) and tile_scale.shape == (2, 4)
+    got = R.e4m3_decode(codes).astype(np.float64) * np.repeat(np.repeat(tile_scale.astype(np.float64), 128, axis=0), 128, axis=1)
+    assert np.array_equal(got, R.mxfp4_dequant(packed, scales))
+    assert np.all(np.log2(tile_scale) == np.round(np.log2(tile_scale)))      # powers of two
+    scales2 = scales.copy()
+    scales2[5, 1] = scales2[5, 0] - 20               # 20 binades below its tile: rounded away and counted
+    _, _, inexact2 = R.mxfp4_expand(packed, scales2)
+    assert inexact2 == np.count_nonzero(np.stack([packed[5, 16:32] & 7, (packed[5, 16:32] >> 4) & 7]))
+
+
 def test_topk_tie_break_and_renormalisation():
     logits = np.zeros((2, 256), np.float32)
     logits[0, [5, 9, 200]] = 2.0             # three-way tie for the top: ids ascending
