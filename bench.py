@@ -371,7 +371,7 @@ def run_ours(args) -> None:
         "gpu_launches": steps * layer.launches_per_call(tokens),
         "e2e": {"value": world * tokens / (e2e_ms / 1e3), "unit": UNIT, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": tokens * 2048 * 2, "d2h_bytes_per_step": tokens * 2048 * 2},
-        "roofline": ({"bound": "tensor", "kernel": "netra_moe_gate_up_umma_sm100", "achieved": gate_up_flops / gu_s / 1e12,
+        "roofline": ({"bound": "tensor", "kernel": "netra_moe_gate_up_tokmajor_sm100" if tokens >= 1536 else "netra_moe_gate_up_umma_sm100", "achieved": gate_up_flops / gu_s / 1e12,
                       "peak": fp8_peak, "unit": "TFLOP/s", "frac": gate_up_flops / gu_s / 1e12 / fp8_peak, "peak_source": fp8_kind,
                       "algorithmic_flops": gate_up_flops, "avg_launch_ms": stage_ms[6], "traffic": None}
                      if prefill else
@@ -559,7 +559,8 @@ def run_expert_parallel(args) -> None:
             "stage_us_rank0": stage_us,
             "e2e": {"value": world * tokens / (e2e_ms / 1e3), "unit": UNIT, "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": tokens * 2048 * 2, "d2h_bytes_per_step": tokens * 2048 * 2},
-            "roofline": {"bound": "hbm", "kernel": "netra_moe_gate_up_umma_sm100 + netra_moe_down_umma_sm100 (expert block, timed alone)",
+            "roofline": {"bound": "hbm", "kernel": ("netra_moe_gate_up_tokmajor_sm100 + netra_ep_down_return_tokmajor_sm100" if world * tokens >= 1536
+                                                    else "netra_moe_gate_up_umma_sm100 + netra_ep_down_return_umma_sm100") + " (expert block, timed alone)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
                          "algorithmic_bytes": block_bytes, "avg_launch_ms": block_ms, "traffic": None},
             "clocks": clocks.summary(),

@@ -257,6 +257,7 @@ uint32_t netra_moe_layer_launch_count(const netra_moe_layer_t* layer, uint32_t t
 
 namespace {
 constexpr uint32_t kStageCount = 9;
+constexpr uint32_t kRouterK8MaxRows = 1024;   // up to here the router runs with eight K-slices per tile
 
 // One launch of the layer's fixed sequence (same idea as the reference's per-operation launch,
 // runtime/gfx950/engine/netra_engine.h:90-92).
@@ -282,8 +283,12 @@ void launch_stage(netra_moe_layer* layer, uint32_t stage, const void* hidden, co
   const uint32_t nseg = (pairs + kSortSegment - 1) / kSortSegment;
   switch (stage) {
     case 0:
-      netra_router_logits_bf16_sm100<<<dim3((tokens + 15) / 16, 8), 256, 0, stream>>>(
-          logits, (const uint16_t*)hidden, (const uint16_t*)layer->desc.router_weight_bf16, tokens);
+      if (tokens <= kRouterK8MaxRows)
+        netra_router_logits_bf16_k8_sm100<<<dim3((tokens + 15) / 16, 8), 512, 0, stream>>>(
+            logits, (const uint16_t*)hidden, (const uint16_t*)layer->desc.router_weight_bf16, tokens);
+      else
+        netra_router_logits_bf16_sm100<<<dim3((tokens + 15) / 16, 8), 256, 0, stream>>>(
+            logits, (const uint16_t*)hidden, (const uint16_t*)layer->desc.router_weight_bf16, tokens);
       break;
     case 1:
       netra_moe_topk_quant_sm100<<<(tokens + 3) / 4, 128, 0, stream>>>(

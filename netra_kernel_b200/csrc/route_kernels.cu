@@ -20,7 +20,7 @@ namespace netra {
 // FP64->BF16 rounding gives the correctly rounded dot product whatever the summation order.
 // The sums run on the FP64 tensor cores (mma.sync m8n8k4): a warp owns 16 tokens x 16 experts
 // over one quarter of K; the four K-quarters are added in fixed order through shared memory.
-// grid (ceil(rows/16), 8), block 256 = 2 expert halves x 4 K-quarters.
+// grid (ceil(rows/16), 8); see the two entry points below.
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint16_t f64_to_bf16_bits(double d) {
   long long bits = __double_as_longlong(d);
@@ -45,12 +45,13 @@ __device__ __forceinline__ void dmma_m8n8k4(double& c0, double& c1, double a, do
                : "+d"(c0), "+d"(c1) : "d"(a), "d"(b));
 }
 
-extern "C" __global__ void __launch_bounds__(256)
-netra_router_logits_bf16_sm100(uint16_t* __restrict__ logits, const uint16_t* __restrict__ hidden,
-                               const uint16_t* __restrict__ weight, uint32_t rows) {
-  __shared__ double part[4][2][16][16];
+// kKSplit warps share one 16 x 16 output tile, each over 1 / kKSplit of K; block = 2 expert halves x kKSplit warps.
+template <int kKSplit>
+__device__ __forceinline__ void router_logits_body(uint16_t* __restrict__ logits, const uint16_t* __restrict__ hidden,
+                                                   const uint16_t* __restrict__ weight, uint32_t rows) {
+  __shared__ double part[kKSplit][2][16][16];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kq = warp & 3, eh = warp >> 2;           // K-quarter, expert half
+  const int kq = warp % kKSplit, eh = warp / kKSplit;   // K-slice, expert half
   const int tok0 = blockIdx.x * 16;
   const int exp0 = blockIdx.y * 32 + eh * 16;
   const int frow = lane >> 2, fk = lane & 3;         // fragment row (token or expert), K position
@@ -60,10 +61,10 @@ netra_router_logits_bf16_sm100(uint16_t* __restrict__ logits, const uint16_t* __
   // Any permutation of K is valid as long as both operands use it: in MMA step j of a 32-wide
   // chunk, fragment position fk holds element k = chunk + 8*fk + j, so a lane needs 8 consecutive
   // BF16 (one 16-byte load) per row and chunk.
-  const int kbase = kq * (kHidden / 4);
+  const int kbase = kq * (kHidden / kKSplit);
   const uint4 zero = make_uint4(0, 0, 0, 0);
 #pragma unroll 2
-  for (int kc = 0; kc < kHidden / 4; kc += 32) {
+  for (int kc = 0; kc < kHidden / kKSplit; kc += 32) {
     const int k = kbase + kc + 8 * fk;
     uint4 hv[2], wv[2];
 #pragma unroll
@@ -95,19 +96,37 @@ netra_router_logits_bf16_sm100(uint16_t* __restrict__ logits, const uint16_t* __
       part[kq][eh][m * 8 + frow][n * 8 + fk * 2 + 1] = acc[m][n][1];
     }
   __syncthreads();
-  // 16 tokens x 32 experts: a thread finishes two adjacent experts of one token
-  const int t = threadIdx.x >> 4, e2 = (threadIdx.x & 15) * 2;
-  if (tok0 + t < (int)rows) {
-    uint32_t packed = 0;
+  // 16 tokens x 32 experts: a thread finishes two adjacent experts of one token, adding the K-slices in order
+  if (threadIdx.x < 256) {
+    const int t = threadIdx.x >> 4, e2 = (threadIdx.x & 15) * 2;
+    if (tok0 + t < (int)rows) {
+      uint32_t packed = 0;
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int e = e2 + i;
-      const double v = ((part[0][e >> 4][t][e & 15] + part[1][e >> 4][t][e & 15]) + part[2][e >> 4][t][e & 15]) +
-                       part[3][e >> 4][t][e & 15];
-      packed |= (uint32_t)f64_to_bf16_bits(v) << (16 * i);
+      for (int i = 0; i < 2; ++i) {
+        const int e = e2 + i;
+        double v = part[0][e >> 4][t][e & 15];
+#pragma unroll
+        for (int q = 1; q < kKSplit; ++q) v += part[q][e >> 4][t][e & 15];
+        packed |= (uint32_t)f64_to_bf16_bits(v) << (16 * i);
+      }
+      *reinterpret_cast<uint32_t*>(logits + (size_t)(tok0 + t) * kRouted + blockIdx.y * 32 + e2) = packed;
     }
-    *reinterpret_cast<uint32_t*>(logits + (size_t)(tok0 + t) * kRouted + blockIdx.y * 32 + e2) = packed;
   }
+}
+
+// grid (ceil(rows/16), 8), block 256: four K-quarters per output tile.
+extern "C" __global__ void __launch_bounds__(256)
+netra_router_logits_bf16_sm100(uint16_t* __restrict__ logits, const uint16_t* __restrict__ hidden,
+                               const uint16_t* __restrict__ weight, uint32_t rows) {
+  router_logits_body<4>(logits, hidden, weight, rows);
+}
+
+// The same with eight K-slices (block 512): twice the warps per SM for calls too small to fill the GPU
+// with blocks (up to about 1,024 rows), where the FP64 pipe would otherwise wait on its own latency.
+extern "C" __global__ void __launch_bounds__(512)
+netra_router_logits_bf16_k8_sm100(uint16_t* __restrict__ logits, const uint16_t* __restrict__ hidden,
+                                  const uint16_t* __restrict__ weight, uint32_t rows) {
+  router_logits_body<8>(logits, hidden, weight, rows);
 }
 
 // ------------------------------------------------------------------------------------------
