@@ -198,7 +198,7 @@ def make_engine_session(args, tokens, device_id, layer, hidden, out):
     from netra_kernel_b200.compiler import compile_engine
     from netra_kernel_b200.compiler.library import KernelLibrary
     from netra_kernel_b200.compiler.profiles import load_profile_registry
-    if args.zipf_alpha or args.row_major_weights:
+    if args.zipf_alpha or args.row_major_weights or args.weights != "fp8":
         return None
     root = KernelLibrary.discover().root
     profile = next((p for p in load_profile_registry(root, "sm_100a", 1)
@@ -230,9 +230,20 @@ def run_ours(args) -> None:
         dist.init_process_group("nccl", device_id=dev)
     tokens, steps, warmup = args.tokens, args.steps, max(args.warmup, 3)
 
-    weights = synth.make_expert_weights(0)
     hidden_cpu, router_w, bias = synth.make_activations(tokens, args.zipf_alpha or None, seed=rank)
-    w13, w13_s, w2, w2_s = (t.to(dev) for t in weights)
+    mxfp4_inexact = None
+    if args.weights == "mxfp4":
+        # the same FP32 slabs quantised to MXFP4 (E2M1 + E8M0 per 32), expanded on the GPU into exact E4M3 tiles
+        from netra_kernel_b200.moe import expand_mxfp4
+        p13, s13, p2, s2 = synth.make_expert_weights_mxfp4(0)
+        w13, w13_s, bad13 = expand_mxfp4(p13.to(dev), s13.to(dev))
+        w2, w2_s, bad2 = expand_mxfp4(p2.to(dev), s2.to(dev))
+        mxfp4_inexact = bad13 + bad2
+        del p13, s13, p2, s2
+        weights = tuple(t.cpu() for t in (w13, w13_s, w2, w2_s))      # the CPU baseline runs on the same expanded operands
+    else:
+        weights = synth.make_expert_weights(0)
+        w13, w13_s, w2, w2_s = (t.to(dev) for t in weights)
     layer = RoutedMoELayer(router_w.to(dev), w13, w13_s, w2, w2_s, tokens, None if bias is None else bias.to(dev),
                            tiled=not args.row_major_weights)
     del w13, w2
@@ -365,6 +376,8 @@ def run_ours(args) -> None:
                    "parallelism": "single GPU" if world == 1 else f"{world} independent replicas (no collective)",
                    "zipf_alpha": args.zipf_alpha or 0.0,
                    "l2": "inputs larger than L2: every step streams %.1f MB of expert weights (L2 is 126 MB)" % (layer_bytes / 1e6),
+                   "expert_weights": ("mxfp4 (E2M1 + E8M0/32) expanded at load to exact E4M3 tiles, %d inexact elements; weight traffic is that of FP8"
+                                      % mxfp4_inexact) if mxfp4_inexact is not None else "fp8 e4m3, 128x128 block scales",
                    "weights": "row-major slabs" if args.row_major_weights else "tile order (repacked once at load)",
                    "launch": "CUDA graph replay of the layer's %d kernels" % layer.launches_per_call(tokens),
                    "api": api_name},
@@ -579,6 +592,8 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=256)
     ap.add_argument("--zipf-alpha", type=float, default=0.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--weights", default="fp8", choices=["fp8", "mxfp4"],
+                    help="expert weights: the FP8 block-scaled slabs (default) or the same slabs quantised to MXFP4 and expanded at load")
     ap.add_argument("--row-major-weights", action="store_true",
                     help="stream the checkpoint's row-major slabs instead of the repacked tile order")
     ap.add_argument("--replicas", action="store_true",

@@ -163,6 +163,23 @@ def make_expert_weights(layer: int = 0, n_slabs: int = N_SLABS, keep_fp32: bool 
     return (w13, w13_s, w2, w2_s, fp32) if keep_fp32 else (w13, w13_s, w2, w2_s)
 
 
+def make_expert_weights_mxfp4(layer: int = 0, n_slabs: int = N_SLABS):
+    """The same FP32 slabs as ``make_expert_weights`` (same seeds, same draw order), quantised to MXFP4 instead:
+    (W13 packed ``[n, 1024, 1024]`` u8, W13 E8M0 scales ``[n, 1024, 64]`` u8, W2 packed ``[n, 2048, 256]``,
+    W2 scales ``[n, 2048, 16]``)."""
+    g = torch.Generator().manual_seed(1000 + layer)
+    p13 = torch.empty(n_slabs, 2 * INTER, HIDDEN // 2, dtype=torch.uint8)
+    s13 = torch.empty(n_slabs, 2 * INTER, HIDDEN // 32, dtype=torch.uint8)
+    p2 = torch.empty(n_slabs, HIDDEN, INTER // 2, dtype=torch.uint8)
+    s2 = torch.empty(n_slabs, HIDDEN, INTER // 32, dtype=torch.uint8)
+    for e in range(n_slabs):
+        a = 0.02 * torch.randn(2 * INTER, HIDDEN, generator=g)
+        b = 0.02 * torch.randn(HIDDEN, INTER, generator=g)
+        p13[e], s13[e] = quantize_mxfp4(a)
+        p2[e], s2[e] = quantize_mxfp4(b)
+    return p13, s13, p2, s2
+
+
 def make_operands(tokens: int, layer: int = 0, zipf_alpha: Optional[float] = None,
                   n_slabs: int = N_SLABS) -> MoEOperands:
     """One layer's operands.  ``n_slabs < 257`` is for small CPU tests only: routing
