@@ -146,6 +146,16 @@ int netra_moe_layer_launch(netra_moe_layer_t* layer, const void* hidden_bf16,
                            const float* shared_weight_f32, void* output_bf16, uint32_t tokens,
                            cudaStream_t stream);
 
+/* The same layer call with a top-k computed by the caller (a serving stack that keeps its own fused top-k:
+ * the reference's position, scripts/rocm/integrations/sglang/sglang-gfx1151-bf16-router.patch:64, and its
+ * apply(layer, hidden, topk_weights, topk_ids) entry, scripts/rocm/integrations/sglang/netra_gfx1151_sglang.py:1297-1311).
+ * topk_ids i32 [tokens, 8] (global expert ids 0..255; out-of-range ids are clamped), topk_weights f32 [tokens, 8]
+ * already normalised by the caller.  The router and top-k stages are skipped; everything from the input
+ * quantisation on is the fused sequence. */
+int netra_moe_layer_launch_with_topk(netra_moe_layer_t* layer, const void* hidden_bf16, const int32_t* topk_ids_i32,
+                                     const float* topk_weights_f32, const float* shared_weight_f32, void* out_bf16,
+                                     uint32_t tokens, cudaStream_t stream);
+
 /* Launches ONE stage of the same sequence (0 router logits, 1 top-k + input quantisation,
  * 2-4 sort (stage 2 alone sorts up to 1024 rows; 3 and 4 then launch nothing), 5 row gather, 6 grouped gate_up, 7 grouped down, 8 combine), for callers that
  * migrate one boundary at a time and for per-kernel timing; same rules as the call above.

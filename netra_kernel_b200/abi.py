@@ -57,6 +57,7 @@ SIGNATURES = {
     "netra_moe_workspace_layout_query": (c_int, [c_u32, ctypes.POINTER(WorkspaceLayout)]),
     "netra_moe_layer_create": (c_int, [ctypes.POINTER(LayerDesc), ctypes.POINTER(c_void_p)]),
     "netra_moe_layer_launch": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_u32, c_void_p]),
+    "netra_moe_layer_launch_with_topk": (c_int, [c_void_p] * 6 + [c_u32, c_void_p]),
     "netra_moe_layer_launch_stage": (c_int, [c_void_p, c_u32, c_void_p, c_void_p, c_void_p, c_u32, c_void_p]),
     "netra_moe_repack_tiles_launch": (c_int, [c_void_p, c_void_p, c_u64, c_u32, c_void_p]),
     "netra_moe_mxfp4_expand_launch": (c_int, [c_void_p] * 5 + [c_u64, c_u32, c_void_p]),

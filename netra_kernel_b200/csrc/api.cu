@@ -342,6 +342,20 @@ int netra_moe_layer_launch(netra_moe_layer_t* layer, const void* hidden, const f
   return check_launch("layer launch");
 }
 
+int netra_moe_layer_launch_with_topk(netra_moe_layer_t* layer, const void* hidden, const int32_t* topk_ids, const float* topk_weights,
+                                     const float* shared_w, void* out, uint32_t tokens, cudaStream_t stream) {
+  if (layer == nullptr || hidden == nullptr || out == nullptr || topk_ids == nullptr || topk_weights == nullptr)
+    return fail("layer_launch_with_topk: null pointer");
+  if (tokens == 0 || tokens > layer->desc.max_tokens) return fail("layer_launch_with_topk: tokens exceed the bound capacity");
+  const netra_moe_workspace_layout_t& L = layer->lay;
+  uint8_t* ws = (uint8_t*)layer->desc.workspace;
+  netra_moe_import_topk_quant_sm100<<<(tokens + 3) / 4, 128, 0, stream>>>(
+      (int32_t*)(ws + L.topk_ids), (float*)(ws + L.topk_weights), ws + L.a_fp8, (float*)(ws + L.a_scale), topk_ids, topk_weights,
+      shared_w, (const uint16_t*)hidden, tokens, tokens * kTopK);
+  for (uint32_t stage = 2; stage < kStageCount; ++stage) launch_stage(layer, stage, hidden, shared_w, out, tokens, stream);
+  return check_launch("layer launch with external top-k");
+}
+
 int netra_moe_layer_launch_stage(netra_moe_layer_t* layer, uint32_t stage, const void* hidden, const float* shared_w, void* out,
                                  uint32_t tokens, cudaStream_t stream) {
   if (layer == nullptr || hidden == nullptr || out == nullptr) return fail("layer_launch_stage: null pointer");

@@ -129,6 +129,45 @@ netra_router_logits_bf16_k8_sm100(uint16_t* __restrict__ logits, const uint16_t*
   router_logits_body<8>(logits, hidden, weight, rows);
 }
 
+// Per-128 FP8 quantisation of one hidden row by one warp: a lane owns 64 values, two lanes one group.
+// The quantised row goes to row (row_base + t) of the activation buffer.
+__device__ __forceinline__ void quantize_hidden_row(uint8_t* __restrict__ a_fp8, float* __restrict__ a_scale,
+                                                    const uint16_t* __restrict__ hidden, int t, uint32_t row_base, int lane) {
+  const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)t * kHidden) + lane * 8;
+  float x[64];
+  float amax = amax_floor();
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    uint4 v = src[c];
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      x[c * 8 + 2 * q] = bf16_bits_to_f32(u[q] & 0xffffu);
+      x[c * 8 + 2 * q + 1] = bf16_bits_to_f32(u[q] >> 16);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 64; ++i) amax = fmaxf(amax, fabsf(x[i]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  const float scale = amax * inv448();
+  const float inv = 1.0f / scale;
+  const size_t row = (size_t)row_base + t;
+  if ((lane & 1) == 0) a_scale[row * kHiddenBlocks + (lane >> 1)] = scale;
+  uint4* dst = reinterpret_cast<uint4*>(a_fp8 + row * kHidden) + lane * 4;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint32_t w[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint32_t b = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b |= (uint32_t)f32_to_e4m3(x[c * 16 + q * 4 + j] * inv) << (8 * j);
+      w[q] = b;
+    }
+    dst[c] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // Softmax / top-8 / renormalise + shared slot + per-token FP8 quantisation.  One warp per token.
 // Selection key is (z desc, expert id asc) with z = f32(logit) + bias; weights are
@@ -200,40 +239,29 @@ netra_moe_topk_quant_sm100(int32_t* __restrict__ ids9, float* __restrict__ w9,
     ids9[t * kSlots + kTopK] = kRouted;
     w9[t * kSlots + kTopK] = shared_w != nullptr ? shared_w[t] : 1.0f;
   }
-  // ---- per-128 FP8 quantisation of the hidden row: a lane owns 64 values, 2 lanes one group
-  const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)t * kHidden) + lane * 8;
-  float x[64];
-  float amax = amax_floor();
-#pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    uint4 v = src[c];
-    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      x[c * 8 + 2 * q] = bf16_bits_to_f32(u[q] & 0xffffu);
-      x[c * 8 + 2 * q + 1] = bf16_bits_to_f32(u[q] >> 16);
-    }
+  quantize_hidden_row(a_fp8, a_scale, hidden, t, row_base, lane);
+}
+
+// The same outputs from a top-k computed elsewhere (a serving stack that keeps its own fused top-k, the
+// position of scripts/rocm/integrations/sglang/sglang-gfx1151-bf16-router.patch:64): copies ids [rows, 8] and
+// weights [rows, 8] into the nine-slot arrays (slot 8 = shared expert), and quantises the hidden rows.
+// Ids outside 0..255 are clamped so that no later stage can index out of range.  grid ceil(rows/4), block 128.
+extern "C" __global__ void __launch_bounds__(128)
+netra_moe_import_topk_quant_sm100(int32_t* __restrict__ ids9, float* __restrict__ w9, uint8_t* __restrict__ a_fp8,
+                                  float* __restrict__ a_scale, const int32_t* __restrict__ ext_ids,
+                                  const float* __restrict__ ext_w, const float* __restrict__ shared_w,
+                                  const uint16_t* __restrict__ hidden, uint32_t rows, uint32_t row_base) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (t >= (int)rows) return;
+  if (lane < kTopK) {
+    ids9[t * kSlots + lane] = min(max(ext_ids[t * kTopK + lane], 0), kRouted - 1);
+    w9[t * kSlots + lane] = ext_w[t * kTopK + lane];
+  } else if (lane == kTopK) {
+    ids9[t * kSlots + kTopK] = kRouted;
+    w9[t * kSlots + kTopK] = shared_w != nullptr ? shared_w[t] : 1.0f;
   }
-#pragma unroll
-  for (int i = 0; i < 64; ++i) amax = fmaxf(amax, fabsf(x[i]));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-  const float scale = amax * inv448();
-  const float inv = 1.0f / scale;
-  const size_t row = (size_t)row_base + t;
-  if ((lane & 1) == 0) a_scale[row * kHiddenBlocks + (lane >> 1)] = scale;
-  uint4* dst = reinterpret_cast<uint4*>(a_fp8 + row * kHidden) + lane * 4;
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    uint32_t w[4];
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      uint32_t b = 0;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) b |= (uint32_t)f32_to_e4m3(x[c * 16 + q * 4 + j] * inv) << (8 * j);
-      w[q] = b;
-    }
-    dst[c] = make_uint4(w[0], w[1], w[2], w[3]);
-  }
+  quantize_hidden_row(a_fp8, a_scale, hidden, t, row_base, lane);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -117,6 +117,28 @@ class RoutedMoELayer:
                                                   out.data_ptr(), tokens, _stream()), "layer_launch")
         return out
 
+    def apply(self, hidden: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
+              shared_weight: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The layer with a top-k computed by the caller (argument order of the reference's
+        ``apply(layer, hidden, topk_weights, topk_ids)``, ``scripts/rocm/integrations/sglang/netra_gfx1151_sglang.py:1297-1311``):
+        ``topk_ids`` int32 ``[tokens, 8]``, ``topk_weights`` float32 ``[tokens, 8]`` (normalised by the caller)."""
+        _require_cuda(hidden, topk_weights, topk_ids, shared_weight, out)
+        tokens = hidden.shape[0]
+        if hidden.dtype != torch.bfloat16 or hidden.dim() != 2 or hidden.shape[1] != HIDDEN or not hidden.is_contiguous():
+            raise ValueError("hidden must be contiguous bf16 [tokens, 2048]")
+        if topk_ids.dtype != torch.int32 or tuple(topk_ids.shape) != (tokens, 8) or not topk_ids.is_contiguous():
+            raise ValueError("topk_ids must be contiguous int32 [tokens, 8]")
+        if topk_weights.dtype != torch.float32 or tuple(topk_weights.shape) != (tokens, 8) or not topk_weights.is_contiguous():
+            raise ValueError("topk_weights must be contiguous float32 [tokens, 8]")
+        if self.routing_only:
+            raise RuntimeError("this layer object only serves the routing stages (expert-parallel use)")
+        if out is None:
+            out = torch.empty_like(hidden)
+        abi.check(self.lib.netra_moe_layer_launch_with_topk(self.handle, hidden.data_ptr(), topk_ids.data_ptr(), topk_weights.data_ptr(),
+                                                            _ptr(shared_weight), out.data_ptr(), tokens, _stream()),
+                  "layer_launch_with_topk")
+        return out
+
     STAGES = ("router_logits", "topk_quant", "sort_hist", "sort_scan", "sort_scatter", "gather_rows",
               "gate_up", "down", "combine")
 

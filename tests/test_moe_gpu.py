@@ -178,6 +178,46 @@ def test_mxfp4_expansion_kernel_and_layer(expert_weights):
     check_against(ref, out, inter, tokens)
 
 
+def test_external_topk_entry_and_custom_ops(gpu_weights):
+    """A caller that keeps its own top-k: feeding the layer's own ids and weights back through apply() (and through
+    the registered torch ops) must reproduce the fused call bit for bit; a different top-k changes the result."""
+    from netra_kernel_b200 import torch_ops
+    tokens = 96
+    hidden, router_w, _ = synth.make_activations(tokens, seed=8)
+    layer = make_layer(gpu_weights, router_w, tokens)
+    h = hidden.cuda()
+    want = layer(h).clone()
+    torch.cuda.synchronize()
+    inter = layer.intermediates(tokens)
+    ids = inter["topk_ids"][:, :8].contiguous().clone()
+    w = inter["topk_w"][:, :8].contiguous().clone()
+    got = layer.apply(h, w, ids)
+    torch.cuda.synchronize()
+    layer.check_status()
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    handle = torch_ops.register_layer(layer)
+    assert torch.equal(torch.ops.netra.moe_layer(h, handle).view(torch.int16), want.view(torch.int16))
+    assert torch.equal(torch.ops.netra.moe_apply(h, w, ids, handle).view(torch.int16), want.view(torch.int16))
+    # a top-k from plain torch ops on the exact logits selects the same experts (ties aside) with FP32 weights close by
+    logits = inter["logits"].float()
+    p = torch.softmax(logits, dim=1)
+    tw, ti = torch.topk(p, 8, dim=1)
+    tw = (tw / tw.sum(1, keepdim=True)).contiguous()
+    other = layer.apply(h, tw, ti.to(torch.int32).contiguous())
+    torch.cuda.synchronize()
+    m = R.parity_metrics(helpers.bits(other.cpu()), helpers.bits(want.cpu()))
+    assert m["max_abs"] <= helpers.MAX_ABS and m["rel_l2"] <= helpers.REL_L2, m
+    # uniform weights over the same experts is a different layer: the entry point really uses what it is given
+    flat = layer.apply(h, torch.full_like(w, 0.125), ids)
+    torch.cuda.synchronize()
+    assert not torch.equal(flat.view(torch.int16), want.view(torch.int16))
+    with pytest.raises(ValueError, match="topk_ids"):
+        layer.apply(h, w, ids.long())
+    torch_ops.release_layer(handle)
+    with pytest.raises(RuntimeError, match="no registered layer"):
+        torch.ops.netra.moe_layer(h, handle)
+
+
 def test_bridge_kernels_against_checker(gpu_weights, expert_weights):
     """The three-launch slot-order boundary of the reference's decode bridges."""
     from netra_kernel_b200 import moe
