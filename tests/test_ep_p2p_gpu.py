@@ -175,8 +175,9 @@ def _peer_rank(rank, world, port, tokens, results):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_gpu_peer_memory_layer_equals_the_one_gpu_layer():
-    world, tokens = 2, 512
+@pytest.mark.parametrize("tokens", [512, 2048])      # 2,048 tokens: 64 rows per expert, the token-major GEMMs and their fused return
+def test_two_gpu_peer_memory_layer_equals_the_one_gpu_layer(tokens):
+    world = 2
     manager = mp.Manager()
     results = manager.dict()
     port = _free_port()
