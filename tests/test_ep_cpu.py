@@ -167,3 +167,26 @@ def test_plan_ownership_and_regroup_index():
     world1 = ExpertParallelPlan(1, 0)
     c = torch.arange(256, dtype=torch.int32)
     assert torch.equal(world1.exchange_counts(c).view(-1), c)
+
+
+def test_peer_memory_layer_sizes_and_capacity_rules():
+    """Host-side parts of the peer-memory layer that need no GPU: size queries through the C ABI, capacity rules,
+    argument errors."""
+    import ctypes
+    from netra_kernel_b200 import abi
+    from netra_kernel_b200.ep import default_row_capacity, ep_sizes
+    assert default_row_capacity(1, 256) == 256 * 9
+    assert default_row_capacity(8, 256) == 256 + 8 * 256 * 8                       # worst case: every pair routed to one rank
+    tight = default_row_capacity(8, 256, headroom=8.0)
+    assert 256 + 2048 < tight < default_row_capacity(8, 256) and (tight - 256) % 64 == 0
+    ws, win = ep_sizes(8, 256, default_row_capacity(8, 256))
+    ws2, win2 = ep_sizes(8, 256, tight)
+    assert ws > ws2 > 0 and win > win2 > 0 and ws % 1024 == 0 and win % 1024 == 0
+    # the window holds at least the activation block, its scales and the FP32 return buffer
+    assert win2 >= tight * 2048 + tight * 64 + 256 * 9 * 8192
+    lib = abi.load()
+    a, b = ctypes.c_uint64(), ctypes.c_uint64()
+    assert lib.netra_ep_sizes_query(3, 256, 4096, ctypes.byref(a), ctypes.byref(b)) != 0       # 3 does not divide 256
+    assert b"world" in lib.netra_moe_last_error()
+    assert lib.netra_ep_sizes_query(8, 256, 100, ctypes.byref(a), ctypes.byref(b)) != 0        # cannot hold the rank's own tokens
+    assert lib.netra_ep_layer_stage_count() == 11
