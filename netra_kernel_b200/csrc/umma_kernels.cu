@@ -1,7 +1,7 @@
 // Block-scaled FP8 grouped GEMMs on the sm_100a tensor cores (tcgen05 + TMEM), fed by TMA.
 //
 // Both expert projections run "swap-AB": the 128 weight rows of a tile are the MMA M dimension
-// and the token rows of an expert are the MMA N dimension (16..64), so a decode-sized expert
+// and the token rows of an expert are the MMA N dimension (16 or 32), so a decode-sized expert
 // (about 8 rows) streams its weights exactly once with no padded M work.
 //
 //   gate_up (replaces kernels/gfx950/templates/moe/decode/gate_up_mfma.inc:13-95 and
@@ -177,10 +177,12 @@ __device__ __forceinline__ Item decode_item(int item, const int* item_pre, const
 template <bool kGateUp>
 struct Cfg {
   static constexpr int kATiles = kGateUp ? 2 : 1;
-  static constexpr int kTokMax = kGateUp ? 64 : 32;       // token rows per work item (UMMA N)
+  // token rows per work item (UMMA N).  32 for both: 64-row items (the shared expert at decode sizes) ran a longer
+  // epilogue than the four TMEM stages could hide, and the CTAs that held them finished 8 us after the rest
+  static constexpr int kTokMax = 32;
   static constexpr int kColsPerGroup = kTokMax / 2;       // token columns owned by one epilogue warp group
   static constexpr int kSlices = kColsPerGroup / 8;       // 8-column TMEM loads per group and tile
-  static constexpr int kTokTileBytes = kTokMax * kBlock;  // 8 KiB | 4 KiB
+  static constexpr int kTokTileBytes = kTokMax * kBlock;  // 4 KiB
   static constexpr int kScaleSlots = kGateUp ? 2 : 4;
   static constexpr int kKBlocks = kGateUp ? kHiddenBlocks : kInterBlocks;
   static constexpr int kSubTiles = 1;                     // consecutive weight tiles per work item (same token rows)
@@ -188,14 +190,14 @@ struct Cfg {
   static constexpr int kSlabRows = kGateUp ? 2 * kInter : kHidden;                     // 1024 | 2048
   static constexpr int kSlabTiles = kSlabRows / kTileRows;                             // 8 | 16
   static constexpr int kKbPerStep = kGateUp ? 1 : 4;      // K-blocks the MMA warp issues per accumulator hand-off
-  static constexpr int kAccCols = kKbPerStep * kATiles * kTokMax;                      // TMEM columns per hand-off: 128 | 128
-  static constexpr int kAccStages = 512 / kAccCols;                                    // 4 | 4
-  static constexpr int kStages = kGateUp ? 5 : 10;
-  static constexpr int kStageBytes = kATiles * kWTileBytes + kTokTileBytes;            // 40 KiB | 20 KiB
+  static constexpr int kAccCols = kKbPerStep * kATiles * kTokMax;                      // TMEM columns per hand-off: 64 | 128
+  static constexpr int kAccStages = 512 / kAccCols;                                    // 8 | 4
+  static constexpr int kStages = kGateUp ? 6 : 10;
+  static constexpr int kStageBytes = kATiles * kWTileBytes + kTokTileBytes;            // 36 KiB | 20 KiB
   static constexpr int kTmemCols = 512;
   static constexpr int kXsBytes = kTokMax * kKBlocks * 4;                              // 4 KiB | 1 KiB
   static constexpr int kWsBytes = kKBlocks * 4;                                        // 64 B | 16 B per tile
-  static constexpr int kItemList = 256;                                                // work items of this CTA decoded once
+  static constexpr int kItemList = 128;                                                // work items of this CTA decoded once
   static constexpr int kScaleSlotBytes = kXsBytes + 128;                               // xs, then ws tiles
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kScaleSlots * kScaleSlotBytes + 2 * 4 * kColsPerGroup * 4 +
                                     2 * 264 * 4 + kItemList * 16 + 512;
