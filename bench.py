@@ -32,7 +32,7 @@ UNIT = "tokens/s"
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes (read + write) of one grouped gate_up launch from the committed ncu capture
 # (profiles/gate_up_umma_decode_t256.md: dram__bytes_read.sum + dram__bytes_write.sum, decode T=256).
-GATE_UP_DRAM_TRAFFIC_BYTES = 549_117_440   # profiles/gate_up_umma_decode_t256.md
+GATE_UP_DRAM_TRAFFIC_BYTES = 550_046_976   # profiles/gate_up_umma_decode_t256.md
 
 _REASONS = {
     0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
