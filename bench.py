@@ -413,6 +413,10 @@ def run_ours(args) -> None:
 
     inter = layer.intermediates(tokens)
     experts_hit = int((inter["counts"] > 0).sum().item())
+    load = inter["counts"].to(torch.float64).cpu()
+    routing_load = {"pairs_per_expert_mean": float(load.mean()), "max": int(load.max()), "median": float(load.median()),
+                    "min": int(load.min()), "hottest_over_mean": float(load.max() / load.mean()),
+                    "experts_below_128_rows": int((load < 128).sum())}
     peak, peak_kind = measured_hbm_peak()
     gate_up_bytes = (experts_hit + 1) * (2 * 512 * 2048 + 8 * 16 * 4)
     down_bytes = (experts_hit + 1) * (2048 * 512 + 16 * 4 * 4)
@@ -428,7 +432,7 @@ def run_ours(args) -> None:
         "steps": steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
         "config": {"workload": f"decode_t{tokens} (1 layer, hidden 2048, 256 routed experts top-8 + shared, inter 512)",
-                   "tokens_per_gpu": tokens, "experts_hit": experts_hit,
+                   "tokens_per_gpu": tokens, "experts_hit": experts_hit, "routing_load": routing_load,
                    "parallelism": "single GPU" if world == 1 else f"{world} independent replicas (no collective)",
                    "zipf_alpha": args.zipf_alpha or 0.0,
                    "l2": "inputs larger than L2: every step streams %.1f MB of expert weights (L2 is 126 MB)" % (layer_bytes / 1e6),
@@ -639,7 +643,8 @@ def run_expert_parallel(args) -> None:
                     "how": "every rank copies its tokens from pinned host memory and its result back every step; the copies run on "
                            "their own streams with two staging slots, so they overlap the neighbouring steps' compute",
                     "serial_ms_per_step": e2e_serial_ms},
-            "roofline": {"bound": "hbm", "kernel": ("netra_moe_gate_up_tokmajor_sm100 + netra_ep_down_return_tokmajor_sm100" if world * tokens >= 1536
+            "roofline": {"bound": "hbm", "kernel": ("netra_moe_gate_up_umma_sm100 + netra_moe_down_umma_sm100" if args.ep_exchange != "peer"
+                                                    else "netra_moe_gate_up_tokmajor_sm100 + netra_ep_down_return_tokmajor_sm100" if world * tokens >= 1536
                                                     else "netra_moe_gate_up_umma_sm100 + netra_ep_down_return_umma_sm100") + " (expert block, timed alone)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
                          "algorithmic_bytes": block_bytes, "avg_launch_ms": block_ms, "traffic": None},

@@ -1,6 +1,8 @@
 """GPU parity tests: the sm_100a path through the C ABI against the CPU checker on identical
 seeded operands.  Integer results (logits bits, ids, permutation, counts, offsets, input FP8
 codes) must be bit-exact; the BF16 output must be within max-abs 2e-2 and relative-L2 5e-3."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -216,6 +218,22 @@ def test_external_topk_entry_and_custom_ops(gpu_weights):
     torch_ops.release_layer(handle)
     with pytest.raises(RuntimeError, match="no registered layer"):
         torch.ops.netra.moe_layer(h, handle)
+    # bring-up modes: the slot-order bridge kernels recompute the expert part from the layer's own routing
+    shadow = torch_ops.register_layer(layer, shadow_weights=gpu_weights)
+    try:
+        os.environ["NETRA_ENGINE_MODE"] = "compare"
+        assert torch.equal(torch.ops.netra.moe_layer(h, shadow).view(torch.int16), want.view(torch.int16))
+        cmp = torch_ops.last_comparison(shadow)
+        assert cmp["max_abs"] <= helpers.MAX_ABS and cmp["rel_l2"] <= helpers.REL_L2, cmp
+        broken = (gpu_weights[0], gpu_weights[1] * 1.5, gpu_weights[2], gpu_weights[3])     # a wrong checkpoint on the shadow side
+        bad = torch_ops.register_layer(layer, shadow_weights=broken)
+        with pytest.raises(RuntimeError, match="disagree"):
+            torch.ops.netra.moe_layer(h, bad)
+        os.environ["NETRA_ENGINE_MODE"] = "shadow"                                         # reports, does not raise
+        torch.ops.netra.moe_layer(h, bad)
+        assert torch_ops.last_comparison(bad)["rel_l2"] > helpers.REL_L2
+    finally:
+        os.environ.pop("NETRA_ENGINE_MODE", None)
 
 
 def test_bridge_kernels_against_checker(gpu_weights, expert_weights):
