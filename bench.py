@@ -447,7 +447,7 @@ def run_ours(args) -> None:
                 "how": "every step copies its input from pinned host memory and its result back; the copies run on their own "
                        "streams with two staging slots, so they overlap the neighbouring steps' compute",
                 "serial_ms_per_step": e2e_serial_ms},
-        "roofline": ({"bound": "tensor", "kernel": "netra_moe_gate_up_tokmajor_sm100" if tokens >= 1536 else "netra_moe_gate_up_umma_sm100", "achieved": gate_up_flops / gu_s / 1e12,
+        "roofline": ({"bound": "tensor", "kernel": "netra_moe_gate_up_tokmajor_sm100" if tokens >= 1024 else "netra_moe_gate_up_umma_sm100", "achieved": gate_up_flops / gu_s / 1e12,
                       "peak": fp8_peak, "unit": "TFLOP/s", "frac": gate_up_flops / gu_s / 1e12 / fp8_peak, "peak_source": fp8_kind,
                       "algorithmic_flops": gate_up_flops, "avg_launch_ms": stage_ms[6], "traffic": None}
                      if prefill else
@@ -644,7 +644,7 @@ def run_expert_parallel(args) -> None:
                            "their own streams with two staging slots, so they overlap the neighbouring steps' compute",
                     "serial_ms_per_step": e2e_serial_ms},
             "roofline": {"bound": "hbm", "kernel": ("netra_moe_gate_up_umma_sm100 + netra_moe_down_umma_sm100" if args.ep_exchange != "peer"
-                                                    else "netra_moe_gate_up_tokmajor_sm100 + netra_ep_down_return_tokmajor_sm100" if world * tokens >= 1536
+                                                    else "netra_moe_gate_up_tokmajor_sm100 + netra_ep_down_return_tokmajor_sm100" if world * tokens >= 1024
                                                     else "netra_moe_gate_up_umma_sm100 + netra_ep_down_return_umma_sm100") + " (expert block, timed alone)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
                          "algorithmic_bytes": block_bytes, "avg_launch_ms": block_ms, "traffic": None},

@@ -284,7 +284,7 @@ int netra_ep_layer_destroy(netra_ep_layer_t* layer);
 int netra_moe_kernel_launch_info(uint32_t which, uint32_t* block_threads, uint32_t* dynamic_smem_bytes);
 
 /* The two grouped GEMMs exist in two forms: swap-AB (weights are the MMA M dimension; decode sizes) and
- * token-major (128 token rows x 256 weight rows per MMA; from an average of 48 rows per routed expert).
+ * token-major (128 token rows x 256 weight rows per MMA; from an average of 32 rows per routed expert).
  * mode 0 (default) picks by the token count of the call, mode 1 always uses the swap-AB kernels.  Both
  * forms produce identical results. */
 int netra_moe_layer_set_gemm_mode(netra_moe_layer_t* layer, uint32_t mode);

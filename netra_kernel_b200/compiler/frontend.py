@@ -108,8 +108,8 @@ def routed_moe_layer_graph(model: dict[str, Any], profile: ShapeProfile) -> Grap
     routing_constants = {"hidden": hidden, "routed_experts": experts}
     gemm_constants = {"hidden": hidden, "intermediate": inter, "scale_block": c["scale_block"], "tile_rows": 128}
 
-    # grouped-GEMM form: token-major (128 token rows x 256 weight rows per MMA) from an average of 48 rows per routed expert
-    token_major = m * c["top_k"] >= 48 * experts
+    # grouped-GEMM form: token-major (128 token rows x 256 weight rows per MMA) from an average of 32 rows per routed expert
+    token_major = m * c["top_k"] >= 32 * experts
     form = ("token_major" if token_major else "swap_ab") + ".sorted_rows." + ("tiles128" if opt["weight_layout"] == "tiles128" else "row_major")
     maps = "tmap2" if token_major else "tmap4"
 

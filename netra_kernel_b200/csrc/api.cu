@@ -99,8 +99,8 @@ int umma_setup() {
 }
 
 // The token-major GEMMs pay off once an expert's rows fill a good part of a 128-row tile: from an average
-// of 48 rows per routed expert (1,536 tokens on one GPU) the layer switches to them.
-constexpr uint32_t kTokMajorMinRowsPerExpert = 48;
+// of 32 rows per routed expert (1,024 tokens on one GPU) the layer switches to them.
+constexpr uint32_t kTokMajorMinRowsPerExpert = 32;
 bool use_tokmajor(uint64_t pairs, uint32_t routed_experts) {
   return g_tokmajor_ok && pairs >= (uint64_t)kTokMajorMinRowsPerExpert * routed_experts;
 }

@@ -97,7 +97,7 @@ class RoutedMoELayer:
                    ops.w2_scale.to(dev), max_tokens or ops.tokens, bias)
 
     def set_gemm_mode(self, mode: int) -> None:
-        """0: the layer picks the grouped-GEMM form by token count (token-major from 1,536 tokens); 1: always swap-AB."""
+        """0: the layer picks the grouped-GEMM form by token count (token-major from 1,024 tokens); 1: always swap-AB."""
         abi.check(self.lib.netra_moe_layer_set_gemm_mode(self.handle, mode), "layer_set_gemm_mode")
 
     def launches_per_call(self, tokens: int) -> int:

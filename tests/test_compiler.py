@@ -176,7 +176,7 @@ def test_planner_selects_by_layout_size_and_never_a_rejected_tactic():
     assert gate.tactic.name == "gate_up_silu_requant_umma_tokmajor_row_major"
     other = [c for c in gate.explanation if c["tactic"] == "gate_up_silu_requant_umma_swapab_tiles128"][0]
     assert any("semantic layouts mismatch" in r for r in other["reasons"])
-    # below 1,536 tokens the token-major tactics are out of their size limits and the swap-AB form is requested
+    # below 1,024 tokens the token-major tactics are out of their size limits and the swap-AB form is requested
     small_gate = next(p for p in plan.operations if p.operation.name == "gate_up")
     assert small_gate.tactic.name == "gate_up_silu_requant_umma_swapab_tiles128" and "registers_per_thread" not in small_gate.contract.launch.to_dict()
 

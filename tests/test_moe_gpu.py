@@ -128,7 +128,7 @@ def test_prefill_t8192_zipf_sampled_tokens(gpu_weights, expert_weights):
 
 @pytest.mark.parametrize("tokens,alpha", [(2048, 0.0), (3000, 1.2)])
 def test_token_major_and_swap_ab_gemms_agree_bitwise(gpu_weights, tokens, alpha):
-    """From 1,536 tokens the layer runs the token-major GEMMs (128 token rows x 256 weight rows per MMA); the
+    """From 1,024 tokens the layer runs the token-major GEMMs (128 token rows x 256 weight rows per MMA); the
     swap-AB kernels computing the same rows must give the same intermediate codes, scales, FP32 rows and output."""
     hidden, router_w, bias = synth.make_activations(tokens, alpha or None, seed=9)
     layer = make_layer(gpu_weights, router_w, tokens, bias)
