@@ -126,7 +126,7 @@ def test_prefill_t8192_zipf_sampled_tokens(gpu_weights, expert_weights):
     assert np.array_equal(np.bincount(flat, minlength=256), inter["counts"].numpy())
 
 
-@pytest.mark.parametrize("tokens,alpha", [(2048, 0.0), (3000, 1.2)])
+@pytest.mark.parametrize("tokens,alpha", [(1024, 0.0), (1031, 0.5), (2048, 0.0), (3000, 1.2), (1500, 3.0), (4096, 0.0)])
 def test_token_major_and_swap_ab_gemms_agree_bitwise(gpu_weights, tokens, alpha):
     """From 1,024 tokens the layer runs the token-major GEMMs (128 token rows x 256 weight rows per MMA); the
     swap-AB kernels computing the same rows must give the same intermediate codes, scales, FP32 rows and output."""
@@ -139,9 +139,11 @@ def test_token_major_and_swap_ab_gemms_agree_bitwise(gpu_weights, tokens, alpha)
     for key in ("h_fp8", "h_scale", "down"):
         assert torch.equal(inter_tm[key][:rows], inter_sw[key][:rows]), key
     assert torch.equal(out_tm.view(torch.int16), out_sw.view(torch.int16))
-    if alpha:
-        counts = inter_tm["counts"].numpy()
+    counts = inter_tm["counts"].numpy()
+    if alpha >= 1.0:
         assert counts.max() > 256 and counts.min() < 16      # several 128-row tiles for the hottest, ragged tails elsewhere
+    if alpha >= 3.0:
+        assert (counts == 0).sum() > 50                      # most experts empty: groups without any work item
 
 
 def test_mxfp4_expansion_kernel_and_layer(expert_weights):
