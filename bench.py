@@ -356,6 +356,15 @@ def run_ours(args) -> None:
         e1.record(stream)
         barrier()
         ms_per_step = max_over_ranks(e0.elapsed_time(e1) / steps)
+        # spread of single steps (an event between consecutive replays; not the headline number)
+        ticks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        ticks[0].record(stream)
+        for k in range(steps):
+            graph.replay()
+            ticks[k + 1].record(stream)
+        barrier()
+        singles = sorted(ticks[k].elapsed_time(ticks[k + 1]) for k in range(steps))
+        step_spread = {"p10": singles[len(singles) // 10], "median": singles[len(singles) // 2], "p90": singles[(len(singles) * 9) // 10]}
 
         # ---- per-kernel timing in place (events between the stages of the same sequence)
         n_stage = len(layer.STAGES)
@@ -442,6 +451,7 @@ def run_ours(args) -> None:
                    "launch": "CUDA graph replay of the layer's %d kernels" % layer.launches_per_call(tokens),
                    "api": api_name},
         "gpu_launches": steps * layer.launches_per_call(tokens),
+        "step_ms_spread": step_spread,
         "e2e": {"value": world * tokens / (e2e_ms / 1e3), "unit": UNIT, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": tokens * 2048 * 2, "d2h_bytes_per_step": tokens * 2048 * 2,
                 "how": "every step copies its input from pinned host memory and its result back; the copies run on their own "
