@@ -654,7 +654,7 @@ def run_expert_parallel(args) -> None:
                            "their own streams with two staging slots, so they overlap the neighbouring steps' compute",
                     "serial_ms_per_step": e2e_serial_ms},
             "roofline": {"bound": "hbm", "kernel": ("netra_moe_gate_up_umma_sm100 + netra_moe_down_umma_sm100" if args.ep_exchange != "peer"
-                                                    else "netra_moe_gate_up_tokmajor_sm100 + netra_ep_down_return_tokmajor_sm100" if world * tokens >= 1024
+                                                    else "netra_moe_gate_up_tokmajor_sm100 + netra_ep_down_return_umma_sm100" if world * tokens >= 1024
                                                     else "netra_moe_gate_up_umma_sm100 + netra_ep_down_return_umma_sm100") + " (expert block, timed alone)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
                          "algorithmic_bytes": block_bytes, "avg_launch_ms": block_ms, "traffic": None},

@@ -437,7 +437,11 @@ void ep_launch_stage(netra_ep_layer* L, uint32_t stage, const void* hidden, cons
             L->blk_h, L->blk_hs, L->e_l + 1, d.weights_tiled, L->tab->status);
       break;
     case 8:
-      if (L->tokmajor_ok && use_tokmajor((uint64_t)d.world * pairs, kRouted))
+      // Across GPUs the swap-AB form is kept for the down projection whatever the size: its epilogue stores 128
+      // contiguous bytes of one row per warp instruction, while a token-major thread owns a whole row and a warp
+      // instruction scatters 32-byte pieces over 32 rows - over NVLink that took three times as long (8 GPUs,
+      // 64 rows per expert: 77 us against 25 us of GEMM time).
+      if (L->tokmajor_ok && d.world == 1 && use_tokmajor((uint64_t)d.world * pairs, kRouted))
         netra_ep_down_return_tokmajor_sm100<<<L->sm_count, kTmThreads, down_tokmajor_smem_bytes(), stream>>>(
             L->tm_w2, L->tm_h128, L->blk_hs, d.w2_scale_f32, L->tab->offsets, L->row_ptr, L->e_l + 1, d.weights_tiled,
             L->tab->status + 1, L->peers, L->wl, L->tab, d.world, d.rank);

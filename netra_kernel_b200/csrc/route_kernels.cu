@@ -365,8 +365,9 @@ netra_moe_sort_scatter_sm100(int32_t* __restrict__ perm, int32_t* __restrict__ i
   }
 }
 
-// Whole sort in one block for up to 8192 pairs (rows <= 1024): 32 warps x 256 consecutive pairs.
-// Same result as the three-launch path; no global scratch.  grid 1, block 1024.
+// Whole sort in one block for up to 8192 pairs (rows <= 1024): each of the 32 warps owns a run of consecutive
+// pairs (a multiple of 32, as short as the pair count allows so that all warps work: 64 at 256 rows, 256 at
+// 1,024 rows).  Same result as the three-launch path; no global scratch.  grid 1, block 1024.
 constexpr int kSortSmallMaxRows = 1024;
 
 extern "C" __global__ void __launch_bounds__(1024)
@@ -378,12 +379,13 @@ netra_moe_sort_small_sm100(int32_t* __restrict__ perm, int32_t* __restrict__ inv
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int i = threadIdx.x; i < 32 * kRouted; i += 1024) (&wbase[0][0])[i] = 0;
   __syncthreads();
-  const int wstart = warp * 256;
+  const int rounds = max(1, (pairs + 1023) / 1024);     // 32-pair rounds per warp: 1..8
+  const int wstart = warp * rounds * 32;
   int my_e[8];
 #pragma unroll
   for (int c = 0; c < 8; ++c) {
     const int pair = wstart + c * 32 + lane;
-    my_e[c] = pair < pairs ? pair_expert(ids9, pair) : -1;
+    my_e[c] = (c < rounds && pair < pairs) ? pair_expert(ids9, pair) : -1;
     if (my_e[c] >= 0) atomicAdd(&wbase[warp][my_e[c]], 1);   // counts only: order independent
   }
   __syncthreads();
@@ -415,6 +417,7 @@ netra_moe_sort_small_sm100(int32_t* __restrict__ perm, int32_t* __restrict__ inv
   __syncthreads();
 #pragma unroll
   for (int c = 0; c < 8; ++c) {
+    if (c >= rounds) break;                                // uniform across the block
     const int pair = wstart + c * 32 + lane;
     const int e = my_e[c];
     const unsigned active = __ballot_sync(0xffffffffu, e >= 0);
