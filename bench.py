@@ -179,7 +179,7 @@ def run_reference(args) -> None:
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_call * 1e3 * tokens / sample_tokens,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
-        "config": {"workload": f"decode_t{tokens}", "tokens": tokens, "routed_experts": 256, "top_k": 8,
+        "config": {"workload": workload_name(tokens), "tokens": tokens, "routed_experts": 256, "top_k": 8,
                    "shared_experts": 1, "hidden": 2048, "intermediate": 512},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -190,6 +190,11 @@ def run_reference(args) -> None:
 
 
 # --------------------------------------------------------------------------- GPU arm
+def workload_name(tokens: int) -> str:
+    """decode_t256 and prefill_t8192 are the two named configurations; other sizes are named by their token count."""
+    return f"prefill_t{tokens}" if tokens >= 1024 else f"decode_t{tokens}"
+
+
 def time_e2e_pipelined(compute, hidden, out, hidden_cpu, steps, warmup, stream):
     """End-to-end time per step with the host copies of neighbouring steps overlapping the compute of this one, as a
     serving loop would run it: every step still moves its own input from pinned host memory to the device and its own
@@ -440,7 +445,7 @@ def run_ours(args) -> None:
         "metric": METRIC, "value": world * tokens / (ms_per_step / 1e3), "unit": UNIT, "n_gpus": world,
         "steps": steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
-        "config": {"workload": f"decode_t{tokens} (1 layer, hidden 2048, 256 routed experts top-8 + shared, inter 512)",
+        "config": {"workload": f"{workload_name(tokens)} (1 layer, hidden 2048, 256 routed experts top-8 + shared, inter 512)",
                    "tokens_per_gpu": tokens, "experts_hit": experts_hit, "routing_load": routing_load,
                    "parallelism": "single GPU" if world == 1 else f"{world} independent replicas (no collective)",
                    "zipf_alpha": args.zipf_alpha or 0.0,
@@ -633,7 +638,7 @@ def run_expert_parallel(args) -> None:
             "metric": METRIC, "value": world * tokens / (ms_per_step / 1e3), "unit": UNIT, "n_gpus": world, "steps": steps,
             "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "fp8_e4m3", "data": "synthetic",
-            "config": {"workload": f"decode_t{tokens} per GPU (1 layer, hidden 2048, 256 routed experts top-8 + shared, inter 512)",
+            "config": {"workload": f"{workload_name(tokens)} per GPU (1 layer, hidden 2048, 256 routed experts top-8 + shared, inter 512)",
                        "tokens_per_gpu": tokens, "tokens_total": world * tokens,
                        "parallelism": f"ep{world}: {plan.experts_per_rank} routed experts per GPU, shared expert and router replicated, "
                                       "rows dispatched to the owners and returned",
