@@ -513,7 +513,8 @@ def run_expert_parallel(args) -> None:
     graph = None
     if args.ep_exchange == "peer":
         # the library's own kernels move the rows through the peers' windows; one CUDA graph replay per step
-        layer = PeerExpertParallelLayer(plan, router_dev, *local, max_local_tokens=tokens)
+        # a generous bound on the flag waits: ranks of a loaded host can drift apart by more than the library's 2 s default
+        layer = PeerExpertParallelLayer(plan, router_dev, *local, max_local_tokens=tokens, wait_timeout_s=10.0)
         torch.cuda.synchronize(dev)
         dist.barrier()
         with torch.cuda.stream(stream):
