@@ -10,6 +10,12 @@ the shared expert; about 811.8 MB of weights streamed per call).  One JSON line 
 rank 0.  `value` is timed on the device with inputs resident in HBM; `e2e` goes through the
 same public call with pinned host buffers (host->device copy of the tokens and device->host
 copy of the result inside the timed region).
+
+The same line carries the other named configurations as objects of their own:
+`prefill_t8192` (T=8192, Zipf-skewed routing, tensor-bound), `mxfp4_t8192` (the same with MXFP4
+expert weights) at N=1, and at every N `ep_stack` (40 layers, 16,384 tokens per step in total,
+experts sharded over the N GPUs: strong scaling) with, for N>1, a `parity` object from one
+untimed call whose result every rank compares bit for bit with the one-GPU layer.
 """
 from __future__ import annotations
 
@@ -30,9 +36,14 @@ sys.path.insert(0, str(ROOT))
 METRIC = "routed_moe_layer_tokens_per_s"
 UNIT = "tokens/s"
 FALLBACK_HBM_GBS = 6650.0
-# DRAM bytes (read + write) of one grouped gate_up launch from the committed ncu capture
-# (profiles/gate_up_umma_decode_t256.md: dram__bytes_read.sum + dram__bytes_write.sum, decode T=256).
-GATE_UP_DRAM_TRAFFIC_BYTES = 550_046_976   # profiles/gate_up_umma_decode_t256.md
+# DRAM bytes (read + write) of one grouped gate_up launch at decode T=256, from one ncu capture
+# (dram__bytes_read.sum + dram__bytes_write.sum), with the hash of the kernel source it was taken on:
+# the figure is reported only while that source is unchanged.
+GATE_UP_DRAM_TRAFFIC = {"bytes": 550_046_976, "source": "netra_kernel_b200/csrc/umma_kernels.cu",
+                        "sha256": "bf5fdde7b3edb0dfc2d7c6eff6092472bd7887889d826484626575ba6d990fa0"}
+STACK_LAYERS = 40
+STACK_TOKENS = 16384
+NVLINK_GBS = 770.0            # measured peer copy per direction per GPU on this pool
 
 _REASONS = {
     0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
@@ -179,8 +190,7 @@ def run_reference(args) -> None:
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_call * 1e3 * tokens / sample_tokens,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
-        "config": {"workload": workload_name(tokens), "tokens": tokens, "routed_experts": 256, "top_k": 8,
-                   "shared_experts": 1, "hidden": 2048, "intermediate": 512},
+        "config": headline_config(tokens),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference has no CPU or CUDA implementation of this path (AMD assembly); this is the CPU "
@@ -191,8 +201,26 @@ def run_reference(args) -> None:
 
 # --------------------------------------------------------------------------- GPU arm
 def workload_name(tokens: int) -> str:
-    """decode_t256 and prefill_t8192 are the two named configurations; other sizes are named by their token count."""
+    """decode_t256 and prefill_t8192 are the two named single-layer configurations; other sizes are named by their token
+    count (token-major GEMMs, i.e. the prefill regime, start at 1,024 tokens)."""
     return f"prefill_t{tokens}" if tokens >= 1024 else f"decode_t{tokens}"
+
+
+def headline_config(tokens: int) -> dict:
+    """The `config` object of the headline line: the same for this repository's arm and the reference arm."""
+    return {"workload": workload_name(tokens), "tokens": tokens, "layers": 1, "routed_experts": 256, "top_k": 8,
+            "shared_experts": 1, "hidden": 2048, "intermediate": 512, "expert_weights": "fp8_e4m3_block128"}
+
+
+def gate_up_traffic_bytes():
+    """The ncu DRAM figure of one decode gate_up launch, or None once the kernel source is no longer the captured one."""
+    import hashlib
+    path = ROOT / GATE_UP_DRAM_TRAFFIC["source"]
+    try:
+        same = hashlib.sha256(path.read_bytes()).hexdigest() == GATE_UP_DRAM_TRAFFIC["sha256"]
+    except OSError:
+        same = False
+    return GATE_UP_DRAM_TRAFFIC["bytes"] if same else None
 
 
 def time_e2e_pipelined(compute, hidden, out, hidden_cpu, steps, warmup, stream):
@@ -318,6 +346,260 @@ def make_engine_session(args, tokens, device_id, layer, hidden, out):
     return session
 
 
+
+class Sync:
+    """Barrier and max-over-ranks helpers of one rank."""
+
+    def __init__(self, dev, world):
+        import torch
+        self.dev, self.world, self.torch = dev, world, torch
+
+    def barrier(self):
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        self.torch.cuda.synchronize(self.dev)
+
+    def max_ms(self, ms: float) -> float:
+        if self.world == 1:
+            return ms
+        import torch.distributed as dist
+        t = self.torch.tensor([ms], device=self.dev, dtype=self.torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_int(self, v: int) -> int:
+        if self.world == 1:
+            return int(v)
+        import torch.distributed as dist
+        t = self.torch.tensor([int(v)], device=self.dev, dtype=self.torch.int64)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return int(t.item())
+
+
+def time_replays(replay, steps, warmup, stream, sync: Sync, spread: bool = False):
+    """Device time per step of `replay()` (CUDA events on `stream`, barrier + synchronize on both sides, max over ranks)."""
+    import torch
+    for _ in range(warmup):
+        replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync.barrier()
+    e0.record(stream)
+    for _ in range(steps):
+        replay()
+    e1.record(stream)
+    sync.barrier()
+    ms = sync.max_ms(e0.elapsed_time(e1) / steps)
+    if not spread:
+        return ms, None
+    ticks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    ticks[0].record(stream)
+    for k in range(steps):
+        replay()
+        ticks[k + 1].record(stream)
+    sync.barrier()
+    singles = sorted(ticks[k].elapsed_time(ticks[k + 1]) for k in range(steps))
+    return ms, {"p10": singles[len(singles) // 10], "median": singles[len(singles) // 2], "p90": singles[(len(singles) * 9) // 10]}
+
+
+def time_stages(layer, hidden, out, steps, warmup, stream, sync: Sync):
+    """Mean device time of every stage of the layer sequence, events between the direct launches of one call."""
+    import torch
+    n_stage = len(layer.STAGES)
+    marks = [[torch.cuda.Event(enable_timing=True) for _ in range(n_stage + 1)] for _ in range(steps)]
+    for _ in range(warmup):
+        layer(hidden, out=out)
+    sync.barrier()
+    for k in range(steps):
+        marks[k][0].record(stream)
+        for st in range(n_stage):
+            layer.launch_stage(st, hidden, out)
+            marks[k][st + 1].record(stream)
+    sync.barrier()
+    return [statistics.mean(marks[k][st].elapsed_time(marks[k][st + 1]) for k in range(steps)) for st in range(n_stage)]
+
+
+def time_e2e(replay, hidden, out, hidden_cpu, steps, warmup, stream, sync: Sync):
+    """End to end per step with pinned host buffers: serial (copy, call, copy on one stream) and pipelined (what `e2e`
+    reports).  Returns (pipelined ms, serial ms, host api name, last host result)."""
+    import torch
+    host_in = hidden_cpu.pin_memory()
+    host_out = torch.empty_like(hidden_cpu).pin_memory()
+
+    def serial_step():
+        hidden.copy_(host_in, non_blocking=True)
+        replay()
+        host_out.copy_(out, non_blocking=True)
+
+    serial_ms, _ = time_replays(serial_step, steps, warmup, stream, sync)
+    sync.barrier()
+    piped_ms, piped_out, host_api = time_e2e_pipelined(replay, hidden, out, hidden_cpu, steps, warmup, stream)
+    sync.barrier()
+    if not torch.equal(piped_out[(steps - 1) & 1], host_out):
+        raise SystemExit("bench: the pipelined end-to-end loop returned a different result than the serial one")
+    return sync.max_ms(piped_ms), serial_ms, host_api, host_out
+
+
+def routing_load(counts) -> dict:
+    import torch
+    load = counts.to(torch.float64).cpu()
+    return {"pairs_per_expert_mean": float(load.mean()), "max": int(load.max()), "median": float(load.median()),
+            "min": int(load.min()), "hottest_over_mean": float(load.max() / load.mean()),
+            "experts_below_128_rows": int((load < 128).sum())}
+
+
+def e2e_object(tokens_total, tokens_per_rank, e2e_ms, serial_ms, host_api) -> dict:
+    return {"value": tokens_total / (e2e_ms / 1e3), "unit": UNIT, "ms_per_step": e2e_ms,
+            "h2d_bytes_per_step": tokens_per_rank * 2048 * 2, "d2h_bytes_per_step": tokens_per_rank * 2048 * 2,
+            "how": "every step copies its input from pinned host memory and its result back; the copies run on their own "
+                   "streams with two staging slots, so they overlap the neighbouring steps' compute",
+            "copies_enqueued_with": host_api, "serial_ms_per_step": serial_ms}
+
+
+def prefill_object(name, layer, hidden_cpu, steps, warmup, dev, stream, sync, extra_config) -> dict:
+    """One tensor-bound single-layer configuration (T=8192): graph replay of the fused-layer call, per-kernel times,
+    end to end, and the FP8 tensor roofline of the dominant kernel and of the whole call."""
+    import torch
+    from netra_kernel_b200 import synth
+    tokens = hidden_cpu.shape[0]
+    hidden = hidden_cpu.to(dev)
+    out = torch.empty_like(hidden)
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            layer(hidden, out=out)
+        stream.synchronize()
+        layer.check_status()
+        stats0 = layer.router_stats()[0]
+        layer(hidden, out=out)
+        stream.synchronize()
+        recomputed = (layer.router_stats()[0] - stats0) & 0xffffffff
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            layer(hidden, out=out)
+        ms, spread = time_replays(graph.replay, steps, warmup, stream, sync, spread=True)
+        stage_ms = time_stages(layer, hidden, out, steps, warmup, stream, sync)
+        e2e_ms, serial_ms, host_api, _ = time_e2e(graph.replay, hidden, out, hidden_cpu, steps, warmup, stream, sync)
+        stream.synchronize()
+    layer.check_status()
+    inter = layer.intermediates(tokens)
+    fp8_peak, fp8_kind = measured_fp8_peak()
+    hbm_peak, hbm_kind = measured_hbm_peak()
+    gate_up_flops = tokens * 9 * 2 * 2048 * 1024
+    layer_flops = synth.workload_flops(tokens)
+    floor_bytes = synth.workload_bytes_decode(tokens, int((inter["counts"] > 0).sum().item()))
+    gu_s = stage_ms[6] / 1e3
+    obj = {
+        "workload": name, "tokens": tokens, **extra_config, "routing_load": routing_load(inter["counts"]),
+        "ms_per_step": ms, "tokens_per_s": tokens / (ms / 1e3), "steps": steps, "warmup": warmup, "step_ms_spread": spread,
+        "launch": "CUDA graph replay of the layer's %d kernels" % layer.launches_per_call(tokens),
+        "api": "netra_moe_layer_launch (fused-layer ABI, captured CUDA graph)",
+        "tactics": {"router": "BF16 tensor-core pass (tcgen05 kind::f16, FP32 accumulate) + FP64 recomputation of the logits whose "
+                              "BF16 rounding the FP32 value cannot decide; emitted logits are the exactly rounded dot products",
+                    "router_logits_recomputed_fraction": recomputed / (tokens * 256),
+                    "gemm_form": "token-major (128 token rows x 256 weight rows per tcgen05.mma)",
+                    "down_rows": "fp16 partial rows + slot-ascending reducer (the reference's prefill contract)" if layer.partial_f16
+                                 else "fp32 rows + slot-ascending combine (decode contract)"},
+        "roofline": {"bound": "tensor", "kernel": "netra_moe_gate_up_tokmajor_sm100", "achieved": gate_up_flops / gu_s / 1e12,
+                     "peak": fp8_peak, "unit": "TFLOP/s", "frac": gate_up_flops / gu_s / 1e12 / fp8_peak, "peak_source": fp8_kind,
+                     "algorithmic_flops": gate_up_flops, "avg_launch_ms": stage_ms[6], "traffic": None},
+        "layer_tensor": {"algorithmic_flops": layer_flops, "achieved": layer_flops / (ms / 1e3) / 1e12, "unit": "TFLOP/s",
+                         "frac": layer_flops / (ms / 1e3) / 1e12 / fp8_peak, "peak": fp8_peak, "peak_source": fp8_kind},
+        "layer_hbm_floor": {"compulsory_bytes": floor_bytes, "ms_at_peak": floor_bytes / hbm_peak / 1e6, "peak": hbm_peak,
+                            "peak_source": hbm_kind},
+        "kernels_ms": {n: round(v, 5) for n, v in zip(layer.STAGES, stage_ms)},
+        "e2e": e2e_object(tokens, tokens, e2e_ms, serial_ms, host_api),
+    }
+    del graph
+    return obj
+
+
+def make_stack_single(dev, layers, tokens, stream):
+    """N=1 form of the 40-layer stack: one fused layer object per layer (own weights, generated on the device), all of
+    them sharing one workspace since they run one after the other."""
+    import torch
+    from netra_kernel_b200 import synth
+    from netra_kernel_b200.moe import RoutedMoELayer, workspace_layout
+    _, router_w, _ = synth.make_activations(16)
+    router_dev = router_w.to(dev)
+    shared = torch.zeros(workspace_layout(tokens).total_bytes + 2048, dtype=torch.uint8, device=dev)
+    shift = (-shared.data_ptr()) % 1024
+    shared = shared[shift:]
+    objs = []
+    with torch.cuda.stream(stream):
+        for l in range(layers):
+            w13, w13_s, w2, w2_s = synth.make_expert_weights_device(l, dev)
+            layer = RoutedMoELayer(router_dev, w13, w13_s, w2, w2_s, tokens, workspace=shared)
+            layer.set_partial_format(1)
+            del w13, w2
+            objs.append(layer)
+        stream.synchronize()
+    return objs
+
+
+def stack_bounds(tokens_total, world, remote_pairs_per_rank) -> dict:
+    """Per-layer lower bounds of one rank: its expert slabs from HBM, its rows on the FP8 tensor cores, its rows over
+    NVLink (FP8 row + scales out, FP32 row back)."""
+    hbm_peak, hbm_kind = measured_hbm_peak()
+    fp8_peak, fp8_kind = measured_fp8_peak()
+    slabs = 256 // world + 1
+    hbm_bytes = slabs * (2 * 512 * 2048 + 2048 * 512 + 4 * (8 * 16 + 16 * 4)) + 2 * (tokens_total // world) * 2048 * 2
+    rows = tokens_total * 8 // world + tokens_total // world
+    flops = rows * (2 * 2048 * 1024 + 2 * 512 * 2048)
+    nv_bytes = remote_pairs_per_rank * (2048 + 64 + 2048 * 4)
+    times = {"hbm": hbm_bytes / hbm_peak / 1e6, "tensor": flops / fp8_peak / 1e9, "nvlink": nv_bytes / NVLINK_GBS / 1e6}
+    bound = max(times, key=times.get)
+    return {"per_layer_ms": times, "binding": bound, "bound_ms_per_layer": times[bound],
+            "hbm_bytes_per_rank_per_layer": hbm_bytes, "fp8_flops_per_rank_per_layer": flops,
+            "nvlink_bytes_per_rank_per_layer": nv_bytes, "peaks": {"hbm_gbs": hbm_peak, "hbm_source": hbm_kind,
+                                                                    "fp8_tflops": fp8_peak, "fp8_source": fp8_kind,
+                                                                    "nvlink_gbs_per_direction": NVLINK_GBS}}
+
+
+def stack_object(layers_objs, hidden_cpu, steps, warmup, dev, stream, sync, world, plan_text, remote_pairs, api) -> dict:
+    import torch
+    tokens_local = hidden_cpu.shape[0]
+    hidden = hidden_cpu.to(dev)
+    out = torch.empty_like(hidden)
+
+    def call_all():
+        for layer in layers_objs:
+            layer(hidden, out=out)
+
+    with torch.cuda.stream(stream):
+        call_all()
+        stream.synchronize()
+        for layer in layers_objs:
+            layer.check_status()
+        sync.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            call_all()
+        ms, spread = time_replays(graph.replay, steps, warmup, stream, sync, spread=True)
+        e2e_ms, serial_ms, host_api, _ = time_e2e(graph.replay, hidden, out, hidden_cpu, steps, warmup, stream, sync)
+        stream.synchronize()
+    for layer in layers_objs:
+        layer.check_status()
+    n_layers = len(layers_objs)
+    tokens_total = tokens_local * world
+    bounds = stack_bounds(tokens_total, world, remote_pairs)
+    launches = sum(l.launches_per_call(tokens_local) for l in layers_objs)
+    obj = {
+        "workload": f"ep_stack_{n_layers}x_t{tokens_total}", "layers": n_layers, "tokens_per_step": tokens_total,
+        "tokens_per_gpu": tokens_local, "n_gpus": world, "experts_per_gpu": 256 // world, "scaling": "strong",
+        "routing": "near-uniform (random router weights, no bias); every layer sees the same seeded hidden distribution",
+        "weights": "independent per layer, drawn and quantised on the device with seed 1000 + layer",
+        "parallelism": plan_text, "api": api,
+        "ms_per_step": ms, "ms_per_layer": ms / n_layers, "tokens_per_s": tokens_total / (ms / 1e3),
+        "layer_tokens_per_s": tokens_total * n_layers / (ms / 1e3), "steps": steps, "warmup": warmup, "step_ms_spread": spread,
+        "launch": "one CUDA graph replay per step (%d kernels)" % launches, "gpu_launches": steps * launches,
+        "bound": {**bounds, "frac": bounds["bound_ms_per_layer"] / (ms / n_layers)},
+        "nvlink_bytes_per_rank_per_step": bounds["nvlink_bytes_per_rank_per_layer"] * n_layers,
+        "e2e": e2e_object(tokens_total, tokens_local, e2e_ms, serial_ms, host_api),
+    }
+    del graph
+    return obj
+
+
 def run_ours(args) -> None:
     import torch
     import torch.distributed as dist
@@ -331,6 +613,7 @@ def run_ours(args) -> None:
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    sync = Sync(dev, world)
     tokens, steps, warmup = args.tokens, args.steps, max(args.warmup, 3)
 
     hidden_cpu, router_w, bias = synth.make_activations(tokens, args.zipf_alpha or None, seed=rank)
@@ -350,21 +633,11 @@ def run_ours(args) -> None:
     layer = RoutedMoELayer(router_w.to(dev), w13, w13_s, w2, w2_s, tokens, None if bias is None else bias.to(dev),
                            tiled=not args.row_major_weights)
     del w13, w2
+    if args.partials == "f16":
+        layer.set_partial_format(1)
     hidden = hidden_cpu.to(dev)
     out = torch.empty_like(hidden)
     stream = torch.cuda.Stream(device=dev)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize(dev)
-
-    def max_over_ranks(ms: float) -> float:
-        if world == 1:
-            return ms
-        t = torch.tensor([ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
 
     if args.profile_only:
         # plain launches only, for a profiler: no graph, no soak loop, no CPU baseline
@@ -378,96 +651,96 @@ def run_ours(args) -> None:
 
     uuid = str(torch.cuda.get_device_properties(dev).uuid)
     uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
-    with torch.cuda.stream(stream), ClockSampler(uuid) as clocks:
-        # ---- device-resident loop (value): the layer's launches captured once into a CUDA graph and replayed
-        # per step, through the engine runtime ABI (netra_engine_launch) when an engine profile exists for this
-        # token count, otherwise through the fused-layer entry point
-        for _ in range(warmup):
-            layer(hidden, out=out)
-        stream.synchronize()
-        layer.check_status()
-        session = make_engine_session(args, tokens, local_rank, layer, hidden, out) if args.api == "engine" else None
-        if session is not None:
-            session.prepare(stream.cuda_stream)
-
-            class _EngineGraph:
-                def replay(self_inner):
-                    session.launch(stream.cuda_stream)
-            graph = _EngineGraph()
-            api_name = "netra_engine_launch (engine runtime ABI, captured CUDA graph)"
-        else:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
+    extras = {}
+    with ClockSampler(uuid) as clocks:
+        with torch.cuda.stream(stream):
+            # ---- device-resident loop (value): the layer's launches captured once into a CUDA graph and replayed
+            # per step, through the engine runtime ABI (netra_engine_launch) when an engine profile exists for this
+            # token count, otherwise through the fused-layer entry point
+            for _ in range(warmup):
                 layer(hidden, out=out)
-            api_name = "netra_moe_layer_launch (fused-layer ABI, captured CUDA graph)"
-        for _ in range(warmup):
-            graph.replay()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        e0.record(stream)
-        for _ in range(steps):
-            graph.replay()
-        e1.record(stream)
-        barrier()
-        ms_per_step = max_over_ranks(e0.elapsed_time(e1) / steps)
-        # spread of single steps (an event between consecutive replays; not the headline number)
-        ticks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
-        ticks[0].record(stream)
-        for k in range(steps):
-            graph.replay()
-            ticks[k + 1].record(stream)
-        barrier()
-        singles = sorted(ticks[k].elapsed_time(ticks[k + 1]) for k in range(steps))
-        step_spread = {"p10": singles[len(singles) // 10], "median": singles[len(singles) // 2], "p90": singles[(len(singles) * 9) // 10]}
-
-        # ---- per-kernel timing in place (events between the stages of the same sequence)
-        n_stage = len(layer.STAGES)
-        marks = [[torch.cuda.Event(enable_timing=True) for _ in range(n_stage + 1)] for _ in range(steps)]
-        for _ in range(warmup):
-            layer(hidden, out=out)
-        barrier()
-        for k in range(steps):
-            marks[k][0].record(stream)
-            for s in range(n_stage):
-                layer.launch_stage(s, hidden, out)
-                marks[k][s + 1].record(stream)
-        barrier()
-        stage_ms = [statistics.mean(marks[k][s].elapsed_time(marks[k][s + 1]) for k in range(steps)) for s in range(n_stage)]
-
-        # ---- end to end through the public call with pinned host buffers
-        host_in = hidden_cpu.pin_memory()
-        host_out = torch.empty_like(hidden_cpu).pin_memory()
-        def e2e_step():
-            hidden.copy_(host_in, non_blocking=True)     # the bound input buffer
-            graph.replay()
-            host_out.copy_(out, non_blocking=True)
-
-        for _ in range(warmup):
-            e2e_step()
-        barrier()
-        e0.record(stream)
-        for _ in range(steps):
-            e2e_step()
-        e1.record(stream)
-        barrier()
-        e2e_serial_ms = max_over_ranks(e0.elapsed_time(e1) / steps)
-        # the same with double-buffered copies on their own streams (what `e2e` reports)
-        barrier()
-        piped_ms, piped_out, e2e_host_api = time_e2e_pipelined(graph.replay, hidden, out, hidden_cpu, steps, warmup, stream)
-        barrier()
-        e2e_ms = max_over_ranks(piped_ms)
-        if not torch.equal(piped_out[(steps - 1) & 1], host_out):
-            raise SystemExit("bench: the pipelined end-to-end loop returned a different result than the serial one")
-
-        # ---- keep the same kernels running long enough for the clock sampler to see them under load
-        soak_end = time.perf_counter() + 1.0
-        while time.perf_counter() < soak_end:
-            for _ in range(50):
-                graph.replay()
             stream.synchronize()
-    layer.check_status()
-    if not torch.equal(host_out.view(torch.int16), out.cpu().view(torch.int16)):
-        raise SystemExit("end-to-end result differs from the device-resident result")
+            layer.check_status()
+            session = make_engine_session(args, tokens, local_rank, layer, hidden, out) if args.api == "engine" else None
+            if session is not None:
+                session.prepare(stream.cuda_stream)
+
+                class _EngineGraph:
+                    def replay(self_inner):
+                        session.launch(stream.cuda_stream)
+                graph = _EngineGraph()
+                api_name = "netra_engine_launch (engine runtime ABI, captured CUDA graph)"
+            else:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    layer(hidden, out=out)
+                api_name = "netra_moe_layer_launch (fused-layer ABI, captured CUDA graph)"
+            ms_per_step, step_spread = time_replays(graph.replay, steps, warmup, stream, sync, spread=True)
+            stage_ms = time_stages(layer, hidden, out, steps, warmup, stream, sync)
+            e2e_ms, e2e_serial_ms, e2e_host_api, host_out = time_e2e(graph.replay, hidden, out, hidden_cpu, steps, warmup, stream, sync)
+
+            # ---- keep the same kernels running long enough for the clock sampler to see them under load
+            soak_end = time.perf_counter() + 1.0
+            while time.perf_counter() < soak_end:
+                for _ in range(50):
+                    graph.replay()
+                stream.synchronize()
+        layer.check_status()
+        if not torch.equal(host_out.view(torch.int16), out.cpu().view(torch.int16)):
+            raise SystemExit("end-to-end result differs from the device-resident result")
+
+        # ---- the other named configurations, each an object of its own in the same line
+        if args.extras and world == 1 and tokens == 256 and args.weights == "fp8" and not args.zipf_alpha:
+            cap = max(5, min(steps, 30))
+            w13_t, w2_t = layer.tiled_weights()
+            h8, _, bias8 = synth.make_activations(8192, synth.ZIPF_ALPHA_T8192)
+            pre = RoutedMoELayer(layer._keep[0], w13_t, layer._keep[2], w2_t, layer._keep[4], 8192, bias8.to(dev),
+                                 tiled=layer.tiled, pretiled=layer.tiled)
+            pre.set_partial_format(1)
+            cfg8 = {"zipf_alpha": synth.ZIPF_ALPHA_T8192, "expert_weights": "fp8 e4m3, 128x128 block scales"}
+            extras["prefill_t8192"] = prefill_object("prefill_t8192", pre, h8, cap, warmup, dev, stream, sync, cfg8)
+            pre.set_partial_format(0)      # the decode-contract rows, for comparison
+            with torch.cuda.stream(stream):
+                hd, od = h8.to(dev), torch.empty(8192, 2048, dtype=torch.bfloat16, device=dev)
+                g32 = torch.cuda.CUDAGraph()
+                for _ in range(2):
+                    pre(hd, out=od)
+                stream.synchronize()
+                with torch.cuda.graph(g32, stream=stream):
+                    pre(hd, out=od)
+                ms32, _ = time_replays(g32.replay, cap, warmup, stream, sync)
+            extras["prefill_t8192"]["fp32_rows_tactic"] = {"ms_per_step": ms32, "tokens_per_s": 8192 / (ms32 / 1e3)}
+            pre.close()
+            del pre, g32, hd, od
+            torch.cuda.empty_cache()
+
+            # MXFP4 expert weights of the same shapes (drawn and quantised on the device), expanded at load
+            from netra_kernel_b200.moe import expand_mxfp4
+            p13, s13, p2, s2 = synth.make_expert_weights_device(0, dev, mxfp4=True)
+            m13, m13_s, bad13 = expand_mxfp4(p13, s13)
+            m2, m2_s, bad2 = expand_mxfp4(p2, s2)
+            del p13, s13, p2, s2
+            mx = RoutedMoELayer(layer._keep[0], m13, m13_s, m2, m2_s, 8192, bias8.to(dev))
+            del m13, m2
+            mx.set_partial_format(1)
+            cfgm = {"zipf_alpha": synth.ZIPF_ALPHA_T8192,
+                    "expert_weights": "mxfp4 (E2M1 + E8M0 per 32 along K), expanded at load into exact E4M3 tiles with power-of-two "
+                                      "tile scales (%d inexact elements); the GEMMs stream FP8 bytes" % (bad13 + bad2)}
+            extras["mxfp4_t8192"] = prefill_object("mxfp4_t8192", mx, h8, cap, warmup, dev, stream, sync, cfgm)
+            mx.close()
+            del mx
+            torch.cuda.empty_cache()
+
+            # config 4 on one GPU: the 40-layer stack, 16,384 tokens per step, all 256 experts local
+            hs, _, _ = synth.make_activations(STACK_TOKENS, None, seed=0)
+            stack = make_stack_single(dev, args.stack_layers, STACK_TOKENS, stream)
+            extras["ep_stack"] = stack_object(stack, hs, max(3, min(steps, 8)), 3, dev, stream, sync, 1,
+                                              "single GPU: all 256 routed experts and the shared expert local, no exchange", 0,
+                                              "netra_moe_layer_launch per layer (fused-layer ABI), one captured CUDA graph")
+            for l in stack:
+                l.close()
+            del stack
+            torch.cuda.empty_cache()
 
     if rank != 0:
         if world > 1:
@@ -476,17 +749,13 @@ def run_ours(args) -> None:
 
     inter = layer.intermediates(tokens)
     experts_hit = int((inter["counts"] > 0).sum().item())
-    load = inter["counts"].to(torch.float64).cpu()
-    routing_load = {"pairs_per_expert_mean": float(load.mean()), "max": int(load.max()), "median": float(load.median()),
-                    "min": int(load.min()), "hottest_over_mean": float(load.max() / load.mean()),
-                    "experts_below_128_rows": int((load < 128).sum())}
     peak, peak_kind = measured_hbm_peak()
     gate_up_bytes = (experts_hit + 1) * (2 * 512 * 2048 + 8 * 16 * 4)
     down_bytes = (experts_hit + 1) * (2048 * 512 + 16 * 4 * 4)
     gu_s, dn_s = stage_ms[6] / 1e3, stage_ms[7] / 1e3
     achieved = gate_up_bytes / gu_s / 1e9
     layer_bytes = synth.workload_bytes_decode(tokens, experts_hit)
-    prefill = tokens >= 2048     # tensor-bound regime: report FP8 flops against 2x the measured BF16 GEMM rate
+    prefill = tokens >= 1024     # token-major regime: report FP8 flops against 2x the measured BF16 GEMM rate
     fp8_peak, fp8_kind = measured_fp8_peak()
     gate_up_flops = tokens * 9 * 2 * 2048 * 1024
     layer_flops = synth.workload_flops(tokens)
@@ -494,37 +763,34 @@ def run_ours(args) -> None:
         "metric": METRIC, "value": world * tokens / (ms_per_step / 1e3), "unit": UNIT, "n_gpus": world,
         "steps": steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
-        "config": {"workload": f"{workload_name(tokens)} (1 layer, hidden 2048, 256 routed experts top-8 + shared, inter 512)",
-                   "tokens_per_gpu": tokens, "experts_hit": experts_hit, "routing_load": routing_load,
-                   "parallelism": "single GPU" if world == 1 else f"{world} independent replicas (no collective)",
-                   "zipf_alpha": args.zipf_alpha or 0.0,
-                   "l2": "inputs larger than L2: every step streams %.1f MB of expert weights (L2 is 126 MB)" % (layer_bytes / 1e6),
-                   "expert_weights": ("mxfp4 (E2M1 + E8M0/32) expanded at load to exact E4M3 tiles, %d inexact elements; weight traffic is that of FP8"
-                                      % mxfp4_inexact) if mxfp4_inexact is not None else "fp8 e4m3, 128x128 block scales",
-                   "weights": "row-major slabs" if args.row_major_weights else "tile order (repacked once at load)",
-                   "launch": "CUDA graph replay of the layer's %d kernels" % layer.launches_per_call(tokens),
-                   "api": api_name},
+        "config": headline_config(tokens),
+        "details": {"tokens_per_gpu": tokens, "experts_hit": experts_hit, "routing_load": routing_load(inter["counts"]),
+                    "parallelism": "single GPU" if world == 1 else f"{world} independent replicas (no collective)",
+                    "zipf_alpha": args.zipf_alpha or 0.0,
+                    "l2": "inputs larger than L2: every step streams %.1f MB of expert weights (L2 is 126 MB)" % (layer_bytes / 1e6),
+                    "expert_weights": ("mxfp4 (E2M1 + E8M0/32) expanded at load to exact E4M3 tiles, %d inexact elements; weight traffic is that of FP8"
+                                       % mxfp4_inexact) if mxfp4_inexact is not None else "fp8 e4m3, 128x128 block scales",
+                    "weights": "row-major slabs" if args.row_major_weights else "tile order (repacked once at load)",
+                    "launch": "CUDA graph replay of the layer's %d kernels" % layer.launches_per_call(tokens),
+                    "api": api_name},
         "gpu_launches": steps * layer.launches_per_call(tokens),
         "step_ms_spread": step_spread,
-        "e2e": {"value": world * tokens / (e2e_ms / 1e3), "unit": UNIT, "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": tokens * 2048 * 2, "d2h_bytes_per_step": tokens * 2048 * 2,
-                "how": "every step copies its input from pinned host memory and its result back; the copies run on their own "
-                       "streams with two staging slots, so they overlap the neighbouring steps' compute",
-                "copies_enqueued_with": e2e_host_api, "serial_ms_per_step": e2e_serial_ms},
-        "roofline": ({"bound": "tensor", "kernel": "netra_moe_gate_up_tokmajor_sm100" if tokens >= 1024 else "netra_moe_gate_up_umma_sm100", "achieved": gate_up_flops / gu_s / 1e12,
+        "e2e": e2e_object(world * tokens, tokens, e2e_ms, e2e_serial_ms, e2e_host_api),
+        "roofline": ({"bound": "tensor", "kernel": "netra_moe_gate_up_tokmajor_sm100", "achieved": gate_up_flops / gu_s / 1e12,
                       "peak": fp8_peak, "unit": "TFLOP/s", "frac": gate_up_flops / gu_s / 1e12 / fp8_peak, "peak_source": fp8_kind,
                       "algorithmic_flops": gate_up_flops, "avg_launch_ms": stage_ms[6], "traffic": None}
                      if prefill else
                      {"bound": "hbm", "kernel": "netra_moe_gate_up_umma_sm100", "achieved": achieved, "peak": peak,
                       "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
                       "algorithmic_bytes": gate_up_bytes, "avg_launch_ms": stage_ms[6],
-                      "traffic": GATE_UP_DRAM_TRAFFIC_BYTES if tokens == 256 else None}),
+                      "traffic": gate_up_traffic_bytes() if tokens == 256 else None}),
         "layer_tensor": {"algorithmic_flops": layer_flops, "achieved": layer_flops / (ms_per_step / 1e3) / 1e12, "unit": "TFLOP/s",
                          "frac": layer_flops / (ms_per_step / 1e3) / 1e12 / fp8_peak, "peak": fp8_peak, "peak_source": fp8_kind},
         "kernels_ms": {name: round(ms, 5) for name, ms in zip(layer.STAGES, stage_ms)},
         "down_kernel": {"achieved": down_bytes / dn_s / 1e9, "unit": "GB/s", "frac": down_bytes / dn_s / 1e9 / peak},
         "layer_hbm": {"algorithmic_bytes": layer_bytes, "achieved": layer_bytes / (ms_per_step / 1e3) / 1e9,
                       "unit": "GB/s", "frac": layer_bytes / (ms_per_step / 1e3) / 1e9 / peak},
+        **extras,
         "clocks": clocks.summary(),
     }
     if world == 1 and not args.no_cpu_baseline:
@@ -535,6 +801,65 @@ def run_ours(args) -> None:
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def expert_parallel_extras(args, plan, dev, stream, sync: Sync, router_dev):
+    """N > 1, every rank: (1) one untimed expert-parallel call of layer 0 whose result this rank compares bit for bit
+    with the one-GPU layer run here on the same tokens; (2) the 40-layer stack at 16,384 tokens per step in total
+    (strong scaling: 16,384 / N tokens and 256 / N experts per GPU).  Returns (parity object, stack object), the sums
+    and maxima over ranks already taken."""
+    import torch
+    import torch.distributed as dist
+    from netra_kernel_b200 import synth
+    from netra_kernel_b200.ep import PeerExpertParallelLayer, shard_expert_weights
+    from netra_kernel_b200.moe import RoutedMoELayer
+    world, rank = plan.world, plan.rank
+    t_local = STACK_TOKENS // world
+    hs, _, _ = synth.make_activations(t_local, None, seed=100 + rank)
+    hidden = hs.to(dev)
+    layers, full0 = [], None
+    with torch.cuda.stream(stream):
+        for l in range(args.stack_layers):
+            full = synth.make_expert_weights_device(l, dev)
+            local = tuple(t.contiguous() for t in shard_expert_weights(full, plan))
+            if l == 0:
+                full0 = full
+            del full
+            layers.append(PeerExpertParallelLayer(plan, router_dev, *local, max_local_tokens=t_local, wait_timeout_s=10.0,
+                                                  share_with=layers[0] if layers else None))
+            del local
+        stream.synchronize()
+        dist.barrier()
+        # ---- parity: layer 0 across the GPUs against layer 0 on this GPU alone
+        got = layers[0](hidden).clone()
+        stream.synchronize()
+        layers[0].check_status()
+        dist.barrier()
+        single = RoutedMoELayer(router_dev, *full0, t_local)
+        del full0
+        want = single(hidden)
+        stream.synchronize()
+        single.check_status()
+        same = torch.equal(got.view(torch.int16), want.view(torch.int16))
+        counts = single.intermediates(t_local)["counts"].clone()
+        single.close()
+        del single, want
+        torch.cuda.empty_cache()
+    mismatched_ranks = sync.sum_int(0 if same else 1)
+    if mismatched_ranks:
+        raise SystemExit(f"expert-parallel parity: {mismatched_ranks} of {world} ranks differ from the one-GPU layer")
+    parity = {"vs": "single-GPU layer (netra_moe_layer_launch) run by every rank on its own tokens with all 257 slabs of layer 0",
+              "bit_exact": True, "rows": STACK_TOKENS, "rows_per_rank": t_local, "ranks": world, "layer": 0}
+    own = plan.local_expert_range()
+    remote_pairs = int(counts.sum().item() - counts[own.start:own.stop].sum().item())
+    remote_pairs = sync.sum_int(remote_pairs) // world          # mean over ranks
+    stack = stack_object(layers, hs, max(3, min(args.steps, 8)), 3, dev, stream, sync, world,
+                         f"ep{world}: {plan.experts_per_rank} routed experts per GPU, shared expert and router replicated; rows "
+                         "pushed into the owners' windows over NVLink, FP32 rows returned by the down epilogue",
+                         remote_pairs, "netra_ep_layer_launch per layer, one captured CUDA graph")
+    for l in layers:
+        l.close()
+    return parity, stack
 
 
 def run_expert_parallel(args) -> None:
@@ -679,6 +1004,13 @@ def run_expert_parallel(args) -> None:
             stage_us = {name: round(sum(evs[it][st].elapsed_time(evs[it][st + 1]) for it in range(reps)) / reps * 1e3, 1)
                         for st, name in enumerate(names)}
     layer.check_status()
+    sync = Sync(dev, world)
+    parity = stack = None
+    if args.extras and args.ep_exchange == "peer":
+        layer.close()
+        del layer, graph, local
+        torch.cuda.empty_cache()
+        parity, stack = expert_parallel_extras(args, plan, dev, stream, sync, router_dev)
     if rank == 0:
         peak, peak_kind = measured_hbm_peak()
         slabs = plan.experts_per_rank + 1
@@ -688,8 +1020,8 @@ def run_expert_parallel(args) -> None:
             "metric": METRIC, "value": world * tokens / (ms_per_step / 1e3), "unit": UNIT, "n_gpus": world, "steps": steps,
             "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "fp8_e4m3", "data": "synthetic",
-            "config": {"workload": f"{workload_name(tokens)} per GPU (1 layer, hidden 2048, 256 routed experts top-8 + shared, inter 512)",
-                       "tokens_per_gpu": tokens, "tokens_total": world * tokens,
+            "config": headline_config(tokens),
+            "details": {"tokens_per_gpu": tokens, "tokens_total": world * tokens,
                        "parallelism": f"ep{world}: {plan.experts_per_rank} routed experts per GPU, shared expert and router replicated, "
                                       "rows dispatched to the owners and returned",
                        "l2": "each step re-reads this GPU's expert slabs (%.1f MB); below the 126 MB L2 at 8 GPUs, so the step is "
@@ -715,6 +1047,9 @@ def run_expert_parallel(args) -> None:
                          "algorithmic_bytes": block_bytes, "avg_launch_ms": block_ms, "traffic": None},
             "clocks": clocks.summary(),
         }
+        if parity is not None:
+            line["parity"] = parity
+            line["ep_stack"] = stack
         print(json.dumps(line), flush=True)
     dist.barrier()
     dist.destroy_process_group()
@@ -740,6 +1075,12 @@ def main() -> None:
                          "fixed slots per rank pair / exact split sizes")
     ap.add_argument("--api", default="engine", choices=["engine", "layer"],
                     help="entry point timed for value/e2e: the engine runtime ABI (default) or the fused-layer call")
+    ap.add_argument("--partials", default="f32", choices=["f32", "f16"],
+                    help="rows between the down projection and the combine where the token-major kernels run: FP32 (decode "
+                         "contract) or FP16 partials (the reference's prefill contract)")
+    ap.add_argument("--no-extras", dest="extras", action="store_false",
+                    help="only the headline workload: skip the prefill, MXFP4 and 40-layer stack objects")
+    ap.add_argument("--stack-layers", type=int, default=STACK_LAYERS, help="layers of the stack object (40 is the named configuration)")
     ap.add_argument("--profile-only", type=int, default=0, metavar="CALLS",
                     help="run CALLS plain layer calls and exit (the command captured under ncu)")
     args = ap.parse_args()

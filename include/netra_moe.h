@@ -93,7 +93,10 @@ typedef struct netra_moe_workspace_layout {
   uint64_t h_fp8;         /* [P + tokens, 512] e4m3 */
   uint64_t h_scale;       /* [P + tokens, 4] f32 */
   uint64_t down_f32;      /* [P + tokens, 2048] f32 */
-  uint64_t status;        /* [4] u32 device status words (0 = ok) */
+  uint64_t status;        /* [4] u32 device status words (0 = ok): 0 gate_up, 1 down, 2 tensor-core router */
+  uint64_t logits_f32;    /* [tokens, 256] f32: tensor-core router output before the exact rounding (calls above 1024 rows) */
+  uint64_t wnorm;         /* [256] f32: Euclidean norms of the router rows (upper bounds) */
+  uint64_t router_stats;  /* [4] u32: word 0 counts the logits recomputed in FP64 since the layer was created */
 } netra_moe_workspace_layout_t;
 
 int netra_moe_workspace_layout_query(uint32_t tokens, netra_moe_workspace_layout_t* output);
@@ -278,8 +281,8 @@ uint32_t netra_ep_layer_launch_count(const netra_ep_layer_t* layer, uint32_t tok
 int netra_ep_layer_status(netra_ep_layer_t* layer, uint32_t status_out[4]);
 int netra_ep_layer_destroy(netra_ep_layer_t* layer);
 
-/* Block size and dynamic shared memory of the grouped GEMM kernels (which: 0 gate_up, 1 down, 2 and 3 their
- * token-major forms), so
+/* Block size and dynamic shared memory of the tensor-core kernels (which: 0 gate_up, 1 down, 2 and 3 their
+ * token-major forms, 4 token-major down with FP16 rows, 5 tensor-core router), so
  * that an engine manifest written ahead of time can be checked against the built library. */
 int netra_moe_kernel_launch_info(uint32_t which, uint32_t* block_threads, uint32_t* dynamic_smem_bytes);
 
@@ -288,6 +291,22 @@ int netra_moe_kernel_launch_info(uint32_t which, uint32_t* block_threads, uint32
  * mode 0 (default) picks by the token count of the call, mode 1 always uses the swap-AB kernels.  Both
  * forms produce identical results. */
 int netra_moe_layer_set_gemm_mode(netra_moe_layer_t* layer, uint32_t mode);
+
+/* Router of calls above 1024 rows.  mode 0 (default): BF16 tensor-core pass with FP32 accumulation, then an FP64
+ * recomputation of exactly those logits whose BF16 rounding the FP32 value cannot decide - the emitted logits are
+ * the correctly rounded exact dot products either way.  mode 1: every logit on the FP64 tensor cores (the form
+ * used up to 1024 rows), several times slower on large calls. */
+int netra_moe_layer_set_router_mode(netra_moe_layer_t* layer, uint32_t mode);
+/* Copies the router statistics words (see netra_moe_workspace_layout_t.router_stats) to the host (synchronises). */
+int netra_moe_layer_router_stats(netra_moe_layer_t* layer, uint32_t stats_out[4]);
+
+/* Format of the down projection's rows between the grouped GEMM and the combine, for calls served by the
+ * token-major kernels.  format 0 (default): FP32 rows (the decode contract,
+ * kernels/gfx950/templates/moe/decode/down_reduce_mfma_2wave.inc:73-217).  format 1: FP16 partial rows, half the
+ * bytes, the reference's prefill contract (kernels/gfx950/templates/moe/prefill/fused_splitk2/down_partial.inc:435-458,
+ * route_reduce_splitk2_f16.inc:107-118: f32(partial) * weight, slot ascending, one BF16 rounding).  Calls served
+ * by the swap-AB kernels keep FP32 rows under either setting. */
+int netra_moe_layer_set_partial_format(netra_moe_layer_t* layer, uint32_t format);
 
 /* Copies the four device status words to the host (synchronises the device). */
 int netra_moe_layer_status(netra_moe_layer_t* layer, uint32_t status_out[4]);
@@ -301,8 +320,9 @@ const char* netra_moe_last_error(void);
  * callers that cannot allocate device memory (a process whose memory belongs to one framework
  * allocator, a plugin barred from driver allocations after start-up, a step inside stream
  * capture): the scratch table lives in a fixed 128 KiB device array inside the library, so only
- * inputs and outputs are passed.  topk_ids_i32 is [rows, 9] (slot 8 ignored); outputs are
- * perm [rows*8], inv_perm [rows*8], counts [256], offsets [258], identical to the fused layer's.
+ * inputs and outputs are passed.  topk_ids_i32 is [rows, 9] (slot 8 ignored; ids outside 0..255
+ * are treated as the nearest valid expert, 0 or 255, so that no id can index out of range); outputs
+ * are perm [rows*8], inv_perm [rows*8], counts [256], offsets [258], identical to the fused layer's.
  * rows must be 1..16384 (larger is refused).  The first call on a device resolves the array's
  * address and should be made outside stream capture.  All calls on a device share the array:
  * calls that overlap on the GPU race and must be serialised by the caller. */

@@ -17,7 +17,8 @@ class WorkspaceLayout(ctypes.Structure):
     _fields_ = [("struct_size", c_u32), ("tokens", c_u32), ("total_bytes", c_u64)] + [
         (name, c_u64) for name in (
             "logits_bf16", "topk_ids", "topk_weights", "perm", "inv_perm", "counts", "offsets",
-            "seg_hist", "a_fp8", "a_scale", "h_fp8", "h_scale", "down_f32", "status")]
+            "seg_hist", "a_fp8", "a_scale", "h_fp8", "h_scale", "down_f32", "status", "logits_f32", "wnorm",
+            "router_stats")]
 
 
 class LayerDesc(ctypes.Structure):
@@ -82,6 +83,9 @@ SIGNATURES = {
     "netra_ep_layer_destroy": (c_int, [c_void_p]),
     "netra_moe_kernel_launch_info": (c_int, [c_u32, ctypes.POINTER(c_u32), ctypes.POINTER(c_u32)]),
     "netra_moe_layer_set_gemm_mode": (c_int, [c_void_p, c_u32]),
+    "netra_moe_layer_set_router_mode": (c_int, [c_void_p, c_u32]),
+    "netra_moe_layer_set_partial_format": (c_int, [c_void_p, c_u32]),
+    "netra_moe_layer_router_stats": (c_int, [c_void_p, ctypes.POINTER(c_u32 * 4)]),
     "netra_moe_layer_status": (c_int, [c_void_p, ctypes.POINTER(c_u32 * 4)]),
     "netra_moe_layer_launch_count": (c_u32, [c_void_p, c_u32]),
     "netra_moe_layer_destroy": (c_int, [c_void_p]),

@@ -4,6 +4,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <mutex>
 #include <new>
 
 #include "../../include/netra_moe.h"
@@ -14,6 +15,7 @@
 #include "route_kernels.cu"
 #include "umma_kernels.cu"
 #include "umma_tokmajor.cu"
+#include "router_umma.cu"
 #include "ep_kernels.cu"
 #include "mxfp4_kernels.cu"
 
@@ -72,11 +74,28 @@ int encode_u8_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row
   return 0;
 }
 
-bool g_umma_ready = false;
-bool g_tokmajor_ok = false;   // the token-major kernels were built with the register allocation they assume
+// Per-device set-up of the tensor-core kernels: the opt-in to more than 48 KiB of dynamic shared memory is a
+// per-device function attribute, so a process that drives several GPUs runs this once for each of them.
+constexpr int kMaxDevices = 64;
+std::mutex g_setup_mutex;
+bool g_umma_ready[kMaxDevices] = {};
+bool g_tokmajor_ok[kMaxDevices] = {};   // the token-major kernels were built with the register allocation they assume
+
+int current_device_index(int* device) {
+  cudaError_t e = cudaGetDevice(device);
+  if (e != cudaSuccess) return fail_cuda("cudaGetDevice", e);
+  if (*device < 0 || *device >= kMaxDevices) return fail("device index out of range (0..63)");
+  return 0;
+}
 
 int umma_setup() {
-  if (g_umma_ready) return 0;
+  int device = 0;
+  if (int rc = current_device_index(&device)) return rc;
+  std::lock_guard<std::mutex> lock(g_setup_mutex);
+  if (g_umma_ready[device]) return 0;
+  int major = 0;
+  cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+  if (major != 10) return fail("this library targets sm_100a (compute capability 10.x)");
   cudaError_t e = cudaFuncSetAttribute(netra_moe_gate_up_umma_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        gate_up_smem_bytes());
   if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(gate_up)", e);
@@ -86,23 +105,28 @@ int umma_setup() {
   if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(gate_up_tokmajor)", e);
   e = cudaFuncSetAttribute(netra_moe_down_tokmajor_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, down_tokmajor_smem_bytes());
   if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(down_tokmajor)", e);
+  e = cudaFuncSetAttribute(netra_moe_down_tokmajor_f16_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, down_tokmajor_f16_smem_bytes());
+  if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(down_tokmajor_f16)", e);
+  e = cudaFuncSetAttribute(netra_router_logits_f32_umma_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, router_umma_smem_bytes());
+  if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(router_umma)", e);
   {
     // the register re-balancing inside these kernels is only deadlock-free for the launch allocation it was written for
-    cudaFuncAttributes a0, a1;
+    cudaFuncAttributes a0, a1, a2;
     e = cudaFuncGetAttributes(&a0, netra_moe_gate_up_tokmajor_sm100);
     if (e == cudaSuccess) e = cudaFuncGetAttributes(&a1, netra_moe_down_tokmajor_sm100);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a2, netra_moe_down_tokmajor_f16_sm100);
     if (e != cudaSuccess) return fail_cuda("cudaFuncGetAttributes(tokmajor)", e);
-    g_tokmajor_ok = a0.numRegs == kTmRegsLaunch && a1.numRegs == kTmRegsLaunch;
+    g_tokmajor_ok[device] = a0.numRegs == kTmRegsLaunch && a1.numRegs == kTmRegsLaunch && a2.numRegs == kTmRegsLaunch;
   }
-  g_umma_ready = true;
+  g_umma_ready[device] = true;
   return 0;
 }
 
 // The token-major GEMMs pay off once an expert's rows fill a good part of a 128-row tile: from an average
 // of 32 rows per routed expert (1,024 tokens on one GPU) the layer switches to them.
 constexpr uint32_t kTokMajorMinRowsPerExpert = 32;
-bool use_tokmajor(uint64_t pairs, uint32_t routed_experts) {
-  return g_tokmajor_ok && pairs >= (uint64_t)kTokMajorMinRowsPerExpert * routed_experts;
+bool use_tokmajor(int device, uint64_t pairs, uint32_t routed_experts) {
+  return g_tokmajor_ok[device] && pairs >= (uint64_t)kTokMajorMinRowsPerExpert * routed_experts;
 }
 
 }  // namespace
@@ -110,10 +134,13 @@ bool use_tokmajor(uint64_t pairs, uint32_t routed_experts) {
 struct netra_moe_layer {
   netra_moe_layer_desc_t desc;
   netra_moe_workspace_layout_t lay;
-  CUtensorMap tm_w13, tm_w2, tm_a32, tm_a64, tm_a128, tm_h32, tm_h64, tm_h128;
+  CUtensorMap tm_w13, tm_w2, tm_a32, tm_a64, tm_a128, tm_h32, tm_h64, tm_h128, tm_router;
   int sm_count;
+  int device;
   uint32_t launches;
-  uint32_t gemm_mode;   // 0: pick the GEMM form by size, 1: always the swap-AB (decode) kernels
+  uint32_t gemm_mode;     // 0: pick the GEMM form by size, 1: always the swap-AB (decode) kernels
+  uint32_t router_mode;   // 0: pick the router by size, 1: always the FP64 tensor-core router
+  uint32_t partial_f16;   // 1: the token-major down projection writes FP16 partial rows (prefill contract)
 };
 
 extern "C" {
@@ -194,6 +221,9 @@ int netra_moe_workspace_layout_query(uint32_t tokens, netra_moe_workspace_layout
   out->h_scale = take((rows + 128) * kInterBlocks * 4);
   out->down_f32 = take(rows * kHidden * 4);
   out->status = take(16);
+  out->logits_f32 = take(t * kRouted * 4);
+  out->wnorm = take(kRouted * 4);
+  out->router_stats = take(16);
   out->total_bytes = o;
   return 0;
 }
@@ -219,8 +249,11 @@ int netra_moe_layer_create(const netra_moe_layer_desc_t* desc, netra_moe_layer_t
   layer->desc = *desc;
   layer->lay = lay;
   layer->sm_count = sms;
+  layer->device = device;
   layer->launches = 9;  // stages of launch_stage()
   layer->gemm_mode = 0;
+  layer->router_mode = 0;
+  layer->partial_f16 = 0;
   const uint64_t slabs = desc->num_expert_slabs ? desc->num_expert_slabs : (uint64_t)(kRouted + 1);
   if (slabs > (uint64_t)(kRouted + 1)) { delete layer; return fail("layer_create: at most 257 expert slabs"); }
   uint8_t* ws = (uint8_t*)desc->workspace;
@@ -233,6 +266,7 @@ int netra_moe_layer_create(const netra_moe_layer_desc_t* desc, netra_moe_layer_t
     rc = rc ? rc : encode_u8_2d(&layer->tm_w13, desc->w13_fp8, slabs * 2 * kInter, kHidden, 128);
     rc = rc ? rc : encode_u8_2d(&layer->tm_w2, desc->w2_fp8, slabs * kHidden, kInter, 128);
   }
+  rc = rc ? rc : encode_u8_2d(&layer->tm_router, desc->router_weight_bf16, kRouted, kHidden * 2, 128);
   rc = rc ? rc : encode_u8_2d(&layer->tm_a32, ws + lay.a_fp8, rows, kHidden, 32);
   rc = rc ? rc : encode_u8_2d(&layer->tm_a64, ws + lay.a_fp8, rows, kHidden, 64);
   rc = rc ? rc : encode_u8_2d(&layer->tm_a128, ws + lay.a_fp8, rows, kHidden, 128);
@@ -241,6 +275,7 @@ int netra_moe_layer_create(const netra_moe_layer_desc_t* desc, netra_moe_layer_t
   rc = rc ? rc : encode_u8_2d(&layer->tm_h128, ws + lay.h_fp8, rows, kInter, 128);
   if (rc == 0) {
     e = cudaMemset(ws + lay.status, 0, 16);
+    if (e == cudaSuccess) e = cudaMemset(ws + lay.router_stats, 0, 16);
     if (e != cudaSuccess) rc = fail_cuda("cudaMemset(status)", e);
   }
   if (rc != 0) { delete layer; return rc; }
@@ -257,12 +292,21 @@ uint32_t netra_moe_layer_launch_count(const netra_moe_layer_t* layer, uint32_t t
 
 namespace {
 constexpr uint32_t kStageCount = 9;
-constexpr uint32_t kRouterK8MaxRows = 1024;   // up to here the router runs with eight K-slices per tile
+constexpr uint32_t kRouterK8MaxRows = 1024;   // up to here the router runs on the FP64 tensor cores with eight K-slices per tile
+
+// Calls above kRouterK8MaxRows rows take the BF16 tensor-core router (FP32 approximations, then FP64 only where
+// the rounding is undecided) unless the layer was told to keep the FP64 router.
+bool use_umma_router(const netra_moe_layer* layer, uint32_t tokens) {
+  return tokens > kRouterK8MaxRows && layer->router_mode == 0;
+}
+bool use_f16_partials(const netra_moe_layer* layer, uint32_t pairs) {
+  return layer->partial_f16 != 0 && layer->gemm_mode != 1 && use_tokmajor(layer->device, pairs, kRouted);
+}
 
 // One launch of the layer's fixed sequence (same idea as the reference's per-operation launch,
-// runtime/gfx950/engine/netra_engine.h:90-92).
-void launch_stage(netra_moe_layer* layer, uint32_t stage, const void* hidden, const float* shared_w, void* out,
-                  uint32_t tokens, cudaStream_t stream) {
+// runtime/gfx950/engine/netra_engine.h:90-92).  Returns 0 or the code of a failed host-side step.
+int launch_stage(netra_moe_layer* layer, uint32_t stage, const void* hidden, const float* shared_w, void* out,
+                 uint32_t tokens, cudaStream_t stream) {
   const netra_moe_workspace_layout_t& L = layer->lay;
   uint8_t* ws = (uint8_t*)layer->desc.workspace;
   uint16_t* logits = (uint16_t*)(ws + L.logits_bf16);
@@ -279,20 +323,38 @@ void launch_stage(netra_moe_layer* layer, uint32_t stage, const void* hidden, co
   float* h_scale = (float*)(ws + L.h_scale);
   float* down = (float*)(ws + L.down_f32);
   uint32_t* status = (uint32_t*)(ws + L.status);
+  float* logits_f32 = (float*)(ws + L.logits_f32);
+  float* wnorm = (float*)(ws + L.wnorm);
+  uint32_t* router_stats = (uint32_t*)(ws + L.router_stats);
+  const uint16_t* router_w = (const uint16_t*)layer->desc.router_weight_bf16;
   const uint32_t pairs = tokens * kTopK;
   const uint32_t nseg = (pairs + kSortSegment - 1) / kSortSegment;
+  const bool tokmajor = use_tokmajor(layer->device, pairs, kRouted) && layer->gemm_mode != 1;
   switch (stage) {
     case 0:
-      if (tokens <= kRouterK8MaxRows)
+      if (use_umma_router(layer, tokens)) {
+        // the token rows are the caller's buffer of this call: their tensor map is encoded here (host work only)
+        CUtensorMap tm_hidden;
+        if (int rc = encode_u8_2d(&tm_hidden, hidden, tokens, kHidden * 2, 128)) return rc;
+        const uint32_t tiles = 2 * ((tokens + kRtTile - 1) / kRtTile);
+        netra_router_logits_f32_umma_sm100<<<tiles + kRtNormCtas, kRtThreads, router_umma_smem_bytes(), stream>>>(
+            tm_hidden, layer->tm_router, logits_f32, wnorm, router_w, tokens, status + 2);
+      } else if (tokens <= kRouterK8MaxRows) {
         netra_router_logits_bf16_k8_sm100<<<dim3((tokens + 15) / 16, 8), 512, 0, stream>>>(
-            logits, (const uint16_t*)hidden, (const uint16_t*)layer->desc.router_weight_bf16, tokens);
-      else
+            logits, (const uint16_t*)hidden, router_w, tokens);
+      } else {
         netra_router_logits_bf16_sm100<<<dim3((tokens + 15) / 16, 8), 256, 0, stream>>>(
-            logits, (const uint16_t*)hidden, (const uint16_t*)layer->desc.router_weight_bf16, tokens);
+            logits, (const uint16_t*)hidden, router_w, tokens);
+      }
       break;
     case 1:
-      netra_moe_topk_quant_sm100<<<(tokens + 3) / 4, 128, 0, stream>>>(
-          ids9, w9, a_fp8, a_scale, logits, layer->desc.router_bias_f32, shared_w, (const uint16_t*)hidden, tokens, pairs);
+      if (use_umma_router(layer, tokens))
+        netra_moe_topk_quant_fix_sm100<<<(tokens + 3) / 4, 128, 0, stream>>>(
+            ids9, w9, a_fp8, a_scale, logits, logits_f32, wnorm, router_w, layer->desc.router_bias_f32, shared_w,
+            (const uint16_t*)hidden, router_stats, tokens, pairs);
+      else
+        netra_moe_topk_quant_sm100<<<(tokens + 3) / 4, 128, 0, stream>>>(
+            ids9, w9, a_fp8, a_scale, logits, layer->desc.router_bias_f32, shared_w, (const uint16_t*)hidden, tokens, pairs);
       break;
     case 2:
       if (tokens <= (uint32_t)kSortSmallMaxRows)   // one block does the whole sort; stages 3 and 4 launch nothing
@@ -308,7 +370,7 @@ void launch_stage(netra_moe_layer* layer, uint32_t stage, const void* hidden, co
       break;
     case 5: netra_moe_gather_rows_sm100<<<(pairs + 7) / 8, 256, 0, stream>>>(a_fp8, a_scale, perm, tokens); break;
     case 6:
-      if (use_tokmajor(pairs, kRouted) && layer->gemm_mode != 1)
+      if (tokmajor)
         netra_moe_gate_up_tokmajor_sm100<<<layer->sm_count, kTmThreads, gate_up_tokmajor_smem_bytes(), stream>>>(
             layer->tm_w13, layer->tm_a128, a_scale, layer->desc.w13_scale_f32, offsets, h_fp8, h_scale, kRouted + 1,
             layer->desc.weights_tiled, status);
@@ -318,7 +380,11 @@ void launch_stage(netra_moe_layer* layer, uint32_t stage, const void* hidden, co
             h_scale, kRouted + 1, layer->desc.weights_tiled, status);
       break;
     case 7:
-      if (use_tokmajor(pairs, kRouted) && layer->gemm_mode != 1)
+      if (tokmajor && layer->partial_f16)
+        netra_moe_down_tokmajor_f16_sm100<<<layer->sm_count, kTmThreads, down_tokmajor_f16_smem_bytes(), stream>>>(
+            layer->tm_w2, layer->tm_h128, h_scale, layer->desc.w2_scale_f32, offsets, down, kRouted + 1,
+            layer->desc.weights_tiled, status + 1);
+      else if (tokmajor)
         netra_moe_down_tokmajor_sm100<<<layer->sm_count, kTmThreads, down_tokmajor_smem_bytes(), stream>>>(
             layer->tm_w2, layer->tm_h128, h_scale, layer->desc.w2_scale_f32, offsets, down, kRouted + 1,
             layer->desc.weights_tiled, status + 1);
@@ -327,8 +393,14 @@ void launch_stage(netra_moe_layer* layer, uint32_t stage, const void* hidden, co
             layer->tm_w2, layer->tm_h32, layer->tm_h64, layer->tm_h128, h_scale, layer->desc.w2_scale_f32, offsets, down,
             kRouted + 1, layer->desc.weights_tiled, status + 1);
       break;
-    default: netra_moe_combine_sm100<<<tokens, 256, 0, stream>>>((uint16_t*)out, down, w9, inv_perm, tokens); break;
+    default:
+      if (use_f16_partials(layer, pairs))
+        netra_moe_combine_f16_sm100<<<tokens, 256, 0, stream>>>((uint16_t*)out, (const __half*)down, w9, inv_perm, tokens);
+      else
+        netra_moe_combine_sm100<<<tokens, 256, 0, stream>>>((uint16_t*)out, down, w9, inv_perm, tokens);
+      break;
   }
+  return 0;
 }
 }  // namespace
 
@@ -338,7 +410,8 @@ int netra_moe_layer_launch(netra_moe_layer_t* layer, const void* hidden, const f
                            cudaStream_t stream) {
   if (layer == nullptr || hidden == nullptr || out == nullptr) return fail("layer_launch: null pointer");
   if (tokens == 0 || tokens > layer->desc.max_tokens) return fail("layer_launch: tokens exceed the bound capacity");
-  for (uint32_t stage = 0; stage < kStageCount; ++stage) launch_stage(layer, stage, hidden, shared_w, out, tokens, stream);
+  for (uint32_t stage = 0; stage < kStageCount; ++stage)
+    if (int rc = launch_stage(layer, stage, hidden, shared_w, out, tokens, stream)) return rc;
   return check_launch("layer launch");
 }
 
@@ -352,7 +425,8 @@ int netra_moe_layer_launch_with_topk(netra_moe_layer_t* layer, const void* hidde
   netra_moe_import_topk_quant_sm100<<<(tokens + 3) / 4, 128, 0, stream>>>(
       (int32_t*)(ws + L.topk_ids), (float*)(ws + L.topk_weights), ws + L.a_fp8, (float*)(ws + L.a_scale), topk_ids, topk_weights,
       shared_w, (const uint16_t*)hidden, tokens, tokens * kTopK);
-  for (uint32_t stage = 2; stage < kStageCount; ++stage) launch_stage(layer, stage, hidden, shared_w, out, tokens, stream);
+  for (uint32_t stage = 2; stage < kStageCount; ++stage)
+    if (int rc = launch_stage(layer, stage, hidden, shared_w, out, tokens, stream)) return rc;
   return check_launch("layer launch with external top-k");
 }
 
@@ -361,7 +435,7 @@ int netra_moe_layer_launch_stage(netra_moe_layer_t* layer, uint32_t stage, const
   if (layer == nullptr || hidden == nullptr || out == nullptr) return fail("layer_launch_stage: null pointer");
   if (tokens == 0 || tokens > layer->desc.max_tokens) return fail("layer_launch_stage: tokens exceed the bound capacity");
   if (stage >= kStageCount) return fail("layer_launch_stage: stage out of range");
-  launch_stage(layer, stage, hidden, shared_w, out, tokens, stream);
+  if (int rc = launch_stage(layer, stage, hidden, shared_w, out, tokens, stream)) return rc;
   return check_launch("layer stage launch");
 }
 
@@ -492,9 +566,10 @@ int netra_ep_unpack_rows_launch(float* down, const float* back_slots, const int3
 }
 
 int netra_moe_kernel_launch_info(uint32_t which, uint32_t* block_threads, uint32_t* dynamic_smem_bytes) {
-  if (!block_threads || !dynamic_smem_bytes || which > 3) return fail("kernel_launch_info: bad argument");
-  *block_threads = which < 2 ? kGemmThreads : kTmThreads;
-  const int bytes[4] = {gate_up_smem_bytes(), down_smem_bytes(), gate_up_tokmajor_smem_bytes(), down_tokmajor_smem_bytes()};
+  if (!block_threads || !dynamic_smem_bytes || which > 5) return fail("kernel_launch_info: bad argument");
+  *block_threads = which < 2 ? kGemmThreads : which == 5 ? kRtThreads : kTmThreads;
+  const int bytes[6] = {gate_up_smem_bytes(), down_smem_bytes(), gate_up_tokmajor_smem_bytes(), down_tokmajor_smem_bytes(),
+                        down_tokmajor_f16_smem_bytes(), router_umma_smem_bytes()};
   *dynamic_smem_bytes = (uint32_t)bytes[which];
   return 0;
 }
@@ -503,6 +578,24 @@ int netra_moe_layer_set_gemm_mode(netra_moe_layer_t* layer, uint32_t mode) {
   if (layer == nullptr || mode > 1) return fail("layer_set_gemm_mode: null layer or unknown mode");
   layer->gemm_mode = mode;
   return 0;
+}
+
+int netra_moe_layer_set_router_mode(netra_moe_layer_t* layer, uint32_t mode) {
+  if (layer == nullptr || mode > 1) return fail("layer_set_router_mode: null layer or unknown mode");
+  layer->router_mode = mode;
+  return 0;
+}
+
+int netra_moe_layer_set_partial_format(netra_moe_layer_t* layer, uint32_t format) {
+  if (layer == nullptr || format > 1) return fail("layer_set_partial_format: null layer or unknown format");
+  layer->partial_f16 = format;
+  return 0;
+}
+
+int netra_moe_layer_router_stats(netra_moe_layer_t* layer, uint32_t stats_out[4]) {
+  if (layer == nullptr || stats_out == nullptr) return fail("layer_router_stats: null pointer");
+  cudaError_t e = cudaMemcpy(stats_out, (uint8_t*)layer->desc.workspace + layer->lay.router_stats, 16, cudaMemcpyDeviceToHost);
+  return e == cudaSuccess ? 0 : fail_cuda("cudaMemcpy(router_stats)", e);
 }
 
 int netra_moe_layer_status(netra_moe_layer_t* layer, uint32_t status_out[4]) {
@@ -523,9 +616,3 @@ int netra_moe_layer_destroy(netra_moe_layer_t* layer) {
 
 // Entry point with library-owned scratch (needs fail(), fail_cuda(), check_launch() from above).
 #include "static_scratch_sort.cu"
-
-#ifdef NETRA_TRACE
-extern "C" int netra_debug_read_trace(long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, netra::g_trace, sizeof(long long) * 8 * 256);
-}
-#endif

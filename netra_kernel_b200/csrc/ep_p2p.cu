@@ -395,17 +395,18 @@ int ep_check_shape(uint32_t world, uint32_t max_tokens, uint32_t capacity) {
   return 0;
 }
 
-void ep_launch_stage(netra_ep_layer* L, uint32_t stage, const void* hidden, const float* shared_w, void* out, uint32_t tokens,
-                     cudaStream_t stream) {
+int ep_launch_stage(netra_ep_layer* L, uint32_t stage, const void* hidden, const float* shared_w, void* out, uint32_t tokens,
+                    cudaStream_t stream) {
   const netra_ep_layer_desc_t& d = L->desc;
   const netra_moe_workspace_layout_t& R = L->route->lay;
   uint8_t* ws = (uint8_t*)L->route->desc.workspace;
   const uint32_t pairs = tokens * kTopK;
   switch (stage) {
-    case 0: launch_stage(L->route, 0, hidden, shared_w, out, tokens, stream); break;
-    case 1: launch_stage(L->route, 1, hidden, shared_w, out, tokens, stream); break;
+    case 0: return launch_stage(L->route, 0, hidden, shared_w, out, tokens, stream);
+    case 1: return launch_stage(L->route, 1, hidden, shared_w, out, tokens, stream);
     case 2:
-      for (uint32_t s = 2; s <= 4; ++s) launch_stage(L->route, s, hidden, shared_w, out, tokens, stream);
+      for (uint32_t s = 2; s <= 4; ++s)
+        if (int rc = launch_stage(L->route, s, hidden, shared_w, out, tokens, stream)) return rc;
       break;
     case 3:
       netra_ep_publish_counts_sm100<<<1, 288, 0, stream>>>(L->peers, L->wl, L->tab, (const int32_t*)(ws + R.counts), tokens, d.world, d.rank);
@@ -427,7 +428,7 @@ void ep_launch_stage(netra_ep_layer* L, uint32_t stage, const void* hidden, cons
     }
     case 7:
       // the pairs of all ranks (equal token counts assumed) spread over 256 routed experts decide the GEMM form
-      if (L->tokmajor_ok && use_tokmajor((uint64_t)d.world * pairs, kRouted))
+      if (L->tokmajor_ok && use_tokmajor(L->route->device, (uint64_t)d.world * pairs, kRouted))
         netra_moe_gate_up_tokmajor_sm100<<<L->sm_count, kTmThreads, gate_up_tokmajor_smem_bytes(), stream>>>(
             L->tm_w13, L->tm_a128, (const float*)(L->window + L->wl.blk_as), d.w13_scale_f32, L->tab->offsets, L->blk_h, L->blk_hs,
             L->e_l + 1, d.weights_tiled, L->tab->status);
@@ -441,7 +442,7 @@ void ep_launch_stage(netra_ep_layer* L, uint32_t stage, const void* hidden, cons
       // contiguous bytes of one row per warp instruction, while a token-major thread owns a whole row and a warp
       // instruction scatters 32-byte pieces over 32 rows - over NVLink that took three times as long (8 GPUs,
       // 64 rows per expert: 77 us against 25 us of GEMM time).
-      if (L->tokmajor_ok && d.world == 1 && use_tokmajor((uint64_t)d.world * pairs, kRouted))
+      if (L->tokmajor_ok && d.world == 1 && use_tokmajor(L->route->device, (uint64_t)d.world * pairs, kRouted))
         netra_ep_down_return_tokmajor_sm100<<<L->sm_count, kTmThreads, down_tokmajor_smem_bytes(), stream>>>(
             L->tm_w2, L->tm_h128, L->blk_hs, d.w2_scale_f32, L->tab->offsets, L->row_ptr, L->e_l + 1, d.weights_tiled,
             L->tab->status + 1, L->peers, L->wl, L->tab, d.world, d.rank);
@@ -456,6 +457,7 @@ void ep_launch_stage(netra_ep_layer* L, uint32_t stage, const void* hidden, cons
                                                           (const float*)(ws + R.topk_weights), (const int32_t*)(ws + R.inv_perm), tokens);
       break;
   }
+  return 0;
 }
 
 }  // namespace
@@ -565,7 +567,7 @@ int netra_ep_layer_create(const netra_ep_layer_desc_t* desc, netra_ep_layer_t** 
     cudaFuncAttributes attr;
     if (e == cudaSuccess) e = cudaFuncGetAttributes(&attr, netra_ep_down_return_tokmajor_sm100);
     if (e != cudaSuccess) { netra_moe_layer_destroy(L->route); delete L; return fail_cuda("cudaFuncSetAttribute(down_return)", e); }
-    L->tokmajor_ok = g_tokmajor_ok && attr.numRegs == kTmRegsLaunch;
+    L->tokmajor_ok = g_tokmajor_ok[L->route->device] && attr.numRegs == kTmRegsLaunch;
   }
   const uint64_t g = L->e_l + 1, rows = desc->row_capacity;
   if (desc->weights_tiled) {
@@ -602,7 +604,8 @@ uint32_t netra_ep_layer_launch_count(const netra_ep_layer_t* L, uint32_t tokens)
 int netra_ep_layer_launch(netra_ep_layer_t* L, const void* hidden, const float* shared_w, void* out, uint32_t tokens, cudaStream_t stream) {
   if (!L || !hidden || !out) return fail("ep_layer_launch: null pointer");
   if (tokens == 0 || tokens > L->desc.max_tokens) return fail("ep_layer_launch: tokens exceed the bound capacity");
-  for (uint32_t s = 0; s < kEpStageCount; ++s) ep_launch_stage(L, s, hidden, shared_w, out, tokens, stream);
+  for (uint32_t s = 0; s < kEpStageCount; ++s)
+    if (int rc = ep_launch_stage(L, s, hidden, shared_w, out, tokens, stream)) return rc;
   return check_launch("ep_layer launch");
 }
 
@@ -611,7 +614,7 @@ int netra_ep_layer_launch_stage(netra_ep_layer_t* L, uint32_t stage, const void*
   if (!L || !hidden || !out) return fail("ep_layer_launch_stage: null pointer");
   if (tokens == 0 || tokens > L->desc.max_tokens) return fail("ep_layer_launch_stage: tokens exceed the bound capacity");
   if (stage >= kEpStageCount) return fail("ep_layer_launch_stage: stage out of range");
-  ep_launch_stage(L, stage, hidden, shared_w, out, tokens, stream);
+  if (int rc = ep_launch_stage(L, stage, hidden, shared_w, out, tokens, stream)) return rc;
   return check_launch("ep_layer stage launch");
 }
 

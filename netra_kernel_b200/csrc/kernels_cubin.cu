@@ -4,3 +4,4 @@
 #include "route_kernels.cu"
 #include "umma_kernels.cu"
 #include "umma_tokmajor.cu"
+#include "router_umma.cu"

@@ -22,13 +22,17 @@ namespace netra {
 // over one quarter of K; the four K-quarters are added in fixed order through shared memory.
 // grid (ceil(rows/16), 8); see the two entry points below.
 // ------------------------------------------------------------------------------------------
+// One rounding FP64 -> BF16 (nearest even).  Results below the smallest normal BF16 are flushed to zero
+// (signed), results at or above 2^128 become infinity, NaN stays NaN (quiet, sign kept).
 __device__ __forceinline__ uint16_t f64_to_bf16_bits(double d) {
   long long bits = __double_as_longlong(d);
   uint16_t sign = (uint16_t)(((unsigned long long)bits >> 63) << 15);
   long long mag = bits & 0x7fffffffffffffffLL;
+  if (mag > 0x7ff0000000000000LL) return (uint16_t)(sign | 0x7fc0u);   // NaN
   long long r = (mag + ((1LL << 44) - 1) + ((mag >> 45) & 1)) >> 45;
   r -= (896LL << 7);
   if (r < (1 << 7)) r = 0;
+  if (r > 0x7f80) r = 0x7f80;                                            // overflow and infinity
   return (uint16_t)(sign | (uint16_t)r);
 }
 
@@ -38,6 +42,17 @@ __device__ __forceinline__ double bf16_bits_to_f64(uint32_t b) {
   if (e != 0u && e != 0x7f80u)
     return __hiloint2double((int)(((b & 0x8000u) << 16) | (((b & 0x7fffu) << 13) + 0x38000000u)), 0);
   return (double)bf16_bits_to_f32(b);   // zero, subnormal, inf, nan
+}
+
+// The same conversion without a branch (zero, subnormal, infinity and NaN included), for code that is unrolled
+// many times: a BF16 subnormal m * 2^-133 is normalised by hand, infinity and NaN keep their payload.
+__device__ __forceinline__ double bf16_bits_to_f64_nobranch(uint32_t b) {
+  const uint32_t e = b & 0x7f80u, m = b & 0x7fu;
+  const int p = 31 - __clz((int)(m | 1u));                                        // position of the leading one (0 when m == 0)
+  const uint32_t hi_sub = m != 0u ? (((890u + (uint32_t)p) << 20) | ((m << (20 - p)) & 0xfffffu)) : 0u;
+  const uint32_t hi_norm = ((b & 0x7fffu) << 13) + 0x38000000u;
+  const uint32_t hi = e == 0u ? hi_sub : (e == 0x7f80u ? (0x7ff00000u | (m << 13)) : hi_norm);
+  return __hiloint2double((int)(((b & 0x8000u) << 16) | hi), 0);
 }
 
 __device__ __forceinline__ void dmma_m8n8k4(double& c0, double& c1, double a, double b) {
@@ -129,13 +144,9 @@ netra_router_logits_bf16_k8_sm100(uint16_t* __restrict__ logits, const uint16_t*
   router_logits_body<8>(logits, hidden, weight, rows);
 }
 
-// Per-128 FP8 quantisation of one hidden row by one warp: a lane owns 64 values, two lanes one group.
-// The quantised row goes to row (row_base + t) of the activation buffer.
-__device__ __forceinline__ void quantize_hidden_row(uint8_t* __restrict__ a_fp8, float* __restrict__ a_scale,
-                                                    const uint16_t* __restrict__ hidden, int t, uint32_t row_base, int lane) {
+// One hidden row into registers, one warp per row: lane owns the 64 consecutive values [lane*64, +64).
+__device__ __forceinline__ void load_hidden_row(float x[64], const uint16_t* __restrict__ hidden, int t, int lane) {
   const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)t * kHidden) + lane * 8;
-  float x[64];
-  float amax = amax_floor();
 #pragma unroll
   for (int c = 0; c < 8; ++c) {
     uint4 v = src[c];
@@ -146,6 +157,13 @@ __device__ __forceinline__ void quantize_hidden_row(uint8_t* __restrict__ a_fp8,
       x[c * 8 + 2 * q + 1] = bf16_bits_to_f32(u[q] >> 16);
     }
   }
+}
+
+// Per-128 FP8 quantisation of a row held as above: two lanes share one group.
+// The quantised row goes to row (row_base + t) of the activation buffer.
+__device__ __forceinline__ void quantize_loaded_row(uint8_t* __restrict__ a_fp8, float* __restrict__ a_scale, const float x[64],
+                                                    int t, uint32_t row_base, int lane) {
+  float amax = amax_floor();
 #pragma unroll
   for (int i = 0; i < 64; ++i) amax = fmaxf(amax, fabsf(x[i]));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
@@ -168,6 +186,50 @@ __device__ __forceinline__ void quantize_hidden_row(uint8_t* __restrict__ a_fp8,
   }
 }
 
+__device__ __forceinline__ void quantize_hidden_row(uint8_t* __restrict__ a_fp8, float* __restrict__ a_scale,
+                                                    const uint16_t* __restrict__ hidden, int t, uint32_t row_base, int lane) {
+  float x[64];
+  load_hidden_row(x, hidden, t, lane);
+  quantize_loaded_row(a_fp8, a_scale, x, t, row_base, lane);
+}
+
+// The same row kept as 32 packed BF16 pairs (half the registers), and its quantisation from that form.
+__device__ __forceinline__ void load_hidden_row_packed(uint32_t xb[32], const uint16_t* __restrict__ hidden, int t, int lane) {
+  const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)t * kHidden) + lane * 8;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const uint4 v = src[c];
+    xb[4 * c] = v.x; xb[4 * c + 1] = v.y; xb[4 * c + 2] = v.z; xb[4 * c + 3] = v.w;
+  }
+}
+
+__device__ __forceinline__ void quantize_packed_row(uint8_t* __restrict__ a_fp8, float* __restrict__ a_scale, const uint32_t xb[32],
+                                                    int t, uint32_t row_base, int lane) {
+  float amax = amax_floor();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    amax = fmaxf(amax, fabsf(bf16_bits_to_f32(xb[i] & 0xffffu)));
+    amax = fmaxf(amax, fabsf(bf16_bits_to_f32(xb[i] >> 16)));
+  }
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  const float scale = amax * inv448();
+  const float inv = 1.0f / scale;
+  const size_t row = (size_t)row_base + t;
+  if ((lane & 1) == 0) a_scale[row * kHiddenBlocks + (lane >> 1)] = scale;
+  uint4* dst = reinterpret_cast<uint4*>(a_fp8 + row * kHidden) + lane * 4;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint32_t w[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint32_t p0 = xb[c * 8 + q * 2], p1 = xb[c * 8 + q * 2 + 1];
+      w[q] = f32x4_to_e4m3x4(bf16_bits_to_f32(p0 & 0xffffu) * inv, bf16_bits_to_f32(p0 >> 16) * inv,
+                             bf16_bits_to_f32(p1 & 0xffffu) * inv, bf16_bits_to_f32(p1 >> 16) * inv);
+    }
+    dst[c] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // Softmax / top-8 / renormalise + shared slot + per-token FP8 quantisation.  One warp per token.
 // Selection key is (z desc, expert id asc) with z = f32(logit) + bias; weights are
@@ -175,30 +237,9 @@ __device__ __forceinline__ void quantize_hidden_row(uint8_t* __restrict__ a_fp8,
 // The quantised row goes to row (row_base + t) of the activation buffer.
 // grid ceil(rows/4), block 128.
 // ------------------------------------------------------------------------------------------
-extern "C" __global__ void __launch_bounds__(128)
-netra_moe_topk_quant_sm100(int32_t* __restrict__ ids9, float* __restrict__ w9,
-                           uint8_t* __restrict__ a_fp8, float* __restrict__ a_scale,
-                           const uint16_t* __restrict__ logits, const float* __restrict__ bias,
-                           const float* __restrict__ shared_w, const uint16_t* __restrict__ hidden,
-                           uint32_t rows, uint32_t row_base) {
-  const int lane = threadIdx.x & 31;
-  const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (t >= (int)rows) return;
-  // lane owns experts lane*8 .. lane*8+7 (ascending id inside the lane)
-  float z[8];
-  {
-    uint4 v = reinterpret_cast<const uint4*>(logits + (size_t)t * kRouted)[lane];
-    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      z[2 * q] = bf16_bits_to_f32(u[q] & 0xffffu);
-      z[2 * q + 1] = bf16_bits_to_f32(u[q] >> 16);
-    }
-    if (bias != nullptr) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) z[i] = z[i] + bias[lane * 8 + i];
-    }
-  }
+// Selection for one token by one warp; lane holds z[i] = f32(logit) + bias of experts lane*8 + i.
+__device__ __forceinline__ void softmax_top8_store(int32_t* __restrict__ ids9, float* __restrict__ w9, const float z[8],
+                                                   const float* __restrict__ shared_w, int t, int lane) {
   float zmax = z[0];
 #pragma unroll
   for (int i = 1; i < 8; ++i) zmax = fmaxf(zmax, z[i]);
@@ -239,7 +280,141 @@ netra_moe_topk_quant_sm100(int32_t* __restrict__ ids9, float* __restrict__ w9,
     ids9[t * kSlots + kTopK] = kRouted;
     w9[t * kSlots + kTopK] = shared_w != nullptr ? shared_w[t] : 1.0f;
   }
+}
+
+extern "C" __global__ void __launch_bounds__(128)
+netra_moe_topk_quant_sm100(int32_t* __restrict__ ids9, float* __restrict__ w9,
+                           uint8_t* __restrict__ a_fp8, float* __restrict__ a_scale,
+                           const uint16_t* __restrict__ logits, const float* __restrict__ bias,
+                           const float* __restrict__ shared_w, const uint16_t* __restrict__ hidden,
+                           uint32_t rows, uint32_t row_base) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (t >= (int)rows) return;
+  // lane owns experts lane*8 .. lane*8+7 (ascending id inside the lane)
+  float z[8];
+  {
+    uint4 v = reinterpret_cast<const uint4*>(logits + (size_t)t * kRouted)[lane];
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      z[2 * q] = bf16_bits_to_f32(u[q] & 0xffffu);
+      z[2 * q + 1] = bf16_bits_to_f32(u[q] >> 16);
+    }
+    if (bias != nullptr) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) z[i] = z[i] + bias[lane * 8 + i];
+    }
+  }
+  softmax_top8_store(ids9, w9, z, shared_w, t, lane);
   quantize_hidden_row(a_fp8, a_scale, hidden, t, row_base, lane);
+}
+
+// ------------------------------------------------------------------------------------------
+// The same stage for calls whose logits come from the tensor-core router (router_umma.cu) as FP32
+// approximations.  The routing contract is the exact dot product rounded once to BF16, so a logit
+// is recomputed in FP64 (exact products, error far below any BF16 spacing) whenever the
+// approximation cannot decide the rounding: the exact value lies within
+//     bound = kRouterErrScale * |hidden[t,:]|_2 * |w[e,:]|_2        (>= the approximation error)
+// of the FP32 value, and the BF16 result can only differ if a rounding boundary (the midpoint of
+// two neighbouring BF16 values) lies inside that interval.  kRouterErrScale is an empirical bound of
+// the tensor-core accumulation error relative to the product of the norms (which itself bounds the
+// sum of the 2048 product magnitudes), with a safety factor; the GPU tests compare every logit of
+// several million against the FP64 kernel above.  One warp per token; the token's hidden row is
+// read once and serves the bound, the FP64 dots and the FP8 quantisation.  grid ceil(rows/4), block 128.
+// ------------------------------------------------------------------------------------------
+constexpr float kRouterErrScale = 3.8146973e-06f;   // 2^-18
+
+extern "C" __global__ void __launch_bounds__(128)
+netra_moe_topk_quant_fix_sm100(int32_t* __restrict__ ids9, float* __restrict__ w9,
+                               uint8_t* __restrict__ a_fp8, float* __restrict__ a_scale,
+                               uint16_t* __restrict__ logits, const float* __restrict__ logits_f32,
+                               const float* __restrict__ wnorm, const uint16_t* __restrict__ router_w,
+                               const float* __restrict__ bias, const float* __restrict__ shared_w,
+                               const uint16_t* __restrict__ hidden, uint32_t* __restrict__ fix_count,
+                               uint32_t rows, uint32_t row_base) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (t >= (int)rows) return;
+  uint32_t xb[32];
+  load_hidden_row_packed(xb, hidden, t, lane);
+  float hn = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const float a = bf16_bits_to_f32(xb[i] & 0xffffu), b = bf16_bits_to_f32(xb[i] >> 16);
+    hn = fmaf(a, a, hn);
+    hn = fmaf(b, b, hn);
+  }
+  hn = sqrtf(warp_sum(hn)) * 1.001f;
+  float z[8];
+  uint32_t pending = 0;
+  {
+    const float4 a0 = reinterpret_cast<const float4*>(logits_f32 + (size_t)t * kRouted)[lane * 2];
+    const float4 a1 = reinterpret_cast<const float4*>(logits_f32 + (size_t)t * kRouted)[lane * 2 + 1];
+    const float4 n0 = reinterpret_cast<const float4*>(wnorm)[lane * 2];
+    const float4 n1 = reinterpret_cast<const float4*>(wnorm)[lane * 2 + 1];
+    const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    const float n[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t bits = __float_as_uint(a[i]);
+      const float ulp = __uint_as_float(bits & 0x7f800000u) * 1.1920929e-07f;        // spacing of FP32 at a[i]; 0 below the normals
+      const float dist = fabsf((float)((int)(bits & 0xffffu) - 0x8000)) * ulp;         // to the rounding boundary of a[i]'s BF16 cell
+      const float bound = kRouterErrScale * hn * n[i];
+      // decided only when the boundary of this cell is out of reach AND the neighbouring cells' boundaries are
+      // (they are at least a quarter of a BF16 spacing = 2^13 FP32 spacings away); NaN and infinity fail both tests
+      const bool decided = dist > bound && bound < 8192.0f * ulp;
+      if (!decided) pending |= 1u << i;
+      z[i] = bf16_round(a[i]);
+    }
+  }
+  uint32_t fixed = 0;
+  for (;;) {
+    const uint32_t any = __ballot_sync(0xffffffffu, pending != 0);
+    if (any == 0) break;
+    const int src = __ffs(any) - 1;
+    const int i = __ffs(__shfl_sync(0xffffffffu, pending, src)) - 1;
+    const uint4* wrow = reinterpret_cast<const uint4*>(router_w + (size_t)(src * 8 + i) * kHidden) + lane * 8;
+    uint4 wv[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) wv[c] = __ldg(wrow + c);          // all eight loads in flight before the first use
+    double acc0 = 0.0, acc1 = 0.0;                                // two chains: the FP64 pipe has latency to hide
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const uint32_t u[4] = {wv[c].x, wv[c].y, wv[c].z, wv[c].w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t h = xb[4 * c + q];
+        asm volatile("" : "+r"(h));   // keeps the 64 conversions of the row inside the loop (hoisted, they would cost 128 registers)
+        acc0 = fma(bf16_bits_to_f64_nobranch(h & 0xffffu), bf16_bits_to_f64_nobranch(u[q] & 0xffffu), acc0);
+        acc1 = fma(bf16_bits_to_f64_nobranch(h >> 16), bf16_bits_to_f64_nobranch(u[q] >> 16), acc1);
+      }
+    }
+    double acc = acc0 + acc1;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+    const float exact = bf16_bits_to_f32(f64_to_bf16_bits(acc));
+    if (lane == src) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        if (k == i) z[k] = exact;
+      pending &= ~(1u << i);
+    }
+    ++fixed;
+  }
+  if (fix_count != nullptr && lane == 0 && fixed != 0) atomicAdd(fix_count, fixed);
+  {
+    uint32_t pk[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) pk[q] = (__float_as_uint(z[2 * q]) >> 16) | (__float_as_uint(z[2 * q + 1]) & 0xffff0000u);
+    reinterpret_cast<uint4*>(logits + (size_t)t * kRouted)[lane] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+  }
+  if (bias != nullptr) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) z[i] = z[i] + bias[lane * 8 + i];
+  }
+  softmax_top8_store(ids9, w9, z, shared_w, t, lane);
+  quantize_packed_row(a_fp8, a_scale, xb, t, row_base, lane);
 }
 
 // The same outputs from a top-k computed elsewhere (a serving stack that keeps its own fused top-k, the
@@ -269,8 +444,10 @@ netra_moe_import_topk_quant_sm100(int32_t* __restrict__ ids9, float* __restrict_
 // Three launches for any size: per-segment histograms, a scan over segments, and a stable
 // scatter; a segment is 1024 consecutive pairs.  No atomics decide an output position.
 // ------------------------------------------------------------------------------------------
+// Ids are clamped to 0..255: the sort kernels index shared-memory tables with them, and one entry point
+// (netra_moe_sort_static_scratch_launch) takes ids produced by the caller.
 __device__ __forceinline__ int pair_expert(const int32_t* ids9, int pair) {
-  return ids9[(pair >> 3) * kSlots + (pair & 7)];
+  return min(max(ids9[(pair >> 3) * kSlots + (pair & 7)], 0), kRouted - 1);
 }
 
 // grid nseg, block 256
@@ -487,6 +664,44 @@ netra_moe_combine_sm100(uint16_t* __restrict__ out, const float* __restrict__ do
   for (int i = 0; i < 4; ++i) {
     __nv_bfloat162 v = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
     pk[i] = *reinterpret_cast<uint32_t*>(&v);
+  }
+  reinterpret_cast<uint4*>(out + (size_t)t * kHidden)[threadIdx.x] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+}
+
+// The same combine over FP16 partial rows (written by netra_moe_down_tokmajor_f16_sm100): each partial is widened to
+// FP32, multiplied by its routing weight and added in slot order, one BF16 rounding at the end - the order of
+// kernels/gfx950/templates/moe/prefill/route_reduce_splitk2_f16.inc:107-118.  grid rows, block 256 (8 columns per thread).
+extern "C" __global__ void __launch_bounds__(256)
+netra_moe_combine_f16_sm100(uint16_t* __restrict__ out, const __half* __restrict__ down,
+                            const float* __restrict__ w9, const int32_t* __restrict__ inv_perm, uint32_t rows) {
+  const int t = blockIdx.x;
+  const int pairs = (int)rows * kTopK;
+  uint4 v[kSlots];
+  float w[kSlots];
+#pragma unroll
+  for (int s = 0; s < kSlots; ++s) {
+    const size_t pos = s < kTopK ? (size_t)inv_perm[t * kTopK + s] : (size_t)pairs + t;
+    w[s] = w9[t * kSlots + s];
+    v[s] = reinterpret_cast<const uint4*>(down + pos * kHidden)[threadIdx.x];
+  }
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+#pragma unroll
+  for (int s = 0; s < kSlots; ++s) {
+    const uint32_t u[4] = {v[s].x, v[s].y, v[s].z, v[s].w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&u[q]));
+      acc[2 * q] = __fadd_rn(acc[2 * q], __fmul_rn(f.x, w[s]));
+      acc[2 * q + 1] = __fadd_rn(acc[2 * q + 1], __fmul_rn(f.y, w[s]));
+    }
+  }
+  uint32_t pk[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __nv_bfloat162 b = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+    pk[i] = *reinterpret_cast<uint32_t*>(&b);
   }
   reinterpret_cast<uint4*>(out + (size_t)t * kHidden)[threadIdx.x] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
 }

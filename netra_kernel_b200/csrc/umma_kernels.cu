@@ -35,14 +35,6 @@ constexpr uint32_t kSpinLimit = 1u << 22;
 
 enum : uint32_t { kStatusOk = 0, kStatusProducerTimeout = 1, kStatusMmaTimeout = 2, kStatusEpilogueTimeout = 3 };
 
-#ifdef NETRA_TRACE
-// Debug builds only: per-K-block SM-clock timestamps of CTA 0 (never compiled into the product library).
-__device__ long long g_trace[8][256];
-#define NETRA_TRACE_MARK(role, idx) do { if (blockIdx.x == 0 && (idx) < 256) g_trace[role][idx] = clock64(); } while (0)
-#else
-#define NETRA_TRACE_MARK(role, idx) do { } while (0)
-#endif
-
 // ---------------------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -329,7 +321,6 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
           if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / C::kStages) & 1) ^ 1, abort_flag)) {
             status[0] = kStatusProducerTimeout; *abort_flag = 1; ok = false; break;
           }
-          NETRA_TRACE_MARK(0, it);
           const uint32_t bar = smem_u32(&full_bar[s]);
           const uint32_t dst = smem_u32(stage_base + s * C::kStageBytes);
           mbar_expect_tx(bar, bytes);
@@ -360,18 +351,15 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
         const uint32_t idesc = make_idesc(n_mma);
         for (int step = 0; ok && step < C::kSubTiles * C::kKBlocks / C::kKbPerStep; ++step, ++jt) {
           const int a = jt % C::kAccStages;
-          NETRA_TRACE_MARK(1, it);
           if (!mbar_wait(smem_u32(&tempty_bar[a]), ((jt / C::kAccStages) & 1) ^ 1, abort_flag)) {
             status[0] = kStatusMmaTimeout; *abort_flag = 1; ok = false; break;
           }
-          NETRA_TRACE_MARK(2, it);
 #pragma unroll 1
           for (int q = 0; q < C::kKbPerStep; ++q, ++it) {
             const int s = it % C::kStages;
             if (!mbar_wait(smem_u32(&full_bar[s]), (it / C::kStages) & 1, abort_flag)) {
               status[0] = kStatusMmaTimeout; *abort_flag = 1; ok = false; break;
             }
-            NETRA_TRACE_MARK(3, it);
             tc_fence_after();
             const uint32_t sa = smem_u32(stage_base + s * C::kStageBytes);
             const uint64_t bdesc = make_smem_desc(sa + C::kATiles * kWTileBytes);
@@ -385,7 +373,6 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
                 umma_f8(d0 + (uint32_t)(tile * C::kTokMax), make_smem_desc(sa + tile * kWTileBytes) + 2 * k, bdesc + 2 * k, idesc, k > 0);
             }
             umma_commit(smem_u32(&empty_bar[s]));
-            NETRA_TRACE_MARK(4, it);
           }
           if (ok) umma_commit(smem_u32(&tfull_bar[a]));
         }
@@ -407,11 +394,9 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
       const int slot = n_item % C::kScaleSlots;
       const float* xs_tile = reinterpret_cast<const float*>(scale_base + slot * C::kScaleSlotBytes);
       const float* ws_tile = xs_tile + C::kTokMax * C::kKBlocks;
-      if (warp == 2 && lane == 0) NETRA_TRACE_MARK(7, n_item * 8 + 5);
       if (ok && !mbar_wait(smem_u32(&sfull_bar[slot]), (n_item / C::kScaleSlots) & 1, abort_flag)) {
         status[0] = kStatusEpilogueTimeout; *abort_flag = 1; ok = false;
       }
-      if (warp == 2 && lane == 0) NETRA_TRACE_MARK(7, n_item * 8 + 6);
       const int my_cols = min(n_mma >> 1, w.m_valid - col_base);         // columns holding real rows; may be <= 0
 #pragma unroll 1
       for (int sub = 0; sub < C::kSubTiles; ++sub) {
@@ -427,7 +412,6 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
           status[0] = kStatusEpilogueTimeout; *abort_flag = 1; ok = false;
         }
         if (!ok) continue;
-        if (warp == 2 && lane == 0) NETRA_TRACE_MARK(5, jt);
         tc_fence_after();
 #pragma unroll
         for (int q = 0; q < C::kKbPerStep; ++q) {
@@ -464,14 +448,12 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
             }
           }
         }   // K-block of the step
-        if (warp == 2 && lane == 0) NETRA_TRACE_MARK(6, jt);
       }
       if (sub == C::kSubTiles - 1) {
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sempty_bar[slot]));   // the scale tiles were last read above
       }
       // ---- tile epilogue (columns of this group that hold real rows), eight columns at a time
-      if (warp == 2 && lane == 0) NETRA_TRACE_MARK(7, n_item * 8 + 0);
       if constexpr (kGateUp) {
         uint32_t* my_red = red + (grp * 4 + gw) * C::kColsPerGroup;
 #pragma unroll
@@ -492,9 +474,7 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
             if (lane < 8) my_red[c0 + lane] = mine;
           }
         }
-        if (warp == 2 && lane == 0) NETRA_TRACE_MARK(7, n_item * 8 + 1);
         group_barrier(grp);
-        if (warp == 2 && lane == 0) NETRA_TRACE_MARK(7, n_item * 8 + 2);
         const uint32_t* g_red = red + grp * 4 * C::kColsPerGroup;
 #pragma unroll
         for (int c0 = 0; c0 < C::kColsPerGroup; c0 += 8) {
@@ -518,9 +498,7 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
             }
           }
         }
-        if (warp == 2 && lane == 0) NETRA_TRACE_MARK(7, n_item * 8 + 3);
         group_barrier(grp);   // red[] is free for the next item
-        if (warp == 2 && lane == 0) NETRA_TRACE_MARK(7, n_item * 8 + 4);
       } else {
         // row_ptr (expert parallelism): each output row goes to its own destination, possibly a peer GPU's memory
 #pragma unroll

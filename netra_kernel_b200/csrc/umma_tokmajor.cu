@@ -61,14 +61,15 @@ __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, i
 // barrier among the 256 epilogue threads
 __device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 3, 256;" ::: "memory"); }
 
-template <bool kGateUp>
+// kF16Out (down only): the output rows are FP16 partials staged in shared memory and written with one bulk copy per row
+template <bool kGateUp, bool kF16Out = false>
 struct TmCfg {
   static constexpr int kTokTile = 128;                                  // token rows per item (UMMA M)
   static constexpr int kKBlocks = kGateUp ? kHiddenBlocks : kInterBlocks;   // 16 | 4
   static constexpr int kNTiles = kGateUp ? kInter / kTileRows : kHidden / (2 * kTileRows);   // items per slab and token tile: 4 | 8
   static constexpr int kSlabTiles = kGateUp ? 2 * kInter / kTileRows : kHidden / kTileRows;  // 8 | 16
   static constexpr int kSlabRows = kGateUp ? 2 * kInter : kHidden;
-  static constexpr int kStages = 4;
+  static constexpr int kStages = kF16Out ? 3 : 4;                       // the FP16 staging rows take the fourth stage's room
   static constexpr int kPrefetch = 4;                                   // K-blocks between an L2 prefetch and its load (kStages..kKBlocks)
   static constexpr int kStageBytes = kTokTile * kBlock + 2 * kWTileBytes;   // 48 KiB: tokens, weight tile 0, weight tile 1
   static constexpr int kAccCols = 256;
@@ -80,23 +81,29 @@ struct TmCfg {
   static constexpr int kScaleSlotBytes = kXsBytes + 128;
   static constexpr int kItemList = 256;
   static constexpr int kEpiGroups = 2;                                      // epilogue warpgroups
-  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kScaleSlots * kScaleSlotBytes + 2 * kEpiGroups * kTokTile * 4 +
-                                    2 * 264 * 4 + kItemList * 16 + 512;
+  // FP16 output staging: one row of 128 halves per epilogue thread, rows 272 bytes apart (16 bytes of padding keep
+  // the 16-byte shared-memory stores of a quarter warp on different banks)
+  static constexpr int kOutRowBytes = 272;
+  static constexpr int kOutStageBytes = kF16Out ? kEpiGroups * kTokTile * kOutRowBytes : 0;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kScaleSlots * kScaleSlotBytes + kOutStageBytes +
+                                    2 * kEpiGroups * kTokTile * 4 + 2 * 264 * 4 + kItemList * 16 + 512;
 };
 
-template <bool kGateUp>
+template <bool kGateUp, bool kF16Out = false>
 __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, const CUtensorMap* tm_x128,
                                                    const float* __restrict__ x_scale, const float* __restrict__ w_scale,
                                                    const int32_t* __restrict__ offsets, uint8_t* __restrict__ h_fp8,
                                                    float* __restrict__ h_scale, float* __restrict__ down,
                                                    float* const* __restrict__ row_ptr, uint32_t num_groups, uint32_t w_tiled,
                                                    uint32_t* status) {
-  using C = TmCfg<kGateUp>;
+  static_assert(!(kGateUp && kF16Out), "FP16 partial rows are an output format of the down projection");
+  using C = TmCfg<kGateUp, kF16Out>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* stage_base = smem;
   uint8_t* scale_base = stage_base + C::kStages * C::kStageBytes;
-  uint32_t* red = reinterpret_cast<uint32_t*>(scale_base + C::kScaleSlots * C::kScaleSlotBytes);   // [2 parities][2 groups][128 rows]
+  uint8_t* out_stage = scale_base + C::kScaleSlots * C::kScaleSlotBytes;                            // [2 groups][128 rows][272 B] (FP16 output only)
+  uint32_t* red = reinterpret_cast<uint32_t*>(out_stage + C::kOutStageBytes);                       // [2 parities][2 groups][128 rows]
   int* offs = reinterpret_cast<int*>(red + 2 * C::kEpiGroups * C::kTokTile);                  // [264]
   int* item_pre = offs + 264;                                                     // [264]
   int4* item_list = reinterpret_cast<int4*>(item_pre + 264);                      // [kItemList]
@@ -238,7 +245,6 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
           if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / C::kStages) & 1) ^ 1, abort_flag)) {
             status[0] = kStatusProducerTimeout; *abort_flag = 1; ok = false; break;
           }
-          NETRA_TRACE_MARK(0, it);
           const uint32_t bar = smem_u32(&full_bar[s]);
           const uint32_t dst = smem_u32(stage_base + s * C::kStageBytes);
           mbar_expect_tx(bar, C::kStageBytes);
@@ -263,16 +269,13 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
         for (int kb = 0; kb < C::kKBlocks; ++kb, ++it) {
           if ((it & 1u) != par) continue;
           const int a = (int)par;
-          NETRA_TRACE_MARK(1, it);
           if (!mbar_wait(smem_u32(&tempty_bar[a]), ((it / C::kAccStages) & 1) ^ 1, abort_flag)) {
             status[0] = kStatusMmaTimeout; *abort_flag = 1; ok = false; break;
           }
-          NETRA_TRACE_MARK(2, it);
           const int s = it % C::kStages;
           if (!mbar_wait(smem_u32(&full_bar[s]), (it / C::kStages) & 1, abort_flag)) {
             status[0] = kStatusMmaTimeout; *abort_flag = 1; ok = false; break;
           }
-          NETRA_TRACE_MARK(3, it);
           tc_fence_after();
           const uint32_t sa = smem_u32(stage_base + s * C::kStageBytes);
           const uint64_t adesc = make_smem_desc(sa);                              // 128 token rows
@@ -282,7 +285,6 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
           for (int k = 0; k < kBlock / 32; ++k) umma_f8(d0, adesc + 2 * k, bdesc + 2 * k, idesc, k > 0);
           umma_commit(smem_u32(&empty_bar[s]));
           umma_commit(smem_u32(&tfull_bar[a]));
-          NETRA_TRACE_MARK(4, it);
         }
       }
     }
@@ -316,7 +318,6 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
           status[0] = kStatusEpilogueTimeout; *abort_flag = 1; ok = false;
         }
         if (!ok) continue;
-        if (warp == 4 && lane == 0) NETRA_TRACE_MARK(5, it);
         tc_fence_after();
         const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * C::kAccCols);
         uint32_t v[2][32];
@@ -342,7 +343,6 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
           acc1[c] = fmaf(__uint_as_float(v[0][c]), s1, acc1[c]);
           acc1[32 + c] = fmaf(__uint_as_float(v[1][c]), s1, acc1[32 + c]);
         }
-        if (warp == 4 && lane == 0) NETRA_TRACE_MARK(6, it);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&sempty_bar[slot]));   // the scale tiles were last read above
@@ -377,6 +377,29 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
           }
           if (wg == 0) h_scale[row * kInterBlocks + w.ntile] = scale;
         }
+      } else if constexpr (kF16Out) {
+        // FP16 partial rows (the reference's prefill contract, kernels/gfx950/templates/moe/prefill/fused_splitk2/down_partial.inc:435-458):
+        // the thread packs its 128 columns into its own staging row and hands the row to the copy engine, which writes
+        // 256 contiguous bytes - the thread itself never issues scattered global stores
+        uint8_t* my_row = out_stage + (size_t)(wg * C::kTokTile + r) * C::kOutRowBytes;
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");      // the previous item's copy has read this row
+#pragma unroll
+        for (int q = 0; q < 16; ++q) {
+          const float* a = q < 8 ? &acc0[8 * q] : &acc1[8 * (q - 8)];
+          uint32_t pk[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const __half2 h = __floats2half2_rn(a[2 * j], a[2 * j + 1]);
+            pk[j] = *reinterpret_cast<const uint32_t*>(&h);
+          }
+          *reinterpret_cast<uint4*>(my_row + 16 * q) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (live) {
+          __half* gdst = reinterpret_cast<__half*>(down) + row * kHidden + w.ntile * 2 * kTileRows + wg * kTileRows;
+          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 256;" ::"l"(gdst), "r"(smem_u32(my_row)) : "memory");
+        }
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
       } else {
         if (live) {
           // a lane owns a whole row, so a warp's stores touch 32 rows: 256-bit stores fill one 32-byte sector each
@@ -388,6 +411,7 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
         }
       }
     }
+    if constexpr (kF16Out) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // this thread's row copies are complete
   }
 
   // ---- teardown
@@ -417,7 +441,19 @@ netra_moe_down_tokmajor_sm100(const __grid_constant__ CUtensorMap tm_w2, const _
                             status);
 }
 
+// The down projection writing FP16 partial rows [rows, 2048] (half the bytes of the FP32 rows; consumed by
+// netra_moe_combine_f16_sm100).  Same accumulation as above, one rounding to FP16 per output element.
+extern "C" __global__ void __launch_bounds__(kTmThreads, 1)
+netra_moe_down_tokmajor_f16_sm100(const __grid_constant__ CUtensorMap tm_w2, const __grid_constant__ CUtensorMap tm_h128,
+                                  const float* h_scale, const float* w2_scale, const int32_t* offsets, void* down_f16,
+                                  uint32_t num_groups, uint32_t w_tiled, uint32_t* status) {
+  tokmajor_gemm_body<false, true>(&tm_w2, &tm_h128, h_scale, w2_scale, offsets, nullptr, nullptr, reinterpret_cast<float*>(down_f16),
+                                  nullptr, num_groups, w_tiled, status);
+}
+
 int gate_up_tokmajor_smem_bytes() { return TmCfg<true>::kSmemBytes; }
 int down_tokmajor_smem_bytes() { return TmCfg<false>::kSmemBytes; }
+int down_tokmajor_f16_smem_bytes() { return TmCfg<false, true>::kSmemBytes; }
+static_assert(TmCfg<false, true>::kSmemBytes <= 232448, "the FP16-output down kernel exceeds the shared memory of one SM");
 
 }  // namespace netra

@@ -352,7 +352,11 @@ class PeerExpertParallelLayer:
 
     def __init__(self, plan: ExpertParallelPlan, router_w, w13, w13_scale, w2, w2_scale, max_local_tokens: int,
                  router_bias=None, tiled: bool = True, row_capacity: Optional[int] = None, wait_timeout_s: float = 2.0,
-                 windows: Optional[list[int]] = None):
+                 windows: Optional[list[int]] = None, share_with: Optional["PeerExpertParallelLayer"] = None):
+        """``share_with``: another layer of the same shape on this rank whose windows, workspace and epoch tables this
+        one uses as well - the layers of a stack, which run one after the other on one stream and whose exchanges the
+        epoch flags already order exactly as they order repeated calls of one layer.  Create every layer of such a
+        group (on every rank) before the first call of any of them."""
         from . import abi
         self.plan, self.abi, self.lib = plan, abi, abi.load()
         world, e_l = plan.world, plan.experts_per_rank
@@ -360,6 +364,11 @@ class PeerExpertParallelLayer:
             raise ValueError(f"this rank holds the shared slab + {e_l} routed slabs, got {w13.shape[0]}")
         dev = router_w.device
         self.device, self.t_max = dev, int(max_local_tokens)
+        if share_with is not None:
+            if (share_with.t_max, share_with.plan.world, share_with.plan.rank) != (self.t_max, world, plan.rank):
+                raise ValueError("layers that share buffers must have the same shape, world and rank")
+            row_capacity = share_with.row_capacity
+            windows = list(share_with._windows)
         self.row_capacity = int(row_capacity) if row_capacity else default_row_capacity(world, self.t_max)
         ws_bytes, win_bytes = ep_sizes(world, self.t_max, self.row_capacity)
         self.window_bytes = win_bytes
@@ -377,7 +386,7 @@ class PeerExpertParallelLayer:
             raise ValueError("one window pointer per rank is required")
         if tiled:
             w13, w2 = self._repack(w13), self._repack(w2)
-        self.workspace = torch.zeros(ws_bytes + 1024, dtype=torch.uint8, device=dev)
+        self.workspace = share_with.workspace if share_with is not None else torch.zeros(ws_bytes + 1024, dtype=torch.uint8, device=dev)
         base = (self.workspace.data_ptr() + 1023) // 1024 * 1024
         desc = abi.EpLayerDesc()
         desc.struct_size = ctypes.sizeof(desc)

@@ -43,10 +43,15 @@ class RoutedMoELayer:
 
     def __init__(self, router_w: torch.Tensor, w13: torch.Tensor, w13_scale: torch.Tensor,
                  w2: torch.Tensor, w2_scale: torch.Tensor, max_tokens: int,
-                 router_bias: Optional[torch.Tensor] = None, tiled: bool = True, routing_only: bool = False):
+                 router_bias: Optional[torch.Tensor] = None, tiled: bool = True, routing_only: bool = False,
+                 pretiled: bool = False, workspace: Optional[torch.Tensor] = None):
         """``w13`` / ``w2`` are the checkpoint's row-major slabs.  With ``tiled`` (default) they are
         rewritten once into the tile order the grouped GEMMs stream best and only that copy is kept
-        by the layer; the caller may drop the row-major tensors."""
+        by the layer; the caller may drop the row-major tensors.  ``pretiled`` says the tensors are
+        already in tile order (another layer's ``tiled_weights()``), so nothing is copied.
+        ``workspace`` lets several layers that never run concurrently (the layers of a stack on one
+        stream) share one scratch buffer: a uint8 CUDA tensor of at least ``workspace_layout(max_tokens).total_bytes
+        + 1024`` bytes."""
         _require_cuda(router_w, w13, w13_scale, w2, w2_scale, router_bias)
         if tuple(router_w.shape) != (N_ROUTED, HIDDEN) or router_w.dtype != torch.bfloat16:
             raise ValueError("router weight must be bf16 [256, 2048]")
@@ -60,12 +65,20 @@ class RoutedMoELayer:
         self.routing_only = routing_only
         self.lib = abi.load()
         self.tiled = bool(tiled)
-        if self.tiled:
+        if pretiled:
+            self.tiled = True
+        elif self.tiled:
             w13, w2 = self._repack(w13), self._repack(w2)
         self.max_tokens = int(max_tokens)
         self.layout = workspace_layout(self.max_tokens)
         self._keep = (router_w, w13, w13_scale, w2, w2_scale, router_bias)
-        raw = torch.zeros(self.layout.total_bytes + 1024, dtype=torch.uint8, device=router_w.device)
+        if workspace is None:
+            raw = torch.zeros(self.layout.total_bytes + 1024, dtype=torch.uint8, device=router_w.device)
+        else:
+            _require_cuda(workspace)
+            if workspace.dtype != torch.uint8 or workspace.numel() < self.layout.total_bytes + 1024:
+                raise ValueError("a shared workspace must be a uint8 tensor of total_bytes + 1024 bytes")
+            raw = workspace
         shift = (-raw.data_ptr()) % 1024
         self.workspace = raw[shift:shift + self.layout.total_bytes]
         self._raw = raw
@@ -82,6 +95,7 @@ class RoutedMoELayer:
         abi.check(self.lib.netra_moe_layer_create(ctypes.byref(desc), ctypes.byref(handle)), "layer_create")
         self.handle = handle
         self.device = router_w.device
+        self.partial_f16 = False
 
     def _repack(self, w: torch.Tensor) -> torch.Tensor:
         out = torch.empty_like(w)
@@ -96,9 +110,28 @@ class RoutedMoELayer:
         return cls(ops.router_w.to(dev), ops.w13.to(dev), ops.w13_scale.to(dev), ops.w2.to(dev),
                    ops.w2_scale.to(dev), max_tokens or ops.tokens, bias)
 
+    def tiled_weights(self):
+        """(w13, w2) as the layer streams them (tile order when ``tiled``), for another layer's ``pretiled`` use."""
+        return self._keep[1], self._keep[3]
+
     def set_gemm_mode(self, mode: int) -> None:
         """0: the layer picks the grouped-GEMM form by token count (token-major from 1,024 tokens); 1: always swap-AB."""
         abi.check(self.lib.netra_moe_layer_set_gemm_mode(self.handle, mode), "layer_set_gemm_mode")
+
+    def set_router_mode(self, mode: int) -> None:
+        """0: calls above 1,024 rows take the BF16 tensor-core router with exact FP64 recomputation where the rounding is
+        undecided; 1: every logit on the FP64 tensor cores.  The emitted logits are identical."""
+        abi.check(self.lib.netra_moe_layer_set_router_mode(self.handle, mode), "layer_set_router_mode")
+
+    def set_partial_format(self, fmt: int) -> None:
+        """0: FP32 down rows (decode contract); 1: FP16 partial rows where the token-major kernels run (prefill contract)."""
+        abi.check(self.lib.netra_moe_layer_set_partial_format(self.handle, fmt), "layer_set_partial_format")
+        self.partial_f16 = bool(fmt)
+
+    def router_stats(self):
+        words = (ctypes.c_uint32 * 4)()
+        abi.check(self.lib.netra_moe_layer_router_stats(self.handle, ctypes.byref(words)), "layer_router_stats")
+        return list(words)
 
     def launches_per_call(self, tokens: int) -> int:
         return int(self.lib.netra_moe_layer_launch_count(self.handle, tokens))
@@ -180,6 +213,9 @@ class RoutedMoELayer:
             "h_fp8": view(lay.h_fp8, rows * INTER, torch.uint8).view(rows, INTER),
             "h_scale": view(lay.h_scale, rows * 4, torch.float32).view(rows, 4),
             "down": view(lay.down_f32, rows * HIDDEN, torch.float32).view(rows, HIDDEN),
+            "down_f16": view(lay.down_f32, rows * HIDDEN, torch.float16).view(rows, HIDDEN),
+            "logits_f32": view(lay.logits_f32, tokens * N_ROUTED, torch.float32).view(tokens, N_ROUTED),
+            "wnorm": view(lay.wnorm, N_ROUTED, torch.float32),
         }
 
     def close(self) -> None:

@@ -71,7 +71,7 @@ def quantize_mxfp4(w: torch.Tensor):
     scale_byte = torch.clamp(exponent + 127, 1, 254).to(torch.uint8)
     scale = torch.exp2(exponent.to(torch.float32))
     normalized = x.abs() / scale.unsqueeze(2)
-    magnitude = torch.bucketize(normalized, _E2M1_THRESHOLDS).to(torch.uint8)
+    magnitude = torch.bucketize(normalized, _E2M1_THRESHOLDS.to(w.device)).to(torch.uint8)
     sign = torch.signbit(x).to(torch.uint8) << 3
     code = (magnitude | sign).reshape(n, k)
     packed = code[:, 0::2] | (code[:, 1::2] << 4)
@@ -94,8 +94,10 @@ def _bf16_from_f64(x: torch.Tensor) -> torch.Tensor:
     rounded = (mag + ((1 << 44) - 1) + ((mag >> 45) & 1)) >> 45
     rounded = rounded - (896 << 7)           # exponent bias 1023 -> 127
     rounded = torch.where(rounded < (1 << 7), torch.zeros_like(rounded), rounded)
-    out = (rounded | torch.where(sign, 0x8000, 0)).to(torch.int32)
-    return (out << 16).view(torch.float32).to(torch.bfloat16)
+    rounded = torch.clamp(rounded, max=0x7F80)                                   # overflow and infinity
+    rounded = torch.where(mag > 0x7FF0000000000000, torch.full_like(rounded, 0x7FC0), rounded)   # NaN
+    out = rounded | torch.where(sign, 0x8000, 0)
+    return torch.where(out >= 0x8000, out - 0x10000, out).to(torch.int16).view(torch.bfloat16)   # bit pattern as is
 
 
 def routed_load(hidden: torch.Tensor, router_w: torch.Tensor, bias: Optional[torch.Tensor]):
@@ -161,6 +163,26 @@ def make_expert_weights(layer: int = 0, n_slabs: int = N_SLABS, keep_fp32: bool 
         if keep_fp32:
             fp32.append((a, b))
     return (w13, w13_s, w2, w2_s, fp32) if keep_fp32 else (w13, w13_s, w2, w2_s)
+
+
+def make_expert_weights_device(layer: int, device, n_slabs: int = N_SLABS, slabs_per_chunk: int = 32, mxfp4: bool = False):
+    """The same distributions drawn and quantised ON THE DEVICE (seed ``1000 + layer`` of that device's generator), for
+    workloads whose weights would take minutes to draw on the host (a 40-layer stack is 32 GB of FP8).  The values differ
+    from ``make_expert_weights`` (another generator) but every rank of a job that calls this with the same layer index on
+    the same GPU model gets the same bytes.  Returns (W13, W13 scales, W2, W2 scales); with ``mxfp4`` the FP32 slabs are
+    quantised to MXFP4 instead: (W13 packed, W13 E8M0 scales, W2 packed, W2 scales) as in ``make_expert_weights_mxfp4``."""
+    g = torch.Generator(device=device).manual_seed(1000 + layer)
+    out13, out13s, out2, out2s = [], [], [], []
+    for first in range(0, n_slabs, slabs_per_chunk):
+        n = min(slabs_per_chunk, n_slabs - first)
+        a = 0.02 * torch.randn(n * 2 * INTER, HIDDEN, generator=g, device=device)
+        b = 0.02 * torch.randn(n * HIDDEN, INTER, generator=g, device=device)
+        qa, sa = (quantize_mxfp4 if mxfp4 else quantize_fp8_block128)(a)
+        qb, sb = (quantize_mxfp4 if mxfp4 else quantize_fp8_block128)(b)
+        out13.append(qa.view(n, 2 * INTER, -1)); out13s.append(sa.view(n, -1, sa.shape[-1]) if mxfp4 else sa.view(n, 2 * INTER // BLOCK, -1))
+        out2.append(qb.view(n, HIDDEN, -1)); out2s.append(sb.view(n, -1, sb.shape[-1]) if mxfp4 else sb.view(n, HIDDEN // BLOCK, -1))
+        del a, b
+    return torch.cat(out13), torch.cat(out13s), torch.cat(out2), torch.cat(out2s)
 
 
 def make_expert_weights_mxfp4(layer: int = 0, n_slabs: int = N_SLABS):

@@ -36,14 +36,16 @@ static uint16_t f32_to_bf16(float f) {
   uint32_t u = f2u(f);
   return (uint16_t)((u + 0x7fffu + ((u >> 16) & 1u)) >> 16);
 }
-/* FP64 -> BF16 with a single rounding (values below 2^-126 flush to zero). */
+/* FP64 -> BF16 with a single rounding: below 2^-126 -> signed zero, 2^128 and above -> infinity, NaN stays NaN. */
 static uint16_t f64_to_bf16(double d) {
   uint64_t u; memcpy(&u, &d, 8);
   uint16_t sign = (uint16_t)((u >> 63) << 15);
   int64_t mag = (int64_t)(u & 0x7fffffffffffffffULL);
+  if (mag > 0x7ff0000000000000LL) return (uint16_t)(sign | 0x7fc0u);
   int64_t r = (mag + ((1LL << 44) - 1) + ((mag >> 45) & 1)) >> 45;
   r -= (896LL << 7);
   if (r < (1 << 7)) r = 0;
+  if (r > 0x7f80) r = 0x7f80;
   return (uint16_t)(sign | (uint16_t)r);
 }
 

@@ -69,13 +69,16 @@ def bf16_round(x: np.ndarray) -> np.ndarray:
 
 
 def f64_to_bf16_bits(x: np.ndarray) -> np.ndarray:
-    """Round FP64 to BF16 once (no intermediate FP32 rounding); |x| < 2^-126 -> 0."""
+    """Round FP64 to BF16 once (no intermediate FP32 rounding); |x| < 2^-126 -> signed zero,
+    |x| >= 2^128 and infinity -> infinity, NaN -> quiet NaN with the sign kept."""
     bits = np.ascontiguousarray(x, dtype=np.float64).view(np.int64)
     sign = bits < 0
     mag = bits & np.int64(0x7FFFFFFFFFFFFFFF)
     r = (mag + np.int64((1 << 44) - 1) + ((mag >> 45) & 1)) >> 45
     r = r - np.int64(896 << 7)
     r = np.where(r < (1 << 7), 0, r)
+    r = np.minimum(r, 0x7F80)
+    r = np.where(mag > np.int64(0x7FF0000000000000), 0x7FC0, r)
     return (r | np.where(sign, 0x8000, 0)).astype(np.uint16)
 
 
@@ -207,8 +210,17 @@ def expert_mlp(aq, a_s, w13q, w13_s, w2q, w2_s):
     return blockscale_matmul(hq, h_s, w2q, w2_s), hq, h_s
 
 
-def combine(down: np.ndarray, w9: np.ndarray) -> np.ndarray:
-    """down FP32 [T,9,H], weights [T,9] -> BF16 bits [T,H]; slot-ascending FP32 sum."""
+def combine(down: np.ndarray, w9: np.ndarray, partials: str = "f32") -> np.ndarray:
+    """down FP32 [T,9,H], weights [T,9] -> BF16 bits [T,H]; slot-ascending FP32 sum.
+
+    ``partials="f16"`` is the reference's prefill contract: each row is rounded to FP16 when it
+    leaves the down projection (``kernels/gfx950/templates/moe/prefill/fused_splitk2/down_partial.inc:435-458``)
+    and the reducer computes ``f32(partial) * weight`` slot ascending with one BF16 rounding
+    (``kernels/gfx950/templates/moe/prefill/route_reduce_splitk2_f16.inc:107-118``)."""
+    if partials == "f16":
+        down = down.astype(np.float16).astype(np.float32)
+    elif partials != "f32":
+        raise ValueError("partials must be 'f32' or 'f16'")
     acc = np.zeros((down.shape[0], down.shape[2]), dtype=np.float32)
     for s in range(down.shape[1]):
         acc = (acc + (down[:, s, :] * w9[:, s, None]).astype(np.float32)).astype(np.float32)
@@ -216,7 +228,7 @@ def combine(down: np.ndarray, w9: np.ndarray) -> np.ndarray:
 
 
 def moe_layer(hidden_bits, router_bits, w13q, w13_s, w2q, w2_s, bias=None, shared_w=None,
-              token_subset=None, external_topk=None):
+              token_subset=None, external_topk=None, partials: str = "f32"):
     """Whole layer.  ``w13q`` etc. hold ``E'+1`` slabs, the last one the shared expert.
     With ``token_subset`` the GEMMs and the output cover only those tokens (routing,
     sort and quantisation are always complete).  Returns a dict of every tensor the
@@ -250,7 +262,7 @@ def moe_layer(hidden_bits, router_bits, w13q, w13_s, w2q, w2_s, bias=None, share
     return {
         "logits": logits, "topk_ids": ids9, "topk_w": w9, "perm": perm, "counts": counts,
         "offsets": offsets, "a_fp8": aq, "a_scale": a_s, "h_fp8": hq_all, "h_scale": hs_all,
-        "tokens": toks, "out": combine(down, w9[toks]),
+        "tokens": toks, "out": combine(down, w9[toks], partials), "down": down,
     }
 
 

@@ -127,7 +127,7 @@ def test_catalog_is_locked_to_the_kernel_sources_and_model_independent(tmp_path)
     root = tmp_path / "lib"
     shutil.copytree(LIB_ROOT / "manifests", root / "manifests")
     (root / "csrc").mkdir()
-    for rel in ("common.cuh", "route_kernels.cu", "bridge_kernels.cu", "umma_kernels.cu", "umma_tokmajor.cu", "kernels_cubin.cu"):
+    for rel in ("common.cuh", "route_kernels.cu", "bridge_kernels.cu", "umma_kernels.cu", "umma_tokmajor.cu", "router_umma.cu", "kernels_cubin.cu"):
         shutil.copyfile(LIB_ROOT / "csrc" / rel, root / "csrc" / rel)
     catalog.load_fixed_tactic_catalog(root, TARGET)
     with open(root / "csrc" / "umma_kernels.cu", "a") as f:

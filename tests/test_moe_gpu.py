@@ -146,6 +146,96 @@ def test_token_major_and_swap_ab_gemms_agree_bitwise(gpu_weights, tokens, alpha)
         assert (counts == 0).sum() > 50                      # most experts empty: groups without any work item
 
 
+def _router_case(kind: str, tokens: int, seed: int):
+    """Hidden rows and router weights for the router comparison: the benchmark distributions, and rows built to stress the
+    error bound (a wide dynamic range across and inside rows, zero rows, exact cancellation, BF16 subnormals)."""
+    g = torch.Generator().manual_seed(seed)
+    hidden = torch.randn(tokens, 2048, generator=g)
+    w = 0.02 * torch.randn(256, 2048, generator=g)
+    if kind == "wide":
+        hidden *= torch.exp2(torch.randint(-20, 21, (tokens, 1), generator=g).float())      # rows from 1e-6 to 1e6
+        hidden[:, ::17] *= 64.0                                                                # outlier channels
+        w *= torch.exp2(torch.randint(-6, 7, (256, 1), generator=g).float())
+        hidden[3] = 0.0
+        hidden[5, 1:] = 0.0                                                                    # one product decides the logit
+        hidden[7, :1024] = hidden[7, 1024:]                                                    # exact cancellation against ...
+        w[9, :1024] = -w[9, 1024:]                                                             # ... this router row: logit 0
+        hidden[11] = 1e-39                                                                     # BF16 subnormals
+    return hidden.to(torch.bfloat16), w.to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("kind,tokens,seed", [("bench", 8192, 0), ("bench", 1025, 1), ("bench", 16384, 2), ("wide", 4096, 3),
+                                               ("wide", 1300, 4)])
+def test_tensor_core_router_emits_the_exactly_rounded_logits(gpu_weights, kind, tokens, seed):
+    """Above 1,024 rows the router runs as a BF16 tensor-core pass plus FP64 recomputation of the logits whose rounding the
+    FP32 value cannot decide.  Every emitted logit must equal the FP64 router's (the correctly rounded exact dot product),
+    the routing that follows must be identical, and the measured accumulation error must stay well inside the bound the
+    recomputation test assumes (kRouterErrScale = 2^-18 of |h| |w|)."""
+    hidden, router_w = _router_case(kind, tokens, seed)
+    layer = make_layer(gpu_weights, router_w, tokens)
+    h = hidden.cuda()
+    out = torch.empty_like(h)
+    results = {}
+    for mode in (1, 0):
+        layer.set_router_mode(mode)
+        before = layer.router_stats()[0]
+        for stage in range(5):
+            layer.launch_stage(stage, h, out)
+        torch.cuda.synchronize()
+        layer.check_status()
+        inter = layer.intermediates(tokens)
+        results[mode] = {k: inter[k].clone() for k in ("logits", "topk_ids", "topk_w", "perm", "counts", "a_fp8", "a_scale",
+                                                       "logits_f32", "wnorm")}
+        results[mode]["fixed"] = layer.router_stats()[0] - before
+    ref, got = results[1], results[0]
+    assert torch.equal(got["logits"].view(torch.int16), ref["logits"].view(torch.int16)), "logits differ from the FP64 router"
+    for key in ("topk_ids", "topk_w", "perm", "counts", "a_fp8", "a_scale"):
+        assert torch.equal(got[key], ref[key]), key
+    assert ref["fixed"] == 0 and got["fixed"] > 0
+    # the FP64 router against the CPU checker on a sample of rows (all rows are covered by the equality above)
+    rows = np.arange(0, tokens, max(1, tokens // 64))
+    want = R.router_logits(helpers.bits(hidden)[rows], helpers.bits(router_w))
+    assert np.array_equal(helpers.bits(ref["logits"].cpu())[rows], want)
+    # measured error of the tensor-core pass relative to the product of the norms
+    exact = h.double() @ router_w.cuda().double().T
+    hn = h.double().norm(dim=1, keepdim=True)
+    wn = router_w.cuda().double().norm(dim=1)[None, :]
+    err = (got["logits_f32"].double() - exact).abs() / (hn * wn).clamp_min(1e-300)
+    err = torch.where((hn * wn) > 0, err, torch.zeros_like(err))
+    worst = float(err.max())
+    frac = got["fixed"] / (tokens * 256)
+    print(f"router[{kind},{tokens}]: max |f32 - exact| / (|h||w|) = {worst:.3e} (bound 2^-18 = {2.0 ** -18:.3e}); "
+          f"recomputed {got['fixed']} of {tokens * 256} logits ({100 * frac:.2f} %)")
+    assert worst <= 2.0 ** -20, "the tensor-core accumulation error is within a factor 4 of the bound: widen kRouterErrScale"
+    assert torch.all(got["wnorm"].double() >= wn[0])
+
+
+def test_prefill_fp16_partial_rows_tactic(gpu_weights, expert_weights):
+    """The prefill contract of the reference: FP16 partial rows out of the down projection, reduced as f32(p) * w in slot
+    order.  Against the checker run with the same rounding point, and against the FP32-row tactic of the same layer."""
+    tokens = 8192
+    hidden, router_w, bias = synth.make_activations(tokens, synth.ZIPF_ALPHA_T8192)
+    subset = np.arange(3, tokens, 311)
+    ref = R.moe_layer(helpers.bits(hidden), helpers.bits(router_w), *helpers.np_weights(expert_weights),
+                      bias=bias.numpy(), token_subset=subset, partials="f16")
+    layer = make_layer(gpu_weights, router_w, tokens, bias)
+    out32, inter32 = run_layer(layer, hidden)
+    down32 = inter32["down"][: tokens * 9].clone()
+    layer.set_partial_format(1)
+    out16, inter16 = run_layer(layer, hidden)
+    m = check_against(ref, out16, inter16, tokens, subset=subset)
+    assert m["rel_l2"] < 2e-3
+    # every FP16 row is the FP32 row of the other tactic rounded once
+    assert torch.equal(inter16["down_f16"][: tokens * 9], down32.to(torch.float16))
+    m2 = R.parity_metrics(helpers.bits(out16), helpers.bits(out32))
+    assert m2["max_abs"] <= 8e-3 and m2["rel_l2"] <= 1e-3, m2
+    # a call below the token-major threshold keeps FP32 rows under the same setting
+    small, _, _ = synth.make_activations(64, seed=3)
+    ref_small = layer(small.cuda()).clone()
+    layer.set_partial_format(0)
+    assert torch.equal(layer(small.cuda()).view(torch.int16), ref_small.view(torch.int16))
+
+
 def test_mxfp4_expansion_kernel_and_layer(expert_weights):
     """MXFP4 expert weights (the reference's quantiser) expanded on the GPU into FP8 tiles: the kernel must equal
     the CPU restatement bit for bit, the expansion must be exact, and the layer on the expanded weights must

@@ -50,6 +50,11 @@ def test_bf16_roundings_match_torch():
     assert R.f64_to_bf16_bits(x).tolist() == [0x3F81, 0x3F80, 0x3F82, 0x8000, 0x0000]
     yd = torch.randn(200000, generator=g, dtype=torch.float64)
     assert np.array_equal(R.f64_to_bf16_bits(yd.numpy()), helpers.bits(synth._bf16_from_f64(yd)))
+    # non-finite and out-of-range sums keep their meaning instead of wrapping into finite patterns
+    z = np.array([np.inf, -np.inf, 2.0 ** 128, -1e300, np.nan, 2.0 ** -127, -2.0 ** -130])
+    want = [0x7F80, 0xFF80, 0x7F80, 0xFF80, 0x7FC0, 0x0000, 0x8000]
+    assert R.f64_to_bf16_bits(z).tolist() == want
+    assert helpers.bits(synth._bf16_from_f64(torch.from_numpy(z))).tolist() == want
 
 
 def test_mxfp4_dequant_matches_reference_vectors():

@@ -5,7 +5,8 @@
 during stream capture): its histogram table is a fixed array inside the library.  The test
 drives it through the C ABI on two calls in a row - the second larger and differently routed,
 so anything left in the shared table by the first call would show - and requires results
-identical to the regular sort stages of the fused layer, which use caller-provided scratch."""
+identical to the regular sort stages of the fused layer, which use caller-provided scratch,
+and to the CPU checker's stable sort as an independent third party."""
 import ctypes
 
 import numpy as np
@@ -13,6 +14,7 @@ import pytest
 import torch
 
 from netra_kernel_b200 import abi, synth
+from oracle import moe_ref as R
 
 pytestmark = pytest.mark.gpu
 
@@ -58,11 +60,41 @@ def test_static_scratch_sort_matches_regular_sort_on_consecutive_calls():
         got = _static_sort(want["topk_ids"])
         for key in ("perm", "inv_perm", "counts", "offsets"):
             assert torch.equal(got[key], want[key]), (tokens, key)
+        # a sort that shares nothing with either GPU path: the CPU checker's
+        c_perm, c_counts, c_offsets = R.sort_pairs(want["topk_ids"][:, :8].cpu().numpy())
+        assert np.array_equal(got["perm"].cpu().numpy(), c_perm), tokens
+        assert np.array_equal(got["counts"].cpu().numpy(), c_counts), tokens
+        assert np.array_equal(got["offsets"].cpu().numpy()[:257], c_offsets), tokens
         # and the result is a stable expert-major order in its own right
         flat = want["topk_ids"][:, :8].reshape(-1).cpu().numpy().astype(np.int64)
         perm = got["perm"].cpu().numpy()
         assert np.all(np.diff(flat[perm] * (tokens * 8) + perm) > 0)
         layer.close()
+
+
+def test_static_scratch_sort_at_its_row_limit_and_with_ids_out_of_range():
+    """All 128 histogram segments in use (16,384 rows), twice in a row, against the CPU checker's sort; then ids
+    outside 0..255, which the kernels clamp to the nearest valid expert instead of indexing with them."""
+    g = torch.Generator().manual_seed(11)
+    for call in range(2):
+        ids = torch.randint(0, 256, (16384, 9), generator=g, dtype=torch.int32)
+        got = _static_sort(ids.cuda())
+        c_perm, c_counts, c_offsets = R.sort_pairs(ids[:, :8].numpy())
+        assert np.array_equal(got["perm"].cpu().numpy(), c_perm), call
+        assert np.array_equal(got["counts"].cpu().numpy(), c_counts), call
+        assert np.array_equal(got["offsets"].cpu().numpy()[:257], c_offsets), call
+        assert got["offsets"][257].item() == 16384 * 9
+        assert np.array_equal(got["inv_perm"].cpu().numpy()[c_perm], np.arange(16384 * 8))
+    wild = torch.randint(0, 256, (300, 9), generator=g, dtype=torch.int32)
+    wild[::7, 3] = -5
+    wild[::11, 0] = 256
+    wild[5, 7] = 2 ** 31 - 1
+    wild[6, 1] = -2 ** 31
+    got = _static_sort(wild.cuda())
+    c_perm, c_counts, c_offsets = R.sort_pairs(wild[:, :8].clamp(0, 255).numpy())
+    assert np.array_equal(got["perm"].cpu().numpy(), c_perm)
+    assert np.array_equal(got["counts"].cpu().numpy(), c_counts)
+    assert np.array_equal(got["offsets"].cpu().numpy()[:257], c_offsets)
 
 
 def test_static_scratch_sort_refuses_sizes_beyond_its_table():
