@@ -293,9 +293,11 @@ int netra_moe_kernel_launch_info(uint32_t which, uint32_t* block_threads, uint32
 int netra_moe_layer_set_gemm_mode(netra_moe_layer_t* layer, uint32_t mode);
 
 /* Router of calls above 1024 rows.  mode 0 (default): BF16 tensor-core pass with FP32 accumulation, then an FP64
- * recomputation of exactly those logits whose BF16 rounding the FP32 value cannot decide - the emitted logits are
- * the correctly rounded exact dot products either way.  mode 1: every logit on the FP64 tensor cores (the form
- * used up to 1024 rows), several times slower on large calls. */
+ * recomputation of those logits that can reach the top 8 and whose BF16 rounding the FP32 value cannot decide:
+ * the selected ids, their logits and the routing weights are those of the exactly rounded dot products; logits
+ * of experts that cannot be selected are within one BF16 step of it.  mode 2: the same with every undecided
+ * logit recomputed, so that the whole logits array is the exactly rounded one (several times slower).  mode 1:
+ * every logit on the FP64 tensor cores (the form used up to 1024 rows). */
 int netra_moe_layer_set_router_mode(netra_moe_layer_t* layer, uint32_t mode);
 /* Copies the router statistics words (see netra_moe_workspace_layout_t.router_stats) to the host (synchronises). */
 int netra_moe_layer_router_stats(netra_moe_layer_t* layer, uint32_t stats_out[4]);

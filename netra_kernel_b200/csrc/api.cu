@@ -139,7 +139,7 @@ struct netra_moe_layer {
   int device;
   uint32_t launches;
   uint32_t gemm_mode;     // 0: pick the GEMM form by size, 1: always the swap-AB (decode) kernels
-  uint32_t router_mode;   // 0: pick the router by size, 1: always the FP64 tensor-core router
+  uint32_t router_mode;   // 0: pick the router by size, 1: always the FP64 tensor-core router, 2: as 0 with every logit exact
   uint32_t partial_f16;   // 1: the token-major down projection writes FP16 partial rows (prefill contract)
 };
 
@@ -297,7 +297,7 @@ constexpr uint32_t kRouterK8MaxRows = 1024;   // up to here the router runs on t
 // Calls above kRouterK8MaxRows rows take the BF16 tensor-core router (FP32 approximations, then FP64 only where
 // the rounding is undecided) unless the layer was told to keep the FP64 router.
 bool use_umma_router(const netra_moe_layer* layer, uint32_t tokens) {
-  return tokens > kRouterK8MaxRows && layer->router_mode == 0;
+  return tokens > kRouterK8MaxRows && layer->router_mode != 1;
 }
 bool use_f16_partials(const netra_moe_layer* layer, uint32_t pairs) {
   return layer->partial_f16 != 0 && layer->gemm_mode != 1 && use_tokmajor(layer->device, pairs, kRouted);
@@ -351,7 +351,7 @@ int launch_stage(netra_moe_layer* layer, uint32_t stage, const void* hidden, con
       if (use_umma_router(layer, tokens))
         netra_moe_topk_quant_fix_sm100<<<(tokens + 3) / 4, 128, 0, stream>>>(
             ids9, w9, a_fp8, a_scale, logits, logits_f32, wnorm, router_w, layer->desc.router_bias_f32, shared_w,
-            (const uint16_t*)hidden, router_stats, tokens, pairs);
+            (const uint16_t*)hidden, router_stats, tokens, pairs, layer->router_mode == 2 ? 1u : 0u);
       else
         netra_moe_topk_quant_sm100<<<(tokens + 3) / 4, 128, 0, stream>>>(
             ids9, w9, a_fp8, a_scale, logits, layer->desc.router_bias_f32, shared_w, (const uint16_t*)hidden, tokens, pairs);
@@ -581,7 +581,7 @@ int netra_moe_layer_set_gemm_mode(netra_moe_layer_t* layer, uint32_t mode) {
 }
 
 int netra_moe_layer_set_router_mode(netra_moe_layer_t* layer, uint32_t mode) {
-  if (layer == nullptr || mode > 1) return fail("layer_set_router_mode: null layer or unknown mode");
+  if (layer == nullptr || mode > 2) return fail("layer_set_router_mode: null layer or unknown mode");
   layer->router_mode = mode;
   return 0;
 }

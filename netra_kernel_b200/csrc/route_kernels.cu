@@ -238,19 +238,20 @@ __device__ __forceinline__ void quantize_packed_row(uint8_t* __restrict__ a_fp8,
 // grid ceil(rows/4), block 128.
 // ------------------------------------------------------------------------------------------
 // Selection for one token by one warp; lane holds z[i] = f32(logit) + bias of experts lane*8 + i.
-__device__ __forceinline__ void softmax_top8_store(int32_t* __restrict__ ids9, float* __restrict__ w9, const float z[8],
-                                                   const float* __restrict__ shared_w, int t, int lane) {
+// On return lane k < 8 holds slot k: expert id, softmax numerator exp(z - max z) and z of the k-th best
+// under the key (z desc, id asc).
+__device__ __forceinline__ void softmax_top8_select(const float z[8], int lane, int& sel_id, float& sel_p, float& sel_z) {
   float zmax = z[0];
 #pragma unroll
   for (int i = 1; i < 8; ++i) zmax = fmaxf(zmax, z[i]);
   zmax = warp_max(zmax);
-  float p[8], part = 0.0f;
+  // exp(z - zmax): the softmax numerators.  The softmax denominator cancels in the renormalisation over the eight
+  // selected experts, so the weights depend on the selected logits only
+  float p[8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) { p[i] = expf(z[i] - zmax); part += p[i]; }
-  const float denom = warp_sum(part);
+  for (int i = 0; i < 8; ++i) p[i] = expf(z[i] - zmax);
   uint32_t taken = 0;
-  float sel_p = 0.0f;   // lane k (< 8) keeps the probability of slot k
-  int sel_id = 0;
+  sel_p = 0.0f; sel_id = 0; sel_z = 0.0f;
 #pragma unroll 1
   for (int k = 0; k < kTopK; ++k) {
     float bv = -INFINITY; int bi = 0x7fffffff; float bp = 0.0f;
@@ -268,11 +269,16 @@ __device__ __forceinline__ void softmax_top8_store(int32_t* __restrict__ ids9, f
       if (take) { bv = ov; bi = oi; bp = op; }
     }
     if ((bi >> 3) == lane) taken |= 1u << (bi & 7);
-    if (lane == k) { sel_p = bp / denom; sel_id = bi; }
+    if (lane == k) { sel_p = bp; sel_id = bi; sel_z = bv; }
   }
+}
+
+// Renormalise over the eight selected probabilities (slot-order FP32 sum) and store ids / weights with the shared slot.
+__device__ __forceinline__ void top8_store(int32_t* __restrict__ ids9, float* __restrict__ w9, int sel_id, float sel_p,
+                                           const float* __restrict__ shared_w, int t, int lane) {
   float s = 0.0f;
 #pragma unroll
-  for (int k = 0; k < kTopK; ++k) s += __shfl_sync(0xffffffffu, sel_p, k);  // slot-order FP32 sum
+  for (int k = 0; k < kTopK; ++k) s += __shfl_sync(0xffffffffu, sel_p, k);
   if (lane < kTopK) {
     ids9[t * kSlots + lane] = sel_id;
     w9[t * kSlots + lane] = sel_p / s;
@@ -280,6 +286,13 @@ __device__ __forceinline__ void softmax_top8_store(int32_t* __restrict__ ids9, f
     ids9[t * kSlots + kTopK] = kRouted;
     w9[t * kSlots + kTopK] = shared_w != nullptr ? shared_w[t] : 1.0f;
   }
+}
+
+__device__ __forceinline__ void softmax_top8_store(int32_t* __restrict__ ids9, float* __restrict__ w9, const float z[8],
+                                                   const float* __restrict__ shared_w, int t, int lane) {
+  int sel_id; float sel_p, sel_z;
+  softmax_top8_select(z, lane, sel_id, sel_p, sel_z);
+  top8_store(ids9, w9, sel_id, sel_p, shared_w, t, lane);
 }
 
 extern "C" __global__ void __launch_bounds__(128)
@@ -312,16 +325,25 @@ netra_moe_topk_quant_sm100(int32_t* __restrict__ ids9, float* __restrict__ w9,
 
 // ------------------------------------------------------------------------------------------
 // The same stage for calls whose logits come from the tensor-core router (router_umma.cu) as FP32
-// approximations.  The routing contract is the exact dot product rounded once to BF16, so a logit
-// is recomputed in FP64 (exact products, error far below any BF16 spacing) whenever the
-// approximation cannot decide the rounding: the exact value lies within
-//     bound = kRouterErrScale * |hidden[t,:]|_2 * |w[e,:]|_2        (>= the approximation error)
-// of the FP32 value, and the BF16 result can only differ if a rounding boundary (the midpoint of
-// two neighbouring BF16 values) lies inside that interval.  kRouterErrScale is an empirical bound of
-// the tensor-core accumulation error relative to the product of the norms (which itself bounds the
-// sum of the 2048 product magnitudes), with a safety factor; the GPU tests compare every logit of
-// several million against the FP64 kernel above.  One warp per token; the token's hidden row is
-// read once and serves the bound, the FP64 dots and the FP8 quantisation.  grid ceil(rows/4), block 128.
+// approximations a[e].  The routing contract is the exact dot product rounded once to BF16.  The exact
+// value lies within
+//     bound[e] = kRouterErrScale * |hidden[t,:]|_2 * |w[e,:]|_2        (>= the approximation error)
+// of a[e], so bf16(a[e]) is already the contract value unless a rounding boundary (the midpoint of two
+// neighbouring BF16 values) lies inside that interval; such a logit is "undecided" and is recomputed in
+// FP64 (exact products, accumulation error far below any BF16 spacing).  kRouterErrScale is an empirical
+// bound of the tensor-core accumulation error relative to the product of the norms (which bounds the sum
+// of the 2048 product magnitudes), eleven times the largest error seen over 7 million logits of the
+// benchmark distributions; the GPU tests measure it again and compare every logit against the FP64 router.
+//
+// exact_all == 0 (default): only undecided logits that can reach the top 8 are recomputed.  Every
+// contract logit differs from z = bf16(a) + bias by at most delta = max bound + two BF16 spacings of the
+// largest logit, so the eight best approximate z prove that the true eighth-best z is at least
+// v8 - delta, and an expert with z < v8 - 2 delta cannot be selected whatever its exact value.  The
+// selected ids, their exact logits and therefore the routing weights are those of the contract; logits of
+// experts out of reach keep bf16(a), at most one BF16 step from the contract value.
+// exact_all != 0: every undecided logit is recomputed, and the logits array equals the contract everywhere.
+// One warp per token; the token's hidden row is read once and serves the bound, the FP64 dots and the FP8
+// quantisation.  stats[0] counts recomputed logits.  grid ceil(rows/4), block 128.
 // ------------------------------------------------------------------------------------------
 constexpr float kRouterErrScale = 3.8146973e-06f;   // 2^-18
 
@@ -331,8 +353,8 @@ netra_moe_topk_quant_fix_sm100(int32_t* __restrict__ ids9, float* __restrict__ w
                                uint16_t* __restrict__ logits, const float* __restrict__ logits_f32,
                                const float* __restrict__ wnorm, const uint16_t* __restrict__ router_w,
                                const float* __restrict__ bias, const float* __restrict__ shared_w,
-                               const uint16_t* __restrict__ hidden, uint32_t* __restrict__ fix_count,
-                               uint32_t rows, uint32_t row_base) {
+                               const uint16_t* __restrict__ hidden, uint32_t* __restrict__ stats,
+                               uint32_t rows, uint32_t row_base, uint32_t exact_all) {
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
   if (t >= (int)rows) return;
@@ -346,8 +368,9 @@ netra_moe_topk_quant_fix_sm100(int32_t* __restrict__ ids9, float* __restrict__ w
     hn = fmaf(b, b, hn);
   }
   hn = sqrtf(warp_sum(hn)) * 1.001f;
-  float z[8];
+  float v[8], bs[8];      // contract candidates bf16(a) and the bias
   uint32_t pending = 0;
+  float bmax = 0.0f, vmax = 0.0f;
   {
     const float4 a0 = reinterpret_cast<const float4*>(logits_f32 + (size_t)t * kRouted)[lane * 2];
     const float4 a1 = reinterpret_cast<const float4*>(logits_f32 + (size_t)t * kRouted)[lane * 2 + 1];
@@ -365,8 +388,30 @@ netra_moe_topk_quant_fix_sm100(int32_t* __restrict__ ids9, float* __restrict__ w
       // (they are at least a quarter of a BF16 spacing = 2^13 FP32 spacings away); NaN and infinity fail both tests
       const bool decided = dist > bound && bound < 8192.0f * ulp;
       if (!decided) pending |= 1u << i;
-      z[i] = bf16_round(a[i]);
+      v[i] = bf16_round(a[i]);
+      bs[i] = bias != nullptr ? bias[lane * 8 + i] : 0.0f;
+      bmax = fmaxf(bmax, bound);
+      vmax = fmaxf(vmax, fabsf(v[i]));
     }
+  }
+  float z[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) z[i] = v[i] + bs[i];
+  int sel_id; float sel_p, sel_z;
+  bool selected = false;
+  if (exact_all == 0u) {
+    softmax_top8_select(z, lane, sel_id, sel_p, sel_z);
+    selected = true;
+    const float v8 = __shfl_sync(0xffffffffu, sel_z, kTopK - 1);
+    // two BF16 spacings at the largest magnitude of the row cover the two roundings (of a and of the exact value, which
+    // may sit one binade higher); 1.01 covers the FP32 roundings of this arithmetic and of the bias addition
+    const float delta = (warp_max(bmax) + warp_max(vmax) * 0.015625f) * 1.01f;
+    const float reach = v8 - 2.0f * delta;
+    uint32_t cand = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (z[i] >= reach) cand |= 1u << i;
+    pending &= cand;
   }
   uint32_t fixed = 0;
   for (;;) {
@@ -397,23 +442,20 @@ netra_moe_topk_quant_fix_sm100(int32_t* __restrict__ ids9, float* __restrict__ w
     if (lane == src) {
 #pragma unroll
       for (int k = 0; k < 8; ++k)
-        if (k == i) z[k] = exact;
+        if (k == i) { v[k] = exact; z[k] = exact + bs[k]; }
       pending &= ~(1u << i);
     }
     ++fixed;
   }
-  if (fix_count != nullptr && lane == 0 && fixed != 0) atomicAdd(fix_count, fixed);
+  if (stats != nullptr && lane == 0 && fixed != 0) atomicAdd(stats, fixed);
   {
     uint32_t pk[4];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) pk[q] = (__float_as_uint(z[2 * q]) >> 16) | (__float_as_uint(z[2 * q + 1]) & 0xffff0000u);
+    for (int q = 0; q < 4; ++q) pk[q] = (__float_as_uint(v[2 * q]) >> 16) | (__float_as_uint(v[2 * q + 1]) & 0xffff0000u);
     reinterpret_cast<uint4*>(logits + (size_t)t * kRouted)[lane] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
   }
-  if (bias != nullptr) {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) z[i] = z[i] + bias[lane * 8 + i];
-  }
-  softmax_top8_store(ids9, w9, z, shared_w, t, lane);
+  if (!selected || fixed != 0) softmax_top8_select(z, lane, sel_id, sel_p, sel_z);   // `fixed` is the same in every lane
+  top8_store(ids9, w9, sel_id, sel_p, shared_w, t, lane);
   quantize_packed_row(a_fp8, a_scale, xb, t, row_base, lane);
 }
 

@@ -119,8 +119,9 @@ class RoutedMoELayer:
         abi.check(self.lib.netra_moe_layer_set_gemm_mode(self.handle, mode), "layer_set_gemm_mode")
 
     def set_router_mode(self, mode: int) -> None:
-        """0: calls above 1,024 rows take the BF16 tensor-core router with exact FP64 recomputation where the rounding is
-        undecided; 1: every logit on the FP64 tensor cores.  The emitted logits are identical."""
+        """0: calls above 1,024 rows take the BF16 tensor-core router with exact FP64 recomputation of the undecided logits
+        that can reach the top 8 (routing identical to the exact logits'); 2: the same with every undecided logit
+        recomputed (the whole logits array exact); 1: every logit on the FP64 tensor cores."""
         abi.check(self.lib.netra_moe_layer_set_router_mode(self.handle, mode), "layer_set_router_mode")
 
     def set_partial_format(self, fmt: int) -> None:

@@ -57,6 +57,65 @@ def test_bf16_roundings_match_torch():
     assert helpers.bits(synth._bf16_from_f64(torch.from_numpy(z))).tolist() == want
 
 
+def _stage_pins():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_stage_golden", helpers.GOLDEN / "make_stage_golden.py")
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    return gen, np.load(helpers.GOLDEN / "reference_stage_pins.npz")
+
+
+def test_gemm_and_combine_arithmetic_matches_the_reference_exporters():
+    """The fixture holds what the reference's own stage-1 / stage-2 exporters computed (run unmodified, see
+    tests/golden/make_stage_golden.py) on operands this test regenerates from the same seeds.  The checker's block-scaled
+    GEMM and combine follow the same arithmetic (dequantise both blocks, FP32 dot per K-block, K-blocks ascending; slot
+    ascending weighted sum; one BF16 rounding): they may differ only by the summation order inside a 128-long FP32 dot,
+    bounded here by 1e-5 of the row's magnitude."""
+    gen, pins = _stage_pins()
+    for case in range(gen.CASES):
+        ops = gen.operands(case)
+        assert bytes(pins[f"case{case}_operands_sha256"]).hex() == gen.operands_sha256(ops), "operands differ from the generator's"
+        aq, a_s = R.quant_fp8_group128(R.bf16_bits_to_f32(helpers.bits(ops["hidden"])))
+        w1, w1_s = helpers.u8(ops["w1"]), ops["w1_scale"].numpy()
+        w2, w2_s = helpers.u8(ops["w2"]), ops["w2_scale"].numpy()
+        # stage 1: slot s uses the slab of its expert (w1[s] here is the slab of slot s)
+        got1 = np.stack([R.blockscale_matmul(aq, a_s, w1[s], w1_s[s])[0] for s in range(9)])
+        want1 = pins[f"case{case}_stage1_f32"]
+        scale1 = np.abs(want1).max(axis=1, keepdims=True)
+        assert np.abs(got1 - want1).max() <= 1e-5 * scale1.max(), np.abs(got1 - want1).max()
+        assert np.all(np.abs(got1 - want1) <= 1e-5 * scale1)
+        # SiLU * up requantisation of the reference's stage-1 values reproduces the activation fed to its stage 2
+        hq, h_s, _ = R.silu_mul_quant(want1)
+        assert np.array_equal(hq, pins[f"case{case}_act_fp8"]) and np.array_equal(h_s, pins[f"case{case}_act_scale"])
+        # stage 2 + combine
+        down = np.stack([R.blockscale_matmul(hq[s:s + 1], h_s[s:s + 1], w2[s], w2_s[s])[0] for s in range(9)])[None]
+        want2 = pins[f"case{case}_stage2_f32"]
+        acc = np.zeros((1, 2048), np.float32)
+        for s in range(9):
+            acc = (acc + (down[:, s] * ops["topk_w"].numpy()[:, s, None]).astype(np.float32)).astype(np.float32)
+        assert np.abs(acc - want2).max() <= 1e-5 * np.abs(want2).max()
+        got_bits = R.combine(down, ops["topk_w"].numpy())
+        m = R.parity_metrics(got_bits, pins[f"case{case}_stage2_bf16"])
+        # BF16 results agree except where the FP32 sums straddle a rounding boundary
+        assert m["exact_fraction"] >= 0.995 and m["max_abs"] <= 2.0 ** -8 * np.abs(want2).max() * 2, m
+
+
+def test_router_logits_against_the_reference_exporter():
+    """The reference's router semantic is torch's BF16 ``F.linear`` (unspecified FP32 order); the checker defines the logit
+    as the exact dot product rounded once.  On the reference's own output for 96 x 256 logits the two agree except for a
+    few values that sit on a rounding boundary, where they differ by exactly one BF16 step."""
+    gen, pins = _stage_pins()
+    hidden, weight = gen.router_operands()
+    digest = __import__("hashlib").sha256(hidden.view(torch.uint8).numpy().tobytes() + weight.view(torch.uint8).numpy().tobytes()).digest()
+    assert bytes(pins["router_operands_sha256"]) == digest
+    want = pins["router_logits_bf16"]
+    got = R.router_logits(helpers.bits(hidden), helpers.bits(weight))
+    differ = got != want
+    assert differ.mean() <= 1e-3, differ.mean()
+    step = np.abs(got.astype(np.int32) - want.astype(np.int32))[differ]
+    assert np.all(step == 1)
+
+
 def test_mxfp4_dequant_matches_reference_vectors():
     data = np.load(helpers.GOLDEN / "mxfp4_dequant.npz")
     got = R.mxfp4_dequant(data["packed"], data["scales"])
