@@ -321,7 +321,7 @@ def time_e2e_pipelined(compute, hidden, out, hidden_cpu, steps, warmup, stream):
     return e0.elapsed_time(e1) / steps, host_out, host_api
 
 
-def make_engine_session(args, tokens, device_id, layer, hidden, out):
+def make_engine_session(args, tokens, device_id, layer, hidden, out, model="routed-moe-layer-fp8.json", bias=None):
     """Compiles an engine directory for this token count and binds it to the layer's own (already
     repacked) weights; None when no engine profile covers the workload."""
     import tempfile
@@ -329,7 +329,7 @@ def make_engine_session(args, tokens, device_id, layer, hidden, out):
     from netra_kernel_b200.compiler import compile_engine
     from netra_kernel_b200.compiler.library import KernelLibrary
     from netra_kernel_b200.compiler.profiles import load_profile_registry
-    if args.zipf_alpha or args.row_major_weights or args.weights != "fp8":
+    if args.row_major_weights or not layer.tiled:
         return None
     root = KernelLibrary.discover().root
     profile = next((p for p in load_profile_registry(root, "sm_100a", 1)
@@ -337,14 +337,16 @@ def make_engine_session(args, tokens, device_id, layer, hidden, out):
     if profile is None:
         return None
     directory = tempfile.mkdtemp(prefix=f"netra_engine_r{device_id}_")
-    compile_engine(root / "manifests" / "sm_100a" / "models" / "routed-moe-layer-fp8.json", profile.name, directory)
+    compile_engine(root / "manifests" / "sm_100a" / "models" / model, profile.name, directory)
     session = engine_runtime.EngineSession(directory, device_id=device_id, enable_graph_capture=True)
     router_w, w13, w13_s, w2, w2_s, _ = layer._keep
-    session.bind({"hidden": hidden, "output": out, "router_weight": router_w, "w13": w13, "w13_scale": w13_s,
-                  "w2": w2, "w2_scale": w2_s})
+    tensors = {"hidden": hidden, "output": out, "router_weight": router_w, "w13": w13, "w13_scale": w13_s,
+               "w2": w2, "w2_scale": w2_s}
+    if bias is not None:
+        tensors["router_bias"] = bias
+    session.bind(tensors)
     session.finalize()
     return session
-
 
 
 class Sync:
@@ -456,7 +458,7 @@ def e2e_object(tokens_total, tokens_per_rank, e2e_ms, serial_ms, host_api) -> di
             "copies_enqueued_with": host_api, "serial_ms_per_step": serial_ms}
 
 
-def prefill_object(name, layer, hidden_cpu, steps, warmup, dev, stream, sync, extra_config) -> dict:
+def prefill_object(name, layer, hidden_cpu, steps, warmup, dev, stream, sync, extra_config, engine=None) -> dict:
     """One tensor-bound single-layer configuration (T=8192): graph replay of the fused-layer call, per-kernel times,
     end to end, and the FP8 tensor roofline of the dominant kernel and of the whole call."""
     import torch
@@ -473,12 +475,27 @@ def prefill_object(name, layer, hidden_cpu, steps, warmup, dev, stream, sync, ex
         layer(hidden, out=out)
         stream.synchronize()
         recomputed = (layer.router_stats()[0] - stats0) & 0xffffffff
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            layer(hidden, out=out)
-        ms, spread = time_replays(graph.replay, steps, warmup, stream, sync, spread=True)
+        session = engine(hidden, out) if engine is not None else None
+        if session is not None:
+            # the engine runtime ABI: the compiled engine's operations captured into a CUDA graph by prepare_profile
+            session.prepare(stream.cuda_stream)
+            replay = lambda: session.launch(stream.cuda_stream)
+            api = "netra_engine_launch (engine runtime ABI, captured CUDA graph)"
+            want = out.clone()
+            out.zero_()
+            replay()
+            stream.synchronize()
+            if not torch.equal(out, want):
+                raise SystemExit(f"bench: {name}: the engine's result differs from the fused-layer call on the same operands")
+        else:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                layer(hidden, out=out)
+            replay = graph.replay
+            api = "netra_moe_layer_launch (fused-layer ABI, captured CUDA graph)"
+        ms, spread = time_replays(replay, steps, warmup, stream, sync, spread=True)
         stage_ms = time_stages(layer, hidden, out, steps, warmup, stream, sync)
-        e2e_ms, serial_ms, host_api, _ = time_e2e(graph.replay, hidden, out, hidden_cpu, steps, warmup, stream, sync)
+        e2e_ms, serial_ms, host_api, _ = time_e2e(replay, hidden, out, hidden_cpu, steps, warmup, stream, sync)
         stream.synchronize()
     layer.check_status()
     inter = layer.intermediates(tokens)
@@ -492,7 +509,7 @@ def prefill_object(name, layer, hidden_cpu, steps, warmup, dev, stream, sync, ex
         "workload": name, "tokens": tokens, **extra_config, "routing_load": routing_load(inter["counts"]),
         "ms_per_step": ms, "tokens_per_s": tokens / (ms / 1e3), "steps": steps, "warmup": warmup, "step_ms_spread": spread,
         "launch": "CUDA graph replay of the layer's %d kernels" % layer.launches_per_call(tokens),
-        "api": "netra_moe_layer_launch (fused-layer ABI, captured CUDA graph)",
+        "api": api,
         "tactics": {"router": "BF16 tensor-core pass (tcgen05 kind::f16, FP32 accumulate) + FP64 recomputation of the logits whose "
                               "BF16 rounding the FP32 value cannot decide; emitted logits are the exactly rounded dot products",
                     "router_logits_recomputed_fraction": recomputed / (tokens * 256),
@@ -509,7 +526,8 @@ def prefill_object(name, layer, hidden_cpu, steps, warmup, dev, stream, sync, ex
         "kernels_ms": {n: round(v, 5) for n, v in zip(layer.STAGES, stage_ms)},
         "e2e": e2e_object(tokens, tokens, e2e_ms, serial_ms, host_api),
     }
-    del graph
+    if session is not None:
+        session.close()
     return obj
 
 
@@ -661,7 +679,8 @@ def run_ours(args) -> None:
                 layer(hidden, out=out)
             stream.synchronize()
             layer.check_status()
-            session = make_engine_session(args, tokens, local_rank, layer, hidden, out) if args.api == "engine" else None
+            session = (make_engine_session(args, tokens, local_rank, layer, hidden, out)
+                       if args.api == "engine" and args.weights == "fp8" and not args.zipf_alpha and args.partials == "f32" else None)
             if session is not None:
                 session.prepare(stream.cuda_stream)
 
@@ -698,7 +717,11 @@ def run_ours(args) -> None:
                                  tiled=layer.tiled, pretiled=layer.tiled)
             pre.set_partial_format(1)
             cfg8 = {"zipf_alpha": synth.ZIPF_ALPHA_T8192, "expert_weights": "fp8 e4m3, 128x128 block scales"}
-            extras["prefill_t8192"] = prefill_object("prefill_t8192", pre, h8, cap, warmup, dev, stream, sync, cfg8)
+            bias_dev = bias8.to(dev)
+            engine8 = (lambda layer8: (lambda hid, res: make_engine_session(args, 8192, local_rank, layer8, hid, res,
+                                                                           model="routed-moe-layer-fp8-prefill.json", bias=bias_dev)))
+            extras["prefill_t8192"] = prefill_object("prefill_t8192", pre, h8, cap, warmup, dev, stream, sync, cfg8,
+                                                     engine=engine8(pre) if args.api == "engine" else None)
             pre.set_partial_format(0)      # the decode-contract rows, for comparison
             with torch.cuda.stream(stream):
                 hd, od = h8.to(dev), torch.empty(8192, 2048, dtype=torch.bfloat16, device=dev)
@@ -726,7 +749,8 @@ def run_ours(args) -> None:
             cfgm = {"zipf_alpha": synth.ZIPF_ALPHA_T8192,
                     "expert_weights": "mxfp4 (E2M1 + E8M0 per 32 along K), expanded at load into exact E4M3 tiles with power-of-two "
                                       "tile scales (%d inexact elements); the GEMMs stream FP8 bytes" % (bad13 + bad2)}
-            extras["mxfp4_t8192"] = prefill_object("mxfp4_t8192", mx, h8, cap, warmup, dev, stream, sync, cfgm)
+            extras["mxfp4_t8192"] = prefill_object("mxfp4_t8192", mx, h8, cap, warmup, dev, stream, sync, cfgm,
+                                                   engine=engine8(mx) if args.api == "engine" else None)
             mx.close()
             del mx
             torch.cuda.empty_cache()
@@ -1006,6 +1030,7 @@ def run_expert_parallel(args) -> None:
     layer.check_status()
     sync = Sync(dev, world)
     parity = stack = None
+    used_graph = graph is not None
     if args.extras and args.ep_exchange == "peer":
         layer.close()
         del layer, graph, local
@@ -1030,7 +1055,7 @@ def run_expert_parallel(args) -> None:
                                             "epoch flags with bounded waits, no NCCL on the data path",
                                     "fixed": "NCCL all-to-all, fixed slots per rank pair, no host read-back",
                                     "exact": "NCCL all-to-all, exact split sizes read on the host once per call"}[args.ep_exchange],
-                       "launch": "one CUDA graph replay per step" if graph is not None else "direct launches",
+                       "launch": "one CUDA graph replay per step" if used_graph else "direct launches",
                        "api": "netra_ep_layer_launch" if args.ep_exchange == "peer"
                               else "ExpertParallelMoELayer over netra_moe_layer_launch_stage / netra_moe_expert_block_launch"},
             "gpu_launches": steps * launches,

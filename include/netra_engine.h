@@ -80,6 +80,12 @@ typedef struct netra_pointer_binding {  /* reference lines 54-58; one boundary p
  * workspace, loads the cubins, resolves every kernel symbol and checks its register contract. */
 netra_status_t netra_engine_create(const char* engine_directory, const netra_engine_options_t* options,
                                    netra_engine_t** output);
+/* No counterpart in the reference, whose create reports every failure as MANIFEST and drops the text with the
+ * half-built engine.  Here create returns IO when a file of the directory cannot be read, UNSUPPORTED_TARGET for
+ * a device that is not sm_100a or a driver older than required_cuda, CUDA for a failed runtime or driver call,
+ * MANIFEST for a malformed or inconsistent engine.json - and this returns the text of the calling thread's most
+ * recent failed create ("" after a successful one). */
+const char* netra_engine_create_error(void);
 /* Reference line 108.  BUSY while a launch call is inside the API; the caller quiesces its streams first. */
 netra_status_t netra_engine_destroy(netra_engine_t* engine);
 /* Reference line 103.  Message of the most recent failure on this engine. */

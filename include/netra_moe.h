@@ -9,6 +9,7 @@
  *      runtime/gfx950/routing/verify/qwen36_router_bf16_bridge.h:10-21
  *      runtime/gfx950/routing/decode/qwen36_shared_gate_append_bridge.h:10-23
  *      runtime/gfx950/fp8/moe/qwen36_moe_silu_mul_quant_bridge.h:14-64
+ *      runtime/gfx950/fp8/moe/moe_prefill_m768_bridge.h:10-23
  *    Differences: hipStream_t -> cudaStream_t; the kernels are linked into the library, so
  *    load(path) ignores its argument (NULL is accepted) and only performs one-time set-up;
  *    `rows` may be any positive count (the reference kernels take 1..16).
@@ -68,6 +69,31 @@ int netra_qwen36_moe_down_reduce_launch(const void* activation_fp8, const float*
                                         void* output_bf16, int rows, cudaStream_t stream);
 int netra_qwen36_moe_down_reduce_unload(void);
 const char* netra_qwen36_moe_down_reduce_last_error(void);
+
+/* The 768-row prefill call (runtime/gfx950/fp8/moe/moe_prefill_m768_bridge.h:10-23): quantised token rows
+ * [768, 2048] + scales [768, 16], the expert slabs in the checkpoint's row-major layout ([257, 1024, 2048] /
+ * [257, 2048, 512], slab 256 = shared expert), and the routing in the sorted-id format of the reference's fused
+ * producer (kernels/gfx950/templates/moe/prefill/fused_splitk2/entry_routing.inc:67-111): sorted_token_ids [23360]
+ * words token | slot << 24 in 64-entry blocks of one expert each (padding words have token >= 768),
+ * sorted_expert_ids [365] per block, num_valid_ids [1], topk_weights [768, 9] in slot order with slot 8 = the
+ * shared expert (id 256, what netra_qwen36_shared_gate_append produces).  Output BF16 [768, 2048].
+ * load(): both paths are ignored; allocates the bridge's scratch (about 90 MB) on the current device.  launch():
+ * allocates nothing; its first call with a given set of slab pointers encodes their descriptors (host work and one
+ * small memset: make it outside stream capture).  sorted_weights_f32, route_scale_workspace_f32 and partials_f16
+ * are accepted for signature compatibility and not used: at 768 rows the rows between down and combine stay FP32.
+ * status(): no counterpart in the reference; word 3 counts routing entries that name the shared expert in a routed
+ * slot or a routed expert in slot 8 (such a call's output is invalid). */
+int netra_moe_prefill_m768_load(const char* unused_producer_path, const char* unused_reducer_path);
+int netra_moe_prefill_m768_launch(const void* hidden_fp8, const float* hidden_scale_f32,
+                                  const void* w13_fp8, const float* w13_scale_f32,
+                                  const void* w2_fp8, const float* w2_scale_f32,
+                                  const int32_t* sorted_token_ids_i32, const float* sorted_weights_f32,
+                                  const int32_t* sorted_expert_ids_i32, const int32_t* num_valid_ids_i32,
+                                  const float* topk_weights_f32, float* route_scale_workspace_f32,
+                                  void* partials_f16, void* output_bf16, cudaStream_t stream);
+int netra_moe_prefill_m768_status(uint32_t status_out[4]);
+int netra_moe_prefill_m768_unload(void);
+const char* netra_moe_prefill_m768_last_error(void);
 
 /* ------------------------------------------------------------------ fused layer */
 typedef struct netra_moe_layer netra_moe_layer_t;
@@ -295,7 +321,8 @@ int netra_moe_layer_set_gemm_mode(netra_moe_layer_t* layer, uint32_t mode);
 /* Router of calls above 1024 rows.  mode 0 (default): BF16 tensor-core pass with FP32 accumulation, then an FP64
  * recomputation of those logits that can reach the top 8 and whose BF16 rounding the FP32 value cannot decide:
  * the selected ids, their logits and the routing weights are those of the exactly rounded dot products; logits
- * of experts that cannot be selected are within one BF16 step of it.  mode 2: the same with every undecided
+ * of experts that cannot be selected keep the rounded tensor-core value (within 2^-18 |h| |w| plus one BF16
+ * spacing of the exact rounding).  mode 2: the same with every undecided
  * logit recomputed, so that the whole logits array is the exactly rounded one (several times slower).  mode 1:
  * every logit on the FP64 tensor cores (the form used up to 1024 rows). */
 int netra_moe_layer_set_router_mode(netra_moe_layer_t* layer, uint32_t mode);

@@ -17,6 +17,7 @@ MODEL_FORMAT = "netra-model-1"
 REQUIRED_CONSTANTS = ("hidden", "intermediate", "routed_experts", "top_k", "shared_experts", "scale_block", "sm_count")
 SORT_SINGLE_BLOCK_MAX_ROWS = 1024
 SORT_SEGMENT_PAIRS = 1024
+ROUTER_FP64_MAX_ROWS = 1024      # above: BF16 tensor-core router + exact recomputation of the selectable undecided logits
 
 
 def load_model(path: Path) -> dict[str, Any]:
@@ -45,6 +46,11 @@ def load_model(path: Path) -> dict[str, Any]:
     options.setdefault("weight_layout", "tiles128")
     if options["weight_layout"] not in ("tiles128", "row_major"):
         raise ValidationError(f"{path}: weight_layout must be tiles128 or row_major")
+    # rows between the down projection and the combine where the token-major kernels run: "f32" (decode contract) or
+    # "f16" (the reference's prefill contract: FP16 partial rows, kernels/gfx950/templates/moe/prefill/route_reduce_splitk2_f16.inc)
+    options.setdefault("prefill_partials", "f32")
+    if options["prefill_partials"] not in ("f32", "f16"):
+        raise ValidationError(f"{path}: prefill_partials must be f32 or f16")
     return doc
 
 
@@ -104,6 +110,11 @@ def routed_moe_layer_graph(model: dict[str, Any], profile: ShapeProfile) -> Grap
         tensors.append(Tensor("shared_weight", "fp32", (m,), "input", m * 4))
     if segmented:
         tensors.append(Tensor("seg_hist", "int32", (nseg, experts), "workspace", nseg * experts * 4))
+    tensor_core_router = m > ROUTER_FP64_MAX_ROWS
+    if tensor_core_router:
+        tensors += [Tensor("logits_f32", "fp32", (m, experts), "workspace", m * experts * 4),
+                    Tensor("wnorm", "fp32", (experts,), "workspace", experts * 4),
+                    Tensor("router_stats", "uint32", (4,), "workspace", 16)]
 
     routing_constants = {"hidden": hidden, "routed_experts": experts}
     gemm_constants = {"hidden": hidden, "intermediate": inter, "scale_block": c["scale_block"], "tile_rows": 128}
@@ -112,21 +123,36 @@ def routed_moe_layer_graph(model: dict[str, Any], profile: ShapeProfile) -> Grap
     token_major = m * c["top_k"] >= 32 * experts
     form = ("token_major" if token_major else "swap_ab") + ".sorted_rows." + ("tiles128" if opt["weight_layout"] == "tiles128" else "row_major")
     maps = "tmap2" if token_major else "tmap4"
+    f16_rows = token_major and opt["prefill_partials"] == "f16"   # the rows keep the down_f32 buffer (half of it is used)
 
     def op(name, family, operation, inputs, outputs, constants, sem):
         return Operation(name, "fixed_kernel", family, operation, tuple(inputs), tuple(outputs),
                          {"constants": constants, "semantics": sem, "fallback": f"framework.{operation}"})
 
     optional_inputs = [t for t, on in (("router_bias", opt["router_bias"]), ("shared_weight", opt["shared_weight"])) if on]
-    ops = [
-        op("router_logits", "moe_routing", "router_logits", ["hidden", "router_weight"], ["logits"], routing_constants,
-           semantics("router_logits.ptr3_u32.v1", "bf16_bf16_to_bf16", "none", "row_major", "exact_dot_rne_bf16.v1")),
-        op("topk_quant", "moe_routing", "softmax_top8_shared_slot_fp8_quant",
-           ["logits", "hidden", *optional_inputs], ["topk_ids", "topk_weights", "a_fp8", "a_scale"],
-           {**routing_constants, "top_k": c["top_k"], "scale_block": c["scale_block"]},
-           semantics("topk_quant.ptr8_u32x2.v1", "bf16_to_i32_f32_fp8e4m3_f32", "fp8_e4m3_per_token_block128_amax448",
-                     "slot9_shared_last.token_rows_after_pairs", "logit_desc_id_asc.fp32_softmax_renorm.v1")),
-    ]
+    if tensor_core_router:
+        ops = [
+            op("router_logits", "moe_routing", "router_logits_tensor_core", ["hidden", "router_weight"], ["logits_f32", "wnorm", "status"],
+               routing_constants,
+               semantics("router_umma.tmap2_ptr3_u32_ptr.v1", "bf16_bf16_to_f32", "none", "row_major", "tcgen05_f16_fp32_accumulate.approximate.v1")),
+            op("topk_quant", "moe_routing", "softmax_top8_exact_fixup_fp8_quant",
+               ["logits_f32", "wnorm", "router_weight", "hidden", *optional_inputs],
+               ["logits", "topk_ids", "topk_weights", "a_fp8", "a_scale", "router_stats"],
+               {**routing_constants, "top_k": c["top_k"], "scale_block": c["scale_block"]},
+               semantics("topk_quant_fix.ptr12_u32x3.v1", "f32_bf16_to_bf16_i32_f32_fp8e4m3_f32", "fp8_e4m3_per_token_block128_amax448",
+                         "slot9_shared_last.token_rows_after_pairs",
+                         "exact_dot_rne_bf16_for_selectable.logit_desc_id_asc.fp32_softmax_renorm.v1")),
+        ]
+    else:
+        ops = [
+            op("router_logits", "moe_routing", "router_logits", ["hidden", "router_weight"], ["logits"], routing_constants,
+               semantics("router_logits.ptr3_u32.v1", "bf16_bf16_to_bf16", "none", "row_major", "exact_dot_rne_bf16.v1")),
+            op("topk_quant", "moe_routing", "softmax_top8_shared_slot_fp8_quant",
+               ["logits", "hidden", *optional_inputs], ["topk_ids", "topk_weights", "a_fp8", "a_scale"],
+               {**routing_constants, "top_k": c["top_k"], "scale_block": c["scale_block"]},
+               semantics("topk_quant.ptr8_u32x2.v1", "bf16_to_i32_f32_fp8e4m3_f32", "fp8_e4m3_per_token_block128_amax448",
+                         "slot9_shared_last.token_rows_after_pairs", "logit_desc_id_asc.fp32_softmax_renorm.v1")),
+        ]
     if segmented:
         ops += [
             op("sort_hist", "moe_sort", "sort_histogram", ["topk_ids"], ["seg_hist"], {"routed_experts": experts, "top_k": c["top_k"]},
@@ -152,11 +178,13 @@ def routed_moe_layer_graph(model: dict[str, Any], profile: ShapeProfile) -> Grap
                      form, "kblock_fma_ascending.silu_fp32.bf16_round_then_amax.v1")),
         op("down", "moe_fp8_grouped_gemm", "down_projection", ["h_fp8", "h_scale", "w2", "w2_scale", "offsets"],
            ["down_f32", "status"], gemm_constants,
-           semantics(f"down_grouped.{maps}_ptr4_u32x2_ptr.v1", "fp8e4m3_fp8e4m3_to_f32", "fp8_e4m3_w128x128_a1x128_amax448",
-                     form, "kblock_fma_ascending.v1")),
+           semantics(f"down_grouped.{maps}_ptr4_u32x2_ptr.v1", "fp8e4m3_fp8e4m3_to_f16" if f16_rows else "fp8e4m3_fp8e4m3_to_f32",
+                     "fp8_e4m3_w128x128_a1x128_amax448", form,
+                     "kblock_fma_ascending.f16_partial_rows.v1" if f16_rows else "kblock_fma_ascending.v1")),
         op("combine", "moe_combine", "weighted_slot_combine", ["down_f32", "topk_weights", "inv_perm"], ["output"],
            {"hidden": hidden, "top_k": c["top_k"]},
-           semantics("combine.ptr4_u32.v1", "f32_f32_to_bf16", "none", "sorted_rows_first.token_rows_after_pairs",
-                     "slot_ascending_mul_add_fp32_rne_bf16.v1")),
+           semantics("combine.ptr4_u32.v1", "f16_f32_to_bf16" if f16_rows else "f32_f32_to_bf16", "none",
+                     "sorted_rows_first.token_rows_after_pairs",
+                     "slot_ascending_widen_mul_add_fp32_rne_bf16.v1" if f16_rows else "slot_ascending_mul_add_fp32_rne_bf16.v1")),
     ]
     return Graph(f"{model['name']}@{profile.name}", tuple(tensors), tuple(ops))

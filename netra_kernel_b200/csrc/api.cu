@@ -616,3 +616,6 @@ int netra_moe_layer_destroy(netra_moe_layer_t* layer) {
 
 // Entry point with library-owned scratch (needs fail(), fail_cuda(), check_launch() from above).
 #include "static_scratch_sort.cu"
+
+// The reference's 768-row prefill bridge on this library's stages (needs launch_stage() from above).
+#include "prefill_m768_bridge.cu"

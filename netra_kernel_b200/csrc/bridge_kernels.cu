@@ -151,12 +151,15 @@ netra_qwen36_shared_gate_append_sm100(int32_t* __restrict__ out_ids, float* __re
                                       const int32_t* __restrict__ ids, const float* __restrict__ w, uint32_t rows) {
   const int t = blockIdx.x, lane = threadIdx.x;
   if (t >= (int)rows) return;
-  float part = 0.0f;
+  // The gate is defined exactly so that it can be compared bit for bit: logit = the exact dot product rounded once to
+  // BF16 (FP64 accumulation of exact products), gate = sigmoid(logit) evaluated in FP64 and rounded once to BF16.
+  double part = 0.0;
   for (int k = lane; k < kHidden; k += 32)
-    part = fmaf(bf16_bits_to_f32(hidden[(size_t)t * kHidden + k]), bf16_bits_to_f32(gate_w[k]), part);
-  part = warp_sum(part);
-  const float logit = bf16_round(part);
-  const float gate = bf16_round(1.0f / (1.0f + expf(-logit)));
+    part = fma((double)bf16_bits_to_f32(hidden[(size_t)t * kHidden + k]), (double)bf16_bits_to_f32(gate_w[k]), part);
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) part += __shfl_xor_sync(0xffffffffu, part, d);
+  const double logit = (double)bf16_bits_to_f32(f64_to_bf16_bits(part));
+  const float gate = bf16_bits_to_f32(f64_to_bf16_bits(1.0 / (1.0 + exp(-logit))));
   if (lane < kTopK) {
     out_ids[t * kSlots + lane] = ids[t * kTopK + lane];
     out_w[t * kSlots + lane] = w[t * kTopK + lane];

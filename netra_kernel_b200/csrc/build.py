@@ -14,7 +14,7 @@ LIB = HERE / "libnetra_sm100.so"
 CUBIN = HERE / "netra_moe_sm100a.cubin"
 SOURCES = ["api.cu", "engine.cpp"]
 DEPENDS = ["api.cu", "engine.cpp", "kernels_cubin.cu", "common.cuh", "route_kernels.cu", "bridge_kernels.cu",
-           "umma_kernels.cu", "umma_tokmajor.cu", "router_umma.cu", "ep_kernels.cu", "mxfp4_kernels.cu", "ep_p2p.cu", "static_scratch_sort.cu", "../../include/netra_moe.h", "../../include/netra_engine.h"]
+           "umma_kernels.cu", "umma_tokmajor.cu", "router_umma.cu", "ep_kernels.cu", "mxfp4_kernels.cu", "ep_p2p.cu", "static_scratch_sort.cu", "prefill_m768_bridge.cu", "../../include/netra_moe.h", "../../include/netra_engine.h"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-ccbin", "g++"]
 NVCC_FLAGS = [*ARCH_FLAGS, "--shared", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 

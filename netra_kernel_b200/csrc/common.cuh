@@ -28,6 +28,20 @@ __device__ __forceinline__ float bf16_bits_to_f32(uint32_t bits16) { return __ui
 
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
+// One rounding FP64 -> BF16 (nearest even).  Results below the smallest normal BF16 are flushed to zero
+// (signed), results at or above 2^128 become infinity, NaN stays NaN (quiet, sign kept).
+__device__ __forceinline__ uint16_t f64_to_bf16_bits(double d) {
+  long long bits = __double_as_longlong(d);
+  uint16_t sign = (uint16_t)(((unsigned long long)bits >> 63) << 15);
+  long long mag = bits & 0x7fffffffffffffffLL;
+  if (mag > 0x7ff0000000000000LL) return (uint16_t)(sign | 0x7fc0u);   // NaN
+  long long r = (mag + ((1LL << 44) - 1) + ((mag >> 45) & 1)) >> 45;
+  r -= (896LL << 7);
+  if (r < (1 << 7)) r = 0;
+  if (r > 0x7f80) r = 0x7f80;                                            // overflow and infinity
+  return (uint16_t)(sign | (uint16_t)r);
+}
+
 __device__ __forceinline__ uint8_t f32_to_e4m3(float x) {
   return (uint8_t)__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
 }

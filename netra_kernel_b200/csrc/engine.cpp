@@ -165,9 +165,14 @@ const std::string& as_text(const Json& v, const char* name) {
   return v.string;
 }
 
+// A file of the engine directory could not be read (reported as NETRA_STATUS_IO, not as a malformed manifest).
+struct IoFailure : std::runtime_error {
+  using std::runtime_error::runtime_error;
+};
+
 std::string read_file(const std::string& path) {
   std::ifstream in(path, std::ios::binary);
-  if (!in) throw std::runtime_error("cannot open " + path);
+  if (!in) throw IoFailure("cannot open " + path);
   std::ostringstream ss; ss << in.rdbuf();
   return ss.str();
 }
@@ -417,45 +422,99 @@ struct netra_engine {
 
 namespace {
 
-netra_status_t fail(netra_engine* e, netra_status_t status, const char* message) {
-  if (e) std::snprintf(e->last_error.data(), e->last_error.size(), "%s", message);
+// ---- error reporting ------------------------------------------------------------------------------
+// Every refusal is a (status, text) pair; the text goes to the engine's 512-byte buffer when there is an engine.
+netra_status_t refuse(netra_engine* e, netra_status_t status, const char* text) {
+  if (e) std::snprintf(e->last_error.data(), e->last_error.size(), "%s", text);
   return status;
 }
-netra_status_t cuda_fail(netra_engine* e, const char* what, cudaError_t err) {
-  if (e) std::snprintf(e->last_error.data(), e->last_error.size(), "%s: %s", what, cudaGetErrorString(err));
+netra_status_t runtime_error(netra_engine* e, const char* call, cudaError_t err) {
+  if (e) std::snprintf(e->last_error.data(), e->last_error.size(), "%s returned %s", call, cudaGetErrorString(err));
   return NETRA_STATUS_CUDA;
 }
-netra_status_t driver_fail(netra_engine* e, const char* what, CUresult err) {
-  if (e) std::snprintf(e->last_error.data(), e->last_error.size(), "%s: CUresult %d", what, (int)err);
+netra_status_t driver_error(netra_engine* e, const char* call, CUresult err) {
+  if (e) std::snprintf(e->last_error.data(), e->last_error.size(), "%s returned CUresult %d", call, (int)err);
   return NETRA_STATUS_CUDA;
+}
+void clear_error(netra_engine* e) { e->last_error[0] = '\0'; }
+
+// A failure while an engine is being built: carries the status the caller will see.  The text outlives the
+// half-built engine in a thread-local buffer (netra_engine_create_error).
+struct CreateFailure {
+  netra_status_t status;
+  std::string text;
+};
+thread_local std::array<char, 512> g_create_error{};
+
+[[noreturn]] void create_fail(netra_status_t status, const std::string& text) { throw CreateFailure{status, text}; }
+
+// ---- launching -------------------------------------------------------------------------------------
+// Counts a caller as being inside a launch entry point for as long as the object lives (destroy answers BUSY meanwhile).
+class InFlight {
+ public:
+  explicit InFlight(netra_engine* e) : e_(e) { e_->in_flight.fetch_add(1, std::memory_order_acq_rel); }
+  ~InFlight() { e_->in_flight.fetch_sub(1, std::memory_order_acq_rel); }
+  InFlight(const InFlight&) = delete;
+  InFlight& operator=(const InFlight&) = delete;
+
+ private:
+  netra_engine* e_;
+};
+
+bool shape_within(const netra_profile_info_t& g, const netra_launch_shape_t& s) {
+  const bool m_ok = g.min_m <= s.m && s.m <= g.max_m;
+  const bool batch_ok = g.min_batch <= s.batch && s.batch <= g.max_batch;
+  const bool seq_ok = g.min_sequence <= s.sequence && s.sequence <= g.max_sequence;
+  return m_ok && batch_ok && seq_ok && s.tensor_parallel == g.tensor_parallel;
 }
 
-bool guard_matches(const netra_profile_info_t& info, const netra_launch_shape_t& shape) {
-  return shape.m >= info.min_m && shape.m <= info.max_m && shape.batch >= info.min_batch && shape.batch <= info.max_batch &&
-         shape.sequence >= info.min_sequence && shape.sequence <= info.max_sequence &&
-         shape.tensor_parallel == info.tensor_parallel;
+// What all three launch entry points establish first: the arguments name a profile (and an operation) of this engine, the
+// calling thread's current device is the engine's, and the shape passes the profile's guards.
+struct LaunchContext {
+  ProfileRecord* profile = nullptr;
+  OpRecord* op = nullptr;     // only for the per-operation entry points
+};
+
+netra_status_t open_launch(netra_engine* e, uint32_t profile_id, const uint32_t* operation_index, const netra_launch_shape_t* shape,
+                           LaunchContext* ctx) {
+  if (!e || !shape || profile_id >= e->profiles.size()) return NETRA_STATUS_INVALID_ARGUMENT;
+  ProfileRecord& profile = e->profiles[profile_id];
+  if (operation_index && *operation_index >= profile.operations.size()) return NETRA_STATUS_INVALID_ARGUMENT;
+  int current = -1;
+  const cudaError_t err = cudaGetDevice(&current);
+  if (err != cudaSuccess) return runtime_error(e, "cudaGetDevice", err);
+  if (current != e->device_id)
+    return refuse(e, NETRA_STATUS_UNSUPPORTED_TARGET, "the calling thread's current device is not the device this engine was created on");
+  if (!shape_within(profile.info, *shape))
+    return refuse(e, NETRA_STATUS_UNSUPPORTED_PROFILE, "launch shape is outside this profile's m / batch / sequence / tensor-parallel guards");
+  ctx->profile = &profile;
+  ctx->op = operation_index ? &profile.operations[*operation_index] : nullptr;
+  return NETRA_STATUS_OK;
 }
 
 netra_status_t launch_record(netra_engine* e, OpRecord& op, void** addresses, cudaStream_t stream) {
-  const CUresult r = driver().LaunchKernel(op.function, op.spec.grid[0], op.spec.grid[1], op.spec.grid[2], op.spec.block[0],
-                                           op.spec.block[1], op.spec.block[2], op.spec.dynamic_lds_bytes, (CUstream)stream,
-                                           addresses, nullptr);
-  return r == CUDA_SUCCESS ? NETRA_STATUS_OK : driver_fail(e, "cuLaunchKernel", r);
+  const OpSpec& k = op.spec;
+  const CUresult r = driver().LaunchKernel(op.function, k.grid[0], k.grid[1], k.grid[2], k.block[0], k.block[1], k.block[2],
+                                           k.dynamic_lds_bytes, (CUstream)stream, addresses, nullptr);
+  return r == CUDA_SUCCESS ? NETRA_STATUS_OK : driver_error(e, "cuLaunchKernel", r);
+}
+
+bool has_unbound_slot(const OpRecord& op) {
+  for (uint32_t i = 0; i < op.argc; ++i)
+    if (op.slots[i].spec.bindable && op.slots[i].pointer == nullptr) return true;
+  return false;
 }
 
 netra_status_t launch_one(netra_engine* e, OpRecord& op, cudaStream_t stream) {
-  if (op.spec.fallback) return fail(e, NETRA_STATUS_FALLBACK_REQUIRED, "operation requires framework fallback");
-  for (uint32_t i = 0; i < op.argc; ++i)
-    if (op.slots[i].spec.bindable && !op.slots[i].pointer) return fail(e, NETRA_STATUS_BINDING, "kernel pointer argument is unbound");
+  if (op.spec.fallback) return refuse(e, NETRA_STATUS_FALLBACK_REQUIRED, "this operation has no fixed kernel: the framework must run it");
+  if (has_unbound_slot(op)) return refuse(e, NETRA_STATUS_BINDING, "a pointer argument of this operation was never bound");
   return launch_record(e, op, op.addresses, stream);
 }
 
 netra_status_t direct_launch(netra_engine* e, ProfileRecord& profile, cudaStream_t stream) {
-  for (auto& op : profile.operations) {
-    const netra_status_t s = launch_one(e, op, stream);
-    if (s != NETRA_STATUS_OK) return s;
-  }
-  return NETRA_STATUS_OK;
+  netra_status_t status = NETRA_STATUS_OK;
+  for (size_t i = 0; i < profile.operations.size() && status == NETRA_STATUS_OK; ++i) status = launch_one(e, profile.operations[i], stream);
+  return status;
 }
 
 void release(netra_engine* e) {
@@ -467,6 +526,119 @@ void release(netra_engine* e) {
     for (auto& kv : e->modules)
       if (kv.second) (void)driver().ModuleUnload(kv.second);
   if (e->workspace) (void)cudaFree(e->workspace);
+}
+
+// ---- engine construction (throws CreateFailure) ------------------------------------------------------
+void check_target(netra_engine* e, const Manifest& manifest) {
+  int major = 0, warp = 0;
+  (void)cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, e->device_id);
+  (void)cudaDeviceGetAttribute(&warp, cudaDevAttrWarpSize, e->device_id);
+  if (major != 10 || warp != 32) create_fail(NETRA_STATUS_UNSUPPORTED_TARGET, "device is not compute capability 10.x with 32-wide warps");
+  int version = 0;
+  const cudaError_t err = cudaDriverGetVersion(&version);
+  if (err != cudaSuccess) create_fail(NETRA_STATUS_CUDA, std::string("cudaDriverGetVersion returned ") + cudaGetErrorString(err));
+  const std::pair<uint32_t, uint32_t> have{(uint32_t)(version / 1000), (uint32_t)((version % 1000) / 10)};
+  if (have < manifest.required_cuda)
+    create_fail(NETRA_STATUS_UNSUPPORTED_TARGET, "the installed driver supports CUDA " + std::to_string(have.first) + "." + std::to_string(have.second) +
+                                                     ", the engine requires " + std::to_string(manifest.required_cuda.first) + "." +
+                                                     std::to_string(manifest.required_cuda.second));
+}
+
+CUmodule load_code_object(netra_engine* e, const std::string& relative) {
+  CUmodule& module = e->modules[relative];
+  if (module) return module;
+  std::string image;
+  try {
+    image = read_file(e->directory + "/" + relative);
+  } catch (const std::exception& ex) {
+    create_fail(NETRA_STATUS_IO, ex.what());
+  }
+  const CUresult r = driver().ModuleLoadData(&module, image.data());
+  if (r != CUDA_SUCCESS) create_fail(NETRA_STATUS_CUDA, "cuModuleLoadData(" + relative + ") returned CUresult " + std::to_string((int)r));
+  return module;
+}
+
+void resolve_kernel(netra_engine* e, OpRecord& op) {
+  const OpSpec& k = op.spec;
+  CUresult r = driver().ModuleGetFunction(&op.function, load_code_object(e, k.cubin), k.symbol.c_str());
+  if (r != CUDA_SUCCESS) create_fail(NETRA_STATUS_CUDA, "cuModuleGetFunction(" + k.symbol + ") returned CUresult " + std::to_string((int)r));
+  if (k.dynamic_lds_bytes > 48 * 1024) {
+    r = driver().FuncSetAttribute(op.function, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)k.dynamic_lds_bytes);
+    if (r != CUDA_SUCCESS) create_fail(NETRA_STATUS_CUDA, "cuFuncSetAttribute(" + k.symbol + ", dynamic shared memory) returned CUresult " + std::to_string((int)r));
+  }
+  if (k.registers_per_thread) {
+    // kernels that move registers between warpgroups (setmaxnreg) only work for the allocation they were written for
+    int regs = 0;
+    r = driver().FuncGetAttribute(&regs, CU_FUNC_ATTRIBUTE_NUM_REGS, op.function);
+    if (r != CUDA_SUCCESS) create_fail(NETRA_STATUS_CUDA, "cuFuncGetAttribute(" + k.symbol + ", registers) returned CUresult " + std::to_string((int)r));
+    if ((uint32_t)regs != k.registers_per_thread)
+      create_fail(NETRA_STATUS_MANIFEST, k.symbol + " was built with " + std::to_string(regs) + " registers per thread, the contract requires " +
+                                             std::to_string(k.registers_per_thread));
+  }
+}
+
+void wire_arguments(netra_engine* e, OpRecord& op) {
+  op.argc = (uint32_t)op.spec.args.size();
+  op.slots.reset(new ArgSlot[op.argc]);
+  for (uint32_t i = 0; i < op.argc; ++i) {
+    ArgSlot& slot = op.slots[i];
+    slot.spec = op.spec.args[i];
+    switch (slot.spec.kind) {
+      case ArgSpec::U32:
+        slot.scalar = slot.spec.value;
+        op.addresses[i] = &slot.scalar;
+        break;
+      case ArgSpec::TensorMap:
+      case ArgSpec::Pointer:
+        if (!slot.spec.bindable && !slot.spec.null_pointer)
+          slot.pointer = static_cast<unsigned char*>(e->workspace) + slot.spec.workspace_offset;
+        if (slot.spec.kind == ArgSpec::TensorMap) {
+          if (!slot.spec.bindable) {   // workspace tensor: the descriptor is final now; bound tensors get theirs in bind()
+            if (!encode_map(&slot.map, slot.pointer, slot.spec.map))
+              create_fail(NETRA_STATUS_CUDA, "cuTensorMapEncodeTiled refused the workspace tensor behind argument " + std::to_string(i) + " of " + op.spec.symbol);
+            slot.map_ready = true;
+          }
+          op.addresses[i] = &slot.map;
+        } else {
+          op.addresses[i] = &slot.pointer;
+        }
+        break;
+    }
+  }
+}
+
+void build_engine(netra_engine* e) {
+  (void)cudaFree(nullptr);   // make the primary context current for the driver entry points
+  if (!driver().ok) create_fail(NETRA_STATUS_UNSUPPORTED_TARGET, "the CUDA driver does not export the entry points this runtime needs");
+  Manifest manifest;
+  try {
+    manifest = parse_manifest(e->directory);
+  } catch (const IoFailure& ex) {
+    create_fail(NETRA_STATUS_IO, ex.what());
+  } catch (const std::exception& ex) {
+    create_fail(NETRA_STATUS_MANIFEST, ex.what());
+  }
+  check_target(e, manifest);
+  e->workspace_bytes = manifest.workspace_bytes;
+  if (e->workspace_bytes) {
+    cudaError_t err = cudaMalloc(&e->workspace, (size_t)e->workspace_bytes);
+    if (err != cudaSuccess) create_fail(NETRA_STATUS_CUDA, std::string("cudaMalloc(workspace) returned ") + cudaGetErrorString(err));
+    err = cudaMemset(e->workspace, 0, (size_t)e->workspace_bytes);
+    if (err != cudaSuccess) create_fail(NETRA_STATUS_CUDA, std::string("cudaMemset(workspace) returned ") + cudaGetErrorString(err));
+  }
+  e->profiles.resize(manifest.profiles.size());
+  for (size_t p = 0; p < manifest.profiles.size(); ++p) {
+    ProfileRecord& profile = e->profiles[p];
+    profile.info = manifest.profiles[p].info;
+    profile.operations.resize(manifest.operations.size());
+    for (size_t o = 0; o < manifest.operations.size(); ++o) {
+      OpRecord& op = profile.operations[o];
+      op.spec = manifest.operations[o];
+      if (op.spec.fallback) continue;
+      resolve_kernel(e, op);
+      wire_arguments(e, op);
+    }
+  }
 }
 
 }  // namespace
@@ -483,107 +655,49 @@ extern "C" netra_status_t netra_engine_check_manifest(const char* directory, cha
   }
 }
 
+extern "C" const char* netra_engine_create_error(void) { return g_create_error.data(); }
+
 extern "C" netra_status_t netra_engine_create(const char* directory, const netra_engine_options_t* options,
                                               netra_engine_t** output) {
+  g_create_error[0] = '\0';
   if (!directory || !*directory || !options || !output || options->struct_size != sizeof(netra_engine_options_t))
     return NETRA_STATUS_INVALID_ARGUMENT;
   *output = nullptr;
-  netra_engine* e = new (std::nothrow) netra_engine;
-  if (!e) return NETRA_STATUS_IO;
-  int previous = -1;
-  try {
+  int caller_device = -1;
+  if (cudaGetDevice(&caller_device) != cudaSuccess) {
+    std::snprintf(g_create_error.data(), g_create_error.size(), "cudaGetDevice failed: no usable CUDA device");
+    return NETRA_STATUS_CUDA;
+  }
+  if (cudaSetDevice(options->device_id) != cudaSuccess) {
+    std::snprintf(g_create_error.data(), g_create_error.size(), "cudaSetDevice(%d) failed", (int)options->device_id);
+    (void)cudaGetLastError();
+    return NETRA_STATUS_CUDA;
+  }
+  std::unique_ptr<netra_engine> e(new (std::nothrow) netra_engine);
+  netra_status_t status = NETRA_STATUS_OK;
+  if (!e) {
+    status = NETRA_STATUS_IO;
+    std::snprintf(g_create_error.data(), g_create_error.size(), "out of host memory");
+  } else {
     e->directory = directory;
     e->device_id = options->device_id;
     e->graph_enabled = options->enable_graph_capture != 0;
-    cudaError_t err = cudaGetDevice(&previous);
-    if (err != cudaSuccess) { delete e; return NETRA_STATUS_CUDA; }
-    err = cudaSetDevice(e->device_id);
-    if (err != cudaSuccess) { delete e; return NETRA_STATUS_CUDA; }
-    int major = 0, warp = 0;
-    (void)cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, e->device_id);
-    (void)cudaDeviceGetAttribute(&warp, cudaDevAttrWarpSize, e->device_id);
-    if (major != 10 || warp != 32) { (void)cudaSetDevice(previous); delete e; return NETRA_STATUS_UNSUPPORTED_TARGET; }
-    (void)cudaFree(nullptr);   // make the primary context current for the driver entry points
-    if (!driver().ok) throw std::runtime_error("CUDA driver entry points are unavailable");
-    const Manifest manifest = parse_manifest(e->directory);
-    int driver_version = 0;
-    err = cudaDriverGetVersion(&driver_version);
-    if (err != cudaSuccess) throw std::runtime_error(std::string("cudaDriverGetVersion: ") + cudaGetErrorString(err));
-    const std::pair<uint32_t, uint32_t> actual{(uint32_t)(driver_version / 1000), (uint32_t)((driver_version % 1000) / 10)};
-    if (actual < manifest.required_cuda) throw std::runtime_error("CUDA driver is older than required_cuda.minimum");
-    e->workspace_bytes = manifest.workspace_bytes;
-    if (e->workspace_bytes) {
-      err = cudaMalloc(&e->workspace, (size_t)e->workspace_bytes);
-      if (err != cudaSuccess) { const auto s = cuda_fail(e, "cudaMalloc(workspace)", err); (void)cudaSetDevice(previous); delete e; return s; }
-      (void)cudaMemset(e->workspace, 0, (size_t)e->workspace_bytes);
+    try {
+      build_engine(e.get());
+    } catch (const CreateFailure& f) {
+      status = f.status;
+      std::snprintf(g_create_error.data(), g_create_error.size(), "%s", f.text.c_str());
+    } catch (const std::exception& ex) {   // nothing may cross the C boundary
+      status = NETRA_STATUS_MANIFEST;
+      std::snprintf(g_create_error.data(), g_create_error.size(), "%s", ex.what());
     }
-    for (const ProfileSpec& pspec : manifest.profiles) {
-      e->profiles.emplace_back();
-      ProfileRecord& profile = e->profiles.back();
-      profile.info = pspec.info;
-      profile.operations.reserve(manifest.operations.size());
-      for (const OpSpec& ospec : manifest.operations) {
-        profile.operations.emplace_back();
-        OpRecord& op = profile.operations.back();
-        op.spec = ospec;
-        if (ospec.fallback) continue;
-        CUmodule& module = e->modules[ospec.cubin];
-        if (!module) {
-          const std::string image = read_file(e->directory + "/" + ospec.cubin);
-          const CUresult r = driver().ModuleLoadData(&module, image.data());
-          if (r != CUDA_SUCCESS) throw std::runtime_error("cuModuleLoadData(" + ospec.cubin + "): CUresult " + std::to_string((int)r));
-        }
-        CUresult r = driver().ModuleGetFunction(&op.function, module, ospec.symbol.c_str());
-        if (r != CUDA_SUCCESS) throw std::runtime_error("cuModuleGetFunction(" + ospec.symbol + "): CUresult " + std::to_string((int)r));
-        if (ospec.dynamic_lds_bytes > 48 * 1024) {
-          r = driver().FuncSetAttribute(op.function, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)ospec.dynamic_lds_bytes);
-          if (r != CUDA_SUCCESS) throw std::runtime_error("cuFuncSetAttribute(max dynamic shared memory): CUresult " + std::to_string((int)r));
-        }
-        if (ospec.registers_per_thread) {
-          // kernels that move registers between warpgroups (setmaxnreg) only work for the allocation they were written for
-          int regs = 0;
-          r = driver().FuncGetAttribute(&regs, CU_FUNC_ATTRIBUTE_NUM_REGS, op.function);
-          if (r != CUDA_SUCCESS) throw std::runtime_error("cuFuncGetAttribute(registers): CUresult " + std::to_string((int)r));
-          if ((uint32_t)regs != ospec.registers_per_thread)
-            throw std::runtime_error(ospec.symbol + " was built with " + std::to_string(regs) + " registers per thread, the contract requires " +
-                                     std::to_string(ospec.registers_per_thread));
-        }
-        op.argc = (uint32_t)ospec.args.size();
-        op.slots.reset(new ArgSlot[op.argc]);
-        for (uint32_t i = 0; i < op.argc; ++i) {
-          ArgSlot& slot = op.slots[i];
-          slot.spec = ospec.args[i];
-          if (slot.spec.kind == ArgSpec::U32) {
-            slot.scalar = slot.spec.value;
-            op.addresses[i] = &slot.scalar;
-          } else {
-            if (!slot.spec.bindable && !slot.spec.null_pointer)
-              slot.pointer = static_cast<unsigned char*>(e->workspace) + slot.spec.workspace_offset;
-            if (slot.spec.kind == ArgSpec::TensorMap) {
-              if (!slot.spec.bindable) {
-                if (!encode_map(&slot.map, slot.pointer, slot.spec.map)) throw std::runtime_error("cuTensorMapEncodeTiled failed for a workspace tensor map");
-                slot.map_ready = true;
-              }
-              op.addresses[i] = &slot.map;
-            } else {
-              op.addresses[i] = &slot.pointer;
-            }
-          }
-        }
-      }
-    }
-    (void)cudaSetDevice(previous);
-    e->last_error[0] = '\0';
-    *output = e;
-    return NETRA_STATUS_OK;
-  } catch (const std::exception& ex) {
-    // the message is lost with the engine; callers that need it use netra_engine_check_manifest
-    (void)ex;
-    release(e);
-    if (previous >= 0) (void)cudaSetDevice(previous);
-    delete e;
-    return NETRA_STATUS_MANIFEST;
+    if (status != NETRA_STATUS_OK) release(e.get());
   }
+  (void)cudaSetDevice(caller_device);   // the caller's current device is restored on every path
+  if (status != NETRA_STATUS_OK) return status;
+  clear_error(e.get());
+  *output = e.release();
+  return NETRA_STATUS_OK;
 }
 
 extern "C" size_t netra_engine_profile_count(const netra_engine_t* e) { return e ? e->profiles.size() : 0; }
@@ -595,161 +709,144 @@ extern "C" netra_status_t netra_engine_query_profile(const netra_engine_t* e, ui
   return NETRA_STATUS_OK;
 }
 
+// ---- control plane: the caller serialises these -------------------------------------------------------
 extern "C" netra_status_t netra_engine_bind(netra_engine_t* e, uint32_t profile_id, uint32_t operation_index,
                                             uint32_t argument_index, void* pointer) {
   if (!e || !pointer) return NETRA_STATUS_INVALID_ARGUMENT;
-  if (e->bindings_finalized.load(std::memory_order_acquire)) return fail(e, NETRA_STATUS_BUSY, "bindings are finalized and immutable");
-  if (e->in_flight.load(std::memory_order_acquire)) return fail(e, NETRA_STATUS_BUSY, "cannot bind during launch");
-  if (profile_id >= e->profiles.size() || operation_index >= e->profiles[profile_id].operations.size())
-    return fail(e, NETRA_STATUS_BINDING, "binding index out of range");
+  // once the table is frozen (explicitly, by a captured graph, or while a launch reads it) it cannot change
+  if (e->bindings_finalized.load(std::memory_order_acquire))
+    return refuse(e, NETRA_STATUS_BUSY, "the binding table was frozen by finalize_bindings");
+  if (e->in_flight.load(std::memory_order_acquire)) return refuse(e, NETRA_STATUS_BUSY, "a launch call is reading the binding table");
+  if (profile_id >= e->profiles.size()) return refuse(e, NETRA_STATUS_BINDING, "no such profile");
   ProfileRecord& profile = e->profiles[profile_id];
-  if (profile.graph_prepared) return fail(e, NETRA_STATUS_BUSY, "bindings are immutable after graph preparation");
+  if (operation_index >= profile.operations.size()) return refuse(e, NETRA_STATUS_BINDING, "no such operation in this profile");
+  if (profile.graph_prepared) return refuse(e, NETRA_STATUS_BUSY, "this profile's graph already holds the bound pointers");
   OpRecord& op = profile.operations[operation_index];
-  if (argument_index >= op.argc) return fail(e, NETRA_STATUS_BINDING, "argument index out of range");
+  if (argument_index >= op.argc) return refuse(e, NETRA_STATUS_BINDING, "no such argument in this operation");
   ArgSlot& slot = op.slots[argument_index];
-  if (!slot.spec.bindable) return fail(e, NETRA_STATUS_BINDING, "constant kernel arguments cannot be rebound");
+  if (!slot.spec.bindable) return refuse(e, NETRA_STATUS_BINDING, "this argument is a constant or a workspace tensor, not a binding slot");
   if (slot.spec.kind == ArgSpec::TensorMap) {
-    if (((uintptr_t)pointer & 15) != 0) return fail(e, NETRA_STATUS_BINDING, "tensor-map pointers must be 16-byte aligned");
-    if (!encode_map(&slot.map, pointer, slot.spec.map)) return fail(e, NETRA_STATUS_BINDING, "cuTensorMapEncodeTiled rejected the bound pointer");
+    if ((reinterpret_cast<uintptr_t>(pointer) & 15u) != 0)
+      return refuse(e, NETRA_STATUS_BINDING, "a tensor read through a TMA descriptor must start on a 16-byte boundary");
+    if (!encode_map(&slot.map, pointer, slot.spec.map))
+      return refuse(e, NETRA_STATUS_BINDING, "cuTensorMapEncodeTiled refused the pointer bound to this tensor-map slot");
     slot.map_ready = true;
   }
   slot.pointer = pointer;
-  e->last_error[0] = '\0';
+  clear_error(e);
   return NETRA_STATUS_OK;
 }
 
 extern "C" netra_status_t netra_engine_finalize_bindings(netra_engine_t* e) {
   if (!e) return NETRA_STATUS_INVALID_ARGUMENT;
-  if (e->in_flight.load(std::memory_order_acquire)) return fail(e, NETRA_STATUS_BUSY, "cannot finalize bindings during launch");
-  for (const auto& profile : e->profiles)
-    for (const auto& op : profile.operations)
-      for (uint32_t i = 0; i < op.argc; ++i)
-        if (op.slots[i].spec.bindable && !op.slots[i].pointer)
-          return fail(e, NETRA_STATUS_BINDING, "all direct-launch pointers must be bound before finalization");
+  if (e->in_flight.load(std::memory_order_acquire)) return refuse(e, NETRA_STATUS_BUSY, "a launch call is reading the binding table");
+  for (const ProfileRecord& profile : e->profiles)
+    for (const OpRecord& op : profile.operations)
+      if (has_unbound_slot(op)) return refuse(e, NETRA_STATUS_BINDING, "every binding slot of every operation must be bound before the table is frozen");
   e->bindings_finalized.store(true, std::memory_order_release);
-  e->last_error[0] = '\0';
+  clear_error(e);
   return NETRA_STATUS_OK;
 }
 
 extern "C" netra_status_t netra_engine_prepare_profile(netra_engine_t* e, uint32_t profile_id, cudaStream_t stream) {
   if (!e || profile_id >= e->profiles.size()) return NETRA_STATUS_INVALID_ARGUMENT;
   ProfileRecord& profile = e->profiles[profile_id];
-  if (!e->graph_enabled) return NETRA_STATUS_OK;
-  if (profile.graph_prepared) return NETRA_STATUS_OK;
-  if (profile.info.requires_fallback) return fail(e, NETRA_STATUS_FALLBACK_REQUIRED, "fallback profile cannot be captured by Netra runtime");
-  const netra_status_t finalized = netra_engine_finalize_bindings(e);
-  if (finalized != NETRA_STATUS_OK) return finalized;
+  if (!e->graph_enabled || profile.graph_prepared) return NETRA_STATUS_OK;   // nothing to capture, or captured already
+  if (profile.info.requires_fallback)
+    return refuse(e, NETRA_STATUS_FALLBACK_REQUIRED, "a profile with a framework-fallback operation cannot be captured by this runtime");
+  if (const netra_status_t frozen = netra_engine_finalize_bindings(e)) return frozen;
   cudaError_t err = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal);
-  if (err != cudaSuccess) return cuda_fail(e, "cudaStreamBeginCapture", err);
-  const netra_status_t status = direct_launch(e, profile, stream);
-  if (status != NETRA_STATUS_OK) {
-    (void)cudaStreamEndCapture(stream, &profile.graph);
-    if (profile.graph) (void)cudaGraphDestroy(profile.graph);
-    profile.graph = nullptr;
-    return status;
+  if (err != cudaSuccess) return runtime_error(e, "cudaStreamBeginCapture", err);
+  const netra_status_t enqueued = direct_launch(e, profile, stream);
+  cudaGraph_t captured = nullptr;
+  err = cudaStreamEndCapture(stream, &captured);   // always ends the capture, also after a refused launch
+  if (enqueued != NETRA_STATUS_OK || err != cudaSuccess) {
+    if (captured) (void)cudaGraphDestroy(captured);
+    return enqueued != NETRA_STATUS_OK ? enqueued : runtime_error(e, "cudaStreamEndCapture", err);
   }
-  err = cudaStreamEndCapture(stream, &profile.graph);
-  if (err != cudaSuccess) return cuda_fail(e, "cudaStreamEndCapture", err);
-  err = cudaGraphInstantiate(&profile.graph_exec, profile.graph, 0);
-  if (err != cudaSuccess) return cuda_fail(e, "cudaGraphInstantiate", err);
+  err = cudaGraphInstantiate(&profile.graph_exec, captured, 0);
+  if (err != cudaSuccess) {
+    (void)cudaGraphDestroy(captured);
+    return runtime_error(e, "cudaGraphInstantiate", err);
+  }
+  profile.graph = captured;
   profile.graph_prepared = true;
   return NETRA_STATUS_OK;
 }
 
+// ---- hot path: no allocation, no synchronisation, no file or string work ---------------------------------
 extern "C" netra_status_t netra_engine_launch(netra_engine_t* e, uint32_t profile_id, const netra_launch_shape_t* shape,
                                               cudaStream_t stream) {
-  if (!e || !shape || profile_id >= e->profiles.size()) return NETRA_STATUS_INVALID_ARGUMENT;
-  int device = -1;
-  const cudaError_t err = cudaGetDevice(&device);
-  if (err != cudaSuccess) return cuda_fail(e, "cudaGetDevice", err);
-  if (device != e->device_id) return fail(e, NETRA_STATUS_UNSUPPORTED_TARGET, "caller stream/device does not belong to engine device");
-  ProfileRecord& profile = e->profiles[profile_id];
-  if (!guard_matches(profile.info, *shape))
-    return fail(e, NETRA_STATUS_UNSUPPORTED_PROFILE, "exact/bounded profile guard failed; framework fallback required");
-  if (profile.info.requires_fallback) return fail(e, NETRA_STATUS_FALLBACK_REQUIRED, "profile contains a framework fallback operation");
+  LaunchContext ctx;
+  if (const netra_status_t s = open_launch(e, profile_id, nullptr, shape, &ctx)) return s;
+  ProfileRecord& profile = *ctx.profile;
+  if (profile.info.requires_fallback)
+    return refuse(e, NETRA_STATUS_FALLBACK_REQUIRED, "this profile contains an operation the framework must run");
   if (!profile.graph_prepared && !e->bindings_finalized.load(std::memory_order_acquire))
-    return fail(e, NETRA_STATUS_BINDING, "direct-launch bindings were not finalized");
-  e->in_flight.fetch_add(1, std::memory_order_acq_rel);
-  netra_status_t status;
-  if (profile.graph_prepared) {
-    const cudaError_t launch = cudaGraphLaunch(profile.graph_exec, stream);
-    status = launch == cudaSuccess ? NETRA_STATUS_OK : cuda_fail(e, "cudaGraphLaunch", launch);
-  } else {
-    status = direct_launch(e, profile, stream);
-  }
-  e->in_flight.fetch_sub(1, std::memory_order_acq_rel);
-  return status;
+    return refuse(e, NETRA_STATUS_BINDING, "call finalize_bindings (or prepare_profile) before the first launch");
+  InFlight guard(e);
+  if (!profile.graph_prepared) return direct_launch(e, profile, stream);
+  const cudaError_t err = cudaGraphLaunch(profile.graph_exec, stream);
+  return err == cudaSuccess ? NETRA_STATUS_OK : runtime_error(e, "cudaGraphLaunch", err);
 }
 
 extern "C" netra_status_t netra_engine_launch_operation(netra_engine_t* e, uint32_t profile_id, uint32_t operation_index,
                                                         const netra_launch_shape_t* shape, cudaStream_t stream) {
-  if (!e || !shape || profile_id >= e->profiles.size() || operation_index >= e->profiles[profile_id].operations.size())
-    return NETRA_STATUS_INVALID_ARGUMENT;
-  int device = -1;
-  const cudaError_t err = cudaGetDevice(&device);
-  if (err != cudaSuccess) return cuda_fail(e, "cudaGetDevice", err);
-  if (device != e->device_id) return fail(e, NETRA_STATUS_UNSUPPORTED_TARGET, "caller stream/device does not belong to engine device");
-  ProfileRecord& profile = e->profiles[profile_id];
-  if (!guard_matches(profile.info, *shape))
-    return fail(e, NETRA_STATUS_UNSUPPORTED_PROFILE, "exact/bounded profile guard failed; framework fallback required");
-  if (profile.graph_prepared) return fail(e, NETRA_STATUS_BUSY, "individual operations cannot launch after graph preparation");
-  if (profile.operations[operation_index].spec.fallback) return fail(e, NETRA_STATUS_FALLBACK_REQUIRED, "operation requires framework fallback");
-  if (!e->bindings_finalized.load(std::memory_order_acquire)) return fail(e, NETRA_STATUS_BINDING, "direct-launch bindings were not finalized");
-  e->in_flight.fetch_add(1, std::memory_order_acq_rel);
-  const netra_status_t status = launch_one(e, profile.operations[operation_index], stream);
-  e->in_flight.fetch_sub(1, std::memory_order_acq_rel);
-  return status;
+  LaunchContext ctx;
+  if (const netra_status_t s = open_launch(e, profile_id, &operation_index, shape, &ctx)) return s;
+  if (ctx.profile->graph_prepared)
+    return refuse(e, NETRA_STATUS_BUSY, "this profile runs as a captured graph: its operations can no longer be launched one by one");
+  if (ctx.op->spec.fallback) return refuse(e, NETRA_STATUS_FALLBACK_REQUIRED, "this operation has no fixed kernel: the framework must run it");
+  if (!e->bindings_finalized.load(std::memory_order_acquire))
+    return refuse(e, NETRA_STATUS_BINDING, "call finalize_bindings before the first launch");
+  InFlight guard(e);
+  return launch_one(e, *ctx.op, stream);
 }
 
 extern "C" netra_status_t netra_engine_launch_operation_bound(netra_engine_t* e, uint32_t profile_id, uint32_t operation_index,
                                                               const netra_launch_shape_t* shape,
                                                               const netra_pointer_binding_t* bindings, uint32_t binding_count,
                                                               cudaStream_t stream) {
-  if (!e || !shape || profile_id >= e->profiles.size() || operation_index >= e->profiles[profile_id].operations.size() ||
-      (binding_count && !bindings) || binding_count > 16)
-    return NETRA_STATUS_INVALID_ARGUMENT;
-  int device = -1;
-  const cudaError_t err = cudaGetDevice(&device);
-  if (err != cudaSuccess) return cuda_fail(e, "cudaGetDevice", err);
-  if (device != e->device_id) return fail(e, NETRA_STATUS_UNSUPPORTED_TARGET, "caller stream/device does not belong to engine device");
-  ProfileRecord& profile = e->profiles[profile_id];
-  if (!guard_matches(profile.info, *shape))
-    return fail(e, NETRA_STATUS_UNSUPPORTED_PROFILE, "exact/bounded profile guard failed; framework fallback required");
-  if (profile.graph_prepared) return fail(e, NETRA_STATUS_BUSY, "operation bindings are immutable after graph preparation");
-  OpRecord& op = profile.operations[operation_index];
-  if (op.spec.fallback) return fail(e, NETRA_STATUS_FALLBACK_REQUIRED, "operation requires framework fallback");
-  uint32_t expected = 0;
-  for (uint32_t i = 0; i < op.argc; ++i)
-    if (op.slots[i].spec.bindable) ++expected;
-  if (binding_count != expected) return fail(e, NETRA_STATUS_BINDING, "bound operation must provide every declared pointer slot");
+  if ((binding_count != 0 && bindings == nullptr) || binding_count > 16) return NETRA_STATUS_INVALID_ARGUMENT;
+  LaunchContext ctx;
+  if (const netra_status_t s = open_launch(e, profile_id, &operation_index, shape, &ctx)) return s;
+  if (ctx.profile->graph_prepared)
+    return refuse(e, NETRA_STATUS_BUSY, "this profile runs as a captured graph: per-call pointers cannot be supplied any more");
+  OpRecord& op = *ctx.op;
+  if (op.spec.fallback) return refuse(e, NETRA_STATUS_FALLBACK_REQUIRED, "this operation has no fixed kernel: the framework must run it");
+
+  // The call must name each binding slot of the operation exactly once.  `seen` has one bit per argument.
+  uint32_t seen = 0, slots = 0;
+  for (uint32_t i = 0; i < op.argc; ++i) slots += op.slots[i].spec.bindable ? 1u : 0u;
   for (uint32_t i = 0; i < binding_count; ++i) {
-    const uint32_t arg = bindings[i].argument_index;
-    if (bindings[i].reserved || !bindings[i].pointer || arg >= op.argc || !op.slots[arg].spec.bindable)
-      return fail(e, NETRA_STATUS_BINDING, "bound operation contains an invalid pointer slot");
-    for (uint32_t prev = 0; prev < i; ++prev)
-      if (bindings[prev].argument_index == arg) return fail(e, NETRA_STATUS_BINDING, "bound operation contains a duplicate pointer slot");
+    const netra_pointer_binding_t& b = bindings[i];
+    if (b.reserved != 0 || b.pointer == nullptr || b.argument_index >= op.argc || !op.slots[b.argument_index].spec.bindable)
+      return refuse(e, NETRA_STATUS_BINDING, "a per-call binding names no binding slot of this operation, or carries a null pointer");
+    if (seen & (1u << b.argument_index)) return refuse(e, NETRA_STATUS_BINDING, "a binding slot appears twice in the per-call bindings");
+    seen |= 1u << b.argument_index;
   }
-  // caller-local launch storage: concurrent calls cannot mix pointer sets
-  void* values[kMaxArguments];
+  if (binding_count != slots) return refuse(e, NETRA_STATUS_BINDING, "the per-call bindings must cover every binding slot of the operation");
+
+  // Argument storage private to this call, so that concurrent calls with different pointers cannot interfere.
+  void* pointers[kMaxArguments];
   void* addresses[kMaxArguments];
-  alignas(64) CUtensorMap local_maps[16];
+  alignas(64) CUtensorMap maps[16];
   uint32_t maps_used = 0;
   for (uint32_t i = 0; i < op.argc; ++i) addresses[i] = op.addresses[i];
   for (uint32_t i = 0; i < binding_count; ++i) {
     const uint32_t arg = bindings[i].argument_index;
-    if (op.slots[arg].spec.kind == ArgSpec::TensorMap) {
-      if (((uintptr_t)bindings[i].pointer & 15) != 0 || !encode_map(&local_maps[maps_used], bindings[i].pointer, op.slots[arg].spec.map))
-        return fail(e, NETRA_STATUS_BINDING, "cuTensorMapEncodeTiled rejected a bound pointer");
-      addresses[arg] = &local_maps[maps_used++];
-    } else {
-      values[arg] = bindings[i].pointer;
-      addresses[arg] = &values[arg];
+    if (op.slots[arg].spec.kind != ArgSpec::TensorMap) {
+      pointers[arg] = bindings[i].pointer;
+      addresses[arg] = &pointers[arg];
+      continue;
     }
+    const bool aligned = (reinterpret_cast<uintptr_t>(bindings[i].pointer) & 15u) == 0;
+    if (!aligned || !encode_map(&maps[maps_used], bindings[i].pointer, op.slots[arg].spec.map))
+      return refuse(e, NETRA_STATUS_BINDING, "cuTensorMapEncodeTiled refused a per-call pointer (tensor-map slots need 16-byte alignment)");
+    addresses[arg] = &maps[maps_used++];
   }
-  e->in_flight.fetch_add(1, std::memory_order_acq_rel);
-  const netra_status_t status = launch_record(e, op, addresses, stream);
-  e->in_flight.fetch_sub(1, std::memory_order_acq_rel);
-  return status;
+  InFlight guard(e);
+  return launch_record(e, op, addresses, stream);
 }
 
 extern "C" const char* netra_engine_last_error(const netra_engine_t* e) { return e ? e->last_error.data() : "netra_engine is null"; }
@@ -758,7 +855,7 @@ extern "C" void* netra_engine_workspace(const netra_engine_t* e) { return e ? e-
 
 extern "C" netra_status_t netra_engine_destroy(netra_engine_t* e) {
   if (!e) return NETRA_STATUS_OK;
-  if (e->in_flight.load(std::memory_order_acquire)) return fail(e, NETRA_STATUS_BUSY, "launches remain in flight");
+  if (e->in_flight.load(std::memory_order_acquire)) return refuse(e, NETRA_STATUS_BUSY, "a launch call is still inside the runtime");
   release(e);
   delete e;
   return NETRA_STATUS_OK;

@@ -22,20 +22,6 @@ namespace netra {
 // over one quarter of K; the four K-quarters are added in fixed order through shared memory.
 // grid (ceil(rows/16), 8); see the two entry points below.
 // ------------------------------------------------------------------------------------------
-// One rounding FP64 -> BF16 (nearest even).  Results below the smallest normal BF16 are flushed to zero
-// (signed), results at or above 2^128 become infinity, NaN stays NaN (quiet, sign kept).
-__device__ __forceinline__ uint16_t f64_to_bf16_bits(double d) {
-  long long bits = __double_as_longlong(d);
-  uint16_t sign = (uint16_t)(((unsigned long long)bits >> 63) << 15);
-  long long mag = bits & 0x7fffffffffffffffLL;
-  if (mag > 0x7ff0000000000000LL) return (uint16_t)(sign | 0x7fc0u);   // NaN
-  long long r = (mag + ((1LL << 44) - 1) + ((mag >> 45) & 1)) >> 45;
-  r -= (896LL << 7);
-  if (r < (1 << 7)) r = 0;
-  if (r > 0x7f80) r = 0x7f80;                                            // overflow and infinity
-  return (uint16_t)(sign | (uint16_t)r);
-}
-
 // exact BF16 -> FP64 with integer ops (the FP64 pipe is kept for the MMAs)
 __device__ __forceinline__ double bf16_bits_to_f64(uint32_t b) {
   const uint32_t e = b & 0x7f80u;
@@ -193,43 +179,6 @@ __device__ __forceinline__ void quantize_hidden_row(uint8_t* __restrict__ a_fp8,
   quantize_loaded_row(a_fp8, a_scale, x, t, row_base, lane);
 }
 
-// The same row kept as 32 packed BF16 pairs (half the registers), and its quantisation from that form.
-__device__ __forceinline__ void load_hidden_row_packed(uint32_t xb[32], const uint16_t* __restrict__ hidden, int t, int lane) {
-  const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)t * kHidden) + lane * 8;
-#pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    const uint4 v = src[c];
-    xb[4 * c] = v.x; xb[4 * c + 1] = v.y; xb[4 * c + 2] = v.z; xb[4 * c + 3] = v.w;
-  }
-}
-
-__device__ __forceinline__ void quantize_packed_row(uint8_t* __restrict__ a_fp8, float* __restrict__ a_scale, const uint32_t xb[32],
-                                                    int t, uint32_t row_base, int lane) {
-  float amax = amax_floor();
-#pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    amax = fmaxf(amax, fabsf(bf16_bits_to_f32(xb[i] & 0xffffu)));
-    amax = fmaxf(amax, fabsf(bf16_bits_to_f32(xb[i] >> 16)));
-  }
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-  const float scale = amax * inv448();
-  const float inv = 1.0f / scale;
-  const size_t row = (size_t)row_base + t;
-  if ((lane & 1) == 0) a_scale[row * kHiddenBlocks + (lane >> 1)] = scale;
-  uint4* dst = reinterpret_cast<uint4*>(a_fp8 + row * kHidden) + lane * 4;
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    uint32_t w[4];
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const uint32_t p0 = xb[c * 8 + q * 2], p1 = xb[c * 8 + q * 2 + 1];
-      w[q] = f32x4_to_e4m3x4(bf16_bits_to_f32(p0 & 0xffffu) * inv, bf16_bits_to_f32(p0 >> 16) * inv,
-                             bf16_bits_to_f32(p1 & 0xffffu) * inv, bf16_bits_to_f32(p1 >> 16) * inv);
-    }
-    dst[c] = make_uint4(w[0], w[1], w[2], w[3]);
-  }
-}
-
 // ------------------------------------------------------------------------------------------
 // Softmax / top-8 / renormalise + shared slot + per-token FP8 quantisation.  One warp per token.
 // Selection key is (z desc, expert id asc) with z = f32(logit) + bias; weights are
@@ -340,10 +289,9 @@ netra_moe_topk_quant_sm100(int32_t* __restrict__ ids9, float* __restrict__ w9,
 // largest logit, so the eight best approximate z prove that the true eighth-best z is at least
 // v8 - delta, and an expert with z < v8 - 2 delta cannot be selected whatever its exact value.  The
 // selected ids, their exact logits and therefore the routing weights are those of the contract; logits of
-// experts out of reach keep bf16(a), at most one BF16 step from the contract value.
+// experts out of reach keep bf16(a), within bound[e] plus one BF16 spacing of the contract value.
 // exact_all != 0: every undecided logit is recomputed, and the logits array equals the contract everywhere.
-// One warp per token; the token's hidden row is read once and serves the bound, the FP64 dots and the FP8
-// quantisation.  stats[0] counts recomputed logits.  grid ceil(rows/4), block 128.
+// One warp per token.  stats[0] counts recomputed logits.  grid ceil(rows/4), block 128.
 // ------------------------------------------------------------------------------------------
 constexpr float kRouterErrScale = 3.8146973e-06f;   // 2^-18
 
@@ -358,14 +306,20 @@ netra_moe_topk_quant_fix_sm100(int32_t* __restrict__ ids9, float* __restrict__ w
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
   if (t >= (int)rows) return;
-  uint32_t xb[32];
-  load_hidden_row_packed(xb, hidden, t, lane);
+  // The row is read three times instead of being held in registers (it would cost a third of the occupancy): here for
+  // its norm (from DRAM), in the rare FP64 recomputation and for the quantisation at the end (from the caches).
+  const uint4* hrow = reinterpret_cast<const uint4*>(hidden + (size_t)t * kHidden) + lane * 8;
   float hn = 0.0f;
 #pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    const float a = bf16_bits_to_f32(xb[i] & 0xffffu), b = bf16_bits_to_f32(xb[i] >> 16);
-    hn = fmaf(a, a, hn);
-    hn = fmaf(b, b, hn);
+  for (int c = 0; c < 8; ++c) {
+    const uint4 hv = __ldg(hrow + c);
+    const uint32_t u[4] = {hv.x, hv.y, hv.z, hv.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float a = bf16_bits_to_f32(u[q] & 0xffffu), b = bf16_bits_to_f32(u[q] >> 16);
+      hn = fmaf(a, a, hn);
+      hn = fmaf(b, b, hn);
+    }
   }
   hn = sqrtf(warp_sum(hn)) * 1.001f;
   float v[8], bs[8];      // contract candidates bf16(a) and the bias
@@ -420,19 +374,16 @@ netra_moe_topk_quant_fix_sm100(int32_t* __restrict__ ids9, float* __restrict__ w
     const int src = __ffs(any) - 1;
     const int i = __ffs(__shfl_sync(0xffffffffu, pending, src)) - 1;
     const uint4* wrow = reinterpret_cast<const uint4*>(router_w + (size_t)(src * 8 + i) * kHidden) + lane * 8;
-    uint4 wv[8];
-#pragma unroll
-    for (int c = 0; c < 8; ++c) wv[c] = __ldg(wrow + c);          // all eight loads in flight before the first use
     double acc0 = 0.0, acc1 = 0.0;                                // two chains: the FP64 pipe has latency to hide
-#pragma unroll
+#pragma unroll 2
     for (int c = 0; c < 8; ++c) {
-      const uint32_t u[4] = {wv[c].x, wv[c].y, wv[c].z, wv[c].w};
+      const uint4 wv = __ldg(wrow + c), hv = __ldg(hrow + c);
+      const uint32_t u[4] = {wv.x, wv.y, wv.z, wv.w};
+      const uint32_t x[4] = {hv.x, hv.y, hv.z, hv.w};
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        uint32_t h = xb[4 * c + q];
-        asm volatile("" : "+r"(h));   // keeps the 64 conversions of the row inside the loop (hoisted, they would cost 128 registers)
-        acc0 = fma(bf16_bits_to_f64_nobranch(h & 0xffffu), bf16_bits_to_f64_nobranch(u[q] & 0xffffu), acc0);
-        acc1 = fma(bf16_bits_to_f64_nobranch(h >> 16), bf16_bits_to_f64_nobranch(u[q] >> 16), acc1);
+        acc0 = fma(bf16_bits_to_f64_nobranch(x[q] & 0xffffu), bf16_bits_to_f64_nobranch(u[q] & 0xffffu), acc0);
+        acc1 = fma(bf16_bits_to_f64_nobranch(x[q] >> 16), bf16_bits_to_f64_nobranch(u[q] >> 16), acc1);
       }
     }
     double acc = acc0 + acc1;
@@ -456,7 +407,7 @@ netra_moe_topk_quant_fix_sm100(int32_t* __restrict__ ids9, float* __restrict__ w
   }
   if (!selected || fixed != 0) softmax_top8_select(z, lane, sel_id, sel_p, sel_z);   // `fixed` is the same in every lane
   top8_store(ids9, w9, sel_id, sel_p, shared_w, t, lane);
-  quantize_packed_row(a_fp8, a_scale, xb, t, row_base, lane);
+  quantize_hidden_row(a_fp8, a_scale, hidden, t, row_base, lane);
 }
 
 // The same outputs from a top-k computed elsewhere (a serving stack that keeps its own fused top-k, the

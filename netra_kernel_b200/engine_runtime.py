@@ -51,6 +51,7 @@ ENGINE_SIGNATURES = {
     "netra_engine_destroy": (ctypes.c_int, [c_void_p]),
     "netra_engine_check_manifest": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_size_t]),
     "netra_engine_workspace": (c_void_p, [c_void_p]),
+    "netra_engine_create_error": (ctypes.c_char_p, []),
 }
 
 _typed = False
@@ -92,8 +93,7 @@ class EngineSession:
         handle = c_void_p()
         rc = self.lib.netra_engine_create(str(self.directory).encode(), ctypes.byref(options), ctypes.byref(handle))
         if rc != 0:
-            _, message = check_manifest(self.directory)
-            raise EngineError(rc, "netra_engine_create", message)
+            raise EngineError(rc, "netra_engine_create", self.lib.netra_engine_create_error().decode(errors="replace"))
         self.handle = handle
         self._keep = []
         guards = self.manifest["profiles"][0]["guards"]

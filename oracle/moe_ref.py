@@ -126,6 +126,16 @@ def router_logits(hidden_bits: np.ndarray, router_bits: np.ndarray) -> np.ndarra
     return f64_to_bf16_bits(h @ w.T)
 
 
+def shared_gate(hidden_bits: np.ndarray, gate_bits: np.ndarray) -> np.ndarray:
+    """Shared-expert gate of ``runtime/gfx950/routing/decode/qwen36_shared_gate_append_bridge.h:10-23``: BF16 bit
+    patterns of sigmoid(hidden . gate_w) per row.  Defined exactly: the logit is the exact dot product rounded once to
+    BF16, the gate is the sigmoid of that BF16 logit evaluated in FP64 and rounded once to BF16."""
+    h = bf16_bits_to_f32(hidden_bits).astype(np.float64)
+    g = bf16_bits_to_f32(gate_bits).astype(np.float64)
+    logit = bf16_bits_to_f32(f64_to_bf16_bits(h @ g)).astype(np.float64)
+    return f64_to_bf16_bits(1.0 / (1.0 + np.exp(-logit)))
+
+
 def route_topk(logit_bits: np.ndarray, bias: np.ndarray | None = None):
     """-> ids int32 [T,8] (logit desc, id asc), weights f32 [T,8] renormalised softmax."""
     z = bf16_bits_to_f32(logit_bits)

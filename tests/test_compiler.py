@@ -140,11 +140,29 @@ def test_catalog_launch_constants_match_the_built_library():
     lib = abi.load()
     tactics = {t.name: t for t in catalog.load_fixed_tactic_catalog(LIB_ROOT, TARGET)}
     for which, name in ((0, "gate_up_silu_requant_umma_swapab_tiles128"), (1, "down_projection_umma_swapab_tiles128"),
-                        (2, "gate_up_silu_requant_umma_tokmajor_tiles128"), (3, "down_projection_umma_tokmajor_row_major")):
+                        (2, "gate_up_silu_requant_umma_tokmajor_tiles128"), (3, "down_projection_umma_tokmajor_row_major"),
+                        (4, "down_projection_umma_tokmajor_f16_tiles128"), (5, "router_logits_f32_bf16_umma")):
         block, smem = ctypes.c_uint32(), ctypes.c_uint32()
         assert lib.netra_moe_kernel_launch_info(which, ctypes.byref(block), ctypes.byref(smem)) == 0
         assert tactics[name].launch["block"][0] == block.value
         assert tactics[name].launch["dynamic_lds_bytes"] == smem.value
+
+
+def test_prefill_profile_selects_the_tensor_core_router_and_the_fp16_row_tactics(tmp_path):
+    """Above 1,024 rows the router pair changes (tensor-core pass + exact fix-up); the prefill model manifest asks for FP16
+    partial rows, which only the token-major profiles can serve - the decode profile of the same model keeps FP32 rows."""
+    prefill = LIB_ROOT / "manifests" / TARGET / "models" / "routed-moe-layer-fp8-prefill.json"
+    picked = {o["name"]: o["tactic"] for o in compile_engine(prefill, "prefill_t8192", tmp_path / "p", copy_cubin=False)["operations"]}
+    assert picked["router_logits"] == "router_logits_f32_bf16_umma" and picked["topk_quant"] == "softmax_top8_quant_exact_fixup"
+    assert picked["down"] == "down_projection_umma_tokmajor_f16_tiles128" and picked["combine"] == "combine_slot_ordered_f16_partials"
+    decode = {o["name"]: o["tactic"] for o in compile_engine(prefill, "decode_t256", tmp_path / "d", copy_cubin=False)["operations"]}
+    assert decode["router_logits"] == "router_logits_bf16_fp64_mma_k8" and decode["combine"] == "combine_slot_ordered_fp32"
+    plain = {o["name"]: o["tactic"] for o in compile_engine(MODEL, "prefill_t8192", tmp_path / "q", copy_cubin=False)["operations"]}
+    assert plain["down"] == "down_projection_umma_tokmajor_tiles128" and plain["combine"] == "combine_slot_ordered_fp32"
+    contracts_p = json.loads((tmp_path / "p" / "contracts.json").read_text())["contracts"]
+    contracts_q = json.loads((tmp_path / "q" / "contracts.json").read_text())["contracts"]
+    numerical = lambda cs, op: next(c["semantics"]["numerical"] for c in cs if c["operation"] == op)
+    assert numerical(contracts_p, "down_projection") != numerical(contracts_q, "down_projection")     # a numerical id of its own
 
 
 def _plan(model_path, profile_name, **kw):

@@ -122,6 +122,29 @@ def test_engine_with_bias_shared_weight_row_major_and_segmented_sort(tmp_path, e
     assert m["max_abs"] <= helpers.MAX_ABS and m["rel_l2"] <= helpers.REL_L2, m
 
 
+def test_engine_prefill_manifest_runs_the_fp16_partial_row_tactics(tmp_path, expert_weights):
+    """The prefill model manifest (router bias, FP16 partial rows) at 2,048 tokens through the engine ABI: the tensor-core
+    router pair, the token-major GEMMs, the FP16-row down projection and its reducer, against the checker run with the same
+    rounding point."""
+    tokens = 2048
+    tensors, hidden, router_w, bias = _tensors(expert_weights, tokens, zipf_alpha=0.8, seed=4)
+    subset = np.arange(1, tokens, 97)
+    ref = R.moe_layer(helpers.bits(hidden), helpers.bits(router_w), *helpers.np_weights(expert_weights), bias=bias.numpy(),
+                      token_subset=subset, partials="f16")
+    session = _session(tmp_path, MANIFESTS / "routed-moe-layer-fp8-prefill.json", "ep8_local_t2048", tensors)
+    symbols = [o["kernel_symbol"] for o in session.manifest["operations"]]
+    assert symbols[:2] == ["netra_router_logits_f32_umma_sm100", "netra_moe_topk_quant_fix_sm100"]
+    assert symbols[-2:] == ["netra_moe_down_tokmajor_f16_sm100", "netra_moe_combine_f16_sm100"]
+    session.prepare(_stream())
+    session.launch(_stream())
+    torch.cuda.synchronize()
+    assert _status_words(session) == [0, 0, 0, 0]
+    assert np.array_equal(session.workspace_view("topk_ids", torch.int32, "cuda").cpu().numpy().reshape(tokens, 9), ref["topk_ids"])
+    assert np.array_equal(session.workspace_view("perm", torch.int32, "cuda").cpu().numpy(), ref["perm"])
+    m = R.parity_metrics(helpers.bits(tensors["output"])[subset], ref["out"])
+    assert m["max_abs"] <= helpers.MAX_ABS and m["rel_l2"] <= helpers.REL_L2, m
+
+
 def test_status_codes_for_guards_and_call_order(tmp_path, expert_weights):
     lib = er.load()
     tensors, *_ = _tensors(expert_weights, 16)
@@ -192,17 +215,65 @@ def test_engine_with_fallback_operation_refuses_to_launch(tmp_path, expert_weigh
     assert lib.netra_engine_launch_operation(session.handle, 0, 0, ctypes.byref(shape), _stream()) == 9
 
 
-def test_create_reports_a_broken_manifest_and_a_missing_cubin(tmp_path):
+def test_create_names_the_cause_of_a_failure(tmp_path):
+    """A missing code object is an IO failure, a driver older than the engine requires an unsupported target, a code
+    object that is not one a CUDA failure, a damaged engine.json a manifest failure - each with its text kept for the
+    calling thread, and the caller's current device left as it was."""
     import json
+    lib = er.load()
+    before = torch.cuda.current_device()
     compile_engine(MODEL, "cpu_t16", tmp_path / "e")
     (tmp_path / "e" / "cubin" / "netra_moe_sm100a.cubin").unlink()
     with pytest.raises(er.EngineError) as err:
         er.EngineSession(tmp_path / "e")
-    assert err.value.status == 3
+    assert err.value.status == 2 and b"cannot open" in lib.netra_engine_create_error()
     compile_engine(MODEL, "cpu_t16", tmp_path / "f")
     doc = json.loads((tmp_path / "f" / "engine.json").read_text())
     doc["required_cuda"]["minimum"] = "99.0"
     (tmp_path / "f" / "engine.json").write_text(json.dumps(doc))
     with pytest.raises(er.EngineError) as err:
         er.EngineSession(tmp_path / "f")
-    assert err.value.status == 3
+    assert err.value.status == 4 and b"requires 99.0" in lib.netra_engine_create_error()
+    compile_engine(MODEL, "cpu_t16", tmp_path / "g")
+    (tmp_path / "g" / "cubin" / "netra_moe_sm100a.cubin").write_bytes(b"not a code object" * 64)
+    with pytest.raises(er.EngineError) as err:
+        er.EngineSession(tmp_path / "g")
+    assert err.value.status == 7 and b"cuModuleLoadData" in lib.netra_engine_create_error()
+    compile_engine(MODEL, "cpu_t16", tmp_path / "h")
+    (tmp_path / "h" / "engine.json").write_text("{")
+    options = er.EngineOptions(ctypes.sizeof(er.EngineOptions), 0, 1)
+    handle = ctypes.c_void_p()
+    assert lib.netra_engine_create(str(tmp_path / "h").encode(), ctypes.byref(options), ctypes.byref(handle)) == 3
+    assert lib.netra_engine_create_error() != b"" and not handle.value
+    assert torch.cuda.current_device() == before
+    # a successful create clears the text
+    compile_engine(MODEL, "cpu_t16", tmp_path / "ok")
+    session = er.EngineSession(tmp_path / "ok")
+    assert lib.netra_engine_create_error() == b""
+    assert session.close() == 0
+
+
+def test_c_caller_runs_the_documented_sequence(tmp_path):
+    """tests/engine_abi_example.c (the sequence INTEGRATION.md documents) compiled with gcc and run on a compiled engine
+    directory: create, query_profile, bind per slot, finalize, prepare (graph capture), three launches, destroy."""
+    import json
+    import subprocess
+    from netra_kernel_b200 import abi
+    exe = tmp_path / "engine_abi_example"
+    cmd = ["gcc", "-std=c11", "-I", str(helpers.ROOT / "include"), "-I", "/usr/local/cuda/include",
+           str(helpers.ROOT / "tests" / "engine_abi_example.c"), "-o", str(exe), "-L", str(abi.LIB_PATH.parent),
+           "-l:" + abi.LIB_PATH.name, "-L", "/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath," + str(abi.LIB_PATH.parent)]
+    subprocess.run(cmd, check=True, capture_output=True)
+    for profile, m in (("cpu_t16", 16), ("decode_t256", 256)):
+        directory = tmp_path / profile
+        compile_engine(MODEL, profile, directory)
+        recipe = json.loads((directory / "graph_recipe.json").read_text())
+        sizes = {t["name"]: t["bytes"] for t in json.loads((directory / "graph.json").read_text())["tensors"]}
+        lines = [f"{name} {slot['operation']} {slot['argument']} {sizes[name]}"
+                 for name, places in sorted(recipe["binding_slots"].items()) for slot in places]
+        (directory / "slots.txt").write_text("\n".join(lines) + "\n")
+        done = subprocess.run([str(exe), str(directory), str(directory / "slots.txt"), str(m)], capture_output=True, text=True, timeout=120)
+        assert done.returncode == 0 and done.stdout.strip() == "ok", (done.returncode, done.stdout, done.stderr)
+    # a shape outside the guards is refused by the example before it binds anything
+    done = subprocess.run([str(exe), str(tmp_path / "cpu_t16"), str(tmp_path / "cpu_t16" / "slots.txt"), "17"], capture_output=True, text=True)
+    assert done.returncode == 1

@@ -8,6 +8,7 @@ import re
 
 import pytest
 
+from netra_kernel_b200 import abi
 from netra_kernel_b200 import engine_runtime as er
 from netra_kernel_b200.compiler import compile_engine
 from netra_kernel_b200.compiler.library import KernelLibrary
@@ -34,7 +35,7 @@ def test_library_exports_the_engine_abi():
     text = (helpers.ROOT / "include" / "netra_engine.h").read_text()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     declared = sorted(set(re.findall(r"\b(netra_engine_[a-z_]+)\s*\(", text)))
-    assert len(declared) == 13 and set(declared) == set(er.ENGINE_SIGNATURES)
+    assert len(declared) == 14 and set(declared) == set(er.ENGINE_SIGNATURES)
     for name in declared:
         assert hasattr(lib, name), name
     # struct layouts of runtime/gfx950/engine/netra_engine.h:27-58
@@ -139,3 +140,30 @@ def test_fused_layer_launch_path_does_not_allocate_or_synchronise():
     scratch = (helpers.ROOT / "netra_kernel_b200" / "csrc" / "static_scratch_sort.cu").read_text()
     code = re.sub(r"//.*", "", scratch)
     assert "cudaMalloc" not in code and "cudaFree" not in code
+
+
+# ------------------------------------------------------------------ the documented C caller
+def _c_example_snippet() -> str:
+    import textwrap
+    c = (helpers.ROOT / "tests" / "engine_abi_example.c").read_text()
+    begin, end = "/* [integration-snippet-begin] */\n", "  /* [integration-snippet-end] */"
+    return textwrap.dedent(c[c.index(begin) + len(begin):c.index(end)])
+
+
+def test_integration_page_quotes_the_c_example_verbatim():
+    page = (helpers.ROOT / "INTEGRATION.md").read_text()
+    assert "```c\n" + _c_example_snippet() + "```" in page, "INTEGRATION.md section 5 and tests/engine_abi_example.c have drifted apart"
+
+
+def test_c_example_compiles_and_links_against_the_header(tmp_path):
+    """gcc (C11) against include/netra_engine.h and the built library: every call of the documented sequence exists with
+    the documented argument list."""
+    import subprocess
+    out = tmp_path / "engine_abi_example"
+    cmd = ["gcc", "-std=c11", "-Wall", "-Werror=implicit-function-declaration", "-Werror=incompatible-pointer-types",
+           "-I", str(helpers.ROOT / "include"), "-I", "/usr/local/cuda/include", str(helpers.ROOT / "tests" / "engine_abi_example.c"),
+           "-o", str(out), "-L", str(abi.LIB_PATH.parent), "-l:" + abi.LIB_PATH.name, "-L", "/usr/local/cuda/lib64", "-lcudart",
+           "-Wl,-rpath," + str(abi.LIB_PATH.parent)]
+    done = subprocess.run(cmd, capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr
+    assert out.exists()

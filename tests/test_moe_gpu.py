@@ -35,23 +35,21 @@ def run_layer(layer, hidden, shared_w=None):
     return out.cpu(), inter
 
 
-def bf16_steps(a_bits: np.ndarray, b_bits: np.ndarray) -> np.ndarray:
-    """Distance of two BF16 bit patterns in representable values (sign-magnitude -> ordered integers)."""
-    def ordered(x):
-        x = x.astype(np.int32)
-        return np.where(x & 0x8000, -(x & 0x7FFF), x & 0x7FFF)
-    return np.abs(ordered(a_bits) - ordered(b_bits))
+def f32_of(bits: np.ndarray) -> np.ndarray:
+    return R.bf16_bits_to_f32(bits).astype(np.float64)
 
 
-def check_logits(inter, ref, tokens):
+def check_logits(inter, ref, tokens, bound=2.5e-4):
     """Up to 1,024 rows (and in router modes 1 and 2) every logit is the exactly rounded dot product.  Above, the default
-    router guarantees that for every logit that can reach the top 8 - checked here on the selected ones - and one BF16
-    step for the rest."""
+    router guarantees that for every logit that can reach the top 8 - checked here on the selected ones - while the rest
+    keep the rounded tensor-core value: within the accumulation bound (2^-18 |h| |w|, about 1.6e-4 for the benchmark
+    distributions) plus one BF16 spacing of the exact rounding."""
     got, want = helpers.bits(inter["logits"]), ref["logits"]
     if tokens <= 1024:
         assert np.array_equal(got, want), "router logits must be bit-exact"
         return
-    assert bf16_steps(got, want).max() <= 1, "a router logit is more than one BF16 step from the exact rounding"
+    g, w = f32_of(got), f32_of(want)
+    assert np.all(np.abs(g - w) <= bound + np.abs(w) * 2.0 ** -7), "a router logit is outside the documented bound"
     ids = ref["topk_ids"][:, :8]
     assert np.array_equal(np.take_along_axis(got, ids, 1), np.take_along_axis(want, ids, 1)), "selected logits must be bit-exact"
 
@@ -192,7 +190,7 @@ def test_tensor_core_router_against_the_fp64_router(gpu_weights, kind, tokens, s
     FP32 value cannot decide.  Mode 2 recomputes every such logit: all logits must equal the FP64 router's (mode 1), i.e.
     the correctly rounded exact dot products.  Mode 0 (default) recomputes only those that can reach the top 8: ids,
     weights, permutation and quantised rows must still be identical, the selected logits exact, every other logit within
-    one BF16 step.  The measured accumulation error must stay well inside the bound the recomputation test assumes
+    the bound plus one BF16 spacing.  The measured accumulation error must stay well inside the bound the recomputation test assumes
     (kRouterErrScale = 2^-18 of |h| |w|)."""
     hidden, router_w = _router_case(kind, tokens, seed)
     bias = synth.zipf_bias(0.5).cuda() if seed % 2 else None
@@ -217,8 +215,6 @@ def test_tensor_core_router_against_the_fp64_router(gpu_weights, kind, tokens, s
         assert torch.equal(full[key], ref[key]), ("mode 2", key)
         assert torch.equal(fast[key], ref[key]), ("mode 0", key)
     assert ref["fixed"] == 0 and 0 < fast["fixed"] < full["fixed"]
-    steps = bf16_steps(helpers.bits(fast["logits"].cpu()), helpers.bits(ref["logits"].cpu()))
-    assert steps.max() <= 1
     ids = ref["topk_ids"][:, :8].long()
     assert torch.equal(torch.gather(fast["logits"].view(torch.int16), 1, ids), torch.gather(ref["logits"].view(torch.int16), 1, ids))
     # the FP64 router against the CPU checker on a sample of rows (all rows are covered by the equalities above)
@@ -233,9 +229,14 @@ def test_tensor_core_router_against_the_fp64_router(gpu_weights, kind, tokens, s
     scale = hn * wn
     err = torch.where(scale > 1e-30, (fast["logits_f32"].double() - exact).abs() / scale.clamp_min(1e-30), torch.zeros_like(scale))
     worst = float(err.max())
+    # mode 0 leaves the logits that cannot be selected at the rounded tensor-core value: inside bound + one BF16 spacing
+    gap = (fast["logits"].double() - ref["logits"].double()).abs()
+    allowed = 1.01 * 2.0 ** -18 * scale + ref["logits"].double().abs() * 2.0 ** -7 + 1e-37
+    assert bool(torch.all(gap <= allowed))
+    off = int((fast["logits"].view(torch.int16) != ref["logits"].view(torch.int16)).sum())
     print(f"router[{kind},{tokens}]: max |f32 - exact| / (|h||w|) = {worst:.3e} (bound 2^-18 = {2.0 ** -18:.3e}); recomputed "
           f"{fast['fixed']} (mode 0) / {full['fixed']} (mode 2) of {tokens * 256} logits; "
-          f"{int((steps > 0).sum())} logits one BF16 step off in mode 0")
+          f"{off} logits differ from the exact rounding in mode 0 (none of them selectable)")
     assert worst <= 2.0 ** -20, "the tensor-core accumulation error is within a factor 4 of the bound: widen kRouterErrScale"
     assert torch.all(full["wnorm"].double() >= wn[0])
 
@@ -397,9 +398,72 @@ def test_shared_gate_append_bridge():
     ids9, w9 = moe.bridge_shared_gate_append(hidden.cuda(), gate_w.cuda(), ids8.cuda(), w8.cuda())
     assert torch.equal(ids9[:, :8].cpu(), ids8) and torch.equal(w9[:, :8].cpu(), w8)
     assert ids9[:, 8].cpu().tolist() == [256] * 5
-    logit = (hidden.double() @ gate_w.double()).float().to(torch.bfloat16).float()
-    want = torch.sigmoid(logit).to(torch.bfloat16).float()
-    assert torch.allclose(w9[:, 8].cpu(), want, atol=8e-3)
+    # bit for bit against the checker's restatement (exact BF16 logit, FP64 sigmoid, one BF16 rounding)
+    want = R.shared_gate(helpers.bits(hidden), helpers.bits(gate_w))
+    got = helpers.bits(w9[:, 8].cpu().to(torch.bfloat16))
+    assert torch.equal(w9[:, 8].cpu().to(torch.bfloat16).float(), w9[:, 8].cpu()), "the gate must be a BF16 value"
+    assert np.array_equal(got, want)
+
+
+def _aiter_sorted_ids(ids9: np.ndarray, rows: int = 768, capacity_blocks: int = 365):
+    """The routing of one call in the sorted-id format the reference's 768-row producer reads
+    (kernels/gfx950/templates/moe/prefill/fused_splitk2/entry_routing.inc:67-111): per expert (ascending id, 256 = shared) the
+    words token | slot << 24 in token order, each expert padded to whole 64-entry blocks with words whose token is >= rows."""
+    words, block_experts = [], []
+    for e in range(257):
+        tok, slot = np.nonzero(ids9 == e)
+        if tok.size == 0:
+            continue
+        w = (tok.astype(np.int64) | (slot.astype(np.int64) << 24)).tolist()
+        w += [rows | (9 << 24)] * ((-len(w)) % 64)
+        words += w
+        block_experts += [e] * (len(w) // 64)
+    assert len(block_experts) <= capacity_blocks
+    num_valid = len(words)
+    words += [rows | (9 << 24)] * (capacity_blocks * 64 - len(words))
+    block_experts += [0] * (capacity_blocks - len(block_experts))
+    return (np.array(words, np.int64).astype(np.uint32).view(np.int32), np.array(block_experts, np.int32),
+            np.array([num_valid], np.int32))
+
+
+def test_prefill_m768_bridge_matches_the_checker(expert_weights):
+    """netra_moe_prefill_m768_launch with the reference's argument list: quantised rows, row-major slabs, sorted ids of
+    64-entry expert blocks.  The output must match the checker run with the same top-k, and a second call with other
+    tokens must not see anything of the first."""
+    import ctypes
+    from netra_kernel_b200 import abi
+    lib = abi.load()
+    w13, w13_s, w2, w2_s = (t.cuda() for t in expert_weights)
+    assert lib.netra_moe_prefill_m768_launch(*([None] * 15)) == -1            # not loaded
+    abi.check(lib.netra_moe_prefill_m768_load(None, None), "prefill_m768_load")
+    abi.check(lib.netra_moe_prefill_m768_load(b"ignored", b"ignored"), "prefill_m768_load")   # idempotent
+    for seed in (11, 12):
+        hidden, router_w, _ = synth.make_activations(768, seed=seed)
+        hb, rb = helpers.bits(hidden), helpers.bits(router_w)
+        ids, w = R.route_topk(R.router_logits(hb, rb))
+        shared_w = np.linspace(0.5, 1.0, 768).astype(np.float32)
+        subset = np.arange(seed % 7, 768, 23)
+        ref = R.moe_layer(hb, rb, *helpers.np_weights(expert_weights), shared_w=shared_w, token_subset=subset, external_topk=(ids, w))
+        aq, a_s = R.quant_fp8_group128(R.bf16_bits_to_f32(hb))
+        sorted_ids, block_experts, num_valid = _aiter_sorted_ids(ref["topk_ids"])
+        dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+        t_aq, t_as, t_sorted, t_blocks, t_valid = dev(aq), dev(a_s), dev(sorted_ids), dev(block_experts), dev(num_valid)
+        t_w9 = dev(ref["topk_w"])
+        t_sw = torch.zeros(365 * 64, device="cuda")
+        scratch = torch.zeros(1024, device="cuda")
+        out = torch.zeros(768, 2048, dtype=torch.bfloat16, device="cuda")
+        rc = lib.netra_moe_prefill_m768_launch(t_aq.data_ptr(), t_as.data_ptr(), w13.data_ptr(), w13_s.data_ptr(), w2.data_ptr(),
+                                               w2_s.data_ptr(), t_sorted.data_ptr(), t_sw.data_ptr(), t_blocks.data_ptr(),
+                                               t_valid.data_ptr(), t_w9.data_ptr(), scratch.data_ptr(), scratch.data_ptr(),
+                                               out.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        abi.check(rc, "prefill_m768_launch")
+        torch.cuda.synchronize()
+        words = (ctypes.c_uint32 * 4)()
+        abi.check(lib.netra_moe_prefill_m768_status(ctypes.byref(words)), "prefill_m768_status")
+        assert list(words) == [0, 0, 0, 0]
+        m = R.parity_metrics(helpers.bits(out.cpu())[subset], ref["out"])
+        assert m["max_abs"] <= helpers.MAX_ABS and m["rel_l2"] <= helpers.REL_L2, m
+    assert lib.netra_moe_prefill_m768_unload() == 0
 
 
 def test_grouped_tensor_core_path_agrees_with_bridge_path(gpu_weights):
