@@ -70,6 +70,21 @@ int netra_qwen36_moe_down_reduce_launch(const void* activation_fp8, const float*
 int netra_qwen36_moe_down_reduce_unload(void);
 const char* netra_qwen36_moe_down_reduce_last_error(void);
 
+/* Residual add + RMSNorm + per-128 FP8 quantisation (runtime/gfx950/group_quant/verify/group_quant_assembly_bridge.h:21-31,
+ * netra_add_rmsnorm_group_quant_n5120_launch, there at width 5120; here at this model's width 2048, same argument list):
+ *   x = f32(input) + f32(residual); residual_out = bf16(x); y = bf16(x * rsqrt(mean(x^2) + epsilon) * weight);
+ *   output_bf16 = y; per 128 columns scale = max(amax |y|, 1e-10) * fl(1/448), code = e4m3_rne_sat(y / scale).
+ * Differences: scales are row-major [rows, 16] (the reference stores them group-major), the mean of squares is
+ * defined exactly (FP64 sum, one rounding) so that the result does not depend on the reduction order, rows may be
+ * any count up to 2^20.  load() ignores its six paths. */
+int netra_group_quant_assembly_load(const char* unused0, const char* unused1, const char* unused2, const char* unused3,
+                                    const char* unused4, const char* unused5);
+int netra_group_quant_assembly_unload(void);
+int netra_add_rmsnorm_group_quant_n2048_launch(const void* input_bf16, const void* residual_bf16, const void* weight_f32,
+                                               void* output_bf16, void* residual_out_bf16, void* output_fp8,
+                                               void* output_scale_f32, uint32_t rows, float epsilon, cudaStream_t stream);
+const char* netra_group_quant_assembly_last_error(void);
+
 /* The 768-row prefill call (runtime/gfx950/fp8/moe/moe_prefill_m768_bridge.h:10-23): quantised token rows
  * [768, 2048] + scales [768, 16], the expert slabs in the checkpoint's row-major layout ([257, 1024, 2048] /
  * [257, 2048, 512], slab 256 = shared expert), and the routing in the sorted-id format of the reference's fused
@@ -174,6 +189,16 @@ int netra_moe_layer_create(const netra_moe_layer_desc_t* desc, netra_moe_layer_t
 int netra_moe_layer_launch(netra_moe_layer_t* layer, const void* hidden_bf16,
                            const float* shared_weight_f32, void* output_bf16, uint32_t tokens,
                            cudaStream_t stream);
+
+/* The layer call with the upstream fusion: residual add + RMSNorm + input quantisation in one kernel (see
+ * netra_add_rmsnorm_group_quant_n2048_launch) that writes the layer's quantised token rows directly, so that the
+ * routing stage no longer reads the hidden row a second time to quantise it.  hidden_out_bf16 [tokens, 2048] receives
+ * the normalised rows (the router reads them), residual_out_bf16 the updated residual.  The result equals
+ * netra_moe_layer_launch on hidden_out_bf16 bit for bit. */
+int netra_moe_layer_launch_with_norm(netra_moe_layer_t* layer, const void* input_bf16, const void* residual_bf16,
+                                     const float* norm_weight_f32, float epsilon, void* hidden_out_bf16,
+                                     void* residual_out_bf16, const float* shared_weight_f32, void* output_bf16,
+                                     uint32_t tokens, cudaStream_t stream);
 
 /* The same layer call with a top-k computed by the caller (a serving stack that keeps its own fused top-k:
  * the reference's position, scripts/rocm/integrations/sglang/sglang-gfx1151-bf16-router.patch:64, and its

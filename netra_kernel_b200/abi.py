@@ -55,6 +55,11 @@ SIGNATURES = {
     "netra_qwen36_moe_gate_up_launch": (c_int, [c_void_p] * 6 + [c_int, c_void_p]),
     "netra_qwen36_moe_silu_mul_quant_launch": (c_int, [c_void_p] * 3 + [c_int, c_void_p]),
     "netra_qwen36_moe_down_reduce_launch": (c_int, [c_void_p] * 7 + [c_int, c_void_p]),
+    "netra_group_quant_assembly_load": (c_int, [ctypes.c_char_p] * 6),
+    "netra_group_quant_assembly_unload": (c_int, []),
+    "netra_group_quant_assembly_last_error": (ctypes.c_char_p, []),
+    "netra_add_rmsnorm_group_quant_n2048_launch": (c_int, [c_void_p] * 7 + [c_u32, ctypes.c_float, c_void_p]),
+    "netra_moe_layer_launch_with_norm": (c_int, [c_void_p] * 4 + [ctypes.c_float] + [c_void_p] * 4 + [c_u32, c_void_p]),
     "netra_moe_prefill_m768_load": (c_int, [ctypes.c_char_p, ctypes.c_char_p]),
     "netra_moe_prefill_m768_launch": (c_int, [c_void_p] * 15),
     "netra_moe_prefill_m768_status": (c_int, [ctypes.POINTER(c_u32 * 4)]),

@@ -141,13 +141,16 @@ struct netra_moe_layer {
   uint32_t gemm_mode;     // 0: pick the GEMM form by size, 1: always the swap-AB (decode) kernels
   uint32_t router_mode;   // 0: pick the router by size, 1: always the FP64 tensor-core router, 2: as 0 with every logit exact
   uint32_t partial_f16;   // 1: the token-major down projection writes FP16 partial rows (prefill contract)
+  bool prequantised;      // set for the duration of a call whose token rows were quantised by the fused norm kernel
 };
 
 extern "C" {
 
 // ------------------------------------------------------------------ bridges
+// load(): the kernels are linked in, so there is no code object to open; it runs the per-device set-up, which refuses a
+// device that is not sm_100a - as the reference's load() refuses a wrong architecture.
 #define NETRA_BRIDGE_COMMON(name)                                       \
-  int name##_load(const char*) { return 0; }                            \
+  int name##_load(const char*) { return umma_setup(); }                 \
   int name##_unload(void) { return 0; }                                 \
   const char* name##_last_error(void) { return g_error; }
 
@@ -194,6 +197,24 @@ int netra_qwen36_moe_down_reduce_launch(const void* act_fp8, const float* act_sc
   netra_qwen36_moe_down_reduce_fp8_sm100<<<grid, 256, 0, stream>>>((const uint8_t*)act_fp8, act_scale, (const uint8_t*)w2, w2_scale,
                                                                    topk_w, topk_ids, (uint16_t*)out, (uint32_t)rows);
   return check_launch("down_reduce launch");
+}
+
+// group-quant bridge (runtime/gfx950/group_quant/verify/group_quant_assembly_bridge.h:21-31), at width 2048
+int netra_group_quant_assembly_load(const char*, const char*, const char*, const char*, const char*, const char*) { return umma_setup(); }
+int netra_group_quant_assembly_unload(void) { return 0; }
+const char* netra_group_quant_assembly_last_error(void) { return g_error; }
+
+int netra_add_rmsnorm_group_quant_n2048_launch(const void* input_bf16, const void* residual_bf16, const void* weight_f32,
+                                               void* output_bf16, void* residual_out_bf16, void* output_fp8,
+                                               void* output_scale_f32, uint32_t rows, float epsilon, cudaStream_t stream) {
+  if (!input_bf16 || !residual_bf16 || !weight_f32 || !output_bf16 || !residual_out_bf16 || !output_fp8 || !output_scale_f32)
+    return fail("add_rmsnorm_group_quant: pointers must be nonnull");
+  if (rows == 0 || rows > (1u << 20)) return fail("add_rmsnorm_group_quant: rows out of range");
+  if (!(epsilon > 0.0f)) return fail("add_rmsnorm_group_quant: epsilon must be positive");
+  netra_add_rmsnorm_group_quant_n2048_sm100<<<(rows + 3) / 4, 128, 0, stream>>>(
+      (const uint16_t*)input_bf16, (const uint16_t*)residual_bf16, (const float*)weight_f32, (uint16_t*)output_bf16,
+      (uint16_t*)residual_out_bf16, (uint8_t*)output_fp8, (float*)output_scale_f32, rows, 0u, epsilon);
+  return check_launch("add_rmsnorm_group_quant launch");
 }
 
 // ------------------------------------------------------------------ fused layer
@@ -254,6 +275,7 @@ int netra_moe_layer_create(const netra_moe_layer_desc_t* desc, netra_moe_layer_t
   layer->gemm_mode = 0;
   layer->router_mode = 0;
   layer->partial_f16 = 0;
+  layer->prequantised = false;
   const uint64_t slabs = desc->num_expert_slabs ? desc->num_expert_slabs : (uint64_t)(kRouted + 1);
   if (slabs > (uint64_t)(kRouted + 1)) { delete layer; return fail("layer_create: at most 257 expert slabs"); }
   uint8_t* ws = (uint8_t*)desc->workspace;
@@ -347,15 +369,17 @@ int launch_stage(netra_moe_layer* layer, uint32_t stage, const void* hidden, con
             logits, (const uint16_t*)hidden, router_w, tokens);
       }
       break;
-    case 1:
+    case 1: {
+      uint8_t* q_rows = layer->prequantised ? nullptr : a_fp8;    // null: the fused norm kernel already wrote the token rows
       if (use_umma_router(layer, tokens))
         netra_moe_topk_quant_fix_sm100<<<(tokens + 3) / 4, 128, 0, stream>>>(
-            ids9, w9, a_fp8, a_scale, logits, logits_f32, wnorm, router_w, layer->desc.router_bias_f32, shared_w,
+            ids9, w9, q_rows, a_scale, logits, logits_f32, wnorm, router_w, layer->desc.router_bias_f32, shared_w,
             (const uint16_t*)hidden, router_stats, tokens, pairs, layer->router_mode == 2 ? 1u : 0u);
       else
         netra_moe_topk_quant_sm100<<<(tokens + 3) / 4, 128, 0, stream>>>(
-            ids9, w9, a_fp8, a_scale, logits, layer->desc.router_bias_f32, shared_w, (const uint16_t*)hidden, tokens, pairs);
+            ids9, w9, q_rows, a_scale, logits, layer->desc.router_bias_f32, shared_w, (const uint16_t*)hidden, tokens, pairs);
       break;
+    }
     case 2:
       if (tokens <= (uint32_t)kSortSmallMaxRows)   // one block does the whole sort; stages 3 and 4 launch nothing
         netra_moe_sort_small_sm100<<<1, 1024, 0, stream>>>(perm, inv_perm, counts, offsets, ids9, tokens);
@@ -413,6 +437,25 @@ int netra_moe_layer_launch(netra_moe_layer_t* layer, const void* hidden, const f
   for (uint32_t stage = 0; stage < kStageCount; ++stage)
     if (int rc = launch_stage(layer, stage, hidden, shared_w, out, tokens, stream)) return rc;
   return check_launch("layer launch");
+}
+
+int netra_moe_layer_launch_with_norm(netra_moe_layer_t* layer, const void* input, const void* residual, const float* norm_weight,
+                                     float epsilon, void* hidden_out, void* residual_out, const float* shared_w, void* out,
+                                     uint32_t tokens, cudaStream_t stream) {
+  if (layer == nullptr || input == nullptr || residual == nullptr || norm_weight == nullptr || hidden_out == nullptr ||
+      residual_out == nullptr || out == nullptr)
+    return fail("layer_launch_with_norm: null pointer");
+  if (tokens == 0 || tokens > layer->desc.max_tokens) return fail("layer_launch_with_norm: tokens exceed the bound capacity");
+  const netra_moe_workspace_layout_t& L = layer->lay;
+  uint8_t* ws = (uint8_t*)layer->desc.workspace;
+  netra_add_rmsnorm_group_quant_n2048_sm100<<<(tokens + 3) / 4, 128, 0, stream>>>(
+      (const uint16_t*)input, (const uint16_t*)residual, norm_weight, (uint16_t*)hidden_out, (uint16_t*)residual_out, ws + L.a_fp8,
+      (float*)(ws + L.a_scale), tokens, tokens * kTopK, epsilon);
+  layer->prequantised = true;
+  int rc = 0;
+  for (uint32_t stage = 0; stage < kStageCount && rc == 0; ++stage) rc = launch_stage(layer, stage, hidden_out, shared_w, out, tokens, stream);
+  layer->prequantised = false;
+  return rc ? rc : check_launch("layer launch with fused norm");
 }
 
 int netra_moe_layer_launch_with_topk(netra_moe_layer_t* layer, const void* hidden, const int32_t* topk_ids, const float* topk_weights,

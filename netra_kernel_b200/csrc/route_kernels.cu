@@ -162,12 +162,9 @@ __device__ __forceinline__ void quantize_loaded_row(uint8_t* __restrict__ a_fp8,
   for (int c = 0; c < 4; ++c) {
     uint32_t w[4];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      uint32_t b = 0;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) b |= (uint32_t)f32_to_e4m3(x[c * 16 + q * 4 + j] * inv) << (8 * j);
-      w[q] = b;
-    }
+    for (int q = 0; q < 4; ++q)
+      w[q] = f32x4_to_e4m3x4(x[c * 16 + q * 4] * inv, x[c * 16 + q * 4 + 1] * inv, x[c * 16 + q * 4 + 2] * inv,
+                             x[c * 16 + q * 4 + 3] * inv);
     dst[c] = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
@@ -180,46 +177,117 @@ __device__ __forceinline__ void quantize_hidden_row(uint8_t* __restrict__ a_fp8,
 }
 
 // ------------------------------------------------------------------------------------------
+// Residual add + RMSNorm + per-128 FP8 quantisation of the normalised row, the fusion that feeds the layer
+// (behaviour replaced: kernels/gfx950/templates/norm/verify/add_rmsnorm_group_quant_n5120.inc, ABI
+// runtime/gfx950/group_quant/verify/group_quant_assembly_bridge.h:21-31, numerical id
+// "residual_add_fp32_rms_bf16_round_then_fp8_rne_fixed"; here at this model's width 2048):
+//   x = f32(input) + f32(residual)                       residual_out = bf16(x)
+//   var = fl32( sum x^2 / 2048 )   (the sum of the exact squares in FP64: one rounding, any order)
+//   y = bf16( (x * (1 / sqrt(var + eps))) * weight )       output_bf16 = y
+//   per 128 columns: scale = max(amax |y|, 1e-10) * fl(1/448), code = e4m3_rne_sat(y * (1 / scale))
+// The codes and scales go to row (row_base + t) of the buffers the grouped GEMMs read (scales row-major [rows, 16]).
+// One warp per row: a lane owns 64 consecutive columns, two lanes one quantisation group.  grid ceil(rows/4), block 128.
+// ------------------------------------------------------------------------------------------
+extern "C" __global__ void __launch_bounds__(128)
+netra_add_rmsnorm_group_quant_n2048_sm100(const uint16_t* __restrict__ input, const uint16_t* __restrict__ residual,
+                                          const float* __restrict__ weight, uint16_t* __restrict__ output,
+                                          uint16_t* __restrict__ residual_out, uint8_t* __restrict__ out_fp8,
+                                          float* __restrict__ out_scale, uint32_t rows, uint32_t row_base, float epsilon) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (t >= (int)rows) return;
+  const uint4* in4 = reinterpret_cast<const uint4*>(input + (size_t)t * kHidden) + lane * 8;
+  const uint4* res4 = reinterpret_cast<const uint4*>(residual + (size_t)t * kHidden) + lane * 8;
+  uint4* resout4 = reinterpret_cast<uint4*>(residual_out + (size_t)t * kHidden) + lane * 8;
+  float x[64];
+  double sq = 0.0;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const uint4 a = in4[c], b = res4[c];
+    const uint32_t ua[4] = {a.x, a.y, a.z, a.w}, ub[4] = {b.x, b.y, b.z, b.w};
+    uint32_t pk[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float lo = __fadd_rn(bf16_bits_to_f32(ua[q] & 0xffffu), bf16_bits_to_f32(ub[q] & 0xffffu));
+      const float hi = __fadd_rn(bf16_bits_to_f32(ua[q] >> 16), bf16_bits_to_f32(ub[q] >> 16));
+      x[c * 8 + 2 * q] = lo;
+      x[c * 8 + 2 * q + 1] = hi;
+      sq = fma((double)lo, (double)lo, sq);
+      sq = fma((double)hi, (double)hi, sq);
+      const __nv_bfloat162 r = __floats2bfloat162_rn(lo, hi);
+      pk[q] = *reinterpret_cast<const uint32_t*>(&r);
+    }
+    resout4[c] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, d);
+  const float var = (float)(sq / (double)kHidden);
+  const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, epsilon)));
+  const float4* w4 = reinterpret_cast<const float4*>(weight) + lane * 16;
+  uint4* out4 = reinterpret_cast<uint4*>(output + (size_t)t * kHidden) + lane * 8;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const float4 w0 = w4[2 * c], w1 = w4[2 * c + 1];
+    const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    uint32_t pk[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float lo = bf16_round(__fmul_rn(__fmul_rn(x[c * 8 + 2 * q], inv), w[2 * q]));
+      const float hi = bf16_round(__fmul_rn(__fmul_rn(x[c * 8 + 2 * q + 1], inv), w[2 * q + 1]));
+      x[c * 8 + 2 * q] = lo;
+      x[c * 8 + 2 * q + 1] = hi;
+      pk[q] = (__float_as_uint(lo) >> 16) | (__float_as_uint(hi) & 0xffff0000u);
+    }
+    out4[c] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+  }
+  quantize_loaded_row(out_fp8, out_scale, x, t, row_base, lane);
+}
+
+// ------------------------------------------------------------------------------------------
 // Softmax / top-8 / renormalise + shared slot + per-token FP8 quantisation.  One warp per token.
 // Selection key is (z desc, expert id asc) with z = f32(logit) + bias; weights are
 // softmax(z)[id] renormalised over the 8 selected entries in slot order.
 // The quantised row goes to row (row_base + t) of the activation buffer.
 // grid ceil(rows/4), block 128.
 // ------------------------------------------------------------------------------------------
+// Floats as unsigned keys whose integer order is the float order (-0 counts as +0, NaN sorts below everything).
+__device__ __forceinline__ uint32_t order_key(float z) {
+  const uint32_t u = __float_as_uint(z + 0.0f);
+  if (z != z) return 1u;
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float order_key_value(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
 // Selection for one token by one warp; lane holds z[i] = f32(logit) + bias of experts lane*8 + i.
 // On return lane k < 8 holds slot k: expert id, softmax numerator exp(z - max z) and z of the k-th best
-// under the key (z desc, id asc).
+// under the key (z desc, id asc).  Each round is two warp-wide integer reductions (redux.sync): the largest
+// remaining key, then the lowest expert id among the lanes that hold it.
 __device__ __forceinline__ void softmax_top8_select(const float z[8], int lane, int& sel_id, float& sel_p, float& sel_z) {
-  float zmax = z[0];
+  uint32_t key[8];
 #pragma unroll
-  for (int i = 1; i < 8; ++i) zmax = fmaxf(zmax, z[i]);
-  zmax = warp_max(zmax);
-  // exp(z - zmax): the softmax numerators.  The softmax denominator cancels in the renormalisation over the eight
-  // selected experts, so the weights depend on the selected logits only
-  float p[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) p[i] = expf(z[i] - zmax);
-  uint32_t taken = 0;
-  sel_p = 0.0f; sel_id = 0; sel_z = 0.0f;
+  for (int i = 0; i < 8; ++i) key[i] = order_key(z[i]);
+  uint32_t taken = 0, my_key = 0;
+  sel_id = 0;
 #pragma unroll 1
   for (int k = 0; k < kTopK; ++k) {
-    float bv = -INFINITY; int bi = 0x7fffffff; float bp = 0.0f;
+    uint32_t bk = 0; int bi = 0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      bool better = !((taken >> i) & 1u) && (bi == 0x7fffffff || z[i] > bv);
-      if (better) { bv = z[i]; bi = lane * 8 + i; bp = p[i]; }
+      const bool better = !((taken >> i) & 1u) && key[i] > bk;    // strict: the lowest index of equal keys stays
+      if (better) { bk = key[i]; bi = i; }
     }
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) {
-      float ov = __shfl_xor_sync(0xffffffffu, bv, d);
-      int oi = __shfl_xor_sync(0xffffffffu, bi, d);
-      float op = __shfl_xor_sync(0xffffffffu, bp, d);
-      bool take = (oi != 0x7fffffff) && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi));
-      if (take) { bv = ov; bi = oi; bp = op; }
-    }
-    if ((bi >> 3) == lane) taken |= 1u << (bi & 7);
-    if (lane == k) { sel_p = bp; sel_id = bi; sel_z = bv; }
+    const uint32_t best = __reduce_max_sync(0xffffffffu, bk);
+    const uint32_t winner = __reduce_min_sync(0xffffffffu, (bk == best && bk != 0u) ? (uint32_t)(lane * 8 + bi) : 0xffffffffu);
+    if ((int)(winner >> 3) == lane) taken |= 1u << (winner & 7u);
+    if (lane == k) { sel_id = (int)winner; my_key = best; }
   }
+  // exp(z - zmax): the softmax numerators.  The softmax denominator cancels in the renormalisation over the eight
+  // selected experts, so the weights depend on the selected logits only (slot 0 holds the largest z)
+  const float zmax = order_key_value(__shfl_sync(0xffffffffu, my_key, 0));
+  sel_z = order_key_value(my_key);
+  sel_p = expf(sel_z - zmax);
 }
 
 // Renormalise over the eight selected probabilities (slot-order FP32 sum) and store ids / weights with the shared slot.
@@ -269,7 +337,7 @@ netra_moe_topk_quant_sm100(int32_t* __restrict__ ids9, float* __restrict__ w9,
     }
   }
   softmax_top8_store(ids9, w9, z, shared_w, t, lane);
-  quantize_hidden_row(a_fp8, a_scale, hidden, t, row_base, lane);
+  if (a_fp8 != nullptr) quantize_hidden_row(a_fp8, a_scale, hidden, t, row_base, lane);   // null: the rows were quantised upstream
 }
 
 // ------------------------------------------------------------------------------------------
@@ -359,7 +427,8 @@ netra_moe_topk_quant_fix_sm100(int32_t* __restrict__ ids9, float* __restrict__ w
     const float v8 = __shfl_sync(0xffffffffu, sel_z, kTopK - 1);
     // two BF16 spacings at the largest magnitude of the row cover the two roundings (of a and of the exact value, which
     // may sit one binade higher); 1.01 covers the FP32 roundings of this arithmetic and of the bias addition
-    const float delta = (warp_max(bmax) + warp_max(vmax) * 0.015625f) * 1.01f;
+    const float delta = (__uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(bmax))) +
+                         __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(vmax))) * 0.015625f) * 1.01f;   // both are >= 0
     const float reach = v8 - 2.0f * delta;
     uint32_t cand = 0;
 #pragma unroll
@@ -407,7 +476,7 @@ netra_moe_topk_quant_fix_sm100(int32_t* __restrict__ ids9, float* __restrict__ w
   }
   if (!selected || fixed != 0) softmax_top8_select(z, lane, sel_id, sel_p, sel_z);   // `fixed` is the same in every lane
   top8_store(ids9, w9, sel_id, sel_p, shared_w, t, lane);
-  quantize_hidden_row(a_fp8, a_scale, hidden, t, row_base, lane);
+  if (a_fp8 != nullptr) quantize_hidden_row(a_fp8, a_scale, hidden, t, row_base, lane);   // null: the rows were quantised upstream
 }
 
 // The same outputs from a top-k computed elsewhere (a serving stack that keeps its own fused top-k, the

@@ -151,6 +151,21 @@ class RoutedMoELayer:
                                                   out.data_ptr(), tokens, _stream()), "layer_launch")
         return out
 
+    def forward_with_norm(self, x: torch.Tensor, residual: torch.Tensor, norm_weight: torch.Tensor, epsilon: float = 1e-6,
+                          shared_weight: Optional[torch.Tensor] = None):
+        """Residual add + RMSNorm + input quantisation fused in front of the layer
+        (``netra_moe_layer_launch_with_norm``).  Returns (layer output, updated residual, normalised hidden)."""
+        _require_cuda(x, residual, norm_weight, shared_weight)
+        if x.dtype != torch.bfloat16 or residual.dtype != torch.bfloat16 or x.shape != residual.shape or x.shape[1] != HIDDEN:
+            raise ValueError("input and residual must be bf16 [tokens, 2048]")
+        if norm_weight.dtype != torch.float32 or norm_weight.numel() != HIDDEN:
+            raise ValueError("norm weight must be float32 [2048]")
+        hidden, res_out, out = torch.empty_like(x), torch.empty_like(x), torch.empty_like(x)
+        abi.check(self.lib.netra_moe_layer_launch_with_norm(self.handle, x.data_ptr(), residual.data_ptr(), norm_weight.data_ptr(),
+                                                            float(epsilon), hidden.data_ptr(), res_out.data_ptr(), _ptr(shared_weight),
+                                                            out.data_ptr(), x.shape[0], _stream()), "layer_launch_with_norm")
+        return out, res_out, hidden
+
     def apply(self, hidden: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
               shared_weight: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """The layer with a top-k computed by the caller (argument order of the reference's
@@ -297,3 +312,16 @@ def bridge_down_reduce(act_fp8, act_scale, w2, w2_scale, topk_w9, topk_ids9) -> 
         act_fp8.data_ptr(), act_scale.data_ptr(), w2.data_ptr(), w2_scale.data_ptr(), topk_w9.data_ptr(),
         topk_ids9.data_ptr(), out.data_ptr(), rows, _stream()), "down_reduce_launch")
     return out
+
+
+def bridge_add_rmsnorm_group_quant(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, epsilon: float = 1e-6):
+    """``netra_add_rmsnorm_group_quant_n2048_launch``: (normalised BF16, updated residual BF16, FP8 codes u8, scales f32 [rows, 16])."""
+    _require_cuda(x, residual, weight)
+    rows = x.shape[0]
+    out, res_out = torch.empty_like(x), torch.empty_like(x)
+    q = torch.empty(rows, HIDDEN, dtype=torch.uint8, device=x.device)
+    s = torch.empty(rows, HIDDEN // 128, dtype=torch.float32, device=x.device)
+    abi.check(abi.load().netra_add_rmsnorm_group_quant_n2048_launch(x.data_ptr(), residual.data_ptr(), weight.data_ptr(), out.data_ptr(),
+                                                                     res_out.data_ptr(), q.data_ptr(), s.data_ptr(), rows, float(epsilon),
+                                                                     _stream()), "add_rmsnorm_group_quant_launch")
+    return out, res_out, q, s

@@ -185,6 +185,21 @@ def quant_fp8_group128(x: np.ndarray):
     return q.reshape(r, c), scale
 
 
+def add_rmsnorm_group_quant(input_bits: np.ndarray, residual_bits: np.ndarray, weight: np.ndarray, epsilon: float = 1e-6):
+    """Residual add + RMSNorm + per-128 FP8 quantisation, numerical id ``residual_add_fp32_rms_bf16_round_then_fp8_rne_fixed``
+    of ``manifests/gfx950/tactics/fixed_assembly.json:754-786`` (ABI ``runtime/gfx950/group_quant/verify/group_quant_assembly_bridge.h:21-31``).
+    The kernel is AMD assembly and its framework fallback (AITER ``add_rmsnorm_quant``) is third-party, so the order of the
+    FP32 operations is restated here as: FP32 add, mean of squares rounded once to FP32 (the squares are summed exactly),
+    ``inv = 1 / sqrt(var + eps)``, ``y = bf16((x * inv) * w)``, then the per-128 quantiser.  PARITY UNPINNED.
+    Returns (output BF16 bits, residual_out BF16 bits, FP8 codes, scales [rows, C/128])."""
+    x = (bf16_bits_to_f32(input_bits) + bf16_bits_to_f32(residual_bits)).astype(np.float32)
+    var = ((x.astype(np.float64) ** 2).sum(axis=1) / x.shape[1]).astype(np.float32)
+    inv = (np.float32(1.0) / np.sqrt((var + np.float32(epsilon)).astype(np.float32))).astype(np.float32)
+    y_bits = f32_to_bf16_bits(((x * inv[:, None]).astype(np.float32) * weight.astype(np.float32)[None, :]).astype(np.float32))
+    q, s = quant_fp8_group128(bf16_bits_to_f32(y_bits))
+    return y_bits, f32_to_bf16_bits(x), q, s
+
+
 def silu_mul_quant(gate_up: np.ndarray):
     """FP32 [R,1024] (gate | up) -> BF16-rounded silu(gate)*up -> per-128 FP8."""
     g = gate_up[:, :INTER].astype(np.float32)

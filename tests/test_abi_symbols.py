@@ -40,4 +40,10 @@ def test_struct_sizes_and_argument_checks_without_a_device():
     # null pointers are refused before any launch
     assert lib.netra_qwen36_router_bf16_launch(None, None, None, 4, None) == -1
     assert lib.netra_qwen36_moe_gate_up_launch(None, None, None, None, None, None, 1, None) == -1
-    assert lib.netra_qwen36_moe_silu_mul_quant_load(None) == 0
+    # load() runs the per-device set-up: without a device it must fail with the runtime's message, never silently succeed
+    rc = lib.netra_qwen36_moe_silu_mul_quant_load(None)
+    import torch
+    if torch.cuda.is_available():
+        assert rc == 0
+    else:
+        assert rc != 0 and b"cudaGetDevice" in lib.netra_qwen36_moe_silu_mul_quant_last_error()

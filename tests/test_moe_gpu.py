@@ -532,3 +532,41 @@ def test_argument_errors_are_reported(gpu_weights):
         layer(torch.zeros(9, 2048, dtype=torch.bfloat16, device="cuda"))
     with pytest.raises(ValueError):
         layer(torch.zeros(8, 1024, dtype=torch.bfloat16, device="cuda"))
+
+
+def test_add_rmsnorm_group_quant_bridge_and_fused_layer_entry(gpu_weights):
+    """The upstream fusion at width 2048: every output of the bridge bit for bit against the checker's restatement (ragged
+    row counts, a zero row, large and tiny rows), and the layer entry that takes the un-normalised input must equal the
+    plain layer call on the normalised rows bit for bit."""
+    from netra_kernel_b200 import moe
+    g = torch.Generator().manual_seed(31)
+    for rows in (1, 5, 260):
+        x = torch.randn(rows, 2048, generator=g)
+        res = torch.randn(rows, 2048, generator=g)
+        if rows > 4:
+            x[1] = 0.0; res[1] = 0.0
+            x[2] *= 1e4
+            x[3] *= 1e-6; res[3] *= 1e-6
+        x, res = x.to(torch.bfloat16), res.to(torch.bfloat16)
+        w = 1.0 + 0.1 * torch.randn(2048, generator=g)
+        y, r, q, s = moe.bridge_add_rmsnorm_group_quant(x.cuda(), res.cuda(), w.cuda(), 1e-6)
+        torch.cuda.synchronize()
+        wy, wr, wq, ws = R.add_rmsnorm_group_quant(helpers.bits(x), helpers.bits(res), w.numpy(), 1e-6)
+        assert np.array_equal(helpers.bits(r), wr), rows
+        assert np.array_equal(helpers.bits(y), wy), rows
+        assert np.array_equal(q.cpu().numpy(), wq) and np.array_equal(s.cpu().numpy(), ws), rows
+    tokens = 200
+    hidden, router_w, _ = synth.make_activations(tokens, seed=14)
+    layer = make_layer(gpu_weights, router_w, 256)
+    res = torch.randn(tokens, 2048, generator=g).to(torch.bfloat16)
+    w = (1.0 + 0.1 * torch.randn(2048, generator=g)).cuda()
+    out, res_out, normed = layer.forward_with_norm(hidden.cuda(), res.cuda(), w, 1e-6)
+    torch.cuda.synchronize()
+    layer.check_status()
+    a_rows = layer.intermediates(tokens)["a_fp8"][tokens * 8:].clone()
+    want = layer(normed)
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+    assert torch.equal(layer.intermediates(tokens)["a_fp8"][tokens * 8:], a_rows)
+    wy, wr, wq, _ = R.add_rmsnorm_group_quant(helpers.bits(hidden), helpers.bits(res), w.cpu().numpy(), 1e-6)
+    assert np.array_equal(helpers.bits(normed), wy) and np.array_equal(helpers.bits(res_out), wr) and np.array_equal(a_rows.cpu().numpy(), wq)
