@@ -333,7 +333,7 @@ def make_engine_session(args, tokens, device_id, layer, hidden, out, model="rout
         return None
     root = KernelLibrary.discover().root
     profile = next((p for p in load_profile_registry(root, "sm_100a", 1)
-                    if p.guard("m").is_exact and p.guard("m").minimum == tokens), None)
+                    if p.guard("m").is_exact and p.guard("m").minimum == tokens and all(k != "route_rows" for k, _ in p.guards)), None)
     if profile is None:
         return None
     directory = tempfile.mkdtemp(prefix=f"netra_engine_r{device_id}_")

@@ -168,6 +168,11 @@ typedef struct netra_moe_layer_desc {
 int netra_moe_repack_tiles_launch(void* dst, const void* src, uint64_t total_rows, uint32_t k_bytes,
                                   cudaStream_t stream);
 
+/* The scale half of the same plan (compiler/netra_compiler/layouts.py:166-206, "widen_bf16_to_fp32_exact"): checkpoints
+ * that store weight_scale_inv as BF16 are widened to the FP32 scales the kernels read; the order of the scales
+ * ([group, N/128, K/128]) is unchanged. */
+int netra_moe_widen_scales_bf16_launch(float* dst_f32, const void* src_bf16, uint64_t count, cudaStream_t stream);
+
 /* MXFP4 expert weights (E2M1 codes, one E8M0 scale per 32 K-elements; encoding of the reference's
  * tools/checkpoint/quantize_qwen36_lm_head_mxfp4.py:58-67 and tests/gfx1151/test_netra_mxfp4_sgl_decode.py:23-31):
  * load-time expansion into the layer's operand format - E4M3 codes [total_rows, k] and one power-of-two FP32

@@ -13,6 +13,7 @@ from . import __name__ as _pkg
 from .catalog import FixedCudaTactic, load_fixed_tactic_catalog
 from .expr import evaluate
 from .frontend import dimensions_for, load_model, options_for, routed_moe_layer_graph
+from .layouts import moe_layer_layout_plan
 from .library import KernelLibrary
 from .memory import BufferRequest, plan_buffers
 from .planner import Plan, PlannedOperation, plan_graph
@@ -172,10 +173,13 @@ def compile_engine(model_path: Path | str, profile_name: str, output: Path | str
             shutil.copyfile(source, out / "cubin" / name)
             artifact_files[f"cubin/{name}"] = file_sha256(source)
 
-    layout_plan = {"format": "netra-layout-plan-1", "steps": [
+    # declarative weight / scale layout plan (layouts.py); "steps" keeps the flat list of device repacks the runtime helper runs
+    layout_plan = moe_layer_layout_plan(model["options"]["weight_layout"], split_gate_up=bool(model["options"].get("split_gate_up", False)),
+                                        scale_dtype=str(model["options"].get("checkpoint_scale_dtype", "fp32")))
+    layout_plan["steps"] = [
         {"tensor": name, "from": "row_major[group,n,k]", "to": "tiles128x128[group,n/128,k/128,128,128]",
          "kernel": "netra_moe_repack_tiles_sm100", "entry_point": "netra_moe_repack_tiles_launch", "scales": "unchanged"}
-        for name in ("w13", "w2")] if opts["w_tiled"] else []}
+        for name in ("w13", "w2")] if opts["w_tiled"] else []
     selected = [{"operation": p.operation.name, "tactic": p.tactic.name, "contract_id": p.contract.stable_id}
                 for p in plan.operations if p.tactic is not None]
     identity = {

@@ -58,8 +58,19 @@ def semantics(abi: str, dtypes: str, quantization: str, layouts: str, numerical:
     return KernelSemantics(abi, dtypes, quantization, layouts, numerical).to_dict()
 
 
+def token_rows(profile: ShapeProfile) -> int:
+    """Rows the routed layer sees.  A verify / speculative profile fixes ``route_rows`` (= m draft positions x batch, the
+    reference's ``manifests/gfx950/profiles/verify_m12_b64_routes768.json``); any other profile's rows are its ``m``."""
+    if any(key == "route_rows" for key, _ in profile.guards):
+        rows = profile.exact_value("route_rows")
+        if rows != profile.exact_value("m") * profile.exact_value("batch"):
+            raise ValidationError(f"profile {profile.name!r}: route_rows must equal m * batch")
+        return rows
+    return profile.exact_value("m")
+
+
 def dimensions_for(model: dict[str, Any], profile: ShapeProfile) -> dict[str, int]:
-    m = profile.exact_value("m")
+    m = token_rows(profile)
     c = model["constants"]
     pairs = m * c["top_k"]
     return {"m": m, "pairs": pairs, "rows": pairs + m, "nseg": -(-pairs // SORT_SEGMENT_PAIRS)}

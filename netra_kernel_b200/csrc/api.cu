@@ -492,6 +492,13 @@ int netra_moe_repack_tiles_launch(void* dst, const void* src, uint64_t total_row
   return check_launch("repack_tiles launch");
 }
 
+int netra_moe_widen_scales_bf16_launch(float* dst_f32, const void* src_bf16, uint64_t count, cudaStream_t stream) {
+  if (!dst_f32 || !src_bf16) return fail("widen_scales: null pointer");
+  if (count == 0 || count > (1ull << 32)) return fail("widen_scales: count out of range");
+  netra_moe_widen_scales_bf16_sm100<<<(unsigned)((count + 255) / 256), 256, 0, stream>>>(dst_f32, (const uint16_t*)src_bf16, count);
+  return check_launch("widen_scales launch");
+}
+
 int netra_moe_mxfp4_expand_launch(void* dst_fp8, float* dst_scale, uint32_t* inexact, const void* packed, const void* scales_e8m0,
                                   uint64_t total_rows, uint32_t k, cudaStream_t stream) {
   if (!dst_fp8 || !dst_scale || !inexact || !packed || !scales_e8m0) return fail("mxfp4_expand: null pointer");

@@ -363,6 +363,58 @@ netra_moe_topk_quant_sm100(int32_t* __restrict__ ids9, float* __restrict__ w9,
 // ------------------------------------------------------------------------------------------
 constexpr float kRouterErrScale = 3.8146973e-06f;   // 2^-18
 
+// Exact dot product of one hidden row and one router row by one warp (every lane returns the sum): lane l owns the
+// 16-byte chunks c*32 + l, so each of the sixteen loads is a fully coalesced 512-byte request and all are in flight
+// together.  Fast path: the product of two BF16 values is exact in FP32 unless it leaves the normal range; the exact
+// FP32 products are widened with integer operations and summed in FP64 (error far below any BF16 spacing).  A product
+// that underflows or overflows FP32 sends the whole dot product to the slow path, which widens the operands first.
+__device__ __noinline__ double exact_dot_slow(const uint4* __restrict__ hrow, const uint4* __restrict__ wrow, int lane) {
+  double acc = 0.0;
+  for (int c = 0; c < 8; ++c) {
+    const uint4 hv = __ldg(hrow + c * 32 + lane), wv = __ldg(wrow + c * 32 + lane);
+    const uint32_t x[4] = {hv.x, hv.y, hv.z, hv.w}, u[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      acc = fma(bf16_bits_to_f64_nobranch(x[q] & 0xffffu), bf16_bits_to_f64_nobranch(u[q] & 0xffffu), acc);
+      acc = fma(bf16_bits_to_f64_nobranch(x[q] >> 16), bf16_bits_to_f64_nobranch(u[q] >> 16), acc);
+    }
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+  return acc;
+}
+
+__device__ __forceinline__ double exact_dot(const uint4* __restrict__ hrow, const uint4* __restrict__ wrow, int lane) {
+  uint4 hv[8], wv[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) { hv[c] = __ldg(hrow + c * 32 + lane); wv[c] = __ldg(wrow + c * 32 + lane); }
+  double acc0 = 0.0, acc1 = 0.0;
+  uint32_t bad = 0;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const uint32_t x[4] = {hv[c].x, hv[c].y, hv[c].z, hv[c].w}, u[4] = {wv[c].x, wv[c].y, wv[c].z, wv[c].w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const uint32_t xa = half ? (x[q] & 0xffff0000u) : (x[q] << 16), ub = half ? (u[q] & 0xffff0000u) : (u[q] << 16);
+        const uint32_t pb = __float_as_uint(__fmul_rn(__uint_as_float(xa), __uint_as_float(ub)));
+        const uint32_t pe = pb & 0x7f800000u;
+        // exact unless the result left the normal range: zero with both factors nonzero (or subnormal), infinity, NaN
+        bad |= (pe == 0x7f800000u) | ((pe == 0u) & ((xa << 1) != 0u) & ((ub << 1) != 0u));
+        const uint32_t hi = pe != 0u ? ((pb & 0x80000000u) | (((pb & 0x7fffffffu) >> 3) + 0x38000000u)) : 0u;
+        const double pd = __hiloint2double((int)hi, (int)(pe != 0u ? pb << 29 : 0u));
+        if (half) acc1 += pd; else acc0 += pd;
+      }
+    }
+  }
+  if (__any_sync(0xffffffffu, bad != 0u)) return exact_dot_slow(hrow, wrow, lane);
+  double acc = acc0 + acc1;
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+  return acc;
+}
+
 extern "C" __global__ void __launch_bounds__(128)
 netra_moe_topk_quant_fix_sm100(int32_t* __restrict__ ids9, float* __restrict__ w9,
                                uint8_t* __restrict__ a_fp8, float* __restrict__ a_scale,
@@ -442,22 +494,8 @@ netra_moe_topk_quant_fix_sm100(int32_t* __restrict__ ids9, float* __restrict__ w
     if (any == 0) break;
     const int src = __ffs(any) - 1;
     const int i = __ffs(__shfl_sync(0xffffffffu, pending, src)) - 1;
-    const uint4* wrow = reinterpret_cast<const uint4*>(router_w + (size_t)(src * 8 + i) * kHidden) + lane * 8;
-    double acc0 = 0.0, acc1 = 0.0;                                // two chains: the FP64 pipe has latency to hide
-#pragma unroll 2
-    for (int c = 0; c < 8; ++c) {
-      const uint4 wv = __ldg(wrow + c), hv = __ldg(hrow + c);
-      const uint32_t u[4] = {wv.x, wv.y, wv.z, wv.w};
-      const uint32_t x[4] = {hv.x, hv.y, hv.z, hv.w};
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        acc0 = fma(bf16_bits_to_f64_nobranch(x[q] & 0xffffu), bf16_bits_to_f64_nobranch(u[q] & 0xffffu), acc0);
-        acc1 = fma(bf16_bits_to_f64_nobranch(x[q] >> 16), bf16_bits_to_f64_nobranch(u[q] >> 16), acc1);
-      }
-    }
-    double acc = acc0 + acc1;
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+    const double acc = exact_dot(reinterpret_cast<const uint4*>(hidden + (size_t)t * kHidden),
+                                 reinterpret_cast<const uint4*>(router_w + (size_t)(src * 8 + i) * kHidden), lane);
     const float exact = bf16_bits_to_f32(f64_to_bf16_bits(acc));
     if (lane == src) {
 #pragma unroll

@@ -561,6 +561,13 @@ netra_moe_repack_tiles_sm100(uint4* __restrict__ dst, const uint4* __restrict__ 
   dst[idx] = src[(srow * k_bytes + (size_t)kb * kBlock) / 16 + chunk];
 }
 
+// Block scales stored as BF16 in a checkpoint -> the FP32 scales the kernels read (exact widening).  grid ceil(count/256).
+extern "C" __global__ void __launch_bounds__(256)
+netra_moe_widen_scales_bf16_sm100(float* __restrict__ dst, const uint16_t* __restrict__ src, uint64_t count) {
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < count) dst[i] = bf16_bits_to_f32(src[i]);
+}
+
 int gate_up_smem_bytes() { return Cfg<true>::kSmemBytes; }
 int down_smem_bytes() { return Cfg<false>::kSmemBytes; }
 

@@ -58,6 +58,16 @@ __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, i
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"((uint64_t)map), "r"(x), "r"(y) : "memory");
 }
 
+// Four rows of a 2-D tensor (box = 128 bytes x 1 row) chosen by index, written as four consecutive 128-byte rows
+// of a swizzled tile: the token rows of a work item are fetched straight from token order, without a sorted copy.
+__device__ __forceinline__ void tma_gather4_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int r0, int r1, int r2, int r3,
+                                               uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2], %8;"
+      ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "l"(policy) : "memory");
+}
+
 // barrier among the 256 epilogue threads
 __device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 3, 256;" ::: "memory"); }
 
@@ -89,14 +99,18 @@ struct TmCfg {
                                     2 * kEpiGroups * kTokTile * 4 + 2 * 264 * 4 + kItemList * 16 + 512;
 };
 
-template <bool kGateUp, bool kF16Out = false>
+// kGatherX (gate_up only): the item's token rows are not read from an expert-sorted copy but gathered from token order:
+// sorted position p holds token-order row tok_row_base + (perm[p] >> 3) (positions from tok_row_base on are token-order
+// rows already: the shared expert).  tm_x128 then is a map with a one-row box over the same buffer, x_scale its scales.
+template <bool kGateUp, bool kF16Out = false, bool kGatherX = false>
 __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, const CUtensorMap* tm_x128,
                                                    const float* __restrict__ x_scale, const float* __restrict__ w_scale,
                                                    const int32_t* __restrict__ offsets, uint8_t* __restrict__ h_fp8,
                                                    float* __restrict__ h_scale, float* __restrict__ down,
                                                    float* const* __restrict__ row_ptr, uint32_t num_groups, uint32_t w_tiled,
-                                                   uint32_t* status) {
+                                                   uint32_t* status, const int32_t* __restrict__ perm = nullptr, uint32_t tok_row_base = 0) {
   static_assert(!(kGateUp && kF16Out), "FP16 partial rows are an output format of the down projection");
+  static_assert(kGateUp || !kGatherX, "only the gate_up projection reads token rows");
   using C = TmCfg<kGateUp, kF16Out>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);

@@ -300,3 +300,100 @@ def test_cli_round_trip(tmp_path, capsys):
     out = capsys.readouterr().out
     assert "engine_id ne_" in out and "router_logits_bf16_fp64_mma" in out
     assert cli.main(["compile", "--model", str(MODEL), "--profile", "nope", "--output", str(tmp_path / "f")]) == 2
+
+
+# ------------------------------------------------------------------ layout plan, dense contract, verify profile
+def test_weight_and_scale_layout_plans_and_their_byte_transforms():
+    import numpy as np
+    from netra_kernel_b200.compiler import layouts as L
+    same = L.plan_weight_layout("w2", L.ROW_MAJOR, L.ROW_MAJOR)
+    assert same.steps == ()
+    tiled = L.plan_weight_layout("w2", L.ROW_MAJOR, L.TILES128, checkpoint_tensors=("w2",))
+    assert [s.operation for s in tiled.steps] == ["tile_128x128"] and tiled.steps[0].entry_point == "netra_moe_repack_tiles_launch"
+    split = L.plan_weight_layout("w13", L.SPLIT_GATE_UP, L.TILES128, checkpoint_tensors=("gate_proj", "up_proj"))
+    assert [s.operation for s in split.steps] == ["concatenate_output_shards", "tile_128x128"]
+    with pytest.raises(ValidationError):
+        L.plan_weight_layout("w13", L.SPLIT_GATE_UP, L.TILES128, checkpoint_tensors=("gate_proj",))
+    with pytest.raises(ValidationError):
+        L.plan_weight_layout("w13", "aiter_shuffle_16x16_fp8_block128", L.TILES128)
+    scale = L.plan_scale_layout("w13_scale", ("gate_proj_scale_inv", "up_proj_scale_inv"), checkpoint_dtype="bf16", kernel_dtype="fp32",
+                                block=(128, 128))
+    assert scale.steps == ("concatenate_output_scale_shards_axis0", "widen_bf16_to_fp32_exact")
+    with pytest.raises(ValidationError):
+        L.plan_scale_layout("s", ("a",), checkpoint_dtype="fp32", kernel_dtype="bf16", block=(128, 128))
+    with pytest.raises(ValidationError):
+        L.plan_scale_layout("s", (), checkpoint_dtype="fp32", kernel_dtype="fp32", block=(128, 128))
+    # byte level: tile (i, j) of the output is rows [128 i, +128) x bytes [128 j, +128) of the input, and the transform inverts
+    rng = np.random.default_rng(0)
+    data = rng.integers(0, 256, (384, 512), dtype=np.uint8)
+    out = L.tile_128x128(data)
+    tiles = out.reshape(3, 4, 128, 128)
+    for i, j in ((0, 0), (1, 3), (2, 1)):
+        assert np.array_equal(tiles[i, j], data[128 * i:128 * i + 128, 128 * j:128 * j + 128])
+    assert np.array_equal(L.untile_128x128(out), data) and out.tobytes() != data.tobytes()
+    gate, up = rng.integers(0, 256, (2, 128, 256), dtype=np.uint8), rng.integers(0, 256, (2, 128, 256), dtype=np.uint8)
+    streamed = L.apply_weight_steps(split, [gate, up])
+    assert streamed.shape == (2, 256, 256)
+    assert np.array_equal(L.untile_128x128(streamed.reshape(512, 256)).reshape(2, 256, 256), np.concatenate([gate, up], axis=1))
+    bits = np.array([0x3F80, 0xBF00, 0x0000, 0x7F7F], np.uint16)
+    assert L.widen_bf16_to_fp32(bits).tolist() == [1.0, -0.5, 0.0, float(np.float32(3.3895313892515355e38))]
+    with pytest.raises(ValidationError):
+        L.tile_128x128(np.zeros((100, 128), np.uint8))
+
+
+def test_engine_layout_plan_names_the_repack_and_scale_steps(tmp_path):
+    compile_engine(MODEL, "decode_t256", tmp_path / "e", copy_cubin=False)
+    plan = json.loads((tmp_path / "e" / "layout_plan.json").read_text())
+    assert plan["format"] == "netra-layout-plan-2" and [w["tensor"] for w in plan["weights"]] == ["w13", "w2"]
+    assert plan["weights"][0]["steps"][0]["entry_point"] == "netra_moe_repack_tiles_launch" and len(plan["steps"]) == 2
+    assert all(sc["steps"] == [] for sc in plan["scales"])                         # FP32 scales need no step
+    doc = json.loads(MODEL.read_text())
+    doc["options"].update({"split_gate_up": True, "checkpoint_scale_dtype": "bf16"})
+    (tmp_path / "m.json").write_text(json.dumps(doc))
+    compile_engine(tmp_path / "m.json", "decode_t256", tmp_path / "f", copy_cubin=False)
+    plan = json.loads((tmp_path / "f" / "layout_plan.json").read_text())
+    assert [st["operation"] for st in plan["weights"][0]["steps"]] == ["concatenate_output_shards", "tile_128x128"]
+    assert plan["scales"][0]["steps"] == ["concatenate_output_scale_shards_axis0", "widen_bf16_to_fp32_exact"]
+    zipf = json.loads((tmp_path / "e" / "layout_plan.json").read_text())
+    compile_engine(MODEL_ZIPF, "decode_t256", tmp_path / "g", copy_cubin=False)      # row-major weights: nothing to repack
+    assert json.loads((tmp_path / "g" / "layout_plan.json").read_text())["steps"] == [] and zipf["steps"]
+
+
+def test_dense_block_scale_contract_and_registry():
+    from netra_kernel_b200.compiler import dense
+    request = dense.dense_request(1, 2048, 4096)
+    contract, explanation = dense.plan_dense(request)
+    assert isinstance(contract, contracts.FallbackKernelContract) and contract.fallback == "framework.fp8_blockscale_linear"
+    assert explanation[0]["selected"] and explanation[0]["reasons"] == []
+    contract2, explanation2 = dense.plan_dense(dense.dense_request(16, 2048, 4096, epilogue="silu"))
+    assert not any(e["selected"] for e in explanation2) and any("M=16" in r for r in explanation2[0]["reasons"])
+    assert any("epilogue" in r for r in explanation2[0]["reasons"]) and contract2.stable_id == contract.stable_id
+    launch = contracts.Launch((16, 1, 1), (320, 1, 1), 0, 200000)
+    kc = dense.KernelContract(TARGET, 32, "dense", 1, 2048, 4096, "fp8_e4m3", "fp8_e4m3", "fp32", "bf16", "fp8_e4m3_per_token_block128_amax448",
+                              "fp8_e4m3_w128x128", 128, (128, 128), "row_major_fp8_block128", "tiles128x128_fp8_block128", "row_major_bf16",
+                              "identity", "probe", launch)
+    assert kc.stable_id.startswith("nk_") and len(kc.stable_id) == 27 and kc.to_dict()["shape"] == [1, 2048, 4096]
+    assert dataclasses.replace(kc, m=2).stable_id != kc.stable_id and dataclasses.replace(kc, evidence_refs=("x",)).stable_id == kc.stable_id
+    for bad in (dict(k=4000), dict(n=2000), dict(accumulator_dtype="bf16"), dict(operation="conv"), dict(m=0),
+                dict(numerical=dense.NumericalContract(deterministic=False))):
+        with pytest.raises(ValidationError):
+            dataclasses.replace(kc, **bad)
+
+
+def test_verify_profile_fixes_the_routed_rows(tmp_path):
+    """The reference's exact verify profile (12 draft positions x 64 sequences = 768 routed rows): the graph is sized by
+    route_rows, the runtime guards are m and batch."""
+    reg = profiles.load_profile_registry(LIB_ROOT, TARGET, tensor_parallel=1)
+    verify = next(p for p in reg if p.name == "verify_m12_b64_routes768")
+    assert frontend.token_rows(verify) == 768
+    hit = profiles.select_profile(reg, {"m": 12, "batch": 64, "sequence": 0, "route_rows": 768}, quantization="fp8_block128", tensor_parallel=1)
+    assert hit.supported and hit.profile.name == "verify_m12_b64_routes768"
+    engine_doc = compile_engine(MODEL, "verify_m12_b64_routes768", tmp_path / "v", copy_cubin=False)
+    guards = engine_doc["profiles"][0]["guards"]
+    assert guards["m"] == {"min": 12, "max": 12} and guards["batch"] == {"min": 64, "max": 64}
+    router = engine_doc["operations"][0]
+    assert router["launch"]["grid"][0] == 768 // 16 and [o["tactic"] for o in engine_doc["operations"]][2] == "token_sort_single_block"
+    bad = profiles.ShapeProfile("bad", (("batch", profiles.DimensionGuard(64, 64)), ("m", profiles.DimensionGuard(12, 12)),
+                                        ("route_rows", profiles.DimensionGuard(700, 700))))
+    with pytest.raises(ValidationError):
+        frontend.token_rows(bad)

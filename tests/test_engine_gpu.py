@@ -277,3 +277,25 @@ def test_c_caller_runs_the_documented_sequence(tmp_path):
     # a shape outside the guards is refused by the example before it binds anything
     done = subprocess.run([str(exe), str(tmp_path / "cpu_t16"), str(tmp_path / "cpu_t16" / "slots.txt"), "17"], capture_output=True, text=True)
     assert done.returncode == 1
+
+
+def test_verify_profile_engine_runs_768_routed_rows(tmp_path, expert_weights):
+    """The exact verify profile (m = 12 draft positions, batch = 64 -> 768 routed rows): launch shape (12, 64), parity of
+    the routing and of sampled outputs against the checker, and the m / batch guards."""
+    tokens = 768
+    tensors, hidden, router_w, _ = _tensors(expert_weights, tokens, seed=6)
+    subset = np.arange(2, tokens, 53)
+    ref = R.moe_layer(helpers.bits(hidden), helpers.bits(router_w), *helpers.np_weights(expert_weights), token_subset=subset)
+    session = _session(tmp_path, MODEL, "verify_m12_b64_routes768", tensors)
+    assert (session.shape.m, session.shape.batch) == (12, 64)
+    session.prepare(_stream())
+    session.launch(_stream())
+    torch.cuda.synchronize()
+    assert _status_words(session) == [0, 0, 0, 0]
+    assert np.array_equal(session.workspace_view("topk_ids", torch.int32, "cuda").cpu().numpy().reshape(tokens, 9), ref["topk_ids"])
+    assert np.array_equal(session.workspace_view("perm", torch.int32, "cuda").cpu().numpy(), ref["perm"])
+    m = R.parity_metrics(helpers.bits(tensors["output"])[subset], ref["out"])
+    assert m["max_abs"] <= helpers.MAX_ABS and m["rel_l2"] <= helpers.REL_L2, m
+    lib = er.load()
+    for bad in (er.LaunchShape(768, 1, 0, 1), er.LaunchShape(12, 63, 0, 1)):
+        assert lib.netra_engine_launch(session.handle, 0, ctypes.byref(bad), _stream()) == 5

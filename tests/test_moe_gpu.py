@@ -570,3 +570,26 @@ def test_add_rmsnorm_group_quant_bridge_and_fused_layer_entry(gpu_weights):
     assert torch.equal(layer.intermediates(tokens)["a_fp8"][tokens * 8:], a_rows)
     wy, wr, wq, _ = R.add_rmsnorm_group_quant(helpers.bits(hidden), helpers.bits(res), w.cpu().numpy(), 1e-6)
     assert np.array_equal(helpers.bits(normed), wy) and np.array_equal(helpers.bits(res_out), wr) and np.array_equal(a_rows.cpu().numpy(), wq)
+
+
+def test_weight_repack_and_scale_widening_match_the_layout_plan_byte_for_byte():
+    """The device steps of the layout plan against their CPU statement (compiler/layouts.py): the 128 x 128 tile repack of
+    random bytes for both slab shapes, and the exact BF16 -> FP32 widening of block scales."""
+    from netra_kernel_b200 import abi
+    from netra_kernel_b200.compiler import layouts as L
+    lib = abi.load()
+    g = torch.Generator().manual_seed(17)
+    for slabs, n, k in ((3, 1024, 2048), (2, 2048, 512), (1, 128, 128)):
+        src = torch.randint(0, 256, (slabs * n, k), generator=g, dtype=torch.uint8)
+        dst = torch.zeros_like(src).cuda()
+        abi.check(lib.netra_moe_repack_tiles_launch(dst.data_ptr(), src.cuda().data_ptr(), slabs * n, k, None), "repack_tiles_launch")
+        torch.cuda.synchronize()
+        assert np.array_equal(dst.cpu().numpy(), L.tile_128x128(src.numpy())), (slabs, n, k)
+    bits = torch.randint(0, 1 << 16, (257 * 8 * 16,), generator=g, dtype=torch.int32).to(torch.uint16)
+    bits = bits[(bits & 0x7F80) != 0x7F80]            # finite values
+    out = torch.zeros(bits.numel(), dtype=torch.float32, device="cuda")
+    abi.check(lib.netra_moe_widen_scales_bf16_launch(out.data_ptr(), bits.cuda().data_ptr(), bits.numel(), None), "widen_scales_launch")
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), L.widen_bf16_to_fp32(bits.numpy()).view(np.uint32))
+    assert lib.netra_moe_widen_scales_bf16_launch(None, None, 4, None) == -1
+    assert lib.netra_moe_repack_tiles_launch(dst.data_ptr(), dst.data_ptr(), 128, 128, None) == -1      # aliased
