@@ -105,18 +105,22 @@ int umma_setup() {
   if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(gate_up_tokmajor)", e);
   e = cudaFuncSetAttribute(netra_moe_down_tokmajor_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, down_tokmajor_smem_bytes());
   if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(down_tokmajor)", e);
+  e = cudaFuncSetAttribute(netra_moe_gate_up_tokmajor_gather_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, gate_up_tokmajor_smem_bytes());
+  if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(gate_up_tokmajor_gather)", e);
   e = cudaFuncSetAttribute(netra_moe_down_tokmajor_f16_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, down_tokmajor_f16_smem_bytes());
   if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(down_tokmajor_f16)", e);
   e = cudaFuncSetAttribute(netra_router_logits_f32_umma_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, router_umma_smem_bytes());
   if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(router_umma)", e);
   {
     // the register re-balancing inside these kernels is only deadlock-free for the launch allocation it was written for
-    cudaFuncAttributes a0, a1, a2;
+    cudaFuncAttributes a0, a1, a2, a3;
     e = cudaFuncGetAttributes(&a0, netra_moe_gate_up_tokmajor_sm100);
     if (e == cudaSuccess) e = cudaFuncGetAttributes(&a1, netra_moe_down_tokmajor_sm100);
     if (e == cudaSuccess) e = cudaFuncGetAttributes(&a2, netra_moe_down_tokmajor_f16_sm100);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a3, netra_moe_gate_up_tokmajor_gather_sm100);
     if (e != cudaSuccess) return fail_cuda("cudaFuncGetAttributes(tokmajor)", e);
-    g_tokmajor_ok[device] = a0.numRegs == kTmRegsLaunch && a1.numRegs == kTmRegsLaunch && a2.numRegs == kTmRegsLaunch;
+    g_tokmajor_ok[device] = a0.numRegs == kTmRegsLaunch && a1.numRegs == kTmRegsLaunch && a2.numRegs == kTmRegsLaunch &&
+                            a3.numRegs == kTmRegsLaunch;
   }
   g_umma_ready[device] = true;
   return 0;
@@ -134,7 +138,7 @@ bool use_tokmajor(int device, uint64_t pairs, uint32_t routed_experts) {
 struct netra_moe_layer {
   netra_moe_layer_desc_t desc;
   netra_moe_workspace_layout_t lay;
-  CUtensorMap tm_w13, tm_w2, tm_a32, tm_a64, tm_a128, tm_h32, tm_h64, tm_h128, tm_router;
+  CUtensorMap tm_w13, tm_w2, tm_a1, tm_a32, tm_a64, tm_a128, tm_h32, tm_h64, tm_h128, tm_router;
   int sm_count;
   int device;
   uint32_t launches;
@@ -289,6 +293,7 @@ int netra_moe_layer_create(const netra_moe_layer_desc_t* desc, netra_moe_layer_t
     rc = rc ? rc : encode_u8_2d(&layer->tm_w2, desc->w2_fp8, slabs * kHidden, kInter, 128);
   }
   rc = rc ? rc : encode_u8_2d(&layer->tm_router, desc->router_weight_bf16, kRouted, kHidden * 2, 128);
+  rc = rc ? rc : encode_u8_2d(&layer->tm_a1, ws + lay.a_fp8, rows, kHidden, 1);     // one-row box: four-row gathers
   rc = rc ? rc : encode_u8_2d(&layer->tm_a32, ws + lay.a_fp8, rows, kHidden, 32);
   rc = rc ? rc : encode_u8_2d(&layer->tm_a64, ws + lay.a_fp8, rows, kHidden, 64);
   rc = rc ? rc : encode_u8_2d(&layer->tm_a128, ws + lay.a_fp8, rows, kHidden, 128);
@@ -307,7 +312,9 @@ int netra_moe_layer_create(const netra_moe_layer_desc_t* desc, netra_moe_layer_t
 
 uint32_t netra_moe_layer_launch_count(const netra_moe_layer_t* layer, uint32_t tokens) {
   if (layer == nullptr) return 0;
-  return tokens <= (uint32_t)kSortSmallMaxRows ? layer->launches - 2 : layer->launches;
+  uint32_t n = tokens <= (uint32_t)kSortSmallMaxRows ? layer->launches - 2 : layer->launches;
+  if (use_tokmajor(layer->device, (uint64_t)tokens * kTopK, kRouted) && layer->gemm_mode != 1) --n;   // no row gather
+  return n;
 }
 
 }  // extern "C" (reopened below)
@@ -392,12 +399,14 @@ int launch_stage(netra_moe_layer* layer, uint32_t stage, const void* hidden, con
     case 4:
       if (tokens > (uint32_t)kSortSmallMaxRows) netra_moe_sort_scatter_sm100<<<nseg, 256, 0, stream>>>(perm, inv_perm, seg_hist, ids9, tokens);
       break;
-    case 5: netra_moe_gather_rows_sm100<<<(pairs + 7) / 8, 256, 0, stream>>>(a_fp8, a_scale, perm, tokens); break;
+    case 5:   // the token-major gate_up gathers its token rows itself: no expert-sorted copy is made for it
+      if (!tokmajor) netra_moe_gather_rows_sm100<<<(pairs + 7) / 8, 256, 0, stream>>>(a_fp8, a_scale, perm, tokens);
+      break;
     case 6:
       if (tokmajor)
-        netra_moe_gate_up_tokmajor_sm100<<<layer->sm_count, kTmThreads, gate_up_tokmajor_smem_bytes(), stream>>>(
-            layer->tm_w13, layer->tm_a128, a_scale, layer->desc.w13_scale_f32, offsets, h_fp8, h_scale, kRouted + 1,
-            layer->desc.weights_tiled, status);
+        netra_moe_gate_up_tokmajor_gather_sm100<<<layer->sm_count, kTmThreads, gate_up_tokmajor_smem_bytes(), stream>>>(
+            layer->tm_w13, layer->tm_a1, a_scale, layer->desc.w13_scale_f32, offsets, perm, h_fp8, h_scale, kRouted + 1,
+            layer->desc.weights_tiled, pairs, status);
       else
         netra_moe_gate_up_umma_sm100<<<layer->sm_count, kGemmThreads, gate_up_smem_bytes(), stream>>>(
             layer->tm_w13, layer->tm_a32, layer->tm_a64, layer->tm_a128, a_scale, layer->desc.w13_scale_f32, offsets, h_fp8,

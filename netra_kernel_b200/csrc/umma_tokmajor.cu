@@ -112,6 +112,7 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
   static_assert(!(kGateUp && kF16Out), "FP16 partial rows are an output format of the down projection");
   static_assert(kGateUp || !kGatherX, "only the gate_up projection reads token rows");
   using C = TmCfg<kGateUp, kF16Out>;
+  static_assert(!kGatherX || C::kTokTile == 128, "a warp of 32 lanes gathers 4 rows each");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* stage_base = smem;
@@ -193,7 +194,85 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
 
   if (warp < 4) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kTmRegsLow));
-    if (warp == 0 && lane == 0) {
+    if (kGatherX && warp == 0) {
+      // =========================== TMA producer, token rows gathered (whole warp) ===========================
+      // Lane l owns rows 4l .. 4l+3 of the 128-row tile: it looks up where those sorted positions live in token order once
+      // per item and fetches them with one four-row gather per K-block (and their scale rows with four small bulk copies);
+      // lane 0 also does the waits, the byte counts and the weight tiles.
+      if (lane == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)tm_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)tm_x128) : "memory");
+      }
+      const uint64_t pol_w = policy_evict_last();
+      const uint64_t pol_x = policy_evict_last();
+      uint32_t it = 0, n_item = 0;
+      bool ok = true;
+      for (int item = first_item; ok && item < total_items; item += stride, ++n_item) {
+        const Item w = get_item((int)n_item, item);
+        int src[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int pos = w.row0 + min(4 * lane + j, w.m_valid - 1);       // rows past the item's end repeat its last row
+          src[j] = pos >= (int)tok_row_base ? pos : (int)tok_row_base + (__ldg(perm + pos) >> 3);
+        }
+        const int slot = n_item % C::kScaleSlots;
+        const uint32_t sbar = smem_u32(&sfull_bar[slot]);
+        const uint32_t sdst = smem_u32(scale_base + slot * C::kScaleSlotBytes);
+        bool good = true;
+        if (lane == 0) {
+          good = mbar_wait(smem_u32(&sempty_bar[slot]), ((n_item / C::kScaleSlots) & 1) ^ 1, abort_flag);
+          if (good) {
+            mbar_expect_tx(sbar, C::kXsBytes + 2 * C::kWsBytes);
+            const float* wsrc = w_scale + ((size_t)w.group * C::kSlabTiles + w.ntile) * C::kKBlocks;
+            bulk_load(sdst + C::kXsBytes, wsrc, C::kWsBytes, sbar);
+            bulk_load(sdst + C::kXsBytes + C::kWsBytes, wsrc + (kInter / kTileRows) * C::kKBlocks, C::kWsBytes, sbar);
+          } else {
+            status[0] = kStatusProducerTimeout; *abort_flag = 1;
+          }
+        }
+        good = __shfl_sync(0xffffffffu, good ? 1 : 0, 0) != 0;
+        if (!good) { ok = false; break; }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          bulk_load(sdst + (uint32_t)(4 * lane + j) * C::kKBlocks * 4, x_scale + (size_t)src[j] * C::kKBlocks, C::kKBlocks * 4, sbar);
+        const bool have_next = item + stride < total_items;
+        const Item wn = have_next ? get_item((int)n_item + 1, item + stride) : w;
+        for (int kb = 0; kb < C::kKBlocks; ++kb, ++it) {
+          const int s = it % C::kStages;
+          const uint32_t bar = smem_u32(&full_bar[s]);
+          const uint32_t dst = smem_u32(stage_base + s * C::kStageBytes);
+          if (lane == 0) {
+            // weight boxes of K-block kb + kPrefetch (in this item or the next) are pulled into the L2 now
+            const int pk = kb + C::kPrefetch;
+            const Item& wp = pk < C::kKBlocks ? w : wn;
+            if (pk < C::kKBlocks || have_next) {
+              const int kp = pk < C::kKBlocks ? pk : pk - C::kKBlocks;
+              const int wx = w_tiled ? 0 : kp * kBlock;
+              const int wy0 = w_tiled ? ((wp.group * C::kSlabTiles + wp.ntile) * C::kKBlocks + kp) * kTileRows
+                                      : wp.group * C::kSlabRows + wp.ntile * kTileRows;
+              const int wy1 = wy0 + (w_tiled ? (kInter / kTileRows) * C::kKBlocks * kTileRows : kInter);
+              tma_prefetch_2d(tm_w, wx, wy0);
+              tma_prefetch_2d(tm_w, wx, wy1);
+            }
+            good = mbar_wait(smem_u32(&empty_bar[s]), ((it / C::kStages) & 1) ^ 1, abort_flag);
+            if (good) {
+              mbar_expect_tx(bar, C::kStageBytes);
+              const int wx = w_tiled ? 0 : kb * kBlock;
+              const int wy0 = w_tiled ? ((w.group * C::kSlabTiles + w.ntile) * C::kKBlocks + kb) * kTileRows
+                                      : w.group * C::kSlabRows + w.ntile * kTileRows;
+              const int wy1 = wy0 + (w_tiled ? (kInter / kTileRows) * C::kKBlocks * kTileRows : kInter);
+              tma_load_2d(dst + C::kTokTile * kBlock, tm_w, bar, wx, wy0, pol_w);
+              tma_load_2d(dst + C::kTokTile * kBlock + kWTileBytes, tm_w, bar, wx, wy1, pol_w);
+            } else {
+              status[0] = kStatusProducerTimeout; *abort_flag = 1;
+            }
+          }
+          good = __shfl_sync(0xffffffffu, good ? 1 : 0, 0) != 0;      // also orders the lanes' gathers after lane 0's wait
+          if (!good) { ok = false; break; }
+          tma_gather4_2d(dst + (uint32_t)lane * 4 * kBlock, tm_x128, bar, kb * kBlock, src[0], src[1], src[2], src[3], pol_x);
+        }
+      }
+    } else if (!kGatherX && warp == 0 && lane == 0) {
       // =========================== TMA producer ===========================
       asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)tm_w) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)tm_x128) : "memory");
@@ -453,6 +532,18 @@ netra_moe_down_tokmajor_sm100(const __grid_constant__ CUtensorMap tm_w2, const _
                               uint32_t num_groups, uint32_t w_tiled, uint32_t* status) {
   tokmajor_gemm_body<false>(&tm_w2, &tm_h128, h_scale, w2_scale, offsets, nullptr, nullptr, down, nullptr, num_groups, w_tiled,
                             status);
+}
+
+// gate_up with the token rows gathered from token order (no expert-sorted copy of the quantised rows is needed):
+// tm_tok1 is a one-row-box map over the quantised-row buffer, tok_scale its scales [rows, 16], perm the sorted
+// position -> pair index table, tok_row_base the first token-order row of that buffer.
+extern "C" __global__ void __launch_bounds__(kTmThreads, 1)
+netra_moe_gate_up_tokmajor_gather_sm100(const __grid_constant__ CUtensorMap tm_w13, const __grid_constant__ CUtensorMap tm_tok1,
+                                        const float* tok_scale, const float* w13_scale, const int32_t* offsets, const int32_t* perm,
+                                        uint8_t* h_fp8, float* h_scale, uint32_t num_groups, uint32_t w_tiled, uint32_t tok_row_base,
+                                        uint32_t* status) {
+  tokmajor_gemm_body<true, false, true>(&tm_w13, &tm_tok1, tok_scale, w13_scale, offsets, h_fp8, h_scale, nullptr, nullptr, num_groups,
+                                        w_tiled, status, perm, tok_row_base);
 }
 
 // The down projection writing FP16 partial rows [rows, 2048] (half the bytes of the FP32 rows; consumed by

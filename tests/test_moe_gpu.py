@@ -69,7 +69,8 @@ def check_against(ref, out, inter, tokens, *, subset=None):
     a = inter["a_fp8"].numpy()
     assert np.array_equal(a[pairs:], ref["a_fp8"]), "input FP8 codes must be bit-exact"
     assert np.array_equal(inter["a_scale"].numpy()[pairs:], ref["a_scale"])
-    assert np.array_equal(a[:pairs], ref["a_fp8"][ref["perm"] // 8])
+    if tokens < 1024:      # the swap-AB gate_up reads an expert-sorted copy of the rows; the token-major one gathers them itself
+        assert np.array_equal(a[:pairs], ref["a_fp8"][ref["perm"] // 8])
     toks = np.arange(tokens) if subset is None else np.asarray(subset)
     # intermediate FP8 codes: slot order in the checker, sorted rows on the GPU
     h = inter["h_fp8"].numpy()
@@ -86,7 +87,7 @@ def test_layer_t16_matches_golden_fixture(gpu_weights):
     data = dict(np.load(helpers.GOLDEN / "moe_layer_t16.npz"))
     hidden, router_w, _ = synth.make_activations(16)
     layer = make_layer(gpu_weights, router_w, 16)
-    assert layer.launches_per_call(16) == 7 and layer.launches_per_call(2048) == 9
+    assert layer.launches_per_call(16) == 7 and layer.launches_per_call(1024) == 6 and layer.launches_per_call(2048) == 8
     out, inter = run_layer(layer, hidden)
     m = check_against(data, out, inter, 16)
     assert m["rel_l2"] < 1e-3
