@@ -348,6 +348,12 @@ int netra_moe_kernel_launch_info(uint32_t which, uint32_t* block_threads, uint32
  * forms produce identical results. */
 int netra_moe_layer_set_gemm_mode(netra_moe_layer_t* layer, uint32_t mode);
 
+/* Where the token-major gate_up takes its token rows from.  in_gemm 0 (default): an expert-sorted copy of the quantised
+ * rows written by the row-gather stage.  in_gemm 1: no copy; the GEMM's producer fetches the rows from token order with
+ * four-row TMA gathers (cp.async.bulk.tensor tile::gather4).  Same results; measured 2.5 times slower at 8,192 tokens
+ * (32 gather instructions per 128-row tile and K-block), kept as a recorded tactic. */
+int netra_moe_layer_set_row_gather(netra_moe_layer_t* layer, uint32_t in_gemm);
+
 /* Router of calls above 1024 rows.  mode 0 (default): BF16 tensor-core pass with FP32 accumulation, then an FP64
  * recomputation of those logits that can reach the top 8 and whose BF16 rounding the FP32 value cannot decide:
  * the selected ids, their logits and the routing weights are those of the exactly rounded dot products; logits

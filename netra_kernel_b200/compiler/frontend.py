@@ -178,25 +178,15 @@ def routed_moe_layer_graph(model: dict[str, Any], profile: ShapeProfile) -> Grap
                       {"routed_experts": experts, "top_k": c["top_k"]},
                       semantics("token_sort.ptr5_u32.v1", "i32", "none", "pair_index_t8_plus_slot.offsets258_shared_group_last",
                                 "stable_expert_major.v1")))
-    layout_name = "tiles128" if opt["weight_layout"] == "tiles128" else "row_major"
-    if token_major:
-        # the token-major gate_up gathers its token rows from token order (TMA four-row gathers): no sorted copy, no gather launch
-        ops.append(op("gate_up", "moe_fp8_grouped_gemm", "gate_up_silu_requant", ["a_fp8", "a_scale", "w13", "w13_scale", "offsets", "perm"],
-                      ["h_fp8", "h_scale", "status"], gemm_constants,
-                      semantics("gate_up_grouped.tmap2_ptr6_u32x3_ptr.v1", "fp8e4m3_fp8e4m3_to_fp8e4m3_f32", "fp8_e4m3_w128x128_a1x128_amax448",
-                                f"token_major.token_rows_gathered.{layout_name}", "kblock_fma_ascending.silu_fp32.bf16_round_then_amax.v1")))
-    else:
-        ops += [
-            op("gather_rows", "moe_sort", "gather_quantized_rows", ["perm", "a_fp8", "a_scale"], ["a_fp8", "a_scale"],
-               {"hidden": hidden, "top_k": c["top_k"], "scale_block": c["scale_block"]},
-               semantics("gather_rows.ptr3_u32.v1", "fp8e4m3_f32", "fp8_e4m3_per_token_block128_amax448",
-                         "sorted_rows_first.token_rows_after_pairs", "copy.v1")),
-            op("gate_up", "moe_fp8_grouped_gemm", "gate_up_silu_requant", ["a_fp8", "a_scale", "w13", "w13_scale", "offsets"],
-               ["h_fp8", "h_scale", "status"], gemm_constants,
-               semantics(f"gate_up_grouped.{maps}_ptr5_u32x2_ptr.v1", "fp8e4m3_fp8e4m3_to_fp8e4m3_f32", "fp8_e4m3_w128x128_a1x128_amax448",
-                         form, "kblock_fma_ascending.silu_fp32.bf16_round_then_amax.v1")),
-        ]
     ops += [
+        op("gather_rows", "moe_sort", "gather_quantized_rows", ["perm", "a_fp8", "a_scale"], ["a_fp8", "a_scale"],
+           {"hidden": hidden, "top_k": c["top_k"], "scale_block": c["scale_block"]},
+           semantics("gather_rows.ptr3_u32.v1", "fp8e4m3_f32", "fp8_e4m3_per_token_block128_amax448",
+                     "sorted_rows_first.token_rows_after_pairs", "copy.v1")),
+        op("gate_up", "moe_fp8_grouped_gemm", "gate_up_silu_requant", ["a_fp8", "a_scale", "w13", "w13_scale", "offsets"],
+           ["h_fp8", "h_scale", "status"], gemm_constants,
+           semantics(f"gate_up_grouped.{maps}_ptr5_u32x2_ptr.v1", "fp8e4m3_fp8e4m3_to_fp8e4m3_f32", "fp8_e4m3_w128x128_a1x128_amax448",
+                     form, "kblock_fma_ascending.silu_fp32.bf16_round_then_amax.v1")),
         op("down", "moe_fp8_grouped_gemm", "down_projection", ["h_fp8", "h_scale", "w2", "w2_scale", "offsets"],
            ["down_f32", "status"], gemm_constants,
            semantics(f"down_grouped.{maps}_ptr4_u32x2_ptr.v1", "fp8e4m3_fp8e4m3_to_f16" if f16_rows else "fp8e4m3_fp8e4m3_to_f32",

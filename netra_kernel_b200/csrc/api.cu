@@ -145,6 +145,7 @@ struct netra_moe_layer {
   uint32_t gemm_mode;     // 0: pick the GEMM form by size, 1: always the swap-AB (decode) kernels
   uint32_t router_mode;   // 0: pick the router by size, 1: always the FP64 tensor-core router, 2: as 0 with every logit exact
   uint32_t partial_f16;   // 1: the token-major down projection writes FP16 partial rows (prefill contract)
+  bool gather_rows_in_gemm;   // the token-major gate_up gathers its rows with four-row TMA gathers (slower; kept as a recorded tactic)
   bool prequantised;      // set for the duration of a call whose token rows were quantised by the fused norm kernel
 };
 
@@ -280,6 +281,7 @@ int netra_moe_layer_create(const netra_moe_layer_desc_t* desc, netra_moe_layer_t
   layer->router_mode = 0;
   layer->partial_f16 = 0;
   layer->prequantised = false;
+  layer->gather_rows_in_gemm = false;
   const uint64_t slabs = desc->num_expert_slabs ? desc->num_expert_slabs : (uint64_t)(kRouted + 1);
   if (slabs > (uint64_t)(kRouted + 1)) { delete layer; return fail("layer_create: at most 257 expert slabs"); }
   uint8_t* ws = (uint8_t*)desc->workspace;
@@ -313,7 +315,7 @@ int netra_moe_layer_create(const netra_moe_layer_desc_t* desc, netra_moe_layer_t
 uint32_t netra_moe_layer_launch_count(const netra_moe_layer_t* layer, uint32_t tokens) {
   if (layer == nullptr) return 0;
   uint32_t n = tokens <= (uint32_t)kSortSmallMaxRows ? layer->launches - 2 : layer->launches;
-  if (use_tokmajor(layer->device, (uint64_t)tokens * kTopK, kRouted) && layer->gemm_mode != 1) --n;   // no row gather
+  if (layer->gather_rows_in_gemm && use_tokmajor(layer->device, (uint64_t)tokens * kTopK, kRouted) && layer->gemm_mode != 1) --n;   // no row gather
   return n;
 }
 
@@ -399,14 +401,21 @@ int launch_stage(netra_moe_layer* layer, uint32_t stage, const void* hidden, con
     case 4:
       if (tokens > (uint32_t)kSortSmallMaxRows) netra_moe_sort_scatter_sm100<<<nseg, 256, 0, stream>>>(perm, inv_perm, seg_hist, ids9, tokens);
       break;
-    case 5:   // the token-major gate_up gathers its token rows itself: no expert-sorted copy is made for it
-      if (!tokmajor) netra_moe_gather_rows_sm100<<<(pairs + 7) / 8, 256, 0, stream>>>(a_fp8, a_scale, perm, tokens);
+    case 5:   // the gathering gate_up fetches its token rows itself: no expert-sorted copy is made for it
+      if (!(tokmajor && layer->gather_rows_in_gemm))
+        netra_moe_gather_rows_sm100<<<(pairs + 7) / 8, 256, 0, stream>>>(a_fp8, a_scale, perm, tokens);
       break;
     case 6:
-      if (tokmajor)
+      if (tokmajor && layer->gather_rows_in_gemm)
+        // Measured at 8,192 tokens: 607 us against 240 us for the form below.  One four-row gather per lane and K-block is 32
+        // TMA instructions where the sorted copy needs one; the copy engine's issue rate, not the bytes, sets the pace.
         netra_moe_gate_up_tokmajor_gather_sm100<<<layer->sm_count, kTmThreads, gate_up_tokmajor_smem_bytes(), stream>>>(
             layer->tm_w13, layer->tm_a1, a_scale, layer->desc.w13_scale_f32, offsets, perm, h_fp8, h_scale, kRouted + 1,
             layer->desc.weights_tiled, pairs, status);
+      else if (tokmajor)
+        netra_moe_gate_up_tokmajor_sm100<<<layer->sm_count, kTmThreads, gate_up_tokmajor_smem_bytes(), stream>>>(
+            layer->tm_w13, layer->tm_a128, a_scale, layer->desc.w13_scale_f32, offsets, h_fp8, h_scale, kRouted + 1,
+            layer->desc.weights_tiled, status);
       else
         netra_moe_gate_up_umma_sm100<<<layer->sm_count, kGemmThreads, gate_up_smem_bytes(), stream>>>(
             layer->tm_w13, layer->tm_a32, layer->tm_a64, layer->tm_a128, a_scale, layer->desc.w13_scale_f32, offsets, h_fp8,
@@ -636,6 +645,12 @@ int netra_moe_kernel_launch_info(uint32_t which, uint32_t* block_threads, uint32
 int netra_moe_layer_set_gemm_mode(netra_moe_layer_t* layer, uint32_t mode) {
   if (layer == nullptr || mode > 1) return fail("layer_set_gemm_mode: null layer or unknown mode");
   layer->gemm_mode = mode;
+  return 0;
+}
+
+int netra_moe_layer_set_row_gather(netra_moe_layer_t* layer, uint32_t in_gemm) {
+  if (layer == nullptr || in_gemm > 1) return fail("layer_set_row_gather: null layer or unknown mode");
+  layer->gather_rows_in_gemm = in_gemm != 0;
   return 0;
 }
 

@@ -118,6 +118,11 @@ class RoutedMoELayer:
         """0: the layer picks the grouped-GEMM form by token count (token-major from 1,024 tokens); 1: always swap-AB."""
         abi.check(self.lib.netra_moe_layer_set_gemm_mode(self.handle, mode), "layer_set_gemm_mode")
 
+    def set_row_gather(self, in_gemm: bool) -> None:
+        """True: the token-major gate_up gathers its token rows with four-row TMA gathers instead of reading an
+        expert-sorted copy (same results, slower: a recorded tactic)."""
+        abi.check(self.lib.netra_moe_layer_set_row_gather(self.handle, int(bool(in_gemm))), "layer_set_row_gather")
+
     def set_router_mode(self, mode: int) -> None:
         """0: calls above 1,024 rows take the BF16 tensor-core router with exact FP64 recomputation of the undecided logits
         that can reach the top 8 (routing identical to the exact logits'); 2: the same with every undecided logit

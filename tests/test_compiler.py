@@ -191,7 +191,7 @@ def test_planner_selects_by_layout_size_and_never_a_rejected_tactic():
     assert down.tactic.name == "down_projection_umma_tokmajor_row_major"
     assert down.contract.launch.registers_per_thread == 168 and down.contract.launch.block == (384, 1, 1)
     gate = next(p for p in big.operations if p.operation.name == "gate_up")
-    assert gate.tactic.name == "gate_up_silu_requant_umma_tokmajor_gather_row_major"
+    assert gate.tactic.name == "gate_up_silu_requant_umma_tokmajor_row_major"
     other = [c for c in gate.explanation if c["tactic"] == "gate_up_silu_requant_umma_swapab_tiles128"][0]
     assert any("semantic layouts mismatch" in r for r in other["reasons"])
     # below 1,024 tokens the token-major tactics are out of their size limits and the swap-AB form is requested
@@ -243,14 +243,12 @@ def test_engine_compile_is_deterministic_and_valid(tmp_path):
 def test_engine_with_bias_shared_weight_and_segmented_sort(tmp_path):
     doc = compile_engine(MODEL_ZIPF, "prefill_t8192", tmp_path / "e")
     names = [o["name"] for o in doc["operations"]]
-    assert names == ["router_logits", "topk_quant", "sort_hist", "sort_scan", "sort_scatter", "gate_up", "down", "combine"]
+    assert names == ["router_logits", "topk_quant", "sort_hist", "sort_scan", "sort_scatter", "gather_rows", "gate_up", "down", "combine"]
     recipe = json.loads((tmp_path / "e" / "graph_recipe.json").read_text())
     assert {"router_bias", "shared_weight"} <= set(recipe["binding_slots"])
     assert json.loads((tmp_path / "e" / "layout_plan.json").read_text())["steps"] == []
-    gate = doc["operations"][5]
+    gate = doc["operations"][6]
     assert gate["arguments"][0]["tensor_map"] == {"rows": 257 * 1024, "row_bytes": 2048, "box_rows": 128, "box_bytes": 128, "swizzle": "128B"}
-    # the token rows are gathered four at a time through a one-row box over the quantised-row buffer
-    assert gate["arguments"][1]["tensor_map"] == {"rows": 8192 * 9, "row_bytes": 2048, "box_rows": 1, "box_bytes": 128, "swizzle": "128B"}
     assert gate["launch"]["grid"] == [148, 1, 1]
 
 

@@ -69,8 +69,7 @@ def check_against(ref, out, inter, tokens, *, subset=None):
     a = inter["a_fp8"].numpy()
     assert np.array_equal(a[pairs:], ref["a_fp8"]), "input FP8 codes must be bit-exact"
     assert np.array_equal(inter["a_scale"].numpy()[pairs:], ref["a_scale"])
-    if tokens < 1024:      # the swap-AB gate_up reads an expert-sorted copy of the rows; the token-major one gathers them itself
-        assert np.array_equal(a[:pairs], ref["a_fp8"][ref["perm"] // 8])
+    assert np.array_equal(a[:pairs], ref["a_fp8"][ref["perm"] // 8])
     toks = np.arange(tokens) if subset is None else np.asarray(subset)
     # intermediate FP8 codes: slot order in the checker, sorted rows on the GPU
     h = inter["h_fp8"].numpy()
@@ -87,7 +86,7 @@ def test_layer_t16_matches_golden_fixture(gpu_weights):
     data = dict(np.load(helpers.GOLDEN / "moe_layer_t16.npz"))
     hidden, router_w, _ = synth.make_activations(16)
     layer = make_layer(gpu_weights, router_w, 16)
-    assert layer.launches_per_call(16) == 7 and layer.launches_per_call(1024) == 6 and layer.launches_per_call(2048) == 8
+    assert layer.launches_per_call(16) == 7 and layer.launches_per_call(2048) == 9
     out, inter = run_layer(layer, hidden)
     m = check_against(data, out, inter, 16)
     assert m["rel_l2"] < 1e-3
@@ -266,6 +265,24 @@ def test_prefill_fp16_partial_rows_tactic(gpu_weights, expert_weights):
     ref_small = layer(small.cuda()).clone()
     layer.set_partial_format(0)
     assert torch.equal(layer(small.cuda()).view(torch.int16), ref_small.view(torch.int16))
+
+
+def test_token_rows_gathered_inside_the_gemm_give_the_same_bytes(gpu_weights):
+    """The recorded tactic that skips the expert-sorted copy: the token-major gate_up fetches its rows from token order with
+    four-row TMA gathers.  Intermediates and output must equal the default form's bit for bit; one launch fewer."""
+    for tokens, alpha in ((2048, 0.0), (1500, 3.0)):
+        hidden, router_w, bias = synth.make_activations(tokens, alpha or None, seed=12)
+        layer = make_layer(gpu_weights, router_w, tokens, bias)
+        out_a, inter_a = run_layer(layer, hidden)
+        layer.set_row_gather(True)
+        assert layer.launches_per_call(tokens) == 8
+        layer.intermediates(tokens)["a_fp8"][: tokens * 8].zero_()          # nothing may read the sorted copy now
+        out_b, inter_b = run_layer(layer, hidden)
+        rows = tokens * 9
+        for key in ("h_fp8", "h_scale", "down"):
+            assert torch.equal(inter_a[key][:rows], inter_b[key][:rows]), key
+        assert torch.equal(out_a.view(torch.int16), out_b.view(torch.int16))
+        assert not inter_b["a_fp8"][: tokens * 8].any()
 
 
 def test_mxfp4_expansion_kernel_and_layer(expert_weights):
