@@ -154,7 +154,9 @@ typedef struct netra_moe_layer_desc {
   void* workspace;                    /* device, 1024-byte aligned */
   uint64_t workspace_bytes;
   uint32_t weights_tiled;             /* 0: w13/w2 are the row-major slabs above; 1: they were rewritten by
-                                         netra_moe_repack_tiles_launch (same bytes, tile order) */
+                                         netra_moe_repack_tiles_launch (same bytes, tile order); 2: the experts are
+                                         MXFP4 - w13_fp8/w2_fp8 are the code blocks and w13_scale_f32/w2_scale_f32 the
+                                         scale atoms (bytes) written by netra_moe_mxfp4_pack_launch */
   uint32_t num_expert_slabs;          /* slabs behind w13/w2; 0 means 257.  Fewer is only meaningful for callers that
                                          use the routing stages (0-5, 8) and run the experts elsewhere */
 } netra_moe_layer_desc_t;
@@ -183,6 +185,18 @@ int netra_moe_widen_scales_bf16_launch(float* dst_f32, const void* src_bf16, uin
  * The 4-bit codes are not streamed by the GEMMs: the weight traffic is that of FP8. */
 int netra_moe_mxfp4_expand_launch(void* dst_fp8, float* dst_scale_f32, uint32_t* inexact_u32, const void* packed_e2m1,
                                   const void* scales_e8m0, uint64_t total_rows, uint32_t k, cudaStream_t stream);
+
+/* The native MXFP4 path (the role of kernels/gfx1151/mxfp4/decode/mxfp4_decode_gate_gfx1151.s:1-15 and
+ * mxfp4_decode_down_gfx1151.s:1-14 in the call sequence of runtime/gfx1151/mxfp4/decode/runtime.h:10-47): the expert
+ * weights stay four-bit in memory and are multiplied by tcgen05.mma.kind::mxf8f6f4.block_scale, the E8M0 scales reaching
+ * the tensor core through TMEM.  This load-time step rewrites the same packed slabs (packed_e2m1 [total_rows, k/2],
+ * scales_e8m0 [total_rows, k/32]) into the operand layout of those kernels, same sizes: dst_codes holds one contiguous
+ * 8 KiB block per (128-row tile, 128-element K-block) and dst_scale_atoms one 512-byte atom per block with row r's
+ * four scale bytes at 16 * (r % 32) + 4 * (r / 32).  A layer created with weights_tiled = 2 on these buffers streams
+ * 0.53 bytes per weight instead of 1.0; it runs the swap-AB kernels at every token count.  Code pointers must be
+ * 32-byte aligned for the layer, total_rows and k multiples of 128, at most 65,535 row tiles per call. */
+int netra_moe_mxfp4_pack_launch(void* dst_codes, void* dst_scale_atoms, const void* packed_e2m1, const void* scales_e8m0,
+                                uint64_t total_rows, uint32_t k, cudaStream_t stream);
 
 /* Control plane (serialised by the caller): encodes the tensor maps of the persistent buffers
  * and clears the status words.  No device memory is allocated. */
@@ -338,7 +352,7 @@ int netra_ep_layer_status(netra_ep_layer_t* layer, uint32_t status_out[4]);
 int netra_ep_layer_destroy(netra_ep_layer_t* layer);
 
 /* Block size and dynamic shared memory of the tensor-core kernels (which: 0 gate_up, 1 down, 2 and 3 their
- * token-major forms, 4 token-major down with FP16 rows, 5 tensor-core router), so
+ * token-major forms, 4 token-major down with FP16 rows, 5 tensor-core router, 6 and 7 gate_up and down on MXFP4 weights), so
  * that an engine manifest written ahead of time can be checked against the built library. */
 int netra_moe_kernel_launch_info(uint32_t which, uint32_t* block_threads, uint32_t* dynamic_smem_bytes);
 

@@ -74,6 +74,27 @@ int encode_u8_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row
   return 0;
 }
 
+// MXFP4 code blocks written by netra_moe_mxfp4_pack_launch: [tile_rows, 128] four-bit elements, 64 bytes per row in
+// memory.  The copy engine widens each group of 16 codes (8 bytes) to 16 bytes of shared memory, so a box of
+// 128 x 128 elements lands as the same 16 KiB, 128-byte-swizzled tile an E4M3 box does.
+int encode_fp4_tiles(CUtensorMap* map, const void* base, uint64_t tile_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return fail("cuTensorMapEncodeTiled is not available from the driver");
+  if (((uintptr_t)base & 31) != 0) return fail("MXFP4 code blocks must be 32-byte aligned");
+  cuuint64_t dims[2] = {128, tile_rows};
+  cuuint64_t strides[1] = {64};
+  cuuint32_t box[2] = {128, 128};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_error, sizeof g_error, "cuTensorMapEncodeTiled (MXFP4 tiles) failed with CUresult %d", (int)r);
+    return -1;
+  }
+  return 0;
+}
+
 // Per-device set-up of the tensor-core kernels: the opt-in to more than 48 KiB of dynamic shared memory is a
 // per-device function attribute, so a process that drives several GPUs runs this once for each of them.
 constexpr int kMaxDevices = 64;
@@ -101,6 +122,10 @@ int umma_setup() {
   if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(gate_up)", e);
   e = cudaFuncSetAttribute(netra_moe_down_umma_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, down_smem_bytes());
   if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(down)", e);
+  e = cudaFuncSetAttribute(netra_moe_gate_up_mxfp4_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, gate_up_mxfp4_smem_bytes());
+  if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(gate_up_mxfp4)", e);
+  e = cudaFuncSetAttribute(netra_moe_down_mxfp4_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, down_mxfp4_smem_bytes());
+  if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(down_mxfp4)", e);
   e = cudaFuncSetAttribute(netra_moe_gate_up_tokmajor_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, gate_up_tokmajor_smem_bytes());
   if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(gate_up_tokmajor)", e);
   e = cudaFuncSetAttribute(netra_moe_down_tokmajor_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, down_tokmajor_smem_bytes());
@@ -132,6 +157,7 @@ constexpr uint32_t kTokMajorMinRowsPerExpert = 32;
 bool use_tokmajor(int device, uint64_t pairs, uint32_t routed_experts) {
   return g_tokmajor_ok[device] && pairs >= (uint64_t)kTokMajorMinRowsPerExpert * routed_experts;
 }
+constexpr uint32_t kWeightsMxfp4 = 2;   // value of weights_tiled: MXFP4 code blocks and scale atoms
 
 }  // namespace
 
@@ -287,7 +313,11 @@ int netra_moe_layer_create(const netra_moe_layer_desc_t* desc, netra_moe_layer_t
   uint8_t* ws = (uint8_t*)desc->workspace;
   const uint64_t rows = (uint64_t)desc->max_tokens * (kTopK + 1);
   int rc = 0;
-  if (desc->weights_tiled) {   // tiles of 128 rows x 128 bytes, one after another
+  if (desc->weights_tiled > kWeightsMxfp4) { delete layer; return fail("layer_create: unknown weights_tiled value"); }
+  if (desc->weights_tiled == kWeightsMxfp4) {   // blocks of 128 rows x 64 bytes of E2M1 codes, one after another
+    rc = rc ? rc : encode_fp4_tiles(&layer->tm_w13, desc->w13_fp8, slabs * 2 * kInter * kHiddenBlocks);
+    rc = rc ? rc : encode_fp4_tiles(&layer->tm_w2, desc->w2_fp8, slabs * kHidden * kInterBlocks);
+  } else if (desc->weights_tiled) {   // tiles of 128 rows x 128 bytes, one after another
     rc = rc ? rc : encode_u8_2d(&layer->tm_w13, desc->w13_fp8, slabs * 2 * kInter * kHiddenBlocks, kBlock, 128);
     rc = rc ? rc : encode_u8_2d(&layer->tm_w2, desc->w2_fp8, slabs * kHidden * kInterBlocks, kBlock, 128);
   } else {
@@ -315,7 +345,8 @@ int netra_moe_layer_create(const netra_moe_layer_desc_t* desc, netra_moe_layer_t
 uint32_t netra_moe_layer_launch_count(const netra_moe_layer_t* layer, uint32_t tokens) {
   if (layer == nullptr) return 0;
   uint32_t n = tokens <= (uint32_t)kSortSmallMaxRows ? layer->launches - 2 : layer->launches;
-  if (layer->gather_rows_in_gemm && use_tokmajor(layer->device, (uint64_t)tokens * kTopK, kRouted) && layer->gemm_mode != 1) --n;   // no row gather
+  if (layer->gather_rows_in_gemm && layer->desc.weights_tiled != kWeightsMxfp4 &&
+      use_tokmajor(layer->device, (uint64_t)tokens * kTopK, kRouted) && layer->gemm_mode != 1) --n;   // no row gather
   return n;
 }
 
@@ -330,8 +361,12 @@ constexpr uint32_t kRouterK8MaxRows = 1024;   // up to here the router runs on t
 bool use_umma_router(const netra_moe_layer* layer, uint32_t tokens) {
   return tokens > kRouterK8MaxRows && layer->router_mode != 1;
 }
+// The token-major GEMMs exist for E4M3 weight tiles; a layer on MXFP4 weights runs the swap-AB kernels at every size.
+bool layer_tokmajor(const netra_moe_layer* layer, uint32_t pairs) {
+  return layer->gemm_mode != 1 && layer->desc.weights_tiled != kWeightsMxfp4 && use_tokmajor(layer->device, pairs, kRouted);
+}
 bool use_f16_partials(const netra_moe_layer* layer, uint32_t pairs) {
-  return layer->partial_f16 != 0 && layer->gemm_mode != 1 && use_tokmajor(layer->device, pairs, kRouted);
+  return layer->partial_f16 != 0 && layer_tokmajor(layer, pairs);
 }
 
 // One launch of the layer's fixed sequence (same idea as the reference's per-operation launch,
@@ -360,7 +395,8 @@ int launch_stage(netra_moe_layer* layer, uint32_t stage, const void* hidden, con
   const uint16_t* router_w = (const uint16_t*)layer->desc.router_weight_bf16;
   const uint32_t pairs = tokens * kTopK;
   const uint32_t nseg = (pairs + kSortSegment - 1) / kSortSegment;
-  const bool tokmajor = use_tokmajor(layer->device, pairs, kRouted) && layer->gemm_mode != 1;
+  const bool tokmajor = layer_tokmajor(layer, pairs);
+  const bool mxfp4 = layer->desc.weights_tiled == kWeightsMxfp4;
   switch (stage) {
     case 0:
       if (use_umma_router(layer, tokens)) {
@@ -416,6 +452,10 @@ int launch_stage(netra_moe_layer* layer, uint32_t stage, const void* hidden, con
         netra_moe_gate_up_tokmajor_sm100<<<layer->sm_count, kTmThreads, gate_up_tokmajor_smem_bytes(), stream>>>(
             layer->tm_w13, layer->tm_a128, a_scale, layer->desc.w13_scale_f32, offsets, h_fp8, h_scale, kRouted + 1,
             layer->desc.weights_tiled, status);
+      else if (mxfp4)
+        netra_moe_gate_up_mxfp4_sm100<<<layer->sm_count, kGemmThreads, gate_up_mxfp4_smem_bytes(), stream>>>(
+            layer->tm_w13, layer->tm_a32, layer->tm_a64, layer->tm_a128, a_scale, (const uint8_t*)layer->desc.w13_scale_f32, offsets,
+            h_fp8, h_scale, kRouted + 1, status);
       else
         netra_moe_gate_up_umma_sm100<<<layer->sm_count, kGemmThreads, gate_up_smem_bytes(), stream>>>(
             layer->tm_w13, layer->tm_a32, layer->tm_a64, layer->tm_a128, a_scale, layer->desc.w13_scale_f32, offsets, h_fp8,
@@ -430,6 +470,10 @@ int launch_stage(netra_moe_layer* layer, uint32_t stage, const void* hidden, con
         netra_moe_down_tokmajor_sm100<<<layer->sm_count, kTmThreads, down_tokmajor_smem_bytes(), stream>>>(
             layer->tm_w2, layer->tm_h128, h_scale, layer->desc.w2_scale_f32, offsets, down, kRouted + 1,
             layer->desc.weights_tiled, status + 1);
+      else if (mxfp4)
+        netra_moe_down_mxfp4_sm100<<<layer->sm_count, kGemmThreads, down_mxfp4_smem_bytes(), stream>>>(
+            layer->tm_w2, layer->tm_h32, layer->tm_h64, layer->tm_h128, h_scale, (const uint8_t*)layer->desc.w2_scale_f32, offsets, down,
+            kRouted + 1, status + 1);
       else
         netra_moe_down_umma_sm100<<<layer->sm_count, kGemmThreads, down_smem_bytes(), stream>>>(
             layer->tm_w2, layer->tm_h32, layer->tm_h64, layer->tm_h128, h_scale, layer->desc.w2_scale_f32, offsets, down,
@@ -528,6 +572,19 @@ int netra_moe_mxfp4_expand_launch(void* dst_fp8, float* dst_scale, uint32_t* ine
   return check_launch("mxfp4_expand launch");
 }
 
+int netra_moe_mxfp4_pack_launch(void* dst_codes, void* dst_scale_atoms, const void* packed, const void* scales_e8m0,
+                                uint64_t total_rows, uint32_t k, cudaStream_t stream) {
+  if (!dst_codes || !dst_scale_atoms || !packed || !scales_e8m0 || dst_codes == packed || dst_scale_atoms == scales_e8m0)
+    return fail("mxfp4_pack: null or aliased pointers");
+  if (total_rows == 0 || total_rows % 128 != 0 || k == 0 || k % 128 != 0) return fail("mxfp4_pack: rows and k must be positive multiples of 128");
+  if (total_rows / 128 > 65535) return fail("mxfp4_pack: at most 65,535 row tiles per call");
+  if ((((uintptr_t)dst_codes | (uintptr_t)packed) & 15) != 0 || (((uintptr_t)dst_scale_atoms | (uintptr_t)scales_e8m0) & 3) != 0)
+    return fail("mxfp4_pack: code pointers must be 16-byte aligned, scale pointers 4-byte aligned");
+  netra_moe_mxfp4_pack_sm100<<<dim3(k / 128, (unsigned)(total_rows / 128)), 128, 0, stream>>>(
+      (uint8_t*)dst_codes, (uint8_t*)dst_scale_atoms, (const uint8_t*)packed, (const uint8_t*)scales_e8m0, k);
+  return check_launch("mxfp4_pack launch");
+}
+
 // ------------------------------------------------------------------ expert block (expert parallelism)
 struct netra_moe_expert_block {
   netra_moe_expert_block_desc_t desc;
@@ -541,6 +598,7 @@ int netra_moe_expert_block_create(const netra_moe_expert_block_desc_t* desc, net
       !desc->h_fp8 || !desc->h_scale_f32 || !desc->down_f32 || !desc->offsets_i32 || !desc->status_u32)
     return fail("expert_block_create: null pointer");
   if (desc->num_groups == 0 || desc->num_groups > kRouted + 1 || desc->max_rows == 0) return fail("expert_block_create: bad group or row count");
+  if (desc->weights_tiled > 1) return fail("expert_block_create: weights_tiled must be 0 or 1");
   int device = 0, major = 0, sms = 0;
   cudaError_t e = cudaGetDevice(&device);
   if (e != cudaSuccess) return fail_cuda("cudaGetDevice", e);
@@ -634,10 +692,10 @@ int netra_ep_unpack_rows_launch(float* down, const float* back_slots, const int3
 }
 
 int netra_moe_kernel_launch_info(uint32_t which, uint32_t* block_threads, uint32_t* dynamic_smem_bytes) {
-  if (!block_threads || !dynamic_smem_bytes || which > 5) return fail("kernel_launch_info: bad argument");
-  *block_threads = which < 2 ? kGemmThreads : which == 5 ? kRtThreads : kTmThreads;
-  const int bytes[6] = {gate_up_smem_bytes(), down_smem_bytes(), gate_up_tokmajor_smem_bytes(), down_tokmajor_smem_bytes(),
-                        down_tokmajor_f16_smem_bytes(), router_umma_smem_bytes()};
+  if (!block_threads || !dynamic_smem_bytes || which > 7) return fail("kernel_launch_info: bad argument");
+  *block_threads = (which < 2 || which > 5) ? kGemmThreads : which == 5 ? kRtThreads : kTmThreads;
+  const int bytes[8] = {gate_up_smem_bytes(), down_smem_bytes(), gate_up_tokmajor_smem_bytes(), down_tokmajor_smem_bytes(),
+                        down_tokmajor_f16_smem_bytes(), router_umma_smem_bytes(), gate_up_mxfp4_smem_bytes(), down_mxfp4_smem_bytes()};
   *dynamic_smem_bytes = (uint32_t)bytes[which];
   return 0;
 }

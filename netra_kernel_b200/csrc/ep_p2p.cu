@@ -312,7 +312,7 @@ netra_ep_down_return_umma_sm100(const __grid_constant__ CUtensorMap tm_w2, const
                                 const float* h_scale, const float* w2_scale, const int32_t* offsets, float* const* row_ptr,
                                 uint32_t num_groups, uint32_t w_tiled, uint32_t* status, EpPeers peers, EpWindowLayout lay,
                                 EpTables* tab, uint32_t world, uint32_t rank) {
-  grouped_gemm_body<false>(&tm_w2, &tm_h32, &tm_h64, &tm_h128, h_scale, w2_scale, offsets, nullptr, nullptr, nullptr, row_ptr,
+  grouped_gemm_body<false>(&tm_w2, &tm_h32, &tm_h64, &tm_h128, h_scale, w2_scale, nullptr, offsets, nullptr, nullptr, nullptr, row_ptr,
                            num_groups, w_tiled, status);
   ep_signal_when_last(peers, lay, tab, &tab->done_ret, 2, world, rank);
 }
@@ -518,6 +518,7 @@ int netra_ep_layer_create(const netra_ep_layer_desc_t* desc, netra_ep_layer_t** 
   if (!desc->router_weight_bf16 || !desc->w13_fp8 || !desc->w13_scale_f32 || !desc->w2_fp8 || !desc->w2_scale_f32 || !desc->workspace ||
       !desc->windows)
     return fail("ep_layer_create: null pointer");
+  if (desc->weights_tiled > 1) return fail("ep_layer_create: weights_tiled must be 0 or 1 (the expert-parallel kernels take E4M3 weights)");
   if (desc->wait_timeout_ns == 0) return fail("ep_layer_create: wait_timeout_ns must be positive (every wait is bounded)");
   for (uint32_t g = 0; g < desc->world; ++g)
     if (!desc->windows[g] || ((uintptr_t)desc->windows[g] & 1023) != 0) return fail("ep_layer_create: every window must be a 1024-byte aligned pointer");

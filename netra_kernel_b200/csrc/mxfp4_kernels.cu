@@ -63,4 +63,25 @@ netra_moe_mxfp4_expand_sm100(uint8_t* __restrict__ dst, float* __restrict__ dst_
   if (bad) atomicAdd(inexact, bad);
 }
 
+// MXFP4 slabs -> the operand layout of the native kernels (netra_moe_gate_up_mxfp4_sm100, netra_moe_down_mxfp4_sm100):
+//   codes  one contiguous 8 KiB block per (128-row tile, K-block): row r of the block holds the 64 bytes
+//          [kb * 64, +64) of source row tile * 128 + r; blocks in (tile, K-block) order
+//   atoms  one 512-byte block per (tile, K-block) in the same order: the four scale bytes of row r and this
+//          K-block sit at byte 16 * (r % 32) + 4 * (r / 32) - the order in which a 32-row x 16-byte copy
+//          into TMEM puts row r's bytes into lane r % 32, column r / 32, the place the tensor core reads them
+// grid (k / 128, rows / 128), block 128: thread r moves row (blockIdx.y * 128 + r), K-block blockIdx.x.
+extern "C" __global__ void __launch_bounds__(128)
+netra_moe_mxfp4_pack_sm100(uint8_t* __restrict__ dst_codes, uint8_t* __restrict__ dst_atoms, const uint8_t* __restrict__ packed,
+                           const uint8_t* __restrict__ scales, uint32_t k) {
+  const uint32_t kb = blockIdx.x, r = threadIdx.x, kblocks = k / 128;
+  const size_t row = (size_t)blockIdx.y * 128 + r;
+  const size_t block = (size_t)blockIdx.y * kblocks + kb;
+  const uint4* src = reinterpret_cast<const uint4*>(packed + row * (k / 2) + kb * 64);
+  uint4* out = reinterpret_cast<uint4*>(dst_codes + (block * 128 + r) * 64);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) out[q] = src[q];
+  const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(scales + row * (k / 32) + kb * 4);
+  *reinterpret_cast<uint32_t*>(dst_atoms + block * 512 + 16 * (r & 31u) + 4 * (r >> 5)) = sc4;
+}
+
 }  // namespace netra

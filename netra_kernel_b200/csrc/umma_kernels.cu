@@ -101,6 +101,26 @@ __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_
       "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// kind::mxf8f6f4 with block scaling: every 32 K-elements of a row of A (B) are multiplied by one UE8M0 scale byte that
+// the tensor core reads from TMEM columns sfa (sfb); the byte used inside each 32-bit column is part of idesc.
+__device__ __forceinline__ void umma_mxf8f6f4(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
+                                              uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
+}
+// shared memory -> TMEM: 32 rows of 16 bytes land in lanes 0..31 of four consecutive columns and are repeated in the
+// other three lane quadrants (each quadrant of the tensor core reads its own copy of the scales)
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+// the calling warp's 32 lanes x 4 columns <- one 32-bit value
+__device__ __forceinline__ void tmem_fill4(uint32_t taddr, uint32_t v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %1, %1, %1};" ::"r"(taddr), "r"(v) : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -141,6 +161,17 @@ __device__ __forceinline__ uint32_t make_idesc(uint32_t n) {
   return (1u << 4) | ((n >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
 }
 
+// 512-byte scale atom: 32 rows of 16 bytes, unswizzled, 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t make_scale_desc(uint32_t addr) {
+  return (uint64_t)((addr & 0x3ffffu) >> 4) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
+}
+// kind::mxf8f6f4.block_scale, A = E2M1 (MXFP4 weight rows), B = E4M3 (token rows), UE8M0 scales, FP32 accumulators,
+// both operands K-major, M = 128; a_scale_byte selects the byte of the A-scale columns (the 32-element group of
+// the 128-element K-block this instruction covers), B always uses byte 0.
+__device__ __forceinline__ uint32_t make_idesc_mxfp4(uint32_t n, uint32_t a_scale_byte) {
+  return (5u << 7) | ((n >> 3) << 17) | (1u << 23) | ((uint32_t)(kTileRows >> 4) << 24) | (a_scale_byte << 29);
+}
+
 // ---------------------------------------------------------------------------- work items
 struct Item {
   int group;    // expert slab index
@@ -166,7 +197,9 @@ __device__ __forceinline__ Item decode_item(int item, const int* item_pre, const
 }
 
 // kGateUp: 2 weight tiles per stage (gate, up), K = 2048, FP8 epilogue.  else: 1 tile, K = 512, FP32 epilogue.
-template <bool kGateUp>
+// kFp4: the weight tiles are MXFP4 (E2M1 codes, 64 bytes per row and K-block in memory, expanded by the copy engine
+// to one byte per element in shared memory) and each tile brings a 512-byte atom of UE8M0 scales.
+template <bool kGateUp, bool kFp4 = false>
 struct Cfg {
   static constexpr int kATiles = kGateUp ? 2 : 1;
   // token rows per work item (UMMA N).  32 for both: 64-row items (the shared expert at decode sizes) ran a longer
@@ -183,32 +216,38 @@ struct Cfg {
   static constexpr int kSlabTiles = kSlabRows / kTileRows;                             // 8 | 16
   static constexpr int kKbPerStep = kGateUp ? 1 : 4;      // K-blocks the MMA warp issues per accumulator hand-off
   static constexpr int kAccCols = kKbPerStep * kATiles * kTokMax;                      // TMEM columns per hand-off: 64 | 128
-  static constexpr int kAccStages = 512 / kAccCols;                                    // 8 | 4
-  static constexpr int kStages = kGateUp ? 6 : 10;
+  static constexpr int kScaleCols = kFp4 ? 4 * kATiles + 4 : 0;                        // TMEM columns of the A and B scales
+  static constexpr int kAccStages = (512 - kScaleCols) / kAccCols;                     // 8 | 4 (MXFP4: 7 | 3)
+  static constexpr int kStages = kGateUp ? (kFp4 ? 5 : 6) : 10;
   static constexpr int kStageBytes = kATiles * kWTileBytes + kTokTileBytes;            // 36 KiB | 20 KiB
+  static constexpr int kWTxBytes = kFp4 ? kWTileBytes / 2 : kWTileBytes;               // bytes one weight-tile copy reports
+  static constexpr int kScaleAtomBytes = 512;                                          // 128 rows x 4 groups of 32
+  static constexpr int kScaleStageBytes = kFp4 ? kATiles * kScaleAtomBytes : 0;
   static constexpr int kTmemCols = 512;
   static constexpr int kXsBytes = kTokMax * kKBlocks * 4;                              // 4 KiB | 1 KiB
   static constexpr int kWsBytes = kKBlocks * 4;                                        // 64 B | 16 B per tile
   static constexpr int kItemList = 128;                                                // work items of this CTA decoded once
   static constexpr int kScaleSlotBytes = kXsBytes + 128;                               // xs, then ws tiles
-  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kScaleSlots * kScaleSlotBytes + 2 * 4 * kColsPerGroup * 4 +
-                                    2 * 264 * 4 + kItemList * 16 + 512;
+  static constexpr int kSmemBytes = 1024 + kStages * (kStageBytes + kScaleStageBytes) + kScaleSlots * kScaleSlotBytes +
+                                    2 * 4 * kColsPerGroup * 4 + 2 * 264 * 4 + kItemList * 16 + 512;
 };
 
-template <bool kGateUp>
+template <bool kGateUp, bool kFp4 = false>
 __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const CUtensorMap* tm_x32,
                                                   const CUtensorMap* tm_x64, const CUtensorMap* tm_x128,
                                                   const float* __restrict__ x_scale, const float* __restrict__ w_scale,
+                                                  const uint8_t* __restrict__ w_scale_atoms,
                                                   const int32_t* __restrict__ offsets, uint8_t* __restrict__ h_fp8,
                                                   float* __restrict__ h_scale, float* __restrict__ down,
                                                   float* const* __restrict__ row_ptr, uint32_t num_groups, uint32_t w_tiled,
                                                   uint32_t* status) {
-  using C = Cfg<kGateUp>;
+  using C = Cfg<kGateUp, kFp4>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* stage_base = smem;
   uint8_t* scale_base = stage_base + C::kStages * C::kStageBytes;                // 2 slots
-  uint32_t* red = reinterpret_cast<uint32_t*>(scale_base + C::kScaleSlots * C::kScaleSlotBytes);   // [2 groups][4 warps][64]
+  uint8_t* atom_base = scale_base + C::kScaleSlots * C::kScaleSlotBytes;         // [kStages][kATiles] scale atoms (MXFP4)
+  uint32_t* red = reinterpret_cast<uint32_t*>(atom_base + C::kStages * C::kScaleStageBytes);       // [2 groups][4 warps][64]
   int* offs = reinterpret_cast<int*>(red + 2 * 4 * C::kColsPerGroup);               // [264]
   int* item_pre = offs + 264;                                                    // [264]
   int4* item_list = reinterpret_cast<int4*>(item_pre + 264);                     // [kItemList]
@@ -266,6 +305,12 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_scale = tmem_base + (uint32_t)(C::kAccStages * C::kAccCols);   // A scales per tile, then the B scales
+  if constexpr (kFp4) {
+    // the token rows carry FP32 scales that the promotion step applies: inside the MMA they count as 2^0 (0x7f)
+    if (warp >= 2 && warp < 6) tmem_fill4(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(C::kAccStages * C::kAccCols + 4 * C::kATiles), 0x7f7f7f7fu);
+    tc_fence_before();
+  }
   const int total_items = item_pre[groups];
   // Work items all cost about the same, so the launch is balanced when every participating CTA gets the
   // same count: with R = ceil(items / grid) rounds only ceil(items / R) CTAs take part (e.g. 130 of 148 for
@@ -300,7 +345,7 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
         const Item w = get_item((int)n_item, item);
         const int box = (C::kTokMax == 32 || w.m_valid <= 32) ? 32 : 64;
         const CUtensorMap* tm_x = box == 32 ? tm_x32 : tm_x64;
-        const uint32_t bytes = C::kATiles * kWTileBytes + box * kBlock;
+        const uint32_t bytes = C::kATiles * C::kWTxBytes + box * kBlock + C::kScaleStageBytes;
         // scales of this item: token-row scales [128][KB] and the tile's weight scales
         {
           const int slot = n_item % C::kScaleSlots;
@@ -309,11 +354,13 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
           }
           const uint32_t sbar = smem_u32(&sfull_bar[slot]);
           const uint32_t sdst = smem_u32(scale_base + slot * C::kScaleSlotBytes);
-          mbar_expect_tx(sbar, C::kXsBytes + C::kATiles * C::kSubTiles * C::kWsBytes);
+          mbar_expect_tx(sbar, C::kXsBytes + (kFp4 ? 0 : C::kATiles * C::kSubTiles * C::kWsBytes));
           bulk_load(sdst, x_scale + (size_t)w.row0 * C::kKBlocks, C::kXsBytes, sbar);
-          const float* wsrc = w_scale + ((size_t)w.group * C::kSlabTiles + w.ntile) * C::kKBlocks;
-          bulk_load(sdst + C::kXsBytes, wsrc, C::kSubTiles * C::kWsBytes, sbar);   // the item's tiles are consecutive
-          if (kGateUp) bulk_load(sdst + C::kXsBytes + C::kWsBytes, wsrc + (kInter / kBlock) * C::kKBlocks, C::kWsBytes, sbar);
+          if constexpr (!kFp4) {
+            const float* wsrc = w_scale + ((size_t)w.group * C::kSlabTiles + w.ntile) * C::kKBlocks;
+            bulk_load(sdst + C::kXsBytes, wsrc, C::kSubTiles * C::kWsBytes, sbar);   // the item's tiles are consecutive
+            if (kGateUp) bulk_load(sdst + C::kXsBytes + C::kWsBytes, wsrc + (kInter / kBlock) * C::kKBlocks, C::kWsBytes, sbar);
+          }
         }
         for (int sub = 0; ok && sub < C::kSubTiles; ++sub)
         for (int kb = 0; kb < C::kKBlocks; ++kb, ++it) {
@@ -325,7 +372,7 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
           const uint32_t dst = smem_u32(stage_base + s * C::kStageBytes);
           mbar_expect_tx(bar, bytes);
           int wx, wy0, wy1;
-          if (w_tiled) {   // one contiguous 16 KiB block per (slab tile, K-block)
+          if (kFp4 || w_tiled) {   // one contiguous block per (slab tile, K-block): 16 KiB of E4M3 or 8 KiB of E2M1 codes
             wx = 0;
             wy0 = ((w.group * C::kSlabTiles + w.ntile + sub) * C::kKBlocks + kb) * kTileRows;
             wy1 = wy0 + (kInter / kTileRows) * C::kKBlocks * kTileRows;
@@ -337,6 +384,11 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
           tma_load_2d(dst, tm_w, bar, wx, wy0, pol_w);
           if (kGateUp) tma_load_2d(dst + kWTileBytes, tm_w, bar, wx, wy1, pol_w);
           tma_load_2d(dst + C::kATiles * kWTileBytes, tm_x, bar, kb * kBlock, w.row0, pol_x);
+          if constexpr (kFp4) {   // the tiles' scale atoms: 512 bytes per (slab tile, K-block), in tile order
+            const uint32_t adst = smem_u32(atom_base + s * C::kScaleStageBytes);
+            bulk_load(adst, w_scale_atoms + (size_t)wy0 * 4, C::kScaleAtomBytes, bar);
+            if (kGateUp) bulk_load(adst + C::kScaleAtomBytes, w_scale_atoms + (size_t)wy1 * 4, C::kScaleAtomBytes, bar);
+          }
         }
       }
     }
@@ -366,11 +418,28 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
             const uint32_t d0 = tmem_base + (uint32_t)(a * C::kAccCols + q * C::kATiles * C::kTokMax);
             // the two tiles accumulate into different TMEM columns: alternate them so that consecutive
             // MMAs never depend on each other
+            if constexpr (kFp4) {
+              // scale atoms -> TMEM; the tensor-core pipe runs copies and MMAs of one thread in issue order, so the
+              // MMAs of the previous K-block have read these columns before they are overwritten
+#pragma unroll
+              for (int tile = 0; tile < C::kATiles; ++tile)
+                tmem_cp_32x128b_warpx4(tmem_scale + (uint32_t)(4 * tile),
+                                       make_scale_desc(smem_u32(atom_base + s * C::kScaleStageBytes + tile * C::kScaleAtomBytes)));
+#pragma unroll
+              for (int k = 0; k < kBlock / 32; ++k) {
+#pragma unroll
+                for (int tile = 0; tile < C::kATiles; ++tile)
+                  umma_mxf8f6f4(d0 + (uint32_t)(tile * C::kTokMax), make_smem_desc(sa + tile * kWTileBytes) + 2 * k, bdesc + 2 * k,
+                                make_idesc_mxfp4(n_mma, (uint32_t)k), (tmem_scale + (uint32_t)(4 * tile)) | ((uint32_t)k << 30),
+                                tmem_scale + (uint32_t)(4 * C::kATiles), k > 0);
+              }
+            } else {
 #pragma unroll
             for (int k = 0; k < kBlock / 32; ++k) {
 #pragma unroll
               for (int tile = 0; tile < C::kATiles; ++tile)
                 umma_f8(d0 + (uint32_t)(tile * C::kTokMax), make_smem_desc(sa + tile * kWTileBytes) + 2 * k, bdesc + 2 * k, idesc, k > 0);
+            }
             }
             umma_commit(smem_u32(&empty_bar[s]));
           }
@@ -432,9 +501,9 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[a]));   // the partials now live in registers
         }
-        float ws[C::kATiles];
+        float ws[C::kATiles];   // MXFP4: the weight scales were applied inside the MMA
 #pragma unroll
-        for (int tile = 0; tile < C::kATiles; ++tile) ws[tile] = ws_tile[(sub + tile) * C::kKBlocks + kb];
+        for (int tile = 0; tile < C::kATiles; ++tile) ws[tile] = kFp4 ? 1.0f : ws_tile[(sub + tile) * C::kKBlocks + kb];
 #pragma unroll
         for (int sl = 0; sl < C::kSlices; ++sl)
           if (sl < nsl) {
@@ -529,7 +598,7 @@ netra_moe_gate_up_umma_sm100(const __grid_constant__ CUtensorMap tm_w13, const _
                              const __grid_constant__ CUtensorMap tm_a64, const __grid_constant__ CUtensorMap tm_a128,
                              const float* a_scale, const float* w13_scale, const int32_t* offsets, uint8_t* h_fp8,
                              float* h_scale, uint32_t num_groups, uint32_t w_tiled, uint32_t* status) {
-  grouped_gemm_body<true>(&tm_w13, &tm_a32, &tm_a64, &tm_a128, a_scale, w13_scale, offsets, h_fp8, h_scale, nullptr, nullptr,
+  grouped_gemm_body<true>(&tm_w13, &tm_a32, &tm_a64, &tm_a128, a_scale, w13_scale, nullptr, offsets, h_fp8, h_scale, nullptr, nullptr,
                           num_groups, w_tiled, status);
 }
 
@@ -538,8 +607,32 @@ netra_moe_down_umma_sm100(const __grid_constant__ CUtensorMap tm_w2, const __gri
                           const __grid_constant__ CUtensorMap tm_h64, const __grid_constant__ CUtensorMap tm_h128,
                           const float* h_scale, const float* w2_scale, const int32_t* offsets, float* down,
                           uint32_t num_groups, uint32_t w_tiled, uint32_t* status) {
-  grouped_gemm_body<false>(&tm_w2, &tm_h32, &tm_h64, &tm_h128, h_scale, w2_scale, offsets, nullptr, nullptr, down, nullptr,
+  grouped_gemm_body<false>(&tm_w2, &tm_h32, &tm_h64, &tm_h128, h_scale, w2_scale, nullptr, offsets, nullptr, nullptr, down, nullptr,
                            num_groups, w_tiled, status);
+}
+
+// The same two projections on MXFP4 expert weights (E2M1 codes with one UE8M0 scale per 32 K-elements; semantics of
+// kernels/gfx1151/mxfp4/prefill/mxfp4_prefill_gate_wmma_gfx1151.s:3-8 and mxfp4_prefill_down_wmma_gfx1151.s:3-5, call
+// sequence of runtime/gfx1151/mxfp4/decode/runtime.h:10-47) through tcgen05.mma.kind::mxf8f6f4.block_scale: the
+// weight tiles stay 4-bit in memory (tm_w*: tiles of 128 rows x 64 bytes written by netra_moe_mxfp4_pack_sm100) and
+// their scales reach the tensor core through TMEM; the token rows are E4M3 with their FP32 per-128 scales applied
+// in the promotion step, as in the FP8 kernels above.
+extern "C" __global__ void __launch_bounds__(kGemmThreads, 1)
+netra_moe_gate_up_mxfp4_sm100(const __grid_constant__ CUtensorMap tm_w13, const __grid_constant__ CUtensorMap tm_a32,
+                              const __grid_constant__ CUtensorMap tm_a64, const __grid_constant__ CUtensorMap tm_a128,
+                              const float* a_scale, const uint8_t* w13_scale_atoms, const int32_t* offsets, uint8_t* h_fp8,
+                              float* h_scale, uint32_t num_groups, uint32_t* status) {
+  grouped_gemm_body<true, true>(&tm_w13, &tm_a32, &tm_a64, &tm_a128, a_scale, nullptr, w13_scale_atoms, offsets, h_fp8, h_scale,
+                                nullptr, nullptr, num_groups, 1u, status);
+}
+
+extern "C" __global__ void __launch_bounds__(kGemmThreads, 1)
+netra_moe_down_mxfp4_sm100(const __grid_constant__ CUtensorMap tm_w2, const __grid_constant__ CUtensorMap tm_h32,
+                           const __grid_constant__ CUtensorMap tm_h64, const __grid_constant__ CUtensorMap tm_h128,
+                           const float* h_scale, const uint8_t* w2_scale_atoms, const int32_t* offsets, float* down,
+                           uint32_t num_groups, uint32_t* status) {
+  grouped_gemm_body<false, true>(&tm_w2, &tm_h32, &tm_h64, &tm_h128, h_scale, nullptr, w2_scale_atoms, offsets, nullptr, nullptr, down,
+                                 nullptr, num_groups, 1u, status);
 }
 
 // Repack row-major slabs [groups * slab_rows, k_bytes] into tiles: destination row
@@ -570,5 +663,7 @@ netra_moe_widen_scales_bf16_sm100(float* __restrict__ dst, const uint16_t* __res
 
 int gate_up_smem_bytes() { return Cfg<true>::kSmemBytes; }
 int down_smem_bytes() { return Cfg<false>::kSmemBytes; }
+int gate_up_mxfp4_smem_bytes() { return Cfg<true, true>::kSmemBytes; }
+int down_mxfp4_smem_bytes() { return Cfg<false, true>::kSmemBytes; }
 
 }  // namespace netra

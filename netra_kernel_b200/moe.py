@@ -44,28 +44,46 @@ class RoutedMoELayer:
     def __init__(self, router_w: torch.Tensor, w13: torch.Tensor, w13_scale: torch.Tensor,
                  w2: torch.Tensor, w2_scale: torch.Tensor, max_tokens: int,
                  router_bias: Optional[torch.Tensor] = None, tiled: bool = True, routing_only: bool = False,
-                 pretiled: bool = False, workspace: Optional[torch.Tensor] = None):
+                 pretiled: bool = False, workspace: Optional[torch.Tensor] = None, mxfp4: bool = False):
         """``w13`` / ``w2`` are the checkpoint's row-major slabs.  With ``tiled`` (default) they are
         rewritten once into the tile order the grouped GEMMs stream best and only that copy is kept
         by the layer; the caller may drop the row-major tensors.  ``pretiled`` says the tensors are
         already in tile order (another layer's ``tiled_weights()``), so nothing is copied.
         ``workspace`` lets several layers that never run concurrently (the layers of a stack on one
         stream) share one scratch buffer: a uint8 CUDA tensor of at least ``workspace_layout(max_tokens).total_bytes
-        + 1024`` bytes."""
+        + 1024`` bytes.
+        ``mxfp4``: the slabs are MXFP4 instead - ``w13`` / ``w2`` the packed E2M1 codes (u8 ``[S, 1024, 1024]`` /
+        ``[S, 2048, 256]``, low nibble = even k) and ``w13_scale`` / ``w2_scale`` the E8M0 scales (u8 ``[S, 1024, 64]`` /
+        ``[S, 2048, 16]``).  They are packed once (``pack_mxfp4``) and stay four-bit in memory: the grouped GEMMs
+        multiply them on the tensor cores' block-scaled path.  With ``pretiled`` the four tensors are already the
+        packed code blocks and scale atoms."""
         _require_cuda(router_w, w13, w13_scale, w2, w2_scale, router_bias)
         if tuple(router_w.shape) != (N_ROUTED, HIDDEN) or router_w.dtype != torch.bfloat16:
             raise ValueError("router weight must be bf16 [256, 2048]")
         slabs = w13.shape[0]
         if not routing_only and slabs != N_ROUTED + 1:
             raise ValueError("a full layer needs 257 expert slabs (slab 256 = shared expert)")
-        if tuple(w13.shape) != (slabs, 2 * INTER, HIDDEN) or tuple(w2.shape) != (slabs, HIDDEN, INTER):
-            raise ValueError("expert slabs must be [S, 1024, 2048] and [S, 2048, 512]")
-        if tuple(w13_scale.shape) != (slabs, 8, 16) or tuple(w2_scale.shape) != (slabs, 16, 4):
-            raise ValueError("block scales must be f32 [S, 8, 16] and [S, 16, 4]")
+        self.mxfp4 = bool(mxfp4)
+        if self.mxfp4:
+            if any(t.dtype != torch.uint8 for t in (w13, w13_scale, w2, w2_scale)):
+                raise ValueError("MXFP4 slabs and scales must be uint8")
+            if tuple(w13.shape) != (slabs, 2 * INTER, HIDDEN // 2) or tuple(w2.shape) != (slabs, HIDDEN, INTER // 2):
+                raise ValueError("MXFP4 expert slabs must be [S, 1024, 1024] and [S, 2048, 256] bytes")
+            if tuple(w13_scale.shape) != (slabs, 2 * INTER, HIDDEN // 32) or tuple(w2_scale.shape) != (slabs, HIDDEN, INTER // 32):
+                raise ValueError("MXFP4 scales must be u8 [S, 1024, 64] and [S, 2048, 16]")
+        else:
+            if tuple(w13.shape) != (slabs, 2 * INTER, HIDDEN) or tuple(w2.shape) != (slabs, HIDDEN, INTER):
+                raise ValueError("expert slabs must be [S, 1024, 2048] and [S, 2048, 512]")
+            if tuple(w13_scale.shape) != (slabs, 8, 16) or tuple(w2_scale.shape) != (slabs, 16, 4):
+                raise ValueError("block scales must be f32 [S, 8, 16] and [S, 16, 4]")
         self.routing_only = routing_only
         self.lib = abi.load()
         self.tiled = bool(tiled)
-        if pretiled:
+        if self.mxfp4:
+            self.tiled = True
+            if not pretiled:
+                (w13, w13_scale), (w2, w2_scale) = pack_mxfp4(w13, w13_scale), pack_mxfp4(w2, w2_scale)
+        elif pretiled:
             self.tiled = True
         elif self.tiled:
             w13, w2 = self._repack(w13), self._repack(w2)
@@ -90,7 +108,7 @@ class RoutedMoELayer:
         desc.w13_fp8, desc.w13_scale_f32 = w13.data_ptr(), w13_scale.data_ptr()
         desc.w2_fp8, desc.w2_scale_f32 = w2.data_ptr(), w2_scale.data_ptr()
         desc.workspace, desc.workspace_bytes = self.workspace.data_ptr(), self.layout.total_bytes
-        desc.weights_tiled, desc.num_expert_slabs = int(self.tiled), int(w13.shape[0])
+        desc.weights_tiled, desc.num_expert_slabs = (2 if self.mxfp4 else int(self.tiled)), int(w13.shape[0])
         handle = ctypes.c_void_p()
         abi.check(self.lib.netra_moe_layer_create(ctypes.byref(desc), ctypes.byref(handle)), "layer_create")
         self.handle = handle
@@ -249,6 +267,29 @@ class RoutedMoELayer:
             self.close()
         except Exception:
             pass
+
+
+def pack_mxfp4(packed: torch.Tensor, scales: torch.Tensor):
+    """MXFP4 slabs (packed E2M1 ``[G, N, K/2]`` u8, E8M0 scales ``[G, N, K/32]`` u8, on the GPU) -> the operand layout of
+    the native MXFP4 kernels, same shapes and sizes: code blocks (8 KiB per 128-row tile and K-block) and scale atoms
+    (512 bytes per tile and K-block).  ``netra_moe_mxfp4_pack_launch``."""
+    _require_cuda(packed, scales)
+    g, n, half_k = packed.shape
+    k = half_k * 2
+    if packed.dtype != torch.uint8 or scales.dtype != torch.uint8 or scales.shape != (g, n, k // 32):
+        raise ValueError("packed must be u8 [G, N, K/2] and scales u8 [G, N, K/32]")
+    codes, atoms = torch.empty_like(packed), torch.empty_like(scales)
+    lib = abi.load()
+    tiles_per_call = 65535 // (n // 128) * (n // 128)        # whole slabs, at most 65,535 row tiles per launch
+    rows_per_call = tiles_per_call * 128
+    total = g * n
+    src_c, src_s = packed.view(total, half_k), scales.view(total, k // 32)
+    dst_c, dst_s = codes.view(total, half_k), atoms.view(total, k // 32)
+    for r0 in range(0, total, rows_per_call):
+        r1 = min(total, r0 + rows_per_call)
+        abi.check(lib.netra_moe_mxfp4_pack_launch(dst_c[r0:r1].data_ptr(), dst_s[r0:r1].data_ptr(), src_c[r0:r1].data_ptr(),
+                                                  src_s[r0:r1].data_ptr(), r1 - r0, k, _stream()), "mxfp4_pack_launch")
+    return codes, atoms
 
 
 def expand_mxfp4(packed: torch.Tensor, scales: torch.Tensor):

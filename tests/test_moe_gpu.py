@@ -321,6 +321,58 @@ def test_mxfp4_expansion_kernel_and_layer(expert_weights):
     check_against(ref, out, inter, tokens)
 
 
+def test_native_mxfp4_layer_streams_four_bit_weights(expert_weights):
+    """The native MXFP4 tactic: the packed E2M1 slabs and E8M0 scales are only re-ordered at load (checked byte for byte
+    against the layout rule) and multiplied on the block-scaled tensor-core path.  The layer must match the checker run on
+    the exactly expanded weights within the output gates, route identically, and agree with the expansion path on nearly
+    every intermediate FP8 code (both sum the same exact products; only the FP32 summation order differs)."""
+    from netra_kernel_b200.moe import RoutedMoELayer, expand_mxfp4, pack_mxfp4
+    g = torch.Generator().manual_seed(22)
+    slabs = 257
+    base13 = [0.02 * torch.randn(1024, 2048, generator=g) for _ in range(3)]
+    base2 = [0.02 * torch.randn(2048, 512, generator=g) for _ in range(3)]
+    base13[1][:, 512:1024] *= 2.0 ** -9            # scale bytes that differ widely inside one tile
+    q13 = [synth.quantize_mxfp4(w) for w in base13]
+    q2 = [synth.quantize_mxfp4(w) for w in base2]
+    p13 = torch.stack([q13[e % 3][0] for e in range(slabs)]).cuda()
+    s13 = torch.stack([q13[e % 3][1] for e in range(slabs)]).cuda()
+    p2 = torch.stack([q2[e % 3][0] for e in range(slabs)]).cuda()
+    s2 = torch.stack([q2[e % 3][1] for e in range(slabs)]).cuda()
+    # the load-time re-ordering, against its definition
+    codes, atoms = pack_mxfp4(p13[:2], s13[:2])
+    torch.cuda.synchronize()
+    src_c, src_s = p13[:2].cpu().numpy().reshape(16, 128, 16, 64), s13[:2].cpu().numpy().reshape(16, 128, 16, 4)
+    want_c = src_c.transpose(0, 2, 1, 3)                                           # [tile, kb, r, 64]
+    assert np.array_equal(codes.cpu().numpy().reshape(16, 16, 128, 64), want_c)
+    want_s = src_s.transpose(0, 2, 1, 3).reshape(16, 16, 4, 32, 4).transpose(0, 1, 3, 2, 4)   # [tile, kb, r % 32, r / 32, 4]
+    assert np.array_equal(atoms.cpu().numpy().reshape(16, 16, 32, 4, 4), want_s)
+    w13, w13_s, bad13 = expand_mxfp4(p13, s13)
+    w2, w2_s, bad2 = expand_mxfp4(p2, s2)
+    assert bad13 == 0 and bad2 == 0
+    np_w = (w13.view(torch.uint8).cpu().numpy(), w13_s.cpu().numpy(), w2.view(torch.uint8).cpu().numpy(), w2_s.cpu().numpy())
+    for tokens, alpha in ((64, None), (300, None), (1500, 3.0)):
+        hidden, router_w, bias = synth.make_activations(tokens, alpha, seed=9)
+        b = None if bias is None else bias.cuda()
+        native = RoutedMoELayer(router_w.cuda(), p13, s13, p2, s2, tokens, b, mxfp4=True)
+        out, inter = run_layer(native, hidden)
+        expanded = RoutedMoELayer(router_w.cuda(), w13, w13_s, w2, w2_s, tokens, b)
+        expanded.set_gemm_mode(1)
+        out_e, inter_e = run_layer(expanded, hidden)
+        rows = tokens * 9
+        assert torch.equal(inter["perm"], inter_e["perm"]) and torch.equal(inter["topk_ids"], inter_e["topk_ids"])
+        differ = (inter["h_fp8"][:rows] != inter_e["h_fp8"][:rows]).float().mean().item()
+        assert differ < 2e-3, f"native and expanded MXFP4 paths differ in {differ:.2%} of the intermediate codes"
+        d, de = inter["down"][:rows].double(), inter_e["down"][:rows].double()
+        assert ((d - de).norm() / de.norm()).item() < 2e-3
+        if tokens <= 300:
+            ref = R.moe_layer(helpers.bits(hidden), helpers.bits(router_w), *np_w)
+            check_against(ref, out, inter, tokens)
+        else:
+            m = R.parity_metrics(helpers.bits(out), helpers.bits(out_e))
+            assert m["max_abs"] <= helpers.MAX_ABS and m["rel_l2"] <= helpers.REL_L2, m
+        native.close(); expanded.close()
+
+
 def test_external_topk_entry_and_custom_ops(gpu_weights):
     """A caller that keeps its own top-k: feeding the layer's own ids and weights back through apply() (and through
     the registered torch ops) must reproduce the fused call bit for bit; a different top-k changes the result."""
