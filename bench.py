@@ -41,6 +41,8 @@ FALLBACK_HBM_GBS = 6650.0
 # the figure is reported only while that source is unchanged.
 GATE_UP_DRAM_TRAFFIC = {"bytes": 550_046_976, "source": "netra_kernel_b200/csrc/umma_kernels.cu",
                         "sha256": "bf5fdde7b3edb0dfc2d7c6eff6092472bd7887889d826484626575ba6d990fa0"}
+# the same two figures for netra_moe_gate_up_mxfp4_sm100 (MXFP4 weights, T=256); None until captured
+MXFP4_GATE_UP_DRAM_TRAFFIC = {"bytes": None, "source": "netra_kernel_b200/csrc/umma_kernels.cu", "sha256": ""}
 STACK_LAYERS = 40
 STACK_TOKENS = 16384
 NVLINK_GBS = 770.0            # measured peer copy per direction per GPU on this pool
@@ -212,15 +214,23 @@ def headline_config(tokens: int) -> dict:
             "shared_experts": 1, "hidden": 2048, "intermediate": 512, "expert_weights": "fp8_e4m3_block128"}
 
 
-def gate_up_traffic_bytes():
-    """The ncu DRAM figure of one decode gate_up launch, or None once the kernel source is no longer the captured one."""
+def _traffic_if_current(record):
     import hashlib
-    path = ROOT / GATE_UP_DRAM_TRAFFIC["source"]
+    path = ROOT / record["source"]
     try:
-        same = hashlib.sha256(path.read_bytes()).hexdigest() == GATE_UP_DRAM_TRAFFIC["sha256"]
+        same = hashlib.sha256(path.read_bytes()).hexdigest() == record["sha256"]
     except OSError:
         same = False
-    return GATE_UP_DRAM_TRAFFIC["bytes"] if same else None
+    return record["bytes"] if same else None
+
+
+def gate_up_traffic_bytes():
+    """The ncu DRAM figure of one decode gate_up launch, or None once the kernel source is no longer the captured one."""
+    return _traffic_if_current(GATE_UP_DRAM_TRAFFIC)
+
+
+def mxfp4_gate_up_traffic_bytes():
+    return _traffic_if_current(MXFP4_GATE_UP_DRAM_TRAFFIC)
 
 
 def time_e2e_pipelined(compute, hidden, out, hidden_cpu, steps, warmup, stream):
@@ -531,6 +541,55 @@ def prefill_object(name, layer, hidden_cpu, steps, warmup, dev, stream, sync, ex
     return obj
 
 
+def mxfp4_decode_object(layer, hidden_cpu, steps, warmup, dev, stream, sync, fp8_ms_per_step) -> dict:
+    """Decode (T=256) on MXFP4 expert weights through the native block-scaled kernels: the weight stream is the E2M1 codes
+    and E8M0 scale bytes, 0.53 of the FP8 layer's bytes; HBM roofline of the gate_up kernel and of the whole call."""
+    import torch
+    from netra_kernel_b200 import synth
+    tokens = hidden_cpu.shape[0]
+    hidden = hidden_cpu.to(dev)
+    out = torch.empty_like(hidden)
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            layer(hidden, out=out)
+        stream.synchronize()
+        layer.check_status()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            layer(hidden, out=out)
+        ms, spread = time_replays(graph.replay, steps, warmup, stream, sync, spread=True)
+        stage_ms = time_stages(layer, hidden, out, steps, warmup, stream, sync)
+        e2e_ms, serial_ms, host_api, _ = time_e2e(graph.replay, hidden, out, hidden_cpu, steps, warmup, stream, sync)
+        stream.synchronize()
+    layer.check_status()
+    inter = layer.intermediates(tokens)
+    hit = int((inter["counts"] > 0).sum().item())
+    peak, peak_kind = measured_hbm_peak()
+    gate_up_bytes = (hit + 1) * (1024 * 2048 // 2 + 1024 * 2048 // 32)
+    down_bytes = (hit + 1) * (2048 * 512 // 2 + 2048 * 512 // 32)
+    layer_bytes = synth.workload_bytes_decode(tokens, hit, mxfp4=True)
+    gu_s, dn_s = stage_ms[6] / 1e3, stage_ms[7] / 1e3
+    return {
+        "workload": "mxfp4_decode_t256", "tokens": tokens, "experts_hit": hit,
+        "expert_weights": "mxfp4 (E2M1 codes + one E8M0 scale per 32 along K), kept four-bit in memory: "
+                          "tcgen05.mma.kind::mxf8f6f4.block_scale with the scales in TMEM",
+        "ms_per_step": ms, "tokens_per_s": tokens / (ms / 1e3), "steps": steps, "warmup": warmup, "step_ms_spread": spread,
+        "speedup_over_fp8_weights": fp8_ms_per_step / ms,
+        "launch": "CUDA graph replay of the layer's %d kernels" % layer.launches_per_call(tokens),
+        "api": "netra_moe_layer_launch (fused-layer ABI, weights_tiled = 2), captured CUDA graph",
+        "l2": "inputs larger than L2: every step streams %.1f MB of expert weights (L2 is 126 MB)" % (layer_bytes / 1e6),
+        "roofline": {"bound": "hbm", "kernel": "netra_moe_gate_up_mxfp4_sm100", "achieved": gate_up_bytes / gu_s / 1e9, "peak": peak,
+                     "unit": "GB/s", "frac": gate_up_bytes / gu_s / 1e9 / peak, "peak_source": peak_kind,
+                     "algorithmic_bytes": gate_up_bytes, "avg_launch_ms": stage_ms[6], "traffic": mxfp4_gate_up_traffic_bytes()},
+        "down_kernel": {"kernel": "netra_moe_down_mxfp4_sm100", "achieved": down_bytes / dn_s / 1e9, "unit": "GB/s",
+                        "frac": down_bytes / dn_s / 1e9 / peak, "algorithmic_bytes": down_bytes},
+        "layer_hbm": {"algorithmic_bytes": layer_bytes, "fp8_layer_bytes": synth.workload_bytes_decode(tokens, hit),
+                      "achieved": layer_bytes / (ms / 1e3) / 1e9, "unit": "GB/s", "frac": layer_bytes / (ms / 1e3) / 1e9 / peak},
+        "kernels_ms": {n: round(v, 5) for n, v in zip(layer.STAGES, stage_ms)},
+        "e2e": e2e_object(tokens, tokens, e2e_ms, serial_ms, host_api),
+    }
+
+
 def make_stack_single(dev, layers, tokens, stream):
     """N=1 form of the 40-layer stack: one fused layer object per layer (own weights, generated on the device), all of
     them sharing one workspace since they run one after the other."""
@@ -645,11 +704,16 @@ def run_ours(args) -> None:
         mxfp4_inexact = bad13 + bad2
         del p13, s13, p2, s2
         weights = tuple(t.cpu() for t in (w13, w13_s, w2, w2_s))      # the CPU baseline runs on the same expanded operands
+    elif args.weights == "mxfp4-native":
+        if not args.profile_only:
+            raise SystemExit("--weights mxfp4-native is a --profile-only workload; the timed figures are the mxfp4_decode_t256 object of the default run")
+        weights = None
+        w13, w13_s, w2, w2_s = synth.make_expert_weights_device(0, dev, mxfp4=True)
     else:
         weights = synth.make_expert_weights(0)
         w13, w13_s, w2, w2_s = (t.to(dev) for t in weights)
     layer = RoutedMoELayer(router_w.to(dev), w13, w13_s, w2, w2_s, tokens, None if bias is None else bias.to(dev),
-                           tiled=not args.row_major_weights)
+                           tiled=not args.row_major_weights, mxfp4=args.weights == "mxfp4-native")
     del w13, w2
     if args.partials == "f16":
         layer.set_partial_format(1)
@@ -742,7 +806,6 @@ def run_ours(args) -> None:
             p13, s13, p2, s2 = synth.make_expert_weights_device(0, dev, mxfp4=True)
             m13, m13_s, bad13 = expand_mxfp4(p13, s13)
             m2, m2_s, bad2 = expand_mxfp4(p2, s2)
-            del p13, s13, p2, s2
             mx = RoutedMoELayer(layer._keep[0], m13, m13_s, m2, m2_s, 8192, bias8.to(dev))
             del m13, m2
             mx.set_partial_format(1)
@@ -753,6 +816,34 @@ def run_ours(args) -> None:
                                                    engine=engine8(mx) if args.api == "engine" else None)
             mx.close()
             del mx
+            torch.cuda.empty_cache()
+
+            # the same MXFP4 slabs kept four-bit in memory: the native block-scaled kernels at decode size, and (swap-AB
+            # form, the only one they have) at the prefill size for the record
+            nat = RoutedMoELayer(layer._keep[0], p13, s13, p2, s2, 8192, bias8.to(dev), mxfp4=True)
+            del p13, s13, p2, s2
+            hd_cpu, _, _ = synth.make_activations(256, None, seed=0)
+            nat_decode = RoutedMoELayer(layer._keep[0], *nat._keep[1:5], 256, None, mxfp4=True, pretiled=True)
+            extras["mxfp4_decode_t256"] = mxfp4_decode_object(nat_decode, hd_cpu, steps, warmup, dev, stream, sync, ms_per_step)
+            nat_decode.close()
+            with torch.cuda.stream(stream):
+                hd, od = h8.to(dev), torch.empty(8192, 2048, dtype=torch.bfloat16, device=dev)
+                for _ in range(2):
+                    nat(hd, out=od)
+                stream.synchronize()
+                nat.check_status()
+                gn = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gn, stream=stream):
+                    nat(hd, out=od)
+                ms_nat, _ = time_replays(gn.replay, cap, warmup, stream, sync)
+                st_nat = time_stages(nat, hd, od, cap, warmup, stream, sync)
+            extras["mxfp4_t8192"]["native_four_bit_weights"] = {
+                "ms_per_step": ms_nat, "tokens_per_s": 8192 / (ms_nat / 1e3),
+                "gemm_form": "swap-AB block-scaled kernels (netra_moe_gate_up_mxfp4_sm100, netra_moe_down_mxfp4_sm100): the form "
+                             "built for weight-streaming-bound calls; at this size the expanded tiles on the token-major kernels are faster",
+                "kernels_ms": {n: round(v, 5) for n, v in zip(nat.STAGES, st_nat)}}
+            nat.close()
+            del nat, nat_decode, gn, hd, od
             torch.cuda.empty_cache()
 
             # config 4 on one GPU: the 40-layer stack, 16,384 tokens per step, all 256 experts local
@@ -1089,8 +1180,9 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=256)
     ap.add_argument("--zipf-alpha", type=float, default=0.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--weights", default="fp8", choices=["fp8", "mxfp4"],
-                    help="expert weights: the FP8 block-scaled slabs (default) or the same slabs quantised to MXFP4 and expanded at load")
+    ap.add_argument("--weights", default="fp8", choices=["fp8", "mxfp4", "mxfp4-native"],
+                    help="expert weights: the FP8 block-scaled slabs (default), the same slabs quantised to MXFP4 and expanded at load, "
+                         "or (with --profile-only) MXFP4 kept four-bit in memory for the native block-scaled kernels")
     ap.add_argument("--row-major-weights", action="store_true",
                     help="stream the checkpoint's row-major slabs instead of the repacked tile order")
     ap.add_argument("--replicas", action="store_true",

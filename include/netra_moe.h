@@ -192,11 +192,15 @@ int netra_moe_mxfp4_expand_launch(void* dst_fp8, float* dst_scale_f32, uint32_t*
  * the tensor core through TMEM.  This load-time step rewrites the same packed slabs (packed_e2m1 [total_rows, k/2],
  * scales_e8m0 [total_rows, k/32]) into the operand layout of those kernels, same sizes: dst_codes holds one contiguous
  * 8 KiB block per (128-row tile, 128-element K-block) and dst_scale_atoms one 512-byte atom per block with row r's
- * four scale bytes at 16 * (r % 32) + 4 * (r / 32).  A layer created with weights_tiled = 2 on these buffers streams
- * 0.53 bytes per weight instead of 1.0; it runs the swap-AB kernels at every token count.  Code pointers must be
- * 32-byte aligned for the layer, total_rows and k multiples of 128, at most 65,535 row tiles per call. */
+ * four scale bytes at 16 * (r % 32) + 4 * (r / 32).  The kernels fetch two blocks per copy (boxes of 256 four-bit
+ * rows are what reaches the HBM rate), so the block order matters: paired_half_rows = 0 gives (tile, K-block) order -
+ * W2: two consecutive K-blocks of a tile are fetched together; paired_half_rows = 512 is for W13, whose slabs of 1024
+ * rows are 512 gate rows followed by 512 up rows: order (slab, channel tile, K-block, gate | up), a gate tile next to
+ * its up tile.  A layer created with weights_tiled = 2 on these buffers streams 0.53 bytes per weight instead of 1.0;
+ * it runs the swap-AB kernels at every token count.  Code pointers must be 32-byte aligned for the layer, total_rows
+ * and k multiples of 128, at most 65,535 row tiles per call. */
 int netra_moe_mxfp4_pack_launch(void* dst_codes, void* dst_scale_atoms, const void* packed_e2m1, const void* scales_e8m0,
-                                uint64_t total_rows, uint32_t k, cudaStream_t stream);
+                                uint64_t total_rows, uint32_t k, uint32_t paired_half_rows, cudaStream_t stream);
 
 /* Control plane (serialised by the caller): encodes the tensor maps of the persistent buffers
  * and clears the status words.  No device memory is allocated. */

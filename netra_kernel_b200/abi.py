@@ -73,7 +73,7 @@ SIGNATURES = {
     "netra_moe_repack_tiles_launch": (c_int, [c_void_p, c_void_p, c_u64, c_u32, c_void_p]),
     "netra_moe_widen_scales_bf16_launch": (c_int, [c_void_p, c_void_p, c_u64, c_void_p]),
     "netra_moe_mxfp4_expand_launch": (c_int, [c_void_p] * 5 + [c_u64, c_u32, c_void_p]),
-    "netra_moe_mxfp4_pack_launch": (c_int, [c_void_p] * 4 + [c_u64, c_u32, c_void_p]),
+    "netra_moe_mxfp4_pack_launch": (c_int, [c_void_p] * 4 + [c_u64, c_u32, c_u32, c_void_p]),
     "netra_moe_expert_block_create": (c_int, [ctypes.POINTER(ExpertBlockDesc), ctypes.POINTER(c_void_p)]),
     "netra_moe_expert_block_launch": (c_int, [c_void_p, c_void_p]),
     "netra_moe_expert_block_destroy": (c_int, [c_void_p]),

@@ -75,15 +75,15 @@ int encode_u8_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row
 }
 
 // MXFP4 code blocks written by netra_moe_mxfp4_pack_launch: [tile_rows, 128] four-bit elements, 64 bytes per row in
-// memory.  The copy engine widens each group of 16 codes (8 bytes) to 16 bytes of shared memory, so a box of
-// 128 x 128 elements lands as the same 16 KiB, 128-byte-swizzled tile an E4M3 box does.
+// memory.  The copy engine widens each group of 16 codes (8 bytes) to 16 bytes of shared memory, so 128 x 128
+// elements land as the same 16 KiB, 128-byte-swizzled tile an E4M3 box gives; a box is two such blocks.
 int encode_fp4_tiles(CUtensorMap* map, const void* base, uint64_t tile_rows) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return fail("cuTensorMapEncodeTiled is not available from the driver");
   if (((uintptr_t)base & 31) != 0) return fail("MXFP4 code blocks must be 32-byte aligned");
   cuuint64_t dims[2] = {128, tile_rows};
   cuuint64_t strides[1] = {64};
-  cuuint32_t box[2] = {128, 128};
+  cuuint32_t box[2] = {128, 256};      // two blocks per copy: boxes of 128 four-bit rows do not reach the HBM rate
   cuuint32_t elem[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, const_cast<void*>(base), dims, strides, box, elem,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -573,15 +573,18 @@ int netra_moe_mxfp4_expand_launch(void* dst_fp8, float* dst_scale, uint32_t* ine
 }
 
 int netra_moe_mxfp4_pack_launch(void* dst_codes, void* dst_scale_atoms, const void* packed, const void* scales_e8m0,
-                                uint64_t total_rows, uint32_t k, cudaStream_t stream) {
+                                uint64_t total_rows, uint32_t k, uint32_t paired_half_rows, cudaStream_t stream) {
   if (!dst_codes || !dst_scale_atoms || !packed || !scales_e8m0 || dst_codes == packed || dst_scale_atoms == scales_e8m0)
     return fail("mxfp4_pack: null or aliased pointers");
   if (total_rows == 0 || total_rows % 128 != 0 || k == 0 || k % 128 != 0) return fail("mxfp4_pack: rows and k must be positive multiples of 128");
   if (total_rows / 128 > 65535) return fail("mxfp4_pack: at most 65,535 row tiles per call");
+  if (paired_half_rows % 128 != 0 || (paired_half_rows != 0 && total_rows % (2ull * paired_half_rows) != 0))
+    return fail("mxfp4_pack: paired_half_rows must be a multiple of 128 and the rows whole slabs of twice that");
+  if (paired_half_rows == 0 && (k / 128) % 2 != 0) return fail("mxfp4_pack: unpaired rows need an even number of K-blocks");
   if ((((uintptr_t)dst_codes | (uintptr_t)packed) & 15) != 0 || (((uintptr_t)dst_scale_atoms | (uintptr_t)scales_e8m0) & 3) != 0)
     return fail("mxfp4_pack: code pointers must be 16-byte aligned, scale pointers 4-byte aligned");
   netra_moe_mxfp4_pack_sm100<<<dim3(k / 128, (unsigned)(total_rows / 128)), 128, 0, stream>>>(
-      (uint8_t*)dst_codes, (uint8_t*)dst_scale_atoms, (const uint8_t*)packed, (const uint8_t*)scales_e8m0, k);
+      (uint8_t*)dst_codes, (uint8_t*)dst_scale_atoms, (const uint8_t*)packed, (const uint8_t*)scales_e8m0, k, paired_half_rows / 128);
   return check_launch("mxfp4_pack launch");
 }
 

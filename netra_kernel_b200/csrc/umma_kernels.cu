@@ -198,7 +198,10 @@ __device__ __forceinline__ Item decode_item(int item, const int* item_pre, const
 
 // kGateUp: 2 weight tiles per stage (gate, up), K = 2048, FP8 epilogue.  else: 1 tile, K = 512, FP32 epilogue.
 // kFp4: the weight tiles are MXFP4 (E2M1 codes, 64 bytes per row and K-block in memory, expanded by the copy engine
-// to one byte per element in shared memory) and each tile brings a 512-byte atom of UE8M0 scales.
+// to one byte per element in shared memory) and each tile brings a 512-byte atom of UE8M0 scales.  The copy engine
+// reaches the HBM rate on four-bit rows only with boxes of 256 rows (16 KiB of codes; boxes of 128 rows stop at about
+// 5 TB/s however many are in flight), so a stage is filled by one such box: the gate and the up tile of a K-block,
+// stored next to each other, or two consecutive K-blocks of a W2 tile.
 template <bool kGateUp, bool kFp4 = false>
 struct Cfg {
   static constexpr int kATiles = kGateUp ? 2 : 1;
@@ -218,11 +221,15 @@ struct Cfg {
   static constexpr int kAccCols = kKbPerStep * kATiles * kTokMax;                      // TMEM columns per hand-off: 64 | 128
   static constexpr int kScaleCols = kFp4 ? 4 * kATiles + 4 : 0;                        // TMEM columns of the A and B scales
   static constexpr int kAccStages = (512 - kScaleCols) / kAccCols;                     // 8 | 4 (MXFP4: 7 | 3)
-  static constexpr int kStages = kGateUp ? (kFp4 ? 5 : 6) : 10;
-  static constexpr int kStageBytes = kATiles * kWTileBytes + kTokTileBytes;            // 36 KiB | 20 KiB
+  static constexpr int kKbPerLoad = (kFp4 && !kGateUp) ? 2 : 1;                        // K-blocks per shared-memory stage
+  static constexpr int kStages = kFp4 ? 5 : (kGateUp ? 6 : 10);
+  static constexpr int kStageTiles = kKbPerLoad * kATiles;                             // weight tiles per stage
+  static constexpr int kStageBytes = kKbPerLoad * (kATiles * kWTileBytes + kTokTileBytes);   // 36 KiB | 20 KiB (MXFP4 down: 40 KiB)
   static constexpr int kWTxBytes = kFp4 ? kWTileBytes / 2 : kWTileBytes;               // bytes one weight-tile copy reports
   static constexpr int kScaleAtomBytes = 512;                                          // 128 rows x 4 groups of 32
-  static constexpr int kScaleStageBytes = kFp4 ? kATiles * kScaleAtomBytes : 0;
+  static constexpr int kScaleStageBytes = kFp4 ? kStageTiles * kScaleAtomBytes : 0;
+  static_assert(!kFp4 || kStageTiles == 2, "an MXFP4 stage is one 256-row box");
+  static_assert(kKbPerStep % kKbPerLoad == 0 && kKBlocks % kKbPerLoad == 0, "stages must tile an accumulator step");
   static constexpr int kTmemCols = 512;
   static constexpr int kXsBytes = kTokMax * kKBlocks * 4;                              // 4 KiB | 1 KiB
   static constexpr int kWsBytes = kKBlocks * 4;                                        // 64 B | 16 B per tile
@@ -345,7 +352,7 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
         const Item w = get_item((int)n_item, item);
         const int box = (C::kTokMax == 32 || w.m_valid <= 32) ? 32 : 64;
         const CUtensorMap* tm_x = box == 32 ? tm_x32 : tm_x64;
-        const uint32_t bytes = C::kATiles * C::kWTxBytes + box * kBlock + C::kScaleStageBytes;
+        const uint32_t bytes = C::kStageTiles * C::kWTxBytes + C::kKbPerLoad * box * kBlock + C::kScaleStageBytes;
         // scales of this item: token-row scales [128][KB] and the tile's weight scales
         {
           const int slot = n_item % C::kScaleSlots;
@@ -363,7 +370,7 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
           }
         }
         for (int sub = 0; ok && sub < C::kSubTiles; ++sub)
-        for (int kb = 0; kb < C::kKBlocks; ++kb, ++it) {
+        for (int kb = 0; kb < C::kKBlocks; kb += C::kKbPerLoad, ++it) {
           const int s = it % C::kStages;
           if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / C::kStages) & 1) ^ 1, abort_flag)) {
             status[0] = kStatusProducerTimeout; *abort_flag = 1; ok = false; break;
@@ -371,8 +378,21 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
           const uint32_t bar = smem_u32(&full_bar[s]);
           const uint32_t dst = smem_u32(stage_base + s * C::kStageBytes);
           mbar_expect_tx(bar, bytes);
+          if constexpr (kFp4) {
+            // one box of 256 code rows = two 8 KiB blocks that the pack step stored next to each other: W13 blocks are
+            // ordered (slab, channel tile, K-block, gate | up), W2 blocks (slab tile, K-block); their 512-byte scale
+            // atoms follow the same order, so the stage's two atoms are one 1 KiB copy
+            const int wy = kGateUp ? (((w.group * C::kNTiles + w.ntile) * C::kKBlocks + kb) * 2) * kTileRows
+                                   : ((w.group * C::kSlabTiles + w.ntile) * C::kKBlocks + kb) * kTileRows;
+            tma_load_2d(dst, tm_w, bar, 0, wy, pol_w);
+#pragma unroll
+            for (int j = 0; j < C::kKbPerLoad; ++j)
+              tma_load_2d(dst + C::kStageTiles * kWTileBytes + j * C::kTokTileBytes, tm_x, bar, (kb + j) * kBlock, w.row0, pol_x);
+            bulk_load(smem_u32(atom_base + s * C::kScaleStageBytes), w_scale_atoms + (size_t)wy * 4, C::kScaleStageBytes, bar);
+            continue;
+          }
           int wx, wy0, wy1;
-          if (kFp4 || w_tiled) {   // one contiguous block per (slab tile, K-block): 16 KiB of E4M3 or 8 KiB of E2M1 codes
+          if (w_tiled) {   // one contiguous 16 KiB block per (slab tile, K-block)
             wx = 0;
             wy0 = ((w.group * C::kSlabTiles + w.ntile + sub) * C::kKBlocks + kb) * kTileRows;
             wy1 = wy0 + (kInter / kTileRows) * C::kKBlocks * kTileRows;
@@ -384,11 +404,6 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
           tma_load_2d(dst, tm_w, bar, wx, wy0, pol_w);
           if (kGateUp) tma_load_2d(dst + kWTileBytes, tm_w, bar, wx, wy1, pol_w);
           tma_load_2d(dst + C::kATiles * kWTileBytes, tm_x, bar, kb * kBlock, w.row0, pol_x);
-          if constexpr (kFp4) {   // the tiles' scale atoms: 512 bytes per (slab tile, K-block), in tile order
-            const uint32_t adst = smem_u32(atom_base + s * C::kScaleStageBytes);
-            bulk_load(adst, w_scale_atoms + (size_t)wy0 * 4, C::kScaleAtomBytes, bar);
-            if (kGateUp) bulk_load(adst + C::kScaleAtomBytes, w_scale_atoms + (size_t)wy1 * 4, C::kScaleAtomBytes, bar);
-          }
         }
       }
     }
@@ -407,39 +422,43 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
             status[0] = kStatusMmaTimeout; *abort_flag = 1; ok = false; break;
           }
 #pragma unroll 1
-          for (int q = 0; q < C::kKbPerStep; ++q, ++it) {
+          for (int q = 0; q < C::kKbPerStep; q += C::kKbPerLoad, ++it) {
             const int s = it % C::kStages;
             if (!mbar_wait(smem_u32(&full_bar[s]), (it / C::kStages) & 1, abort_flag)) {
               status[0] = kStatusMmaTimeout; *abort_flag = 1; ok = false; break;
             }
             tc_fence_after();
             const uint32_t sa = smem_u32(stage_base + s * C::kStageBytes);
-            const uint64_t bdesc = make_smem_desc(sa + C::kATiles * kWTileBytes);
-            const uint32_t d0 = tmem_base + (uint32_t)(a * C::kAccCols + q * C::kATiles * C::kTokMax);
-            // the two tiles accumulate into different TMEM columns: alternate them so that consecutive
-            // MMAs never depend on each other
-            if constexpr (kFp4) {
-              // scale atoms -> TMEM; the tensor-core pipe runs copies and MMAs of one thread in issue order, so the
-              // MMAs of the previous K-block have read these columns before they are overwritten
 #pragma unroll
-              for (int tile = 0; tile < C::kATiles; ++tile)
-                tmem_cp_32x128b_warpx4(tmem_scale + (uint32_t)(4 * tile),
-                                       make_scale_desc(smem_u32(atom_base + s * C::kScaleStageBytes + tile * C::kScaleAtomBytes)));
-#pragma unroll
-              for (int k = 0; k < kBlock / 32; ++k) {
+            for (int j = 0; j < C::kKbPerLoad; ++j) {      // K-blocks held by this stage
+              const uint32_t sw = sa + (uint32_t)(j * C::kATiles * kWTileBytes);            // their weight tiles
+              const uint64_t bdesc = make_smem_desc(sa + C::kStageTiles * kWTileBytes + j * C::kTokTileBytes);
+              const uint32_t d0 = tmem_base + (uint32_t)(a * C::kAccCols + (q + j) * C::kATiles * C::kTokMax);
+              // the two tiles accumulate into different TMEM columns: alternate them so that consecutive
+              // MMAs never depend on each other
+              if constexpr (kFp4) {
+                // scale atoms -> TMEM; the tensor-core pipe runs copies and MMAs of one thread in issue order, so the
+                // MMAs of the previous K-block have read these columns before they are overwritten
 #pragma unroll
                 for (int tile = 0; tile < C::kATiles; ++tile)
-                  umma_mxf8f6f4(d0 + (uint32_t)(tile * C::kTokMax), make_smem_desc(sa + tile * kWTileBytes) + 2 * k, bdesc + 2 * k,
-                                make_idesc_mxfp4(n_mma, (uint32_t)k), (tmem_scale + (uint32_t)(4 * tile)) | ((uint32_t)k << 30),
-                                tmem_scale + (uint32_t)(4 * C::kATiles), k > 0);
+                  tmem_cp_32x128b_warpx4(tmem_scale + (uint32_t)(4 * tile),
+                                         make_scale_desc(smem_u32(atom_base + s * C::kScaleStageBytes + (j * C::kATiles + tile) * C::kScaleAtomBytes)));
+#pragma unroll
+                for (int k = 0; k < kBlock / 32; ++k) {
+#pragma unroll
+                  for (int tile = 0; tile < C::kATiles; ++tile)
+                    umma_mxf8f6f4(d0 + (uint32_t)(tile * C::kTokMax), make_smem_desc(sw + tile * kWTileBytes) + 2 * k, bdesc + 2 * k,
+                                  make_idesc_mxfp4(n_mma, (uint32_t)k), (tmem_scale + (uint32_t)(4 * tile)) | ((uint32_t)k << 30),
+                                  tmem_scale + (uint32_t)(4 * C::kATiles), k > 0);
+                }
+              } else {
+#pragma unroll
+                for (int k = 0; k < kBlock / 32; ++k) {
+#pragma unroll
+                  for (int tile = 0; tile < C::kATiles; ++tile)
+                    umma_f8(d0 + (uint32_t)(tile * C::kTokMax), make_smem_desc(sw + tile * kWTileBytes) + 2 * k, bdesc + 2 * k, idesc, k > 0);
+                }
               }
-            } else {
-#pragma unroll
-            for (int k = 0; k < kBlock / 32; ++k) {
-#pragma unroll
-              for (int tile = 0; tile < C::kATiles; ++tile)
-                umma_f8(d0 + (uint32_t)(tile * C::kTokMax), make_smem_desc(sa + tile * kWTileBytes) + 2 * k, bdesc + 2 * k, idesc, k > 0);
-            }
             }
             umma_commit(smem_u32(&empty_bar[s]));
           }

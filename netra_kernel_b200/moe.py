@@ -82,7 +82,7 @@ class RoutedMoELayer:
         if self.mxfp4:
             self.tiled = True
             if not pretiled:
-                (w13, w13_scale), (w2, w2_scale) = pack_mxfp4(w13, w13_scale), pack_mxfp4(w2, w2_scale)
+                (w13, w13_scale), (w2, w2_scale) = pack_mxfp4(w13, w13_scale, paired_half_rows=INTER), pack_mxfp4(w2, w2_scale)
         elif pretiled:
             self.tiled = True
         elif self.tiled:
@@ -269,10 +269,11 @@ class RoutedMoELayer:
             pass
 
 
-def pack_mxfp4(packed: torch.Tensor, scales: torch.Tensor):
+def pack_mxfp4(packed: torch.Tensor, scales: torch.Tensor, paired_half_rows: int = 0):
     """MXFP4 slabs (packed E2M1 ``[G, N, K/2]`` u8, E8M0 scales ``[G, N, K/32]`` u8, on the GPU) -> the operand layout of
     the native MXFP4 kernels, same shapes and sizes: code blocks (8 KiB per 128-row tile and K-block) and scale atoms
-    (512 bytes per tile and K-block).  ``netra_moe_mxfp4_pack_launch``."""
+    (512 bytes per tile and K-block).  ``paired_half_rows``: 0 for W2 (blocks in (tile, K-block) order), 512 for W13
+    (a gate tile's block next to its up tile's).  ``netra_moe_mxfp4_pack_launch``."""
     _require_cuda(packed, scales)
     g, n, half_k = packed.shape
     k = half_k * 2
@@ -288,7 +289,7 @@ def pack_mxfp4(packed: torch.Tensor, scales: torch.Tensor):
     for r0 in range(0, total, rows_per_call):
         r1 = min(total, r0 + rows_per_call)
         abi.check(lib.netra_moe_mxfp4_pack_launch(dst_c[r0:r1].data_ptr(), dst_s[r0:r1].data_ptr(), src_c[r0:r1].data_ptr(),
-                                                  src_s[r0:r1].data_ptr(), r1 - r0, k, _stream()), "mxfp4_pack_launch")
+                                                  src_s[r0:r1].data_ptr(), r1 - r0, k, paired_half_rows, _stream()), "mxfp4_pack_launch")
     return codes, atoms
 
 

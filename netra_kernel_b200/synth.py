@@ -215,10 +215,12 @@ def make_operands(tokens: int, layer: int = 0, zipf_alpha: Optional[float] = Non
                         "seeds": {"hidden": 0, "router": 1, "experts": 1000 + layer}})
 
 
-def workload_bytes_decode(tokens: int, experts_hit: int = N_ROUTED) -> int:
+def workload_bytes_decode(tokens: int, experts_hit: int = N_ROUTED, mxfp4: bool = False) -> int:
     """Algorithmic HBM bytes of one layer call: every hit expert slab and its scales
-    once, the shared slab, the router weight, BF16 hidden in and BF16 out."""
-    slab = 2 * INTER * HIDDEN + HIDDEN * INTER + 4 * (8 * 16 + 16 * 4)
+    once, the shared slab, the router weight, BF16 hidden in and BF16 out.  ``mxfp4``: the slabs are
+    E2M1 codes (half a byte per weight) with one E8M0 byte per 32 weights."""
+    weights = 2 * INTER * HIDDEN + HIDDEN * INTER
+    slab = weights // 2 + weights // 32 if mxfp4 else weights + 4 * (8 * 16 + 16 * 4)
     return (experts_hit + 1) * slab + N_ROUTED * HIDDEN * 2 + 2 * tokens * HIDDEN * 2
 
 
