@@ -578,10 +578,10 @@ def mxfp4_decode_object(layer, hidden_cpu, steps, warmup, dev, stream, sync, fp8
         "launch": "CUDA graph replay of the layer's %d kernels" % layer.launches_per_call(tokens),
         "api": "netra_moe_layer_launch (fused-layer ABI, weights_tiled = 2), captured CUDA graph",
         "l2": "inputs larger than L2: every step streams %.1f MB of expert weights (L2 is 126 MB)" % (layer_bytes / 1e6),
-        "roofline": {"bound": "hbm", "kernel": "netra_moe_gate_up_mxfp4_sm100", "achieved": gate_up_bytes / gu_s / 1e9, "peak": peak,
+        "roofline": {"bound": "hbm", "kernel": "netra_moe_gate_up_mxfp4_umma_sm100", "achieved": gate_up_bytes / gu_s / 1e9, "peak": peak,
                      "unit": "GB/s", "frac": gate_up_bytes / gu_s / 1e9 / peak, "peak_source": peak_kind,
                      "algorithmic_bytes": gate_up_bytes, "avg_launch_ms": stage_ms[6], "traffic": mxfp4_gate_up_traffic_bytes()},
-        "down_kernel": {"kernel": "netra_moe_down_mxfp4_sm100", "achieved": down_bytes / dn_s / 1e9, "unit": "GB/s",
+        "down_kernel": {"kernel": "netra_moe_down_mxfp4_umma_sm100", "achieved": down_bytes / dn_s / 1e9, "unit": "GB/s",
                         "frac": down_bytes / dn_s / 1e9 / peak, "algorithmic_bytes": down_bytes},
         "layer_hbm": {"algorithmic_bytes": layer_bytes, "fp8_layer_bytes": synth.workload_bytes_decode(tokens, hit),
                       "achieved": layer_bytes / (ms / 1e3) / 1e9, "unit": "GB/s", "frac": layer_bytes / (ms / 1e3) / 1e9 / peak},
@@ -818,8 +818,8 @@ def run_ours(args) -> None:
             del mx
             torch.cuda.empty_cache()
 
-            # the same MXFP4 slabs kept four-bit in memory: the native block-scaled kernels at decode size, and (swap-AB
-            # form, the only one they have) at the prefill size for the record
+            # the same MXFP4 slabs kept four-bit in memory: the native block-scaled kernels at decode size (swap-AB form) and at
+            # the prefill size (token-major form)
             nat = RoutedMoELayer(layer._keep[0], p13, s13, p2, s2, 8192, bias8.to(dev), mxfp4=True)
             del p13, s13, p2, s2
             hd_cpu, _, _ = synth.make_activations(256, None, seed=0)
@@ -839,8 +839,10 @@ def run_ours(args) -> None:
                 st_nat = time_stages(nat, hd, od, cap, warmup, stream, sync)
             extras["mxfp4_t8192"]["native_four_bit_weights"] = {
                 "ms_per_step": ms_nat, "tokens_per_s": 8192 / (ms_nat / 1e3),
-                "gemm_form": "swap-AB block-scaled kernels (netra_moe_gate_up_mxfp4_sm100, netra_moe_down_mxfp4_sm100): the form "
-                             "built for weight-streaming-bound calls; at this size the expanded tiles on the token-major kernels are faster",
+                "gemm_form": "token-major block-scaled kernels (netra_moe_gate_up_mxfp4_tokmajor_sm100, netra_moe_down_mxfp4_tokmajor_sm100): "
+                             "tcgen05.mma.kind::mxf8f6f4.block_scale, 128 token rows x 256 four-bit weight rows per instruction; the scale "
+                             "columns leave TMEM room for one accumulator stage, so the expanded tiles on the FP8 kernels stay the faster tactic here",
+                "weight_bytes": 257 * (3 * 1024 * 1024 // 2 + 3 * 1024 * 1024 // 32),
                 "kernels_ms": {n: round(v, 5) for n, v in zip(nat.STAGES, st_nat)}}
             nat.close()
             del nat, nat_decode, gn, hd, od

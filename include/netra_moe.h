@@ -193,12 +193,13 @@ int netra_moe_mxfp4_expand_launch(void* dst_fp8, float* dst_scale_f32, uint32_t*
  * scales_e8m0 [total_rows, k/32]) into the operand layout of those kernels, same sizes: dst_codes holds one contiguous
  * 8 KiB block per (128-row tile, 128-element K-block) and dst_scale_atoms one 512-byte atom per block with row r's
  * four scale bytes at 16 * (r % 32) + 4 * (r / 32).  The kernels fetch two blocks per copy (boxes of 256 four-bit
- * rows are what reaches the HBM rate), so the block order matters: paired_half_rows = 0 gives (tile, K-block) order -
- * W2: two consecutive K-blocks of a tile are fetched together; paired_half_rows = 512 is for W13, whose slabs of 1024
- * rows are 512 gate rows followed by 512 up rows: order (slab, channel tile, K-block, gate | up), a gate tile next to
- * its up tile.  A layer created with weights_tiled = 2 on these buffers streams 0.53 bytes per weight instead of 1.0;
- * it runs the swap-AB kernels at every token count.  Code pointers must be 32-byte aligned for the layer, total_rows
- * and k multiples of 128, at most 65,535 row tiles per call. */
+ * rows are what reaches the HBM rate) - the two weight tiles one MMA stage consumes - so the block order matters.  The
+ * rows come in groups of 2 * paired_half_rows rows whose two halves are consumed together; blocks are ordered (group,
+ * tile within the half, K-block, half).  W2: paired_half_rows = 128 (tiles 2p and 2p + 1 side by side).  W13:
+ * paired_half_rows = 512, its slabs of 1024 rows being 512 gate rows followed by 512 up rows: a gate tile next to
+ * its up tile.  A layer created with weights_tiled = 2 on these buffers streams 0.53 bytes per weight instead of 1.0.
+ * Code pointers must be 32-byte aligned for the layer, total_rows and k multiples of 128, at most 65,535 row tiles per
+ * call. */
 int netra_moe_mxfp4_pack_launch(void* dst_codes, void* dst_scale_atoms, const void* packed_e2m1, const void* scales_e8m0,
                                 uint64_t total_rows, uint32_t k, uint32_t paired_half_rows, cudaStream_t stream);
 
@@ -356,7 +357,8 @@ int netra_ep_layer_status(netra_ep_layer_t* layer, uint32_t status_out[4]);
 int netra_ep_layer_destroy(netra_ep_layer_t* layer);
 
 /* Block size and dynamic shared memory of the tensor-core kernels (which: 0 gate_up, 1 down, 2 and 3 their
- * token-major forms, 4 token-major down with FP16 rows, 5 tensor-core router, 6 and 7 gate_up and down on MXFP4 weights), so
+ * token-major forms, 4 token-major down with FP16 rows, 5 tensor-core router, 6 and 7 gate_up and down on MXFP4 weights,
+ * 8 and 9 their token-major forms), so
  * that an engine manifest written ahead of time can be checked against the built library. */
 int netra_moe_kernel_launch_info(uint32_t which, uint32_t* block_threads, uint32_t* dynamic_smem_bytes);
 

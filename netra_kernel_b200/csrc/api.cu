@@ -122,10 +122,14 @@ int umma_setup() {
   if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(gate_up)", e);
   e = cudaFuncSetAttribute(netra_moe_down_umma_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, down_smem_bytes());
   if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(down)", e);
-  e = cudaFuncSetAttribute(netra_moe_gate_up_mxfp4_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, gate_up_mxfp4_smem_bytes());
+  e = cudaFuncSetAttribute(netra_moe_gate_up_mxfp4_umma_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, gate_up_mxfp4_smem_bytes());
   if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(gate_up_mxfp4)", e);
-  e = cudaFuncSetAttribute(netra_moe_down_mxfp4_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, down_mxfp4_smem_bytes());
+  e = cudaFuncSetAttribute(netra_moe_down_mxfp4_umma_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, down_mxfp4_smem_bytes());
   if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(down_mxfp4)", e);
+  e = cudaFuncSetAttribute(netra_moe_gate_up_mxfp4_tokmajor_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, gate_up_mxfp4_tokmajor_smem_bytes());
+  if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(gate_up_mxfp4_tokmajor)", e);
+  e = cudaFuncSetAttribute(netra_moe_down_mxfp4_tokmajor_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, down_mxfp4_tokmajor_smem_bytes());
+  if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(down_mxfp4_tokmajor)", e);
   e = cudaFuncSetAttribute(netra_moe_gate_up_tokmajor_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, gate_up_tokmajor_smem_bytes());
   if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(gate_up_tokmajor)", e);
   e = cudaFuncSetAttribute(netra_moe_down_tokmajor_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, down_tokmajor_smem_bytes());
@@ -138,14 +142,16 @@ int umma_setup() {
   if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(router_umma)", e);
   {
     // the register re-balancing inside these kernels is only deadlock-free for the launch allocation it was written for
-    cudaFuncAttributes a0, a1, a2, a3;
+    cudaFuncAttributes a0, a1, a2, a3, a4, a5;
     e = cudaFuncGetAttributes(&a0, netra_moe_gate_up_tokmajor_sm100);
     if (e == cudaSuccess) e = cudaFuncGetAttributes(&a1, netra_moe_down_tokmajor_sm100);
     if (e == cudaSuccess) e = cudaFuncGetAttributes(&a2, netra_moe_down_tokmajor_f16_sm100);
     if (e == cudaSuccess) e = cudaFuncGetAttributes(&a3, netra_moe_gate_up_tokmajor_gather_sm100);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a4, netra_moe_gate_up_mxfp4_tokmajor_sm100);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a5, netra_moe_down_mxfp4_tokmajor_sm100);
     if (e != cudaSuccess) return fail_cuda("cudaFuncGetAttributes(tokmajor)", e);
     g_tokmajor_ok[device] = a0.numRegs == kTmRegsLaunch && a1.numRegs == kTmRegsLaunch && a2.numRegs == kTmRegsLaunch &&
-                            a3.numRegs == kTmRegsLaunch;
+                            a3.numRegs == kTmRegsLaunch && a4.numRegs == kTmRegsLaunch && a5.numRegs == kTmRegsLaunch;
   }
   g_umma_ready[device] = true;
   return 0;
@@ -361,12 +367,12 @@ constexpr uint32_t kRouterK8MaxRows = 1024;   // up to here the router runs on t
 bool use_umma_router(const netra_moe_layer* layer, uint32_t tokens) {
   return tokens > kRouterK8MaxRows && layer->router_mode != 1;
 }
-// The token-major GEMMs exist for E4M3 weight tiles; a layer on MXFP4 weights runs the swap-AB kernels at every size.
 bool layer_tokmajor(const netra_moe_layer* layer, uint32_t pairs) {
-  return layer->gemm_mode != 1 && layer->desc.weights_tiled != kWeightsMxfp4 && use_tokmajor(layer->device, pairs, kRouted);
+  return layer->gemm_mode != 1 && use_tokmajor(layer->device, pairs, kRouted);
 }
+// FP16 partial rows are an output format of the E4M3 token-major down projection
 bool use_f16_partials(const netra_moe_layer* layer, uint32_t pairs) {
-  return layer->partial_f16 != 0 && layer_tokmajor(layer, pairs);
+  return layer->partial_f16 != 0 && layer->desc.weights_tiled != kWeightsMxfp4 && layer_tokmajor(layer, pairs);
 }
 
 // One launch of the layer's fixed sequence (same idea as the reference's per-operation launch,
@@ -438,11 +444,19 @@ int launch_stage(netra_moe_layer* layer, uint32_t stage, const void* hidden, con
       if (tokens > (uint32_t)kSortSmallMaxRows) netra_moe_sort_scatter_sm100<<<nseg, 256, 0, stream>>>(perm, inv_perm, seg_hist, ids9, tokens);
       break;
     case 5:   // the gathering gate_up fetches its token rows itself: no expert-sorted copy is made for it
-      if (!(tokmajor && layer->gather_rows_in_gemm))
+      if (!(tokmajor && layer->gather_rows_in_gemm && !mxfp4))
         netra_moe_gather_rows_sm100<<<(pairs + 7) / 8, 256, 0, stream>>>(a_fp8, a_scale, perm, tokens);
       break;
     case 6:
-      if (tokmajor && layer->gather_rows_in_gemm)
+      if (mxfp4 && tokmajor)
+        netra_moe_gate_up_mxfp4_tokmajor_sm100<<<layer->sm_count, kTmThreads, gate_up_mxfp4_tokmajor_smem_bytes(), stream>>>(
+            layer->tm_w13, layer->tm_a128, a_scale, (const uint8_t*)layer->desc.w13_scale_f32, offsets, h_fp8, h_scale, kRouted + 1,
+            status);
+      else if (mxfp4)
+        netra_moe_gate_up_mxfp4_umma_sm100<<<layer->sm_count, kGemmThreads, gate_up_mxfp4_smem_bytes(), stream>>>(
+            layer->tm_w13, layer->tm_a32, layer->tm_a64, layer->tm_a128, a_scale, (const uint8_t*)layer->desc.w13_scale_f32, offsets,
+            h_fp8, h_scale, kRouted + 1, status);
+      else if (tokmajor && layer->gather_rows_in_gemm)
         // Measured at 8,192 tokens: 607 us against 240 us for the form below.  One four-row gather per lane and K-block is 32
         // TMA instructions where the sorted copy needs one; the copy engine's issue rate, not the bytes, sets the pace.
         netra_moe_gate_up_tokmajor_gather_sm100<<<layer->sm_count, kTmThreads, gate_up_tokmajor_smem_bytes(), stream>>>(
@@ -452,17 +466,20 @@ int launch_stage(netra_moe_layer* layer, uint32_t stage, const void* hidden, con
         netra_moe_gate_up_tokmajor_sm100<<<layer->sm_count, kTmThreads, gate_up_tokmajor_smem_bytes(), stream>>>(
             layer->tm_w13, layer->tm_a128, a_scale, layer->desc.w13_scale_f32, offsets, h_fp8, h_scale, kRouted + 1,
             layer->desc.weights_tiled, status);
-      else if (mxfp4)
-        netra_moe_gate_up_mxfp4_sm100<<<layer->sm_count, kGemmThreads, gate_up_mxfp4_smem_bytes(), stream>>>(
-            layer->tm_w13, layer->tm_a32, layer->tm_a64, layer->tm_a128, a_scale, (const uint8_t*)layer->desc.w13_scale_f32, offsets,
-            h_fp8, h_scale, kRouted + 1, status);
       else
         netra_moe_gate_up_umma_sm100<<<layer->sm_count, kGemmThreads, gate_up_smem_bytes(), stream>>>(
             layer->tm_w13, layer->tm_a32, layer->tm_a64, layer->tm_a128, a_scale, layer->desc.w13_scale_f32, offsets, h_fp8,
             h_scale, kRouted + 1, layer->desc.weights_tiled, status);
       break;
     case 7:
-      if (tokmajor && layer->partial_f16)
+      if (mxfp4 && tokmajor)
+        netra_moe_down_mxfp4_tokmajor_sm100<<<layer->sm_count, kTmThreads, down_mxfp4_tokmajor_smem_bytes(), stream>>>(
+            layer->tm_w2, layer->tm_h128, h_scale, (const uint8_t*)layer->desc.w2_scale_f32, offsets, down, kRouted + 1, status + 1);
+      else if (mxfp4)
+        netra_moe_down_mxfp4_umma_sm100<<<layer->sm_count, kGemmThreads, down_mxfp4_smem_bytes(), stream>>>(
+            layer->tm_w2, layer->tm_h32, layer->tm_h64, layer->tm_h128, h_scale, (const uint8_t*)layer->desc.w2_scale_f32, offsets, down,
+            kRouted + 1, status + 1);
+      else if (tokmajor && layer->partial_f16)
         netra_moe_down_tokmajor_f16_sm100<<<layer->sm_count, kTmThreads, down_tokmajor_f16_smem_bytes(), stream>>>(
             layer->tm_w2, layer->tm_h128, h_scale, layer->desc.w2_scale_f32, offsets, down, kRouted + 1,
             layer->desc.weights_tiled, status + 1);
@@ -470,10 +487,6 @@ int launch_stage(netra_moe_layer* layer, uint32_t stage, const void* hidden, con
         netra_moe_down_tokmajor_sm100<<<layer->sm_count, kTmThreads, down_tokmajor_smem_bytes(), stream>>>(
             layer->tm_w2, layer->tm_h128, h_scale, layer->desc.w2_scale_f32, offsets, down, kRouted + 1,
             layer->desc.weights_tiled, status + 1);
-      else if (mxfp4)
-        netra_moe_down_mxfp4_sm100<<<layer->sm_count, kGemmThreads, down_mxfp4_smem_bytes(), stream>>>(
-            layer->tm_w2, layer->tm_h32, layer->tm_h64, layer->tm_h128, h_scale, (const uint8_t*)layer->desc.w2_scale_f32, offsets, down,
-            kRouted + 1, status + 1);
       else
         netra_moe_down_umma_sm100<<<layer->sm_count, kGemmThreads, down_smem_bytes(), stream>>>(
             layer->tm_w2, layer->tm_h32, layer->tm_h64, layer->tm_h128, h_scale, layer->desc.w2_scale_f32, offsets, down,
@@ -578,9 +591,8 @@ int netra_moe_mxfp4_pack_launch(void* dst_codes, void* dst_scale_atoms, const vo
     return fail("mxfp4_pack: null or aliased pointers");
   if (total_rows == 0 || total_rows % 128 != 0 || k == 0 || k % 128 != 0) return fail("mxfp4_pack: rows and k must be positive multiples of 128");
   if (total_rows / 128 > 65535) return fail("mxfp4_pack: at most 65,535 row tiles per call");
-  if (paired_half_rows % 128 != 0 || (paired_half_rows != 0 && total_rows % (2ull * paired_half_rows) != 0))
-    return fail("mxfp4_pack: paired_half_rows must be a multiple of 128 and the rows whole slabs of twice that");
-  if (paired_half_rows == 0 && (k / 128) % 2 != 0) return fail("mxfp4_pack: unpaired rows need an even number of K-blocks");
+  if (paired_half_rows == 0 || paired_half_rows % 128 != 0 || total_rows % (2ull * paired_half_rows) != 0)
+    return fail("mxfp4_pack: paired_half_rows must be a positive multiple of 128 and the rows whole groups of twice that");
   if ((((uintptr_t)dst_codes | (uintptr_t)packed) & 15) != 0 || (((uintptr_t)dst_scale_atoms | (uintptr_t)scales_e8m0) & 3) != 0)
     return fail("mxfp4_pack: code pointers must be 16-byte aligned, scale pointers 4-byte aligned");
   netra_moe_mxfp4_pack_sm100<<<dim3(k / 128, (unsigned)(total_rows / 128)), 128, 0, stream>>>(
@@ -695,10 +707,11 @@ int netra_ep_unpack_rows_launch(float* down, const float* back_slots, const int3
 }
 
 int netra_moe_kernel_launch_info(uint32_t which, uint32_t* block_threads, uint32_t* dynamic_smem_bytes) {
-  if (!block_threads || !dynamic_smem_bytes || which > 7) return fail("kernel_launch_info: bad argument");
-  *block_threads = (which < 2 || which > 5) ? kGemmThreads : which == 5 ? kRtThreads : kTmThreads;
-  const int bytes[8] = {gate_up_smem_bytes(), down_smem_bytes(), gate_up_tokmajor_smem_bytes(), down_tokmajor_smem_bytes(),
-                        down_tokmajor_f16_smem_bytes(), router_umma_smem_bytes(), gate_up_mxfp4_smem_bytes(), down_mxfp4_smem_bytes()};
+  if (!block_threads || !dynamic_smem_bytes || which > 9) return fail("kernel_launch_info: bad argument");
+  *block_threads = (which < 2 || which == 6 || which == 7) ? kGemmThreads : which == 5 ? kRtThreads : kTmThreads;
+  const int bytes[10] = {gate_up_smem_bytes(), down_smem_bytes(), gate_up_tokmajor_smem_bytes(), down_tokmajor_smem_bytes(),
+                         down_tokmajor_f16_smem_bytes(), router_umma_smem_bytes(), gate_up_mxfp4_smem_bytes(), down_mxfp4_smem_bytes(),
+                         gate_up_mxfp4_tokmajor_smem_bytes(), down_mxfp4_tokmajor_smem_bytes()};
   *dynamic_smem_bytes = (uint32_t)bytes[which];
   return 0;
 }

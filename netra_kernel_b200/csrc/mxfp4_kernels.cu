@@ -69,23 +69,19 @@ netra_moe_mxfp4_expand_sm100(uint8_t* __restrict__ dst, float* __restrict__ dst_
 //   atoms  one 512-byte block per (tile, K-block) in the same order: the four scale bytes of row r and this
 //          K-block sit at byte 16 * (r % 32) + 4 * (r / 32) - the order in which a 32-row x 16-byte copy
 //          into TMEM puts row r's bytes into lane r % 32, column r / 32, the place the tensor core reads them
-// Block order: (tile, K-block) when paired_half_tiles is 0 - two consecutive K-blocks of a tile are then one
-// 256-row box.  Otherwise the rows come in slabs of 2 * paired_half_tiles tiles whose two halves (the gate rows
-// and the up rows of W13) are consumed together: order (slab, tile within the half, K-block, half), so that a
-// gate tile and its up tile are one 256-row box.
+// The kernels fetch two blocks per copy - the two weight tiles one MMA stage consumes - so blocks are ordered (group,
+// tile within the half, K-block, half): the rows come in groups of 2 * paired_half_tiles tiles whose two halves are
+// consumed together (W13: 4, a gate tile next to its up tile; W2: 1, tiles 2p and 2p + 1).
 // grid (k / 128, rows / 128), block 128: thread r moves row (blockIdx.y * 128 + r), K-block blockIdx.x.
 extern "C" __global__ void __launch_bounds__(128)
 netra_moe_mxfp4_pack_sm100(uint8_t* __restrict__ dst_codes, uint8_t* __restrict__ dst_atoms, const uint8_t* __restrict__ packed,
                            const uint8_t* __restrict__ scales, uint32_t k, uint32_t paired_half_tiles) {
   const uint32_t kb = blockIdx.x, r = threadIdx.x, kblocks = k / 128;
   const size_t row = (size_t)blockIdx.y * 128 + r;
-  size_t block = (size_t)blockIdx.y * kblocks + kb;
-  if (paired_half_tiles != 0) {
-    const uint32_t slab_tiles = 2 * paired_half_tiles;
-    const size_t slab = blockIdx.y / slab_tiles;
-    const uint32_t t = blockIdx.y % slab_tiles, half = t / paired_half_tiles, tile = t % paired_half_tiles;
-    block = (((slab * paired_half_tiles + tile) * kblocks + kb) * 2) + half;
-  }
+  const uint32_t group_tiles = 2 * paired_half_tiles;
+  const size_t group = blockIdx.y / group_tiles;
+  const uint32_t t = blockIdx.y % group_tiles, half = t / paired_half_tiles, tile = t % paired_half_tiles;
+  const size_t block = (((group * paired_half_tiles + tile) * kblocks + kb) * 2) + half;
   const uint4* src = reinterpret_cast<const uint4*>(packed + row * (k / 2) + kb * 64);
   uint4* out = reinterpret_cast<uint4*>(dst_codes + (block * 128 + r) * 64);
 #pragma unroll

@@ -200,11 +200,11 @@ __device__ __forceinline__ Item decode_item(int item, const int* item_pre, const
 // kFp4: the weight tiles are MXFP4 (E2M1 codes, 64 bytes per row and K-block in memory, expanded by the copy engine
 // to one byte per element in shared memory) and each tile brings a 512-byte atom of UE8M0 scales.  The copy engine
 // reaches the HBM rate on four-bit rows only with boxes of 256 rows (16 KiB of codes; boxes of 128 rows stop at about
-// 5 TB/s however many are in flight), so a stage is filled by one such box: the gate and the up tile of a K-block,
-// stored next to each other, or two consecutive K-blocks of a W2 tile.
+// 5 TB/s however many are in flight), so a stage is filled by one such box: the gate and the up tile of a K-block, or
+// two neighbouring W2 tiles, which the pack step stored next to each other.
 template <bool kGateUp, bool kFp4 = false>
 struct Cfg {
-  static constexpr int kATiles = kGateUp ? 2 : 1;
+  static constexpr int kATiles = (kGateUp || kFp4) ? 2 : 1;   // weight tiles per stage (MXFP4 down: two neighbouring W2 tiles)
   // token rows per work item (UMMA N).  32 for both: 64-row items (the shared expert at decode sizes) ran a longer
   // epilogue than the four TMEM stages could hide, and the CTAs that held them finished 8 us after the rest
   static constexpr int kTokMax = 32;
@@ -214,14 +214,14 @@ struct Cfg {
   static constexpr int kScaleSlots = kGateUp ? 2 : 4;
   static constexpr int kKBlocks = kGateUp ? kHiddenBlocks : kInterBlocks;
   static constexpr int kSubTiles = 1;                     // consecutive weight tiles per work item (same token rows)
-  static constexpr int kNTiles = (kGateUp ? kInter / kTileRows : kHidden / kTileRows) / kSubTiles;   // items per slab and chunk: 4 | 16
+  static constexpr int kNTiles = (kGateUp ? kInter / kTileRows : kHidden / kTileRows / kATiles) / kSubTiles;   // items per slab and chunk: 4 | 16 (MXFP4: 8)
   static constexpr int kSlabRows = kGateUp ? 2 * kInter : kHidden;                     // 1024 | 2048
   static constexpr int kSlabTiles = kSlabRows / kTileRows;                             // 8 | 16
-  static constexpr int kKbPerStep = kGateUp ? 1 : 4;      // K-blocks the MMA warp issues per accumulator hand-off
+  static constexpr int kKbPerStep = (kGateUp || kFp4) ? 1 : 4;   // K-blocks the MMA warp issues per accumulator hand-off
   static constexpr int kAccCols = kKbPerStep * kATiles * kTokMax;                      // TMEM columns per hand-off: 64 | 128
   static constexpr int kScaleCols = kFp4 ? 4 * kATiles + 4 : 0;                        // TMEM columns of the A and B scales
   static constexpr int kAccStages = (512 - kScaleCols) / kAccCols;                     // 8 | 4 (MXFP4: 7 | 3)
-  static constexpr int kKbPerLoad = (kFp4 && !kGateUp) ? 2 : 1;                        // K-blocks per shared-memory stage
+  static constexpr int kKbPerLoad = 1;                                                 // K-blocks per shared-memory stage
   static constexpr int kStages = kFp4 ? 5 : (kGateUp ? 6 : 10);
   static constexpr int kStageTiles = kKbPerLoad * kATiles;                             // weight tiles per stage
   static constexpr int kStageBytes = kKbPerLoad * (kATiles * kWTileBytes + kTokTileBytes);   // 36 KiB | 20 KiB (MXFP4 down: 40 KiB)
@@ -379,11 +379,10 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
           const uint32_t dst = smem_u32(stage_base + s * C::kStageBytes);
           mbar_expect_tx(bar, bytes);
           if constexpr (kFp4) {
-            // one box of 256 code rows = two 8 KiB blocks that the pack step stored next to each other: W13 blocks are
-            // ordered (slab, channel tile, K-block, gate | up), W2 blocks (slab tile, K-block); their 512-byte scale
-            // atoms follow the same order, so the stage's two atoms are one 1 KiB copy
-            const int wy = kGateUp ? (((w.group * C::kNTiles + w.ntile) * C::kKBlocks + kb) * 2) * kTileRows
-                                   : ((w.group * C::kSlabTiles + w.ntile) * C::kKBlocks + kb) * kTileRows;
+            // one box of 256 code rows = two 8 KiB blocks that the pack step stored next to each other: blocks are
+            // ordered (slab, tile pair, K-block, tile of the pair) - W13 pairs a gate tile with its up tile, W2 pairs
+            // tiles 2p and 2p + 1; the 512-byte scale atoms follow the same order, so the stage's two are one 1 KiB copy
+            const int wy = (((w.group * C::kNTiles + w.ntile) * C::kKBlocks + kb) * 2) * kTileRows;
             tma_load_2d(dst, tm_w, bar, 0, wy, pol_w);
 #pragma unroll
             for (int j = 0; j < C::kKbPerLoad; ++j)
@@ -594,7 +593,8 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
           if (c < my_cols) {
             const int row = w.row0 + col_base + c;
             float* dst = row_ptr != nullptr ? row_ptr[row] : down + (size_t)row * kHidden;
-            dst[ntile * kTileRows + r] = acc[0][c];
+#pragma unroll
+            for (int tile = 0; tile < C::kATiles; ++tile) dst[(ntile * C::kATiles + tile) * kTileRows + r] = acc[tile][c];
           }
       }
       }   // sub tile
@@ -637,7 +637,7 @@ netra_moe_down_umma_sm100(const __grid_constant__ CUtensorMap tm_w2, const __gri
 // their scales reach the tensor core through TMEM; the token rows are E4M3 with their FP32 per-128 scales applied
 // in the promotion step, as in the FP8 kernels above.
 extern "C" __global__ void __launch_bounds__(kGemmThreads, 1)
-netra_moe_gate_up_mxfp4_sm100(const __grid_constant__ CUtensorMap tm_w13, const __grid_constant__ CUtensorMap tm_a32,
+netra_moe_gate_up_mxfp4_umma_sm100(const __grid_constant__ CUtensorMap tm_w13, const __grid_constant__ CUtensorMap tm_a32,
                               const __grid_constant__ CUtensorMap tm_a64, const __grid_constant__ CUtensorMap tm_a128,
                               const float* a_scale, const uint8_t* w13_scale_atoms, const int32_t* offsets, uint8_t* h_fp8,
                               float* h_scale, uint32_t num_groups, uint32_t* status) {
@@ -646,7 +646,7 @@ netra_moe_gate_up_mxfp4_sm100(const __grid_constant__ CUtensorMap tm_w13, const 
 }
 
 extern "C" __global__ void __launch_bounds__(kGemmThreads, 1)
-netra_moe_down_mxfp4_sm100(const __grid_constant__ CUtensorMap tm_w2, const __grid_constant__ CUtensorMap tm_h32,
+netra_moe_down_mxfp4_umma_sm100(const __grid_constant__ CUtensorMap tm_w2, const __grid_constant__ CUtensorMap tm_h32,
                            const __grid_constant__ CUtensorMap tm_h64, const __grid_constant__ CUtensorMap tm_h128,
                            const float* h_scale, const uint8_t* w2_scale_atoms, const int32_t* offsets, float* down,
                            uint32_t num_groups, uint32_t* status) {

@@ -72,9 +72,15 @@ __device__ __forceinline__ void tma_gather4_2d(uint32_t dst, const CUtensorMap* 
 __device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 3, 256;" ::: "memory"); }
 
 // kF16Out (down only): the output rows are FP16 partials staged in shared memory and written with one bulk copy per row
-template <bool kGateUp, bool kF16Out = false>
+// kFp4: the weight rows are MXFP4 (E2M1 codes + one UE8M0 scale per 32 along K) multiplied by
+//   tcgen05.mma.kind::mxf8f6f4.block_scale; the two weight tiles of a K-block are one 256-row box of code blocks that the
+//   pack step stored next to each other, and their two 512-byte scale atoms one 1 KiB copy.  The scales take TMEM columns
+//   (4 for the token rows' unit scales, 8 for the 256 weight rows), which leaves room for one 256-column accumulator
+//   stage instead of two: the MMAs of a K-block start when the previous K-block's partial sums have left TMEM.
+template <bool kGateUp, bool kF16Out = false, bool kFp4 = false>
 struct TmCfg {
   static constexpr int kTokTile = 128;                                  // token rows per item (UMMA M)
+  static constexpr int kLanes = kTokTile;
   static constexpr int kKBlocks = kGateUp ? kHiddenBlocks : kInterBlocks;   // 16 | 4
   static constexpr int kNTiles = kGateUp ? kInter / kTileRows : kHidden / (2 * kTileRows);   // items per slab and token tile: 4 | 8
   static constexpr int kSlabTiles = kGateUp ? 2 * kInter / kTileRows : kHidden / kTileRows;  // 8 | 16
@@ -83,7 +89,10 @@ struct TmCfg {
   static constexpr int kPrefetch = 4;                                   // K-blocks between an L2 prefetch and its load (kStages..kKBlocks)
   static constexpr int kStageBytes = kTokTile * kBlock + 2 * kWTileBytes;   // 48 KiB: tokens, weight tile 0, weight tile 1
   static constexpr int kAccCols = 256;
-  static constexpr int kAccStages = 2;
+  static constexpr int kAccStages = kFp4 ? 1 : 2;
+  static constexpr int kScaleCol = kAccStages * kAccCols;                   // MXFP4: token-row scales, then weight-row scales
+  static constexpr int kWTxBytes = kFp4 ? kWTileBytes / 2 : kWTileBytes;    // bytes one weight-tile copy reports
+  static constexpr int kAtomStageBytes = kFp4 ? 1024 : 0;                   // the two tiles' scale atoms
   static constexpr int kTmemCols = 512;
   static constexpr int kXsBytes = kTokTile * kKBlocks * 4;                  // 8 KiB | 2 KiB
   static constexpr int kWsBytes = kKBlocks * 4;                             // per weight tile
@@ -94,15 +103,23 @@ struct TmCfg {
   // FP16 output staging: one row of 128 halves per epilogue thread, rows 272 bytes apart (16 bytes of padding keep
   // the 16-byte shared-memory stores of a quarter warp on different banks)
   static constexpr int kOutRowBytes = 272;
-  static constexpr int kOutStageBytes = kF16Out ? kEpiGroups * kTokTile * kOutRowBytes : 0;
-  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kScaleSlots * kScaleSlotBytes + kOutStageBytes +
-                                    2 * kEpiGroups * kTokTile * 4 + 2 * 264 * 4 + kItemList * 16 + 512;
+  static constexpr int kOutStageBytes = kF16Out ? kEpiGroups * kLanes * kOutRowBytes : 0;
+  static constexpr int kSmemBytes = 1024 + kStages * (kStageBytes + kAtomStageBytes) + kScaleSlots * kScaleSlotBytes + kOutStageBytes +
+                                    2 * kEpiGroups * kLanes * 4 + 2 * 264 * 4 + kItemList * 16 + 512;
+  static_assert(!(kFp4 && kF16Out), "the MXFP4 down projection writes FP32 rows");
+  static_assert(kSmemBytes <= 232448, "exceeds the shared memory of one SM");
 };
+
+// kind::mxf8f6f4.block_scale, A = E4M3 token rows (unit scales), B = E2M1 weight rows, N = 256, M = 128, both K-major;
+// b_scale_byte selects the byte of the weight-scale columns that belongs to this instruction's 32-element K-group.
+__device__ __forceinline__ uint32_t make_idesc_mxfp4_b(uint32_t b_scale_byte) {
+  return (b_scale_byte << 4) | (5u << 10) | ((256u >> 3) << 17) | (1u << 23) | ((uint32_t)(128 >> 4) << 24);
+}
 
 // kGatherX (gate_up only): the item's token rows are not read from an expert-sorted copy but gathered from token order:
 // sorted position p holds token-order row tok_row_base + (perm[p] >> 3) (positions from tok_row_base on are token-order
 // rows already: the shared expert).  tm_x128 then is a map with a one-row box over the same buffer, x_scale its scales.
-template <bool kGateUp, bool kF16Out = false, bool kGatherX = false>
+template <bool kGateUp, bool kF16Out = false, bool kGatherX = false, bool kFp4 = false>
 __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, const CUtensorMap* tm_x128,
                                                    const float* __restrict__ x_scale, const float* __restrict__ w_scale,
                                                    const int32_t* __restrict__ offsets, uint8_t* __restrict__ h_fp8,
@@ -111,15 +128,19 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
                                                    uint32_t* status, const int32_t* __restrict__ perm = nullptr, uint32_t tok_row_base = 0) {
   static_assert(!(kGateUp && kF16Out), "FP16 partial rows are an output format of the down projection");
   static_assert(kGateUp || !kGatherX, "only the gate_up projection reads token rows");
-  using C = TmCfg<kGateUp, kF16Out>;
+  using C = TmCfg<kGateUp, kF16Out, kFp4>;
   static_assert(!kGatherX || C::kTokTile == 128, "a warp of 32 lanes gathers 4 rows each");
+  static_assert(!(kGatherX && kFp4), "the gathering producer exists for E4M3 weights only");
+  // MXFP4: w_scale points at the scale atoms (bytes), in the order of the code blocks
+  const uint8_t* w_scale_atoms = reinterpret_cast<const uint8_t*>(w_scale);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* stage_base = smem;
   uint8_t* scale_base = stage_base + C::kStages * C::kStageBytes;
-  uint8_t* out_stage = scale_base + C::kScaleSlots * C::kScaleSlotBytes;                            // [2 groups][128 rows][272 B] (FP16 output only)
+  uint8_t* atom_base = scale_base + C::kScaleSlots * C::kScaleSlotBytes;                            // [kStages][2 atoms] (MXFP4 only)
+  uint8_t* out_stage = atom_base + C::kStages * C::kAtomStageBytes;                                 // [2 groups][128 rows][272 B] (FP16 output only)
   uint32_t* red = reinterpret_cast<uint32_t*>(out_stage + C::kOutStageBytes);                       // [2 parities][2 groups][128 rows]
-  int* offs = reinterpret_cast<int*>(red + 2 * C::kEpiGroups * C::kTokTile);                  // [264]
+  int* offs = reinterpret_cast<int*>(red + 2 * C::kEpiGroups * C::kLanes);                    // [264]
   int* item_pre = offs + 264;                                                     // [264]
   int4* item_list = reinterpret_cast<int4*>(item_pre + 264);                      // [kItemList]
   uint64_t* bars = reinterpret_cast<uint64_t*>(item_list + C::kItemList);
@@ -175,6 +196,12 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_scale = tmem_base + (uint32_t)C::kScaleCol;
+  if constexpr (kFp4) {
+    // the token rows carry FP32 scales that the promotion step applies: inside the MMA they count as 2^0 (0x7f)
+    if (warp >= 4 && warp < 8) tmem_fill4(tmem_scale + ((uint32_t)((warp & 3) * 32) << 16), 0x7f7f7f7fu);
+    tc_fence_before();
+  }
   const int total_items = item_pre[groups];
   const int rounds = (total_items + (int)gridDim.x - 1) / (int)gridDim.x;
   const int stride = rounds > 0 ? (total_items + rounds - 1) / rounds : 1;
@@ -289,9 +316,11 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
           }
           const uint32_t sbar = smem_u32(&sfull_bar[slot]);
           const uint32_t sdst = smem_u32(scale_base + slot * C::kScaleSlotBytes);
-          mbar_expect_tx(sbar, C::kXsBytes + 2 * C::kWsBytes);
+          mbar_expect_tx(sbar, C::kXsBytes + (kFp4 ? 0 : 2 * C::kWsBytes));
           bulk_load(sdst, x_scale + (size_t)w.row0 * C::kKBlocks, C::kXsBytes, sbar);
-          if (kGateUp) {     // gate tile ntile, up tile 4 + ntile
+          if constexpr (kFp4) {
+            // the weight scales travel with the weight tiles, stage by stage
+          } else if (kGateUp) {     // gate tile ntile, up tile 4 + ntile
             const float* wsrc = w_scale + ((size_t)w.group * C::kSlabTiles + w.ntile) * C::kKBlocks;
             bulk_load(sdst + C::kXsBytes, wsrc, C::kWsBytes, sbar);
             bulk_load(sdst + C::kXsBytes + C::kWsBytes, wsrc + (kInter / kTileRows) * C::kKBlocks, C::kWsBytes, sbar);
@@ -303,7 +332,12 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
         const int tile0 = kGateUp ? w.ntile : 2 * w.ntile;
         const int tile_step = kGateUp ? kInter / kTileRows : 1;
         auto weight_xy = [&](const Item& wi, int t0, int kb, int& wx, int& wy0, int& wy1) {
-          if (w_tiled) {
+          if constexpr (kFp4) {
+            // code blocks in (slab, tile pair, K-block, tile of the pair) order: the item's two tiles are one 256-row box
+            wx = 0;
+            wy0 = (((wi.group * C::kNTiles + wi.ntile) * C::kKBlocks + kb) * 2) * kTileRows;
+            wy1 = wy0 + kTileRows;
+          } else if (w_tiled) {
             wx = 0;
             wy0 = ((wi.group * C::kSlabTiles + t0) * C::kKBlocks + kb) * kTileRows;
             wy1 = wy0 + tile_step * C::kKBlocks * kTileRows;
@@ -325,12 +359,12 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
             if (pk < C::kKBlocks) {
               weight_xy(w, tile0, pk, wx, wy0, wy1);
               tma_prefetch_2d(tm_w, wx, wy0);
-              tma_prefetch_2d(tm_w, wx, wy1);
+              if (!kFp4) tma_prefetch_2d(tm_w, wx, wy1);
               tma_prefetch_2d(tm_x128, pk * kBlock, w.row0);
             } else if (have_next) {
               weight_xy(wn, tile0_next, pk - C::kKBlocks, wx, wy0, wy1);
               tma_prefetch_2d(tm_w, wx, wy0);
-              tma_prefetch_2d(tm_w, wx, wy1);
+              if (!kFp4) tma_prefetch_2d(tm_w, wx, wy1);
               tma_prefetch_2d(tm_x128, (pk - C::kKBlocks) * kBlock, wn.row0);
             }
           }
@@ -340,12 +374,15 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
           }
           const uint32_t bar = smem_u32(&full_bar[s]);
           const uint32_t dst = smem_u32(stage_base + s * C::kStageBytes);
-          mbar_expect_tx(bar, C::kStageBytes);
+          mbar_expect_tx(bar, C::kTokTile * kBlock + 2 * C::kWTxBytes + C::kAtomStageBytes);
           int wx, wy0, wy1;
           weight_xy(w, tile0, kb, wx, wy0, wy1);
           tma_load_2d(dst, tm_x128, bar, kb * kBlock, w.row0, pol_x);
           tma_load_2d(dst + C::kTokTile * kBlock, tm_w, bar, wx, wy0, pol_w);
-          tma_load_2d(dst + C::kTokTile * kBlock + kWTileBytes, tm_w, bar, wx, wy1, pol_w);
+          if constexpr (kFp4)
+            bulk_load(smem_u32(atom_base + s * C::kAtomStageBytes), w_scale_atoms + (size_t)wy0 * 4, C::kAtomStageBytes, bar);
+          else
+            tma_load_2d(dst + C::kTokTile * kBlock + kWTileBytes, tm_w, bar, wx, wy1, pol_w);
         }
       }
     } else if ((warp == 1 || warp == 2) && lane == 0) {
@@ -354,14 +391,15 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
       // stage 1): while one is blocked feeding its four MMAs to the tensor pipe, the other has already passed its
       // barrier waits, so the pipe does not drain between K-blocks.  The K-blocks are independent (own shared-memory
       // stage, own TMEM stage) and a commit covers the MMAs of the thread that issues it.
+      // (MXFP4: one accumulator stage, so warp 1 issues every K-block and warp 2 has nothing to do)
       const uint32_t idesc = make_idesc(256);
       const uint32_t par = (uint32_t)(warp - 1);
-      bool ok = true;
+      bool ok = !(kFp4 && warp == 2);
       uint32_t it = 0;
       for (int item = first_item; ok && item < total_items; item += stride) {
         for (int kb = 0; kb < C::kKBlocks; ++kb, ++it) {
-          if ((it & 1u) != par) continue;
-          const int a = (int)par;
+          if (!kFp4 && (it & 1u) != par) continue;
+          const int a = kFp4 ? 0 : (int)par;
           if (!mbar_wait(smem_u32(&tempty_bar[a]), ((it / C::kAccStages) & 1) ^ 1, abort_flag)) {
             status[0] = kStatusMmaTimeout; *abort_flag = 1; ok = false; break;
           }
@@ -374,8 +412,20 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
           const uint64_t adesc = make_smem_desc(sa);                              // 128 token rows
           const uint64_t bdesc = make_smem_desc(sa + C::kTokTile * kBlock);       // 256 weight rows
           const uint32_t d0 = tmem_base + (uint32_t)(a * C::kAccCols);
+          if constexpr (kFp4) {
+            // the two tiles' scale atoms -> eight TMEM columns (weight row n: lane n % 32, column n / 32); copies and
+            // MMAs of one thread run in issue order, so the previous K-block's MMAs have read the columns by now
+            const uint32_t at = smem_u32(atom_base + s * C::kAtomStageBytes);
+            tmem_cp_32x128b_warpx4(tmem_scale + 4, make_scale_desc(at));
+            tmem_cp_32x128b_warpx4(tmem_scale + 8, make_scale_desc(at + 512));
 #pragma unroll
-          for (int k = 0; k < kBlock / 32; ++k) umma_f8(d0, adesc + 2 * k, bdesc + 2 * k, idesc, k > 0);
+            for (int k = 0; k < kBlock / 32; ++k)
+              umma_mxf8f6f4(d0, adesc + 2 * k, bdesc + 2 * k, make_idesc_mxfp4_b((uint32_t)k), tmem_scale,
+                            (tmem_scale + 4) | ((uint32_t)k << 30), k > 0);
+          } else {
+#pragma unroll
+            for (int k = 0; k < kBlock / 32; ++k) umma_f8(d0, adesc + 2 * k, bdesc + 2 * k, idesc, k > 0);
+          }
           umma_commit(smem_u32(&empty_bar[s]));
           umma_commit(smem_u32(&tfull_bar[a]));
         }
@@ -412,13 +462,22 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
         }
         if (!ok) continue;
         tc_fence_after();
+        if (kFp4 && quad * 32 >= w.m_valid) {
+          // no row of this item lives in this warp's TMEM lanes (the tail tile of an expert): nothing to promote, the
+          // warp only keeps step with the hand-off
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[a]));
+          continue;
+        }
         const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * C::kAccCols);
         uint32_t v[2][32];
         tmem_ld32_nowait(tbase + (uint32_t)seg_col0, v[0]);
         tmem_ld32_nowait(tbase + (uint32_t)(seg_col0 + 32), v[1]);
         const float x = xs_tile[r * C::kKBlocks + kb];
-        const float s0 = __fmul_rn(x, ws_tile[ws0 * C::kKBlocks + kb]);
-        const float s1 = __fmul_rn(x, ws_tile[ws1 * C::kKBlocks + kb]);
+        // MXFP4: the weight scales were applied inside the MMA
+        const float s0 = kFp4 ? x : __fmul_rn(x, ws_tile[ws0 * C::kKBlocks + kb]);
+        const float s1 = kFp4 ? x : __fmul_rn(x, ws_tile[ws1 * C::kKBlocks + kb]);
         tmem_ld_wait();
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
@@ -450,10 +509,10 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
           acc0[c] = bf16_round(__fmul_rn(silu, acc1[c]));
           amax = fmaxf(amax, fabsf(acc0[c]));
         }
-        uint32_t* my_red = red + (n_item & 1) * C::kEpiGroups * C::kTokTile;   // double-buffered by item parity: one barrier per item
-        my_red[wg * C::kTokTile + r] = __float_as_uint(amax);
+        uint32_t* my_red = red + (n_item & 1) * C::kEpiGroups * C::kLanes;     // double-buffered by item parity: one barrier per item
+        my_red[wg * C::kLanes + r] = __float_as_uint(amax);
         epilogue_barrier();
-        const float m = fmaxf(__uint_as_float(my_red[r]), __uint_as_float(my_red[C::kTokTile + r]));
+        const float m = fmaxf(__uint_as_float(my_red[r]), __uint_as_float(my_red[C::kLanes + r]));
         const float scale = fmaxf(m, amax_floor()) * inv448();
         const float inv = rcp_newton(scale);
         if (live) {
@@ -474,7 +533,7 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
         // FP16 partial rows (the reference's prefill contract, kernels/gfx950/templates/moe/prefill/fused_splitk2/down_partial.inc:435-458):
         // the thread packs its 128 columns into its own staging row and hands the row to the copy engine, which writes
         // 256 contiguous bytes - the thread itself never issues scattered global stores
-        uint8_t* my_row = out_stage + (size_t)(wg * C::kTokTile + r) * C::kOutRowBytes;
+        uint8_t* my_row = out_stage + (size_t)(wg * C::kLanes + r) * C::kOutRowBytes;
         asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");      // the previous item's copy has read this row
 #pragma unroll
         for (int q = 0; q < 16; ++q) {
@@ -556,9 +615,32 @@ netra_moe_down_tokmajor_f16_sm100(const __grid_constant__ CUtensorMap tm_w2, con
                                   nullptr, num_groups, w_tiled, status);
 }
 
+// The two projections on MXFP4 expert weights (E2M1 codes, one UE8M0 scale per 32 K-elements; semantics of
+// kernels/gfx1151/mxfp4/prefill/mxfp4_prefill_gate_wmma_gfx1151.s:3-8, mxfp4_prefill_up_silu_wmma_gfx1151.s:3-8 and
+// mxfp4_prefill_down_wmma_gfx1151.s:3-5; decode call sequence runtime/gfx1151/mxfp4/decode/runtime.h:10-47): the weights
+// stay four-bit in memory (tm_w*: code blocks of 128 rows x 64 bytes written by netra_moe_mxfp4_pack_sm100, fetched two at
+// a time) and their scales reach the tensor core through TMEM.  For calls whose experts hold many rows; the swap-AB
+// forms (umma_kernels.cu) serve decode sizes.
+extern "C" __global__ void __launch_bounds__(kTmThreads, 1)
+netra_moe_gate_up_mxfp4_tokmajor_sm100(const __grid_constant__ CUtensorMap tm_w13, const __grid_constant__ CUtensorMap tm_a128,
+                              const float* a_scale, const uint8_t* w13_scale_atoms, const int32_t* offsets, uint8_t* h_fp8,
+                              float* h_scale, uint32_t num_groups, uint32_t* status) {
+  tokmajor_gemm_body<true, false, false, true>(&tm_w13, &tm_a128, a_scale, reinterpret_cast<const float*>(w13_scale_atoms), offsets, h_fp8,
+                                               h_scale, nullptr, nullptr, num_groups, 1u, status);
+}
+
+extern "C" __global__ void __launch_bounds__(kTmThreads, 1)
+netra_moe_down_mxfp4_tokmajor_sm100(const __grid_constant__ CUtensorMap tm_w2, const __grid_constant__ CUtensorMap tm_h128,
+                           const float* h_scale, const uint8_t* w2_scale_atoms, const int32_t* offsets, float* down,
+                           uint32_t num_groups, uint32_t* status) {
+  tokmajor_gemm_body<false, false, false, true>(&tm_w2, &tm_h128, h_scale, reinterpret_cast<const float*>(w2_scale_atoms), offsets, nullptr,
+                                                nullptr, down, nullptr, num_groups, 1u, status);
+}
+
+int gate_up_mxfp4_tokmajor_smem_bytes() { return TmCfg<true, false, true>::kSmemBytes; }
+int down_mxfp4_tokmajor_smem_bytes() { return TmCfg<false, false, true>::kSmemBytes; }
 int gate_up_tokmajor_smem_bytes() { return TmCfg<true>::kSmemBytes; }
 int down_tokmajor_smem_bytes() { return TmCfg<false>::kSmemBytes; }
 int down_tokmajor_f16_smem_bytes() { return TmCfg<false, true>::kSmemBytes; }
-static_assert(TmCfg<false, true>::kSmemBytes <= 232448, "the FP16-output down kernel exceeds the shared memory of one SM");
 
 }  // namespace netra

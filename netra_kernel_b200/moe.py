@@ -82,7 +82,7 @@ class RoutedMoELayer:
         if self.mxfp4:
             self.tiled = True
             if not pretiled:
-                (w13, w13_scale), (w2, w2_scale) = pack_mxfp4(w13, w13_scale, paired_half_rows=INTER), pack_mxfp4(w2, w2_scale)
+                (w13, w13_scale), (w2, w2_scale) = pack_mxfp4(w13, w13_scale, paired_half_rows=INTER), pack_mxfp4(w2, w2_scale, paired_half_rows=128)
         elif pretiled:
             self.tiled = True
         elif self.tiled:
@@ -269,10 +269,10 @@ class RoutedMoELayer:
             pass
 
 
-def pack_mxfp4(packed: torch.Tensor, scales: torch.Tensor, paired_half_rows: int = 0):
+def pack_mxfp4(packed: torch.Tensor, scales: torch.Tensor, paired_half_rows: int = 128):
     """MXFP4 slabs (packed E2M1 ``[G, N, K/2]`` u8, E8M0 scales ``[G, N, K/32]`` u8, on the GPU) -> the operand layout of
     the native MXFP4 kernels, same shapes and sizes: code blocks (8 KiB per 128-row tile and K-block) and scale atoms
-    (512 bytes per tile and K-block).  ``paired_half_rows``: 0 for W2 (blocks in (tile, K-block) order), 512 for W13
+    (512 bytes per tile and K-block).  ``paired_half_rows``: 128 for W2 (tiles 2p and 2p + 1 side by side), 512 for W13
     (a gate tile's block next to its up tile's).  ``netra_moe_mxfp4_pack_launch``."""
     _require_cuda(packed, scales)
     g, n, half_k = packed.shape

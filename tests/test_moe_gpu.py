@@ -339,18 +339,18 @@ def test_native_mxfp4_layer_streams_four_bit_weights(expert_weights):
     p2 = torch.stack([q2[e % 3][0] for e in range(slabs)]).cuda()
     s2 = torch.stack([q2[e % 3][1] for e in range(slabs)]).cuda()
     # the load-time re-ordering, against its definition: W13 blocks in (slab, channel tile, K-block, gate | up) order,
-    # W2 blocks in (row tile, K-block) order; inside a scale atom row r sits at 16 * (r % 32) + 4 * (r / 32)
+    # W2 blocks in (tile pair, K-block, tile of the pair) order; inside a scale atom row r sits at 16 * (r % 32) + 4 * (r / 32)
     codes, atoms = pack_mxfp4(p13[:2], s13[:2], paired_half_rows=512)
-    codes2, atoms2 = pack_mxfp4(p2[:1], s2[:1])
+    codes2, atoms2 = pack_mxfp4(p2[:1], s2[:1], paired_half_rows=128)
     torch.cuda.synchronize()
     src_c = p13[:2].cpu().numpy().reshape(2, 2, 4, 128, 16, 64)                    # [slab, half, tile, r, kb, 64]
     assert np.array_equal(codes.cpu().numpy().reshape(2, 4, 16, 2, 128, 64), src_c.transpose(0, 2, 4, 1, 3, 5))
     src_s = s13[:2].cpu().numpy().reshape(2, 2, 4, 4, 32, 16, 4)                   # [slab, half, tile, r / 32, r % 32, kb, 4]
     assert np.array_equal(atoms.cpu().numpy().reshape(2, 4, 16, 2, 32, 4, 4), src_s.transpose(0, 2, 5, 1, 4, 3, 6))
-    src_c2 = p2[:1].cpu().numpy().reshape(16, 128, 4, 64)                          # [tile, r, kb, 64]
-    assert np.array_equal(codes2.cpu().numpy().reshape(16, 4, 128, 64), src_c2.transpose(0, 2, 1, 3))
-    src_s2 = s2[:1].cpu().numpy().reshape(16, 4, 32, 4, 4)                         # [tile, r / 32, r % 32, kb, 4]
-    assert np.array_equal(atoms2.cpu().numpy().reshape(16, 4, 32, 4, 4), src_s2.transpose(0, 3, 2, 1, 4))
+    src_c2 = p2[:1].cpu().numpy().reshape(8, 2, 128, 4, 64)                        # [tile pair, tile of the pair, r, kb, 64]
+    assert np.array_equal(codes2.cpu().numpy().reshape(8, 4, 2, 128, 64), src_c2.transpose(0, 3, 1, 2, 4))
+    src_s2 = s2[:1].cpu().numpy().reshape(8, 2, 4, 32, 4, 4)                       # [pair, tile, r / 32, r % 32, kb, 4]
+    assert np.array_equal(atoms2.cpu().numpy().reshape(8, 4, 2, 32, 4, 4), src_s2.transpose(0, 4, 1, 3, 2, 5))
     w13, w13_s, bad13 = expand_mxfp4(p13, s13)
     w2, w2_s, bad2 = expand_mxfp4(p2, s2)
     assert bad13 == 0 and bad2 == 0
