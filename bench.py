@@ -342,8 +342,10 @@ def make_engine_session(args, tokens, device_id, layer, hidden, out, model="rout
     if args.row_major_weights or not layer.tiled:
         return None
     root = KernelLibrary.discover().root
+    quantization = json.loads((root / "manifests" / "sm_100a" / "models" / model).read_text())["quantization"]
     profile = next((p for p in load_profile_registry(root, "sm_100a", 1)
-                    if p.guard("m").is_exact and p.guard("m").minimum == tokens and all(k != "route_rows" for k, _ in p.guards)), None)
+                    if p.quantization == quantization and p.guard("m").is_exact and p.guard("m").minimum == tokens
+                    and all(k != "route_rows" for k, _ in p.guards)), None)
     if profile is None:
         return None
     directory = tempfile.mkdtemp(prefix=f"netra_engine_r{device_id}_")
@@ -541,7 +543,7 @@ def prefill_object(name, layer, hidden_cpu, steps, warmup, dev, stream, sync, ex
     return obj
 
 
-def mxfp4_decode_object(layer, hidden_cpu, steps, warmup, dev, stream, sync, fp8_ms_per_step) -> dict:
+def mxfp4_decode_object(layer, hidden_cpu, steps, warmup, dev, stream, sync, fp8_ms_per_step, engine=None) -> dict:
     """Decode (T=256) on MXFP4 expert weights through the native block-scaled kernels: the weight stream is the E2M1 codes
     and E8M0 scale bytes, 0.53 of the FP8 layer's bytes; HBM roofline of the gate_up kernel and of the whole call."""
     import torch
@@ -554,12 +556,26 @@ def mxfp4_decode_object(layer, hidden_cpu, steps, warmup, dev, stream, sync, fp8
             layer(hidden, out=out)
         stream.synchronize()
         layer.check_status()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            layer(hidden, out=out)
-        ms, spread = time_replays(graph.replay, steps, warmup, stream, sync, spread=True)
+        session = engine(hidden, out) if engine is not None else None
+        if session is not None:
+            session.prepare(stream.cuda_stream)
+            replay = lambda: session.launch(stream.cuda_stream)
+            api = "netra_engine_launch (engine runtime ABI on the MXFP4 model manifest, captured CUDA graph)"
+            want = out.clone()
+            out.zero_()
+            replay()
+            stream.synchronize()
+            if not torch.equal(out, want):
+                raise SystemExit("bench: mxfp4_decode_t256: the engine's result differs from the fused-layer call on the same operands")
+        else:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                layer(hidden, out=out)
+            replay = graph.replay
+            api = "netra_moe_layer_launch (fused-layer ABI, weights_tiled = 2), captured CUDA graph"
+        ms, spread = time_replays(replay, steps, warmup, stream, sync, spread=True)
         stage_ms = time_stages(layer, hidden, out, steps, warmup, stream, sync)
-        e2e_ms, serial_ms, host_api, _ = time_e2e(graph.replay, hidden, out, hidden_cpu, steps, warmup, stream, sync)
+        e2e_ms, serial_ms, host_api, _ = time_e2e(replay, hidden, out, hidden_cpu, steps, warmup, stream, sync)
         stream.synchronize()
     layer.check_status()
     inter = layer.intermediates(tokens)
@@ -569,14 +585,14 @@ def mxfp4_decode_object(layer, hidden_cpu, steps, warmup, dev, stream, sync, fp8
     down_bytes = (hit + 1) * (2048 * 512 // 2 + 2048 * 512 // 32)
     layer_bytes = synth.workload_bytes_decode(tokens, hit, mxfp4=True)
     gu_s, dn_s = stage_ms[6] / 1e3, stage_ms[7] / 1e3
-    return {
+    obj = {
         "workload": "mxfp4_decode_t256", "tokens": tokens, "experts_hit": hit,
         "expert_weights": "mxfp4 (E2M1 codes + one E8M0 scale per 32 along K), kept four-bit in memory: "
                           "tcgen05.mma.kind::mxf8f6f4.block_scale with the scales in TMEM",
         "ms_per_step": ms, "tokens_per_s": tokens / (ms / 1e3), "steps": steps, "warmup": warmup, "step_ms_spread": spread,
         "speedup_over_fp8_weights": fp8_ms_per_step / ms,
         "launch": "CUDA graph replay of the layer's %d kernels" % layer.launches_per_call(tokens),
-        "api": "netra_moe_layer_launch (fused-layer ABI, weights_tiled = 2), captured CUDA graph",
+        "api": api,
         "l2": "inputs larger than L2: every step streams %.1f MB of expert weights (L2 is 126 MB)" % (layer_bytes / 1e6),
         "roofline": {"bound": "hbm", "kernel": "netra_moe_gate_up_mxfp4_umma_sm100", "achieved": gate_up_bytes / gu_s / 1e9, "peak": peak,
                      "unit": "GB/s", "frac": gate_up_bytes / gu_s / 1e9 / peak, "peak_source": peak_kind,
@@ -588,6 +604,54 @@ def mxfp4_decode_object(layer, hidden_cpu, steps, warmup, dev, stream, sync, fp8
         "kernels_ms": {n: round(v, 5) for n, v in zip(layer.STAGES, stage_ms)},
         "e2e": e2e_object(tokens, tokens, e2e_ms, serial_ms, host_api),
     }
+    if session is not None:
+        session.close()
+    return obj
+
+
+def decode_bridges_object(layer, dev, stream, sync) -> dict:
+    """The reference's decode boundary at M = 1: its three per-kernel bridges (gate_up, SiLU*up + quantise, down + reduce),
+    each timed alone over launches that rotate through 64 different expert selections (64 x 28 MB of slabs, so the
+    weights come from HBM, as in the reference's in-trace figure), and the fused layer call at one token beside them."""
+    import torch
+    from netra_kernel_b200 import moe as M
+    w13, w13_s, w2, w2_s = layer._keep[1], layer._keep[2], layer._keep[3], layer._keep[4]
+    if layer.tiled:
+        raise SystemExit("bench: the bridges take row-major slabs")
+    g = torch.Generator().manual_seed(77)
+    sets = 64
+    hidden = torch.randn(1, 2048, generator=g).to(torch.bfloat16).to(dev)
+    a_fp8 = torch.randint(0, 120, (1, 2048), generator=g, dtype=torch.uint8).to(dev)
+    a_s = (torch.rand(1, 16, generator=g) * 0.01 + 0.001).to(dev)
+    ids = [torch.cat([torch.randperm(256, generator=g)[:8], torch.tensor([256])]).to(torch.int32).view(1, 9).to(dev) for _ in range(sets)]
+    w9 = torch.full((1, 9), 1.0 / 9, dtype=torch.float32, device=dev)
+    out = {}
+    with torch.cuda.stream(stream):
+        gu = M.bridge_gate_up(a_fp8, a_s, w13, w13_s, ids[0])
+        hq, hs = M.bridge_silu_mul_quant(gu)
+        calls = {
+            "gate_up": lambda i: M.bridge_gate_up(a_fp8, a_s, w13, w13_s, ids[i % sets]),
+            "silu_mul_quant": lambda i: M.bridge_silu_mul_quant(gu),
+            "down_reduce": lambda i: M.bridge_down_reduce(hq, hs, w2, w2_s, w9, ids[i % sets]),
+        }
+        for name, fn in calls.items():
+            for i in range(8):
+                fn(i)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            sync.barrier()
+            e0.record(stream)
+            for i in range(128):
+                fn(i)
+            e1.record(stream)
+            stream.synchronize()
+            out[name] = e0.elapsed_time(e1) / 128 * 1e3
+    return {"workload": "decode_bridges_m1", "rows": 1,
+            "api": "netra_qwen36_moe_gate_up_launch / netra_qwen36_moe_silu_mul_quant_launch / netra_qwen36_moe_down_reduce_launch",
+            "us_per_launch": {k: round(v, 2) for k, v in out.items()},
+            "timing": "128 back-to-back launches per kernel between two CUDA events (launch overhead included), expert "
+                      "selections rotating through 64 sets so that the slabs are read from HBM",
+            "reference_published": {"us_per_launch": {"gate_up": 13.486, "silu_mul_quant": 2.846, "down_reduce": 24.773},
+                                    "hardware": "MI350X, inside a 40-layer decode trace", "comparable": False}}
 
 
 def make_stack_single(dev, layers, tokens, stream):
@@ -824,7 +888,10 @@ def run_ours(args) -> None:
             del p13, s13, p2, s2
             hd_cpu, _, _ = synth.make_activations(256, None, seed=0)
             nat_decode = RoutedMoELayer(layer._keep[0], *nat._keep[1:5], 256, None, mxfp4=True, pretiled=True)
-            extras["mxfp4_decode_t256"] = mxfp4_decode_object(nat_decode, hd_cpu, steps, warmup, dev, stream, sync, ms_per_step)
+            engine_mx = ((lambda hid, res: make_engine_session(args, 256, local_rank, nat_decode, hid, res, model="routed-moe-layer-mxfp4.json"))
+                         if args.api == "engine" else None)
+            extras["mxfp4_decode_t256"] = mxfp4_decode_object(nat_decode, hd_cpu, steps, warmup, dev, stream, sync, ms_per_step,
+                                                              engine=engine_mx)
             nat_decode.close()
             with torch.cuda.stream(stream):
                 hd, od = h8.to(dev), torch.empty(8192, 2048, dtype=torch.bfloat16, device=dev)
@@ -846,6 +913,22 @@ def run_ours(args) -> None:
                 "kernels_ms": {n: round(v, 5) for n, v in zip(nat.STAGES, st_nat)}}
             nat.close()
             del nat, nat_decode, gn, hd, od
+            torch.cuda.empty_cache()
+
+            # the reference's own decode boundary: the three per-kernel bridges at one row (row-major slabs)
+            rm = RoutedMoELayer(layer._keep[0], *(t.to(dev) for t in weights), 16, None, tiled=False)
+            extras["decode_bridges_m1"] = decode_bridges_object(rm, dev, stream, sync)
+            with torch.cuda.stream(stream):
+                h1, o1 = hidden[:1].contiguous(), torch.empty(1, 2048, dtype=torch.bfloat16, device=dev)
+                for _ in range(3):
+                    rm(h1, out=o1)
+                g1 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g1, stream=stream):
+                    rm(h1, out=o1)
+                ms1, _ = time_replays(g1.replay, 50, warmup, stream, sync)
+            extras["decode_bridges_m1"]["fused_layer_one_token_us_weights_in_l2"] = round(ms1 * 1e3, 2)
+            rm.close()
+            del rm, g1
             torch.cuda.empty_cache()
 
             # config 4 on one GPU: the 40-layer stack, 16,384 tokens per step, all 256 experts local

@@ -104,6 +104,8 @@ def _argument_records(planned: PlannedOperation, plan: Plan, offsets: dict[str, 
                     raise ValidationError(f"tensor_map argument {arg.name} cannot be optional")
                 record["tensor_map"] = {"rows": evaluate(arg.map["rows"], env), "row_bytes": evaluate(arg.map["row_bytes"], env),
                                         "box_rows": evaluate(arg.map["box_rows"], env), "box_bytes": 128, "swizzle": "128B"}
+                if arg.map.get("element", "u8") != "u8":      # "e2m1": four-bit codes, 64 bytes per 128-element row in memory
+                    record["tensor_map"]["element"] = str(arg.map["element"])
                 span = record["tensor_map"]["rows"] * record["tensor_map"]["row_bytes"]
                 if span > tensor.bytes:
                     raise ValidationError(f"tensor map {arg.name} covers {span} bytes but tensor {tensor.name} has {tensor.bytes}")
@@ -176,10 +178,17 @@ def compile_engine(model_path: Path | str, profile_name: str, output: Path | str
     # declarative weight / scale layout plan (layouts.py); "steps" keeps the flat list of device repacks the runtime helper runs
     layout_plan = moe_layer_layout_plan(model["options"]["weight_layout"], split_gate_up=bool(model["options"].get("split_gate_up", False)),
                                         scale_dtype=str(model["options"].get("checkpoint_scale_dtype", "fp32")))
-    layout_plan["steps"] = [
-        {"tensor": name, "from": "row_major[group,n,k]", "to": "tiles128x128[group,n/128,k/128,128,128]",
-         "kernel": "netra_moe_repack_tiles_sm100", "entry_point": "netra_moe_repack_tiles_launch", "scales": "unchanged"}
-        for name in ("w13", "w2")] if opts["w_tiled"] else []
+    if model["options"]["weight_layout"] == "mxfp4_paired_blocks":
+        layout_plan["steps"] = [
+            {"tensor": name, "scale_tensor": name + "_scale", "from": "row_major[group,n,k/2] e2m1x2 + [group,n,k/32] ue8m0",
+             "to": "blocks128x64B[pair,k/128,2,128,64] + scale_atoms512B[pair,k/128,2]", "kernel": "netra_moe_mxfp4_pack_sm100",
+             "entry_point": "netra_moe_mxfp4_pack_launch", "paired_half_rows": half}
+            for name, half in (("w13", 512), ("w2", 128))]
+    else:
+        layout_plan["steps"] = [
+            {"tensor": name, "from": "row_major[group,n,k]", "to": "tiles128x128[group,n/128,k/128,128,128]",
+             "kernel": "netra_moe_repack_tiles_sm100", "entry_point": "netra_moe_repack_tiles_launch", "scales": "unchanged"}
+            for name in ("w13", "w2")] if opts["w_tiled"] else []
     selected = [{"operation": p.operation.name, "tactic": p.tactic.name, "contract_id": p.contract.stable_id}
                 for p in plan.operations if p.tactic is not None]
     identity = {

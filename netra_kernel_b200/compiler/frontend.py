@@ -44,8 +44,10 @@ def load_model(path: Path) -> dict[str, Any]:
     options.setdefault("router_bias", False)
     options.setdefault("shared_weight", False)
     options.setdefault("weight_layout", "tiles128")
-    if options["weight_layout"] not in ("tiles128", "row_major"):
-        raise ValidationError(f"{path}: weight_layout must be tiles128 or row_major")
+    if options["weight_layout"] not in ("tiles128", "row_major", "mxfp4_paired_blocks"):
+        raise ValidationError(f"{path}: weight_layout must be tiles128, row_major or mxfp4_paired_blocks")
+    if (options["weight_layout"] == "mxfp4_paired_blocks") != (doc.get("quantization") == "mxfp4_block32"):
+        raise ValidationError(f"{path}: the mxfp4_paired_blocks layout and the mxfp4_block32 quantization go together")
     # rows between the down projection and the combine where the token-major kernels run: "f32" (decode contract) or
     # "f16" (the reference's prefill contract: FP16 partial rows, kernels/gfx950/templates/moe/prefill/route_reduce_splitk2_f16.inc)
     options.setdefault("prefill_partials", "f32")
@@ -82,6 +84,9 @@ def options_for(model: dict[str, Any]) -> dict[str, int]:
             "w_tiled": 1 if model["options"]["weight_layout"] == "tiles128" else 0}
 
 
+MXFP4 = "mxfp4_block32"      # model quantization: E2M1 expert weights with one UE8M0 scale per 32 along K; FP8 activations
+
+
 def routed_moe_layer_graph(model: dict[str, Any], profile: ShapeProfile) -> Graph:
     c = model["constants"]
     opt = model["options"]
@@ -92,14 +97,28 @@ def routed_moe_layer_graph(model: dict[str, Any], profile: ShapeProfile) -> Grap
     kb_h, kb_i = hidden // c["scale_block"], inter // c["scale_block"]
     segmented = m > SORT_SINGLE_BLOCK_MAX_ROWS
 
+    mxfp4 = model.get("quantization") == MXFP4
+    if mxfp4 and opt["weight_layout"] != "mxfp4_paired_blocks":
+        raise ValidationError("an MXFP4 model streams its weights in the mxfp4_paired_blocks layout")
+    if mxfp4 and opt.get("prefill_partials", "f32") != "f32":
+        raise ValidationError("FP16 partial rows are an output format of the E4M3 kernels")
+    if mxfp4:      # codes two per byte, scales one byte per 32 weights; both re-ordered by the pack step (layout plan)
+        expert_tensors = [
+            Tensor("w13", "e2m1x2", (groups, 2 * inter, hidden // 2), "weight", groups * 2 * inter * hidden // 2),
+            Tensor("w13_scale", "ue8m0", (groups, 2 * inter, hidden // 32), "weight", groups * 2 * inter * hidden // 32),
+            Tensor("w2", "e2m1x2", (groups, hidden, inter // 2), "weight", groups * hidden * inter // 2),
+            Tensor("w2_scale", "ue8m0", (groups, hidden, inter // 32), "weight", groups * hidden * inter // 32)]
+    else:
+        expert_tensors = [
+            Tensor("w13", "fp8_e4m3", (groups, 2 * inter, hidden), "weight", groups * 2 * inter * hidden),
+            Tensor("w13_scale", "fp32", (groups, 2 * inter // c["scale_block"], kb_h), "weight", groups * (2 * inter // c["scale_block"]) * kb_h * 4),
+            Tensor("w2", "fp8_e4m3", (groups, hidden, inter), "weight", groups * hidden * inter),
+            Tensor("w2_scale", "fp32", (groups, kb_h, kb_i), "weight", groups * kb_h * kb_i * 4)]
     tensors = [
         Tensor("hidden", "bf16", (m, hidden), "input", m * hidden * 2),
         Tensor("output", "bf16", (m, hidden), "output", m * hidden * 2),
         Tensor("router_weight", "bf16", (experts, hidden), "weight", experts * hidden * 2),
-        Tensor("w13", "fp8_e4m3", (groups, 2 * inter, hidden), "weight", groups * 2 * inter * hidden),
-        Tensor("w13_scale", "fp32", (groups, 2 * inter // c["scale_block"], kb_h), "weight", groups * (2 * inter // c["scale_block"]) * kb_h * 4),
-        Tensor("w2", "fp8_e4m3", (groups, hidden, inter), "weight", groups * hidden * inter),
-        Tensor("w2_scale", "fp32", (groups, kb_h, kb_i), "weight", groups * kb_h * kb_i * 4),
+        *expert_tensors,
         Tensor("logits", "bf16", (m, experts), "workspace", m * experts * 2),
         Tensor("topk_ids", "int32", (m, slots), "workspace", m * slots * 4),
         Tensor("topk_weights", "fp32", (m, slots), "workspace", m * slots * 4),
@@ -132,8 +151,13 @@ def routed_moe_layer_graph(model: dict[str, Any], profile: ShapeProfile) -> Grap
 
     # grouped-GEMM form: token-major (128 token rows x 256 weight rows per MMA) from an average of 32 rows per routed expert
     token_major = m * c["top_k"] >= 32 * experts
-    form = ("token_major" if token_major else "swap_ab") + ".sorted_rows." + ("tiles128" if opt["weight_layout"] == "tiles128" else "row_major")
+    form = ("token_major" if token_major else "swap_ab") + ".sorted_rows." + (
+        "mxfp4_paired_blocks" if mxfp4 else "tiles128" if opt["weight_layout"] == "tiles128" else "row_major")
     maps = "tmap2" if token_major else "tmap4"
+    # the MXFP4 kernels take no weight-layout flag (one u32 fewer) and apply the weight scales inside the MMA
+    gemm_abi = ("{}_grouped." + maps + "_ptr{}_u32_ptr.mxfp4.v1") if mxfp4 else ("{}_grouped." + maps + "_ptr{}_u32x2_ptr.v1")
+    gemm_dtypes = "fp8e4m3_e2m1_to_{}" if mxfp4 else "fp8e4m3_fp8e4m3_to_{}"
+    gemm_quant = "mxfp4_w1x32_ue8m0.a_fp8_e4m3_1x128_amax448" if mxfp4 else "fp8_e4m3_w128x128_a1x128_amax448"
     f16_rows = token_major and opt["prefill_partials"] == "f16"   # the rows keep the down_f32 buffer (half of it is used)
 
     def op(name, family, operation, inputs, outputs, constants, sem):
@@ -185,12 +209,11 @@ def routed_moe_layer_graph(model: dict[str, Any], profile: ShapeProfile) -> Grap
                      "sorted_rows_first.token_rows_after_pairs", "copy.v1")),
         op("gate_up", "moe_fp8_grouped_gemm", "gate_up_silu_requant", ["a_fp8", "a_scale", "w13", "w13_scale", "offsets"],
            ["h_fp8", "h_scale", "status"], gemm_constants,
-           semantics(f"gate_up_grouped.{maps}_ptr5_u32x2_ptr.v1", "fp8e4m3_fp8e4m3_to_fp8e4m3_f32", "fp8_e4m3_w128x128_a1x128_amax448",
+           semantics(gemm_abi.format("gate_up", 5), gemm_dtypes.format("fp8e4m3_f32"), gemm_quant,
                      form, "kblock_fma_ascending.silu_fp32.bf16_round_then_amax.v1")),
         op("down", "moe_fp8_grouped_gemm", "down_projection", ["h_fp8", "h_scale", "w2", "w2_scale", "offsets"],
            ["down_f32", "status"], gemm_constants,
-           semantics(f"down_grouped.{maps}_ptr4_u32x2_ptr.v1", "fp8e4m3_fp8e4m3_to_f16" if f16_rows else "fp8e4m3_fp8e4m3_to_f32",
-                     "fp8_e4m3_w128x128_a1x128_amax448", form,
+           semantics(gemm_abi.format("down", 4), gemm_dtypes.format("f16" if f16_rows else "f32"), gemm_quant, form,
                      "kblock_fma_ascending.f16_partial_rows.v1" if f16_rows else "kblock_fma_ascending.v1")),
         op("combine", "moe_combine", "weighted_slot_combine", ["down_f32", "topk_weights", "inv_perm"], ["output"],
            {"hidden": hidden, "top_k": c["top_k"]},

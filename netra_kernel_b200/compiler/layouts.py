@@ -16,6 +16,8 @@ from .types import ValidationError
 ROW_MAJOR = "checkpoint_row_major_fp8_block128"
 SPLIT_GATE_UP = "checkpoint_split_gate_up_row_major_fp8_block128"     # gate_proj and up_proj as two tensors
 TILES128 = "tiles128x128_fp8_block128"
+MXFP4_ROW_MAJOR = "checkpoint_row_major_mxfp4_block32"               # e2m1 codes [n, k/2] + ue8m0 scales [n, k/32]
+MXFP4_PAIRED_BLOCKS = "paired_blocks128x64B_mxfp4_block32"           # 8 KiB code blocks + 512-byte scale atoms, tile pairs adjacent
 TILE = 128
 
 
@@ -66,6 +68,12 @@ _TILE_STEP = RepackStep(ROW_MAJOR, TILES128, "tile_128x128", (("tile_rows", TILE
                         "netra_moe_repack_tiles_launch")
 
 
+def _mxfp4_pack_step(paired_half_rows: int) -> RepackStep:
+    return RepackStep(MXFP4_ROW_MAJOR, MXFP4_PAIRED_BLOCKS, "mxfp4_pair_blocks",
+                      (("block_rows", TILE), ("block_k", TILE), ("paired_half_rows", paired_half_rows), ("scale_atom_bytes", 512)),
+                      "netra_moe_mxfp4_pack_launch")
+
+
 def plan_weight_layout(tensor: str, checkpoint_layout: str, kernel_layout: str, *,
                        checkpoint_tensors: tuple[str, ...] = ()) -> LayoutBinding:
     """One explicit chain of steps from the checkpoint's layout to the kernel's; unknown pairs are refused."""
@@ -81,6 +89,9 @@ def plan_weight_layout(tensor: str, checkpoint_layout: str, kernel_layout: str, 
     if current == ROW_MAJOR and kernel_layout == TILES128:
         steps.append(_TILE_STEP)
         current = TILES128
+    if current == MXFP4_ROW_MAJOR and kernel_layout == MXFP4_PAIRED_BLOCKS:
+        steps.append(_mxfp4_pack_step(512 if tensor == "w13" else TILE))
+        current = MXFP4_PAIRED_BLOCKS
     if current != kernel_layout:
         raise ValidationError(f"unsupported weight layout transform: {checkpoint_layout} -> {kernel_layout}")
     return LayoutBinding(tensor, checkpoint_layout, kernel_layout, tuple(steps), checkpoint_tensors)
@@ -93,6 +104,9 @@ def plan_scale_layout(tensor: str, checkpoint_tensors: tuple[str, ...], *, check
         raise ValidationError("a scale layout needs its checkpoint source tensors")
     if len(block) != 2 or min(block) <= 0:
         raise ValidationError("a scale layout needs a positive two-dimensional block")
+    if checkpoint_dtype == kernel_dtype == "ue8m0":
+        # MXFP4: one byte per 32 weights along K; the pack step of the weight tensor re-orders the bytes into 512-byte atoms
+        return ScaleBinding(tensor, tuple(checkpoint_tensors), "ue8m0", "ue8m0", tuple(block), ("reorder_with_weight_blocks",))
     if checkpoint_dtype not in ("bf16", "fp32") or kernel_dtype not in ("bf16", "fp32"):
         raise ValidationError("unsupported checkpoint or kernel scale dtype")
     steps = []
@@ -128,6 +142,23 @@ def widen_bf16_to_fp32(bits: np.ndarray) -> np.ndarray:
     return (bits.astype(np.uint32) << 16).view(np.float32)
 
 
+def mxfp4_pair_blocks(codes: np.ndarray, scales: np.ndarray, paired_half_rows: int) -> tuple[np.ndarray, np.ndarray]:
+    """CPU statement of ``netra_moe_mxfp4_pack_launch``: uint8 codes ``[rows, k/2]`` and scale bytes ``[rows, k/32]`` ->
+    code blocks and scale atoms in (group, tile within the half, K-block, half) order; inside an atom row r's four
+    bytes sit at ``16 (r % 32) + 4 (r / 32)``.  Shapes are kept; only the byte order changes."""
+    rows, half_k = codes.shape
+    k = 2 * half_k
+    h = paired_half_rows // TILE
+    if codes.dtype != np.uint8 or scales.dtype != np.uint8 or scales.shape != (rows, k // 32):
+        raise ValidationError("mxfp4_pair_blocks takes uint8 codes [rows, k/2] and scales [rows, k/32]")
+    if paired_half_rows <= 0 or paired_half_rows % TILE or rows % (2 * paired_half_rows) or k % TILE:
+        raise ValidationError("rows must be whole groups of 2 * paired_half_rows and k a multiple of 128")
+    groups, kb = rows // (2 * paired_half_rows), k // TILE
+    c = codes.reshape(groups, 2, h, TILE, kb, 64).transpose(0, 2, 4, 1, 3, 5)            # [group, tile, kb, half, r, 64]
+    s = scales.reshape(groups, 2, h, 4, 32, kb, 4).transpose(0, 2, 5, 1, 4, 3, 6)         # [group, tile, kb, half, r % 32, r / 32, 4]
+    return np.ascontiguousarray(c).reshape(rows, half_k), np.ascontiguousarray(s).reshape(rows, k // 32)
+
+
 def apply_weight_steps(binding: LayoutBinding, sources: list[np.ndarray]) -> np.ndarray:
     """Runs a binding's steps on uint8 ``[slabs, N, K]`` sources (CPU); returns the bytes the kernel will stream."""
     data = sources
@@ -146,6 +177,14 @@ def apply_weight_steps(binding: LayoutBinding, sources: list[np.ndarray]) -> np.
 
 def moe_layer_layout_plan(weight_layout: str, *, split_gate_up: bool = False, scale_dtype: str = "fp32") -> dict[str, Any]:
     """The ``layout_plan.json`` document of one routed-MoE layer."""
+    if weight_layout == "mxfp4_paired_blocks":
+        if split_gate_up:
+            raise ValidationError("the MXFP4 plan takes the concatenated gate/up tensor")
+        weights = [plan_weight_layout("w13", MXFP4_ROW_MAJOR, MXFP4_PAIRED_BLOCKS, checkpoint_tensors=("w13",)),
+                   plan_weight_layout("w2", MXFP4_ROW_MAJOR, MXFP4_PAIRED_BLOCKS, checkpoint_tensors=("w2",))]
+        scales = [plan_scale_layout(name + "_scale", (name + "_scale",), checkpoint_dtype="ue8m0", kernel_dtype="ue8m0", block=(1, 32))
+                  for name in ("w13", "w2")]
+        return {"format": "netra-layout-plan-2", "weights": [w.to_dict() for w in weights], "scales": [s.to_dict() for s in scales]}
     kernel = TILES128 if weight_layout == "tiles128" else ROW_MAJOR
     w13_sources = ("gate_proj", "up_proj") if split_gate_up else ("w13",)
     w13 = plan_weight_layout("w13", SPLIT_GATE_UP if split_gate_up else ROW_MAJOR, kernel, checkpoint_tensors=w13_sources)

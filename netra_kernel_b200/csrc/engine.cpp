@@ -209,6 +209,7 @@ constexpr uint32_t kMaxArguments = 32;
 struct TensorMapSpec {
   uint64_t rows = 0, row_bytes = 0;
   uint32_t box_rows = 0, box_bytes = 0;
+  bool four_bit = false;   // element "e2m1": rows of 128 four-bit codes (64 bytes in memory) widened to 128 bytes of shared memory
 };
 
 struct ArgSpec {
@@ -302,8 +303,14 @@ Manifest parse_manifest(const std::string& directory) {
             arg.map.row_bytes = as_u64(t.at("row_bytes"), "tensor_map.row_bytes");
             arg.map.box_rows = as_u32(t.at("box_rows"), "tensor_map.box_rows");
             arg.map.box_bytes = as_u32(t.at("box_bytes"), "tensor_map.box_bytes");
+            if (t.find("element") != nullptr) {
+              const std::string element = as_text(t.at("element"), "tensor_map.element");
+              if (element != "u8" && element != "e2m1") throw std::runtime_error("unsupported tensor_map element");
+              arg.map.four_bit = element == "e2m1";
+            }
             if (as_text(t.at("swizzle"), "tensor_map.swizzle") != "128B" || arg.map.box_bytes != 128 || !arg.map.rows ||
-                !arg.map.row_bytes || arg.map.row_bytes % 16 || !arg.map.box_rows || arg.map.box_rows > 256)
+                !arg.map.row_bytes || arg.map.row_bytes % 16 || !arg.map.box_rows || arg.map.box_rows > 256 ||
+                (arg.map.four_bit && arg.map.row_bytes != 64))
               throw std::runtime_error("unsupported tensor_map description");
             if (!arg.bindable && arg.workspace_offset % 16) throw std::runtime_error("tensor_map workspace offset must be 16-byte aligned");
           }
@@ -371,6 +378,16 @@ const Driver& driver() {
 }
 
 bool encode_map(CUtensorMap* map, void* base, const TensorMapSpec& s) {
+  if (s.four_bit) {   // 128 codes per row, 64 bytes apart in memory; the base must be 32-byte aligned
+    cuuint64_t dims[2] = {128, s.rows};
+    cuuint64_t strides[1] = {64};
+    cuuint32_t box[2] = {128, s.box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return ((uintptr_t)base & 31) == 0 &&
+           driver().TensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, base, dims, strides, box, elem,
+                                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  }
   cuuint64_t dims[2] = {s.row_bytes, s.rows};
   cuuint64_t strides[1] = {s.row_bytes};
   cuuint32_t box[2] = {s.box_bytes, s.box_rows};

@@ -115,6 +115,11 @@ class EngineSession:
         import torch
         out = dict(tensors)
         for step in self.layout_plan.get("steps", []):
+            if step["entry_point"] == "netra_moe_mxfp4_pack_launch":     # codes and scale bytes are re-ordered together
+                from .moe import pack_mxfp4
+                out[step["tensor"]], out[step["scale_tensor"]] = pack_mxfp4(out[step["tensor"]], out[step["scale_tensor"]],
+                                                                            paired_half_rows=int(step["paired_half_rows"]))
+                continue
             w = out[step["tensor"]]
             packed = torch.empty_like(w)
             abi.check(self.lib.netra_moe_repack_tiles_launch(packed.data_ptr(), w.data_ptr(), w.shape[0] * w.shape[1],

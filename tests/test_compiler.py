@@ -6,11 +6,12 @@ import json
 import shutil
 from pathlib import Path
 
+import numpy as np
 import pytest
 
 from netra_kernel_b200 import abi
 from netra_kernel_b200.compiler import compile_engine, validate_engine_directory
-from netra_kernel_b200.compiler import catalog, contracts, engine, expr, frontend, memory, planner, profiles
+from netra_kernel_b200.compiler import catalog, contracts, engine, expr, frontend, layouts, memory, planner, profiles
 from netra_kernel_b200.compiler.library import KernelLibrary
 from netra_kernel_b200.compiler.types import TARGET, Maturity, ValidationError, canonical_json, stable_hash
 from tests import helpers
@@ -141,7 +142,9 @@ def test_catalog_launch_constants_match_the_built_library():
     tactics = {t.name: t for t in catalog.load_fixed_tactic_catalog(LIB_ROOT, TARGET)}
     for which, name in ((0, "gate_up_silu_requant_umma_swapab_tiles128"), (1, "down_projection_umma_swapab_tiles128"),
                         (2, "gate_up_silu_requant_umma_tokmajor_tiles128"), (3, "down_projection_umma_tokmajor_row_major"),
-                        (4, "down_projection_umma_tokmajor_f16_tiles128"), (5, "router_logits_f32_bf16_umma")):
+                        (4, "down_projection_umma_tokmajor_f16_tiles128"), (5, "router_logits_f32_bf16_umma"),
+                        (6, "gate_up_silu_requant_mxfp4_block_scaled_swapab"), (7, "down_projection_mxfp4_block_scaled_swapab"),
+                        (8, "gate_up_silu_requant_mxfp4_block_scaled_tokmajor"), (9, "down_projection_mxfp4_block_scaled_tokmajor")):
         block, smem = ctypes.c_uint32(), ctypes.c_uint32()
         assert lib.netra_moe_kernel_launch_info(which, ctypes.byref(block), ctypes.byref(smem)) == 0
         assert tactics[name].launch["block"][0] == block.value
@@ -163,6 +166,52 @@ def test_prefill_profile_selects_the_tensor_core_router_and_the_fp16_row_tactics
     contracts_q = json.loads((tmp_path / "q" / "contracts.json").read_text())["contracts"]
     numerical = lambda cs, op: next(c["semantics"]["numerical"] for c in cs if c["operation"] == op)
     assert numerical(contracts_p, "down_projection") != numerical(contracts_q, "down_projection")     # a numerical id of its own
+
+
+def test_mxfp4_model_selects_the_block_scaled_tactics_and_a_pack_step(tmp_path):
+    """An MXFP4 model manifest: the two grouped GEMMs resolve to the block-scaled kernels (swap-AB at decode size, token-major
+    at prefill size), the four-bit weight tensor maps are described as such, the layout plan names the pack entry point, and
+    an FP8 profile cannot serve the model."""
+    model = LIB_ROOT / "manifests" / TARGET / "models" / "routed-moe-layer-mxfp4.json"
+    dec = compile_engine(model, "decode_t256_mxfp4", tmp_path / "d", copy_cubin=False)
+    picked = {o["name"]: o["tactic"] for o in dec["operations"]}
+    assert picked["gate_up"] == "gate_up_silu_requant_mxfp4_block_scaled_swapab"
+    assert picked["down"] == "down_projection_mxfp4_block_scaled_swapab"
+    assert picked["router_logits"] == "router_logits_bf16_fp64_mma_k8" and picked["combine"] == "combine_slot_ordered_fp32"
+    pre = compile_engine(model, "prefill_t8192_mxfp4", tmp_path / "p", copy_cubin=False)
+    picked = {o["name"]: o["tactic"] for o in pre["operations"]}
+    assert picked["gate_up"] == "gate_up_silu_requant_mxfp4_block_scaled_tokmajor"
+    assert picked["down"] == "down_projection_mxfp4_block_scaled_tokmajor"
+    engine = json.loads((tmp_path / "d" / "engine.json").read_text())
+    gate_up = next(o for o in engine["operations"] if o["name"] == "gate_up")
+    w13_map = gate_up["arguments"][0]["tensor_map"]
+    assert w13_map == {"rows": 257 * 1024 * 16, "row_bytes": 64, "box_rows": 256, "box_bytes": 128, "swizzle": "128B", "element": "e2m1"}
+    assert "element" not in gate_up["arguments"][1]["tensor_map"]
+    plan = json.loads((tmp_path / "d" / "layout_plan.json").read_text())
+    assert [s["entry_point"] for s in plan["steps"]] == ["netra_moe_mxfp4_pack_launch"] * 2
+    assert [s["paired_half_rows"] for s in plan["steps"]] == [512, 128]
+    assert plan["weights"][0]["steps"][0]["operation"] == "mxfp4_pair_blocks"
+    with pytest.raises(ValidationError):
+        compile_engine(model, "decode_t256", tmp_path / "x", copy_cubin=False)          # an FP8 profile
+    with pytest.raises(ValidationError):
+        compile_engine(MODEL, "decode_t256_mxfp4", tmp_path / "y", copy_cubin=False)    # an FP8 model
+
+
+def test_mxfp4_pair_blocks_byte_transform():
+    """CPU statement of the pack step: every source byte appears once, rows of a tile pair end up side by side."""
+    rng = np.random.default_rng(3)
+    codes = rng.integers(0, 256, (512, 256), dtype=np.uint8)         # 512 rows, k = 512
+    scales = rng.integers(0, 256, (512, 16), dtype=np.uint8)
+    c, s = layouts.mxfp4_pair_blocks(codes, scales, 128)
+    assert c.shape == codes.shape and s.shape == scales.shape
+    blocks = c.reshape(2, 4, 2, 128, 64)                              # [pair, kb, tile of the pair, r, 64]
+    assert np.array_equal(blocks[1, 2, 1], codes[384:512, 128:192])   # pair 1 = tiles 2 and 3; tile 3, K-block 2
+    atoms = s.reshape(2, 4, 2, 32, 4, 4)
+    assert np.array_equal(atoms[0, 3, 0, 5, 2], scales[2 * 32 + 5, 12:16])     # row 69 of tile 0, K-block 3
+    c13, _ = layouts.mxfp4_pair_blocks(np.tile(codes, (4, 1)), np.tile(scales, (4, 1)), 512)      # 2 slabs of 1024 rows
+    assert np.array_equal(c13.reshape(2, 4, 4, 2, 128, 64)[1, 3, 0, 1], np.tile(codes, (4, 1))[1024 + 512 + 384:1024 + 1024, 0:64])
+    with pytest.raises(ValidationError):
+        layouts.mxfp4_pair_blocks(codes, scales, 96)
 
 
 def _plan(model_path, profile_name, **kw):

@@ -145,6 +145,32 @@ def test_engine_prefill_manifest_runs_the_fp16_partial_row_tactics(tmp_path, exp
     assert m["max_abs"] <= helpers.MAX_ABS and m["rel_l2"] <= helpers.REL_L2, m
 
 
+def test_engine_on_mxfp4_weights_equals_the_fused_layer_call(tmp_path):
+    """The MXFP4 model manifest through the engine ABI at both profile sizes: the layout plan's pack step, four-bit tensor
+    maps encoded by the runtime, the block-scaled kernels launched from the cubin - bit for bit the fused-layer call."""
+    from netra_kernel_b200.moe import RoutedMoELayer
+    p13, s13, p2, s2 = synth.make_expert_weights_device(0, torch.device("cuda", 0), mxfp4=True)
+    for profile, tokens, symbol in (("decode_t256_mxfp4", 256, "netra_moe_gate_up_mxfp4_umma_sm100"),
+                                    ("prefill_t8192_mxfp4", 8192, "netra_moe_gate_up_mxfp4_tokmajor_sm100")):
+        hidden, router_w, _ = synth.make_activations(tokens, None, seed=3)
+        tensors = {"hidden": hidden.cuda(), "output": torch.zeros(tokens, 2048, dtype=torch.bfloat16, device="cuda"),
+                   "router_weight": router_w.cuda(), "w13": p13, "w13_scale": s13, "w2": p2, "w2_scale": s2}
+        session = _session(tmp_path, MANIFESTS / "routed-moe-layer-mxfp4.json", profile, tensors)
+        assert symbol in [o["kernel_symbol"] for o in session.manifest["operations"]]
+        session.prepare(_stream())
+        session.launch(_stream())
+        torch.cuda.synchronize()
+        assert _status_words(session) == [0, 0, 0, 0]
+        layer = RoutedMoELayer(tensors["router_weight"], p13, s13, p2, s2, tokens, mxfp4=True)
+        want = layer(tensors["hidden"])
+        torch.cuda.synchronize()
+        layer.check_status()
+        assert torch.equal(tensors["output"].view(torch.int16), want.view(torch.int16))
+        assert tensors["output"].float().abs().max().item() > 0
+        layer.close()
+        session.close()
+
+
 def test_status_codes_for_guards_and_call_order(tmp_path, expert_weights):
     lib = er.load()
     tensors, *_ = _tensors(expert_weights, 16)
