@@ -609,47 +609,57 @@ def mxfp4_decode_object(layer, hidden_cpu, steps, warmup, dev, stream, sync, fp8
     return obj
 
 
+def abi_lib():
+    from netra_kernel_b200 import abi
+    return abi.load()
+
+
 def decode_bridges_object(layer, dev, stream, sync) -> dict:
     """The reference's decode boundary at M = 1: its three per-kernel bridges (gate_up, SiLU*up + quantise, down + reduce),
     each timed alone over launches that rotate through 64 different expert selections (64 x 28 MB of slabs, so the
     weights come from HBM, as in the reference's in-trace figure), and the fused layer call at one token beside them."""
     import torch
-    from netra_kernel_b200 import moe as M
     w13, w13_s, w2, w2_s = layer._keep[1], layer._keep[2], layer._keep[3], layer._keep[4]
     if layer.tiled:
         raise SystemExit("bench: the bridges take row-major slabs")
     g = torch.Generator().manual_seed(77)
     sets = 64
-    hidden = torch.randn(1, 2048, generator=g).to(torch.bfloat16).to(dev)
     a_fp8 = torch.randint(0, 120, (1, 2048), generator=g, dtype=torch.uint8).to(dev)
     a_s = (torch.rand(1, 16, generator=g) * 0.01 + 0.001).to(dev)
     ids = [torch.cat([torch.randperm(256, generator=g)[:8], torch.tensor([256])]).to(torch.int32).view(1, 9).to(dev) for _ in range(sets)]
     w9 = torch.full((1, 9), 1.0 / 9, dtype=torch.float32, device=dev)
+    lib = abi_lib()
+    gu = torch.empty(9, 1024, dtype=torch.float32, device=dev)
+    hq = torch.empty(9, 512, dtype=torch.uint8, device=dev)
+    hs = torch.empty(9, 4, dtype=torch.float32, device=dev)
+    y = torch.empty(1, 2048, dtype=torch.bfloat16, device=dev)
     out = {}
     with torch.cuda.stream(stream):
-        gu = M.bridge_gate_up(a_fp8, a_s, w13, w13_s, ids[0])
-        hq, hs = M.bridge_silu_mul_quant(gu)
+        st = stream.cuda_stream
         calls = {
-            "gate_up": lambda i: M.bridge_gate_up(a_fp8, a_s, w13, w13_s, ids[i % sets]),
-            "silu_mul_quant": lambda i: M.bridge_silu_mul_quant(gu),
-            "down_reduce": lambda i: M.bridge_down_reduce(hq, hs, w2, w2_s, w9, ids[i % sets]),
+            "gate_up": lambda i: lib.netra_qwen36_moe_gate_up_launch(a_fp8.data_ptr(), a_s.data_ptr(), w13.data_ptr(), w13_s.data_ptr(),
+                                                                     ids[i % sets].data_ptr(), gu.data_ptr(), 1, st),
+            "silu_mul_quant": lambda i: lib.netra_qwen36_moe_silu_mul_quant_launch(gu.data_ptr(), hq.data_ptr(), hs.data_ptr(), 9, st),
+            "down_reduce": lambda i: lib.netra_qwen36_moe_down_reduce_launch(hq.data_ptr(), hs.data_ptr(), w2.data_ptr(), w2_s.data_ptr(),
+                                                                             w9.data_ptr(), ids[i % sets].data_ptr(), y.data_ptr(), 1, st),
         }
-        for name, fn in calls.items():
-            for i in range(8):
-                fn(i)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            sync.barrier()
-            e0.record(stream)
-            for i in range(128):
-                fn(i)
-            e1.record(stream)
+        for name in ("gate_up", "silu_mul_quant", "down_reduce"):      # in data-flow order: each leaves valid inputs for the next
+            fn = calls[name]
+            for i in range(4):
+                if fn(i) != 0:
+                    raise SystemExit(f"bench: bridge {name} failed")
             stream.synchronize()
-            out[name] = e0.elapsed_time(e1) / 128 * 1e3
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for i in range(sets):
+                    fn(i)
+            ms, _ = time_replays(graph.replay, 10, 3, stream, sync)
+            out[name] = ms / sets * 1e3
     return {"workload": "decode_bridges_m1", "rows": 1,
             "api": "netra_qwen36_moe_gate_up_launch / netra_qwen36_moe_silu_mul_quant_launch / netra_qwen36_moe_down_reduce_launch",
             "us_per_launch": {k: round(v, 2) for k, v in out.items()},
-            "timing": "128 back-to-back launches per kernel between two CUDA events (launch overhead included), expert "
-                      "selections rotating through 64 sets so that the slabs are read from HBM",
+            "timing": "device time per launch inside a captured CUDA graph of 64 launches of the kernel, expert selections "
+                      "rotating through 64 sets so that the slabs are read from HBM",
             "reference_published": {"us_per_launch": {"gate_up": 13.486, "silu_mul_quant": 2.846, "down_reduce": 24.773},
                                     "hardware": "MI350X, inside a 40-layer decode trace", "comparable": False}}
 
