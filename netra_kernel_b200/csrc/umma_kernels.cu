@@ -196,7 +196,8 @@ __device__ __forceinline__ Item decode_item(int item, const int* item_pre, const
   return it;
 }
 
-// kGateUp: 2 weight tiles per stage (gate, up), K = 2048, FP8 epilogue.  else: 1 tile, K = 512, FP32 epilogue.
+// kGateUp: K = 2048, a stage holds a gate tile and its up tile, FP8 epilogue.  else: K = 512, a stage holds two
+// neighbouring W2 tiles (an item is 256 output columns), FP32 epilogue.
 // kFp4: the weight tiles are MXFP4 (E2M1 codes, 64 bytes per row and K-block in memory, expanded by the copy engine
 // to one byte per element in shared memory) and each tile brings a 512-byte atom of UE8M0 scales.  The copy engine
 // reaches the HBM rate on four-bit rows only with boxes of 256 rows (16 KiB of codes; boxes of 128 rows stop at about
@@ -204,7 +205,7 @@ __device__ __forceinline__ Item decode_item(int item, const int* item_pre, const
 // two neighbouring W2 tiles, which the pack step stored next to each other.
 template <bool kGateUp, bool kFp4 = false>
 struct Cfg {
-  static constexpr int kATiles = (kGateUp || kFp4) ? 2 : 1;   // weight tiles per stage (MXFP4 down: two neighbouring W2 tiles)
+  static constexpr int kATiles = 2;   // weight tiles per stage: a gate tile and its up tile | two neighbouring W2 tiles
   // token rows per work item (UMMA N).  32 for both: 64-row items (the shared expert at decode sizes) ran a longer
   // epilogue than the four TMEM stages could hide, and the CTAs that held them finished 8 us after the rest
   static constexpr int kTokMax = 32;
@@ -217,12 +218,12 @@ struct Cfg {
   static constexpr int kNTiles = (kGateUp ? kInter / kTileRows : kHidden / kTileRows / kATiles) / kSubTiles;   // items per slab and chunk: 4 | 16 (MXFP4: 8)
   static constexpr int kSlabRows = kGateUp ? 2 * kInter : kHidden;                     // 1024 | 2048
   static constexpr int kSlabTiles = kSlabRows / kTileRows;                             // 8 | 16
-  static constexpr int kKbPerStep = (kGateUp || kFp4) ? 1 : 4;   // K-blocks the MMA warp issues per accumulator hand-off
+  static constexpr int kKbPerStep = (kGateUp || kFp4) ? 1 : 2;   // K-blocks the MMA warp issues per accumulator hand-off
   static constexpr int kAccCols = kKbPerStep * kATiles * kTokMax;                      // TMEM columns per hand-off: 64 | 128
   static constexpr int kScaleCols = kFp4 ? 4 * kATiles + 4 : 0;                        // TMEM columns of the A and B scales
   static constexpr int kAccStages = (512 - kScaleCols) / kAccCols;                     // 8 | 4 (MXFP4: 7 | 3)
   static constexpr int kKbPerLoad = 1;                                                 // K-blocks per shared-memory stage
-  static constexpr int kStages = kFp4 ? 5 : (kGateUp ? 6 : 10);
+  static constexpr int kStages = kFp4 ? 5 : 6;
   static constexpr int kStageTiles = kKbPerLoad * kATiles;                             // weight tiles per stage
   static constexpr int kStageBytes = kKbPerLoad * (kATiles * kWTileBytes + kTokTileBytes);   // 36 KiB | 20 KiB (MXFP4 down: 40 KiB)
   static constexpr int kWTxBytes = kFp4 ? kWTileBytes / 2 : kWTileBytes;               // bytes one weight-tile copy reports
@@ -364,9 +365,14 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
           mbar_expect_tx(sbar, C::kXsBytes + (kFp4 ? 0 : C::kATiles * C::kSubTiles * C::kWsBytes));
           bulk_load(sdst, x_scale + (size_t)w.row0 * C::kKBlocks, C::kXsBytes, sbar);
           if constexpr (!kFp4) {
-            const float* wsrc = w_scale + ((size_t)w.group * C::kSlabTiles + w.ntile) * C::kKBlocks;
-            bulk_load(sdst + C::kXsBytes, wsrc, C::kSubTiles * C::kWsBytes, sbar);   // the item's tiles are consecutive
-            if (kGateUp) bulk_load(sdst + C::kXsBytes + C::kWsBytes, wsrc + (kInter / kBlock) * C::kKBlocks, C::kWsBytes, sbar);
+            if (kGateUp) {     // gate tile ntile, up tile 4 + ntile
+              const float* wsrc = w_scale + ((size_t)w.group * C::kSlabTiles + w.ntile) * C::kKBlocks;
+              bulk_load(sdst + C::kXsBytes, wsrc, C::kWsBytes, sbar);
+              bulk_load(sdst + C::kXsBytes + C::kWsBytes, wsrc + (kInter / kBlock) * C::kKBlocks, C::kWsBytes, sbar);
+            } else {           // tiles 2 * ntile and 2 * ntile + 1: consecutive scale rows
+              const float* wsrc = w_scale + ((size_t)w.group * C::kSlabTiles + 2 * w.ntile) * C::kKBlocks;
+              bulk_load(sdst + C::kXsBytes, wsrc, 2 * C::kWsBytes, sbar);
+            }
           }
         }
         for (int sub = 0; ok && sub < C::kSubTiles; ++sub)
@@ -390,18 +396,21 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
             bulk_load(smem_u32(atom_base + s * C::kScaleStageBytes), w_scale_atoms + (size_t)wy * 4, C::kScaleStageBytes, bar);
             continue;
           }
+          // the stage's two weight tiles: gate tile ntile and up tile 4 + ntile | W2 tiles 2 ntile and 2 ntile + 1
+          const int tile0 = kGateUp ? w.ntile + sub : 2 * (w.ntile + sub);
+          const int tile_step = kGateUp ? kInter / kTileRows : 1;
           int wx, wy0, wy1;
           if (w_tiled) {   // one contiguous 16 KiB block per (slab tile, K-block)
             wx = 0;
-            wy0 = ((w.group * C::kSlabTiles + w.ntile + sub) * C::kKBlocks + kb) * kTileRows;
-            wy1 = wy0 + (kInter / kTileRows) * C::kKBlocks * kTileRows;
+            wy0 = ((w.group * C::kSlabTiles + tile0) * C::kKBlocks + kb) * kTileRows;
+            wy1 = wy0 + tile_step * C::kKBlocks * kTileRows;
           } else {
             wx = kb * kBlock;
-            wy0 = w.group * C::kSlabRows + (w.ntile + sub) * kTileRows;
-            wy1 = wy0 + kInter;
+            wy0 = w.group * C::kSlabRows + tile0 * kTileRows;
+            wy1 = wy0 + tile_step * kTileRows;
           }
           tma_load_2d(dst, tm_w, bar, wx, wy0, pol_w);
-          if (kGateUp) tma_load_2d(dst + kWTileBytes, tm_w, bar, wx, wy1, pol_w);
+          tma_load_2d(dst + kWTileBytes, tm_w, bar, wx, wy1, pol_w);
           tma_load_2d(dst + C::kATiles * kWTileBytes, tm_x, bar, kb * kBlock, w.row0, pol_x);
         }
       }
