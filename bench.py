@@ -233,14 +233,21 @@ def mxfp4_gate_up_traffic_bytes():
     return _traffic_if_current(MXFP4_GATE_UP_DRAM_TRAFFIC)
 
 
-def time_e2e_pipelined(compute, hidden, out, hidden_cpu, steps, warmup, stream):
+def time_e2e_pipelined(compute, hidden, out, hidden_cpu, steps, warmup, stream, second=None):
     """End-to-end time per step with the host copies of neighbouring steps overlapping the compute of this one, as a
     serving loop would run it: every step still moves its own input from pinned host memory to the device and its own
     result back.  `compute()` enqueues one layer call on `stream`, reading `hidden` and writing `out` (the buffers the
     call is bound to); two staging slots on either side decouple the copies from those buffers.
+    `second = (compute2, hidden2, out2)`: a second call bound to its own pair of buffers.  Steps then alternate between
+    the two calls and the host copies go straight into and out of the bound buffers (no staging copies on the device).
     Returns milliseconds per step (device time from the first copy to the last result landing on the host)."""
     import torch
     dev = hidden.device
+    if second is not None:
+        try:
+            return _time_e2e_double_bound([(compute, hidden, out), second], hidden_cpu, steps, warmup, stream)
+        except ImportError:                              # no runtime bindings: the staged loop below does the same work
+            pass
     s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
     host_in = [hidden_cpu.clone().pin_memory() for _ in range(2)]
     host_out = [torch.empty_like(hidden_cpu).pin_memory() for _ in range(2)]
@@ -329,6 +336,59 @@ def time_e2e_pipelined(compute, hidden, out, hidden_cpu, steps, warmup, stream):
     e1.record(s_out)
     torch.cuda.synchronize(dev)
     return e0.elapsed_time(e1) / steps, host_out, host_api
+
+
+def _time_e2e_double_bound(calls, hidden_cpu, steps, warmup, stream):
+    """The pipelined end-to-end loop over two calls bound to their own input / output buffers: step i uses pair i mod 2.
+    H2D of step i+1 and D2H of step i-1 run on their own streams beside the compute of step i."""
+    import torch
+    from cuda.bindings import runtime as rt
+    dev = calls[0][1].device
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    host_in = [hidden_cpu.clone().pin_memory() for _ in range(2)]
+    host_out = [torch.empty_like(hidden_cpu).pin_memory() for _ in range(2)]
+    names = ("in", "done", "out")              # input k is on the device | call k has run (input free, result there) | result k is on the host
+    events = {n: [torch.cuda.Event() for _ in range(2)] for n in names}
+    for n, st in (("in", s_in), ("done", stream), ("out", s_out)):
+        for e in events[n]:
+            e.record(st)                                 # torch creates the CUDA event at its first record
+    torch.cuda.synchronize(dev)
+    raw = {n: [e.cuda_event for e in events[n]] for n in names}
+    nbytes = hidden_cpu.numel() * hidden_cpu.element_size()
+    default = rt.cudaMemcpyKind.cudaMemcpyDefault
+    h_in, h_main, h_out = s_in.cuda_stream, stream.cuda_stream, s_out.cuda_stream
+    p_hi, p_ho = [t.data_ptr() for t in host_in], [t.data_ptr() for t in host_out]
+    p_h, p_o = [c[1].data_ptr() for c in calls], [c[2].data_ptr() for c in calls]
+
+    def ok(result):
+        code = result[0] if isinstance(result, tuple) else result
+        if int(code) != 0:
+            raise RuntimeError(f"CUDA runtime call failed with {code}")
+
+    def step(i):
+        k = i & 1
+        ok(rt.cudaStreamWaitEvent(h_in, raw["done"][k], 0))        # the previous call on this pair has read its input
+        ok(rt.cudaMemcpyAsync(p_h[k], p_hi[k], nbytes, default, h_in))
+        ok(rt.cudaEventRecord(raw["in"][k], h_in))
+        ok(rt.cudaStreamWaitEvent(h_main, raw["in"][k], 0))
+        ok(rt.cudaStreamWaitEvent(h_main, raw["out"][k], 0))       # the previous result of this pair is on the host
+        with torch.cuda.stream(stream):
+            calls[k][0]()
+        ok(rt.cudaEventRecord(raw["done"][k], h_main))
+        ok(rt.cudaStreamWaitEvent(h_out, raw["done"][k], 0))
+        ok(rt.cudaMemcpyAsync(p_ho[k], p_o[k], nbytes, default, h_out))
+        ok(rt.cudaEventRecord(raw["out"][k], h_out))
+
+    for i in range(max(warmup, 2)):
+        step(i)
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(s_in)
+    for i in range(steps):
+        step(i)
+    e1.record(s_out)
+    torch.cuda.synchronize(dev)
+    return e0.elapsed_time(e1) / steps, host_out, "CUDA runtime bindings (two bound calls)"
 
 
 def make_engine_session(args, tokens, device_id, layer, hidden, out, model="routed-moe-layer-fp8.json", bias=None):
@@ -433,7 +493,7 @@ def time_stages(layer, hidden, out, steps, warmup, stream, sync: Sync):
     return [statistics.mean(marks[k][st].elapsed_time(marks[k][st + 1]) for k in range(steps)) for st in range(n_stage)]
 
 
-def time_e2e(replay, hidden, out, hidden_cpu, steps, warmup, stream, sync: Sync):
+def time_e2e(replay, hidden, out, hidden_cpu, steps, warmup, stream, sync: Sync, second=None):
     """End to end per step with pinned host buffers: serial (copy, call, copy on one stream) and pipelined (what `e2e`
     reports).  Returns (pipelined ms, serial ms, host api name, last host result)."""
     import torch
@@ -447,7 +507,7 @@ def time_e2e(replay, hidden, out, hidden_cpu, steps, warmup, stream, sync: Sync)
 
     serial_ms, _ = time_replays(serial_step, steps, warmup, stream, sync)
     sync.barrier()
-    piped_ms, piped_out, host_api = time_e2e_pipelined(replay, hidden, out, hidden_cpu, steps, warmup, stream)
+    piped_ms, piped_out, host_api = time_e2e_pipelined(replay, hidden, out, hidden_cpu, steps, warmup, stream, second=second)
     sync.barrier()
     if not torch.equal(piped_out[(steps - 1) & 1], host_out):
         raise SystemExit("bench: the pipelined end-to-end loop returned a different result than the serial one")
@@ -462,11 +522,14 @@ def routing_load(counts) -> dict:
             "experts_below_128_rows": int((load < 128).sum())}
 
 
-def e2e_object(tokens_total, tokens_per_rank, e2e_ms, serial_ms, host_api) -> dict:
+def e2e_object(tokens_total, tokens_per_rank, e2e_ms, serial_ms, host_api, double_bound=False) -> dict:
     return {"value": tokens_total / (e2e_ms / 1e3), "unit": UNIT, "ms_per_step": e2e_ms,
             "h2d_bytes_per_step": tokens_per_rank * 2048 * 2, "d2h_bytes_per_step": tokens_per_rank * 2048 * 2,
-            "how": "every step copies its input from pinned host memory and its result back; the copies run on their own "
-                   "streams with two staging slots, so they overlap the neighbouring steps' compute",
+            "how": ("every step copies its input from pinned host memory into one of two device buffers and its result back from "
+                    "one of two; the call of step i is a captured graph bound to pair i mod 2, and the copies run on their own "
+                    "streams, so they overlap the neighbouring steps' compute") if double_bound else
+                   ("every step copies its input from pinned host memory and its result back; the copies run on their own "
+                    "streams with two staging slots, so they overlap the neighbouring steps' compute"),
             "copies_enqueued_with": host_api, "serial_ms_per_step": serial_ms}
 
 
@@ -834,7 +897,19 @@ def run_ours(args) -> None:
                 api_name = "netra_moe_layer_launch (fused-layer ABI, captured CUDA graph)"
             ms_per_step, step_spread = time_replays(graph.replay, steps, warmup, stream, sync, spread=True)
             stage_ms = time_stages(layer, hidden, out, steps, warmup, stream, sync)
-            e2e_ms, e2e_serial_ms, e2e_host_api, host_out = time_e2e(graph.replay, hidden, out, hidden_cpu, steps, warmup, stream, sync)
+            # a serving loop double-buffers its activations: a second call of the same kind bound to its own input / output pair
+            hidden2, out2 = torch.empty_like(hidden), torch.empty_like(out)
+            if session is not None:
+                session2 = make_engine_session(args, tokens, local_rank, layer, hidden2, out2)
+                session2.prepare(stream.cuda_stream)
+                replay2 = lambda: session2.launch(stream.cuda_stream)
+            else:
+                graph2 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph2, stream=stream):
+                    layer(hidden2, out=out2)
+                replay2 = graph2.replay
+            e2e_ms, e2e_serial_ms, e2e_host_api, host_out = time_e2e(graph.replay, hidden, out, hidden_cpu, steps, warmup, stream, sync,
+                                                                     second=(replay2, hidden2, out2))
 
             # ---- keep the same kernels running long enough for the clock sampler to see them under load
             soak_end = time.perf_counter() + 1.0
@@ -985,7 +1060,7 @@ def run_ours(args) -> None:
                     "api": api_name},
         "gpu_launches": steps * layer.launches_per_call(tokens),
         "step_ms_spread": step_spread,
-        "e2e": e2e_object(world * tokens, tokens, e2e_ms, e2e_serial_ms, e2e_host_api),
+        "e2e": e2e_object(world * tokens, tokens, e2e_ms, e2e_serial_ms, e2e_host_api, double_bound=e2e_host_api == "CUDA runtime bindings (two bound calls)"),
         "roofline": ({"bound": "tensor", "kernel": "netra_moe_gate_up_tokmajor_sm100", "achieved": gate_up_flops / gu_s / 1e12,
                       "peak": fp8_peak, "unit": "TFLOP/s", "frac": gate_up_flops / gu_s / 1e12 / fp8_peak, "peak_source": fp8_kind,
                       "algorithmic_flops": gate_up_flops, "avg_launch_ms": stage_ms[6], "traffic": None}

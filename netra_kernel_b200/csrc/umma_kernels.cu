@@ -214,8 +214,10 @@ struct Cfg {
   static constexpr int kTokTileBytes = kTokMax * kBlock;  // 4 KiB
   static constexpr int kScaleSlots = kGateUp ? 2 : 4;
   static constexpr int kKBlocks = kGateUp ? kHiddenBlocks : kInterBlocks;
-  static constexpr int kSubTiles = 1;                     // consecutive weight tiles per work item (same token rows)
-  static constexpr int kNTiles = (kGateUp ? kInter / kTileRows : kHidden / kTileRows / kATiles) / kSubTiles;   // items per slab and chunk: 4 | 16 (MXFP4: 8)
+  // consecutive tile pairs per work item (same token rows).  down: two, i.e. 512 output columns per item - with 256
+  // the per-item costs (scale tile, drained pipeline, epilogue) showed: 52.4 us against 49.7 us at 256 tokens
+  static constexpr int kSubTiles = (kGateUp || kFp4) ? 1 : 2;
+  static constexpr int kNTiles = (kGateUp ? kInter / kTileRows : kHidden / kTileRows / kATiles) / kSubTiles;   // items per slab and chunk: 4 | 4 (MXFP4 down: 8)
   static constexpr int kSlabRows = kGateUp ? 2 * kInter : kHidden;                     // 1024 | 2048
   static constexpr int kSlabTiles = kSlabRows / kTileRows;                             // 8 | 16
   static constexpr int kKbPerStep = (kGateUp || kFp4) ? 1 : 2;   // K-blocks the MMA warp issues per accumulator hand-off
@@ -371,7 +373,7 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
               bulk_load(sdst + C::kXsBytes + C::kWsBytes, wsrc + (kInter / kBlock) * C::kKBlocks, C::kWsBytes, sbar);
             } else {           // tiles 2 * ntile and 2 * ntile + 1: consecutive scale rows
               const float* wsrc = w_scale + ((size_t)w.group * C::kSlabTiles + 2 * w.ntile) * C::kKBlocks;
-              bulk_load(sdst + C::kXsBytes, wsrc, 2 * C::kWsBytes, sbar);
+              bulk_load(sdst + C::kXsBytes, wsrc, C::kSubTiles * 2 * C::kWsBytes, sbar);
             }
           }
         }
@@ -388,7 +390,7 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
             // one box of 256 code rows = two 8 KiB blocks that the pack step stored next to each other: blocks are
             // ordered (slab, tile pair, K-block, tile of the pair) - W13 pairs a gate tile with its up tile, W2 pairs
             // tiles 2p and 2p + 1; the 512-byte scale atoms follow the same order, so the stage's two are one 1 KiB copy
-            const int wy = (((w.group * C::kNTiles + w.ntile) * C::kKBlocks + kb) * 2) * kTileRows;
+            const int wy = (((w.group * C::kNTiles * C::kSubTiles + w.ntile + sub) * C::kKBlocks + kb) * 2) * kTileRows;
             tma_load_2d(dst, tm_w, bar, 0, wy, pol_w);
 #pragma unroll
             for (int j = 0; j < C::kKbPerLoad; ++j)
@@ -530,7 +532,7 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
         }
         float ws[C::kATiles];   // MXFP4: the weight scales were applied inside the MMA
 #pragma unroll
-        for (int tile = 0; tile < C::kATiles; ++tile) ws[tile] = kFp4 ? 1.0f : ws_tile[(sub + tile) * C::kKBlocks + kb];
+        for (int tile = 0; tile < C::kATiles; ++tile) ws[tile] = kFp4 ? 1.0f : ws_tile[((kGateUp ? sub : 2 * sub) + tile) * C::kKBlocks + kb];
 #pragma unroll
         for (int sl = 0; sl < C::kSlices; ++sl)
           if (sl < nsl) {
