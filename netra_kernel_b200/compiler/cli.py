@@ -27,6 +27,8 @@ def _parser() -> argparse.ArgumentParser:
     c.add_argument("--target", default=TARGET)
     c.add_argument("--allow-experimental", action="store_true")
     c.add_argument("--checkpoint-hash", default="")
+    c.add_argument("--binding-sets", type=int, default=1,
+                   help="emit the profile this many times: one set of bound pointers and one captured graph each, one workspace")
     for name in ("inspect", "explain", "validate"):
         s = sub.add_parser(name)
         s.add_argument("engine")
@@ -46,7 +48,8 @@ def main(argv=None) -> int:
             if args.target != TARGET:
                 raise NetraCompilerError(f"this compiler emits {TARGET} engines only")
             engine = compile_engine(args.model, args.profile, args.output, library_root=root,
-                                    allow_experimental=args.allow_experimental, checkpoint_hash=args.checkpoint_hash)
+                                    allow_experimental=args.allow_experimental, checkpoint_hash=args.checkpoint_hash,
+                                    binding_sets=args.binding_sets)
             print("engine_id", engine["engine_id"])
         elif args.command == "validate":
             engine = validate_engine_directory(args.engine)

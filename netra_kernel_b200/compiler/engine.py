@@ -115,7 +115,13 @@ def _argument_records(planned: PlannedOperation, plan: Plan, offsets: dict[str, 
 
 
 def compile_engine(model_path: Path | str, profile_name: str, output: Path | str, *, library_root: Path | str | None = None,
-                   allow_experimental: bool = False, checkpoint_hash: str = "", copy_cubin: bool = True) -> dict[str, Any]:
+                   allow_experimental: bool = False, checkpoint_hash: str = "", copy_cubin: bool = True,
+                   binding_sets: int = 1) -> dict[str, Any]:
+    """``binding_sets`` > 1 emits the profile that many times (``name``, ``name@1``, ...): every entry is a profile id of its
+    own at run time - its own bound pointers and captured graph - over the engine's one workspace and code object.  A
+    serving loop that double-buffers its activations binds one input / output pair per set and alternates the profile id."""
+    if not 1 <= int(binding_sets) <= 8:
+        raise ValidationError("binding_sets must be between 1 and 8")
     library = KernelLibrary.discover(library_root)
     model = load_model(Path(model_path))
     tp = int(model["deployment"]["tensor_parallel"])
@@ -201,8 +207,9 @@ def compile_engine(model_path: Path | str, profile_name: str, output: Path | str
         **identity, "engine_id": "ne_" + stable_hash(identity)[:24],
         "required_cuda": {"minimum": REQUIRED_CUDA_MINIMUM, "cubin_arch": TARGET},
         "workspace_bytes": memory["workspace_bytes"], "tensor_parallel": tp,
-        "profiles": [{"name": profile.name, "guards": {k: g.to_dict() for k, g in profile.guards},
-                      "tensor_parallel": profile.tensor_parallel, "quantization": profile.quantization}],
+        "profiles": [{"name": profile.name if i == 0 else f"{profile.name}@{i}", "guards": {k: g.to_dict() for k, g in profile.guards},
+                      "tensor_parallel": profile.tensor_parallel, "quantization": profile.quantization}
+                     for i in range(int(binding_sets))],
         "fallbacks": fallbacks, "kernel_symbols": sorted(set(symbols)), "selected_tactics": selected,
         "artifact_files": artifact_files,
         "deployment_guards": {"device": "NVIDIA B200", "compute_capability": "10.0", "sm_count": opts["sm_count"],

@@ -197,6 +197,19 @@ def test_mxfp4_model_selects_the_block_scaled_tactics_and_a_pack_step(tmp_path):
         compile_engine(MODEL, "decode_t256_mxfp4", tmp_path / "y", copy_cubin=False)    # an FP8 model
 
 
+def test_binding_sets_replicate_the_profile_over_one_workspace(tmp_path):
+    """binding_sets = 2: two profile ids with the same guards (their own pointers and graph at run time), one operation
+    list, one workspace; the directory still validates."""
+    one = compile_engine(MODEL, "decode_t256", tmp_path / "one", copy_cubin=False)
+    two = compile_engine(MODEL, "decode_t256", tmp_path / "two", binding_sets=2)
+    assert [p["name"] for p in two["profiles"]] == ["decode_t256", "decode_t256@1"]
+    assert two["profiles"][0]["guards"] == two["profiles"][1]["guards"] == one["profiles"][0]["guards"]
+    assert two["workspace_bytes"] == one["workspace_bytes"] and two["operations"] == one["operations"]
+    validate_engine_directory(tmp_path / "two")
+    with pytest.raises(ValidationError):
+        compile_engine(MODEL, "decode_t256", tmp_path / "bad", copy_cubin=False, binding_sets=0)
+
+
 def test_mxfp4_pair_blocks_byte_transform():
     """CPU statement of the pack step: every source byte appears once, rows of a tile pair end up side by side."""
     rng = np.random.default_rng(3)

@@ -171,6 +171,37 @@ def test_engine_on_mxfp4_weights_equals_the_fused_layer_call(tmp_path):
         session.close()
 
 
+def test_two_binding_sets_share_one_engine(tmp_path, expert_weights):
+    """An engine compiled with two binding sets: profile ids 0 and 1 are bound to different input / output buffers, captured
+    separately and launched alternately over the one workspace; each reproduces the result of its own input."""
+    tokens = 256
+    tensors, hidden, router_w, _ = _tensors(expert_weights, tokens)
+    other, _, _ = synth.make_activations(tokens, None, seed=11)
+    compile_engine(MODEL, "decode_t256", tmp_path / "e", binding_sets=2)
+    session = er.EngineSession(tmp_path / "e", device_id=0, enable_graph_capture=True)
+    bound = session.prepare_weights(tensors)
+    second = {**bound, "hidden": other.cuda(), "output": torch.zeros(tokens, 2048, dtype=torch.bfloat16, device="cuda")}
+    torch.cuda.synchronize()
+    session.bind(bound, profile_id=0)
+    session.bind(second, profile_id=1)
+    session.finalize()
+    session.prepare(_stream(), profile_id=0)
+    session.prepare(_stream(), profile_id=1)
+    for _ in range(3):
+        session.launch(_stream(), profile_id=0)
+        session.launch(_stream(), profile_id=1)
+    torch.cuda.synchronize()
+    assert _status_words(session) == [0, 0, 0, 0]
+    from netra_kernel_b200.moe import RoutedMoELayer
+    layer = RoutedMoELayer(tensors["router_weight"], *(t.cuda() for t in expert_weights), tokens)
+    for io in (bound, second):
+        want = layer(io["hidden"]).clone()
+        torch.cuda.synchronize()
+        assert torch.equal(io["output"].view(torch.int16), want.view(torch.int16))
+    assert not torch.equal(bound["output"], second["output"])
+    session.close()
+
+
 def test_status_codes_for_guards_and_call_order(tmp_path, expert_weights):
     lib = er.load()
     tensors, *_ = _tensors(expert_weights, 16)
