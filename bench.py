@@ -1187,6 +1187,11 @@ def run_expert_parallel(args) -> None:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             layer(hidden, out=out)
+        # the same call bound to a second input / output pair, for the double-buffered end-to-end loop
+        hidden2, out2 = torch.empty_like(hidden), torch.empty_like(out)
+        graph2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph2, stream=stream):
+            layer(hidden2, out=out2)
         launches = layer.launches_per_call(tokens)
     else:
         layer = ExpertParallelMoELayer(plan, router_dev, *local, max_local_tokens=tokens, exchange=args.ep_exchange)
@@ -1259,7 +1264,8 @@ def run_expert_parallel(args) -> None:
         e2e_serial_ms = max_over_ranks(e0.elapsed_time(e1) / steps)
         # the same with double-buffered copies on their own streams (what `e2e` reports)
         barrier()
-        piped_ms, _, e2e_host_api = time_e2e_pipelined(step, hidden, out, hidden_cpu, steps, warmup, stream)
+        piped_ms, _, e2e_host_api = time_e2e_pipelined(step, hidden, out, hidden_cpu, steps, warmup, stream,
+                                                       second=(graph2.replay, hidden2, out2) if graph is not None else None)
         barrier()
         e2e_ms = max_over_ranks(piped_ms)
 
@@ -1296,7 +1302,7 @@ def run_expert_parallel(args) -> None:
     used_graph = graph is not None
     if args.extras and args.ep_exchange == "peer":
         layer.close()
-        del layer, graph, local
+        del layer, graph, graph2, local
         torch.cuda.empty_cache()
         parity, stack = expert_parallel_extras(args, plan, dev, stream, sync, router_dev)
     if rank == 0:
@@ -1325,8 +1331,11 @@ def run_expert_parallel(args) -> None:
             "stage_us_rank0": stage_us,
             "e2e": {"value": world * tokens / (e2e_ms / 1e3), "unit": UNIT, "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": tokens * 2048 * 2, "d2h_bytes_per_step": tokens * 2048 * 2,
-                    "how": "every rank copies its tokens from pinned host memory and its result back every step; the copies run on "
-                           "their own streams with two staging slots, so they overlap the neighbouring steps' compute",
+                    "how": ("every rank copies its tokens from pinned host memory into one of two device buffers and its result back from "
+                            "one of two every step; the call of step i is a captured graph bound to pair i mod 2, the copies run on "
+                            "their own streams and overlap the neighbouring steps' compute") if e2e_host_api.endswith("(two bound calls)") else
+                           ("every rank copies its tokens from pinned host memory and its result back every step; the copies run on "
+                            "their own streams with two staging slots, so they overlap the neighbouring steps' compute"),
                     "copies_enqueued_with": e2e_host_api, "serial_ms_per_step": e2e_serial_ms},
             "roofline": {"bound": "hbm", "kernel": ("netra_moe_gate_up_umma_sm100 + netra_moe_down_umma_sm100" if args.ep_exchange != "peer"
                                                     else "netra_moe_gate_up_tokmajor_sm100 + netra_ep_down_return_umma_sm100" if world * tokens >= 1024
