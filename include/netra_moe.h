@@ -138,6 +138,7 @@ typedef struct netra_moe_workspace_layout {
   uint64_t logits_f32;    /* [tokens, 256] f32: tensor-core router output before the exact rounding (calls above 1024 rows) */
   uint64_t wnorm;         /* [256] f32: Euclidean norms of the router rows (upper bounds) */
   uint64_t router_stats;  /* [4] u32: word 0 counts the logits recomputed in FP64 since the layer was created */
+  uint64_t gemm_ready;    /* [1024] u32: per-unit arrival counters of the launch that runs both projections (decode sizes) */
 } netra_moe_workspace_layout_t;
 
 int netra_moe_workspace_layout_query(uint32_t tokens, netra_moe_workspace_layout_t* output);
@@ -358,14 +359,17 @@ int netra_ep_layer_destroy(netra_ep_layer_t* layer);
 
 /* Block size and dynamic shared memory of the tensor-core kernels (which: 0 gate_up, 1 down, 2 and 3 their
  * token-major forms, 4 token-major down with FP16 rows, 5 tensor-core router, 6 and 7 gate_up and down on MXFP4 weights,
- * 8 and 9 their token-major forms), so
+ * 8 and 9 their token-major forms, 10 gate_up and down in one launch), so
  * that an engine manifest written ahead of time can be checked against the built library. */
 int netra_moe_kernel_launch_info(uint32_t which, uint32_t* block_threads, uint32_t* dynamic_smem_bytes);
 
 /* The two grouped GEMMs exist in two forms: swap-AB (weights are the MMA M dimension; decode sizes) and
  * token-major (128 token rows x 256 weight rows per MMA; from an average of 32 rows per routed expert).
  * mode 0 (default) picks by the token count of the call, mode 1 always uses the swap-AB kernels.  Both
- * forms produce identical results. */
+ * forms produce identical results.  mode 2 = swap-AB with the two projections in one launch for calls of up to 1,024
+ * tokens on E4M3 weights (netra_moe_gate_up_down_umma_sm100: the down half starts on an expert chunk's rows as soon as
+ * the gate_up half has written them): the same results, one launch fewer, measured 4 us slower per 256-token call
+ * than two launches - a recorded tactic. */
 int netra_moe_layer_set_gemm_mode(netra_moe_layer_t* layer, uint32_t mode);
 
 /* Where the token-major gate_up takes its token rows from.  in_gemm 0 (default): an expert-sorted copy of the quantised

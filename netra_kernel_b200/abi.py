@@ -18,7 +18,7 @@ class WorkspaceLayout(ctypes.Structure):
         (name, c_u64) for name in (
             "logits_bf16", "topk_ids", "topk_weights", "perm", "inv_perm", "counts", "offsets",
             "seg_hist", "a_fp8", "a_scale", "h_fp8", "h_scale", "down_f32", "status", "logits_f32", "wnorm",
-            "router_stats")]
+            "router_stats", "gemm_ready")]
 
 
 class LayerDesc(ctypes.Structure):

@@ -205,7 +205,7 @@ def routed_moe_layer_graph(model: dict[str, Any], profile: ShapeProfile) -> Grap
     ops += [
         op("gather_rows", "moe_sort", "gather_quantized_rows", ["perm", "a_fp8", "a_scale"], ["a_fp8", "a_scale"],
            {"hidden": hidden, "top_k": c["top_k"], "scale_block": c["scale_block"]},
-           semantics("gather_rows.ptr3_u32.v1", "fp8e4m3_f32", "fp8_e4m3_per_token_block128_amax448",
+           semantics("gather_rows.ptr3_u32_ptr_u32.v1", "fp8e4m3_f32", "fp8_e4m3_per_token_block128_amax448",
                      "sorted_rows_first.token_rows_after_pairs", "copy.v1")),
         op("gate_up", "moe_fp8_grouped_gemm", "gate_up_silu_requant", ["a_fp8", "a_scale", "w13", "w13_scale", "offsets"],
            ["h_fp8", "h_scale", "status"], gemm_constants,

@@ -122,6 +122,8 @@ int umma_setup() {
   if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(gate_up)", e);
   e = cudaFuncSetAttribute(netra_moe_down_umma_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, down_smem_bytes());
   if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(down)", e);
+  e = cudaFuncSetAttribute(netra_moe_gate_up_down_umma_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, gate_up_down_smem_bytes());
+  if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(gate_up_down)", e);
   e = cudaFuncSetAttribute(netra_moe_gate_up_mxfp4_umma_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, gate_up_mxfp4_smem_bytes());
   if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(gate_up_mxfp4)", e);
   e = cudaFuncSetAttribute(netra_moe_down_mxfp4_umma_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, down_mxfp4_smem_bytes());
@@ -174,12 +176,16 @@ struct netra_moe_layer {
   int sm_count;
   int device;
   uint32_t launches;
-  uint32_t gemm_mode;     // 0: pick the GEMM form by size, 1: always the swap-AB (decode) kernels
+  uint32_t gemm_mode;     // 0: pick the GEMM form by size, 1: always the swap-AB (decode) kernels, 2: swap-AB, both projections in one launch
   uint32_t router_mode;   // 0: pick the router by size, 1: always the FP64 tensor-core router, 2: as 0 with every logit exact
   uint32_t partial_f16;   // 1: the token-major down projection writes FP16 partial rows (prefill contract)
   bool gather_rows_in_gemm;   // the token-major gate_up gathers its rows with four-row TMA gathers (slower; kept as a recorded tactic)
   bool prequantised;      // set for the duration of a call whose token rows were quantised by the fused norm kernel
 };
+
+namespace {
+bool layer_merged_gemm(const netra_moe_layer* layer, uint32_t pairs);
+}
 
 extern "C" {
 
@@ -282,6 +288,7 @@ int netra_moe_workspace_layout_query(uint32_t tokens, netra_moe_workspace_layout
   out->logits_f32 = take(t * kRouted * 4);
   out->wnorm = take(kRouted * 4);
   out->router_stats = take(16);
+  out->gemm_ready = take(kReadyWords * 4);
   out->total_bytes = o;
   return 0;
 }
@@ -351,8 +358,9 @@ int netra_moe_layer_create(const netra_moe_layer_desc_t* desc, netra_moe_layer_t
 uint32_t netra_moe_layer_launch_count(const netra_moe_layer_t* layer, uint32_t tokens) {
   if (layer == nullptr) return 0;
   uint32_t n = tokens <= (uint32_t)kSortSmallMaxRows ? layer->launches - 2 : layer->launches;
+  if (layer_merged_gemm(layer, tokens * kTopK)) --n;   // both projections in one launch
   if (layer->gather_rows_in_gemm && layer->desc.weights_tiled != kWeightsMxfp4 &&
-      use_tokmajor(layer->device, (uint64_t)tokens * kTopK, kRouted) && layer->gemm_mode != 1) --n;   // no row gather
+      use_tokmajor(layer->device, (uint64_t)tokens * kTopK, kRouted) && layer->gemm_mode == 0) --n;   // no row gather
   return n;
 }
 
@@ -368,7 +376,14 @@ bool use_umma_router(const netra_moe_layer* layer, uint32_t tokens) {
   return tokens > kRouterK8MaxRows && layer->router_mode != 1;
 }
 bool layer_tokmajor(const netra_moe_layer* layer, uint32_t pairs) {
-  return layer->gemm_mode != 1 && use_tokmajor(layer->device, pairs, kRouted);
+  return layer->gemm_mode == 0 && use_tokmajor(layer->device, pairs, kRouted);
+}
+// Recorded tactic (gemm_mode 2): both projections in one launch.  Measured at 256 tokens: 164.4 us per call against 160.4 us
+// for two launches - every CTA reaches the boundary between the halves at the same time (the items are spread evenly), so
+// the drained pipeline and the second set-up idle the HBM as long as the launch gap did.  (The work-item units fit the
+// counter table up to 8,192 + 1,024 rows in 32-row chunks over 257 groups: 545 units.)
+bool layer_merged_gemm(const netra_moe_layer* layer, uint32_t pairs) {
+  return layer->gemm_mode == 2 && layer->desc.weights_tiled != kWeightsMxfp4 && pairs <= (uint32_t)kTokMajorMinRowsPerExpert * kRouted;
 }
 // FP16 partial rows are an output format of the E4M3 token-major down projection
 bool use_f16_partials(const netra_moe_layer* layer, uint32_t pairs) {
@@ -403,6 +418,8 @@ int launch_stage(netra_moe_layer* layer, uint32_t stage, const void* hidden, con
   const uint32_t nseg = (pairs + kSortSegment - 1) / kSortSegment;
   const bool tokmajor = layer_tokmajor(layer, pairs);
   const bool mxfp4 = layer->desc.weights_tiled == kWeightsMxfp4;
+  const bool merged = layer_merged_gemm(layer, pairs);
+  uint32_t* gemm_ready = (uint32_t*)(ws + L.gemm_ready);
   switch (stage) {
     case 0:
       if (use_umma_router(layer, tokens)) {
@@ -445,10 +462,15 @@ int launch_stage(netra_moe_layer* layer, uint32_t stage, const void* hidden, con
       break;
     case 5:   // the gathering gate_up fetches its token rows itself: no expert-sorted copy is made for it
       if (!(tokmajor && layer->gather_rows_in_gemm && !mxfp4))
-        netra_moe_gather_rows_sm100<<<(pairs + 7) / 8, 256, 0, stream>>>(a_fp8, a_scale, perm, tokens);
+        netra_moe_gather_rows_sm100<<<(pairs + 7) / 8, 256, 0, stream>>>(a_fp8, a_scale, perm, tokens, merged ? gemm_ready : nullptr,
+                                                                         (uint32_t)kReadyWords);
       break;
     case 6:
-      if (mxfp4 && tokmajor)
+      if (merged)
+        netra_moe_gate_up_down_umma_sm100<<<layer->sm_count, kGemmThreads, gate_up_down_smem_bytes(), stream>>>(
+            layer->tm_w13, layer->tm_a32, layer->tm_w2, layer->tm_h32, a_scale, layer->desc.w13_scale_f32, layer->desc.w2_scale_f32, offsets,
+            h_fp8, h_scale, down, kRouted + 1, layer->desc.weights_tiled, gemm_ready, status);
+      else if (mxfp4 && tokmajor)
         netra_moe_gate_up_mxfp4_tokmajor_sm100<<<layer->sm_count, kTmThreads, gate_up_mxfp4_tokmajor_smem_bytes(), stream>>>(
             layer->tm_w13, layer->tm_a128, a_scale, (const uint8_t*)layer->desc.w13_scale_f32, offsets, h_fp8, h_scale, kRouted + 1,
             status);
@@ -472,6 +494,8 @@ int launch_stage(netra_moe_layer* layer, uint32_t stage, const void* hidden, con
             h_scale, kRouted + 1, layer->desc.weights_tiled, status);
       break;
     case 7:
+      if (merged)
+        break;      // the down projection ran inside stage 6's launch
       if (mxfp4 && tokmajor)
         netra_moe_down_mxfp4_tokmajor_sm100<<<layer->sm_count, kTmThreads, down_mxfp4_tokmajor_smem_bytes(), stream>>>(
             layer->tm_w2, layer->tm_h128, h_scale, (const uint8_t*)layer->desc.w2_scale_f32, offsets, down, kRouted + 1, status + 1);
@@ -707,17 +731,17 @@ int netra_ep_unpack_rows_launch(float* down, const float* back_slots, const int3
 }
 
 int netra_moe_kernel_launch_info(uint32_t which, uint32_t* block_threads, uint32_t* dynamic_smem_bytes) {
-  if (!block_threads || !dynamic_smem_bytes || which > 9) return fail("kernel_launch_info: bad argument");
-  *block_threads = (which < 2 || which == 6 || which == 7) ? kGemmThreads : which == 5 ? kRtThreads : kTmThreads;
-  const int bytes[10] = {gate_up_smem_bytes(), down_smem_bytes(), gate_up_tokmajor_smem_bytes(), down_tokmajor_smem_bytes(),
+  if (!block_threads || !dynamic_smem_bytes || which > 10) return fail("kernel_launch_info: bad argument");
+  *block_threads = (which < 2 || which == 6 || which == 7 || which == 10) ? kGemmThreads : which == 5 ? kRtThreads : kTmThreads;
+  const int bytes[11] = {gate_up_smem_bytes(), down_smem_bytes(), gate_up_tokmajor_smem_bytes(), down_tokmajor_smem_bytes(),
                          down_tokmajor_f16_smem_bytes(), router_umma_smem_bytes(), gate_up_mxfp4_smem_bytes(), down_mxfp4_smem_bytes(),
-                         gate_up_mxfp4_tokmajor_smem_bytes(), down_mxfp4_tokmajor_smem_bytes()};
+                         gate_up_mxfp4_tokmajor_smem_bytes(), down_mxfp4_tokmajor_smem_bytes(), gate_up_down_smem_bytes()};
   *dynamic_smem_bytes = (uint32_t)bytes[which];
   return 0;
 }
 
 int netra_moe_layer_set_gemm_mode(netra_moe_layer_t* layer, uint32_t mode) {
-  if (layer == nullptr || mode > 1) return fail("layer_set_gemm_mode: null layer or unknown mode");
+  if (layer == nullptr || mode > 2) return fail("layer_set_gemm_mode: null layer or unknown mode");
   layer->gemm_mode = mode;
   return 0;
 }

@@ -715,7 +715,10 @@ netra_moe_sort_small_sm100(int32_t* __restrict__ perm, int32_t* __restrict__ inv
 // One warp per row (2048 B codes + 64 B scales).  grid ceil(pairs/8), block 256.
 extern "C" __global__ void __launch_bounds__(256)
 netra_moe_gather_rows_sm100(uint8_t* __restrict__ a_fp8, float* __restrict__ a_scale,
-                            const int32_t* __restrict__ perm, uint32_t rows) {
+                            const int32_t* __restrict__ perm, uint32_t rows, uint32_t* __restrict__ ready, uint32_t ready_words) {
+  // ready (may be null): the per-unit arrival counters of the launch that follows (both projections in one kernel) start at zero
+  if (blockIdx.x == 0 && ready != nullptr)
+    for (uint32_t i = threadIdx.x; i < ready_words; i += blockDim.x) ready[i] = 0;
   const int pairs = (int)rows * kTopK;
   const int pos = blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;

@@ -242,16 +242,27 @@ struct Cfg {
                                     2 * 4 * kColsPerGroup * 4 + 2 * 264 * 4 + kItemList * 16 + 512;
 };
 
-template <bool kGateUp, bool kFp4 = false>
-__device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const CUtensorMap* tm_x32,
+// kChain: 0 = a kernel of its own.  1 and 2 = the two halves of netra_moe_gate_up_down_umma_sm100, one launch for both
+// projections: the gate_up half (1) counts, per unit of four work items (an expert's token chunk), the epilogue groups
+// that have written their part of the intermediate rows (`ready[unit]`, two per item); the down half (2), whose units
+// are the same chunks in the same order, makes its producer wait for the eight arrivals of a unit before it fetches that
+// unit's rows.  Every CTA finishes its gate_up items before it starts on down items and nothing in the gate_up half waits
+// for another CTA, so with all CTAs resident (grid <= SM count, one CTA per SM) the wait always ends; it is bounded anyway.
+// Returns false when this CTA gave up on a wait.
+template <bool kGateUp, bool kFp4 = false, int kChain = 0>
+__device__ __forceinline__ bool grouped_gemm_body(const CUtensorMap* tm_w, const CUtensorMap* tm_x32,
                                                   const CUtensorMap* tm_x64, const CUtensorMap* tm_x128,
                                                   const float* __restrict__ x_scale, const float* __restrict__ w_scale,
                                                   const uint8_t* __restrict__ w_scale_atoms,
                                                   const int32_t* __restrict__ offsets, uint8_t* __restrict__ h_fp8,
                                                   float* __restrict__ h_scale, float* __restrict__ down,
                                                   float* const* __restrict__ row_ptr, uint32_t num_groups, uint32_t w_tiled,
-                                                  uint32_t* status) {
+                                                  uint32_t* status, uint32_t* __restrict__ ready = nullptr,
+                                                  uint32_t* tmem_chain = nullptr) {
+  // tmem_chain (chained halves): a CTA may allocate TMEM only until it gives up its permit, so the first half allocates
+  // and hands the base address on, the second half frees it
   using C = Cfg<kGateUp, kFp4>;
+  static_assert(kChain == 0 || (!kFp4 && C::kNTiles == 4), "the chained halves share units of four work items");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* stage_base = smem;
@@ -268,7 +279,8 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
   uint64_t* tempty_bar = tfull_bar + C::kAccStages;   // [C::kAccStages]
   uint64_t* sfull_bar = tempty_bar + C::kAccStages;   // [kScaleSlots]
   uint64_t* sempty_bar = sfull_bar + C::kScaleSlots;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sempty_bar + C::kScaleSlots);
+  uint64_t* hdone_bar = sempty_bar + C::kScaleSlots;  // [4] (chained gate_up half): both epilogue groups have stored an item's rows
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(hdone_bar + 4);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -280,6 +292,7 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
     for (int s = 0; s < C::kStages; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
     for (int a = 0; a < C::kAccStages; ++a) { mbar_init(smem_u32(&tfull_bar[a]), 1); mbar_init(smem_u32(&tempty_bar[a]), 8); }
     for (int a = 0; a < C::kScaleSlots; ++a) { mbar_init(smem_u32(&sfull_bar[a]), 1); mbar_init(smem_u32(&sempty_bar[a]), 8); }
+    for (int a = 0; a < 4; ++a) mbar_init(smem_u32(&hdone_bar[a]), 2);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -310,11 +323,12 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
       run += cnt[j];
     }
   }
-  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
+  if (kChain != 2 && warp == 1) tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = kChain == 2 ? *tmem_chain : *tmem_slot;
+  if constexpr (kChain == 1) *tmem_chain = tmem_base;
   const uint32_t tmem_scale = tmem_base + (uint32_t)(C::kAccStages * C::kAccCols);   // A scales per tile, then the B scales
   if constexpr (kFp4) {
     // the token rows carry FP32 scales that the promotion step applies: inside the MMA they count as 2^0 (0x7f)
@@ -343,6 +357,17 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
   };
 
   if (warp == 0) {
+    if (kChain == 1 && lane == 1) {
+      // =========================== publisher (chained gate_up half) ===========================
+      // item n's rows are in memory once both epilogue groups have arrived; release them to the other CTAs' down halves
+      uint32_t n_item = 0;
+      for (int item = first_item; item < total_items; item += stride, ++n_item) {
+        if (!mbar_wait(smem_u32(&hdone_bar[n_item & 3]), (n_item >> 2) & 1, abort_flag)) {
+          status[0] = kStatusEpilogueTimeout; *abort_flag = 1; break;
+        }
+        asm volatile("red.release.gpu.global.add.u32 [%0], 2;" ::"l"(ready + (item >> 2)) : "memory");
+      }
+    }
     // =========================== TMA producer ===========================
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)tm_w) : "memory");
@@ -353,6 +378,20 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
       bool ok = true;
       for (int item = first_item; ok && item < total_items; item += stride, ++n_item) {
         const Item w = get_item((int)n_item, item);
+        if constexpr (kChain == 2) {
+          // the unit's intermediate rows and their scales were written by other CTAs' epilogues: wait for all eight
+          // epilogue groups, then order the copy engine's reads after what this thread has now observed
+          const uint32_t* flag = ready + (item >> 2);
+          uint32_t seen = 0, spin = 0;
+          for (; spin < kSpinLimit; ++spin) {
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+            if (seen >= 8u) break;
+            if ((spin & 0xff) == 0xff && *abort_flag != 0) break;
+            __nanosleep(64);
+          }
+          if (seen < 8u) { status[0] = kStatusProducerTimeout; *abort_flag = 1; ok = false; break; }
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
         const int box = (C::kTokMax == 32 || w.m_valid <= 32) ? 32 : 64;
         const CUtensorMap* tm_x = box == 32 ? tm_x32 : tm_x64;
         const uint32_t bytes = C::kStageTiles * C::kWTxBytes + C::kKbPerLoad * box * kBlock + C::kScaleStageBytes;
@@ -597,6 +636,11 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
           }
         }
         group_barrier(grp);   // red[] is free for the next item
+        if constexpr (kChain == 1) {
+          // every thread of the group has issued its stores of this item's rows before the barrier above; the publication
+          // (a device-wide release) is left to an idle lane of warp 0 so that it does not hold up the next item's hand-offs
+          if (gw == 0 && lane == 0) mbar_arrive(smem_u32(&hdone_bar[n_item & 3]));
+        }
       } else {
         // row_ptr (expert parallelism): each output row goes to its own destination, possibly a peer GPU's memory
 #pragma unroll
@@ -615,12 +659,21 @@ __device__ __forceinline__ void grouped_gemm_body(const CUtensorMap* tm_w, const
   // ---- teardown
   tc_fence_before();
   __syncthreads();
-  if (*abort_flag != 0) __nanosleep(200000);   // let copies already in flight land before the CTA exits
-  if (warp == 1) {
+  const bool gave_up = *abort_flag != 0;
+  if (gave_up) __nanosleep(200000);   // let copies already in flight land before the CTA exits
+  if (warp == 1 && (kChain != 1 || gave_up)) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, C::kTmemCols);
   }
+  if constexpr (kChain == 1) {
+    // the shared memory is about to be carved up again: retire this half's barriers first
+    if (threadIdx.x == 0)
+      for (int b = 0; b < 2 * C::kStages + 2 * C::kAccStages + 2 * C::kScaleSlots + 4; ++b)
+        asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(&bars[b])) : "memory");
+    __syncthreads();
+  }
+  return !gave_up;
 }
 
 extern "C" __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -691,6 +744,24 @@ netra_moe_widen_scales_bf16_sm100(float* __restrict__ dst, const uint16_t* __res
   if (i < count) dst[i] = bf16_bits_to_f32(src[i]);
 }
 
+// Both projections in one launch (decode sizes, E4M3 weights): see kChain above.  ready: one zeroed word per unit
+// (at most kReadyWords); zeroed by netra_moe_gather_rows_sm100, the launch before this one.
+constexpr int kReadyWords = 1024;
+extern "C" __global__ void __launch_bounds__(kGemmThreads, 1)
+netra_moe_gate_up_down_umma_sm100(const __grid_constant__ CUtensorMap tm_w13, const __grid_constant__ CUtensorMap tm_a32,
+                                  const __grid_constant__ CUtensorMap tm_w2, const __grid_constant__ CUtensorMap tm_h32,
+                                  const float* a_scale, const float* w13_scale, const float* w2_scale, const int32_t* offsets,
+                                  uint8_t* h_fp8, float* h_scale, float* down, uint32_t num_groups, uint32_t w_tiled, uint32_t* ready,
+                                  uint32_t* status) {
+  uint32_t tmem = 0;
+  if (!grouped_gemm_body<true, false, 1>(&tm_w13, &tm_a32, &tm_a32, &tm_a32, a_scale, w13_scale, nullptr, offsets, h_fp8, h_scale, nullptr,
+                                         nullptr, num_groups, w_tiled, status, ready, &tmem))
+    return;
+  grouped_gemm_body<false, false, 2>(&tm_w2, &tm_h32, &tm_h32, &tm_h32, h_scale, w2_scale, nullptr, offsets, nullptr, nullptr, down, nullptr,
+                                     num_groups, w_tiled, status + 1, ready, &tmem);
+}
+
+int gate_up_down_smem_bytes() { return Cfg<true>::kSmemBytes > Cfg<false>::kSmemBytes ? Cfg<true>::kSmemBytes : Cfg<false>::kSmemBytes; }
 int gate_up_smem_bytes() { return Cfg<true>::kSmemBytes; }
 int down_smem_bytes() { return Cfg<false>::kSmemBytes; }
 int gate_up_mxfp4_smem_bytes() { return Cfg<true, true>::kSmemBytes; }

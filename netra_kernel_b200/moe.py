@@ -133,7 +133,8 @@ class RoutedMoELayer:
         return self._keep[1], self._keep[3]
 
     def set_gemm_mode(self, mode: int) -> None:
-        """0: the layer picks the grouped-GEMM form by token count (token-major from 1,024 tokens); 1: always swap-AB."""
+        """0: the layer picks the grouped-GEMM form by token count (token-major from 1,024 tokens); 1: always swap-AB;
+        2: swap-AB with both projections in one launch up to 1,024 tokens (same results, slower: a recorded tactic)."""
         abi.check(self.lib.netra_moe_layer_set_gemm_mode(self.handle, mode), "layer_set_gemm_mode")
 
     def set_row_gather(self, in_gemm: bool) -> None:

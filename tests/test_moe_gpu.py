@@ -267,6 +267,28 @@ def test_prefill_fp16_partial_rows_tactic(gpu_weights, expert_weights):
     assert torch.equal(layer(small.cuda()).view(torch.int16), ref_small.view(torch.int16))
 
 
+@pytest.mark.parametrize("tokens,alpha", [(1, 0.0), (16, 0.0), (256, 0.0), (700, 3.0), (1000, 0.0)])
+def test_both_projections_in_one_launch_equal_the_two_launch_form(gpu_weights, tokens, alpha):
+    """The recorded tactic that runs gate_up and down in one launch (the down half waits per expert chunk for the gate_up
+    half's rows): every intermediate and the output must equal the two-launch form bit for bit, call after call (the
+    arrival counters are zeroed by the gather launch each time), also with most experts empty and one far above a chunk."""
+    hidden, router_w, bias = synth.make_activations(tokens, alpha or None, seed=31)
+    layer = make_layer(gpu_weights, router_w, 1024, bias)
+    two = layer.launches_per_call(tokens)
+    out_b, inter_b = run_layer(layer, hidden)
+    layer.set_gemm_mode(2)
+    assert layer.launches_per_call(tokens) == two - 1
+    outs = []
+    for _ in range(3):
+        out_a, inter_a = run_layer(layer, hidden)
+        outs.append(out_a)
+    rows = tokens * 9
+    for key in ("h_fp8", "h_scale", "down"):
+        assert torch.equal(inter_a[key][:rows], inter_b[key][:rows]), key
+    for out_a in outs:
+        assert torch.equal(out_a.view(torch.int16), out_b.view(torch.int16))
+
+
 def test_token_rows_gathered_inside_the_gemm_give_the_same_bytes(gpu_weights):
     """The recorded tactic that skips the expert-sorted copy: the token-major gate_up fetches its rows from token order with
     four-row TMA gathers.  Intermediates and output must equal the default form's bit for bit; one launch fewer."""
