@@ -139,6 +139,7 @@ typedef struct netra_moe_workspace_layout {
   uint64_t wnorm;         /* [256] f32: Euclidean norms of the router rows (upper bounds) */
   uint64_t router_stats;  /* [4] u32: word 0 counts the logits recomputed in FP64 since the layer was created */
   uint64_t gemm_ready;    /* [1024] u32: per-unit arrival counters of the launch that runs both projections (decode sizes) */
+  uint64_t front_counters; /* [128] u32: arrival counters of the one-launch routing front end; zero between launches */
 } netra_moe_workspace_layout_t;
 
 int netra_moe_workspace_layout_query(uint32_t tokens, netra_moe_workspace_layout_t* output);
@@ -371,6 +372,12 @@ int netra_moe_kernel_launch_info(uint32_t which, uint32_t* block_threads, uint32
  * the gate_up half has written them): the same results, one launch fewer, measured 4 us slower per 256-token call
  * than two launches - a recorded tactic. */
 int netra_moe_layer_set_gemm_mode(netra_moe_layer_t* layer, uint32_t mode);
+
+/* mode 1: calls of up to 1,024 tokens run router logits, softmax / top-8 + quantisation and the expert sort in one launch
+ * (netra_moe_route_front_sm100: blocks hand over by last-arriver counters, nothing waits): stage 0 is then the whole
+ * routing front end and stages 1 and 2 launch nothing.  Same results as the three launches of mode 0 (default), two
+ * launches fewer, measured 4 us slower per 256-token call: a recorded tactic. */
+int netra_moe_layer_set_front_mode(netra_moe_layer_t* layer, uint32_t mode);
 
 /* Where the token-major gate_up takes its token rows from.  in_gemm 0 (default): an expert-sorted copy of the quantised
  * rows written by the row-gather stage.  in_gemm 1: no copy; the GEMM's producer fetches the rows from token order with

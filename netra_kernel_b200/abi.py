@@ -18,7 +18,7 @@ class WorkspaceLayout(ctypes.Structure):
         (name, c_u64) for name in (
             "logits_bf16", "topk_ids", "topk_weights", "perm", "inv_perm", "counts", "offsets",
             "seg_hist", "a_fp8", "a_scale", "h_fp8", "h_scale", "down_f32", "status", "logits_f32", "wnorm",
-            "router_stats", "gemm_ready")]
+            "router_stats", "gemm_ready", "front_counters")]
 
 
 class LayerDesc(ctypes.Structure):
@@ -95,6 +95,7 @@ SIGNATURES = {
     "netra_ep_layer_destroy": (c_int, [c_void_p]),
     "netra_moe_kernel_launch_info": (c_int, [c_u32, ctypes.POINTER(c_u32), ctypes.POINTER(c_u32)]),
     "netra_moe_layer_set_gemm_mode": (c_int, [c_void_p, c_u32]),
+    "netra_moe_layer_set_front_mode": (c_int, [c_void_p, c_u32]),
     "netra_moe_layer_set_row_gather": (c_int, [c_void_p, c_u32]),
     "netra_moe_layer_set_router_mode": (c_int, [c_void_p, c_u32]),
     "netra_moe_layer_set_partial_format": (c_int, [c_void_p, c_u32]),

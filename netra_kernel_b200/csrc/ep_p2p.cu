@@ -599,7 +599,8 @@ uint32_t netra_ep_layer_stage_count(void) { return kEpStageCount; }
 
 uint32_t netra_ep_layer_launch_count(const netra_ep_layer_t* L, uint32_t tokens) {
   if (!L) return 0;
-  return kEpStageCount + (tokens <= (uint32_t)kSortSmallMaxRows ? 0 : 2);
+  if (tokens > (uint32_t)kSortSmallMaxRows) return kEpStageCount + 2;                // the sort is three launches
+  return kEpStageCount - (L->route->front_mode == 1 ? 2 : 0);                           // router, top-k and sort as one launch
 }
 
 int netra_ep_layer_launch(netra_ep_layer_t* L, const void* hidden, const float* shared_w, void* out, uint32_t tokens, cudaStream_t stream) {

@@ -139,9 +139,11 @@ int netra_moe_prefill_m768_launch(const void* hidden_fp8, const float* hidden_sc
     e = cudaMemcpyAsync(ws + L.a_scale + (size_t)pairs * netra::kHiddenBlocks * 4, hidden_scale_f32,
                         (size_t)rows * netra::kHiddenBlocks * 4, cudaMemcpyDeviceToDevice, stream);
   if (e != cudaSuccess) return fail_cuda("prefill_m768: cudaMemcpyAsync(token rows)", e);
-  for (uint32_t stage = 2; stage < kStageCount; ++stage)
-    if (int rc = launch_stage(layer, stage, hidden_fp8, nullptr, output_bf16, rows, stream)) return rc;
-  return check_launch("prefill_m768 launch");
+  layer->external_topk = true;      // the routing came from the caller: the sort is a launch of its own
+  int rc = 0;
+  for (uint32_t stage = 2; stage < kStageCount && rc == 0; ++stage) rc = launch_stage(layer, stage, hidden_fp8, nullptr, output_bf16, rows, stream);
+  layer->external_topk = false;
+  return rc ? rc : check_launch("prefill_m768 launch");
 }
 
 // Device status words of the last launches (synchronises): 0 gate_up wait expired, 1 down wait expired, 3 number of

@@ -47,10 +47,11 @@ __device__ __forceinline__ void dmma_m8n8k4(double& c0, double& c1, double a, do
 }
 
 // kKSplit warps share one 16 x 16 output tile, each over 1 / kKSplit of K; block = 2 expert halves x kKSplit warps.
+// part_mem: kKSplit * 4 KiB of shared memory for the K-slices' partial tiles.
 template <int kKSplit>
 __device__ __forceinline__ void router_logits_body(uint16_t* __restrict__ logits, const uint16_t* __restrict__ hidden,
-                                                   const uint16_t* __restrict__ weight, uint32_t rows) {
-  __shared__ double part[kKSplit][2][16][16];
+                                                   const uint16_t* __restrict__ weight, uint32_t rows, double* part_mem) {
+  double (*part)[2][16][16] = reinterpret_cast<double (*)[2][16][16]>(part_mem);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kq = warp % kKSplit, eh = warp / kKSplit;   // K-slice, expert half
   const int tok0 = blockIdx.x * 16;
@@ -119,7 +120,8 @@ __device__ __forceinline__ void router_logits_body(uint16_t* __restrict__ logits
 extern "C" __global__ void __launch_bounds__(256)
 netra_router_logits_bf16_sm100(uint16_t* __restrict__ logits, const uint16_t* __restrict__ hidden,
                                const uint16_t* __restrict__ weight, uint32_t rows) {
-  router_logits_body<4>(logits, hidden, weight, rows);
+  __shared__ double part[4 * 2 * 16 * 16];
+  router_logits_body<4>(logits, hidden, weight, rows, part);
 }
 
 // The same with eight K-slices (block 512): twice the warps per SM for calls too small to fill the GPU
@@ -127,7 +129,8 @@ netra_router_logits_bf16_sm100(uint16_t* __restrict__ logits, const uint16_t* __
 extern "C" __global__ void __launch_bounds__(512)
 netra_router_logits_bf16_k8_sm100(uint16_t* __restrict__ logits, const uint16_t* __restrict__ hidden,
                                   const uint16_t* __restrict__ weight, uint32_t rows) {
-  router_logits_body<8>(logits, hidden, weight, rows);
+  __shared__ double part[8 * 2 * 16 * 16];
+  router_logits_body<8>(logits, hidden, weight, rows, part);
 }
 
 // One hidden row into registers, one warp per row: lane owns the 64 consecutive values [lane*64, +64).
@@ -312,19 +315,19 @@ __device__ __forceinline__ void softmax_top8_store(int32_t* __restrict__ ids9, f
   top8_store(ids9, w9, sel_id, sel_p, shared_w, t, lane);
 }
 
-extern "C" __global__ void __launch_bounds__(128)
-netra_moe_topk_quant_sm100(int32_t* __restrict__ ids9, float* __restrict__ w9,
-                           uint8_t* __restrict__ a_fp8, float* __restrict__ a_scale,
-                           const uint16_t* __restrict__ logits, const float* __restrict__ bias,
-                           const float* __restrict__ shared_w, const uint16_t* __restrict__ hidden,
-                           uint32_t rows, uint32_t row_base) {
-  const int lane = threadIdx.x & 31;
-  const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (t >= (int)rows) return;
+// One token's softmax / top-8 / renormalise and FP8 quantisation by one warp.  kFromL2: the logits were written by other
+// blocks of the same launch, so they are read around the L1.
+template <bool kFromL2>
+__device__ __forceinline__ void topk_quant_token(int32_t* __restrict__ ids9, float* __restrict__ w9,
+                                                 uint8_t* __restrict__ a_fp8, float* __restrict__ a_scale,
+                                                 const uint16_t* logits, const float* __restrict__ bias,
+                                                 const float* __restrict__ shared_w, const uint16_t* __restrict__ hidden,
+                                                 uint32_t row_base, int t, int lane) {
   // lane owns experts lane*8 .. lane*8+7 (ascending id inside the lane)
   float z[8];
   {
-    uint4 v = reinterpret_cast<const uint4*>(logits + (size_t)t * kRouted)[lane];
+    const uint4* src = reinterpret_cast<const uint4*>(logits + (size_t)t * kRouted) + lane;
+    uint4 v = kFromL2 ? __ldcg(src) : *src;
     const uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
@@ -338,6 +341,18 @@ netra_moe_topk_quant_sm100(int32_t* __restrict__ ids9, float* __restrict__ w9,
   }
   softmax_top8_store(ids9, w9, z, shared_w, t, lane);
   if (a_fp8 != nullptr) quantize_hidden_row(a_fp8, a_scale, hidden, t, row_base, lane);   // null: the rows were quantised upstream
+}
+
+extern "C" __global__ void __launch_bounds__(128)
+netra_moe_topk_quant_sm100(int32_t* __restrict__ ids9, float* __restrict__ w9,
+                           uint8_t* __restrict__ a_fp8, float* __restrict__ a_scale,
+                           const uint16_t* __restrict__ logits, const float* __restrict__ bias,
+                           const float* __restrict__ shared_w, const uint16_t* __restrict__ hidden,
+                           uint32_t rows, uint32_t row_base) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (t >= (int)rows) return;
+  topk_quant_token<false>(ids9, w9, a_fp8, a_scale, logits, bias, shared_w, hidden, row_base, t, lane);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -647,30 +662,38 @@ netra_moe_sort_scatter_sm100(int32_t* __restrict__ perm, int32_t* __restrict__ i
 // 1,024 rows).  Same result as the three-launch path; no global scratch.  grid 1, block 1024.
 constexpr int kSortSmallMaxRows = 1024;
 
-extern "C" __global__ void __launch_bounds__(1024)
-netra_moe_sort_small_sm100(int32_t* __restrict__ perm, int32_t* __restrict__ inv_perm, int32_t* __restrict__ counts,
-                           int32_t* __restrict__ offsets, const int32_t* __restrict__ ids9, uint32_t rows) {
-  __shared__ int wbase[32][kRouted];
-  __shared__ int warp_tot[8];
+// kWarps warps of one block; wbase: [kWarps][256] ints and warp_tot: [8] ints of shared memory.  kFromL2: the ids were
+// written by other blocks of the same launch.
+template <int kWarps, bool kFromL2>
+__device__ __forceinline__ void sort_small_body(int32_t* __restrict__ perm, int32_t* __restrict__ inv_perm, int32_t* __restrict__ counts,
+                                                int32_t* __restrict__ offsets, const int32_t* ids9, uint32_t rows,
+                                                int (*wbase)[kRouted], int* warp_tot) {
+  constexpr int kThreads = kWarps * 32;
+  constexpr int kMaxRounds = kSortSmallMaxRows * kTopK / kThreads;     // 32-pair rounds per warp at the largest call: 8 | 16
   const int pairs = (int)rows * kTopK;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int i = threadIdx.x; i < 32 * kRouted; i += 1024) (&wbase[0][0])[i] = 0;
+  for (int i = threadIdx.x; i < kWarps * kRouted; i += kThreads) (&wbase[0][0])[i] = 0;
   __syncthreads();
-  const int rounds = max(1, (pairs + 1023) / 1024);     // 32-pair rounds per warp: 1..8
+  const int rounds = max(1, (pairs + kThreads - 1) / kThreads);
   const int wstart = warp * rounds * 32;
-  int my_e[8];
+  int my_e[kMaxRounds];
 #pragma unroll
-  for (int c = 0; c < 8; ++c) {
+  for (int c = 0; c < kMaxRounds; ++c) {
     const int pair = wstart + c * 32 + lane;
-    my_e[c] = (c < rounds && pair < pairs) ? pair_expert(ids9, pair) : -1;
-    if (my_e[c] >= 0) atomicAdd(&wbase[warp][my_e[c]], 1);   // counts only: order independent
+    int e = -1;
+    if (c < rounds && pair < pairs) {
+      const int32_t* src = ids9 + (pair >> 3) * kSlots + (pair & 7);
+      e = min(max(kFromL2 ? __ldcg(src) : *src, 0), kRouted - 1);
+    }
+    my_e[c] = e;
+    if (e >= 0) atomicAdd(&wbase[warp][e], 1);   // counts only: order independent
   }
   __syncthreads();
   if (threadIdx.x < kRouted) {
     const int e = threadIdx.x;
     int total = 0;
 #pragma unroll 8
-    for (int w = 0; w < 32; ++w) total += wbase[w][e];
+    for (int w = 0; w < kWarps; ++w) total += wbase[w][e];
     counts[e] = total;
     int incl = total;
 #pragma unroll
@@ -689,11 +712,11 @@ netra_moe_sort_small_sm100(int32_t* __restrict__ perm, int32_t* __restrict__ inv
       offsets[kRouted + 1] = running + total + (int)rows;
     }
 #pragma unroll 8
-    for (int w = 0; w < 32; ++w) { int c = wbase[w][e]; wbase[w][e] = running; running += c; }
+    for (int w = 0; w < kWarps; ++w) { int c = wbase[w][e]; wbase[w][e] = running; running += c; }
   }
   __syncthreads();
 #pragma unroll
-  for (int c = 0; c < 8; ++c) {
+  for (int c = 0; c < kMaxRounds; ++c) {
     if (c >= rounds) break;                                // uniform across the block
     const int pair = wstart + c * 32 + lane;
     const int e = my_e[c];
@@ -709,6 +732,57 @@ netra_moe_sort_small_sm100(int32_t* __restrict__ perm, int32_t* __restrict__ inv
     }
     __syncwarp();
   }
+}
+
+extern "C" __global__ void __launch_bounds__(1024)
+netra_moe_sort_small_sm100(int32_t* __restrict__ perm, int32_t* __restrict__ inv_perm, int32_t* __restrict__ counts,
+                           int32_t* __restrict__ offsets, const int32_t* __restrict__ ids9, uint32_t rows) {
+  __shared__ int wbase[32][kRouted];
+  __shared__ int warp_tot[8];
+  sort_small_body<32, false>(perm, inv_perm, counts, offsets, ids9, rows, wbase, warp_tot);
+}
+
+// ------------------------------------------------------------------------------------------
+// The routing front end of a call of up to 1,024 tokens in one launch: router logits, softmax / top-8 / renormalise +
+// FP8 quantisation, expert sort - the three kernels above, handed from block to block by last-arriver counters (no block
+// ever waits for another one):
+//   every block          its 16 tokens x 32 experts of exactly rounded logits (FP64 tensor cores), then one arrival on
+//                        its token tile's counter;
+//   the eighth arrival   of a tile runs the top-8 + quantisation of the tile's 16 tokens, a warp per token, while other
+//                        tiles' router blocks are still at work; then one arrival on the launch's counter;
+//   the last tile        to finish sorts the call's pairs by expert (the single-block sort with sixteen warps) and
+//                        returns the counters to zero for the next launch.
+// counters: [1 + ceil(rows/16)] zeroed words, word 0 for the launch.  grid (ceil(rows/16), 8), block 512.
+// ------------------------------------------------------------------------------------------
+extern "C" __global__ void __launch_bounds__(512)
+netra_moe_route_front_sm100(uint16_t* __restrict__ logits, const uint16_t* __restrict__ hidden, const uint16_t* __restrict__ weight,
+                            int32_t* __restrict__ ids9, float* __restrict__ w9, uint8_t* __restrict__ a_fp8, float* __restrict__ a_scale,
+                            const float* __restrict__ bias, const float* __restrict__ shared_w, int32_t* __restrict__ perm,
+                            int32_t* __restrict__ inv_perm, int32_t* __restrict__ counts, int32_t* __restrict__ offsets,
+                            uint32_t* __restrict__ counters, uint32_t rows, uint32_t row_base) {
+  __shared__ __align__(16) double scratch[8 * 2 * 16 * 16];      // 32 KiB: the router's partial tiles, later the sort's tables
+  __shared__ int warp_tot[8];
+  __shared__ uint32_t arrived;
+  router_logits_body<8>(logits, hidden, weight, rows, scratch);
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) arrived = atomicAdd(&counters[1 + blockIdx.x], 1u);
+  __syncthreads();
+  if (arrived != gridDim.y - 1) return;
+  __threadfence();
+  {
+    const int t = blockIdx.x * 16 + (threadIdx.x >> 5);
+    if (t < (int)rows)
+      topk_quant_token<true>(ids9, w9, a_fp8, a_scale, logits, bias, shared_w, hidden, row_base, t, threadIdx.x & 31);
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) arrived = atomicAdd(&counters[0], 1u);
+  __syncthreads();
+  if (arrived != gridDim.x - 1) return;
+  __threadfence();
+  sort_small_body<16, true>(perm, inv_perm, counts, offsets, ids9, rows, reinterpret_cast<int (*)[kRouted]>(scratch), warp_tot);
+  for (uint32_t i = threadIdx.x; i <= gridDim.x; i += blockDim.x) counters[i] = 0;
 }
 
 // Gather quantised hidden rows into expert-sorted order: row pos <- row (row_base + perm[pos]/8).

@@ -137,6 +137,11 @@ class RoutedMoELayer:
         2: swap-AB with both projections in one launch up to 1,024 tokens (same results, slower: a recorded tactic)."""
         abi.check(self.lib.netra_moe_layer_set_gemm_mode(self.handle, mode), "layer_set_gemm_mode")
 
+    def set_front_mode(self, mode: int) -> None:
+        """1: calls of up to 1,024 tokens run router, top-8 + quantisation and sort in one launch (stage 0; stages 1 and 2
+        then launch nothing); 0 (default): three launches.  Same results; the one-launch form measured slower."""
+        abi.check(self.lib.netra_moe_layer_set_front_mode(self.handle, mode), "layer_set_front_mode")
+
     def set_row_gather(self, in_gemm: bool) -> None:
         """True: the token-major gate_up gathers its token rows with four-row TMA gathers instead of reading an
         expert-sorted copy (same results, slower: a recorded tactic)."""

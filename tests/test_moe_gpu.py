@@ -267,6 +267,29 @@ def test_prefill_fp16_partial_rows_tactic(gpu_weights, expert_weights):
     assert torch.equal(layer(small.cuda()).view(torch.int16), ref_small.view(torch.int16))
 
 
+@pytest.mark.parametrize("tokens,alpha", [(1, 0.0), (15, 0.0), (256, 0.0), (700, 3.0), (1024, 0.5)])
+def test_routing_front_end_in_one_launch_equals_the_three_launches(gpu_weights, tokens, alpha):
+    """The recorded tactic that runs router, top-8 + quantisation and sort as one launch whose blocks hand over by
+    last-arriver counters.  Logits, ids, weights, quantised rows, permutation, counts and offsets must equal the three-launch form bit
+    for bit, call after call (the counters return to zero), with a shared-expert weight and a bias in play."""
+    hidden, router_w, bias = synth.make_activations(tokens, alpha or None, seed=41)
+    shared_w = np.linspace(0.5, 1.5, tokens).astype(np.float32)
+    layer = make_layer(gpu_weights, router_w, 1024, bias)
+    three = layer.launches_per_call(tokens)
+    out_b, inter_b = run_layer(layer, hidden, shared_w)
+    layer.set_front_mode(1)
+    assert layer.launches_per_call(tokens) == three - 2
+    fused = [run_layer(layer, hidden, shared_w) for _ in range(3)]
+    pairs = tokens * 8
+    for out_a, inter_a in fused:
+        for key in ("logits", "topk_ids", "topk_w", "perm", "inv_perm", "counts"):
+            assert torch.equal(inter_a[key], inter_b[key]), key
+        assert torch.equal(inter_a["offsets"][:258], inter_b["offsets"][:258])
+        assert torch.equal(inter_a["a_fp8"][pairs:pairs + tokens], inter_b["a_fp8"][pairs:pairs + tokens])
+        assert torch.equal(inter_a["a_scale"][pairs:pairs + tokens], inter_b["a_scale"][pairs:pairs + tokens])
+        assert torch.equal(out_a.view(torch.int16), out_b.view(torch.int16))
+
+
 @pytest.mark.parametrize("tokens,alpha", [(1, 0.0), (16, 0.0), (256, 0.0), (700, 3.0), (1000, 0.0)])
 def test_both_projections_in_one_launch_equal_the_two_launch_form(gpu_weights, tokens, alpha):
     """The recorded tactic that runs gate_up and down in one launch (the down half waits per expert chunk for the gate_up
