@@ -39,10 +39,11 @@ FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes (read + write) of one grouped gate_up launch at decode T=256, from one ncu capture
 # (dram__bytes_read.sum + dram__bytes_write.sum), with the hash of the kernel source it was taken on:
 # the figure is reported only while that source is unchanged.
-GATE_UP_DRAM_TRAFFIC = {"bytes": 550_046_976, "source": "netra_kernel_b200/csrc/umma_kernels.cu",
-                        "sha256": "bf5fdde7b3edb0dfc2d7c6eff6092472bd7887889d826484626575ba6d990fa0"}
+GATE_UP_DRAM_TRAFFIC = {"bytes": 544_990_037, "source": "netra_kernel_b200/csrc/umma_kernels.cu",
+                        "sha256": "63884baad35be62934a91b2dec096ba9e581627fe7990a13d13e0edef4cc0610"}
 # the same two figures for netra_moe_gate_up_mxfp4_sm100 (MXFP4 weights, T=256); None until captured
-MXFP4_GATE_UP_DRAM_TRAFFIC = {"bytes": None, "source": "netra_kernel_b200/csrc/umma_kernels.cu", "sha256": ""}
+MXFP4_GATE_UP_DRAM_TRAFFIC = {"bytes": 291_713_024, "source": "netra_kernel_b200/csrc/umma_kernels.cu",
+                              "sha256": "63884baad35be62934a91b2dec096ba9e581627fe7990a13d13e0edef4cc0610"}
 STACK_LAYERS = 40
 STACK_TOKENS = 16384
 NVLINK_GBS = 770.0            # measured peer copy per direction per GPU on this pool
