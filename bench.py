@@ -1216,8 +1216,8 @@ def run_expert_parallel(args) -> None:
 
     def expert_block():
         if args.ep_exchange == "peer":
-            layer.launch_stage(7, hidden, out)
-            layer.launch_stage(8, hidden, out)
+            layer.launch_stage(6, hidden, out)      # gate_up (finds the rows of the last call and their flags in place)
+            layer.launch_stage(7, hidden, out)      # down + return
         else:
             layer.launch_expert_block()
 
@@ -1284,8 +1284,8 @@ def run_expert_parallel(args) -> None:
         stage_us = None
         if args.ep_exchange == "peer":
             # each stage between two events, direct launches (small stages read high: the gap includes launch latency)
-            names = ["router", "topk_quant", "sort", "publish_counts", "plan", "push_rows", "wait_rows_and_table", "gate_up",
-                     "down_and_return", "wait_return", "combine"]
+            names = ["router", "topk_quant", "sort", "publish_counts", "plan", "push_rows_and_table", "wait_rows_gate_up",
+                     "down_and_return", "wait_return_combine"]
             reps = min(steps, 50)
             evs = [[torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)] for _ in range(reps)]
             barrier()

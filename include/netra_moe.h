@@ -305,7 +305,7 @@ int netra_ep_unpack_rows_launch(float* down_f32, const float* back_slots_f32, co
  * FP8 rows to the owners' expert-major blocks, FP32 rows back to the senders' sorted order) is done
  * by this library's kernels with stores into the peers' windows and epoch flags; every wait is
  * bounded by wait_timeout_ns and reports through the status words instead of hanging.  One call is
- * netra_ep_layer_stage_count() launches (two more above 1024 tokens), no host read-back, so a
+ * netra_ep_layer_launch_count() launches (eight up to 1024 tokens, ten above), no host read-back, so a
  * caller may capture it into a CUDA graph.  All ranks must make the same sequence of calls.
  *
  * A window is device memory that the peers can write: netra_ep_window_create allocates one
@@ -345,10 +345,11 @@ int netra_ep_layer_create(const netra_ep_layer_desc_t* desc, netra_ep_layer_t** 
 /* hidden BF16 [tokens, 2048], out BF16 [tokens, 2048], shared_weight FP32 [tokens] or NULL (1.0). */
 int netra_ep_layer_launch(netra_ep_layer_t* layer, const void* hidden_bf16, const float* shared_weight_f32, void* out_bf16,
                           uint32_t tokens, cudaStream_t stream);
-/* One stage of the call (0 router, 1 top-8 + quantise, 2 sort, 3 publish counts, 4 plan, 5 push rows,
- * 6 wait + return table, 7 gate_up, 8 down with the return fused in, 9 wait, 10 combine): for per-stage timing, and for
- * running several ranks' calls interleaved stage by stage on one stream of one GPU, where every wait
- * finds its flags already raised. */
+/* One stage of the call (0 router, 1 top-8 + quantise, 2 sort, 3 publish counts, 4 plan, 5 push rows + return table,
+ * 6 gate_up (waits for the pushed rows first), 7 down with the return fused in, 8 combine (waits for the returned rows
+ * first)): for per-stage timing, and for running several ranks' calls interleaved stage by stage on one stream of one
+ * GPU, where every wait finds its flags already raised.  netra_ep_layer_launch runs stages 3 and 4 as one launch, which
+ * is only possible when every rank has a GPU of its own. */
 int netra_ep_layer_launch_stage(netra_ep_layer_t* layer, uint32_t stage, const void* hidden_bf16, const float* shared_weight_f32,
                                 void* out_bf16, uint32_t tokens, cudaStream_t stream);
 uint32_t netra_ep_layer_stage_count(void);

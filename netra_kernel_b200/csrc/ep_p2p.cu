@@ -12,12 +12,15 @@
 //            block, and for each block row the (rank, sorted row) it is returned to
 //   push     each sorted row (2048 FP8 codes + 16 scales) is stored straight into its expert-major
 //            position in the owner's activation block; the rank's own tokens become the shared
-//            expert's rows (group 0)                                                        (flag 1)
-//   wait     for the pushed rows; the same launch builds the table "block row -> where its result goes"
-//   gate_up  grouped GEMM over E_l + 1 slabs
+//            expert's rows (group 0); the same launch builds the table "block row -> where its
+//            result goes"                                                                   (flag 1)
+//   gate_up  waits for the pushed rows, then the grouped GEMM over E_l + 1 slabs
 //   down     grouped GEMM whose epilogue stores each FP32 row straight into the sending rank's
 //            sorted-order buffer (the return overlaps the remaining tiles)                   (flag 2)
-//   wait, slot-ordered combine (the same kernel as on one GPU)
+//   combine  waits for the returned rows, then the slot-ordered combine of the one-GPU layer
+// One call is nine stages; a real multi-GPU call runs publish and plan as one launch (eight launches up to
+// 1,024 tokens).  Ranks emulated on one GPU are driven stage by stage instead, so that every wait finds its
+// flags raised (two kernels that wait on one another must never be in flight on one GPU).
 // A flag holds the epoch (call number) of its writer; a wait spins until the flag reaches the
 // current epoch or a time limit passes, in which case a status word records it and the kernel
 // returns.  Buffer reuse is ordered by the flags themselves: a rank's next push follows its wait for
@@ -74,10 +77,9 @@ __device__ __forceinline__ bool ep_wait_flag(const uint32_t* flag, uint32_t epoc
   }
 }
 
-// publish: this rank's counts row -> every peer's matrix, then flag 0.  grid 1, block 288.
-extern "C" __global__ void __launch_bounds__(288)
-netra_ep_publish_counts_sm100(EpPeers peers, EpWindowLayout lay, EpTables* __restrict__ tab, const int32_t* __restrict__ counts,
-                              uint32_t tokens, uint32_t world, uint32_t rank) {
+// publish: this rank's counts row -> every peer's matrix, then flag 0.  One block of at least 288 threads.
+__device__ __forceinline__ void ep_publish_body(const EpPeers& peers, const EpWindowLayout& lay, EpTables* __restrict__ tab,
+                                                const int32_t* __restrict__ counts, uint32_t tokens, uint32_t world, uint32_t rank) {
   __shared__ uint32_t s_epoch;
   const int tid = threadIdx.x;
   if (tid == 0) {
@@ -94,6 +96,13 @@ netra_ep_publish_counts_sm100(EpPeers peers, EpWindowLayout lay, EpTables* __res
   if (tid < (int)world) st_release_sys(reinterpret_cast<uint32_t*>(peers.win[tid] + lay.flags) + 0 * kEpFlagPitch + rank, s_epoch);
 }
 
+// grid 1, block 288
+extern "C" __global__ void __launch_bounds__(288)
+netra_ep_publish_counts_sm100(EpPeers peers, EpWindowLayout lay, EpTables* __restrict__ tab, const int32_t* __restrict__ counts,
+                              uint32_t tokens, uint32_t world, uint32_t rank) {
+  ep_publish_body(peers, lay, tab, counts, tokens, world, rank);
+}
+
 // wait for one phase's flags from every rank.  grid 1, block 32.
 extern "C" __global__ void __launch_bounds__(32)
 netra_ep_wait_sm100(const uint8_t* __restrict__ window, EpWindowLayout lay, EpTables* __restrict__ tab, uint32_t phase,
@@ -105,11 +114,9 @@ netra_ep_wait_sm100(const uint8_t* __restrict__ window, EpWindowLayout lay, EpTa
   }
 }
 
-// plan: wait for flag 0 of every rank, then derive all row placements from the count matrix.
-// grid 1, block 1024.
-extern "C" __global__ void __launch_bounds__(1024)
-netra_ep_plan_sm100(const uint8_t* __restrict__ window, EpWindowLayout lay, EpTables* __restrict__ tab, uint32_t world,
-                    uint32_t rank, uint32_t capacity, uint64_t timeout_ns) {
+// plan: wait for flag 0 of every rank, then derive all row placements from the count matrix.  One block of 1,024 threads.
+__device__ __forceinline__ void ep_plan_body(const uint8_t* __restrict__ window, const EpWindowLayout& lay, EpTables* __restrict__ tab,
+                                             uint32_t world, uint32_t rank, uint32_t capacity, uint64_t timeout_ns) {
   __shared__ int C[kEpMaxRanks][kRouted];    // C[s][e]: pairs of rank s for global expert e
   __shared__ int rowpre[kEpMaxRanks][kRouted];
   __shared__ int colsum[kRouted];
@@ -203,6 +210,23 @@ netra_ep_plan_sm100(const uint8_t* __restrict__ window, EpWindowLayout lay, EpTa
   }
 }
 
+// grid 1, block 1024
+extern "C" __global__ void __launch_bounds__(1024)
+netra_ep_plan_sm100(const uint8_t* __restrict__ window, EpWindowLayout lay, EpTables* __restrict__ tab, uint32_t world,
+                    uint32_t rank, uint32_t capacity, uint64_t timeout_ns) {
+  ep_plan_body(window, lay, tab, world, rank, capacity, timeout_ns);
+}
+
+// publish and plan in one launch, for ranks that live on GPUs of their own (the wait inside would never end for ranks
+// emulated one after another on one GPU).  grid 1, block 1024.
+extern "C" __global__ void __launch_bounds__(1024)
+netra_ep_publish_plan_sm100(EpPeers peers, EpWindowLayout lay, EpTables* __restrict__ tab, const int32_t* __restrict__ counts,
+                            uint32_t tokens, uint32_t world, uint32_t rank, uint32_t capacity, uint64_t timeout_ns) {
+  ep_publish_body(peers, lay, tab, counts, tokens, world, rank);
+  __syncthreads();
+  ep_plan_body(peers.win[rank], lay, tab, world, rank, capacity, timeout_ns);
+}
+
 // Signal a phase to every peer once all blocks of the calling kernel have fenced their stores.
 __device__ __forceinline__ void ep_signal_when_last(const EpPeers& peers, const EpWindowLayout& lay, EpTables* tab, uint32_t* counter,
                                                     uint32_t phase, uint32_t world, uint32_t rank) {
@@ -228,6 +252,10 @@ __device__ __forceinline__ void ep_signal_when_last(const EpPeers& peers, const 
   }
 }
 
+__device__ __forceinline__ void ep_build_return_table(const EpPeers& peers, const EpWindowLayout& lay, const EpTables* __restrict__ tab,
+                                                      float** __restrict__ row_ptr, float* __restrict__ blk_down, uint32_t tokens,
+                                                      uint32_t max_tokens, uint32_t world, uint32_t rank, uint32_t capacity);
+
 // push: sorted row i (i < pairs) of this rank -> its expert-major row in the owner's block;
 // rows pairs .. pairs + tokens - 1 are the rank's own tokens -> rows [0, tokens) of its own block.
 // a_fp8 / a_scale hold the per-token quantised rows at row (pairs + t).  One warp per row.
@@ -236,7 +264,8 @@ extern "C" __global__ void __launch_bounds__(256)
 netra_ep_push_rows_sm100(EpPeers peers, EpWindowLayout lay, EpTables* __restrict__ tab, const uint8_t* __restrict__ a_fp8,
                          const float* __restrict__ a_scale, const int32_t* __restrict__ perm, const int32_t* __restrict__ ids9,
                          const int32_t* __restrict__ sorted_offsets, uint32_t tokens, uint32_t world, uint32_t rank,
-                         uint32_t capacity) {
+                         uint32_t capacity, float** __restrict__ row_ptr, float* __restrict__ blk_down, uint32_t max_tokens) {
+  ep_build_return_table(peers, lay, tab, row_ptr, blk_down, tokens, max_tokens, world, rank, capacity);
   const int pairs = (int)tokens * kTopK;
   const int i = blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -267,19 +296,17 @@ netra_ep_push_rows_sm100(EpPeers peers, EpWindowLayout lay, EpTables* __restrict
   ep_signal_when_last(peers, lay, tab, &tab->done_push, 1, world, rank);
 }
 
-// wait for the pushed rows (flag 1 of every rank; block 0) and build the return table: row_ptr[r] = where
-// block row r's FP32 down row goes - the sorted-order buffer of the rank it came from, or this rank's
-// own shared rows (pairs + t) for the shared group.  Rows without a valid destination point at the local
-// block buffer.  grid: any (grid-stride), block 256.
-extern "C" __global__ void __launch_bounds__(256)
-netra_ep_wait_table_sm100(EpPeers peers, EpWindowLayout lay, EpTables* __restrict__ tab, float** __restrict__ row_ptr,
-                          float* __restrict__ blk_down, uint32_t tokens, uint32_t max_tokens, uint32_t world, uint32_t rank,
-                          uint32_t capacity, uint64_t timeout_ns) {
+// The return table: row_ptr[r] = where block row r's FP32 down row goes - the sorted-order buffer of the rank it came
+// from, or this rank's own shared rows (pairs + t) for the shared group.  Rows without a valid destination point at the
+// local block buffer.  Grid-stride over the block rows, block 256; needs only what the plan wrote.
+__device__ __forceinline__ void ep_build_return_table(const EpPeers& peers, const EpWindowLayout& lay, const EpTables* __restrict__ tab,
+                                                      float** __restrict__ row_ptr, float* __restrict__ blk_down, uint32_t tokens,
+                                                      uint32_t max_tokens, uint32_t world, uint32_t rank, uint32_t capacity) {
   __shared__ int s_start[kRouted + 1];
-  for (int i = threadIdx.x; i <= kRouted; i += 256) s_start[i] = tab->blk_start[i];
+  for (int i = threadIdx.x; i <= kRouted; i += blockDim.x) s_start[i] = tab->blk_start[i];
   __syncthreads();
   const int total = min(s_start[kRouted], (int)capacity);
-  for (int r = blockIdx.x * 256 + threadIdx.x; r < total; r += gridDim.x * 256) {
+  for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < total; r += gridDim.x * blockDim.x) {
     int g, dst_row;
     if (r < (int)tokens) {
       g = (int)rank;
@@ -297,10 +324,48 @@ netra_ep_wait_table_sm100(EpPeers peers, EpWindowLayout lay, EpTables* __restric
                      ? reinterpret_cast<float*>(peers.win[g] + lay.down) + (size_t)dst_row * kHidden
                      : blk_down + (size_t)r * kHidden;
   }
-  if (blockIdx.x == 0 && threadIdx.x < world) {
-    const uint32_t* flag = reinterpret_cast<const uint32_t*>(peers.win[rank] + lay.flags) + 1 * kEpFlagPitch + threadIdx.x;
-    if (!ep_wait_flag(flag, tab->epoch, timeout_ns)) atomicOr(&tab->status[3], (1u << 8) << min((int)threadIdx.x, 7));
+}
+
+// Every thread below `world` waits for one rank's flag of `phase` in this rank's window; the block then goes on together,
+// with the copy engine's later reads ordered after what the waiting threads observed.
+__device__ __forceinline__ void ep_block_wait_phase(const uint8_t* __restrict__ window, const EpWindowLayout& lay, EpTables* __restrict__ tab,
+                                                    uint32_t phase, uint32_t world, uint64_t timeout_ns) {
+  if (threadIdx.x < world) {
+    const uint32_t* flag = reinterpret_cast<const uint32_t*>(window + lay.flags) + phase * kEpFlagPitch + threadIdx.x;
+    if (!ep_wait_flag(flag, tab->epoch, timeout_ns)) atomicOr(&tab->status[3], (1u << (8 * phase)) << min((int)threadIdx.x, 7));
   }
+  __syncthreads();
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
+
+// gate_up over the rows the peers pushed: every CTA waits for flag 1 of every rank (bounded), then runs the grouped GEMM.
+extern "C" __global__ void __launch_bounds__(kGemmThreads, 1)
+netra_ep_gate_up_umma_sm100(const __grid_constant__ CUtensorMap tm_w13, const __grid_constant__ CUtensorMap tm_a32,
+                            const __grid_constant__ CUtensorMap tm_a64, const __grid_constant__ CUtensorMap tm_a128,
+                            const float* a_scale, const float* w13_scale, const int32_t* offsets, uint8_t* h_fp8, float* h_scale,
+                            uint32_t num_groups, uint32_t w_tiled, uint32_t* status, const uint8_t* window, EpWindowLayout lay,
+                            EpTables* tab, uint32_t world, uint64_t timeout_ns) {
+  ep_block_wait_phase(window, lay, tab, 1, world, timeout_ns);
+  grouped_gemm_body<true>(&tm_w13, &tm_a32, &tm_a64, &tm_a128, a_scale, w13_scale, nullptr, offsets, h_fp8, h_scale, nullptr, nullptr,
+                          num_groups, w_tiled, status);
+}
+
+extern "C" __global__ void __launch_bounds__(kTmThreads, 1)
+netra_ep_gate_up_tokmajor_sm100(const __grid_constant__ CUtensorMap tm_w13, const __grid_constant__ CUtensorMap tm_a128,
+                                const float* a_scale, const float* w13_scale, const int32_t* offsets, uint8_t* h_fp8, float* h_scale,
+                                uint32_t num_groups, uint32_t w_tiled, uint32_t* status, const uint8_t* window, EpWindowLayout lay,
+                                EpTables* tab, uint32_t world, uint64_t timeout_ns) {
+  ep_block_wait_phase(window, lay, tab, 1, world, timeout_ns);
+  tokmajor_gemm_body<true>(&tm_w13, &tm_a128, a_scale, w13_scale, offsets, h_fp8, h_scale, nullptr, nullptr, num_groups, w_tiled, status);
+}
+
+// The slot-ordered combine over the rows the peers returned: every block waits for flag 2 of every rank (bounded) first.
+// grid rows, block 256.
+extern "C" __global__ void __launch_bounds__(256)
+netra_ep_combine_sm100(uint16_t* __restrict__ out, const float* down, const float* __restrict__ w9, const int32_t* __restrict__ inv_perm,
+                       uint32_t rows, const uint8_t* window, EpWindowLayout lay, EpTables* tab, uint32_t world, uint64_t timeout_ns) {
+  ep_block_wait_phase(window, lay, tab, 2, world, timeout_ns);
+  combine_rows_body<true>(out, down, w9, inv_perm, rows);
 }
 
 // The down projection with the return fused in: every FP32 output row is stored straight to row_ptr[row]
@@ -353,7 +418,7 @@ struct netra_ep_layer {
 
 namespace {
 
-constexpr uint32_t kEpStageCount = 11;
+constexpr uint32_t kEpStageCount = 9;
 
 EpWindowLayout ep_window_layout(uint32_t world, uint32_t max_tokens, uint32_t capacity) {
   EpWindowLayout l;
@@ -417,27 +482,21 @@ int ep_launch_stage(netra_ep_layer* L, uint32_t stage, const void* hidden, const
     case 5:
       netra_ep_push_rows_sm100<<<(pairs + tokens + 7) / 8, 256, 0, stream>>>(
           L->peers, L->wl, L->tab, ws + R.a_fp8, (const float*)(ws + R.a_scale), (const int32_t*)(ws + R.perm),
-          (const int32_t*)(ws + R.topk_ids), (const int32_t*)(ws + R.offsets), tokens, d.world, d.rank, d.row_capacity);
+          (const int32_t*)(ws + R.topk_ids), (const int32_t*)(ws + R.offsets), tokens, d.world, d.rank, d.row_capacity, L->row_ptr,
+          L->blk_down, d.max_tokens);
       break;
-    case 6: {
-      const uint32_t expected = d.max_tokens * (1 + 2 * kTopK);          // own tokens + twice an even share of the pairs
-      const uint32_t rows = expected < d.row_capacity ? expected : d.row_capacity;
-      netra_ep_wait_table_sm100<<<(rows + 255) / 256, 256, 0, stream>>>(L->peers, L->wl, L->tab, L->row_ptr, L->blk_down, tokens,
-                                                                       d.max_tokens, d.world, d.rank, d.row_capacity, d.wait_timeout_ns);
-      break;
-    }
-    case 7:
+    case 6:
       // the pairs of all ranks (equal token counts assumed) spread over 256 routed experts decide the GEMM form
       if (L->tokmajor_ok && use_tokmajor(L->route->device, (uint64_t)d.world * pairs, kRouted))
-        netra_moe_gate_up_tokmajor_sm100<<<L->sm_count, kTmThreads, gate_up_tokmajor_smem_bytes(), stream>>>(
+        netra_ep_gate_up_tokmajor_sm100<<<L->sm_count, kTmThreads, gate_up_tokmajor_smem_bytes(), stream>>>(
             L->tm_w13, L->tm_a128, (const float*)(L->window + L->wl.blk_as), d.w13_scale_f32, L->tab->offsets, L->blk_h, L->blk_hs,
-            L->e_l + 1, d.weights_tiled, L->tab->status);
+            L->e_l + 1, d.weights_tiled, L->tab->status, L->window, L->wl, L->tab, d.world, d.wait_timeout_ns);
       else
-        netra_moe_gate_up_umma_sm100<<<L->sm_count, kGemmThreads, gate_up_smem_bytes(), stream>>>(
+        netra_ep_gate_up_umma_sm100<<<L->sm_count, kGemmThreads, gate_up_smem_bytes(), stream>>>(
             L->tm_w13, L->tm_a32, L->tm_a64, L->tm_a128, (const float*)(L->window + L->wl.blk_as), d.w13_scale_f32, L->tab->offsets,
-            L->blk_h, L->blk_hs, L->e_l + 1, d.weights_tiled, L->tab->status);
+            L->blk_h, L->blk_hs, L->e_l + 1, d.weights_tiled, L->tab->status, L->window, L->wl, L->tab, d.world, d.wait_timeout_ns);
       break;
-    case 8:
+    case 7:
       // Across GPUs the swap-AB form is kept for the down projection whatever the size: its epilogue stores 128
       // contiguous bytes of one row per warp instruction, while a token-major thread owns a whole row and a warp
       // instruction scatters 32-byte pieces over 32 rows - over NVLink that took three times as long (8 GPUs,
@@ -451,10 +510,10 @@ int ep_launch_stage(netra_ep_layer* L, uint32_t stage, const void* hidden, const
             L->tm_w2, L->tm_h32, L->tm_h64, L->tm_h128, L->blk_hs, d.w2_scale_f32, L->tab->offsets, L->row_ptr, L->e_l + 1,
             d.weights_tiled, L->tab->status + 1, L->peers, L->wl, L->tab, d.world, d.rank);
       break;
-    case 9: netra_ep_wait_sm100<<<1, 32, 0, stream>>>(L->window, L->wl, L->tab, 2, d.world, d.wait_timeout_ns); break;
     default:
-      netra_moe_combine_sm100<<<tokens, 256, 0, stream>>>((uint16_t*)out, (const float*)(L->window + L->wl.down),
-                                                          (const float*)(ws + R.topk_weights), (const int32_t*)(ws + R.inv_perm), tokens);
+      netra_ep_combine_sm100<<<tokens, 256, 0, stream>>>((uint16_t*)out, (const float*)(L->window + L->wl.down),
+                                                         (const float*)(ws + R.topk_weights), (const int32_t*)(ws + R.inv_perm), tokens,
+                                                         L->window, L->wl, L->tab, d.world, d.wait_timeout_ns);
       break;
   }
   return 0;
@@ -564,11 +623,16 @@ int netra_ep_layer_create(const netra_ep_layer_desc_t* desc, netra_ep_layer_t** 
   {
     cudaError_t e = cudaFuncSetAttribute(netra_ep_down_return_umma_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, down_smem_bytes());
     if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(netra_ep_gate_up_umma_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, gate_up_smem_bytes());
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(netra_ep_gate_up_tokmajor_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, gate_up_tokmajor_smem_bytes());
+    if (e == cudaSuccess)
       e = cudaFuncSetAttribute(netra_ep_down_return_tokmajor_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, down_tokmajor_smem_bytes());
-    cudaFuncAttributes attr;
+    cudaFuncAttributes attr, attr_gate_up;
     if (e == cudaSuccess) e = cudaFuncGetAttributes(&attr, netra_ep_down_return_tokmajor_sm100);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&attr_gate_up, netra_ep_gate_up_tokmajor_sm100);
     if (e != cudaSuccess) { netra_moe_layer_destroy(L->route); delete L; return fail_cuda("cudaFuncSetAttribute(down_return)", e); }
-    L->tokmajor_ok = g_tokmajor_ok[L->route->device] && attr.numRegs == kTmRegsLaunch;
+    L->tokmajor_ok = g_tokmajor_ok[L->route->device] && attr.numRegs == kTmRegsLaunch && attr_gate_up.numRegs == kTmRegsLaunch;
   }
   const uint64_t g = L->e_l + 1, rows = desc->row_capacity;
   if (desc->weights_tiled) {
@@ -599,15 +663,25 @@ uint32_t netra_ep_layer_stage_count(void) { return kEpStageCount; }
 
 uint32_t netra_ep_layer_launch_count(const netra_ep_layer_t* L, uint32_t tokens) {
   if (!L) return 0;
-  if (tokens > (uint32_t)kSortSmallMaxRows) return kEpStageCount + 2;                // the sort is three launches
-  return kEpStageCount - (L->route->front_mode == 1 ? 2 : 0);                           // router, top-k and sort as one launch
+  // a whole call runs publish and plan as one launch; above 1,024 tokens the sort is three launches
+  if (tokens > (uint32_t)kSortSmallMaxRows) return kEpStageCount - 1 + 2;
+  return kEpStageCount - 1 - (L->route->front_mode == 1 ? 2 : 0);                       // router, top-k and sort as one launch
 }
 
 int netra_ep_layer_launch(netra_ep_layer_t* L, const void* hidden, const float* shared_w, void* out, uint32_t tokens, cudaStream_t stream) {
   if (!L || !hidden || !out) return fail("ep_layer_launch: null pointer");
   if (tokens == 0 || tokens > L->desc.max_tokens) return fail("ep_layer_launch: tokens exceed the bound capacity");
-  for (uint32_t s = 0; s < kEpStageCount; ++s)
+  for (uint32_t s = 0; s < kEpStageCount; ++s) {
+    if (s == 3) {      // publish and plan in one launch: this rank's GPU is its own, the peers' flags arrive while it waits
+      const netra_ep_layer_desc_t& d = L->desc;
+      const uint8_t* ws = (const uint8_t*)L->route->desc.workspace;
+      netra_ep_publish_plan_sm100<<<1, 1024, 0, stream>>>(L->peers, L->wl, L->tab, (const int32_t*)(ws + L->route->lay.counts), tokens,
+                                                          d.world, d.rank, d.row_capacity, d.wait_timeout_ns);
+      ++s;             // stage 4 (plan) is done
+      continue;
+    }
     if (int rc = ep_launch_stage(L, s, hidden, shared_w, out, tokens, stream)) return rc;
+  }
   return check_launch("ep_layer launch");
 }
 

@@ -810,9 +810,10 @@ netra_moe_gather_rows_sm100(uint8_t* __restrict__ a_fp8, float* __restrict__ a_s
 // one multiply and one add per slot.  pos(t,s) = inv_perm[t*8+s] for routed slots and
 // pairs + t for the shared slot.  grid rows, block 256 (8 columns per thread).
 // ------------------------------------------------------------------------------------------
-extern "C" __global__ void __launch_bounds__(256)
-netra_moe_combine_sm100(uint16_t* __restrict__ out, const float* __restrict__ down,
-                        const float* __restrict__ w9, const int32_t* __restrict__ inv_perm, uint32_t rows) {
+// kFromL2: the rows were written by other GPUs while this kernel was already running, so they are read around the L1.
+template <bool kFromL2>
+__device__ __forceinline__ void combine_rows_body(uint16_t* __restrict__ out, const float* down, const float* __restrict__ w9,
+                                                  const int32_t* __restrict__ inv_perm, uint32_t rows) {
   const int t = blockIdx.x;
   const int pairs = (int)rows * kTopK;
   // all nine rows are requested before the first is used; the sum itself stays slot-ascending
@@ -823,8 +824,8 @@ netra_moe_combine_sm100(uint16_t* __restrict__ out, const float* __restrict__ do
     const size_t pos = s < kTopK ? (size_t)inv_perm[t * kTopK + s] : (size_t)pairs + t;
     w[s] = w9[t * kSlots + s];
     const float4* src = reinterpret_cast<const float4*>(down + pos * kHidden) + threadIdx.x * 2;
-    a[s] = src[0];
-    b[s] = src[1];
+    a[s] = kFromL2 ? __ldcg(src) : src[0];
+    b[s] = kFromL2 ? __ldcg(src + 1) : src[1];
   }
   float acc[8];
 #pragma unroll
@@ -843,6 +844,12 @@ netra_moe_combine_sm100(uint16_t* __restrict__ out, const float* __restrict__ do
     pk[i] = *reinterpret_cast<uint32_t*>(&v);
   }
   reinterpret_cast<uint4*>(out + (size_t)t * kHidden)[threadIdx.x] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+}
+
+extern "C" __global__ void __launch_bounds__(256)
+netra_moe_combine_sm100(uint16_t* __restrict__ out, const float* __restrict__ down,
+                        const float* __restrict__ w9, const int32_t* __restrict__ inv_perm, uint32_t rows) {
+  combine_rows_body<false>(out, down, w9, inv_perm, rows);
 }
 
 // The same combine over FP16 partial rows (written by netra_moe_down_tokmajor_f16_sm100): each partial is widened to

@@ -160,7 +160,7 @@ class ExpertParallelMoELayer:
             raise ValueError(f"this rank holds the shared slab + {e_l} routed slabs, got {w13.shape[0]}")
         dev = router_w.device
         self.device, self.t_max = dev, int(max_local_tokens)
-        # routing stages (0-5) and the combine (8) of the single-GPU layer, on the local tokens
+        # routing stages (0-5) and the combine (8) of the single-GPU layer, on the local tokens (NCCL arm)
         self.route = RoutedMoELayer(router_w, w13, w13_scale, w2, w2_scale, self.t_max, router_bias, tiled=tiled,
                                     routing_only=True)
         w13, w2 = self.route._keep[1], self.route._keep[3]           # the copies the kernels read (tile order if tiled)

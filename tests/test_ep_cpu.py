@@ -189,4 +189,4 @@ def test_peer_memory_layer_sizes_and_capacity_rules():
     assert lib.netra_ep_sizes_query(3, 256, 4096, ctypes.byref(a), ctypes.byref(b)) != 0       # 3 does not divide 256
     assert b"world" in lib.netra_moe_last_error()
     assert lib.netra_ep_sizes_query(8, 256, 100, ctypes.byref(a), ctypes.byref(b)) != 0        # cannot hold the rank's own tokens
-    assert lib.netra_ep_layer_stage_count() == 11
+    assert lib.netra_ep_layer_stage_count() == 9
