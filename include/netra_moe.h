@@ -380,10 +380,11 @@ int netra_moe_layer_set_gemm_mode(netra_moe_layer_t* layer, uint32_t mode);
  * launches fewer, measured 4 us slower per 256-token call: a recorded tactic. */
 int netra_moe_layer_set_front_mode(netra_moe_layer_t* layer, uint32_t mode);
 
-/* Where the token-major gate_up takes its token rows from.  in_gemm 0 (default): an expert-sorted copy of the quantised
+/* Where gate_up (E4M3 weights) takes its token rows from.  in_gemm 0 (default): an expert-sorted copy of the quantised
  * rows written by the row-gather stage.  in_gemm 1: no copy; the GEMM's producer fetches the rows from token order with
- * four-row TMA gathers (cp.async.bulk.tensor tile::gather4).  Same results; measured 2.5 times slower at 8,192 tokens
- * (32 gather instructions per 128-row tile and K-block), kept as a recorded tactic. */
+ * four-row TMA gathers (cp.async.bulk.tensor tile::gather4).  Same results, one launch fewer; measured 2.5 times slower
+ * at 8,192 tokens (token-major form: 32 gather instructions per 128-row tile and K-block) and 9 us slower per 256-token
+ * call (swap-AB form: eight per 32-row tile and K-block), kept as a recorded tactic. */
 int netra_moe_layer_set_row_gather(netra_moe_layer_t* layer, uint32_t in_gemm);
 
 /* Router of calls above 1024 rows.  mode 0 (default): BF16 tensor-core pass with FP32 accumulation, then an FP64

@@ -80,6 +80,16 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       " [%0], [%1, {%3, %4}], [%2], %5;"
       ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y), "l"(policy) : "memory");
 }
+// Four rows of a 2-D tensor (box = 128 bytes x 1 row) chosen by index, written as four consecutive 128-byte rows
+// of a swizzled tile: the token rows of a work item are fetched straight from token order, without a sorted copy.
+__device__ __forceinline__ void tma_gather4_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int r0, int r1, int r2, int r3,
+                                               uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2], %8;"
+      ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "l"(policy) : "memory");
+}
+
 // contiguous global -> shared copy; both addresses 16-byte aligned, size a multiple of 16
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -249,7 +259,11 @@ struct Cfg {
 // unit's rows.  Every CTA finishes its gate_up items before it starts on down items and nothing in the gate_up half waits
 // for another CTA, so with all CTAs resident (grid <= SM count, one CTA per SM) the wait always ends; it is bounded anyway.
 // Returns false when this CTA gave up on a wait.
-template <bool kGateUp, bool kFp4 = false, int kChain = 0>
+// kGatherX (gate_up on E4M3 weights): the item's token rows are not read from an expert-sorted copy but gathered from token
+// order: sorted position p holds token-order row tok_row_base + (perm[p] >> 3) (positions from tok_row_base on are
+// token-order rows already: the shared expert).  tm_x32 then is a map with a one-row box over the same buffer and x_scale
+// its scales.
+template <bool kGateUp, bool kFp4 = false, int kChain = 0, bool kGatherX = false>
 __device__ __forceinline__ bool grouped_gemm_body(const CUtensorMap* tm_w, const CUtensorMap* tm_x32,
                                                   const CUtensorMap* tm_x64, const CUtensorMap* tm_x128,
                                                   const float* __restrict__ x_scale, const float* __restrict__ w_scale,
@@ -258,7 +272,9 @@ __device__ __forceinline__ bool grouped_gemm_body(const CUtensorMap* tm_w, const
                                                   float* __restrict__ h_scale, float* __restrict__ down,
                                                   float* const* __restrict__ row_ptr, uint32_t num_groups, uint32_t w_tiled,
                                                   uint32_t* status, uint32_t* __restrict__ ready = nullptr,
-                                                  uint32_t* tmem_chain = nullptr) {
+                                                  uint32_t* tmem_chain = nullptr, const int32_t* __restrict__ perm = nullptr,
+                                                  uint32_t tok_row_base = 0) {
+  static_assert(!kGatherX || (kGateUp && !kFp4 && kChain == 0), "the gathering producer serves the stand-alone E4M3 gate_up");
   // tmem_chain (chained halves): a CTA may allocate TMEM only until it gives up its permit, so the first half allocates
   // and hands the base address on, the second half frees it
   using C = Cfg<kGateUp, kFp4>;
@@ -368,6 +384,79 @@ __device__ __forceinline__ bool grouped_gemm_body(const CUtensorMap* tm_w, const
         asm volatile("red.release.gpu.global.add.u32 [%0], 2;" ::"l"(ready + (item >> 2)) : "memory");
       }
     }
+    if constexpr (kGatherX) {
+      // =========================== TMA producer, token rows gathered (whole warp) ===========================
+      // Lanes 0..7 own four rows each of the 32-row token tile: they look up where those sorted positions live in token
+      // order once per item and fetch them with one four-row gather per K-block; every lane copies one row of token
+      // scales; lane 0 also does the waits, the byte counts and the weight tiles.
+      if (lane == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)tm_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)tm_x32) : "memory");
+      }
+      const uint64_t pol_w = policy_evict_first();
+      const uint64_t pol_x = policy_evict_last();
+      uint32_t it = 0, n_item = 0;
+      bool ok = true;
+      for (int item = first_item; ok && item < total_items; item += stride, ++n_item) {
+        const Item w = get_item((int)n_item, item);
+        auto source_row = [&](int r) {       // rows past the item's end repeat its last row
+          const int pos = w.row0 + min(r, w.m_valid - 1);
+          return pos >= (int)tok_row_base ? pos : (int)tok_row_base + (__ldg(perm + pos) >> 3);
+        };
+        int src[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) src[j] = source_row(4 * (lane & 7) + j);
+        const int my_scale_row = source_row(lane);
+        const int slot = n_item % C::kScaleSlots;
+        const uint32_t sbar = smem_u32(&sfull_bar[slot]);
+        const uint32_t sdst = smem_u32(scale_base + slot * C::kScaleSlotBytes);
+        bool good = true;
+        if (lane == 0) {
+          good = mbar_wait(smem_u32(&sempty_bar[slot]), ((n_item / C::kScaleSlots) & 1) ^ 1, abort_flag);
+          if (good) {
+            mbar_expect_tx(sbar, C::kXsBytes + C::kATiles * C::kWsBytes);
+            const float* wsrc = w_scale + ((size_t)w.group * C::kSlabTiles + w.ntile) * C::kKBlocks;
+            bulk_load(sdst + C::kXsBytes, wsrc, C::kWsBytes, sbar);
+            bulk_load(sdst + C::kXsBytes + C::kWsBytes, wsrc + (kInter / kBlock) * C::kKBlocks, C::kWsBytes, sbar);
+          } else {
+            status[0] = kStatusProducerTimeout; *abort_flag = 1;
+          }
+        }
+        good = __shfl_sync(0xffffffffu, good ? 1 : 0, 0) != 0;
+        if (!good) { ok = false; break; }
+        bulk_load(sdst + (uint32_t)lane * C::kKBlocks * 4, x_scale + (size_t)my_scale_row * C::kKBlocks, C::kKBlocks * 4, sbar);
+        for (int kb = 0; kb < C::kKBlocks; ++kb, ++it) {
+          const int s = it % C::kStages;
+          const uint32_t bar = smem_u32(&full_bar[s]);
+          const uint32_t dst = smem_u32(stage_base + s * C::kStageBytes);
+          if (lane == 0) {
+            good = mbar_wait(smem_u32(&empty_bar[s]), ((it / C::kStages) & 1) ^ 1, abort_flag);
+            if (good) {
+              mbar_expect_tx(bar, C::kATiles * kWTileBytes + C::kTokTileBytes);
+              int wx, wy0, wy1;
+              if (w_tiled) {
+                wx = 0;
+                wy0 = ((w.group * C::kSlabTiles + w.ntile) * C::kKBlocks + kb) * kTileRows;
+                wy1 = wy0 + (kInter / kTileRows) * C::kKBlocks * kTileRows;
+              } else {
+                wx = kb * kBlock;
+                wy0 = w.group * C::kSlabRows + w.ntile * kTileRows;
+                wy1 = wy0 + kInter;
+              }
+              tma_load_2d(dst, tm_w, bar, wx, wy0, pol_w);
+              tma_load_2d(dst + kWTileBytes, tm_w, bar, wx, wy1, pol_w);
+            } else {
+              status[0] = kStatusProducerTimeout; *abort_flag = 1;
+            }
+          }
+          good = __shfl_sync(0xffffffffu, good ? 1 : 0, 0) != 0;      // also orders the lanes' gathers after lane 0's wait
+          if (!good) { ok = false; break; }
+          if (lane < 8)
+            tma_gather4_2d(dst + C::kATiles * kWTileBytes + (uint32_t)lane * 4 * kBlock, tm_x32, bar, kb * kBlock, src[0], src[1], src[2],
+                           src[3], pol_x);
+        }
+      }
+    } else
     // =========================== TMA producer ===========================
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)tm_w) : "memory");
@@ -759,6 +848,18 @@ netra_moe_gate_up_down_umma_sm100(const __grid_constant__ CUtensorMap tm_w13, co
     return;
   grouped_gemm_body<false, false, 2>(&tm_w2, &tm_h32, &tm_h32, &tm_h32, h_scale, w2_scale, nullptr, offsets, nullptr, nullptr, down, nullptr,
                                      num_groups, w_tiled, status + 1, ready, &tmem);
+}
+
+// gate_up with the token rows gathered from token order (no expert-sorted copy of the quantised rows is made for it):
+// tm_tok1 is a one-row-box map over the quantised-row buffer, tok_scale its scales [rows, 16], perm the sorted
+// position -> pair index table, tok_row_base the first token-order row of that buffer.
+extern "C" __global__ void __launch_bounds__(kGemmThreads, 1)
+netra_moe_gate_up_umma_gather_sm100(const __grid_constant__ CUtensorMap tm_w13, const __grid_constant__ CUtensorMap tm_tok1,
+                                    const float* tok_scale, const float* w13_scale, const int32_t* offsets, const int32_t* perm,
+                                    uint8_t* h_fp8, float* h_scale, uint32_t num_groups, uint32_t w_tiled, uint32_t tok_row_base,
+                                    uint32_t* status) {
+  grouped_gemm_body<true, false, 0, true>(&tm_w13, &tm_tok1, &tm_tok1, &tm_tok1, tok_scale, w13_scale, nullptr, offsets, h_fp8, h_scale,
+                                          nullptr, nullptr, num_groups, w_tiled, status, nullptr, nullptr, perm, tok_row_base);
 }
 
 int gate_up_down_smem_bytes() { return Cfg<true>::kSmemBytes > Cfg<false>::kSmemBytes ? Cfg<true>::kSmemBytes : Cfg<false>::kSmemBytes; }

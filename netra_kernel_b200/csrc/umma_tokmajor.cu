@@ -58,16 +58,6 @@ __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, i
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"((uint64_t)map), "r"(x), "r"(y) : "memory");
 }
 
-// Four rows of a 2-D tensor (box = 128 bytes x 1 row) chosen by index, written as four consecutive 128-byte rows
-// of a swizzled tile: the token rows of a work item are fetched straight from token order, without a sorted copy.
-__device__ __forceinline__ void tma_gather4_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int r0, int r1, int r2, int r3,
-                                               uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes.L2::cache_hint"
-      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2], %8;"
-      ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "l"(policy) : "memory");
-}
-
 // barrier among the 256 epilogue threads
 __device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 3, 256;" ::: "memory"); }
 

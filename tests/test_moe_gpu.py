@@ -313,14 +313,16 @@ def test_both_projections_in_one_launch_equal_the_two_launch_form(gpu_weights, t
 
 
 def test_token_rows_gathered_inside_the_gemm_give_the_same_bytes(gpu_weights):
-    """The recorded tactic that skips the expert-sorted copy: the token-major gate_up fetches its rows from token order with
-    four-row TMA gathers.  Intermediates and output must equal the default form's bit for bit; one launch fewer."""
-    for tokens, alpha in ((2048, 0.0), (1500, 3.0)):
+    """The recorded tactic that skips the expert-sorted copy: gate_up (token-major form, and swap-AB form at decode sizes)
+    fetches its rows from token order with four-row TMA gathers.  Intermediates and output must equal the default form's
+    bit for bit; one launch fewer."""
+    for tokens, alpha in ((2048, 0.0), (1500, 3.0), (256, 0.0), (37, 2.0), (1, 0.0)):
         hidden, router_w, bias = synth.make_activations(tokens, alpha or None, seed=12)
         layer = make_layer(gpu_weights, router_w, tokens, bias)
         out_a, inter_a = run_layer(layer, hidden)
+        launches = layer.launches_per_call(tokens)
         layer.set_row_gather(True)
-        assert layer.launches_per_call(tokens) == 8
+        assert layer.launches_per_call(tokens) == launches - 1
         layer.intermediates(tokens)["a_fp8"][: tokens * 8].zero_()          # nothing may read the sorted copy now
         out_b, inter_b = run_layer(layer, hidden)
         rows = tokens * 9
