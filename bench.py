@@ -39,11 +39,11 @@ FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes (read + write) of one grouped gate_up launch at decode T=256, from one ncu capture
 # (dram__bytes_read.sum + dram__bytes_write.sum), with the hash of the kernel source it was taken on:
 # the figure is reported only while that source is unchanged.
-GATE_UP_DRAM_TRAFFIC = {"bytes": 544_990_037, "source": "netra_kernel_b200/csrc/umma_kernels.cu",
-                        "sha256": "63884baad35be62934a91b2dec096ba9e581627fe7990a13d13e0edef4cc0610"}
+GATE_UP_DRAM_TRAFFIC = {"bytes": 545_067_520, "source": "netra_kernel_b200/csrc/umma_kernels.cu",
+                        "sha256": "b2fcd87e1fb92d2502b4abf24ba60658e82304b954101d119098ac6b18edb4ee"}
 # the same two figures for netra_moe_gate_up_mxfp4_sm100 (MXFP4 weights, T=256); None until captured
-MXFP4_GATE_UP_DRAM_TRAFFIC = {"bytes": 291_713_024, "source": "netra_kernel_b200/csrc/umma_kernels.cu",
-                              "sha256": "63884baad35be62934a91b2dec096ba9e581627fe7990a13d13e0edef4cc0610"}
+MXFP4_GATE_UP_DRAM_TRAFFIC = {"bytes": 291_597_739, "source": "netra_kernel_b200/csrc/umma_kernels.cu",
+                              "sha256": "b2fcd87e1fb92d2502b4abf24ba60658e82304b954101d119098ac6b18edb4ee"}
 STACK_LAYERS = 40
 STACK_TOKENS = 16384
 NVLINK_GBS = 770.0            # measured peer copy per direction per GPU on this pool
