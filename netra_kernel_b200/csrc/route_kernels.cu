@@ -852,7 +852,8 @@ netra_moe_combine_sm100(uint16_t* __restrict__ out, const float* __restrict__ do
   combine_rows_body<false>(out, down, w9, inv_perm, rows);
 }
 
-// The same combine over FP16 partial rows (written by netra_moe_down_tokmajor_f16_sm100): each partial is widened to
+// The same combine over FP16 partial rows (written by netra_moe_down_tokmajor_f16_sm100 as sixteen column panels
+// [rows * 9][128 halves] with the 16-byte chunks of a row permuted by the row index): each partial is widened to
 // FP32, multiplied by its routing weight and added in slot order, one BF16 rounding at the end - the order of
 // kernels/gfx950/templates/moe/prefill/route_reduce_splitk2_f16.inc:107-118.  grid rows, block 256 (8 columns per thread).
 extern "C" __global__ void __launch_bounds__(256)
@@ -860,13 +861,16 @@ netra_moe_combine_f16_sm100(uint16_t* __restrict__ out, const __half* __restrict
                             const float* __restrict__ w9, const int32_t* __restrict__ inv_perm, uint32_t rows) {
   const int t = blockIdx.x;
   const int pairs = (int)rows * kTopK;
+  const size_t total = (size_t)pairs + rows;      // rows of every column panel
   uint4 v[kSlots];
   float w[kSlots];
 #pragma unroll
   for (int s = 0; s < kSlots; ++s) {
     const size_t pos = s < kTopK ? (size_t)inv_perm[t * kTopK + s] : (size_t)pairs + t;
     w[s] = w9[t * kSlots + s];
-    v[s] = reinterpret_cast<const uint4*>(down + pos * kHidden)[threadIdx.x];
+    // panel threadIdx.x / 16 (128 columns), chunk threadIdx.x % 16 of the row, stored at chunk ^ (row & 15)
+    const size_t chunk = ((size_t)(threadIdx.x >> 4) * total + pos) * 16 + ((threadIdx.x & 15u) ^ ((uint32_t)pos & 15u));
+    v[s] = reinterpret_cast<const uint4*>(down)[chunk];
   }
   float acc[8];
 #pragma unroll

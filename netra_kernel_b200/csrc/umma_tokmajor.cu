@@ -90,9 +90,10 @@ struct TmCfg {
   static constexpr int kScaleSlotBytes = kXsBytes + 128;
   static constexpr int kItemList = 256;
   static constexpr int kEpiGroups = 2;                                      // epilogue warpgroups
-  // FP16 output staging: one row of 128 halves per epilogue thread, rows 272 bytes apart (16 bytes of padding keep
-  // the 16-byte shared-memory stores of a quarter warp on different banks)
-  static constexpr int kOutRowBytes = 272;
+  // FP16 output staging: one tile of 128 rows x 128 halves per epilogue warpgroup, rows 256 bytes apart; the 16-byte
+  // chunks of a row are permuted (chunk j sits at j ^ (row & 15)), which keeps the 16-byte shared-memory stores of a
+  // quarter warp on different banks and is the layout the rows keep in global memory
+  static constexpr int kOutRowBytes = 256;
   static constexpr int kOutStageBytes = kF16Out ? kEpiGroups * kLanes * kOutRowBytes : 0;
   static constexpr int kSmemBytes = 1024 + kStages * (kStageBytes + kAtomStageBytes) + kScaleSlots * kScaleSlotBytes + kOutStageBytes +
                                     2 * kEpiGroups * kLanes * 4 + 2 * 264 * 4 + kItemList * 16 + 512;
@@ -432,6 +433,7 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
     const int seg_col0 = kGateUp ? wg * 64 : wg * 128;
     const int seg_col1 = kGateUp ? 128 + wg * 64 : wg * 128 + 64;
     const int ws0 = kGateUp ? 0 : wg, ws1 = kGateUp ? 1 : wg;
+    const int total_rows = offs[groups];     // rows of this call: the row count of every FP16 output panel
     uint32_t it = 0, n_item = 0;
     bool ok = true;
     for (int item = first_item; item < total_items; item += stride, ++n_item) {
@@ -520,11 +522,19 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
           if (wg == 0) h_scale[row * kInterBlocks + w.ntile] = scale;
         }
       } else if constexpr (kF16Out) {
-        // FP16 partial rows (the reference's prefill contract, kernels/gfx950/templates/moe/prefill/fused_splitk2/down_partial.inc:435-458):
-        // the thread packs its 128 columns into its own staging row and hands the row to the copy engine, which writes
-        // 256 contiguous bytes - the thread itself never issues scattered global stores
-        uint8_t* my_row = out_stage + (size_t)(wg * C::kLanes + r) * C::kOutRowBytes;
-        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");      // the previous item's copy has read this row
+        // FP16 partial rows (the reference's prefill contract, kernels/gfx950/templates/moe/prefill/fused_splitk2/down_partial.inc:435-458).
+        // Layout in global memory: sixteen column panels of 128 halves, panel p = [total rows][256 bytes], the sixteen
+        // 16-byte chunks of a row permuted by the row's index (chunk j at position j ^ (row & 15); the reducer
+        // netra_moe_combine_f16_sm100 reads them back the same way).  A warpgroup's item is then one contiguous block
+        // of its panel: the threads stage their rows in shared memory in exactly that image and ONE bulk copy of
+        // m_valid x 256 bytes writes it - the copy engine's cost is per copy (one 256-byte copy per thread took
+        // 3,500 of an item's 8,700 cycles), not per byte.
+        uint8_t* tile = out_stage + (size_t)wg * (C::kLanes * C::kOutRowBytes);
+        const bool elected = quad == 0 && lane == 0;
+        if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous item's copy has read the tile
+        group_barrier(wg);
+        const uint32_t key = (uint32_t)(w.row0 + r) & 15u;
+        uint8_t* my_row = tile + (size_t)r * C::kOutRowBytes;
 #pragma unroll
         for (int q = 0; q < 16; ++q) {
           const float* a = q < 8 ? &acc0[8 * q] : &acc1[8 * (q - 8)];
@@ -534,14 +544,16 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
             const __half2 h = __floats2half2_rn(a[2 * j], a[2 * j + 1]);
             pk[j] = *reinterpret_cast<const uint32_t*>(&h);
           }
-          *reinterpret_cast<uint4*>(my_row + 16 * q) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          *reinterpret_cast<uint4*>(my_row + 16 * ((uint32_t)q ^ key)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        if (live) {
-          __half* gdst = reinterpret_cast<__half*>(down) + row * kHidden + w.ntile * 2 * kTileRows + wg * kTileRows;
-          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 256;" ::"l"(gdst), "r"(smem_u32(my_row)) : "memory");
+        group_barrier(wg);
+        if (elected) {
+          __half* gdst = reinterpret_cast<__half*>(down) + ((size_t)(w.ntile * 2 + wg) * (size_t)total_rows + (size_t)w.row0) * kTileRows;
+          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(tile)),
+                       "r"((uint32_t)w.m_valid * (uint32_t)C::kOutRowBytes) : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
-        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
       } else {
         if (live) {
           // a lane owns a whole row, so a warp's stores touch 32 rows: 256-bit stores fill one 32-byte sector each

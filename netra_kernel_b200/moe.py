@@ -38,6 +38,15 @@ def workspace_layout(tokens: int) -> abi.WorkspaceLayout:
     return lay
 
 
+def _f16_rows_from_panels(raw: "torch.Tensor", rows: int) -> "torch.Tensor":
+    """Row-major [rows, 2048] copy of the FP16 partial rows, which the down projection stores as sixteen column panels
+    [rows, 128] whose 16-byte chunks are permuted by the row index (chunk j of row p sits at position j ^ (p & 15))."""
+    panels = raw.view(HIDDEN // 128, rows, 16, 8)
+    pos = torch.arange(16, device=raw.device)[None, :] ^ (torch.arange(rows, device=raw.device)[:, None] & 15)   # [rows, chunk j] -> position
+    idx = pos[None, :, :, None].expand(HIDDEN // 128, rows, 16, 8)
+    return panels.gather(2, idx).permute(1, 0, 2, 3).reshape(rows, HIDDEN)
+
+
 class RoutedMoELayer:
     """One routed-MoE layer bound to persistent device weights and a private workspace."""
 
@@ -258,7 +267,7 @@ class RoutedMoELayer:
             "h_fp8": view(lay.h_fp8, rows * INTER, torch.uint8).view(rows, INTER),
             "h_scale": view(lay.h_scale, rows * 4, torch.float32).view(rows, 4),
             "down": view(lay.down_f32, rows * HIDDEN, torch.float32).view(rows, HIDDEN),
-            "down_f16": view(lay.down_f32, rows * HIDDEN, torch.float16).view(rows, HIDDEN),
+            "down_f16": _f16_rows_from_panels(view(lay.down_f32, rows * HIDDEN, torch.float16), rows),
             "logits_f32": view(lay.logits_f32, tokens * N_ROUTED, torch.float32).view(tokens, N_ROUTED),
             "wnorm": view(lay.wnorm, N_ROUTED, torch.float32),
         }
