@@ -24,3 +24,16 @@ def test_handles_and_the_missing_cpu_path():
     assert handle not in torch_ops._layers
     with pytest.raises(Exception):          # no CPU kernel is registered: the ops exist for CUDA tensors only
         torch.ops.netra.moe_layer(torch.zeros(2, 2048, dtype=torch.bfloat16), handle)
+
+
+def test_fp16_partial_row_panels_read_back_as_rows():
+    """The down projection's FP16 partial rows are stored as sixteen column panels [rows, 128] with the 16-byte chunks
+    of a panel row permuted by the row index; the host-side view used by the parity tests undoes exactly that."""
+    from netra_kernel_b200.moe import _f16_rows_from_panels
+    rows = 37
+    logical = torch.arange(rows * 2048, dtype=torch.float32).remainder(2039).view(rows, 2048).to(torch.float16)
+    raw = torch.zeros(16, rows, 16, 8, dtype=torch.float16)
+    for p in range(rows):
+        for j in range(16):
+            raw[:, p, j ^ (p & 15)] = logical[p].view(16, 16, 8)[:, j]
+    assert torch.equal(_f16_rows_from_panels(raw.reshape(-1), rows), logical)
