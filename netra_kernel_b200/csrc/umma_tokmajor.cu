@@ -508,16 +508,18 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
         const float scale = fmaxf(m, amax_floor()) * inv448();
         const float inv = rcp_newton(scale);
         if (live) {
-          uint4* dst = reinterpret_cast<uint4*>(h_fp8 + row * kInter + w.ntile * kTileRows + wg * 64);
+          // the thread's 64 bytes as two 32-byte stores: a lane owns a row, so every store is a sector of its own, and
+          // a full one (16-byte stores half-fill each sector twice)
+          float* dst = reinterpret_cast<float*>(h_fp8 + row * kInter + w.ntile * kTileRows + wg * 64);
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint32_t p[4];
+          for (int q = 0; q < 2; ++q) {
+            float p[8];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int c = q * 16 + j * 4;
-              p[j] = f32x4_to_e4m3x4(acc0[c] * inv, acc0[c + 1] * inv, acc0[c + 2] * inv, acc0[c + 3] * inv);
+            for (int j = 0; j < 8; ++j) {
+              const int c = q * 32 + j * 4;
+              p[j] = __uint_as_float(f32x4_to_e4m3x4(acc0[c] * inv, acc0[c + 1] * inv, acc0[c + 2] * inv, acc0[c + 3] * inv));
             }
-            dst[q] = make_uint4(p[0], p[1], p[2], p[3]);
+            st_global_v8(dst + 8 * q, p);
           }
           if (wg == 0) h_scale[row * kInterBlocks + w.ntile] = scale;
         }
