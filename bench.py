@@ -756,14 +756,14 @@ def make_stack_single(dev, layers, tokens, stream):
 
 def stack_bounds(tokens_total, world, remote_pairs_per_rank) -> dict:
     """Per-layer lower bounds of one rank: its expert slabs from HBM, its rows on the FP8 tensor cores, its rows over
-    NVLink (FP8 row + scales out, FP32 row back)."""
+    NVLink (FP8 row + scales out, FP16 partial row back)."""
     hbm_peak, hbm_kind = measured_hbm_peak()
     fp8_peak, fp8_kind = measured_fp8_peak()
     slabs = 256 // world + 1
     hbm_bytes = slabs * (2 * 512 * 2048 + 2048 * 512 + 4 * (8 * 16 + 16 * 4)) + 2 * (tokens_total // world) * 2048 * 2
     rows = tokens_total * 8 // world + tokens_total // world
     flops = rows * (2 * 2048 * 1024 + 2 * 512 * 2048)
-    nv_bytes = remote_pairs_per_rank * (2048 + 64 + 2048 * 4)
+    nv_bytes = remote_pairs_per_rank * (2048 + 64 + 2048 * 2)
     times = {"hbm": hbm_bytes / hbm_peak / 1e6, "tensor": flops / fp8_peak / 1e9, "nvlink": nv_bytes / NVLINK_GBS / 1e6}
     bound = max(times, key=times.get)
     return {"per_layer_ms": times, "binding": bound, "bound_ms_per_layer": times[bound],
@@ -1115,6 +1115,7 @@ def expert_parallel_extras(args, plan, dev, stream, sync: Sync, router_dev):
             del full
             layers.append(PeerExpertParallelLayer(plan, router_dev, *local, max_local_tokens=t_local, wait_timeout_s=10.0,
                                                   share_with=layers[0] if layers else None))
+            layers[-1].set_partial_format(1)       # the prefill contract, as the one-GPU stack: FP16 partial rows
             del local
         stream.synchronize()
         dist.barrier()
@@ -1124,6 +1125,7 @@ def expert_parallel_extras(args, plan, dev, stream, sync: Sync, router_dev):
         layers[0].check_status()
         dist.barrier()
         single = RoutedMoELayer(router_dev, *full0, t_local)
+        single.set_partial_format(1)
         del full0
         want = single(hidden)
         stream.synchronize()
@@ -1136,14 +1138,15 @@ def expert_parallel_extras(args, plan, dev, stream, sync: Sync, router_dev):
     mismatched_ranks = sync.sum_int(0 if same else 1)
     if mismatched_ranks:
         raise SystemExit(f"expert-parallel parity: {mismatched_ranks} of {world} ranks differ from the one-GPU layer")
-    parity = {"vs": "single-GPU layer (netra_moe_layer_launch) run by every rank on its own tokens with all 257 slabs of layer 0",
+    parity = {"vs": "single-GPU layer (netra_moe_layer_launch, FP16 partial rows as in the stack) run by every rank on its own tokens "
+                    "with all 257 slabs of layer 0",
               "bit_exact": True, "rows": STACK_TOKENS, "rows_per_rank": t_local, "ranks": world, "layer": 0}
     own = plan.local_expert_range()
     remote_pairs = int(counts.sum().item() - counts[own.start:own.stop].sum().item())
     remote_pairs = sync.sum_int(remote_pairs) // world          # mean over ranks
     stack = stack_object(layers, hs, max(3, min(args.steps, 8)), 3, dev, stream, sync, world,
                          f"ep{world}: {plan.experts_per_rank} routed experts per GPU, shared expert and router replicated; rows "
-                         "pushed into the owners' windows over NVLink, FP32 rows returned by the down epilogue",
+                         "pushed into the owners' windows over NVLink, FP16 partial rows sent home by a pass after the down projection",
                          remote_pairs, "netra_ep_layer_launch per layer, one captured CUDA graph")
     for l in layers:
         l.close()

@@ -93,6 +93,7 @@ SIGNATURES = {
     "netra_ep_layer_launch_count": (c_u32, [c_void_p, c_u32]),
     "netra_ep_layer_status": (c_int, [c_void_p, ctypes.POINTER(c_u32 * 4)]),
     "netra_ep_layer_destroy": (c_int, [c_void_p]),
+    "netra_ep_layer_set_partial_format": (c_int, [c_void_p, c_u32]),
     "netra_moe_kernel_launch_info": (c_int, [c_u32, ctypes.POINTER(c_u32), ctypes.POINTER(c_u32)]),
     "netra_moe_layer_set_gemm_mode": (c_int, [c_void_p, c_u32]),
     "netra_moe_layer_set_front_mode": (c_int, [c_void_p, c_u32]),

@@ -393,6 +393,59 @@ netra_ep_down_return_tokmajor_sm100(const __grid_constant__ CUtensorMap tm_w2, c
   ep_signal_when_last(peers, lay, tab, &tab->done_ret, 2, world, rank);
 }
 
+// FP16 partial rows (the prefill contract) across GPUs, for blocks served by the token-major GEMMs: the down projection
+// (netra_moe_down_tokmajor_f16_sm100) writes this rank's block as column panels into local memory at full speed, and this
+// kernel sends every block row home - to the sorted-order buffer of the rank it came from, in that rank's own panel
+// layout (sixteen panels [9 * its tokens][128 halves], 16-byte chunks of a panel row permuted by the row index), which is
+// what its reducer reads.  Half the NVLink bytes of the FP32 return, and 256 contiguous bytes per half warp.
+// One warp per block row, grid-stride; block 256.  The last block raises flag 2 at every peer.
+extern "C" __global__ void __launch_bounds__(256)
+netra_ep_return_rows_f16_sm100(EpPeers peers, EpWindowLayout lay, EpTables* __restrict__ tab, const uint8_t* __restrict__ window,
+                               const __half* __restrict__ blk_rows, uint32_t tokens, uint32_t max_tokens, uint32_t world,
+                               uint32_t rank, uint32_t capacity, uint32_t groups) {
+  __shared__ int s_start[kRouted + 1];
+  for (int i = threadIdx.x; i <= kRouted; i += blockDim.x) s_start[i] = tab->blk_start[i];
+  __syncthreads();
+  const int total = min(s_start[kRouted], (int)capacity);
+  const size_t src_total = (size_t)tab->offsets[groups];          // the panel pitch the down projection used
+  const int lane = threadIdx.x & 31;
+  const uint4* src = reinterpret_cast<const uint4*>(blk_rows);
+  for (int r = blockIdx.x * 8 + (threadIdx.x >> 5); r < total; r += gridDim.x * 8) {
+    int g, dst_row;
+    if (r < (int)tokens) {
+      g = (int)rank;
+      dst_row = (int)tokens * kTopK + r;
+    } else {
+      int lo = 0, hi = kRouted;              // last bucket whose first row is <= r
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (s_start[mid] <= r) lo = mid; else hi = mid;
+      }
+      g = lo % (int)world;
+      dst_row = tab->ret_row[lo] + (r - s_start[lo]);
+    }
+    if (dst_row < 0 || dst_row >= (int)max_tokens * kSlots) continue;
+    const size_t dst_total = (size_t)reinterpret_cast<const int32_t*>(window + lay.matrix)[g * kEpMatrixPitch + kRouted] * kSlots;
+    uint4* dst = reinterpret_cast<uint4*>(peers.win[g] + lay.down);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t c = (uint32_t)(i * 32 + lane), panel = c >> 4, j = c & 15u;      // chunk j of the row's panel
+      const uint4 v = src[((size_t)panel * src_total + (size_t)r) * 16 + (j ^ ((uint32_t)r & 15u))];
+      dst[((size_t)panel * dst_total + (size_t)dst_row) * 16 + (j ^ ((uint32_t)dst_row & 15u))] = v;
+    }
+  }
+  ep_signal_when_last(peers, lay, tab, &tab->done_ret, 2, world, rank);
+}
+
+// The reducer over FP16 partial rows that the peers returned: every block waits for flag 2 of every rank (bounded) first.
+extern "C" __global__ void __launch_bounds__(256)
+netra_ep_combine_f16_sm100(uint16_t* __restrict__ out, const __half* down, const float* __restrict__ w9,
+                           const int32_t* __restrict__ inv_perm, uint32_t rows, const uint8_t* window, EpWindowLayout lay,
+                           EpTables* tab, uint32_t world, uint64_t timeout_ns) {
+  ep_block_wait_phase(window, lay, tab, 2, world, timeout_ns);
+  combine_f16_rows_body<true>(out, down, w9, inv_perm, rows);
+}
+
 }  // namespace netra
 
 // ------------------------------------------------------------------ host side (C ABI, include/netra_moe.h)
@@ -414,6 +467,7 @@ struct netra_ep_layer {
   int sm_count;
   uint32_t e_l;
   bool tokmajor_ok;                // the fused-return token-major kernel was built with the register allocation it assumes
+  bool partial_f16;                // calls served by the token-major GEMMs return FP16 partial rows (the prefill contract)
 };
 
 namespace {
@@ -460,6 +514,11 @@ int ep_check_shape(uint32_t world, uint32_t max_tokens, uint32_t capacity) {
   return 0;
 }
 
+// FP16 partial rows are a contract of the token-major GEMM form (calls whose experts hold many rows), as in the one-GPU layer
+bool ep_f16_call(const netra_ep_layer* L, uint32_t pairs) {
+  return L->partial_f16 && L->tokmajor_ok && use_tokmajor(L->route->device, (uint64_t)L->desc.world * pairs, kRouted);
+}
+
 int ep_launch_stage(netra_ep_layer* L, uint32_t stage, const void* hidden, const float* shared_w, void* out, uint32_t tokens,
                     cudaStream_t stream) {
   const netra_ep_layer_desc_t& d = L->desc;
@@ -497,7 +556,17 @@ int ep_launch_stage(netra_ep_layer* L, uint32_t stage, const void* hidden, const
             L->blk_h, L->blk_hs, L->e_l + 1, d.weights_tiled, L->tab->status, L->window, L->wl, L->tab, d.world, d.wait_timeout_ns);
       break;
     case 7:
-      // Across GPUs the swap-AB form is kept for the down projection whatever the size: its epilogue stores 128
+      if (ep_f16_call(L, pairs)) {
+        // the prefill contract: the block's FP16 rows at the speed of the one-GPU kernel, then one pass that sends them home
+        netra_moe_down_tokmajor_f16_sm100<<<L->sm_count, kTmThreads, down_tokmajor_f16_smem_bytes(), stream>>>(
+            L->tm_w2, L->tm_h128, L->blk_hs, d.w2_scale_f32, L->tab->offsets, (void*)L->blk_down, L->e_l + 1, d.weights_tiled,
+            L->tab->status + 1);
+        netra_ep_return_rows_f16_sm100<<<2 * L->sm_count, 256, 0, stream>>>(L->peers, L->wl, L->tab, L->window,
+                                                                            (const __half*)L->blk_down, tokens, d.max_tokens, d.world,
+                                                                            d.rank, d.row_capacity, L->e_l + 1);
+        break;
+      }
+      // Across GPUs the swap-AB form is kept for the FP32-row down projection whatever the size: its epilogue stores 128
       // contiguous bytes of one row per warp instruction, while a token-major thread owns a whole row and a warp
       // instruction scatters 32-byte pieces over 32 rows - over NVLink that took three times as long (8 GPUs,
       // 64 rows per expert: 77 us against 25 us of GEMM time).
@@ -511,6 +580,12 @@ int ep_launch_stage(netra_ep_layer* L, uint32_t stage, const void* hidden, const
             d.weights_tiled, L->tab->status + 1, L->peers, L->wl, L->tab, d.world, d.rank);
       break;
     default:
+      if (ep_f16_call(L, pairs)) {
+        netra_ep_combine_f16_sm100<<<tokens, 256, 0, stream>>>((uint16_t*)out, (const __half*)(L->window + L->wl.down),
+                                                               (const float*)(ws + R.topk_weights), (const int32_t*)(ws + R.inv_perm),
+                                                               tokens, L->window, L->wl, L->tab, d.world, d.wait_timeout_ns);
+        break;
+      }
       netra_ep_combine_sm100<<<tokens, 256, 0, stream>>>((uint16_t*)out, (const float*)(L->window + L->wl.down),
                                                          (const float*)(ws + R.topk_weights), (const int32_t*)(ws + R.inv_perm), tokens,
                                                          L->window, L->wl, L->tab, d.world, d.wait_timeout_ns);
@@ -592,6 +667,7 @@ int netra_ep_layer_create(const netra_ep_layer_desc_t* desc, netra_ep_layer_t** 
   L->desc = *desc;
   L->desc.windows = nullptr;       // the pointers are copied below; the caller's array need not outlive this call
   L->e_l = kRouted / desc->world;
+  L->partial_f16 = false;
   L->wl = wl;
   memset(&L->peers, 0, sizeof L->peers);
   for (uint32_t g = 0; g < desc->world; ++g) L->peers.win[g] = (uint8_t*)desc->windows[g];
@@ -664,7 +740,7 @@ uint32_t netra_ep_layer_stage_count(void) { return kEpStageCount; }
 uint32_t netra_ep_layer_launch_count(const netra_ep_layer_t* L, uint32_t tokens) {
   if (!L) return 0;
   // a whole call runs publish and plan as one launch; above 1,024 tokens the sort is three launches
-  if (tokens > (uint32_t)kSortSmallMaxRows) return kEpStageCount - 1 + 2;
+  if (tokens > (uint32_t)kSortSmallMaxRows) return kEpStageCount - 1 + 2 + (ep_f16_call(L, tokens * kTopK) ? 1 : 0);   // + the FP16 return pass
   return kEpStageCount - 1 - (L->route->front_mode == 1 ? 2 : 0);                       // router, top-k and sort as one launch
 }
 
@@ -692,6 +768,12 @@ int netra_ep_layer_launch_stage(netra_ep_layer_t* L, uint32_t stage, const void*
   if (stage >= kEpStageCount) return fail("ep_layer_launch_stage: stage out of range");
   if (int rc = ep_launch_stage(L, stage, hidden, shared_w, out, tokens, stream)) return rc;
   return check_launch("ep_layer stage launch");
+}
+
+int netra_ep_layer_set_partial_format(netra_ep_layer_t* L, uint32_t format) {
+  if (L == nullptr || format > 1) return fail("ep_layer_set_partial_format: null layer or unknown format");
+  L->partial_f16 = format == 1;
+  return 0;
 }
 
 int netra_ep_layer_status(netra_ep_layer_t* L, uint32_t status_out[4]) {

@@ -856,9 +856,10 @@ netra_moe_combine_sm100(uint16_t* __restrict__ out, const float* __restrict__ do
 // [rows * 9][128 halves] with the 16-byte chunks of a row permuted by the row index): each partial is widened to
 // FP32, multiplied by its routing weight and added in slot order, one BF16 rounding at the end - the order of
 // kernels/gfx950/templates/moe/prefill/route_reduce_splitk2_f16.inc:107-118.  grid rows, block 256 (8 columns per thread).
-extern "C" __global__ void __launch_bounds__(256)
-netra_moe_combine_f16_sm100(uint16_t* __restrict__ out, const __half* __restrict__ down,
-                            const float* __restrict__ w9, const int32_t* __restrict__ inv_perm, uint32_t rows) {
+// kFromL2: the rows were written by other GPUs into this one's memory and are read around the L1.
+template <bool kFromL2>
+__device__ __forceinline__ void combine_f16_rows_body(uint16_t* __restrict__ out, const __half* down,
+                                                      const float* __restrict__ w9, const int32_t* __restrict__ inv_perm, uint32_t rows) {
   const int t = blockIdx.x;
   const int pairs = (int)rows * kTopK;
   const size_t total = (size_t)pairs + rows;      // rows of every column panel
@@ -870,7 +871,8 @@ netra_moe_combine_f16_sm100(uint16_t* __restrict__ out, const __half* __restrict
     w[s] = w9[t * kSlots + s];
     // panel threadIdx.x / 16 (128 columns), chunk threadIdx.x % 16 of the row, stored at chunk ^ (row & 15)
     const size_t chunk = ((size_t)(threadIdx.x >> 4) * total + pos) * 16 + ((threadIdx.x & 15u) ^ ((uint32_t)pos & 15u));
-    v[s] = reinterpret_cast<const uint4*>(down)[chunk];
+    const uint4* src = reinterpret_cast<const uint4*>(down) + chunk;
+    v[s] = kFromL2 ? __ldcg(src) : *src;
   }
   float acc[8];
 #pragma unroll
@@ -892,6 +894,12 @@ netra_moe_combine_f16_sm100(uint16_t* __restrict__ out, const __half* __restrict
     pk[i] = *reinterpret_cast<uint32_t*>(&b);
   }
   reinterpret_cast<uint4*>(out + (size_t)t * kHidden)[threadIdx.x] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+}
+
+extern "C" __global__ void __launch_bounds__(256)
+netra_moe_combine_f16_sm100(uint16_t* __restrict__ out, const __half* __restrict__ down,
+                            const float* __restrict__ w9, const int32_t* __restrict__ inv_perm, uint32_t rows) {
+  combine_f16_rows_body<false>(out, down, w9, inv_perm, rows);
 }
 
 }  // namespace netra

@@ -416,6 +416,11 @@ class PeerExpertParallelLayer:
     def launches_per_call(self, tokens: int) -> int:
         return int(self.lib.netra_ep_layer_launch_count(self.handle, tokens))
 
+    def set_partial_format(self, fmt: int) -> None:
+        """1: calls served by the token-major GEMMs return FP16 partial rows (the reference's prefill contract; half the
+        NVLink bytes); 0: FP32 rows.  Every rank of the world must use the same format."""
+        self.abi.check(self.lib.netra_ep_layer_set_partial_format(self.handle, fmt), "ep_layer_set_partial_format")
+
     def _args(self, hidden, shared_weight, out):
         if hidden.dtype != torch.bfloat16 or hidden.dim() != 2 or hidden.shape[1] != HIDDEN or not hidden.is_contiguous():
             raise ValueError("hidden must be contiguous BF16 [tokens, 2048]")

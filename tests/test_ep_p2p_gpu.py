@@ -84,6 +84,51 @@ def test_emulated_ranks_equal_the_one_gpu_layer(expert_weights, world, tokens, a
     full.close()
 
 
+@pytest.mark.parametrize("world,tokens,alpha", [(1, 1024, 0.0), (2, 4096, 0.3), (4, 2048, 0.6), (8, 2048, 0.0)])
+def test_emulated_ranks_with_fp16_partial_rows_equal_the_one_gpu_layer(expert_weights, world, tokens, alpha):
+    """The prefill contract across ranks: the block's down rows as FP16 partials, sent home by the return pass in the
+    receiver's panel layout, reduced by the FP16 reducer - bit for bit the one-GPU layer with the same setting."""
+    from netra_kernel_b200.moe import RoutedMoELayer
+    dev = torch.device("cuda", 0)
+    hidden, router_w, bias = synth.make_activations(tokens, alpha or None, seed=9)
+    hidden, router_w = hidden.to(dev), router_w.to(dev)
+    bias = bias.to(dev) if bias is not None else None
+    layers, keep = _emulated_ranks(world, tokens, expert_weights, router_w, bias, dev)
+    for layer in layers:
+        layer.set_partial_format(1)
+    t_l = tokens // world
+    parts = [hidden[r * t_l:(r + 1) * t_l].contiguous() for r in range(world)]
+    outs = [torch.zeros_like(p) for p in parts]
+    for call in range(2):                                           # the second call reuses every buffer and flag
+        _interleaved_call(layers, parts, outs)
+        torch.cuda.synchronize()
+        for layer in layers:
+            layer.check_status()
+        if call == 0:
+            first = torch.cat(outs).clone()
+    full = RoutedMoELayer(router_w, *(t.to(dev) for t in expert_weights), tokens, bias)
+    full.set_partial_format(1)
+    want = full(hidden)
+    torch.cuda.synchronize()
+    full.check_status()
+    assert torch.equal(torch.cat(outs).view(torch.int16), want.view(torch.int16))
+    assert torch.equal(first.view(torch.int16), want.view(torch.int16))
+    full.set_partial_format(0)
+    assert not torch.equal(full(hidden).view(torch.int16), want.view(torch.int16))     # the two contracts do differ
+    # a small call under the same setting keeps the FP32 rows (swap-AB forms), as the one-GPU layer does
+    small = [p[:8].contiguous() for p in parts]
+    small_out = [torch.zeros_like(p) for p in small]
+    _interleaved_call(layers, small, small_out)
+    torch.cuda.synchronize()
+    for layer in layers:
+        layer.check_status()
+    want_small = full(torch.cat(small))
+    assert torch.equal(torch.cat(small_out).view(torch.int16), want_small.view(torch.int16))
+    for layer in layers:
+        layer.close()
+    full.close()
+
+
 def test_block_that_needs_more_rows_than_its_capacity_is_reported(expert_weights):
     dev = torch.device("cuda", 0)
     world, tokens = 2, 256
@@ -130,7 +175,7 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _peer_rank(rank, world, port, tokens, results):
+def _peer_rank(rank, world, port, tokens, results, partial_format=0):
     try:
         import torch.distributed as dist
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -143,6 +188,7 @@ def _peer_rank(rank, world, port, tokens, results):
         local = tuple(t.to(dev) for t in shard_expert_weights(weights, plan))
         t_l = tokens // world
         layer = PeerExpertParallelLayer(plan, router_w.to(dev), *local, max_local_tokens=t_l, router_bias=bias.to(dev))
+        layer.set_partial_format(partial_format)
         mine = hidden[rank * t_l:(rank + 1) * t_l].to(dev)
         stream = torch.cuda.Stream(device=dev)
         torch.cuda.synchronize(dev)
@@ -165,6 +211,7 @@ def _peer_rank(rank, world, port, tokens, results):
         if rank == 0:                                        # one-GPU layer over all tokens, same weights
             from netra_kernel_b200.moe import RoutedMoELayer
             full = RoutedMoELayer(router_w.to(dev), *(t.to(dev) for t in weights), tokens, bias.to(dev))
+            full.set_partial_format(partial_format)
             results["ref"] = full(hidden.to(dev)).cpu()
             full.check_status()
         dist.barrier()
@@ -175,13 +222,13 @@ def _peer_rank(rank, world, port, tokens, results):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("tokens", [512, 2048])      # 2,048 tokens: 64 rows per expert, the token-major GEMMs and their fused return
-def test_two_gpu_peer_memory_layer_equals_the_one_gpu_layer(tokens):
+@pytest.mark.parametrize("tokens,partial_format", [(512, 0), (2048, 0), (2048, 1)])      # 2,048 tokens: 64 rows per expert, the
+def test_two_gpu_peer_memory_layer_equals_the_one_gpu_layer(tokens, partial_format):       # token-major GEMMs; 1: FP16 rows sent home
     world = 2
     manager = mp.Manager()
     results = manager.dict()
     port = _free_port()
-    procs = [mp.get_context("spawn").Process(target=_peer_rank, args=(r, world, port, tokens, results)) for r in range(world)]
+    procs = [mp.get_context("spawn").Process(target=_peer_rank, args=(r, world, port, tokens, results, partial_format)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
