@@ -355,9 +355,9 @@ int netra_ep_layer_launch_stage(netra_ep_layer_t* layer, uint32_t stage, const v
 uint32_t netra_ep_layer_stage_count(void);
 uint32_t netra_ep_layer_launch_count(const netra_ep_layer_t* layer, uint32_t tokens);
 /* format 1: calls served by the token-major GEMMs (an average of 32 rows per routed expert over all ranks, or more) use
- * the prefill contract of netra_moe_layer_set_partial_format: the down projection writes this rank's block as FP16 partial
- * rows, a second launch sends every row home over NVLink (half the bytes of the FP32 return, 256 contiguous bytes per half
- * warp), and the reducer widens them (f32(p) * w, slot ascending, one BF16 rounding).  Results equal the one-GPU layer
+ * the prefill contract of netra_moe_layer_set_partial_format: the token-major down projection rounds its rows to FP16
+ * partials and its epilogue sends every run of rows that one source sent to one expert home as one bulk copy over NVLink
+ * (half the bytes of the FP32 return), and the reducer widens them (f32(p) * w, slot ascending, one BF16 rounding).  Results equal the one-GPU layer
  * with the same setting bit for bit.  Every rank of a world must use the same format.  format 0 (default): FP32 rows
  * stored by the down projection's epilogue. */
 int netra_ep_layer_set_partial_format(netra_ep_layer_t* layer, uint32_t format);

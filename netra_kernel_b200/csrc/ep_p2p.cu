@@ -254,7 +254,7 @@ __device__ __forceinline__ void ep_signal_when_last(const EpPeers& peers, const 
 
 __device__ __forceinline__ void ep_build_return_table(const EpPeers& peers, const EpWindowLayout& lay, const EpTables* __restrict__ tab,
                                                       float** __restrict__ row_ptr, float* __restrict__ blk_down, uint32_t tokens,
-                                                      uint32_t max_tokens, uint32_t world, uint32_t rank, uint32_t capacity);
+                                                      uint32_t max_tokens, uint32_t world, uint32_t rank, uint32_t capacity, uint32_t as_pairs);
 
 // push: sorted row i (i < pairs) of this rank -> its expert-major row in the owner's block;
 // rows pairs .. pairs + tokens - 1 are the rank's own tokens -> rows [0, tokens) of its own block.
@@ -264,8 +264,9 @@ extern "C" __global__ void __launch_bounds__(256)
 netra_ep_push_rows_sm100(EpPeers peers, EpWindowLayout lay, EpTables* __restrict__ tab, const uint8_t* __restrict__ a_fp8,
                          const float* __restrict__ a_scale, const int32_t* __restrict__ perm, const int32_t* __restrict__ ids9,
                          const int32_t* __restrict__ sorted_offsets, uint32_t tokens, uint32_t world, uint32_t rank,
-                         uint32_t capacity, float** __restrict__ row_ptr, float* __restrict__ blk_down, uint32_t max_tokens) {
-  ep_build_return_table(peers, lay, tab, row_ptr, blk_down, tokens, max_tokens, world, rank, capacity);
+                         uint32_t capacity, float** __restrict__ row_ptr, float* __restrict__ blk_down, uint32_t max_tokens,
+                         uint32_t table_as_pairs) {
+  ep_build_return_table(peers, lay, tab, row_ptr, blk_down, tokens, max_tokens, world, rank, capacity, table_as_pairs);
   const int pairs = (int)tokens * kTopK;
   const int i = blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -298,10 +299,11 @@ netra_ep_push_rows_sm100(EpPeers peers, EpWindowLayout lay, EpTables* __restrict
 
 // The return table: row_ptr[r] = where block row r's FP32 down row goes - the sorted-order buffer of the rank it came
 // from, or this rank's own shared rows (pairs + t) for the shared group.  Rows without a valid destination point at the
-// local block buffer.  Grid-stride over the block rows, block 256; needs only what the plan wrote.
+// local block buffer.  as_pairs: the same 8 bytes per row hold (rank, sorted row) instead, (-1, -1) without a valid
+// destination - the form the FP16 return takes.  Grid-stride over the block rows, block 256; needs only what the plan wrote.
 __device__ __forceinline__ void ep_build_return_table(const EpPeers& peers, const EpWindowLayout& lay, const EpTables* __restrict__ tab,
                                                       float** __restrict__ row_ptr, float* __restrict__ blk_down, uint32_t tokens,
-                                                      uint32_t max_tokens, uint32_t world, uint32_t rank, uint32_t capacity) {
+                                                      uint32_t max_tokens, uint32_t world, uint32_t rank, uint32_t capacity, uint32_t as_pairs) {
   __shared__ int s_start[kRouted + 1];
   for (int i = threadIdx.x; i <= kRouted; i += blockDim.x) s_start[i] = tab->blk_start[i];
   __syncthreads();
@@ -320,9 +322,11 @@ __device__ __forceinline__ void ep_build_return_table(const EpPeers& peers, cons
       g = lo % (int)world;
       dst_row = tab->ret_row[lo] + (r - s_start[lo]);
     }
-    row_ptr[r] = (dst_row >= 0 && dst_row < (int)max_tokens * kSlots)
-                     ? reinterpret_cast<float*>(peers.win[g] + lay.down) + (size_t)dst_row * kHidden
-                     : blk_down + (size_t)r * kHidden;
+    const bool valid = dst_row >= 0 && dst_row < (int)max_tokens * kSlots;
+    if (as_pairs)
+      reinterpret_cast<int2*>(row_ptr)[r] = valid ? make_int2(g, dst_row) : make_int2(-1, -1);
+    else
+      row_ptr[r] = valid ? reinterpret_cast<float*>(peers.win[g] + lay.down) + (size_t)dst_row * kHidden : blk_down + (size_t)r * kHidden;
   }
 }
 
@@ -393,47 +397,16 @@ netra_ep_down_return_tokmajor_sm100(const __grid_constant__ CUtensorMap tm_w2, c
   ep_signal_when_last(peers, lay, tab, &tab->done_ret, 2, world, rank);
 }
 
-// FP16 partial rows (the prefill contract) across GPUs, for blocks served by the token-major GEMMs: the down projection
-// (netra_moe_down_tokmajor_f16_sm100) writes this rank's block as column panels into local memory at full speed, and this
-// kernel sends every block row home - to the sorted-order buffer of the rank it came from, in that rank's own panel
-// layout (sixteen panels [9 * its tokens][128 halves], 16-byte chunks of a panel row permuted by the row index), which is
-// what its reducer reads.  Half the NVLink bytes of the FP32 return, and 256 contiguous bytes per half warp.
-// One warp per block row, grid-stride; block 256.  The last block raises flag 2 at every peer.
-extern "C" __global__ void __launch_bounds__(256)
-netra_ep_return_rows_f16_sm100(EpPeers peers, EpWindowLayout lay, EpTables* __restrict__ tab, const uint8_t* __restrict__ window,
-                               const __half* __restrict__ blk_rows, uint32_t tokens, uint32_t max_tokens, uint32_t world,
-                               uint32_t rank, uint32_t capacity, uint32_t groups) {
-  __shared__ int s_start[kRouted + 1];
-  for (int i = threadIdx.x; i <= kRouted; i += blockDim.x) s_start[i] = tab->blk_start[i];
-  __syncthreads();
-  const int total = min(s_start[kRouted], (int)capacity);
-  const size_t src_total = (size_t)tab->offsets[groups];          // the panel pitch the down projection used
-  const int lane = threadIdx.x & 31;
-  const uint4* src = reinterpret_cast<const uint4*>(blk_rows);
-  for (int r = blockIdx.x * 8 + (threadIdx.x >> 5); r < total; r += gridDim.x * 8) {
-    int g, dst_row;
-    if (r < (int)tokens) {
-      g = (int)rank;
-      dst_row = (int)tokens * kTopK + r;
-    } else {
-      int lo = 0, hi = kRouted;              // last bucket whose first row is <= r
-      while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (s_start[mid] <= r) lo = mid; else hi = mid;
-      }
-      g = lo % (int)world;
-      dst_row = tab->ret_row[lo] + (r - s_start[lo]);
-    }
-    if (dst_row < 0 || dst_row >= (int)max_tokens * kSlots) continue;
-    const size_t dst_total = (size_t)reinterpret_cast<const int32_t*>(window + lay.matrix)[g * kEpMatrixPitch + kRouted] * kSlots;
-    uint4* dst = reinterpret_cast<uint4*>(peers.win[g] + lay.down);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const uint32_t c = (uint32_t)(i * 32 + lane), panel = c >> 4, j = c & 15u;      // chunk j of the row's panel
-      const uint4 v = src[((size_t)panel * src_total + (size_t)r) * 16 + (j ^ ((uint32_t)r & 15u))];
-      dst[((size_t)panel * dst_total + (size_t)dst_row) * 16 + (j ^ ((uint32_t)dst_row & 15u))] = v;
-    }
-  }
+// The down projection of the prefill contract with the return fused in: every run of FP16 partial rows that one source
+// sent to one expert leaves the epilogue's staging tile as one bulk copy into that source's panels (its own sorted
+// order), over NVLink while the next items are computed; the last CTA raises flag 2 at every peer.
+extern "C" __global__ void __launch_bounds__(kTmThreads, 1)
+netra_ep_down_return_tokmajor_f16_sm100(const __grid_constant__ CUtensorMap tm_w2, const __grid_constant__ CUtensorMap tm_h128,
+                                        const float* h_scale, const float* w2_scale, const int32_t* offsets,
+                                        const __grid_constant__ F16RowReturn ret, uint32_t num_groups, uint32_t w_tiled, uint32_t* status,
+                                        EpPeers peers, EpWindowLayout lay, EpTables* tab, uint32_t world, uint32_t rank) {
+  tokmajor_gemm_body<false, true>(&tm_w2, &tm_h128, h_scale, w2_scale, offsets, nullptr, nullptr, nullptr, nullptr, num_groups, w_tiled,
+                                  status, nullptr, 0, &ret);
   ep_signal_when_last(peers, lay, tab, &tab->done_ret, 2, world, rank);
 }
 
@@ -542,7 +515,7 @@ int ep_launch_stage(netra_ep_layer* L, uint32_t stage, const void* hidden, const
       netra_ep_push_rows_sm100<<<(pairs + tokens + 7) / 8, 256, 0, stream>>>(
           L->peers, L->wl, L->tab, ws + R.a_fp8, (const float*)(ws + R.a_scale), (const int32_t*)(ws + R.perm),
           (const int32_t*)(ws + R.topk_ids), (const int32_t*)(ws + R.offsets), tokens, d.world, d.rank, d.row_capacity, L->row_ptr,
-          L->blk_down, d.max_tokens);
+          L->blk_down, d.max_tokens, ep_f16_call(L, pairs) ? 1u : 0u);
       break;
     case 6:
       // the pairs of all ranks (equal token counts assumed) spread over 256 routed experts decide the GEMM form
@@ -557,13 +530,16 @@ int ep_launch_stage(netra_ep_layer* L, uint32_t stage, const void* hidden, const
       break;
     case 7:
       if (ep_f16_call(L, pairs)) {
-        // the prefill contract: the block's FP16 rows at the speed of the one-GPU kernel, then one pass that sends them home
-        netra_moe_down_tokmajor_f16_sm100<<<L->sm_count, kTmThreads, down_tokmajor_f16_smem_bytes(), stream>>>(
-            L->tm_w2, L->tm_h128, L->blk_hs, d.w2_scale_f32, L->tab->offsets, (void*)L->blk_down, L->e_l + 1, d.weights_tiled,
-            L->tab->status + 1);
-        netra_ep_return_rows_f16_sm100<<<2 * L->sm_count, 256, 0, stream>>>(L->peers, L->wl, L->tab, L->window,
-                                                                            (const __half*)L->blk_down, tokens, d.max_tokens, d.world,
-                                                                            d.rank, d.row_capacity, L->e_l + 1);
+        // the prefill contract: the token-major kernel of the one-GPU layer, its FP16 rows leaving run by run for their senders
+        F16RowReturn ret;
+        memset(&ret, 0, sizeof ret);
+        ret.row_dst = reinterpret_cast<const int2*>(L->row_ptr);
+        ret.tokens_of_rank = reinterpret_cast<const int32_t*>(L->window + L->wl.matrix) + kRouted;
+        ret.tokens_pitch = kEpMatrixPitch;
+        for (uint32_t g = 0; g < d.world; ++g) ret.base[g] = L->peers.win[g] + L->wl.down;
+        netra_ep_down_return_tokmajor_f16_sm100<<<L->sm_count, kTmThreads, down_tokmajor_f16_smem_bytes(), stream>>>(
+            L->tm_w2, L->tm_h128, L->blk_hs, d.w2_scale_f32, L->tab->offsets, ret, L->e_l + 1, d.weights_tiled, L->tab->status + 1,
+            L->peers, L->wl, L->tab, d.world, d.rank);
         break;
       }
       // Across GPUs the swap-AB form is kept for the FP32-row down projection whatever the size: its epilogue stores 128
@@ -704,11 +680,15 @@ int netra_ep_layer_create(const netra_ep_layer_desc_t* desc, netra_ep_layer_t** 
       e = cudaFuncSetAttribute(netra_ep_gate_up_tokmajor_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, gate_up_tokmajor_smem_bytes());
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(netra_ep_down_return_tokmajor_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, down_tokmajor_smem_bytes());
-    cudaFuncAttributes attr, attr_gate_up;
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(netra_ep_down_return_tokmajor_f16_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, down_tokmajor_f16_smem_bytes());
+    cudaFuncAttributes attr, attr_gate_up, attr_f16;
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&attr_f16, netra_ep_down_return_tokmajor_f16_sm100);
     if (e == cudaSuccess) e = cudaFuncGetAttributes(&attr, netra_ep_down_return_tokmajor_sm100);
     if (e == cudaSuccess) e = cudaFuncGetAttributes(&attr_gate_up, netra_ep_gate_up_tokmajor_sm100);
     if (e != cudaSuccess) { netra_moe_layer_destroy(L->route); delete L; return fail_cuda("cudaFuncSetAttribute(down_return)", e); }
-    L->tokmajor_ok = g_tokmajor_ok[L->route->device] && attr.numRegs == kTmRegsLaunch && attr_gate_up.numRegs == kTmRegsLaunch;
+    L->tokmajor_ok = g_tokmajor_ok[L->route->device] && attr.numRegs == kTmRegsLaunch && attr_gate_up.numRegs == kTmRegsLaunch &&
+                     attr_f16.numRegs == kTmRegsLaunch;
   }
   const uint64_t g = L->e_l + 1, rows = desc->row_capacity;
   if (desc->weights_tiled) {
@@ -740,7 +720,7 @@ uint32_t netra_ep_layer_stage_count(void) { return kEpStageCount; }
 uint32_t netra_ep_layer_launch_count(const netra_ep_layer_t* L, uint32_t tokens) {
   if (!L) return 0;
   // a whole call runs publish and plan as one launch; above 1,024 tokens the sort is three launches
-  if (tokens > (uint32_t)kSortSmallMaxRows) return kEpStageCount - 1 + 2 + (ep_f16_call(L, tokens * kTopK) ? 1 : 0);   // + the FP16 return pass
+  if (tokens > (uint32_t)kSortSmallMaxRows) return kEpStageCount - 1 + 2;
   return kEpStageCount - 1 - (L->route->front_mode == 1 ? 2 : 0);                       // router, top-k and sort as one launch
 }
 

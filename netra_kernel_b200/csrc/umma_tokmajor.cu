@@ -107,6 +107,16 @@ __device__ __forceinline__ uint32_t make_idesc_mxfp4_b(uint32_t b_scale_byte) {
   return (b_scale_byte << 4) | (5u << 10) | ((256u >> 3) << 17) | (1u << 23) | ((uint32_t)(128 >> 4) << 24);
 }
 
+// Where the FP16 partial rows of a block go when they are not kept in this GPU's panels (expert parallelism): block row r
+// belongs to sorted row row_dst[r].y of rank row_dst[r].x (x < 0: nowhere), whose panels start at base[x] and hold
+// nine rows per token of that rank (tokens_of_rank[x * tokens_pitch]).
+struct F16RowReturn {
+  const int2* row_dst;
+  const int32_t* tokens_of_rank;
+  uint32_t tokens_pitch;
+  uint8_t* base[16];
+};
+
 // kGatherX (gate_up only): the item's token rows are not read from an expert-sorted copy but gathered from token order:
 // sorted position p holds token-order row tok_row_base + (perm[p] >> 3) (positions from tok_row_base on are token-order
 // rows already: the shared expert).  tm_x128 then is a map with a one-row box over the same buffer, x_scale its scales.
@@ -116,7 +126,8 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
                                                    const int32_t* __restrict__ offsets, uint8_t* __restrict__ h_fp8,
                                                    float* __restrict__ h_scale, float* __restrict__ down,
                                                    float* const* __restrict__ row_ptr, uint32_t num_groups, uint32_t w_tiled,
-                                                   uint32_t* status, const int32_t* __restrict__ perm = nullptr, uint32_t tok_row_base = 0) {
+                                                   uint32_t* status, const int32_t* __restrict__ perm = nullptr, uint32_t tok_row_base = 0,
+                                                   const F16RowReturn* ret = nullptr) {
   static_assert(!(kGateUp && kF16Out), "FP16 partial rows are an output format of the down projection");
   static_assert(kGateUp || !kGatherX, "only the gate_up projection reads token rows");
   using C = TmCfg<kGateUp, kF16Out, kFp4>;
@@ -533,9 +544,30 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
         // 3,500 of an item's 8,700 cycles), not per byte.
         uint8_t* tile = out_stage + (size_t)wg * (C::kLanes * C::kOutRowBytes);
         const bool elected = quad == 0 && lane == 0;
-        if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous item's copy has read the tile
+        // the copies of the previous item have read the tile (with a return table any thread may have issued one)
+        if (elected || ret != nullptr) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         group_barrier(wg);
-        const uint32_t key = (uint32_t)(w.row0 + r) & 15u;
+        // With a return table the row goes to another rank's panels (or this rank's own): it is staged with the
+        // permutation of its destination row, and every run of rows that lands on consecutive rows of one rank - the
+        // rows one source sent to one expert - leaves as one bulk copy, over NVLink while the next items are computed.
+        // A run starts where the destination is not the previous row's plus one; its length is the distance to the next
+        // start or to the first row without a destination, found from the warps' ballots (four words per warpgroup in
+        // the area the amax exchange of gate_up uses, which is idle here).
+        uint32_t* brk_masks = red + wg * 4;
+        int2 mine = make_int2(-1, -1);
+        bool head = false;
+        uint32_t my_brk = 0;
+        if (ret != nullptr) {
+          if (live) mine = ret->row_dst[row];
+          int2 prev;
+          prev.x = __shfl_up_sync(0xffffffffu, mine.x, 1);
+          prev.y = __shfl_up_sync(0xffffffffu, mine.y, 1);
+          if (lane == 0) prev = (r > 0 && live) ? ret->row_dst[row - 1] : make_int2(-1, -1);
+          head = mine.x >= 0 && (r == 0 || prev.x != mine.x || prev.y + 1 != mine.y);
+          my_brk = __ballot_sync(0xffffffffu, head || mine.x < 0);
+          if (lane == 0) brk_masks[quad] = my_brk;
+        }
+        const uint32_t key = (ret != nullptr ? (uint32_t)max(mine.y, 0) : (uint32_t)(w.row0 + r)) & 15u;
         uint8_t* my_row = tile + (size_t)r * C::kOutRowBytes;
 #pragma unroll
         for (int q = 0; q < 16; ++q) {
@@ -550,11 +582,33 @@ __device__ __forceinline__ void tokmajor_gemm_body(const CUtensorMap* tm_w, cons
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         group_barrier(wg);
-        if (elected) {
-          __half* gdst = reinterpret_cast<__half*>(down) + ((size_t)(w.ntile * 2 + wg) * (size_t)total_rows + (size_t)w.row0) * kTileRows;
-          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(tile)),
-                       "r"((uint32_t)w.m_valid * (uint32_t)C::kOutRowBytes) : "memory");
-          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        if (ret == nullptr) {
+          if (elected) {
+            __half* gdst = reinterpret_cast<__half*>(down) + ((size_t)(w.ntile * 2 + wg) * (size_t)total_rows + (size_t)w.row0) * kTileRows;
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(tile)),
+                         "r"((uint32_t)w.m_valid * (uint32_t)C::kOutRowBytes) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        } else {
+          if (head) {
+            int len;
+            const uint32_t above = lane < 31 ? my_brk >> (lane + 1) : 0u;
+            if (above != 0u) {
+              len = __ffs(above);
+            } else {
+              len = 32 - lane;
+              for (int q2 = quad + 1; q2 < 4; ++q2) {
+                const uint32_t m = brk_masks[q2];
+                if (m != 0u) { len += __ffs(m) - 1; break; }
+                len += 32;
+              }
+            }
+            const size_t dst_total = (size_t)ret->tokens_of_rank[(size_t)mine.x * ret->tokens_pitch] * kSlots;
+            uint8_t* gdst = ret->base[mine.x] + ((size_t)(w.ntile * 2 + wg) * dst_total + (size_t)mine.y) * (size_t)C::kOutRowBytes;
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(my_row)),
+                         "r"((uint32_t)len * (uint32_t)C::kOutRowBytes) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
         }
       } else {
         if (live) {
