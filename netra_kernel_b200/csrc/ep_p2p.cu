@@ -32,6 +32,7 @@ namespace netra {
 constexpr int kEpMaxRanks = 16;
 constexpr int kEpMatrixPitch = 264;          // ints per count row: 256 counts, [256] = tokens, rest spare
 constexpr int kEpFlagPitch = 32;             // uint32 per phase
+constexpr int kEpTableBlocks = 296;          // blocks of the push launch that also build the return table
 
 struct EpPeers {
   uint8_t* win[kEpMaxRanks];
@@ -258,41 +259,58 @@ __device__ __forceinline__ void ep_build_return_table(const EpPeers& peers, cons
 
 // push: sorted row i (i < pairs) of this rank -> its expert-major row in the owner's block;
 // rows pairs .. pairs + tokens - 1 are the rank's own tokens -> rows [0, tokens) of its own block.
-// a_fp8 / a_scale hold the per-token quantised rows at row (pairs + t).  One warp per row.
-// grid ceil((pairs + tokens) / 8), block 256.
+// a_fp8 / a_scale hold the per-token quantised rows at row (pairs + t).  One warp per two rows (i and i + half): the two
+// chains of dependent index loads (perm -> ids -> push_base / offsets) run side by side, and the sixteen 16-byte loads of
+// both rows are in flight before the first store.  The first blocks also build the return table.
+// grid ceil(ceil((pairs + tokens) / 2) / 8), block 256.
 extern "C" __global__ void __launch_bounds__(256)
 netra_ep_push_rows_sm100(EpPeers peers, EpWindowLayout lay, EpTables* __restrict__ tab, const uint8_t* __restrict__ a_fp8,
                          const float* __restrict__ a_scale, const int32_t* __restrict__ perm, const int32_t* __restrict__ ids9,
                          const int32_t* __restrict__ sorted_offsets, uint32_t tokens, uint32_t world, uint32_t rank,
                          uint32_t capacity, float** __restrict__ row_ptr, float* __restrict__ blk_down, uint32_t max_tokens,
                          uint32_t table_as_pairs) {
-  ep_build_return_table(peers, lay, tab, row_ptr, blk_down, tokens, max_tokens, world, rank, capacity, table_as_pairs);
+  if (blockIdx.x < kEpTableBlocks)
+    ep_build_return_table(peers, lay, tab, row_ptr, blk_down, tokens, max_tokens, world, rank, capacity, table_as_pairs);
   const int pairs = (int)tokens * kTopK;
-  const int i = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int rows = pairs + (int)tokens, half = (rows + 1) / 2;
+  const int i0 = blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
-  if (i < pairs + (int)tokens) {
-    int t, g, dst_row;
-    if (i < pairs) {
-      const int pair = perm[i];
-      t = pair >> 3;
-      const int e = ids9[t * kSlots + (pair & 7)];
-      g = e / (kRouted / (int)world);
-      dst_row = tab->push_base[e] + (i - sorted_offsets[e]);
-    } else {
-      t = i - pairs;
-      g = (int)rank;
-      dst_row = t;
-    }
-    if (dst_row >= 0 && dst_row < (int)capacity) {
-      const size_t src_row = (size_t)pairs + t;
-      const uint4* src = reinterpret_cast<const uint4*>(a_fp8 + src_row * kHidden);
-      uint4* dst = reinterpret_cast<uint4*>(peers.win[g] + lay.blk_a + (size_t)dst_row * kHidden);
+  if (i0 < half) {
+    int t[2], g[2], dst_row[2];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) dst[c * 32 + lane] = src[c * 32 + lane];
-      if (lane < 4)
-        reinterpret_cast<uint4*>(peers.win[g] + lay.blk_as + (size_t)dst_row * (kHiddenBlocks * 4))[lane] =
-            reinterpret_cast<const uint4*>(a_scale + src_row * kHiddenBlocks)[lane];
+    for (int k = 0; k < 2; ++k) {
+      const int i = i0 + k * half;
+      t[k] = 0; g[k] = (int)rank; dst_row[k] = -1;
+      if (i < pairs) {
+        const int pair = perm[i];
+        t[k] = pair >> 3;
+        const int e = ids9[t[k] * kSlots + (pair & 7)];
+        g[k] = e / (kRouted / (int)world);
+        dst_row[k] = tab->push_base[e] + (i - sorted_offsets[e]);
+      } else if (i < rows) {
+        t[k] = i - pairs;
+        dst_row[k] = t[k];
+      }
+      if (dst_row[k] >= (int)capacity) dst_row[k] = -1;
     }
+    uint4 v[2][4], sc[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k)
+      if (dst_row[k] >= 0) {
+        const size_t src_row = (size_t)pairs + t[k];
+        const uint4* src = reinterpret_cast<const uint4*>(a_fp8 + src_row * kHidden);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) v[k][c] = src[c * 32 + lane];
+        if (lane < 4) sc[k] = reinterpret_cast<const uint4*>(a_scale + src_row * kHiddenBlocks)[lane];
+      }
+#pragma unroll
+    for (int k = 0; k < 2; ++k)
+      if (dst_row[k] >= 0) {
+        uint4* dst = reinterpret_cast<uint4*>(peers.win[g[k]] + lay.blk_a + (size_t)dst_row[k] * kHidden);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) dst[c * 32 + lane] = v[k][c];
+        if (lane < 4) reinterpret_cast<uint4*>(peers.win[g[k]] + lay.blk_as + (size_t)dst_row[k] * (kHiddenBlocks * 4))[lane] = sc[k];
+      }
   }
   ep_signal_when_last(peers, lay, tab, &tab->done_push, 1, world, rank);
 }
@@ -308,7 +326,8 @@ __device__ __forceinline__ void ep_build_return_table(const EpPeers& peers, cons
   for (int i = threadIdx.x; i <= kRouted; i += blockDim.x) s_start[i] = tab->blk_start[i];
   __syncthreads();
   const int total = min(s_start[kRouted], (int)capacity);
-  for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < total; r += gridDim.x * blockDim.x) {
+  const int table_blocks = min((int)gridDim.x, kEpTableBlocks);
+  for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < total; r += table_blocks * blockDim.x) {
     int g, dst_row;
     if (r < (int)tokens) {
       g = (int)rank;
@@ -512,7 +531,7 @@ int ep_launch_stage(netra_ep_layer* L, uint32_t stage, const void* hidden, const
       netra_ep_plan_sm100<<<1, 1024, 0, stream>>>(L->window, L->wl, L->tab, d.world, d.rank, d.row_capacity, d.wait_timeout_ns);
       break;
     case 5:
-      netra_ep_push_rows_sm100<<<(pairs + tokens + 7) / 8, 256, 0, stream>>>(
+      netra_ep_push_rows_sm100<<<((pairs + tokens + 1) / 2 + 7) / 8, 256, 0, stream>>>(
           L->peers, L->wl, L->tab, ws + R.a_fp8, (const float*)(ws + R.a_scale), (const int32_t*)(ws + R.perm),
           (const int32_t*)(ws + R.topk_ids), (const int32_t*)(ws + R.offsets), tokens, d.world, d.rank, d.row_capacity, L->row_ptr,
           L->blk_down, d.max_tokens, ep_f16_call(L, pairs) ? 1u : 0u);
